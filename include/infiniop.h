@@ -1,0 +1,220 @@
+/*
+ * infiniop.h - C ABI of the B200 (sm_100a) backend for the InfiniOperators
+ * decode hot path.
+ *
+ * The library built from operators_b200/csrc exports exactly the symbols the
+ * reference's `libinfiniop.so` exports for these operators, with identical
+ * argument lists, enum values and struct layouts, so the reference's ctypes
+ * wrapper (operatorspy/liboperators.py) and C callers load it unchanged as the
+ * `DevNvGpu` device.  Every declaration cites the reference header it
+ * replaces (paths relative to the reference project root).
+ *
+ * Call pattern ("3+1 stages", reference README.md:9-40):
+ *   infiniopCreate<Op>Descriptor -> infiniopGet<Op>WorkspaceSize ->
+ *   infiniop<Op> (asynchronous on `stream`) -> infiniopDestroy<Op>Descriptor.
+ * All data pointers are device pointers on the handle's GPU; `stream` is a
+ * cudaStream_t (NULL = legacy default stream).  Nothing allocates device
+ * memory inside a compute call; no call synchronises the device.
+ */
+#ifndef INFINIOP_B200_H
+#define INFINIOP_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+#define INFINIOP_C extern "C"
+#else
+#define INFINIOP_C
+#endif
+#if defined(__GNUC__)
+#define INFINIOP_EXPORT __attribute__((visibility("default")))
+#else
+#define INFINIOP_EXPORT
+#endif
+#define INFINIOP_API INFINIOP_C INFINIOP_EXPORT
+
+/* Names the reference headers use for the same two macros (include/export.h:4-16). */
+#ifndef __export
+#define __export INFINIOP_EXPORT
+#endif
+#ifndef __C
+#define __C INFINIOP_C
+#endif
+
+/* ---- status codes: include/status.h:4-14 ---------------------------------- */
+typedef enum {
+    STATUS_SUCCESS = 0,
+    STATUS_EXECUTION_FAILED = 1,
+    STATUS_BAD_PARAM = 2,
+    STATUS_BAD_TENSOR_DTYPE = 3,
+    STATUS_BAD_TENSOR_SHAPE = 4,
+    STATUS_BAD_TENSOR_STRIDES = 5,
+    STATUS_MEMORY_NOT_ALLOCATED = 6,
+    STATUS_INSUFFICIENT_WORKSPACE = 7,
+    STATUS_BAD_DEVICE = 8,
+} infiniopStatus_t;
+
+/* ---- device enum: include/device.h:4-9.  Only DevNvGpu is served here. ---- */
+enum DeviceEnum {
+    DevCpu = 0,
+    DevNvGpu = 1,
+    DevCambriconMlu = 2,
+    DevAscendNpu = 3,
+};
+typedef enum DeviceEnum Device;
+
+/* ---- data layout: include/data_type.h:4-47 -------------------------------- *
+ * A 32-bit bit-field passed BY VALUE; two layouts are equal when their 32-bit
+ * images are equal.  Little-endian images: F16 0x050A0501, BF16 0x08070501,
+ * F32 0x08170901, U64 0x00401001.
+ */
+typedef struct DataLayout {
+    unsigned short packed : 8, sign : 1, size : 7, mantissa : 8, exponent : 8;
+} DataLayout;
+typedef struct DataLayout DT;
+
+#define INFINIOP_DT(p, s, z, m, e) {p, s, z, m, e}
+static const DataLayout I8 = INFINIOP_DT(1, 1, 1, 7, 0), I16 = INFINIOP_DT(1, 1, 2, 15, 0),
+                        I32 = INFINIOP_DT(1, 1, 4, 31, 0), I64 = INFINIOP_DT(1, 1, 8, 63, 0),
+                        U8 = INFINIOP_DT(1, 0, 1, 8, 0), U16 = INFINIOP_DT(1, 0, 2, 16, 0),
+                        U32 = INFINIOP_DT(1, 0, 4, 32, 0), U64 = INFINIOP_DT(1, 0, 8, 64, 0),
+                        F16 = INFINIOP_DT(1, 1, 2, 10, 5), BF16 = INFINIOP_DT(1, 1, 2, 7, 8),
+                        F32 = INFINIOP_DT(1, 1, 4, 23, 8), F64 = INFINIOP_DT(1, 1, 8, 52, 11);
+
+/* ---- tensor descriptor: include/tensor.h:7-18 ----------------------------- *
+ * Layout is visible to callers (the Python wrapper mirrors it field by field).
+ * Strides are in ELEMENTS and may describe a view into a larger buffer.
+ */
+struct TensorDescriptor {
+    DT dt;
+    uint64_t ndim;
+    uint64_t *shape;
+    int64_t *strides;
+};
+typedef struct TensorDescriptor *infiniopTensorDescriptor_t;
+
+/* include/tensor/tensor_descriptor.h:8-10.  Copies shape and strides;
+ * strides == NULL means contiguous row-major; ndim == 0 is legal. */
+INFINIOP_API infiniopStatus_t infiniopCreateTensorDescriptor(infiniopTensorDescriptor_t *desc_ptr, uint64_t ndim,
+                                                             uint64_t const *shape, int64_t const *strides,
+                                                             DataLayout datatype);
+INFINIOP_API infiniopStatus_t infiniopDestroyTensorDescriptor(infiniopTensorDescriptor_t desc);
+
+/* ---- handle: include/handle.h:6-10, include/handle/handle_export.h:8-10 --- *
+ * The object behind the pointer starts with `Device device`.  Errors:
+ * NULL handle_ptr -> MEMORY_NOT_ALLOCATED, device_id < 0 -> BAD_PARAM, a device
+ * other than DevNvGpu or a device_id beyond the visible GPUs -> BAD_DEVICE. */
+typedef struct HandleStruct {
+    Device device;
+} HandleStruct;
+typedef HandleStruct *infiniopHandle_t;
+
+INFINIOP_API infiniopStatus_t infiniopCreateHandle(infiniopHandle_t *handle_ptr, Device device, int device_id);
+INFINIOP_API infiniopStatus_t infiniopDestroyHandle(infiniopHandle_t handle);
+
+/* Every operator descriptor starts with `Device device`
+ * (e.g. include/ops/rms_norm/rms_norm.h:7-11); the rest is private. */
+
+/* ---- RMSNorm: include/ops/rms_norm/rms_norm.h:13-26 ----------------------- *
+ * y[n,d] = x[n,d] * rsqrt(mean(x^2) + epsilon) * w[d]; y, x fp16 with unit
+ * column stride and free row strides, w fp16 or fp32. */
+typedef struct RMSNormDescriptor {
+    Device device;
+} RMSNormDescriptor;
+typedef RMSNormDescriptor *infiniopRMSNormDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateRMSNormDescriptor(infiniopHandle_t handle,
+                                                              infiniopRMSNormDescriptor_t *desc_ptr,
+                                                              infiniopTensorDescriptor_t y_desc,
+                                                              infiniopTensorDescriptor_t x_desc,
+                                                              infiniopTensorDescriptor_t w_desc, float epsilon);
+INFINIOP_API infiniopStatus_t infiniopGetRMSNormWorkspaceSize(infiniopRMSNormDescriptor_t desc, uint64_t *size);
+INFINIOP_API infiniopStatus_t infiniopRMSNorm(infiniopRMSNormDescriptor_t desc, void *workspace,
+                                              uint64_t workspace_size, void *y, void const *x, void const *w,
+                                              void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyRMSNormDescriptor(infiniopRMSNormDescriptor_t desc);
+
+/* ---- RoPE: include/ops/rotary_embedding/rotary_embedding.h:7-30 ----------- *
+ * In place on t[tokens, heads, dh] fp16 (unit last stride), rotating adjacent
+ * pairs with caller-supplied fp32 sin/cos tables [max_pos, dh] indexed by the
+ * u64 position ids.  A NULL data pointer returns STATUS_BAD_PARAM. */
+typedef struct RoPEDescriptor RoPEDescriptor;
+typedef RoPEDescriptor *infiniopRoPEDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateRoPEDescriptor(infiniopHandle_t handle, infiniopRoPEDescriptor_t *desc_ptr,
+                                                           infiniopTensorDescriptor_t t,
+                                                           infiniopTensorDescriptor_t pos_ids,
+                                                           infiniopTensorDescriptor_t sin_table,
+                                                           infiniopTensorDescriptor_t cos_table);
+INFINIOP_API infiniopStatus_t infiniopGetRoPEWorkspaceSize(infiniopRoPEDescriptor_t desc, uint64_t *size);
+INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *workspace, uint64_t workspace_size,
+                                           void *t, void const *pos_ids, void const *sin_table,
+                                           void const *cos_table, void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyRoPEDescriptor(infiniopRoPEDescriptor_t desc);
+
+/* ---- SwiGLU: include/ops/swiglu/swiglu.h:7-25 ----------------------------- *
+ * c = a * silu(b), 2-D fp16, unit column stride, free row strides; c may alias
+ * a or b.  No workspace entry point exists for this operator. */
+typedef struct SwiGLUDescriptor {
+    Device device;
+} SwiGLUDescriptor;
+typedef SwiGLUDescriptor *infiniopSwiGLUDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateSwiGLUDescriptor(infiniopHandle_t handle,
+                                                             infiniopSwiGLUDescriptor_t *desc_ptr,
+                                                             infiniopTensorDescriptor_t c_desc,
+                                                             infiniopTensorDescriptor_t a_desc,
+                                                             infiniopTensorDescriptor_t b_desc);
+INFINIOP_API infiniopStatus_t infiniopSwiGLU(infiniopSwiGLUDescriptor_t desc, void *c, void const *a, void const *b,
+                                             void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroySwiGLUDescriptor(infiniopSwiGLUDescriptor_t desc);
+
+/* ---- Add: include/ops/add/add.h:7-25 -------------------------------------- *
+ * c = a + b with numpy-style broadcasting of a and b to c's shape; contiguous
+ * fp16 or fp32 tensors; c may alias a or b when nothing is broadcast. */
+typedef struct AddDescriptor {
+    Device device;
+} AddDescriptor;
+typedef AddDescriptor *infiniopAddDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateAddDescriptor(infiniopHandle_t handle, infiniopAddDescriptor_t *desc_ptr,
+                                                          infiniopTensorDescriptor_t c, infiniopTensorDescriptor_t a,
+                                                          infiniopTensorDescriptor_t b);
+INFINIOP_API infiniopStatus_t infiniopAdd(infiniopAddDescriptor_t desc, void *c, void const *a, void const *b,
+                                          void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyAddDescriptor(infiniopAddDescriptor_t desc);
+
+/* ---- causal softmax: include/ops/causal_softmax/causal_softmax.h:7-25 ----- *
+ * In place on fp16 [.., seq_len, total_seq_len] (2-D or 3-D, unit last
+ * stride): row i keeps columns j <= total_seq_len - seq_len + i, the rest
+ * become exact zeros. */
+typedef struct CausalSoftmaxDescriptor {
+    Device device;
+} CausalSoftmaxDescriptor;
+typedef CausalSoftmaxDescriptor *infiniopCausalSoftmaxDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateCausalSoftmaxDescriptor(infiniopHandle_t handle,
+                                                                    infiniopCausalSoftmaxDescriptor_t *desc_ptr,
+                                                                    infiniopTensorDescriptor_t y_desc);
+INFINIOP_API infiniopStatus_t infiniopGetCausalSoftmaxWorkspaceSize(infiniopCausalSoftmaxDescriptor_t desc,
+                                                                    uint64_t *size);
+INFINIOP_API infiniopStatus_t infiniopCausalSoftmax(infiniopCausalSoftmaxDescriptor_t desc, void *workspace,
+                                                    uint64_t workspace_size, void *data, void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyCausalSoftmaxDescriptor(infiniopCausalSoftmaxDescriptor_t desc);
+
+/* ---- random sample: include/ops/random_sample/random_sample.h:7-28 -------- *
+ * probs: 1-D fp16 logits [voc]; result: u64 [1].  topp > 0 && topk > 1 selects
+ * temperature / top-k / top-p sampling driven by the uniform draw random_val,
+ * otherwise argmax.  The sampled index follows the reference's CPU backend. */
+typedef struct RandomSampleDescriptor {
+    Device device;
+} RandomSampleDescriptor;
+typedef RandomSampleDescriptor *infiniopRandomSampleDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateRandomSampleDescriptor(infiniopHandle_t handle,
+                                                                   infiniopRandomSampleDescriptor_t *desc_ptr,
+                                                                   infiniopTensorDescriptor_t result,
+                                                                   infiniopTensorDescriptor_t probs);
+INFINIOP_API infiniopStatus_t infiniopGetRandomSampleWorkspaceSize(infiniopRandomSampleDescriptor_t desc,
+                                                                   uint64_t *size);
+INFINIOP_API infiniopStatus_t infiniopRandomSample(infiniopRandomSampleDescriptor_t desc, void *workspace,
+                                                   uint64_t workspace_size, void *result, void const *probs,
+                                                   float random_val, float topp, int topk, float temperature,
+                                                   void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyRandomSampleDescriptor(infiniopRandomSampleDescriptor_t desc);
+
+#endif /* INFINIOP_B200_H */

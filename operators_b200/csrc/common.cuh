@@ -1,0 +1,136 @@
+// Shared device/host toolkit of the sm_100a backend: descriptor helpers, the
+// reference's fp16 rounding rule, 128-bit streaming accesses, warp / CTA
+// reductions and an exact 32-bit divider for flat-index -> (row, column) math.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/infiniop.h"
+#include "fastdiv.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------- host side --
+
+// 32-bit image of a DataLayout; the reference compares layouts the same way
+// (reference src/ops/utils.h:62-72).
+static inline uint32_t dt_bits(DataLayout d) {
+    union {
+        DataLayout l;
+        uint32_t u;
+    } p;
+    p.u = 0;
+    p.l = d;
+    return p.u;
+}
+static inline bool dt_eq(DataLayout a, DataLayout b) { return dt_bits(a) == dt_bits(b); }
+
+// Handle object behind infiniopHandle_t: first field is the device enum, as the
+// reference's CudaContext (reference src/devices/cuda/cuda_handle.h:12-20).
+struct Handle {
+    Device device;
+    int device_id;
+    int sm_count;
+    int max_smem_optin;
+};
+
+// RAII "run on this device" guard used by every compute entry point: the
+// reference calls cudaSetDevice(desc->device_id) in most of them
+// (e.g. reference src/ops/rms_norm/cuda/rms_norm.cu:164) and never restores it;
+// restoring keeps multi-GPU hosts (one handle per GPU in one thread) sane.
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) {
+            switched = cudaSetDevice(dev) == cudaSuccess;
+        }
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+// Launch errors are reported like the reference reports CUDA API failures
+// (reference src/devices/cuda/common_cuda.h:10-32): a line on stderr and a
+// status code; nothing throws across the C ABI.
+static inline infiniopStatus_t check_launch(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fprintf(stderr, "infiniop[b200]: %s launch failed: %s\n", what, cudaGetErrorString(e));
+        return STATUS_EXECUTION_FAILED;
+    }
+    return STATUS_SUCCESS;
+}
+
+static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline bool aligned4(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
+
+// -------------------------------------------------------------- device side --
+
+// fp32 -> fp16 with the reference CPU backend's rule (reference
+// src/devices/cpu/common_cpu.cc:41-64): mantissa TRUNCATED, |x| < 2^-24 to
+// signed zero, NaN -> sign|0x7E00, and for finite |x| >= 65536 the raw
+// `sign | ((e+15) << 10) | (mantissa >> 13)` with the exponent field spilling
+// into bit 15.  cvt.rz agrees with that rule everywhere below 65536, so the
+// integer path is only taken for the out-of-range tail and NaN.
+__device__ __forceinline__ uint16_t f32_to_f16_ref(float v) {
+    uint32_t u = __float_as_uint(v);
+    uint32_t au = u & 0x7FFFFFFFu;
+    if (au < 0x47800000u) {// |v| < 65536
+        return __half_as_ushort(__float2half_rz(v));
+    }
+    uint32_t sign = (u >> 16) & 0x8000u;
+    int32_t e = (int32_t) ((u >> 23) & 0xFFu) - 127;
+    uint32_t man = u & 0x7FFFFFu;
+    if (e >= 31) {
+        return (uint16_t) ((e == 128 && man != 0) ? (sign | 0x7E00u) : (sign | 0x7C00u));
+    }
+    return (uint16_t) (sign | ((uint32_t) (e + 15) << 10) | (man >> 13));
+}
+
+__device__ __forceinline__ float f16_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+__device__ __forceinline__ uint32_t pack2_ref(float lo, float hi) {
+    return (uint32_t) f32_to_f16_ref(lo) | ((uint32_t) f32_to_f16_ref(hi) << 16);
+}
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&w));
+}
+
+// 128-bit accesses with the streaming (evict-first) policy.  Loads are
+// ordinary coherent loads, not the read-only path, so operators whose output
+// aliases an input (in-place SwiGLU / Add / RoPE / softmax) stay well defined.
+__device__ __forceinline__ uint4 ld_stream(const void *p) { return __ldcs(reinterpret_cast<const uint4 *>(p)); }
+__device__ __forceinline__ void st_stream(void *p, uint4 v) { __stcs(reinterpret_cast<uint4 *>(p), v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// CTA-wide reduction for kernels that give one whole CTA to a row.  `slot` is
+// 32 floats of shared memory; all threads of the CTA must call it.
+template<bool IS_MAX>
+__device__ __forceinline__ float cta_reduce(float v, float *slot) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    if (nwarps == 1) return v;
+    if (lane == 0) slot[warp] = v;
+    __syncthreads();
+    float r = slot[0];
+    for (int w = 1; w < nwarps; ++w) r = IS_MAX ? fmaxf(r, slot[w]) : r + slot[w];
+    __syncthreads();
+    return r;
+}
+
+}// namespace b200

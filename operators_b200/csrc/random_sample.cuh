@@ -1,0 +1,33 @@
+// Launch interface of the random-sample kernel, shared by the reference-shaped
+// single-row entry point and the batched extension.
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kDebugStride = 1 + 2 * 64;// floats per row of the optional trace buffer
+
+struct RandomSampleArgs {
+    const uint16_t *logits; // fp16 rows
+    int64_t logits_stride;  // elements between rows
+    uint16_t *work;         // per-row working copy of the row as 16-bit keys
+    int64_t work_pitch;     // elements between working rows (multiple of 256)
+    uint64_t *result;       // one index per row
+    int64_t result_stride;
+    const float *random_vals;// device array of per-row uniform draws, or NULL to use random_val
+    float random_val;
+    float topp;
+    int topk;
+    float temperature;
+    int voc;
+    // Optional device trace per row: [0] = softmax denominator S, [1..64] = the
+    // top-k indices (bit patterns), [65..128] = their truncated probabilities.
+    float *debug;
+};
+
+uint64_t random_sample_work_pitch(int voc);
+uint64_t random_sample_workspace_bytes(int voc, int rows);
+infiniopStatus_t random_sample_launch(const RandomSampleArgs &args, int rows, void *workspace, uint64_t workspace_size,
+                                      cudaStream_t stream);
+
+}// namespace b200

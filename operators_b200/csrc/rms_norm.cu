@@ -1,0 +1,264 @@
+// RMSNorm: y[n,d] = x[n,d] * rsqrt(mean(x^2) + eps) * w[d], fp16 data, fp16 or
+// fp32 weight.
+//
+// Replaces reference src/ops/rms_norm/cuda/rms_norm.cu:8-173 and
+// src/ops/rms_norm/cuda/rms_norm.cc:5-41 behind include/ops/rms_norm/rms_norm.h.
+// Arithmetic follows the CPU backend (src/ops/rms_norm/cpu/rms_norm_cpu.cc:
+// 63-85): fp32 sum of squares, the scale k = (ss/d + eps)^-1/2 and the product
+// k * x * w evaluated in DOUBLE, one rounding to fp32, then the reference's
+// truncating fp32 -> fp16 conversion.  The only departure is the order of the
+// fp32 sum of squares (tree instead of sequential).
+//
+// HBM-bound, 4 bytes per element.  A row lives in registers between the
+// reduction and the scaling pass, so x is read from HBM exactly once: each
+// thread holds up to 8 x 128-bit vectors, a row is owned either by one warp
+// (shuffle reduction only) or by one CTA (shuffles + one shared-memory step).
+// Rows that are not 16-byte aligned, or longer than 64 Ki elements, take the
+// two-pass scalar kernel.
+#include "common.cuh"
+
+#include <new>
+
+using namespace b200;
+
+namespace {
+
+struct RMSNormDesc {
+    Device device;
+    int device_id;
+    int sm_count;
+    uint64_t n, d;
+    int64_t stride_y, stride_x;
+    bool w_f16;
+    float epsilon;
+};
+
+__device__ __forceinline__ double h2d(uint16_t h) {
+    double r;
+    asm("cvt.f64.f16 %0, %1;" : "=d"(r) : "h"(h));
+    return r;
+}
+
+// (ss / d + eps) ^ -1/2 in double, from the fp32 sum of squares.
+__device__ __forceinline__ double rms_scale(float ss, uint64_t d, float eps) {
+    const float m = __fadd_rn(__fdiv_rn(ss, (float) d), eps);
+    return rsqrt((double) m);
+}
+
+__device__ __forceinline__ uint16_t rms_out(double k, uint16_t x, double w) {
+    return f32_to_f16_ref(__double2float_rn(__dmul_rn(__dmul_rn(k, h2d(x)), w)));
+}
+
+// VPT vectors (8 halves each) per thread; CTA_ROW: the whole CTA owns one row,
+// otherwise each warp owns one row.
+template<int VPT, bool W_F16, bool CTA_ROW>
+__global__ void rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs,
+                                     uint64_t d, int64_t stride_y, int64_t stride_x, float eps) {
+    __shared__ float red[32];
+    const int lane = threadIdx.x & 31;
+    const uint32_t group = CTA_ROW ? blockDim.x : 32;
+    const uint32_t t = CTA_ROW ? threadIdx.x : lane;
+    const uint64_t rows_per_cta = CTA_ROW ? 1 : (blockDim.x >> 5);
+    const uint64_t row0 = (uint64_t) blockIdx.x * rows_per_cta + (CTA_ROW ? 0 : (threadIdx.x >> 5));
+    const uint64_t row_step = (uint64_t) gridDim.x * rows_per_cta;
+
+    // CTA_ROW: every thread of the CTA sees the same row, so the CTA-wide
+    // reduction below is reached uniformly; warp rows only use shuffles.
+    for (uint64_t row = row0; row < n; row += row_step) {
+        const uint16_t *xr = x + (int64_t) row * stride_x;
+        uint4 v[VPT];
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+            const uint32_t j = t + u * group;
+            if (j < vecs) v[u] = ld_stream(xr + (uint64_t) j * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+            const uint32_t j = t + u * group;
+            if (j < vecs) {
+                const uint32_t *p = reinterpret_cast<const uint32_t *>(&v[u]);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = unpack2(p[k]);
+                    ss = fmaf(f.x, f.x, ss);
+                    ss = fmaf(f.y, f.y, ss);
+                }
+            }
+        }
+        ss = CTA_ROW ? cta_reduce<false>(ss, red) : warp_sum(ss);
+        const double k = rms_scale(ss, d, eps);
+        uint16_t *yr = y + (int64_t) row * stride_y;
+#pragma unroll
+        for (int u = 0; u < VPT; ++u) {
+            const uint32_t j = t + u * group;
+            if (j < vecs) {
+                const uint16_t *hx = reinterpret_cast<const uint16_t *>(&v[u]);
+                uint4 out;
+                uint16_t *ho = reinterpret_cast<uint16_t *>(&out);
+                if (W_F16) {
+                    const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(w) + j);
+                    const uint16_t *hw = reinterpret_cast<const uint16_t *>(&wv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ho[e] = rms_out(k, hx[e], h2d(hw[e]));
+                } else {
+                    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * j);
+                    const float4 w1 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * j + 1);
+                    const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) ho[e] = rms_out(k, hx[e], (double) wf[e]);
+                }
+                st_stream(yr + (uint64_t) j * 8, out);
+            }
+        }
+    }
+}
+
+// Any alignment, any d: one CTA per row, two passes over x (the second one is
+// served by L2).
+template<bool W_F16>
+__global__ void rms_norm_generic_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint64_t d,
+                                        int64_t stride_y, int64_t stride_x, float eps) {
+    __shared__ float red[32];
+    for (uint64_t row = blockIdx.x; row < n; row += gridDim.x) {
+        const uint16_t *xr = x + (int64_t) row * stride_x;
+        uint16_t *yr = y + (int64_t) row * stride_y;
+        float ss = 0.f;
+        for (uint64_t j = threadIdx.x; j < d; j += blockDim.x) {
+            const float f = f16_to_f32(xr[j]);
+            ss = fmaf(f, f, ss);
+        }
+        ss = cta_reduce<false>(ss, red);
+        const double k = rms_scale(ss, d, eps);
+        for (uint64_t j = threadIdx.x; j < d; j += blockDim.x) {
+            const double wv = W_F16 ? h2d(reinterpret_cast<const uint16_t *>(w)[j])
+                                    : (double) reinterpret_cast<const float *>(w)[j];
+            yr[j] = rms_out(k, xr[j], wv);
+        }
+        __syncthreads();
+    }
+}
+
+template<int VPT, bool W_F16>
+void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t vecs, void *y, const void *x,
+                 const void *w, cudaStream_t st) {
+    auto *yp = reinterpret_cast<uint16_t *>(y);
+    auto *xp = reinterpret_cast<const uint16_t *>(x);
+    if (cta_row) {
+        const uint64_t cap = (uint64_t) d->sm_count * (2048 / threads);
+        const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap);
+        rms_norm_regs_kernel<VPT, W_F16, true>
+            <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon);
+    } else {
+        const uint64_t ctas = (d->n + 7) / 8;
+        const uint64_t cap = (uint64_t) d->sm_count * 8;
+        const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
+        rms_norm_regs_kernel<VPT, W_F16, false>
+            <<<grid, 256, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon);
+    }
+}
+
+template<bool W_F16>
+void dispatch_regs(const RMSNormDesc *d, int vpt, bool cta_row, uint32_t threads, uint32_t vecs, void *y,
+                   const void *x, const void *w, cudaStream_t st) {
+    switch (vpt) {
+        case 1: launch_regs<1, W_F16>(d, cta_row, threads, vecs, y, x, w, st); break;
+        case 2: launch_regs<2, W_F16>(d, cta_row, threads, vecs, y, x, w, st); break;
+        case 4: launch_regs<4, W_F16>(d, cta_row, threads, vecs, y, x, w, st); break;
+        default: launch_regs<8, W_F16>(d, cta_row, threads, vecs, y, x, w, st); break;
+    }
+}
+
+}// namespace
+
+INFINIOP_API infiniopStatus_t infiniopCreateRMSNormDescriptor(infiniopHandle_t handle,
+                                                              infiniopRMSNormDescriptor_t *desc_ptr,
+                                                              infiniopTensorDescriptor_t y_desc,
+                                                              infiniopTensorDescriptor_t x_desc,
+                                                              infiniopTensorDescriptor_t w_desc, float epsilon) {
+    if (handle == nullptr || handle->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (desc_ptr == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    if (y_desc == nullptr || x_desc == nullptr || w_desc == nullptr) return STATUS_BAD_PARAM;
+    // Shape checks and codes of reference rms_norm.cc:10-19.
+    if (y_desc->ndim != 2 || x_desc->ndim != 2 || w_desc->ndim != 1) return STATUS_BAD_TENSOR_SHAPE;
+    const uint64_t n = y_desc->shape[0], d = y_desc->shape[1];
+    if (x_desc->shape[0] != n || x_desc->shape[1] != d || w_desc->shape[0] != d) return STATUS_BAD_TENSOR_SHAPE;
+    // The reference defers the dtype check to the compute call
+    // (rms_norm.cu:165-171: anything but fp16 data -> BAD_TENSOR_DTYPE) and reads
+    // any non-fp16 weight as fp32; the weight must really be one of the two here.
+    if (!dt_eq(y_desc->dt, F16) || !dt_eq(x_desc->dt, F16)) return STATUS_BAD_TENSOR_DTYPE;
+    if (!dt_eq(w_desc->dt, F16) && !dt_eq(w_desc->dt, F32)) return STATUS_BAD_TENSOR_DTYPE;
+    if (y_desc->strides[1] != 1 || x_desc->strides[1] != 1 || w_desc->strides[0] != 1) return STATUS_BAD_TENSOR_STRIDES;
+
+    auto *h = reinterpret_cast<Handle *>(handle);
+    auto *r = new (std::nothrow) RMSNormDesc{DevNvGpu, h->device_id,         h->sm_count,           n,
+                                             d,        y_desc->strides[0],   x_desc->strides[0],    dt_eq(w_desc->dt, F16),
+                                             epsilon};
+    if (r == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    *desc_ptr = reinterpret_cast<infiniopRMSNormDescriptor_t>(r);
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopGetRMSNormWorkspaceSize(infiniopRMSNormDescriptor_t desc, uint64_t *size) {
+    if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (size == nullptr) return STATUS_BAD_PARAM;
+    *size = 0;
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopRMSNorm(infiniopRMSNormDescriptor_t desc, void *workspace,
+                                              uint64_t workspace_size, void *y, void const *x, void const *w,
+                                              void *stream) {
+    (void) workspace;
+    (void) workspace_size;
+    if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (y == nullptr || x == nullptr || w == nullptr) return STATUS_BAD_PARAM;
+    auto *d = reinterpret_cast<RMSNormDesc *>(desc);
+    if (d->n == 0 || d->d == 0) return STATUS_SUCCESS;
+    DeviceGuard guard(d->device_id);
+    auto st = reinterpret_cast<cudaStream_t>(stream);
+
+    const bool vec_ok = d->d % 8 == 0 && d->d / 8 <= 8192 && d->stride_x % 8 == 0 && d->stride_y % 8 == 0 &&
+                        aligned16(y) && aligned16(x) && aligned16(w);
+    if (vec_ok) {
+        const uint32_t vecs = (uint32_t) (d->d / 8);
+        // Enough rows to fill the GPU: favour bytes in flight per thread (8
+        // vectors each, a warp per row when the row fits).  Few rows: favour
+        // latency, spread each row over as many threads as it has vectors.
+        const bool big = d->n * (uint64_t) vecs >= (1u << 20);
+        int vpt;
+        bool cta_row;
+        uint32_t threads = 256;
+        if (big && vecs <= 256) {
+            cta_row = false;
+            const uint32_t need = (vecs + 31) / 32;
+            vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+        } else {
+            cta_row = true;
+            const uint32_t min_vpt = (vecs + 1023) / 1024;
+            uint32_t want = big ? 8 : min_vpt;
+            if (want < min_vpt) want = min_vpt;
+            vpt = want <= 1 ? 1 : want <= 2 ? 2 : want <= 4 ? 4 : 8;
+            threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;
+        }
+        if (d->w_f16) dispatch_regs<true>(d, vpt, cta_row, threads, vecs, y, x, w, st);
+        else dispatch_regs<false>(d, vpt, cta_row, threads, vecs, y, x, w, st);
+        return check_launch("rms_norm");
+    }
+    const uint64_t cap = (uint64_t) d->sm_count * 8;
+    const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap);
+    auto *yp = reinterpret_cast<uint16_t *>(y);
+    auto *xp = reinterpret_cast<const uint16_t *>(x);
+    if (d->w_f16) {
+        rms_norm_generic_kernel<true><<<grid, 256, 0, st>>>(yp, xp, w, d->n, d->d, d->stride_y, d->stride_x, d->epsilon);
+    } else {
+        rms_norm_generic_kernel<false><<<grid, 256, 0, st>>>(yp, xp, w, d->n, d->d, d->stride_y, d->stride_x, d->epsilon);
+    }
+    return check_launch("rms_norm");
+}
+
+INFINIOP_API infiniopStatus_t infiniopDestroyRMSNormDescriptor(infiniopRMSNormDescriptor_t desc) {
+    if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    delete reinterpret_cast<RMSNormDesc *>(desc);
+    return STATUS_SUCCESS;
+}

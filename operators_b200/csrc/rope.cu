@@ -1,0 +1,228 @@
+// Rotary position embedding, in place on t[tokens, heads, dh] fp16.
+//
+// Replaces reference src/ops/rotary_embedding/cuda/rotary_embedding.cu:5-68 and
+// src/ops/rotary_embedding/cuda/rotary_embedding.cc:5-65 behind
+// include/ops/rotary_embedding/rotary_embedding.h.  Arithmetic follows the CPU
+// backend (src/ops/rotary_embedding/cpu/rotary_embedding_cpu.cc:16-44): for the
+// pair (a, b) = (t[2k], t[2k+1]) of token i with p = pos_ids[i],
+//   t[2k]   = trunc16(a * cos[p*dh + 2k]     - b * sin[p*dh + 2k])
+//   t[2k+1] = trunc16(a * sin[p*dh + 2k + 1] + b * cos[p*dh + 2k + 1])
+// with un-fused fp32 multiplies and adds, so results are bit-identical.  As in
+// the reference the table row offset is p * dh (the table's own row stride is
+// not used) and p is not range-checked.
+//
+// HBM-bound: t is read and written once; a token's two table rows are read
+// from HBM once and shared by all its heads.  Thread -> (token, slice of the
+// head dimension); the thread keeps its slice of the sin/cos rows in registers
+// and walks over the heads with several 128-bit loads in flight.
+#include "common.cuh"
+
+#include <new>
+
+using namespace b200;
+
+namespace {
+
+struct RoPEDesc {
+    Device device;
+    int device_id;
+    int sm_count;
+    uint64_t seq_len, nhead, dim;
+    int64_t stride_0, stride_1;
+};
+
+// One slice = V halves of one head (V = 8: a 128-bit vector, V = 2: one pair).
+// ALIGNED says whether a slice may be moved with a single V*2-byte access.
+template<int V, bool ALIGNED>
+struct Slice {
+    uint16_t h[V];
+    __device__ __forceinline__ void load(const uint16_t *p) {
+        if (ALIGNED && V == 8) {
+            *reinterpret_cast<uint4 *>(h) = ld_stream(p);
+        } else if (ALIGNED && V == 2) {
+            *reinterpret_cast<uint32_t *>(h) = *reinterpret_cast<const uint32_t *>(p);
+        } else {
+#pragma unroll
+            for (int e = 0; e < V; ++e) h[e] = p[e];
+        }
+    }
+    __device__ __forceinline__ void store(uint16_t *p) const {
+        if (ALIGNED && V == 8) {
+            st_stream(p, *reinterpret_cast<const uint4 *>(h));
+        } else if (ALIGNED && V == 2) {
+            *reinterpret_cast<uint32_t *>(p) = *reinterpret_cast<const uint32_t *>(h);
+        } else {
+#pragma unroll
+            for (int e = 0; e < V; ++e) p[e] = h[e];
+        }
+    }
+};
+
+constexpr int kHeadsInFlight = 4;
+
+// Block = tokens_per_cta x threads_per_token.  threads_per_token is a multiple
+// of slices_per_head, so a thread's slice index within the head never changes
+// while it strides over (head, slice) items: its table values load once.
+template<int V, bool ALIGNED>
+__global__ void rope_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table,
+                            uint64_t seq_len, uint32_t nhead, uint32_t dim, int64_t stride_0, int64_t stride_1,
+                            uint32_t threads_per_token, uint32_t slices_per_head) {
+    const uint32_t tok_in_cta = threadIdx.x / threads_per_token;
+    const uint32_t lt = threadIdx.x - tok_in_cta * threads_per_token;
+    const uint32_t tokens_per_cta = blockDim.x / threads_per_token;
+    // Usual case: the token's threads cover every slice of a head at least once
+    // and a thread keeps one slice.  Very wide heads (more slices than threads):
+    // a thread walks over slices as well and visits every head.
+    const bool wide = threads_per_token < slices_per_head;
+    const uint32_t slice0 = wide ? lt : lt % slices_per_head;
+    const uint32_t slice_step = wide ? threads_per_token : slices_per_head;
+    const uint32_t head0 = wide ? 0 : lt / slices_per_head;
+    const uint32_t head_step = wide ? 1 : threads_per_token / slices_per_head;
+
+    for (uint64_t tok = (uint64_t) blockIdx.x * tokens_per_cta + tok_in_cta; tok < seq_len;
+         tok += (uint64_t) gridDim.x * tokens_per_cta) {
+        const uint64_t p = pos_ids[tok];
+        for (uint32_t slice = slice0; slice < slices_per_head; slice += slice_step) {
+            const float *sr = sin_table + p * dim + slice * V;
+            const float *cr = cos_table + p * dim + slice * V;
+            float sn[V], cs[V];
+            if constexpr (V == 8) {
+                const float4 s0 = __ldg(reinterpret_cast<const float4 *>(sr)), s1 = __ldg(reinterpret_cast<const float4 *>(sr) + 1);
+                const float4 c0 = __ldg(reinterpret_cast<const float4 *>(cr)), c1 = __ldg(reinterpret_cast<const float4 *>(cr) + 1);
+                sn[0] = s0.x, sn[1] = s0.y, sn[2] = s0.z, sn[3] = s0.w, sn[4] = s1.x, sn[5] = s1.y, sn[6] = s1.z, sn[7] = s1.w;
+                cs[0] = c0.x, cs[1] = c0.y, cs[2] = c0.z, cs[3] = c0.w, cs[4] = c1.x, cs[5] = c1.y, cs[6] = c1.z, cs[7] = c1.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    sn[e] = __ldg(sr + e);
+                    cs[e] = __ldg(cr + e);
+                }
+            }
+            uint16_t *base = t + (int64_t) tok * stride_0 + slice * V;
+            for (uint32_t h = head0; h < nhead; h += head_step * kHeadsInFlight) {
+                Slice<V, ALIGNED> x[kHeadsInFlight];
+#pragma unroll
+                for (int u = 0; u < kHeadsInFlight; ++u) {
+                    const uint32_t hh = h + u * head_step;
+                    if (hh < nhead) x[u].load(base + (int64_t) hh * stride_1);
+                }
+#pragma unroll
+                for (int u = 0; u < kHeadsInFlight; ++u) {
+                    const uint32_t hh = h + u * head_step;
+                    if (hh < nhead) {
+#pragma unroll
+                        for (int k = 0; k < V / 2; ++k) {
+                            const float a = f16_to_f32(x[u].h[2 * k]), b = f16_to_f32(x[u].h[2 * k + 1]);
+                            const float r0 = __fsub_rn(__fmul_rn(a, cs[2 * k]), __fmul_rn(b, sn[2 * k]));
+                            const float r1 = __fadd_rn(__fmul_rn(a, sn[2 * k + 1]), __fmul_rn(b, cs[2 * k + 1]));
+                            x[u].h[2 * k] = f32_to_f16_ref(r0);
+                            x[u].h[2 * k + 1] = f32_to_f16_ref(r1);
+                        }
+                        x[u].store(base + (int64_t) hh * stride_1);
+                    }
+                }
+            }
+        }
+    }
+}
+
+}// namespace
+
+INFINIOP_API infiniopStatus_t infiniopCreateRoPEDescriptor(infiniopHandle_t handle, infiniopRoPEDescriptor_t *desc_ptr,
+                                                           infiniopTensorDescriptor_t t,
+                                                           infiniopTensorDescriptor_t pos_ids,
+                                                           infiniopTensorDescriptor_t sin_table,
+                                                           infiniopTensorDescriptor_t cos_table) {
+    if (handle == nullptr || handle->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    // Checks, order and codes of reference rotary_embedding.cc:11-50.  The
+    // reference's nv-gpu limit dh/2 <= 1024 (rotary_embedding.cc:35-37) comes from
+    // its one-thread-per-pair launch and does not apply here.
+    if (desc_ptr == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    if (t == nullptr || pos_ids == nullptr || sin_table == nullptr || cos_table == nullptr) return STATUS_BAD_PARAM;
+    if (t->ndim != 3 || pos_ids->ndim != 1 || sin_table->ndim != 2 || cos_table->ndim != 2) return STATUS_BAD_TENSOR_SHAPE;
+    const uint64_t seq_len = t->shape[0], nhead = t->shape[1], dim = t->shape[2];
+    if (dim % 2 != 0) return STATUS_BAD_TENSOR_SHAPE;
+    if (pos_ids->shape[0] != seq_len || sin_table->shape[1] != dim || cos_table->shape[1] != dim ||
+        sin_table->shape[0] != cos_table->shape[0]) {
+        return STATUS_BAD_TENSOR_SHAPE;
+    }
+    if (nhead > 0xFFFFFFFFull || dim > 0xFFFFFFFFull) return STATUS_BAD_TENSOR_SHAPE;
+    if (t->strides[2] != 1 || pos_ids->strides[0] != 1 || sin_table->strides[1] != 1 || cos_table->strides[1] != 1) {
+        return STATUS_BAD_TENSOR_STRIDES;
+    }
+    if (!dt_eq(t->dt, F16)) return STATUS_BAD_TENSOR_DTYPE;
+    if (!dt_eq(sin_table->dt, F32) || !dt_eq(cos_table->dt, F32)) return STATUS_BAD_TENSOR_DTYPE;
+    if (!dt_eq(pos_ids->dt, U64)) return STATUS_BAD_TENSOR_DTYPE;
+
+    auto *h = reinterpret_cast<Handle *>(handle);
+    auto *d = new (std::nothrow)
+        RoPEDesc{DevNvGpu, h->device_id, h->sm_count, seq_len, nhead, dim, t->strides[0], t->strides[1]};
+    if (d == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    *desc_ptr = reinterpret_cast<infiniopRoPEDescriptor_t>(d);
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopGetRoPEWorkspaceSize(infiniopRoPEDescriptor_t desc, uint64_t *size) {
+    if (desc == nullptr) return STATUS_BAD_DEVICE;
+    if (size == nullptr) return STATUS_BAD_PARAM;
+    *size = 0;
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *workspace, uint64_t workspace_size,
+                                           void *t, void const *pos_ids, void const *sin_table,
+                                           void const *cos_table, void *stream) {
+    (void) workspace;
+    (void) workspace_size;
+    if (desc == nullptr) return STATUS_BAD_DEVICE;
+    auto *d = reinterpret_cast<RoPEDesc *>(desc);
+    if (d->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (t == nullptr || pos_ids == nullptr || sin_table == nullptr || cos_table == nullptr) return STATUS_BAD_PARAM;
+    if (d->seq_len == 0 || d->nhead == 0 || d->dim == 0) return STATUS_SUCCESS;
+    DeviceGuard guard(d->device_id);
+    auto st = reinterpret_cast<cudaStream_t>(stream);
+    auto *tp = reinterpret_cast<uint16_t *>(t);
+    auto *pp = reinterpret_cast<const uint64_t *>(pos_ids);
+    auto *sp = reinterpret_cast<const float *>(sin_table);
+    auto *cp = reinterpret_cast<const float *>(cos_table);
+    const uint32_t nhead = (uint32_t) d->nhead, dim = (uint32_t) d->dim;
+
+    // Widest slice the layout allows: 8 halves need 16-byte aligned rows of t
+    // and of both tables (dh % 8 == 0 makes p*dh*4 a multiple of 32 bytes).
+    const bool v8 = dim % 8 == 0 && d->stride_0 % 8 == 0 && d->stride_1 % 8 == 0 && aligned16(t) &&
+                    aligned16(sin_table) && aligned16(cos_table);
+    const bool v2_aligned = d->stride_0 % 2 == 0 && d->stride_1 % 2 == 0 && aligned4(t);
+    const uint32_t V = v8 ? 8 : 2;
+    const uint32_t slices = dim / V;
+    // threads per token: a multiple of `slices`, about (items / kHeadsInFlight)
+    // so that every thread has a full set of loads in flight, capped at 1024.
+    uint32_t heads_per_pass = (nhead + kHeadsInFlight - 1) / kHeadsInFlight;
+    uint32_t tpt = slices * heads_per_pass;
+    while (tpt > 1024 && heads_per_pass > 1) {
+        heads_per_pass = (heads_per_pass + 1) / 2;
+        tpt = slices * heads_per_pass;
+    }
+    if (tpt > 1024) tpt = 1024;// more slices per head than a CTA has threads
+    uint32_t tokens_per_cta = 1, threads = tpt;
+    if (tpt < 256) {
+        tokens_per_cta = 256 / tpt;
+        threads = tokens_per_cta * tpt;
+    }
+    const uint64_t ctas = (d->seq_len + tokens_per_cta - 1) / tokens_per_cta;
+    const uint64_t cap = (uint64_t) d->sm_count * 32;
+    const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
+    if (v8) {
+        rope_kernel<8, true><<<grid, threads, 0, st>>>(tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1, tpt, slices);
+    } else if (v2_aligned) {
+        rope_kernel<2, true><<<grid, threads, 0, st>>>(tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1, tpt, slices);
+    } else {
+        rope_kernel<2, false><<<grid, threads, 0, st>>>(tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1, tpt, slices);
+    }
+    return check_launch("rope");
+}
+
+INFINIOP_API infiniopStatus_t infiniopDestroyRoPEDescriptor(infiniopRoPEDescriptor_t desc) {
+    if (desc == nullptr) return STATUS_BAD_DEVICE;
+    delete reinterpret_cast<RoPEDesc *>(desc);
+    return STATUS_SUCCESS;
+}

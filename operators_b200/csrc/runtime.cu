@@ -1,0 +1,82 @@
+// Handle and tensor-descriptor entry points of the C ABI.
+//
+// Replaces, for the DevNvGpu device only, reference src/devices/handle.cc:16-74
+// with src/devices/cuda/cuda_handle.cc:3-47 (no cuBLAS / cuDNN handle pools:
+// none of the operators served here calls a library) and
+// src/tensor/tensor_descriptor.cc:4-26.
+#include "common.cuh"
+
+#include <new>
+
+using namespace b200;
+
+INFINIOP_API infiniopStatus_t infiniopCreateHandle(infiniopHandle_t *handle_ptr, Device device, int device_id) {
+    if (handle_ptr == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    if (device_id < 0) return STATUS_BAD_PARAM;
+    // This library is the nv-gpu device and nothing else: there is no CPU path
+    // to fall back to, so every other device is refused.
+    if (device != DevNvGpu) return STATUS_BAD_DEVICE;
+
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device_id >= count) {
+        cudaGetLastError();
+        return STATUS_BAD_DEVICE;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device_id) != cudaSuccess) return STATUS_BAD_DEVICE;
+    if (prop.major < 10) {
+        fprintf(stderr, "infiniop[b200]: device %d is sm_%d%d; this build carries sm_100a code only\n", device_id,
+                prop.major, prop.minor);
+        return STATUS_BAD_DEVICE;
+    }
+    auto *h = new (std::nothrow) Handle{DevNvGpu, device_id, prop.multiProcessorCount,
+                                        (int) prop.sharedMemPerBlockOptin};
+    if (h == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    *handle_ptr = reinterpret_cast<infiniopHandle_t>(h);
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopDestroyHandle(infiniopHandle_t handle) {
+    if (handle == nullptr || handle->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    delete reinterpret_cast<Handle *>(handle);
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopCreateTensorDescriptor(infiniopTensorDescriptor_t *desc_ptr, uint64_t ndim,
+                                                             uint64_t const *shape_, int64_t const *strides_,
+                                                             DataLayout datatype) {
+    if (desc_ptr == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    uint64_t *shape = new (std::nothrow) uint64_t[ndim ? ndim : 1];
+    int64_t *strides = new (std::nothrow) int64_t[ndim ? ndim : 1];
+    auto *d = new (std::nothrow) TensorDescriptor;
+    if (!shape || !strides || !d) {
+        delete[] shape;
+        delete[] strides;
+        delete d;
+        return STATUS_MEMORY_NOT_ALLOCATED;
+    }
+    for (uint64_t i = 0; i < ndim; ++i) shape[i] = shape_[i];
+    if (strides_ != nullptr) {
+        for (uint64_t i = 0; i < ndim; ++i) strides[i] = strides_[i];
+    } else {
+        int64_t run = 1;
+        for (int64_t i = (int64_t) ndim - 1; i >= 0; --i) {
+            strides[i] = run;
+            run *= (int64_t) shape[i];
+        }
+    }
+    d->dt = datatype;
+    d->ndim = ndim;
+    d->shape = shape;
+    d->strides = strides;
+    *desc_ptr = d;
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopDestroyTensorDescriptor(infiniopTensorDescriptor_t desc) {
+    if (desc == nullptr) return STATUS_BAD_PARAM;
+    delete[] desc->shape;
+    delete[] desc->strides;
+    delete desc;
+    return STATUS_SUCCESS;
+}

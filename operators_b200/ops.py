@@ -1,0 +1,278 @@
+"""Per-operator call sequences over the C ABI.
+
+Each `*Op` object performs the reference's create-descriptor and
+workspace-size stages once (exactly the ctypes sequence of the reference's test
+scripts, e.g. reference operatorspy/tests/rms_norm.py:56-79) and can then be
+launched many times; the module-level functions are the one-shot forms.  All
+tensors are torch tensors living on the handle's device; nothing here computes
+anything in Python.  The same code drives any library that exports this ABI,
+which is how the tests run the reference's own CPU build through it.
+"""
+import ctypes
+from ctypes import POINTER, c_float, c_int, c_int64, c_uint64, c_void_p
+
+from .data_layout import U64
+from .liboperators import infiniopHandle_t, infiniopTensorDescriptor_t
+from .utils import check_error, create_workspace, destroy_tensor_descriptor, to_tensor
+
+_desc_t = c_void_p  # operator descriptors are opaque to Python
+
+
+def _declare(lib):
+    """Type every operator entry point once per loaded library."""
+    if getattr(lib, "_b200_declared", False):
+        return
+    T, H, D = infiniopTensorDescriptor_t, infiniopHandle_t, _desc_t
+    sigs = {
+        "infiniopCreateRMSNormDescriptor": [H, POINTER(D), T, T, T, c_float],
+        "infiniopGetRMSNormWorkspaceSize": [D, POINTER(c_uint64)],
+        "infiniopRMSNorm": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroyRMSNormDescriptor": [D],
+        "infiniopCreateRoPEDescriptor": [H, POINTER(D), T, T, T, T],
+        "infiniopGetRoPEWorkspaceSize": [D, POINTER(c_uint64)],
+        "infiniopRoPE": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroyRoPEDescriptor": [D],
+        "infiniopCreateSwiGLUDescriptor": [H, POINTER(D), T, T, T],
+        "infiniopSwiGLU": [D, c_void_p, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroySwiGLUDescriptor": [D],
+        "infiniopCreateAddDescriptor": [H, POINTER(D), T, T, T],
+        "infiniopAdd": [D, c_void_p, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroyAddDescriptor": [D],
+        "infiniopCreateCausalSoftmaxDescriptor": [H, POINTER(D), T],
+        "infiniopGetCausalSoftmaxWorkspaceSize": [D, POINTER(c_uint64)],
+        "infiniopCausalSoftmax": [D, c_void_p, c_uint64, c_void_p, c_void_p],
+        "infiniopDestroyCausalSoftmaxDescriptor": [D],
+        "infiniopCreateRandomSampleDescriptor": [H, POINTER(D), T, T],
+        "infiniopGetRandomSampleWorkspaceSize": [D, POINTER(c_uint64)],
+        "infiniopRandomSample": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_float, c_float, c_int, c_float, c_void_p],
+        "infiniopDestroyRandomSampleDescriptor": [D],
+        # extensions of this backend (include/infiniop_ext.h); absent from the reference library
+        "infiniopGetRandomSampleBatchWorkspaceSize": [D, c_uint64, POINTER(c_uint64)],
+        "infiniopRandomSampleBatch": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_int64, c_uint64, c_void_p,
+                                      c_float, c_int, c_float, c_void_p],
+        "infiniopRandomSampleBatchTrace": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_int64, c_uint64, c_void_p,
+                                           c_float, c_int, c_float, c_void_p, c_void_p],
+    }
+    for name, argtypes in sigs.items():
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.argtypes = argtypes
+            fn.restype = c_int
+    lib._b200_declared = True
+
+
+def _stream_ptr(stream):
+    if stream is None:
+        return None
+    return getattr(stream, "cuda_stream", stream)
+
+
+class _Op:
+    """Common life cycle: descriptors of the tensors, operator descriptor, workspace."""
+
+    _destroy = None
+    _wsize = None
+
+    def __init__(self, lib, handle):
+        _declare(lib)
+        self.lib, self.handle = lib, handle
+        self.desc = _desc_t()
+        self._tensor_descs = []
+        self.workspace = None
+        self.workspace_size = 0
+
+    def _t(self, tensor, layout=None):
+        ct = to_tensor(tensor, self.lib)
+        if layout is not None:
+            ct.descriptor.contents.dt = layout
+        self._tensor_descs.append(ct.descriptor)
+        return ct
+
+    def _make_workspace(self, device):
+        if self._wsize is None:
+            return
+        size = c_uint64(0)
+        check_error(getattr(self.lib, self._wsize)(self.desc, ctypes.byref(size)))
+        self.workspace_size = size.value
+        self.workspace = create_workspace(size.value, device)
+
+    def _ws_ptr(self):
+        return self.workspace.data_ptr() if self.workspace is not None else None
+
+    def destroy(self):
+        if self.desc:
+            check_error(getattr(self.lib, self._destroy)(self.desc))
+            self.desc = _desc_t()
+        for d in self._tensor_descs:
+            destroy_tensor_descriptor(self.lib, d)
+        self._tensor_descs = []
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.destroy()
+
+
+class RMSNormOp(_Op):
+    _destroy, _wsize = "infiniopDestroyRMSNormDescriptor", "infiniopGetRMSNormWorkspaceSize"
+
+    def __init__(self, lib, handle, y, x, w, epsilon=1e-5):
+        super().__init__(lib, handle)
+        yt, xt, wt = self._t(y), self._t(x), self._t(w)
+        check_error(lib.infiniopCreateRMSNormDescriptor(handle, ctypes.byref(self.desc), yt.descriptor,
+                                                        xt.descriptor, wt.descriptor, epsilon))
+        self._make_workspace(y.device)
+
+    def __call__(self, y, x, w, stream=None):
+        check_error(self.lib.infiniopRMSNorm(self.desc, self._ws_ptr(), self.workspace_size, y.data_ptr(),
+                                             x.data_ptr(), w.data_ptr(), _stream_ptr(stream)))
+
+
+class RoPEOp(_Op):
+    _destroy, _wsize = "infiniopDestroyRoPEDescriptor", "infiniopGetRoPEWorkspaceSize"
+
+    def __init__(self, lib, handle, t, pos_ids, sin_table, cos_table):
+        super().__init__(lib, handle)
+        # position ids are u64 in the ABI; torch callers may hold them as int64
+        tt, pt = self._t(t), self._t(pos_ids, U64)
+        st, ct = self._t(sin_table), self._t(cos_table)
+        check_error(lib.infiniopCreateRoPEDescriptor(handle, ctypes.byref(self.desc), tt.descriptor, pt.descriptor,
+                                                     st.descriptor, ct.descriptor))
+        self._make_workspace(t.device)
+
+    def __call__(self, t, pos_ids, sin_table, cos_table, stream=None):
+        check_error(self.lib.infiniopRoPE(self.desc, self._ws_ptr(), self.workspace_size, t.data_ptr(),
+                                          pos_ids.data_ptr(), sin_table.data_ptr(), cos_table.data_ptr(),
+                                          _stream_ptr(stream)))
+
+
+class SwiGLUOp(_Op):
+    _destroy = "infiniopDestroySwiGLUDescriptor"
+
+    def __init__(self, lib, handle, c, a, b):
+        super().__init__(lib, handle)
+        ct, at, bt = self._t(c), self._t(a), self._t(b)
+        check_error(lib.infiniopCreateSwiGLUDescriptor(handle, ctypes.byref(self.desc), ct.descriptor, at.descriptor,
+                                                       bt.descriptor))
+
+    def __call__(self, c, a, b, stream=None):
+        check_error(self.lib.infiniopSwiGLU(self.desc, c.data_ptr(), a.data_ptr(), b.data_ptr(), _stream_ptr(stream)))
+
+
+class AddOp(_Op):
+    _destroy = "infiniopDestroyAddDescriptor"
+
+    def __init__(self, lib, handle, c, a, b):
+        super().__init__(lib, handle)
+        ct, at, bt = self._t(c), self._t(a), self._t(b)
+        check_error(lib.infiniopCreateAddDescriptor(handle, ctypes.byref(self.desc), ct.descriptor, at.descriptor,
+                                                    bt.descriptor))
+
+    def __call__(self, c, a, b, stream=None):
+        check_error(self.lib.infiniopAdd(self.desc, c.data_ptr(), a.data_ptr(), b.data_ptr(), _stream_ptr(stream)))
+
+    def destroy(self):
+        # The reference's CPU Add descriptor keeps a pointer into c's tensor
+        # descriptor (reference src/ops/add/cpu/add_cpu.cc:55): destroy the
+        # operator descriptor before the tensor descriptors.
+        super().destroy()
+
+
+class CausalSoftmaxOp(_Op):
+    _destroy, _wsize = "infiniopDestroyCausalSoftmaxDescriptor", "infiniopGetCausalSoftmaxWorkspaceSize"
+
+    def __init__(self, lib, handle, y):
+        super().__init__(lib, handle)
+        yt = self._t(y)
+        check_error(lib.infiniopCreateCausalSoftmaxDescriptor(handle, ctypes.byref(self.desc), yt.descriptor))
+        self._make_workspace(y.device)
+
+    def __call__(self, y, stream=None):
+        check_error(self.lib.infiniopCausalSoftmax(self.desc, self._ws_ptr(), self.workspace_size, y.data_ptr(),
+                                                   _stream_ptr(stream)))
+
+
+class RandomSampleOp(_Op):
+    """One row of fp16 logits -> one u64 index (reference ABI), plus the batched
+    extension when the library exports it."""
+
+    _destroy, _wsize = "infiniopDestroyRandomSampleDescriptor", "infiniopGetRandomSampleWorkspaceSize"
+
+    def __init__(self, lib, handle, result, probs):
+        super().__init__(lib, handle)
+        rt, pt = self._t(result, U64), self._t(probs)
+        check_error(lib.infiniopCreateRandomSampleDescriptor(handle, ctypes.byref(self.desc), rt.descriptor,
+                                                             pt.descriptor))
+        self._make_workspace(probs.device)
+        self._batch_ws = None
+        self._batch_ws_size = 0
+
+    def __call__(self, result, probs, random_val, topp, topk, temperature, stream=None):
+        check_error(self.lib.infiniopRandomSample(self.desc, self._ws_ptr(), self.workspace_size, result.data_ptr(),
+                                                  probs.data_ptr(), random_val, topp, topk, temperature,
+                                                  _stream_ptr(stream)))
+
+    def _ensure_batch_ws(self, rows, device):
+        size = c_uint64(0)
+        check_error(self.lib.infiniopGetRandomSampleBatchWorkspaceSize(self.desc, rows, ctypes.byref(size)))
+        if self._batch_ws is None or self._batch_ws_size < size.value:
+            self._batch_ws = create_workspace(size.value, device)
+            self._batch_ws_size = size.value
+
+    def batch(self, results, logits, random_vals, topp, topk, temperature, stream=None, trace=None):
+        """results u64/int64 [rows], logits fp16 [rows, voc] (unit column stride),
+        random_vals fp32 [rows], all on the device."""
+        rows = logits.shape[0]
+        self._ensure_batch_ws(rows, logits.device)
+        args = [self.desc, self._batch_ws.data_ptr(), self._batch_ws_size, results.data_ptr(), logits.data_ptr(),
+                logits.stride(0), rows, random_vals.data_ptr(), topp, topk, temperature]
+        if trace is not None:
+            check_error(self.lib.infiniopRandomSampleBatchTrace(*args, trace.data_ptr(), _stream_ptr(stream)))
+        else:
+            check_error(self.lib.infiniopRandomSampleBatch(*args, _stream_ptr(stream)))
+
+
+# ---- one-shot forms ----------------------------------------------------------
+
+def rms_norm(lib, handle, y, x, w, epsilon=1e-5, stream=None):
+    with RMSNormOp(lib, handle, y, x, w, epsilon) as op:
+        op(y, x, w, stream)
+
+
+def rope(lib, handle, t, pos_ids, sin_table, cos_table, stream=None):
+    with RoPEOp(lib, handle, t, pos_ids, sin_table, cos_table) as op:
+        op(t, pos_ids, sin_table, cos_table, stream)
+
+
+def swiglu(lib, handle, c, a, b, stream=None):
+    with SwiGLUOp(lib, handle, c, a, b) as op:
+        op(c, a, b, stream)
+
+
+def add(lib, handle, c, a, b, stream=None):
+    with AddOp(lib, handle, c, a, b) as op:
+        op(c, a, b, stream)
+
+
+def causal_softmax(lib, handle, y, stream=None):
+    with CausalSoftmaxOp(lib, handle, y) as op:
+        op(y, stream)
+
+
+def random_sample(lib, handle, result, probs, random_val, topp, topk, temperature, stream=None):
+    with RandomSampleOp(lib, handle, result, probs) as op:
+        op(result, probs, random_val, topp, topk, temperature, stream)
+
+
+def sin_cos_table(max_seq_len, dim, theta=1e4, device="cpu"):
+    """fp32 sin/cos tables [max_seq_len, dim] with pair-duplicated frequencies,
+    the layout the RoPE entry point consumes (same construction as the
+    reference's test helper, reference operatorspy/tests/rotary_embedding.py:54-64)."""
+    import torch
+
+    pos = torch.arange(0, max_seq_len, dtype=torch.float32, device=device)
+    freqs = 1.0 / (theta ** (torch.arange(0, dim, 2, device=device)[: dim // 2].float() / dim))
+    freqs = torch.repeat_interleave(freqs, repeats=2)
+    angles = torch.outer(pos, freqs)
+    return torch.sin(angles), torch.cos(angles)

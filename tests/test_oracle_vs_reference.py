@@ -1,0 +1,122 @@
+"""The C oracle must reproduce the reference's own CPU backend bit for bit.
+
+The reference library (compiled from its sources into oracle/_ref, see
+oracle/Makefile) is called through its C ABI exactly as its test scripts do
+(reference operatorspy/tests/*.py); the oracle is called on the same seeded
+inputs; outputs are compared as raw bit patterns.
+"""
+import numpy as np
+import pytest
+import torch
+
+from operators_b200 import ops
+
+
+def _bits(t):
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("w_dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(16, 2048), (5, 33), (1, 1)])
+def test_rms_norm(oracle, ref_cpu, shape, w_dtype):
+    lib, handle = ref_cpu
+    g = torch.Generator().manual_seed(1)
+    x = (torch.rand(shape, generator=g) * 2 - 1).half()
+    w = (torch.rand(shape[1], generator=g) * 2 - 1).to(w_dtype)
+    y = torch.zeros(shape, dtype=torch.float16)
+    ops.rms_norm(lib, handle, y, x, w, 1e-5)
+    mine = oracle.rms_norm(x.numpy(), w.numpy(), 1e-5)
+    assert np.array_equal(mine.view(np.uint16), _bits(y))
+
+
+@pytest.mark.parametrize("shape,strides", [((7, 4, 32), None), ((3, 32, 128), (8000, 200, 1)), ((4, 1, 2), None)])
+def test_rope(oracle, ref_cpu, shape, strides):
+    from operators_b200 import rearrange_tensor
+
+    lib, handle = ref_cpu
+    g = torch.Generator().manual_seed(2)
+    t = torch.randn(shape, generator=g).half()
+    if strides is not None:
+        t = rearrange_tensor(t, strides)
+    pos = torch.randperm(2 * shape[0], generator=g)[: shape[0]].to(torch.int64)
+    sin, cos = ops.sin_cos_table(2 * shape[0], shape[2])
+    t_np = t.numpy().copy() if strides is None else None
+    expect_in = t.clone()
+    ops.rope(lib, handle, t, pos, sin, cos)
+    # oracle on an identically laid out copy
+    if strides is None:
+        mine = oracle.rope(t_np, pos.numpy().astype(np.uint64), sin.numpy(), cos.numpy())
+        assert np.array_equal(mine.view(np.uint16), _bits(t).reshape(shape))
+    else:
+        buf = rearrange_tensor(expect_in, strides)
+        arr = np.lib.stride_tricks.as_strided(
+            buf.numpy(), shape=shape, strides=[s * 2 for s in strides], writeable=True)
+        oracle.rope(arr, pos.numpy().astype(np.uint64), sin.numpy(), cos.numpy())
+        assert np.array_equal(np.ascontiguousarray(arr).view(np.uint16), _bits(t).reshape(shape))
+
+
+@pytest.mark.parametrize("shape,stride", [((13, 4), None), ((13, 4), 10), ((16, 5632), None), ((16, 5632), 13312)])
+def test_swiglu(oracle, ref_cpu, shape, stride):
+    from operators_b200 import rearrange_tensor
+
+    lib, handle = ref_cpu
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(shape, generator=g).half()
+    b = (torch.randn(shape, generator=g) * 4).half()
+    if stride is not None:
+        a, b = rearrange_tensor(a, (stride, 1)), rearrange_tensor(b, (stride, 1))
+    c = torch.zeros(shape, dtype=torch.float16)
+    ops.swiglu(lib, handle, c, a, b)
+    mine = oracle.swiglu(a.contiguous().numpy(), b.contiguous().numpy())
+    assert np.array_equal(mine.view(np.uint16), _bits(c))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("shapes", [((), (), ()), ((3, 3), (3, 3), (3, 3)), ((2, 20, 3), (2, 1, 3), (2, 20, 3)),
+                                    ((4, 5, 6), (6,), (4, 5, 6)), ((2, 3, 4, 5), (2, 3, 4, 5), (2, 3, 4, 5))])
+def test_add(oracle, ref_cpu, shapes, dtype):
+    lib, handle = ref_cpu
+    cs, as_, bs = shapes[2], shapes[0], shapes[1]
+    g = torch.Generator().manual_seed(4)
+    a = (torch.randn(as_, generator=g) * 100).to(dtype)
+    b = torch.randn(bs, generator=g).to(dtype)
+    c = torch.zeros(cs, dtype=dtype)
+    ops.add(lib, handle, c, a, b)
+    mine = oracle.add(a.numpy(), b.numpy())
+    if dtype == torch.float16:
+        assert np.array_equal(mine.view(np.uint16).reshape(cs), _bits(c).reshape(cs))
+    else:
+        assert np.array_equal(mine.reshape(cs), c.numpy())
+
+
+@pytest.mark.parametrize("shape", [(32, 20, 512), (5, 64), (2, 7, 7), (3, 1, 9)])
+def test_causal_softmax(oracle, ref_cpu, shape):
+    lib, handle = ref_cpu
+    g = torch.Generator().manual_seed(5)
+    y = (torch.randn(shape, generator=g) * 2).half()
+    mine = oracle.causal_softmax(y.numpy().copy())
+    ops.causal_softmax(lib, handle, y)
+    assert np.array_equal(mine.view(np.uint16), _bits(y).reshape(shape))
+
+
+@pytest.mark.parametrize("voc,u,topp,topk,temp", [
+    (512, 0.92, 0.8, 3, 0.5), (4096, 0.95, 0.9, 5, 1.0), (16384, 0.85, 0.85, 10, 2.0),
+    (512, 0.92, 0.0, 3, 0.5), (4096, 0.95, 0.9, 1, 1.0), (3000, 0.3, 0.9, 50, 0.8), (40, 0.5, 1.0, 64, 1.0)])
+@pytest.mark.parametrize("dist", ["uniform", "normal3"])
+def test_random_sample(oracle, ref_cpu, voc, u, topp, topk, temp, dist):
+    lib, handle = ref_cpu
+    g = torch.Generator().manual_seed(6)
+    for _ in range(3):
+        logits = torch.rand(voc, generator=g).half() if dist == "uniform" else (torch.randn(voc, generator=g) * 3).half()
+        res = torch.zeros(1, dtype=torch.int64)
+        ops.random_sample(lib, handle, res, logits, u, topp, topk, temp)
+        assert oracle.random_sample(logits.numpy(), u, topp, topk, temp) == int(res[0])
+
+
+def test_f32_to_f16_rule(oracle):
+    """Truncation, subnormals, flush to zero and the out-of-range bit patterns
+    of the reference conversion (src/devices/cpu/common_cpu.cc:41-64)."""
+    cases = {1.0: 0x3C00, 1.0009765: 0x3C00, 1.00097656255: 0x3C01, -2.5: 0xC100, 65504.0: 0x7BFF, 65519.9: 0x7BFF,
+             6e-8: 0x0001, 5.9e-8: 0x0000, -5.9e-8: 0x8000, float("inf"): 0x7C00, 65536.0: 0x7C00, 131072.0: 0x8000}
+    for v, bits in cases.items():
+        assert int(oracle.f32_to_f16(np.float32(v))) == bits, (v, hex(bits))
