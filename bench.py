@@ -1,0 +1,492 @@
+#!/usr/bin/env python
+"""Benchmark of the decode hot path: RMSNorm, RoPE, SwiGLU, Add, causal softmax
+and random sample at the configurations of BASELINE.json.
+
+One "step" runs the six operators once, each on its BASELINE.json configuration
+(seeded synthetic inputs of those shapes and value distributions).  The metric
+is achieved HBM bandwidth: algorithmic bytes of the step / time, reported for
+the whole step (`value`) and per operator (`ops`), plus tokens/s for sampling.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]        this library (sm_100a kernels)
+  python bench.py --impl reference [...]                      the reference CPU backend on the host cores
+
+Under torchrun (N > 1) every rank runs the same step on its own GPU and its
+own rows (weak scaling, no data-path collective); time = max over ranks.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# ---- BASELINE.json configurations ---------------------------------------------------
+RMS_N, RMS_D = 16, 2048
+ROPE_T, ROPE_H, ROPE_DH = 4096, 32, 128
+SWI_T, SWI_DI = 8192, 14336
+ADD_T, ADD_D = 8192, 4096
+SM_H, SM_Q, SM_KV = 32, 512, 4096
+RS_B, RS_V = 64, 128256
+RS_TEMP, RS_TOPK, RS_TOPP = 0.8, 50, 0.9
+
+# Algorithmic bytes per operator launch: every input element read once, every
+# output element written once (for causal softmax only the visible part is read).
+ALGO_BYTES = {
+    "rms_norm": 2 * RMS_N * RMS_D * 2 + RMS_D * 2,
+    "rope": 2 * ROPE_T * ROPE_H * ROPE_DH * 2 + ROPE_T * 8 + 2 * ROPE_T * ROPE_DH * 4,
+    "swiglu": 3 * SWI_T * SWI_DI * 2,
+    "add": 3 * ADD_T * ADD_D * 2,
+    "causal_softmax": SM_H * sum((SM_KV - SM_Q + i + 1) for i in range(SM_Q)) * 2 + SM_H * SM_Q * SM_KV * 2,
+    "random_sample": RS_B * RS_V * 2 + RS_B * 4 + RS_B * 8,
+}
+OPS = list(ALGO_BYTES)
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the
+# dominant kernel from an ncu capture; None until a capture exists.
+NCU_TRAFFIC_BYTES = {"swiglu": None}
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def make_inputs(seed, rows_fraction=1.0):
+    """Seeded CPU tensors of the six configurations (fp32 draws cast to fp16)."""
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+
+    def frac(n):
+        return max(1, int(round(n * rows_fraction)))
+
+    d = {}
+    d["rms_x"] = (torch.rand((frac(RMS_N), RMS_D), generator=g) * 2 - 1).half()
+    d["rms_w"] = (torch.rand(RMS_D, generator=g) * 2 - 1).half()
+    nt = frac(ROPE_T)
+    d["rope_t"] = torch.randn((nt, ROPE_H, ROPE_DH), generator=g).half()
+    d["rope_pos"] = torch.arange(nt, dtype=torch.int64)
+    from operators_b200.ops import sin_cos_table
+
+    d["rope_sin"], d["rope_cos"] = sin_cos_table(ROPE_T, ROPE_DH, 1e4)
+    # 235M-element normal draws dominate set-up time: draw once in fp32 chunks
+    gu = torch.empty((frac(SWI_T), 2 * SWI_DI), dtype=torch.float16)
+    step = 512
+    for r in range(0, gu.shape[0], step):
+        gu[r:r + step] = torch.randn((min(step, gu.shape[0] - r), 2 * SWI_DI), generator=g).half()
+    d["gate_up"] = gu
+    d["add_a"] = torch.randn((frac(ADD_T), ADD_D), generator=g).half()
+    d["add_b"] = torch.randn((frac(ADD_T), ADD_D), generator=g).half()
+    d["att"] = (torch.randn((frac(SM_H), SM_Q, SM_KV), generator=g) * 2).half()
+    nb = frac(RS_B)
+    d["logits"] = (torch.randn((nb, RS_V), generator=g) * 3).half()
+    d["u"] = torch.rand(nb, generator=g)
+    return d
+
+
+def sample_bytes(inputs):
+    """Algorithmic bytes of a step over `inputs` (which may hold a row sample)."""
+    b = {}
+    n = inputs["rms_x"].shape[0]
+    b["rms_norm"] = 2 * n * RMS_D * 2 + RMS_D * 2
+    nt = inputs["rope_t"].shape[0]
+    b["rope"] = 2 * nt * ROPE_H * ROPE_DH * 2 + nt * 8 + 2 * nt * ROPE_DH * 4
+    b["swiglu"] = 3 * inputs["gate_up"].shape[0] * SWI_DI * 2
+    b["add"] = 3 * inputs["add_a"].shape[0] * ADD_D * 2
+    h = inputs["att"].shape[0]
+    b["causal_softmax"] = h * sum((SM_KV - SM_Q + i + 1) for i in range(SM_Q)) * 2 + h * SM_Q * SM_KV * 2
+    nb = inputs["logits"].shape[0]
+    b["random_sample"] = nb * RS_V * 2 + nb * 4 + nb * 8
+    return b
+
+
+# ---- clocks ---------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples of one GPU while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                smax = float(f[1])
+            except ValueError:
+                continue
+            for nme, val in zip(names, f[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nme)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- this library ------------------------------------------------------------------------
+class DecodeStep:
+    """The six operators bound to device buffers; run() launches one step."""
+
+    def __init__(self, lib, handle, dev, inputs):
+        import torch
+
+        from operators_b200 import ops
+
+        self.torch, self.dev = torch, dev
+        t = {k: (v.to(dev) if v is not None else None) for k, v in inputs.items()}
+        self.t = t
+        t["rms_y"] = torch.zeros_like(t["rms_x"])
+        di = SWI_DI
+        t["swi_b"], t["swi_a"] = t["gate_up"][:, :di], t["gate_up"][:, di:]  # gate half -> silu, up half -> multiplier
+        t["swi_c"] = torch.zeros((t["gate_up"].shape[0], di), dtype=torch.float16, device=dev)
+        t["add_c"] = torch.zeros_like(t["add_a"])
+        t["rs_out"] = torch.zeros(t["logits"].shape[0], dtype=torch.int64, device=dev)
+        self.rms = ops.RMSNormOp(lib, handle, t["rms_y"], t["rms_x"], t["rms_w"], 1e-5)
+        self.rope = ops.RoPEOp(lib, handle, t["rope_t"], t["rope_pos"], t["rope_sin"], t["rope_cos"])
+        self.swi = ops.SwiGLUOp(lib, handle, t["swi_c"], t["swi_a"], t["swi_b"])
+        self.add = ops.AddOp(lib, handle, t["add_c"], t["add_a"], t["add_b"])
+        self.sm = ops.CausalSoftmaxOp(lib, handle, t["att"])
+        self.rs = ops.RandomSampleOp(lib, handle, t["rs_out"][:1], t["logits"][0])
+        self.launches_per_step = 6
+
+    def calls(self):
+        t = self.t
+        return [
+            ("rms_norm", lambda s: self.rms(t["rms_y"], t["rms_x"], t["rms_w"], s)),
+            ("rope", lambda s: self.rope(t["rope_t"], t["rope_pos"], t["rope_sin"], t["rope_cos"], s)),
+            ("swiglu", lambda s: self.swi(t["swi_c"], t["swi_a"], t["swi_b"], s)),
+            ("add", lambda s: self.add(t["add_c"], t["add_a"], t["add_b"], s)),
+            ("causal_softmax", lambda s: self.sm(t["att"], s)),
+            ("random_sample", lambda s: self.rs.batch(t["rs_out"], t["logits"], t["u"], RS_TOPP, RS_TOPK, RS_TEMP, s)),
+        ]
+
+
+def run_b200(args):
+    import torch
+
+    from operators_b200 import DeviceEnum, create_handle, open_lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU path in this library"
+    torch.cuda.set_device(local)
+    dev = "cuda:%d" % local
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    lib = open_lib(os.path.join(ROOT, "operators_b200", "lib"))
+    handle = create_handle(lib, DeviceEnum.DEVICE_CUDA, local)
+
+    inputs = make_inputs(1000 + rank)
+    step = DecodeStep(lib, handle, dev, inputs)
+    calls = step.calls()
+    stream = torch.cuda.current_stream()
+    sptr = stream.cuda_stream
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        for _, fn in calls:
+            fn(sptr)
+    barrier()
+
+    # ---- timed region: K steps, device events around every operator ----
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(calls) + 1)] for _ in range(args.steps)]
+    clocks = ClockSampler(local)
+    clocks.start()
+    barrier()
+    for k in range(args.steps):
+        ev[k][0].record(stream)
+        for i, (_, fn) in enumerate(calls):
+            fn(sptr)
+            ev[k][i + 1].record(stream)
+    barrier()
+    clk = clocks.stop()
+    total_ms = ev[0][0].elapsed_time(ev[-1][-1])
+    per_op_ms = {name: sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(args.steps)) / args.steps
+                 for i, (name, _) in enumerate(calls)}
+    ms_per_step = total_ms / args.steps
+
+    # ---- end to end: host buffers in, host results out, every step ----
+    host_in = {k: inputs[k].pin_memory() for k in
+               ("rms_x", "rms_w", "rope_t", "rope_pos", "rope_sin", "rope_cos", "gate_up", "add_a", "add_b", "att",
+                "logits", "u")}
+    out_names = ["rms_y", "rope_t", "swi_c", "add_c", "att", "rs_out"]
+    host_out = {k: torch.empty_like(step.t[k], device="cpu").pin_memory() for k in out_names}
+    h2d = sum(v.numel() * v.element_size() for v in host_in.values())
+    d2h = sum(v.numel() * v.element_size() for v in host_out.values())
+
+    def e2e_step():
+        for k, v in host_in.items():
+            step.t[k].copy_(v, non_blocking=True)
+        for _, fn in calls:
+            fn(sptr)
+        for k in out_names:
+            host_out[k].copy_(step.t[k], non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # ---- max over ranks ----
+    vals = torch.tensor([ms_per_step, e2e_ms] + [per_op_ms[o] for o in OPS], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    vals = vals.cpu().tolist()
+    ms_per_step, e2e_ms = vals[0], vals[1]
+    per_op_ms = dict(zip(OPS, vals[2:]))
+
+    step_bytes = sum(ALGO_BYTES.values())
+    peak, peak_kind = measured_peak()
+    ops_out = {}
+    for o in OPS:
+        gbs = ALGO_BYTES[o] * world / (per_op_ms[o] * 1e-3) / 1e9
+        ops_out[o] = {"bytes": ALGO_BYTES[o], "ms": round(per_op_ms[o], 5), "gbs": round(gbs, 1),
+                      "frac_of_%s_peak" % peak_kind: round(gbs / world / peak, 4),
+                      "frac_of_8TBs": round(gbs / world / NOMINAL_HBM_GBS, 4)}
+    ops_out["random_sample"]["tokens_per_s"] = round(RS_B * world / (per_op_ms["random_sample"] * 1e-3), 1)
+
+    line = {
+        "metric": "achieved_hbm_gbs_decode_hot_path",
+        "value": round(step_bytes * world / (ms_per_step * 1e-3) / 1e9, 1),
+        "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 storage, f32/f64 arithmetic", "data": "synthetic (seeded, BASELINE.json shapes and distributions)",
+        "config": {"workload": "six-operator decode step at BASELINE.json configs: rms_norm[16,2048] rope[4096,32,128] "
+                               "swiglu[8192,2x14336] add[8192,4096] causal_softmax[32,512,4096] "
+                               "random_sample[64,128256] T0.8 k50 p0.9",
+                   "bytes_per_step": step_bytes, "sharding": "rows per GPU fixed (weak), no collective",
+                   "l2": "step working set 1.25 GB > 126 MB L2; every operator's buffers were last touched a full step earlier",
+                   "random_sample": "batched extension entry, one launch for 64 rows"},
+        "ops": ops_out,
+        "sample_tokens_per_s": ops_out["random_sample"]["tokens_per_s"],
+        "e2e": {"value": round(step_bytes * world / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3)},
+        "gpu_launches": step.launches_per_step * args.steps,
+        "clocks": clk,
+    }
+    sw_ms = per_op_ms["swiglu"]
+    ach = ALGO_BYTES["swiglu"] / (sw_ms * 1e-3) / 1e9
+    line["roofline"] = {"kernel": "swiglu_vec8_kernel", "bound": "hbm", "achieved": round(ach, 1), "peak": peak,
+                        "peak_kind": "of " + peak_kind, "unit": "GB/s", "frac": round(ach / peak, 4),
+                        "traffic": NCU_TRAFFIC_BYTES["swiglu"]}
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(sample_seconds=20.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+# ---- the reference CPU backend on the host cores --------------------------------------------
+def _cpu_backend():
+    """(kind, lib, handle): the reference's own CPU build when it was compiled
+    into oracle/_ref, else None (the oracle port is then used)."""
+    from operators_b200 import DeviceEnum, create_handle, open_lib
+    from oracle import cpu_oracle
+
+    d = cpu_oracle.reference_lib_dir()
+    if d is None:
+        return "port", None, None
+    lib = open_lib(d)
+    return "reference", lib, create_handle(lib, DeviceEnum.DEVICE_CPU)
+
+
+def cpu_step(kind, lib, handle, inputs, threads):
+    """One step of the CPU path over `inputs`, rows split over `threads` host
+    threads (the reference functions are single-threaded; rows are independent).
+    Returns seconds."""
+    import numpy as np
+    import torch
+
+    from operators_b200 import ops
+    from oracle import cpu_oracle
+
+    def chunks(n):
+        t = min(threads, n)
+        edges = [n * i // t for i in range(t + 1)]
+        return [(edges[i], edges[i + 1]) for i in range(t) if edges[i + 1] > edges[i]]
+
+    jobs = []
+    x, w = inputs["rms_x"], inputs["rms_w"]
+    y = torch.zeros_like(x)
+    tt, pos, sin, cos = inputs["rope_t"].clone(), inputs["rope_pos"], inputs["rope_sin"], inputs["rope_cos"]
+    gu = inputs["gate_up"]
+    c = torch.zeros((gu.shape[0], SWI_DI), dtype=torch.float16)
+    a, b = inputs["add_a"], inputs["add_b"]
+    s = torch.zeros_like(a)
+    att = inputs["att"].clone()
+    logits, u = inputs["logits"], inputs["u"]
+    res = torch.zeros(logits.shape[0], dtype=torch.int64)
+
+    if kind == "reference":
+        for lo, hi in chunks(x.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: ops.rms_norm(lib, handle, y[lo:hi], x[lo:hi], w, 1e-5))
+        for lo, hi in chunks(tt.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: ops.rope(lib, handle, tt[lo:hi], pos[lo:hi], sin, cos))
+        for lo, hi in chunks(gu.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: ops.swiglu(lib, handle, c[lo:hi], gu[lo:hi, SWI_DI:], gu[lo:hi, :SWI_DI]))
+        for lo, hi in chunks(a.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: ops.add(lib, handle, s[lo:hi], a[lo:hi], b[lo:hi]))
+        for lo, hi in chunks(att.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: ops.causal_softmax(lib, handle, att[lo:hi]))
+        for r in range(logits.shape[0]):
+            jobs.append(lambda r=r: ops.random_sample(lib, handle, res[r:r + 1], logits[r], float(u[r]), RS_TOPP,
+                                                      RS_TOPK, RS_TEMP))
+    else:
+        xn, wn, tn = x.numpy(), w.numpy(), tt.numpy()
+        for lo, hi in chunks(x.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: cpu_oracle.rms_norm(xn[lo:hi], wn, 1e-5))
+        for lo, hi in chunks(tt.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: cpu_oracle.rope(tn[lo:hi], pos.numpy()[lo:hi].astype(np.uint64),
+                                                             sin.numpy(), cos.numpy()))
+        gn = gu.numpy()
+        for lo, hi in chunks(gu.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: cpu_oracle.swiglu(gn[lo:hi, SWI_DI:], gn[lo:hi, :SWI_DI]))
+        an, bn = a.numpy(), b.numpy()
+        for lo, hi in chunks(a.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: cpu_oracle.add(an[lo:hi], bn[lo:hi]))
+        attn = att.numpy()
+        for lo, hi in chunks(att.shape[0]):
+            jobs.append(lambda lo=lo, hi=hi: cpu_oracle.causal_softmax(attn[lo:hi]))
+        ln = logits.numpy()
+        for r in range(logits.shape[0]):
+            jobs.append(lambda r=r: cpu_oracle.random_sample(ln[r], float(u[r]), RS_TOPP, RS_TOPK, RS_TEMP))
+
+    from concurrent.futures import ThreadPoolExecutor
+
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as pool:  # ctypes calls release the GIL
+        list(pool.map(lambda j: j(), jobs))
+    return time.perf_counter() - t0
+
+
+def _host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def cpu_baseline(sample_seconds=20.0):
+    """The CPU path on a bounded row sample of the same step (about
+    `sample_seconds` of CPU work), all host threads."""
+    kind, lib, handle = _cpu_backend()
+    threads = _host_threads()
+    # one full step costs roughly 7 core-seconds; pick the row fraction for the budget
+    fraction = max(1.0 / 64, min(1.0, sample_seconds / 7.0))
+    inputs = make_inputs(1000, rows_fraction=fraction)
+    secs = cpu_step(kind, lib, handle, inputs, threads)
+    nbytes = sum(sample_bytes(inputs).values())
+    return {"value": round(nbytes / secs / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": "one step over %.3g of the rows of every operator (%d bytes) in %.2f s" % (fraction, nbytes, secs)}
+
+
+def run_reference(args):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    kind, lib, handle = _cpu_backend()
+    threads = _host_threads()
+    # bounded sample: a quarter of the rows of every operator per step
+    fraction = 0.25 if threads >= 8 else 1.0 / 16
+    inputs = make_inputs(1000, rows_fraction=fraction)
+    nbytes = sum(sample_bytes(inputs).values())
+    for _ in range(args.warmup):
+        cpu_step(kind, lib, handle, inputs, threads)
+    secs = [cpu_step(kind, lib, handle, inputs, threads) for _ in range(args.steps)]
+    per = sum(secs) / len(secs)
+    value = round(nbytes / per / 1e9, 3)
+    sample = "each step = %.3g of the rows of every operator (%d algorithmic bytes)" % (fraction, nbytes)
+    line = {
+        "impl": "reference",
+        "metric": "achieved_hbm_gbs_decode_hot_path", "value": value, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(per * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 storage, f32/f64 arithmetic", "data": "synthetic (seeded, BASELINE.json shapes and distributions)",
+        "config": {"workload": "six-operator decode step at BASELINE.json configs (row sample)", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -127,8 +127,12 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
-// Row-major contiguity over all axes (reference src/ops/utils.h:174-188).
+// Row-major contiguity over all axes (reference src/ops/utils.h:174-188).  The
+// reference only compares neighbouring strides, so a tensor whose innermost
+// stride is 2 passes there and is then read as if it were dense; here the
+// innermost stride must be 1 as well.
 bool contiguous(infiniopTensorDescriptor_t t) {
+    if (t->ndim > 0 && t->shape[t->ndim - 1] > 1 && t->strides[t->ndim - 1] != 1) return false;
     for (uint64_t i = 1; i < t->ndim; ++i) {
         if (t->strides[i - 1] != (int64_t) t->shape[i] * t->strides[i]) return false;
     }

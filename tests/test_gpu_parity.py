@@ -1,0 +1,293 @@
+"""Parity of the sm_100a kernels with the CPU oracle, through the C ABI.
+
+Tolerances are the ones the task states: fp16 outputs within atol = rtol = 1e-3
+(causal softmax 2e-3) of the reference CPU path, Add and RoPE bit-exact,
+sampled indices identical for the same uniform draw.  Shapes cover the
+reference's own test cases (reference operatorspy/tests/*.py) and ragged /
+unaligned / strided / in-place variants.
+"""
+import numpy as np
+import pytest
+import torch
+
+from operators_b200 import ops, rearrange_tensor
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _bits(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def _close(got_bits, want_f16, atol, rtol):
+    got = got_bits.view(np.float16).astype(np.float32)
+    want = want_f16.astype(np.float32)
+    err = np.abs(got - want)
+    tol = atol + rtol * np.abs(want)
+    assert (err <= tol).all(), "max err %g at %s" % (err.max(), np.unravel_index(err.argmax(), err.shape))
+    return int((got_bits.reshape(-1) != want_f16.view(np.uint16).reshape(-1)).sum())
+
+
+def _few(mismatches, total, rate):
+    """Bitwise mismatches (each within tolerance) stay a small fraction."""
+    return mismatches <= max(3, rate * total)
+
+
+# ---- RMSNorm -----------------------------------------------------------------
+@pytest.mark.parametrize("w_dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("shape,stride", [((16, 2048), None), ((16, 2048), 4096), ((5, 33), None), ((1, 8), None),
+                                          ((700, 4096), None), ((2048, 2048), None), ((3, 16384), None),
+                                          ((2, 70000), None), ((9, 264), 272)])
+def test_rms_norm(oracle, cuda_lib, shape, stride, w_dtype):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(1)
+    x = (torch.rand(shape, generator=g) * 2 - 1).half()
+    w = (torch.rand(shape[1], generator=g) * 2 - 1).to(w_dtype)
+    want = oracle.rms_norm(x.numpy(), w.numpy(), 1e-5)
+    xd = x.to(DEV)
+    yd = torch.full(shape, 7.0, dtype=torch.float16, device=DEV)
+    if stride is not None:
+        xd, yd = rearrange_tensor(xd, (stride, 1)), rearrange_tensor(yd, (stride, 1))
+    ops.rms_norm(lib, handle, yd, xd, w.to(DEV), 1e-5)
+    torch.cuda.synchronize()
+    mism = _close(_bits(yd).reshape(shape), want, 1e-3, 1e-3)
+    assert _few(mism, x.numel(), 0.02)  # only the order of the fp32 sum of squares differs
+
+
+# ---- RoPE (bit-exact) ----------------------------------------------------------
+@pytest.mark.parametrize("shape,strides", [((1, 32, 128), None), ((1, 32, 64), None), ((4, 1, 32), None),
+                                           ((3, 32, 128), (8000, 200, 1)), ((64, 32, 128), None),
+                                           ((5, 3, 6), None), ((5, 3, 6), (37, 7, 1)), ((7, 5, 96), None),
+                                           ((2, 2, 4096), None), ((9, 40, 128), (40 * 256, 256, 1))])
+def test_rope(oracle, cuda_lib, shape, strides):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(2)
+    t = torch.randn(shape, generator=g).half()
+    pos = torch.randperm(2 * shape[0], generator=g)[: shape[0]].to(torch.int64)
+    sin, cos = ops.sin_cos_table(2 * shape[0], shape[2])
+    want = oracle.rope(t.numpy().copy(), pos.numpy().astype(np.uint64), sin.numpy(), cos.numpy())
+    td = t.to(DEV)
+    if strides is not None:
+        td = rearrange_tensor(td, strides)
+    ops.rope(lib, handle, td, pos.to(DEV), sin.to(DEV), cos.to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(td).reshape(shape), want.view(np.uint16))
+
+
+# ---- SwiGLU ------------------------------------------------------------------
+@pytest.mark.parametrize("inplace", [None, "a", "b"])
+@pytest.mark.parametrize("shape,stride", [((13, 4), None), ((13, 4), 10), ((16, 5632), None), ((16, 5632), 13312),
+                                          ((3, 8), None), ((257, 1024), 2048)])
+def test_swiglu(oracle, cuda_lib, shape, stride, inplace):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(shape, generator=g).half()
+    b = (torch.randn(shape, generator=g) * 4).half()
+    want = oracle.swiglu(a.numpy(), b.numpy())
+    ad, bd = a.to(DEV), b.to(DEV)
+    if stride is not None:
+        ad, bd = rearrange_tensor(ad, (stride, 1)), rearrange_tensor(bd, (stride, 1))
+    cd = {None: torch.zeros(shape, dtype=torch.float16, device=DEV), "a": ad, "b": bd}[inplace]
+    ops.swiglu(lib, handle, cd, ad, bd)
+    torch.cuda.synchronize()
+    mism = _close(_bits(cd).reshape(shape), want, 1e-3, 1e-3)
+    assert _few(mism, a.numel(), 2e-3)  # expf differs from libm by an fp32 ulp now and then
+
+
+def test_swiglu_fused_gate_up_halves(oracle, cuda_lib):
+    """The MLP layout: a and b are the column halves of one [tokens, 2*di]
+    buffer (reference src/ops/mlp/operator.cc:48-57,111-115)."""
+    lib, handle = cuda_lib
+    tokens, di = 64, 1792
+    g = torch.Generator().manual_seed(33)
+    gate_up = torch.randn((tokens, 2 * di), generator=g).half()
+    want = oracle.swiglu(gate_up[:, di:].numpy(), gate_up[:, :di].numpy())
+    gd = gate_up.to(DEV)
+    cd = torch.zeros((tokens, di), dtype=torch.float16, device=DEV)
+    ops.swiglu(lib, handle, cd, gd[:, di:], gd[:, :di])
+    torch.cuda.synchronize()
+    _close(_bits(cd).reshape(tokens, di), want, 1e-3, 1e-3)
+
+
+# ---- Add (bit-exact) -------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("shapes", [((), (), ()), ((3, 3), (3, 3), (3, 3)), ((2, 20, 3), (2, 1, 3), (2, 20, 3)),
+                                    ((32, 20, 512), (32, 20, 512), (32, 20, 512)), ((4, 5, 6), (6,), (4, 5, 6)),
+                                    ((3, 1, 7), (1, 5, 1), (3, 5, 7)), ((1000003,), (1000003,), (1000003,)),
+                                    ((2, 3, 4, 5), (5,), (2, 3, 4, 5)), ((32, 64, 28, 28), (32, 64, 28, 28), (32, 64, 28, 28))])
+def test_add(oracle, cuda_lib, shapes, dtype):
+    lib, handle = cuda_lib
+    as_, bs, cs = shapes
+    g = torch.Generator().manual_seed(4)
+    a = (torch.randn(as_, generator=g) * 100).to(dtype)
+    b = torch.randn(bs, generator=g).to(dtype)
+    want = oracle.add(a.numpy(), b.numpy()).reshape(cs)
+    cd = torch.zeros(cs, dtype=dtype, device=DEV)
+    ops.add(lib, handle, cd, a.to(DEV), b.to(DEV))
+    torch.cuda.synchronize()
+    got = cd.cpu().numpy()
+    if dtype == torch.float16:
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    else:
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("which", ["a", "b"])
+def test_add_inplace(oracle, cuda_lib, which):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(44)
+    a = torch.randn((33, 129), generator=g).half()
+    b = torch.randn((33, 129), generator=g).half()
+    want = oracle.add(a.numpy(), b.numpy())
+    ad, bd = a.to(DEV), b.to(DEV)
+    cd = ad if which == "a" else bd
+    ops.add(lib, handle, cd, ad, bd)
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(cd).reshape(33, 129), want.view(np.uint16))
+
+
+def test_add_unaligned_views(oracle, cuda_lib):
+    """Contiguous tensors that start 2 bytes into an allocation."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(45)
+    n = 4099
+    a = torch.randn(n + 1, generator=g).half()
+    b = torch.randn(n + 1, generator=g).half()
+    want = oracle.add(a[1:].numpy(), b[1:].numpy())
+    ad, bd, cd = a.to(DEV), b.to(DEV), torch.zeros(n + 1, dtype=torch.float16, device=DEV)
+    ops.add(lib, handle, cd[1:], ad[1:], bd[1:])
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(cd)[1:], want.view(np.uint16))
+    assert _bits(cd)[0] == 0
+
+
+# ---- causal softmax --------------------------------------------------------------
+@pytest.mark.parametrize("shape,strides", [((32, 20, 512), None), ((32, 20, 512), (20480, 1024, 1)), ((5, 64), None),
+                                           ((2, 7, 7), None), ((3, 1, 9), None), ((2, 128, 4096), None),
+                                           ((4, 33, 1000), None), ((1, 3, 20000), None), ((2, 2, 70000), None)])
+def test_causal_softmax(oracle, cuda_lib, shape, strides):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(5)
+    y = (torch.randn(shape, generator=g) * 2).half()
+    want = oracle.causal_softmax(y.numpy().copy())
+    yd = y.to(DEV)
+    if strides is not None:
+        yd = rearrange_tensor(yd, strides)
+    ops.causal_softmax(lib, handle, yd)
+    torch.cuda.synchronize()
+    got = _bits(yd).reshape(shape)
+    _close(got, want, 2e-3, 2e-3)
+    # masked entries are exact zeros, as the reference's own test demands
+    assert np.array_equal(got == 0, want.view(np.uint16) == 0) or (got[want.view(np.uint16) == 0] == 0).all()
+
+
+# ---- random sample (index-exact) ---------------------------------------------------
+REF_CASES = [(512, 0.92, 0.8, 3, 0.5), (4096, 0.95, 0.9, 5, 1.0), (16384, 0.85, 0.85, 10, 2.0),
+             (512, 0.92, 0.0, 3, 0.5), (4096, 0.95, 0.9, 1, 1.0), (16384, 0.85, 0.0, 1, 2.0),
+             (32000, 0.8, 0.8, 50, 1.0), (32000, 0.8, 1.0, 25, 1.0)]
+
+
+@pytest.mark.parametrize("voc,u,topp,topk,temp", REF_CASES + [(40, 0.5, 1.0, 64, 1.0), (7, 0.99, 0.9, 3, 0.7),
+                                                              (128256, 0.3, 0.9, 50, 0.8), (1000, 0.0, 0.5, 2, 1.5)])
+@pytest.mark.parametrize("dist", ["uniform", "normal3"])
+def test_random_sample_single_row_abi(oracle, cuda_lib, voc, u, topp, topk, temp, dist):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(6)
+    for _ in range(2):
+        logits = torch.rand(voc, generator=g).half() if dist == "uniform" else (torch.randn(voc, generator=g) * 3).half()
+        want = oracle.random_sample(logits.numpy(), u, topp, topk, temp, previous=12345)
+        res = torch.full((1,), 12345, dtype=torch.int64, device=DEV)
+        ops.random_sample(lib, handle, res, logits.to(DEV), u, topp, topk, temp)
+        torch.cuda.synchronize()
+        assert int(res[0]) == want
+
+
+@pytest.mark.parametrize("voc,rows,topp,topk,temp,dist", [
+    (128256, 64, 0.9, 50, 0.8, "normal3"), (32000, 96, 0.8, 50, 1.0, "uniform"), (32000, 64, 1.0, 25, 1.0, "uniform"),
+    (16384, 64, 0.85, 10, 2.0, "normal3"), (5000, 200, 0.95, 64, 0.3, "normal3"), (777, 50, 0.9, 7, 1.0, "coarse"),
+    (4096, 32, 0.9, 40, 1.0, "constant"), (8192, 16, 0.9, 50, 1.0, "ascending"), (8192, 16, 0.9, 50, 1.0, "descending")])
+def test_random_sample_batch_with_trace(oracle, cuda_lib, voc, rows, topp, topk, temp, dist):
+    """Batched extension: the denominator, the top-k order and probabilities and
+    the final index all equal the oracle's, row by row."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(7)
+    if dist == "uniform":
+        logits = torch.rand((rows, voc), generator=g).half()
+    elif dist == "normal3":
+        logits = (torch.randn((rows, voc), generator=g) * 3).half()
+    elif dist == "coarse":  # few distinct values: ties everywhere
+        logits = torch.randint(0, 12, (rows, voc), generator=g).half()
+    elif dist == "constant":
+        logits = torch.full((rows, voc), 1.5).half()
+    elif dist == "ascending":
+        logits = (torch.arange(voc).float() / voc * 8).half().repeat(rows, 1)
+    else:
+        logits = (torch.arange(voc, 0, -1).float() / voc * 8).half().repeat(rows, 1)
+    u = torch.rand(rows, generator=g)
+    ld, ud = logits.to(DEV), u.to(DEV)
+    res = torch.full((rows,), 999, dtype=torch.int64, device=DEV)
+    trace = torch.zeros((rows, 129), dtype=torch.float32, device=DEV)
+    with ops.RandomSampleOp(lib, handle, res[:1], ld[0]) as op:
+        op.batch(res, ld, ud, topp, topk, temp, trace=trace)
+        torch.cuda.synchronize()
+        res2 = torch.full((rows,), 999, dtype=torch.int64, device=DEV)
+        op.batch(res2, ld, ud, topp, topk, temp)  # workspace reuse, no trace
+        torch.cuda.synchronize()
+    tr = trace.cpu().numpy()
+    k = min(topk, voc)
+    bad = []
+    for r in range(rows):
+        row = logits[r].numpy()
+        want = oracle.random_sample(row, float(u[r]), topp, topk, temp, previous=999)
+        ot = oracle.random_sample_trace(row, topk, temp)
+        got_idx = tr[r, 1:1 + k].view(np.uint32).astype(np.uint64)
+        ok = (np.array_equal(got_idx, ot["top_idx"]) and tr[r, 0] == ot["denom"]
+              and np.array_equal(tr[r, 65:65 + k], ot["top_p"].astype(np.float32))
+              and int(res[r]) == want and int(res2[r]) == want)
+        if not ok:
+            bad.append((r, int(res[r]), want, float(tr[r, 0]), float(ot["denom"])))
+    assert not bad, bad[:5]
+
+
+def test_random_sample_argmax_ties(oracle, cuda_lib):
+    lib, handle = cuda_lib
+    logits = torch.zeros(5000).half()
+    logits[[77, 4000, 123]] = 3.0
+    logits[10] = -0.0
+    res = torch.zeros(1, dtype=torch.int64, device=DEV)
+    ops.random_sample(lib, handle, res, logits.to(DEV), 0.5, 0.0, 5, 1.0)
+    torch.cuda.synchronize()
+    assert int(res[0]) == 77 == oracle.random_sample(logits.numpy(), 0.5, 0.0, 5, 1.0)
+
+
+# ---- descriptor validation: same status codes as the reference ------------------------
+def test_status_codes(cuda_lib):
+    import ctypes
+
+    from operators_b200 import DeviceEnum, InfiniopError, create_handle, open_lib
+
+    lib, handle = cuda_lib
+    h16 = torch.zeros((4, 8), dtype=torch.float16, device=DEV)
+    f32 = torch.zeros((4, 8), dtype=torch.float32, device=DEV)
+
+    def status(fn):
+        with pytest.raises(InfiniopError) as e:
+            fn()
+        return e.value.status
+
+    assert status(lambda: ops.SwiGLUOp(lib, handle, h16, h16, h16[:2])) == 2       # BAD_PARAM (shape mismatch of a/b)
+    assert status(lambda: ops.SwiGLUOp(lib, handle, f32, f32, f32)) == 3           # BAD_TENSOR_DTYPE
+    assert status(lambda: ops.SwiGLUOp(lib, handle, h16.t(), h16.t(), h16.t())) == 5  # BAD_TENSOR_STRIDES
+    assert status(lambda: ops.SwiGLUOp(lib, handle, h16[0], h16[0], h16[0])) == 4  # BAD_TENSOR_SHAPE
+    assert status(lambda: ops.AddOp(lib, handle, h16, h16, h16[:, :3])) == 4
+    assert status(lambda: ops.AddOp(lib, handle, h16, h16, f32)) == 3
+    assert status(lambda: ops.AddOp(lib, handle, h16[:, ::2], h16[:, ::2], h16[:, ::2])) == 5
+    assert status(lambda: ops.RMSNormOp(lib, handle, h16, h16, h16[0, :4])) == 4
+    assert status(lambda: ops.CausalSoftmaxOp(lib, handle, h16[0])) == 4
+    assert status(lambda: ops.CausalSoftmaxOp(lib, handle, f32)) == 3
+    assert status(lambda: ops.RoPEOp(lib, handle, h16, torch.zeros(4, dtype=torch.int64, device=DEV), f32, f32)) == 4
+    assert status(lambda: create_handle(lib, DeviceEnum.DEVICE_CPU)) == 8          # no CPU path in this library
+    assert status(lambda: create_handle(lib, DeviceEnum.DEVICE_CUDA, 1000)) == 8
+    assert status(lambda: create_handle(lib, DeviceEnum.DEVICE_CUDA, -1)) == 2
+    assert lib.infiniopCreateHandle(None, 1, 0) == 6
