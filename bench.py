@@ -63,34 +63,37 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
-def make_inputs(seed, rows_fraction=1.0):
-    """Seeded CPU tensors of the six configurations (fp32 draws cast to fp16)."""
+def make_inputs(seed, rows_fraction=1.0, only=None):
+    """Seeded CPU tensors of the six configurations (fp32 draws cast to fp16).
+    `only` names one operator: the other operators then get one-row stand-ins."""
     import torch
 
     g = torch.Generator().manual_seed(seed)
 
-    def frac(n):
+    def frac(n, op=None):
+        if only is not None and op != only:
+            return 1
         return max(1, int(round(n * rows_fraction)))
 
     d = {}
-    d["rms_x"] = (torch.rand((frac(RMS_N), RMS_D), generator=g) * 2 - 1).half()
+    d["rms_x"] = (torch.rand((frac(RMS_N, "rms_norm"), RMS_D), generator=g) * 2 - 1).half()
     d["rms_w"] = (torch.rand(RMS_D, generator=g) * 2 - 1).half()
-    nt = frac(ROPE_T)
+    nt = frac(ROPE_T, "rope")
     d["rope_t"] = torch.randn((nt, ROPE_H, ROPE_DH), generator=g).half()
     d["rope_pos"] = torch.arange(nt, dtype=torch.int64)
     from operators_b200.ops import sin_cos_table
 
     d["rope_sin"], d["rope_cos"] = sin_cos_table(ROPE_T, ROPE_DH, 1e4)
     # 235M-element normal draws dominate set-up time: draw once in fp32 chunks
-    gu = torch.empty((frac(SWI_T), 2 * SWI_DI), dtype=torch.float16)
+    gu = torch.empty((frac(SWI_T, "swiglu"), 2 * SWI_DI), dtype=torch.float16)
     step = 512
     for r in range(0, gu.shape[0], step):
         gu[r:r + step] = torch.randn((min(step, gu.shape[0] - r), 2 * SWI_DI), generator=g).half()
     d["gate_up"] = gu
-    d["add_a"] = torch.randn((frac(ADD_T), ADD_D), generator=g).half()
-    d["add_b"] = torch.randn((frac(ADD_T), ADD_D), generator=g).half()
-    d["att"] = (torch.randn((frac(SM_H), SM_Q, SM_KV), generator=g) * 2).half()
-    nb = frac(RS_B)
+    d["add_a"] = torch.randn((frac(ADD_T, "add"), ADD_D), generator=g).half()
+    d["add_b"] = torch.randn((frac(ADD_T, "add"), ADD_D), generator=g).half()
+    d["att"] = (torch.randn((frac(SM_H, "causal_softmax"), SM_Q, SM_KV), generator=g) * 2).half()
+    nb = frac(RS_B, "random_sample")
     d["logits"] = (torch.randn((nb, RS_V), generator=g) * 3).half()
     d["u"] = torch.rand(nb, generator=g)
     return d
@@ -114,53 +117,53 @@ def sample_bytes(inputs):
 
 # ---- clocks ---------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples of one GPU while a region runs."""
+    """SM clock and throttle reasons of one GPU, polled through NVML (read-only
+    queries) from a host thread while the timed region runs."""
 
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
-    def __init__(self, index):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, torch_index):
+        self.samples, self.reason_bits, self.stop_flag, self.thread = [], 0, False, None
+        self.handle, self.max_mhz = None, None
+        try:
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                uuid = str(torch.cuda.get_device_properties(torch_index).uuid)
+                if not uuid.startswith("GPU-"):
+                    uuid = "GPU-" + uuid
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(torch_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.handle = None
+
+    def _poll(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+            except Exception:
+                break
+            time.sleep(0.001)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._poll, daemon=True)
             self.thread.start()
-        except Exception:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, smax, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            f = [x.strip() for x in ln.split(",")]
-            if len(f) < 7:
-                continue
-            try:
-                sm.append(float(f[0]))
-                smax = float(f[1])
-            except ValueError:
-                continue
-            for nme, val in zip(names, f[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(nme)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        sm = sorted(self.samples)
+        reasons = sorted(k for k, bit in self.REASONS.items() if self.reason_bits & bit)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz, "reasons": reasons,
                 "samples": len(sm)}
 
 
@@ -220,9 +223,26 @@ def run_b200(args):
     lib = open_lib(os.path.join(ROOT, "operators_b200", "lib"))
     handle = create_handle(lib, DeviceEnum.DEVICE_CUDA, local)
 
-    inputs = make_inputs(1000 + rank)
+    inputs = make_inputs(1000 + rank, only=args.only)
     step = DecodeStep(lib, handle, dev, inputs)
     calls = step.calls()
+    if args.only:  # profiling runs: a single operator, nothing else launched
+        calls = [c for c in calls if c[0] == args.only]
+        step.launches_per_step = 1
+        for _ in range(args.warmup):
+            calls[0][1](None)
+        torch.cuda.synchronize()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            calls[0][1](None)
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        print(json.dumps({"only": args.only, "ms": round(ms, 5), "gbs": round(ALGO_BYTES[args.only] / ms / 1e6, 1),
+                          "note": "back-to-back launches of one operator; not a bench value"}))
+        return
     stream = torch.cuda.current_stream()
     sptr = stream.cuda_stream
 
@@ -480,6 +500,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
+    ap.add_argument("--only", choices=OPS, help="launch a single operator at its configuration (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":

@@ -145,13 +145,13 @@ void launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uin
                  cudaStream_t st) {
     const uint64_t rows = d->batch * d->seq_len;
     if (cta_row) {
-        const uint64_t cap = (uint64_t) d->sm_count * (2048 / threads);
+        const uint64_t cap = 0x7FFFFFFFull;// one CTA per row; rows beyond 2^31 loop
         const uint32_t grid = (uint32_t) (rows < cap ? rows : cap);
         causal_softmax_regs_kernel<VPT, true>
             <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i);
     } else {
         const uint64_t ctas = (rows + 7) / 8;
-        const uint64_t cap = (uint64_t) d->sm_count * 8;
+        const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
         causal_softmax_regs_kernel<VPT, false>
             <<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i);

@@ -94,7 +94,14 @@ __device__ __forceinline__ uint16_t f32_to_f16_ref(float v) {
 
 __device__ __forceinline__ float f16_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 
+// Two conversions at once: one packed cvt.rz when both values are in range,
+// the element-wise rule otherwise.
 __device__ __forceinline__ uint32_t pack2_ref(float lo, float hi) {
+    if (fmaxf(fabsf(lo), fabsf(hi)) < 65536.0f) {// false for NaN as well
+        uint32_t r;
+        asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+        return r;
+    }
     return (uint32_t) f32_to_f16_ref(lo) | ((uint32_t) f32_to_f16_ref(hi) << 16);
 }
 __device__ __forceinline__ float2 unpack2(uint32_t w) {

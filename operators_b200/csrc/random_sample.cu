@@ -259,6 +259,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     const bool sampling = a.topp > 0.f && a.topk > 1;
     int k = a.topk > n ? n : a.topk;
+    const long long t_entry = clock64();
+    int stamp_i = 0;
+    auto stamp = [&]() {// phase boundary -> trace buffer (thread 0, only when tracing)
+        if (a.debug && tid == 0 && stamp_i < 15) {
+            a.debug[(int64_t) row * kDebugStride + 129 + stamp_i] = (float) (clock64() - t_entry);
+        }
+        ++stamp_i;
+    };
 
     // ---- pass A: logits -> keys (working copy), per-thread and row maximum --
     const bool in_aligned = (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
@@ -319,6 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         return;
     }
 
+    stamp();// 0: row converted to keys
     if (tid < kWarps) sm.list_cnt[tid] = 0;
     if (tid == 0) {
         sm.overflow = 0;
@@ -341,6 +350,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // Fewer than k threads hold data (tiny rows): every element is a candidate.
     const uint32_t L = have_lt_k ? 1u : lo;
     __syncthreads();// working copy and list counters visible to the whole CTA
+    stamp();// 1: lower bound of the k-th largest key
 
     // ---- pass B: candidates (key >= L) in index order ------------------------
     const uint32_t span = (nblk + kWarps - 1) / kWarps;// blocks per warp, contiguous
@@ -356,6 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     }
     __syncthreads();
+    stamp();// 2: candidate lists
 
     // ---- exact top-k with the reference's tie order (warp 0) -----------------
     TopBuf tb{0, 0, 0, 0};
@@ -398,6 +409,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         sm.top_idx[lane + 32] = tb.i1;
     }
     __syncthreads();
+    stamp();// 3: top-k in order
     const float M = val_of(sm.top_key[0]);
     const float T = a.temperature;
 
@@ -457,6 +469,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     }
     __syncthreads();
+    stamp();// 4: records patched
 
     // ---- denominator S: sequential fp32 sum over the permuted row ------------
     if (warp == 0) {
@@ -472,7 +485,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncthreads();
 
-    for (uint32_t pass = 0; pass <= nblk && !sm.done; ++pass) {// a pass ends at the first order-dependent block
+    stamp();// 5: top-k terms summed
+    uint32_t pass = 0;
+    for (; pass <= nblk && !sm.done; ++pass) {// a pass ends at the first order-dependent block
         const float s = sm.s;
         const uint32_t pos = sm.pos;
         const uint32_t sbits = __float_as_uint(s);
@@ -563,6 +578,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         __syncthreads();
     }
 
+    stamp();// 6: denominator
+    if (a.debug && tid == 0) a.debug[(int64_t) row * kDebugStride + 129 + 15] = (float) pass;
     // ---- probabilities of the top-k, top-p cut and the pick ------------------
     if (warp == 0) {
         const float S = sm.s;

@@ -5,7 +5,7 @@
 
 namespace b200 {
 
-constexpr int kDebugStride = 1 + 2 * 64;// floats per row of the optional trace buffer
+constexpr int kDebugStride = 1 + 2 * 64 + 16;// floats per row of the optional trace buffer
 
 struct RandomSampleArgs {
     const uint16_t *logits; // fp16 rows
@@ -21,7 +21,9 @@ struct RandomSampleArgs {
     float temperature;
     int voc;
     // Optional device trace per row: [0] = softmax denominator S, [1..64] = the
-    // top-k indices (bit patterns), [65..128] = their truncated probabilities.
+    // top-k indices (bit patterns), [65..128] = their truncated probabilities,
+    // [129..144] = SM cycle counts at the phase boundaries (relative to entry)
+    // followed by the number of denominator passes.
     float *debug;
 };
 

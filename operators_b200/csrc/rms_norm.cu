@@ -145,13 +145,13 @@ void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t 
     auto *yp = reinterpret_cast<uint16_t *>(y);
     auto *xp = reinterpret_cast<const uint16_t *>(x);
     if (cta_row) {
-        const uint64_t cap = (uint64_t) d->sm_count * (2048 / threads);
+        const uint64_t cap = 0x7FFFFFFFull;// one CTA per row; rows beyond 2^31 loop
         const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap);
         rms_norm_regs_kernel<VPT, W_F16, true>
             <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon);
     } else {
         const uint64_t ctas = (d->n + 7) / 8;
-        const uint64_t cap = (uint64_t) d->sm_count * 8;
+        const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
         rms_norm_regs_kernel<VPT, W_F16, false>
             <<<grid, 256, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon);

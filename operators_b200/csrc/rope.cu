@@ -209,7 +209,7 @@ INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *
         threads = tokens_per_cta * tpt;
     }
     const uint64_t ctas = (d->seq_len + tokens_per_cta - 1) / tokens_per_cta;
-    const uint64_t cap = (uint64_t) d->sm_count * 32;
+    const uint64_t cap = 0x7FFFFFFFull;// one CTA per token group; more tokens than that loop
     const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
     if (v8) {
         rope_kernel<8, true><<<grid, threads, 0, st>>>(tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1, tpt, slices);

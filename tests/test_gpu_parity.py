@@ -227,7 +227,7 @@ def test_random_sample_batch_with_trace(oracle, cuda_lib, voc, rows, topp, topk,
     u = torch.rand(rows, generator=g)
     ld, ud = logits.to(DEV), u.to(DEV)
     res = torch.full((rows,), 999, dtype=torch.int64, device=DEV)
-    trace = torch.zeros((rows, 129), dtype=torch.float32, device=DEV)
+    trace = torch.zeros((rows, 145), dtype=torch.float32, device=DEV)
     with ops.RandomSampleOp(lib, handle, res[:1], ld[0]) as op:
         op.batch(res, ld, ud, topp, topk, temp, trace=trace)
         torch.cuda.synchronize()
