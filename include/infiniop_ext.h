@@ -39,4 +39,32 @@ INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchTrace(infiniopRandomSampl
                                                              void const *random_vals, float topp, int topk,
                                                              float temperature, void *trace, void *stream);
 
+/*
+ * No counterpart in the reference library.
+ *
+ * infiniopRandomSampleBatch for callers that cannot hand over a workspace:
+ * hosts that gave all device memory to their own arena and may not call
+ * cudaMalloc where they sample, or plug-ins that only ever receive input and
+ * output pointers.  The per-row working copies live in a 32 MiB array that is
+ * part of the library image on every GPU that loads it, so the call performs
+ * no allocation of any kind (no cudaMalloc / cudaFree, no allocating library
+ * routine).  Inputs, outputs and semantics are those of
+ * infiniopRandomSampleBatch.
+ *
+ * Limits and rules:
+ *  - rows * round_up(voc, 256) * 2 + 256 bytes must fit in 32 MiB (64 rows of
+ *    128256 logits do); larger requests return STATUS_INSUFFICIENT_WORKSPACE
+ *    and print the sizes.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress with that device current); make that first call
+ *    before starting any stream capture.
+ *  - All calls on a device share the one array.  Each call rewrites every byte
+ *    it later reads, so nothing has to be cleared between calls, but two calls
+ *    that overlap on the GPU (different streams) race: serialise them.
+ */
+INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchStatic(infiniopRandomSampleDescriptor_t desc, void *results,
+                                                              void const *logits, int64_t row_stride, uint64_t rows,
+                                                              void const *random_vals, float topp, int topk,
+                                                              float temperature, void *stream);
+
 #endif /* INFINIOP_B200_EXT_H */

@@ -763,3 +763,69 @@ INFINIOP_API infiniopStatus_t infiniopRandomSampleBatch(infiniopRandomSampleDesc
     return infiniopRandomSampleBatchTrace(desc, workspace, workspace_size, results, logits, row_stride, rows,
                                           random_vals, topp, topk, temperature, nullptr, stream);
 }
+
+// ---- batched sampling without a caller-provided workspace -----------------------
+//
+// Some hosts of this library may not allocate device memory at the point where
+// they sample: a serving loop that has handed every byte of HBM to its own KV
+// cache / arena allocator and has no workspace slab to lend, or a plug-in that
+// is only given input and output pointers.  For them the working copy of the
+// rows lives in a fixed array inside the library image.  Every GPU that loads
+// the library carries these 32 MiB until the process exits.
+constexpr uint64_t kStaticScratchBytes = 32ull << 20;
+static __device__ __align__(256) unsigned char g_sample_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void *g_scratch_addr[kMaxDevices];// device address of g_sample_scratch per device ordinal
+bool g_scratch_ready[kMaxDevices];
+}// namespace
+
+INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchStatic(infiniopRandomSampleDescriptor_t desc, void *results,
+                                                              void const *logits, int64_t row_stride, uint64_t rows,
+                                                              void const *random_vals, float topp, int topk,
+                                                              float temperature, void *stream) {
+    if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (results == nullptr || logits == nullptr || random_vals == nullptr) return STATUS_BAD_PARAM;
+    if (rows == 0) return STATUS_SUCCESS;
+    auto *d = reinterpret_cast<RandomSampleDesc *>(desc);
+    if (d->device_id < 0 || d->device_id >= kMaxDevices) return STATUS_BAD_DEVICE;
+    if (rows > 0x7FFFFFFFull || random_sample_workspace_bytes(d->voc, (int) rows) > kStaticScratchBytes) {
+        fprintf(stderr,
+                "infiniop[b200]: infiniopRandomSampleBatchStatic: %llu rows of %d logits need %llu bytes of scratch, "
+                "the built-in array holds %llu; use infiniopRandomSampleBatch with a workspace\n",
+                (unsigned long long) rows, d->voc,
+                (unsigned long long) (rows > 0x7FFFFFFFull ? 0 : random_sample_workspace_bytes(d->voc, (int) rows)),
+                (unsigned long long) kStaticScratchBytes);
+        return STATUS_INSUFFICIENT_WORKSPACE;
+    }
+    DeviceGuard guard(d->device_id);
+    if (!g_scratch_ready[d->device_id]) {
+        // The array's name is only a host-side handle; the kernel needs the
+        // address the array has on THIS device, asked for once per device with
+        // that device current (the guard above made it so).
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_sample_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            fprintf(stderr, "infiniop[b200]: cudaGetSymbolAddress(g_sample_scratch) failed: %s\n", cudaGetErrorString(e));
+            cudaGetLastError();
+            return STATUS_EXECUTION_FAILED;
+        }
+        g_scratch_addr[d->device_id] = p;
+        g_scratch_ready[d->device_id] = true;
+    }
+    RandomSampleArgs a{};
+    a.logits = reinterpret_cast<const uint16_t *>(logits);
+    a.logits_stride = row_stride;
+    a.result = reinterpret_cast<uint64_t *>(results);
+    a.result_stride = 1;
+    a.random_vals = reinterpret_cast<const float *>(random_vals);
+    a.random_val = 0.f;
+    a.topp = topp;
+    a.topk = topk;
+    a.temperature = temperature;
+    a.voc = d->voc;
+    a.debug = nullptr;
+    return random_sample_launch(a, (int) rows, g_scratch_addr[d->device_id], kStaticScratchBytes,
+                                reinterpret_cast<cudaStream_t>(stream));
+}

@@ -50,6 +50,8 @@ def _declare(lib):
         "infiniopGetRandomSampleBatchWorkspaceSize": [D, c_uint64, POINTER(c_uint64)],
         "infiniopRandomSampleBatch": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_int64, c_uint64, c_void_p,
                                       c_float, c_int, c_float, c_void_p],
+        "infiniopRandomSampleBatchStatic": [D, c_void_p, c_void_p, c_int64, c_uint64, c_void_p, c_float, c_int, c_float,
+                                            c_void_p],
         "infiniopRandomSampleBatchTrace": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_int64, c_uint64, c_void_p,
                                            c_float, c_int, c_float, c_void_p, c_void_p],
     }
@@ -231,6 +233,14 @@ class RandomSampleOp(_Op):
             check_error(self.lib.infiniopRandomSampleBatchTrace(*args, trace.data_ptr(), _stream_ptr(stream)))
         else:
             check_error(self.lib.infiniopRandomSampleBatch(*args, _stream_ptr(stream)))
+
+
+    def batch_static(self, results, logits, random_vals, topp, topk, temperature, stream=None):
+        """`batch` without a workspace: the library's built-in scratch array is
+        used, nothing is allocated (see infiniopRandomSampleBatchStatic)."""
+        check_error(self.lib.infiniopRandomSampleBatchStatic(
+            self.desc, results.data_ptr(), logits.data_ptr(), logits.stride(0), logits.shape[0],
+            random_vals.data_ptr(), topp, topk, temperature, _stream_ptr(stream)))
 
 
 # ---- one-shot forms ----------------------------------------------------------
