@@ -6,14 +6,14 @@
 // (src/ops/causal_softmax/cpu/causal_softmax_cpu.cc:52-82): row i keeps columns
 // j <= total - seq + i, masked columns become exact zeros, the maximum and the
 // sum of expf(x - max) are taken over the visible columns in fp32 and each
-// output is expf(x - max) / sum narrowed with the reference's truncating
-// conversion.  Departures: the fp32 sum is a tree (not sequential) and the
-// quotient is formed as e * (1/sum) with one fused correction step, which
-// returns the correctly rounded quotient in all but rare half-ulp cases.
+// output is exp(x - max) / sum narrowed with the reference's truncating
+// conversion.  Departures, all far inside the 2e-3 tolerance: the fp32 sum is a
+// tree (not sequential), exp is 2^(.) on the special-function unit (relative
+// error ~2^-20) and the quotient is e * (1/sum).
 //
 // HBM-bound: every visible element is read once and every element written
-// once; masked tails are never read.  A row lives in registers as fp32 between
-// the three steps (max, exp+sum, scale), owned by one warp or one CTA.
+// once; masked tails are never read.  A row lives in registers between the
+// three steps (max, exp+sum, scale), owned by one warp or one CTA.
 #include "common.cuh"
 
 #include <new>
@@ -36,6 +36,13 @@ __device__ __forceinline__ uint64_t visible_cols(uint64_t i, uint64_t seq_len, u
     return last >= total - 1 ? total : last + 1;
 }
 
+// The row stays in registers as the PACKED fp16 it was loaded as (4 registers
+// per vector), which keeps the register count low enough for 12-16 resident
+// rows per SM, i.e. ~100 KB of loads in flight.  The maximum is taken on the
+// packed halves; the exponential is evaluated twice (once for the sum, once for
+// the output) as the CPU code does, which costs less than holding the row in
+// fp32 would cost in occupancy.  (The compiler is free to keep the first
+// evaluation instead; measured, that is the faster of the two on B200.)
 template<int VPT, bool CTA_ROW>
 __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total,
                                            uint32_t vecs, int64_t stride_b, int64_t stride_i) {
@@ -46,44 +53,49 @@ __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t 
     const uint64_t rows_per_cta = CTA_ROW ? 1 : (blockDim.x >> 5);
     const uint64_t row0 = (uint64_t) blockIdx.x * rows_per_cta + (CTA_ROW ? 0 : (threadIdx.x >> 5));
     const uint64_t row_step = (uint64_t) gridDim.x * rows_per_cta;
+    constexpr uint32_t kNegInf2 = 0xFC00FC00u;// two fp16 -inf
 
     for (uint64_t row = row0; row < rows; row += row_step) {
         const uint64_t b = row / seq_len, i = row - b * seq_len;
         uint16_t *yr = y + (int64_t) b * stride_b + (int64_t) i * stride_i;
         const uint32_t vis = (uint32_t) visible_cols(i, seq_len, total);
 
-        float f[VPT][8];
         uint4 raw[VPT];
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
             const uint32_t j = t + u * group;
             if (j < vecs && j * 8 < vis) raw[u] = ld_stream(yr + (uint64_t) j * 8);
+            else raw[u] = make_uint4(kNegInf2, kNegInf2, kNegInf2, kNegInf2);// masked: exp -> 0, output 0
         }
-        float m = -INFINITY;
+        __half2 m2 = __halves2half2(__ushort_as_half((unsigned short) 0xFC00), __ushort_as_half((unsigned short) 0xFC00));
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
             const uint32_t j = t + u * group;
-            const bool loaded = j < vecs && j * 8 < vis;
-            const uint32_t *p = reinterpret_cast<const uint32_t *>(&raw[u]);
+            uint32_t *p = reinterpret_cast<uint32_t *>(&raw[u]);
+            if (j * 8 < vis && j * 8 + 8 > vis) {// the one vector that straddles the mask boundary
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float2 v = loaded ? unpack2(p[k]) : make_float2(-INFINITY, -INFINITY);
-                if (j * 8 + 2 * k >= vis) v.x = -INFINITY;
-                if (j * 8 + 2 * k + 1 >= vis) v.y = -INFINITY;
-                f[u][2 * k] = v.x;
-                f[u][2 * k + 1] = v.y;
-                m = fmaxf(m, fmaxf(v.x, v.y));
+                for (int k = 0; k < 4; ++k) {
+                    if (j * 8 + 2 * k >= vis) p[k] = (p[k] & 0xFFFF0000u) | 0xFC00u;
+                    if (j * 8 + 2 * k + 1 >= vis) p[k] = (p[k] & 0x0000FFFFu) | 0xFC000000u;
+                }
             }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) m2 = __hmax2(m2, *reinterpret_cast<const __half2 *>(&p[k]));
         }
+        float m = fmaxf(__low2float(m2), __high2float(m2));
         m = CTA_ROW ? cta_reduce<true>(m, red) : warp_max(m);
+        // exp(x - m) = 2^(x*log2e - m*log2e); the rounding of m*log2e is common to
+        // the whole row and cancels in the quotient.
+        const float mk = -m * kLog2e;
         float s = 0.f;
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
+            const uint32_t *p = reinterpret_cast<const uint32_t *>(&raw[u]);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                // masked slots hold -inf: expf(-inf - m) = 0 contributes nothing
-                f[u][e] = expf(__fsub_rn(f[u][e], m));
-                s += f[u][e];
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = unpack2(p[k]);
+                s += fast_exp2(fmaf(f.x, kLog2e, mk));
+                s += fast_exp2(fmaf(f.y, kLog2e, mk));
             }
         }
         s = CTA_ROW ? cta_reduce<false>(s, red) : warp_sum(s);
@@ -92,18 +104,16 @@ __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t 
         for (int u = 0; u < VPT; ++u) {
             const uint32_t j = t + u * group;
             if (j < vecs) {
+                const uint32_t *p = reinterpret_cast<const uint32_t *>(&raw[u]);
                 uint4 out;
                 uint32_t *po = reinterpret_cast<uint32_t *>(&out);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    float q[2];
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const float e = f[u][2 * k + h];
-                        const float q0 = __fmul_rn(e, r);
-                        q[h] = fmaf(fmaf(-q0, s, e), r, q0);
-                    }
-                    po[k] = pack2_ref(q[0], q[1]);
+                    const float2 f = unpack2(p[k]);
+                    const float q0 = __fmul_rn(fast_exp2(fmaf(f.x, kLog2e, mk)), r);
+                    const float q1 = __fmul_rn(fast_exp2(fmaf(f.y, kLog2e, mk)), r);
+                    // quotients lie in [0, 1]: the packed truncating convert needs no range check
+                    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(po[k]) : "f"(q1), "f"(q0));
                 }
                 st_stream(yr + (uint64_t) j * 8, out);
             }
@@ -214,13 +224,15 @@ INFINIOP_API infiniopStatus_t infiniopCausalSoftmax(infiniopCausalSoftmaxDescrip
         int vpt;
         bool cta_row;
         uint32_t threads = 256;
-        if (big && vecs <= 128) {
+        if (big && vecs <= 256) {
             cta_row = false;
             const uint32_t need = (vecs + 31) / 32;
-            vpt = need <= 1 ? 1 : need <= 2 ? 2 : 4;
+            vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
         } else {
             cta_row = true;
             const uint32_t min_vpt = (vecs + 1023) / 1024;
+            // measured at [32,512,4096]: 4 vectors per thread (128 threads per 4096-column
+            // row) 50 us, 8 per thread 52 us, 2 per thread 63 us
             uint32_t want = big ? 4 : min_vpt;
             if (want < min_vpt) want = min_vpt;
             vpt = want <= 1 ? 1 : want <= 2 ? 2 : want <= 4 ? 4 : 8;

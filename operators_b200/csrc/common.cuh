@@ -108,6 +108,15 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
     return __half22float2(*reinterpret_cast<const __half2 *>(&w));
 }
 
+// 2^x by the special-function unit (ex2.approx: relative error about 2^-22,
+// -inf -> +0, results below 2^-126 flush to zero).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+constexpr float kLog2e = 1.4426950408889634f;
+
 // 128-bit accesses with the streaming (evict-first) policy.  Loads are
 // ordinary coherent loads, not the read-only path, so operators whose output
 // aliases an input (in-place SwiGLU / Add / RoPE / softmax) stay well defined.
