@@ -303,15 +303,43 @@ def run_b200(args):
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
+    # ---- vocabulary-sharded sampling (N > 1): local stage, one NCCL all-gather, finishing stage ----
+    sharded_ms = None
+    if world > 1:
+        import torch.distributed as dist
+
+        from operators_b200 import ops as _ops
+        from operators_b200.sharding import VocabShardedSampler, vocab_range
+
+        gsh = torch.Generator().manual_seed(77)  # the same logits on every rank, each keeps its columns
+        full = (torch.randn((RS_B, RS_V), generator=gsh) * 3).half()
+        ush = torch.rand(RS_B, generator=gsh).to(dev)
+        b0, e0 = vocab_range(RS_V, world, rank)
+        shard = full[:, b0:e0].contiguous().to(dev)
+        out = torch.zeros(RS_B, dtype=torch.int64, device=dev)
+        sop = _ops.RandomSampleOp(lib, handle, out[:1], shard[0])
+        sampler = VocabShardedSampler(lib, handle, sop, RS_V, b0, world)
+        for _ in range(3):
+            sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, sptr, check=False)
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        for _ in range(args.steps):
+            sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, sptr, check=False)
+        s1.record(stream)
+        barrier()
+        sharded_ms = s0.elapsed_time(s1) / args.steps
+
     # ---- max over ranks ----
-    vals = torch.tensor([ms_per_step, e2e_ms] + [per_op_ms[o] for o in OPS], dtype=torch.float64, device=dev)
+    vals = torch.tensor([ms_per_step, e2e_ms, sharded_ms or 0.0] + [per_op_ms[o] for o in OPS], dtype=torch.float64,
+                        device=dev)
     if world > 1:
         import torch.distributed as dist
 
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
     vals = vals.cpu().tolist()
-    ms_per_step, e2e_ms = vals[0], vals[1]
-    per_op_ms = dict(zip(OPS, vals[2:]))
+    ms_per_step, e2e_ms, sharded_ms = vals[0], vals[1], vals[2]
+    per_op_ms = dict(zip(OPS, vals[3:]))
 
     step_bytes = sum(ALGO_BYTES.values())
     peak, peak_kind = measured_peak()
@@ -344,6 +372,11 @@ def run_b200(args):
         "gpu_launches": step.launches_per_step * args.steps,
         "clocks": clk,
     }
+    if world > 1:
+        line["random_sample_vocab_sharded"] = {
+            "ms": round(sharded_ms, 4), "tokens_per_s": round(RS_B / (sharded_ms * 1e-3), 1),
+            "what": "64 rows, vocabulary 128256 split over %d GPUs: local candidates, one NCCL all-gather of "
+                    "%d bytes per rank, finishing kernel" % (world, RS_B * 1056)}
     sw_ms = per_op_ms["swiglu"]
     ach = ALGO_BYTES["swiglu"] / (sw_ms * 1e-3) / 1e9
     line["roofline"] = {"kernel": "swiglu_vec8_kernel", "bound": "hbm", "achieved": round(ach, 1), "peak": peak,

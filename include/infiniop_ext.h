@@ -40,6 +40,36 @@ INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchTrace(infiniopRandomSampl
                                                              float temperature, void *trace, void *stream);
 
 /*
+ * Vocabulary-sharded sampling (no counterpart in the reference, which has no
+ * multi-device code).  Each rank holds columns [shard_offset, shard_offset +
+ * voc_local) of the [rows, voc_total] logits; voc_local is the descriptor's voc.
+ *
+ *   1. infiniopRandomSampleShardLocal on every rank writes `rows` records of
+ *      infiniopRandomSampleShardRecordBytes() bytes each (local maximum, local
+ *      softmax sum, and in index order the candidates that can reach the global
+ *      top-k).
+ *   2. The host all-gathers the record buffers (rank-major: [ranks][rows][record]).
+ *   3. infiniopRandomSampleShardFinish on any rank merges them: the top-k set,
+ *      its tie order and the numerators are those of infiniopRandomSample on the
+ *      concatenated row; the denominator is the correctly rounded sum, whereas
+ *      the unsharded path reproduces the reference's sequential fp32 sum, so
+ *      about one row in a thousand can pick a neighbouring candidate.
+ *      *status_flag (device int, zeroed by the caller) becomes 1 when a shard
+ *      had more than 128 tied candidates and the row was not sampled.
+ * Only the sampling branch (topp > 0, 2 <= topk <= 64) is provided.
+ */
+INFINIOP_API uint64_t infiniopRandomSampleShardRecordBytes(void);
+INFINIOP_API infiniopStatus_t infiniopRandomSampleShardLocal(infiniopRandomSampleDescriptor_t desc, void *records,
+                                                             void const *logits, int64_t row_stride, uint64_t rows,
+                                                             uint64_t shard_offset, int topk, float temperature,
+                                                             void *stream);
+INFINIOP_API infiniopStatus_t infiniopRandomSampleShardFinish(infiniopHandle_t handle, void *results,
+                                                              void const *gathered_records, int ranks, uint64_t rows,
+                                                              uint64_t voc_total, void const *random_vals, float topp,
+                                                              int topk, float temperature, void *status_flag,
+                                                              void *stream);
+
+/*
  * No counterpart in the reference library.
  *
  * infiniopRandomSampleBatch for callers that cannot hand over a workspace:

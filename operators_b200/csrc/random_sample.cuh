@@ -5,6 +5,15 @@
 
 namespace b200 {
 
+// Object behind infiniopRandomSampleDescriptor_t.
+struct RandomSampleDesc {
+    Device device;
+    int device_id;
+    int sm_count;
+    int voc;
+    int result_len;
+};
+
 constexpr int kDebugStride = 1 + 2 * 64 + 16;// floats per row of the optional trace buffer
 
 struct RandomSampleArgs {

@@ -52,6 +52,9 @@ def _declare(lib):
                                       c_float, c_int, c_float, c_void_p],
         "infiniopRandomSampleBatchStatic": [D, c_void_p, c_void_p, c_int64, c_uint64, c_void_p, c_float, c_int, c_float,
                                             c_void_p],
+        "infiniopRandomSampleShardLocal": [D, c_void_p, c_void_p, c_int64, c_uint64, c_uint64, c_int, c_float, c_void_p],
+        "infiniopRandomSampleShardFinish": [H, c_void_p, c_void_p, c_int, c_uint64, c_uint64, c_void_p, c_float, c_int,
+                                            c_float, c_void_p, c_void_p],
         "infiniopRandomSampleBatchTrace": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_int64, c_uint64, c_void_p,
                                            c_float, c_int, c_float, c_void_p, c_void_p],
     }
@@ -60,6 +63,9 @@ def _declare(lib):
         if fn is not None:
             fn.argtypes = argtypes
             fn.restype = c_int
+    if hasattr(lib, "infiniopRandomSampleShardRecordBytes"):
+        lib.infiniopRandomSampleShardRecordBytes.argtypes = []
+        lib.infiniopRandomSampleShardRecordBytes.restype = c_uint64
     lib._b200_declared = True
 
 

@@ -291,3 +291,76 @@ def test_status_codes(cuda_lib):
     assert status(lambda: create_handle(lib, DeviceEnum.DEVICE_CUDA, 1000)) == 8
     assert status(lambda: create_handle(lib, DeviceEnum.DEVICE_CUDA, -1)) == 2
     assert lib.infiniopCreateHandle(None, 1, 0) == 6
+
+
+# ---- vocabulary-sharded sampling: both device stages on one GPU, shards played in turn ----------
+@pytest.mark.parametrize("ranks", [1, 2, 8])
+@pytest.mark.parametrize("voc,rows,topp,topk,temp,dist", [(128256, 64, 0.9, 50, 0.8, "normal3"),
+                                                          (32000, 40, 0.8, 50, 1.0, "uniform"),
+                                                          (16384, 32, 0.85, 10, 2.0, "normal3")])
+def test_vocab_sharded_sampling(oracle, cuda_lib, ranks, voc, rows, topp, topk, temp, dist):
+    """Stage 1 per shard, records concatenated in rank order (what the all-gather
+    delivers), stage 2.  The top-k and its tie order must be the oracle's in every
+    row; the index may differ in rare rows because the sharded denominator is the
+    correctly rounded sum, not the reference's sequential fp32 sum."""
+    from operators_b200.sharding import VocabShardedSampler, vocab_range
+
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(8)
+    logits = torch.rand((rows, voc), generator=g).half() if dist == "uniform" else (torch.randn((rows, voc), generator=g) * 3).half()
+    u = torch.rand(rows, generator=g)
+    ld, ud = logits.to(DEV), u.to(DEV)
+    res = torch.full((rows,), -1, dtype=torch.int64, device=DEV)
+    words = int(lib.infiniopRandomSampleShardRecordBytes()) // 4 if hasattr(lib, "infiniopRandomSampleShardRecordBytes") else 264
+    shards, samplers, keep = [], [], []
+    for r in range(ranks):
+        b, e = vocab_range(voc, ranks, r)
+        shard = ld[:, b:e]
+        op = ops.RandomSampleOp(lib, handle, res[:1], shard[0])
+        keep.append(op)
+        shards.append((shard, b))
+        samplers.append(VocabShardedSampler(lib, handle, op, voc, b, ranks, all_gather=lambda out, inp: None))
+    # play stage 1 of every rank, then hand rank 0 the gathered buffer
+    locals_ = []
+    for (shard, b), s in zip(shards, samplers):
+        local, gathered, status = s._buffers(rows, shard.device)
+        from operators_b200.utils import check_error
+        check_error(lib.infiniopRandomSampleShardLocal(s.op.desc, local.data_ptr(), shard.data_ptr(), shard.stride(0), rows,
+                                                       b, topk, temp, None))
+        locals_.append(local)
+    all_records = torch.stack(locals_)
+
+    def fake_gather(out, inp):
+        out.copy_(all_records)
+
+    samplers[0]._gather = fake_gather
+    samplers[0].sample(res, shards[0][0], ud, topp, topk, temp)
+    torch.cuda.synchronize()
+    want = [oracle.random_sample(logits[r].numpy(), float(u[r]), topp, topk, temp) for r in range(rows)]
+    same = sum(int(int(res[r]) == want[r]) for r in range(rows))
+    assert same >= rows - max(1, rows // 20), (same, rows)
+    # candidates gathered from the shards contain the oracle's top-k, in index order per shard
+    rec = all_records.cpu().numpy().view(np.uint32)
+    for r in range(0, rows, 7):
+        top = set(int(i) for i in oracle.random_sample_trace(logits[r].numpy(), topk, temp)["top_idx"])
+        have = set()
+        for k in range(ranks):
+            cnt = int(rec[k, r, 0])
+            idx = rec[k, r, 8:8 + 2 * cnt:2]
+            assert (np.diff(idx.astype(np.int64)) > 0).all()
+            have |= set(int(i) for i in idx)
+        assert top <= have
+    for op in keep:
+        op.destroy()
+
+
+def test_vocab_sharded_overflow_is_reported(cuda_lib):
+    from operators_b200.sharding import VocabShardedSampler
+
+    lib, handle = cuda_lib
+    logits = torch.full((4, 4096), 1.0, dtype=torch.float16, device=DEV)  # every element ties with every other
+    res = torch.zeros(4, dtype=torch.int64, device=DEV)
+    with ops.RandomSampleOp(lib, handle, res[:1], logits[0]) as op:
+        s = VocabShardedSampler(lib, handle, op, 4096, 0, 1)
+        with pytest.raises(RuntimeError):
+            s.sample(res, logits, torch.rand(4, device=DEV), 0.9, 20, 1.0)
