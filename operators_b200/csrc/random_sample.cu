@@ -39,6 +39,7 @@
 #include "random_sample.cuh"
 #include "random_sample_device.cuh"
 
+#include <cstdlib>
 #include <new>
 
 using namespace b200;
@@ -539,6 +540,12 @@ infiniopStatus_t random_sample_launch(const RandomSampleArgs &args_in, int rows,
             return STATUS_BAD_PARAM;
         }
         if (!(a.temperature > 0.f)) return STATUS_BAD_PARAM;
+        // Rows that fit two CTAs' shared memory never touch the workspace.  The
+        // environment switch exists so that the tests can hold both kernels to
+        // the same oracle on the same inputs.
+        const char *pick = getenv("INFINIOP_RANDOM_SAMPLE_KERNEL");
+        const bool want_global = pick != nullptr && pick[0] == 'g';
+        if (random_sample_pair_supported(a.voc) && !want_global) return random_sample_pair_launch(a, rows, st);
         if (workspace == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
         if (workspace_size < random_sample_workspace_bytes(a.voc, rows)) return STATUS_INSUFFICIENT_WORKSPACE;
         a.work = reinterpret_cast<uint16_t *>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t) 255);

@@ -36,6 +36,10 @@ struct RandomSampleArgs {
     float *debug;
 };
 
+// Shared-memory resident two-CTA form (random_sample_pair.cu): sampling branch, voc <= 131072.
+bool random_sample_pair_supported(int voc);
+infiniopStatus_t random_sample_pair_launch(const RandomSampleArgs &args, int rows, cudaStream_t stream);
+
 uint64_t random_sample_work_pitch(int voc);
 uint64_t random_sample_workspace_bytes(int voc, int rows);
 infiniopStatus_t random_sample_launch(const RandomSampleArgs &args, int rows, void *workspace, uint64_t workspace_size,

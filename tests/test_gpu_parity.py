@@ -203,11 +203,24 @@ def test_random_sample_single_row_abi(oracle, cuda_lib, voc, u, topp, topk, temp
         assert int(res[0]) == want
 
 
+@pytest.fixture(params=["shared", "global"])
+def sampler_kernel(request, monkeypatch):
+    """Both sampling kernels: the shared-memory resident pair kernel (default for
+    voc <= 131072) and the global-memory kernel (any voc)."""
+    if request.param == "global":
+        monkeypatch.setenv("INFINIOP_RANDOM_SAMPLE_KERNEL", "global")
+    else:
+        monkeypatch.delenv("INFINIOP_RANDOM_SAMPLE_KERNEL", raising=False)
+    return request.param
+
+
 @pytest.mark.parametrize("voc,rows,topp,topk,temp,dist", [
-    (128256, 64, 0.9, 50, 0.8, "normal3"), (32000, 96, 0.8, 50, 1.0, "uniform"), (32000, 64, 1.0, 25, 1.0, "uniform"),
+    (128256, 64, 0.9, 50, 0.8, "normal3"), (131072, 8, 0.9, 64, 1.0, "normal3"), (200000, 6, 0.9, 50, 0.8, "normal3"),
+    (65536, 8, 0.9, 50, 0.8, "normal3"), (65537, 8, 0.9, 50, 1.3, "uniform"), (70000, 4, 0.9, 50, 1.0, "ascending"),
+    (100000, 4, 0.95, 33, 0.6, "coarse"), (128256, 4, 0.9, 50, 1.0, "constant"), (128256, 6, 0.9, 50, 5.0, "normal3"), (32000, 96, 0.8, 50, 1.0, "uniform"), (32000, 64, 1.0, 25, 1.0, "uniform"),
     (16384, 64, 0.85, 10, 2.0, "normal3"), (5000, 200, 0.95, 64, 0.3, "normal3"), (777, 50, 0.9, 7, 1.0, "coarse"),
     (4096, 32, 0.9, 40, 1.0, "constant"), (8192, 16, 0.9, 50, 1.0, "ascending"), (8192, 16, 0.9, 50, 1.0, "descending")])
-def test_random_sample_batch_with_trace(oracle, cuda_lib, voc, rows, topp, topk, temp, dist):
+def test_random_sample_batch_with_trace(oracle, cuda_lib, sampler_kernel, voc, rows, topp, topk, temp, dist):
     """Batched extension: the denominator, the top-k order and probabilities and
     the final index all equal the oracle's, row by row."""
     lib, handle = cuda_lib
