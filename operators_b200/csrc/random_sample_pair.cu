@@ -7,9 +7,9 @@
 // (streaming insertion, closed form of the permuted row, binade-wise integer
 // sum).  What differs is where the row lives and how the work is spread:
 //
-//  * The row is read from HBM exactly once and kept in shared memory as 16-bit
-//    order-preserving keys: the leader CTA holds elements [0, 65536), the helper
-//    the rest.  Every later step (candidate search, record patches, block sums)
+//  * The row is read from HBM exactly once and kept in shared memory as the
+//    fp16 bit patterns it came as: the leader CTA holds elements [0, 65536), the
+//    helper the rest.  Every later step (candidate search, record patches, block sums)
 //    runs on shared memory; the two CTAs exchange a few hundred bytes through
 //    distributed shared memory and meet at hardware cluster barriers (no
 //    flag spinning anywhere).
@@ -37,12 +37,14 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kBlk = 256;
 constexpr int kListCap = 64;      // per-warp ordered list
 constexpr int kFlatCap = 1024;    // per-CTA ordered list (candidates, flagged records)
-constexpr int kHalfElems = 65536; // keys held by one CTA
+constexpr int kHalfElems = 65536; // elements held by one CTA
 constexpr int kMaxBlk = 2 * kHalfElems / kBlk;
 constexpr int kLevels = 4;
 constexpr int kUncCap = 6144;
 constexpr int kMaxRounds = 6;     // 6 x 4 binades covers any sum of <= 2^17 terms <= 1
+constexpr int kTieGroups = 64;
 constexpr uint32_t kEmptyMin = 0xFFFFFFFFu;
+constexpr uint16_t kPad = 0xFC00u;// fp16 -inf: never a candidate, contributes nothing
 
 struct WarpLists {
     uint32_t idx[kWarps][kListCap];
@@ -50,11 +52,16 @@ struct WarpLists {
     int cnt[kWarps];
     int overflow;
 };
+// Ordered (index order) list of (position, key) pairs.  Slots [0, kFlatCap) hold
+// this CTA's entries; at the leader, slots [kFlatCap, 2*kFlatCap) receive the
+// helper's entries.
 struct FlatList {
-    uint32_t idx[kFlatCap];
-    uint16_t key[kFlatCap];
-    int cnt;
-    int overflow;
+    uint32_t idx[2 * kFlatCap];
+    uint16_t key[2 * kFlatCap];
+    int cnt;      // own entries
+    int overflow; // own entries did not fit
+    int peer_cnt; // leader: helper's entries
+    int peer_overflow;
 };
 struct Mail {// written by the other CTA of the pair (the leader also fills its own copy)
     uint32_t L_peer;
@@ -66,33 +73,53 @@ struct Mail {// written by the other CTA of the pair (the leader also fills its 
 };
 struct Aux {
     WarpLists wl;
-    FlatList own;
-    FlatList peer;// leader: copy of the helper's list
+    FlatList fl;
+    uint16_t gbuf[2 * kFlatCap];// top-k: per-key-group queues of candidate ordinals
+    uint32_t tie_key[kTieGroups];
+    uint32_t tie_greater[kTieGroups];
+    uint32_t tie_same[kTieGroups];
+    int tie_groups;
     uint32_t top_key[kSlots];
     uint32_t top_idx[kSlots];
     float top_term[kSlots];
     float blk_terms[kBlk];
     uint32_t C[kLevels][kMaxBlk];// integer block sums per binade level
     uint32_t tie[kMaxBlk];       // bit d: block holds an exact half-way case at level d
+    uint8_t relq[kWarps][kBlk];  // per warp: in-block indices of the elements that can contribute
     uint32_t unc[kUncCap];       // positions (local) to re-evaluate exactly
     int unc_cnt;
     Mail mail;
 };
 
 constexpr size_t kSmemBytes = (size_t) kHalfElems * 2 + sizeof(Aux);
+static_assert(kSmemBytes <= 227 * 1024, "row half + bookkeeping must fit one SM's shared memory");
 
-__device__ __forceinline__ void lds_keys(const uint16_t *p, uint32_t keys[8]) {
-    const uint4 v = *reinterpret_cast<const uint4 *>(p);
-    const uint32_t *w = reinterpret_cast<const uint32_t *>(&v);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        keys[2 * k] = w[k] & 0xFFFFu;
-        keys[2 * k + 1] = w[k] >> 16;
-    }
+__device__ __forceinline__ uint16_t half_of_key(uint32_t key) {
+    return key >= 0x8000u ? (uint16_t) (key - 0x8000u) : (uint16_t) (0x8000u | (0x8000u - key));
 }
+__device__ __forceinline__ __half2 h2_of(uint32_t w) { return *reinterpret_cast<const __half2 *>(&w); }
 
-// Ordered append of the flagged elements of one block to this warp's list.
-__device__ __forceinline__ void warp_append(WarpLists &wl, int warp, int lane, uint32_t mask, const uint32_t keys[8],
+// 8 consecutive fp16 values (4 packed words) against a threshold: bit e of the
+// result is set when element e is > thr (strict) or >= thr.
+__device__ __forceinline__ uint32_t flag8(const uint32_t w[4], __half2 thr2, bool strict) {
+    uint32_t mask = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint32_t m = strict ? __hgt2_mask(h2_of(w[q]), thr2) : __hge2_mask(h2_of(w[q]), thr2);
+        mask |= ((m & 1u) << (2 * q)) | (((m >> 16) & 1u) << (2 * q + 1));
+    }
+    return mask;
+}
+__device__ __forceinline__ void lds_raw(const uint16_t *p, uint32_t w[4]) {
+    const uint4 v = *reinterpret_cast<const uint4 *>(p);
+    w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+}
+__device__ __forceinline__ uint16_t half_at(const uint32_t *w, int e) { return (uint16_t) (w[e >> 1] >> ((e & 1) * 16)); }
+
+// Ordered append of the flagged elements a warp looked at (E consecutive
+// elements per lane held as packed fp16 words, lane-major order = index order).
+template<int E>
+__device__ __forceinline__ void warp_append(WarpLists &wl, int warp, int lane, uint32_t mask, const uint32_t *words,
                                             uint32_t base_idx) {
     const uint32_t any = __ballot_sync(0xffffffffu, mask != 0);
     if (any == 0) return;
@@ -110,10 +137,10 @@ __device__ __forceinline__ void warp_append(WarpLists &wl, int warp, int lane, u
     } else {
         int at = start + pre - cnt;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
+        for (int e = 0; e < E; ++e) {
             if (mask & (1u << e)) {
-                wl.idx[warp][at] = base_idx + lane * 8 + e;
-                wl.key[warp][at] = (uint16_t) keys[e];
+                wl.idx[warp][at] = base_idx + lane * E + e;
+                wl.key[warp][at] = (uint16_t) key_of(half_at(words, e));
                 ++at;
             }
         }
@@ -123,53 +150,75 @@ __device__ __forceinline__ void warp_append(WarpLists &wl, int warp, int lane, u
     __syncwarp();
 }
 
-// Warp lists -> one ordered list (warp 0 of the CTA calls it).
-__device__ __forceinline__ void flatten(const WarpLists &wl, FlatList &fl, int lane) {
-    int total = 0;
-    bool over = wl.overflow != 0;
-    for (int w = 0; w < kWarps && !over; ++w) {
-        const int c = wl.cnt[w];
-        if (total + c > kFlatCap) {
-            over = true;
-            break;
+// Warp lists -> this CTA's part of the ordered list.  All threads of the CTA
+// call it (it contains CTA barriers).
+__device__ __forceinline__ void flatten(WarpLists &wl, FlatList &fl, int tid) {
+    __shared__ int s_off[kWarps];
+    if (tid < 32) {// kWarps == 32: one lane per warp list
+        const int c = wl.cnt[tid];
+        int pre = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, pre, o);
+            if (tid >= o) pre += t;
         }
+        s_off[tid] = pre - c;
+        if (tid == 31) {
+            const bool over = wl.overflow != 0 || pre > kFlatCap;
+            fl.cnt = over ? 0 : pre;
+            fl.overflow = over ? 1 : 0;
+        }
+    }
+    __syncthreads();
+    if (!fl.overflow) {
+        const int w = tid >> 5, lane = tid & 31;
+        const int c = wl.cnt[w], off = s_off[w];
         for (int i = lane; i < c; i += 32) {
-            fl.idx[total + i] = wl.idx[w][i];
-            fl.key[total + i] = wl.key[w][i];
+            fl.idx[off + i] = wl.idx[w][i];
+            fl.key[off + i] = wl.key[w][i];
         }
-        total += c;
     }
-    __syncwarp();
-    if (lane == 0) {
-        fl.cnt = over ? 0 : total;
-        fl.overflow = over ? 1 : 0;
-    }
+    __syncthreads();
 }
 
+// Running multiset of the k largest keys seen so far, 2 slots per lane.  Each
+// slot holds (key << 6) | slot_id, so that a single warp-wide minimum `p`
+// returns both the k-th largest key (p >> 6) and the slot that holds it
+// (p & 63).  Slots >= k hold 0xFFFFFFFF.  Because slot ids fill the low bits,
+// "key > tau" is the same as "(key << 6) > p".
 struct MinBuf {
-    uint32_t v0, v1, tau;
+    uint32_t v0, v1;// packed slots lane and lane + 32
+    uint32_t p;     // packed minimum
+    __device__ __forceinline__ uint32_t tau() const { return p >> 6; }
 };
-__device__ __forceinline__ void minbuf_replace(MinBuf &m, int lane, uint32_t key) {
-    const uint32_t h0 = __ballot_sync(0xffffffffu, m.v0 == m.tau);
-    if (h0) {
-        if (lane == __ffs(h0) - 1) m.v0 = key;
-    } else {
-        const uint32_t h1 = __ballot_sync(0xffffffffu, m.v1 == m.tau);
-        if (lane == __ffs(h1) - 1) m.v1 = key;
-    }
-    m.tau = __reduce_min_sync(0xffffffffu, min(m.v0, m.v1));
+__device__ __forceinline__ void minbuf_init(MinBuf &m, int lane, int k, const uint16_t *first_raw) {
+    m.v0 = lane < k ? (key_of(first_raw[lane]) << 6) | (uint32_t) lane : kEmptyMin;
+    m.v1 = lane + 32 < k ? (key_of(first_raw[lane + 32]) << 6) | (uint32_t) (lane + 32) : kEmptyMin;
+    m.p = __reduce_min_sync(0xffffffffu, min(m.v0, m.v1));
+}
+// Replace the smallest held key by the key in `key_shl6` (= key << 6, known to
+// every lane).  The dependent chain from the old minimum to the new one is:
+// mask, compare, move, min, warp-wide min.
+__device__ __forceinline__ void minbuf_replace(MinBuf &m, int lane, uint32_t key_shl6) {
+    const uint32_t slot = m.p & 63u;
+    const uint32_t np = key_shl6 | slot;
+    if ((uint32_t) lane == slot) m.v0 = np;
+    if ((uint32_t) lane + 32u == slot) m.v1 = np;
+    m.p = __reduce_min_sync(0xffffffffu, min(m.v0, m.v1));
 }
 
 // One warp walks a 256-element block (local or the peer's shared memory) in
 // index order and feeds every element above the running k-th largest value;
-// a record is overwritten with that value.
+// a record is overwritten with that value.  Slow path (list overflow only).
 __device__ __forceinline__ void records_direct_block(uint16_t *blk, uint32_t first_in_blk, int lane, MinBuf &m) {
-    uint32_t keys[8];
-    lds_keys(blk + lane * 8, keys);
+    uint32_t w[4], keys[8];
+    lds_raw(blk + lane * 8, w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) keys[e] = half_at(w, e) == kPad ? 0u : key_of(half_at(w, e));
     uint32_t mask = 0;
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-        if ((uint32_t) (lane * 8 + e) >= first_in_blk && keys[e] > m.tau) mask |= 1u << e;
+        if ((uint32_t) (lane * 8 + e) >= first_in_blk && keys[e] > m.tau()) mask |= 1u << e;
     }
     uint32_t any = __ballot_sync(0xffffffffu, mask != 0);
     while (any) {
@@ -182,12 +231,40 @@ __device__ __forceinline__ void records_direct_block(uint16_t *blk, uint32_t fir
             if (t == e) key = keys[t];
         }
         key = __shfl_sync(0xffffffffu, key, src);
-        if (key > m.tau) {
-            if (lane == 0) blk[src * 8 + e] = (uint16_t) m.tau;
-            minbuf_replace(m, lane, key);
-        }
         if (lane == src) mask &= mask - 1;
+        if (key > m.tau()) {
+            if (lane == 0) blk[src * 8 + e] = half_of_key(m.tau());
+            minbuf_replace(m, lane, key << 6);
+            // the bar moved: drop what no longer clears it
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                if (keys[t] <= m.tau()) mask &= ~(1u << t);
+            }
+        }
         any = __ballot_sync(0xffffffffu, mask != 0);
+    }
+}
+
+// Warp 0 replays an ordered list of (position, key): every entry above the
+// running k-th largest value is a record and is overwritten with that value in
+// `dst` (positions are taken relative to `pos_offset`).  Sixteen keys at a time
+// are read into registers of every lane, so the only serial dependency between
+// entries is the running value itself (one warp-wide minimum per record).
+__device__ __forceinline__ void replay_list(const FlatList &fl, int first, int count, uint16_t *dst,
+                                            uint32_t pos_offset, int lane, MinBuf &m) {
+    constexpr int kBatch = 16;
+    for (int c0 = 0; c0 < count; c0 += kBatch) {
+        uint32_t kb[kBatch];// key << 6
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) kb[i] = c0 + i < count ? (uint32_t) fl.key[first + c0 + i] << 6 : 0u;
+        const uint32_t my_idx = (lane < kBatch && c0 + lane < count) ? fl.idx[first + c0 + lane] : 0u;
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+            if (kb[i] > m.p) {// key > tau, uniform across the warp
+                if (lane == i) dst[my_idx - pos_offset] = half_of_key(m.tau());
+                minbuf_replace(m, lane, kb[i]);
+            }
+        }
     }
 }
 
@@ -216,12 +293,12 @@ __device__ __forceinline__ void exact_contrib(Aux &ax, uint32_t blk, float v, fl
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomSampleArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint16_t *keys = reinterpret_cast<uint16_t *>(smem_raw);
+    uint16_t *raw = reinterpret_cast<uint16_t *>(smem_raw);// this CTA's half of the row, fp16 bit patterns
     Aux &ax = *reinterpret_cast<Aux *>(smem_raw + (size_t) kHalfElems * 2);
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned rank = cluster.block_rank();
     const bool leader = rank == 0;
-    uint16_t *peer_keys = cluster.map_shared_rank(keys, rank ^ 1u);
+    uint16_t *peer_raw = cluster.map_shared_rank(raw, rank ^ 1u);
     Aux *peer_ax = cluster.map_shared_rank(&ax, rank ^ 1u);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -242,53 +319,57 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
     const long long t_entry = clock64();
     int stamp_i = 0;
     auto stamp = [&]() {
-        if (a.debug && leader && tid == 0 && stamp_i < 15) {
+        if (a.debug && leader && tid == 0 && stamp_i < 6) {
             a.debug[(int64_t) row * kDebugStride + 129 + stamp_i] = (float) (clock64() - t_entry);
         }
         ++stamp_i;
     };
+#ifdef RS_TILE_STAMPS
+    int sub_i = 0;
+#define SUBSTAMP()                                                                                            \
+    do {                                                                                                      \
+        if (a.debug && leader && tid == 0 && sub_i < 9)                                                       \
+            a.debug[(int64_t) row * kDebugStride + 135 + sub_i] = (float) (clock64() - t_entry);              \
+        ++sub_i;                                                                                              \
+    } while (0)
+#else
+#define SUBSTAMP() do {} while (0)
+#endif
 
-    // ---- P1: logits -> keys in shared memory; per-thread maxima -------------------------
+    // ---- P1: this CTA's half of the row -> shared memory; per-thread maxima --------------
     const bool in_aligned = (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
-    uint32_t tmax = 0;
+    __half2 tmax2 = h2_of(0xFC00FC00u);
     constexpr int kInFlight = 8;
     for (uint32_t base0 = tid * 8; base0 < my_pad; base0 += kThreads * 8 * kInFlight) {
-        uint4 raw[kInFlight];
+        uint4 ld[kInFlight];
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
             const uint32_t base = base0 + u * kThreads * 8;
-            if (in_aligned && base + 8 <= my_n) raw[u] = ld_stream(logits + base);
+            if (in_aligned && base + 8 <= my_n) ld[u] = ld_stream(logits + base);
         }
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
             const uint32_t base = base0 + u * kThreads * 8;
             if (base >= my_pad) break;
-            uint32_t kk[8];
-            if (in_aligned && base + 8 <= my_n) {
-                const uint32_t *p = reinterpret_cast<const uint32_t *>(&raw[u]);
+            if (!(in_aligned && base + 8 <= my_n)) {// ragged end or unaligned row: element-wise, padded with -inf
+                uint16_t h[8];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    kk[2 * q] = key_of((uint16_t) (p[q] & 0xFFFFu));
-                    kk[2 * q + 1] = key_of((uint16_t) (p[q] >> 16));
-                }
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) kk[e] = base + e < my_n ? key_of(logits[base + e]) : 0u;
+                for (int e = 0; e < 8; ++e) h[e] = base + e < my_n ? logits[base + e] : kPad;
+                ld[u].x = h[0] | ((uint32_t) h[1] << 16);
+                ld[u].y = h[2] | ((uint32_t) h[3] << 16);
+                ld[u].z = h[4] | ((uint32_t) h[5] << 16);
+                ld[u].w = h[6] | ((uint32_t) h[7] << 16);
             }
-            uint4 o;
-            o.x = kk[0] | (kk[1] << 16);
-            o.y = kk[2] | (kk[3] << 16);
-            o.z = kk[4] | (kk[5] << 16);
-            o.w = kk[6] | (kk[7] << 16);
-            *reinterpret_cast<uint4 *>(keys + base) = o;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) tmax = max(tmax, kk[e]);
+            *reinterpret_cast<uint4 *>(raw + base) = ld[u];
+            tmax2 = __hmax2(tmax2, __hmax2(__hmax2(h2_of(ld[u].x), h2_of(ld[u].y)), __hmax2(h2_of(ld[u].z), h2_of(ld[u].w))));
         }
     }
-    if (tid < kWarps) ax.wl.cnt[tid] = 0;
-    if (tid == 0) {
-        ax.wl.overflow = 0;
-        ax.unc_cnt = 0;
+    // thread maximum as an order-preserving key (0 when the thread saw nothing but padding)
+    uint32_t tmax = 0;
+    {
+        const __half hm = __hmax(__low2half(tmax2), __high2half(tmax2));
+        const uint16_t hb = __half_as_ushort(hm);
+        tmax = hb == kPad ? 0u : key_of(hb);
     }
     // local lower bound of the k-th largest key: k-th largest per-thread maximum
     uint32_t L_mine = 0;
@@ -305,40 +386,73 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             L_mine = have < k ? 1u : lo;
         }
     }
-    if (tid == 0) peer_ax->mail.L_peer = L_mine;
+    if (tid == 0) {
+        peer_ax->mail.L_peer = L_mine;
+        ax.fl.peer_cnt = 0;// the helper fills these in after the barrier
+        ax.fl.peer_overflow = 0;
+    }
     cluster.sync();// CS1
-    stamp();       // 0: keys resident
+    stamp();       // 0: row resident
     const uint32_t L = max(max(L_mine, ax.mail.L_peer), 1u);
 
     // ---- P2: candidates (key >= L), ordered --------------------------------------------
-    auto scan_blocks = [&](uint32_t blk_begin, uint32_t blk_end, uint32_t thresh, bool strict) {
-        // all warps of this CTA: blocks [blk_begin, blk_end) of the LOCAL half, contiguous span per warp
-        const uint32_t cnt = blk_end - blk_begin;
-        const uint32_t span = (cnt + kWarps - 1) / kWarps;
-        const uint32_t b0 = blk_begin + warp * span, b1 = min(blk_end, b0 + span);
-        for (uint32_t b = b0; b < b1; ++b) {
-            uint32_t kk[8];
-            lds_keys(keys + b * kBlk + lane * 8, kk);
-            uint32_t mask = 0;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) mask |= ((strict ? kk[e] > thresh : kk[e] >= thresh) ? 1u : 0u) << e;
-            warp_append(ax.wl, warp, lane, mask, kk, my_base + b * kBlk);
+    // Flag elements of [e_begin, e_end) of the LOCAL half against the key `thresh`
+    // into the per-warp ordered lists.  Short ranges are cut into 64-element
+    // pieces (one per warp, two elements per lane) so that the first,
+    // record-dense tiles neither overflow a warp's list nor leave most warps idle.
+    auto scan_range = [&](uint32_t e_begin, uint32_t e_end, uint32_t thresh, bool strict) {
+        if (tid < kWarps) ax.wl.cnt[tid] = 0;
+        if (tid == 0) ax.wl.overflow = 0;
+        __syncthreads();
+        // keys below 0x0400 lie under every fp16 value (0x0400 is -inf): compare with -inf then.
+        // Padding is -inf too, so positions at or beyond the real end are masked out by index.
+        const uint16_t th = thresh < 0x0400u ? kPad : half_of_key(thresh);
+        const __half2 thr2 = h2_of((uint32_t) th | ((uint32_t) th << 16));
+        e_end = min(e_end, my_n);
+        if (e_end <= e_begin) {
+            // nothing to scan
+        } else if (e_end - e_begin <= 2048u) {
+            const uint32_t base64 = e_begin & ~63u;
+            for (uint32_t c = base64 + warp * 64; c < e_end; c += kWarps * 64) {
+                const uint32_t w2 = *reinterpret_cast<const uint32_t *>(raw + c + lane * 2);
+                const uint32_t m = strict ? __hgt2_mask(h2_of(w2), thr2) : __hge2_mask(h2_of(w2), thr2);
+                const uint32_t j = c + lane * 2;
+                uint32_t mask = 0;
+                if ((m & 1u) && j >= e_begin && j < e_end) mask |= 1u;
+                if ((m >> 16) && j + 1 >= e_begin && j + 1 < e_end) mask |= 2u;
+                warp_append<2>(ax.wl, warp, lane, mask, &w2, my_base + c);
+            }
+        } else {// whole 256-element blocks, a contiguous span of blocks per warp
+            const uint32_t bb = e_begin / kBlk, be = (e_end + kBlk - 1) / kBlk;
+            const uint32_t span = (be - bb + kWarps - 1) / kWarps;
+            const uint32_t b0 = bb + warp * span, b1 = min(be, b0 + span);
+            for (uint32_t b = b0; b < b1; ++b) {
+                uint32_t w[4];
+                lds_raw(raw + b * kBlk + lane * 8, w);
+                uint32_t mask = flag8(w, thr2, strict);
+                const uint32_t first = b * kBlk + lane * 8;// drop positions outside [e_begin, e_end)
+                if (first + 8 > e_end) mask &= first >= e_end ? 0u : (1u << (e_end - first)) - 1u;
+                if (first < e_begin) mask &= first + 8 <= e_begin ? 0u : ~((1u << (e_begin - first)) - 1u);
+                warp_append<8>(ax.wl, warp, lane, mask, w, my_base + b * kBlk);
+            }
         }
+        __syncthreads();
+        flatten(ax.wl, ax.fl, tid);
     };
-    scan_blocks(0, my_nblk, L, false);
-    __syncthreads();
-    if (warp == 0) flatten(ax.wl, ax.own, lane);
-    __syncthreads();
-    if (!leader) {
-        for (int i = tid; i < ax.own.cnt; i += kThreads) {
-            peer_ax->peer.idx[i] = ax.own.idx[i];
-            peer_ax->peer.key[i] = ax.own.key[i];
+    // Helper: hand this CTA's list to the leader (second half of the leader's arrays).
+    auto ship_list = [&]() {
+        for (int i = tid; i < ax.fl.cnt; i += kThreads) {
+            peer_ax->fl.idx[kFlatCap + i] = ax.fl.idx[i];
+            peer_ax->fl.key[kFlatCap + i] = ax.fl.key[i];
         }
         if (tid == 0) {
-            peer_ax->peer.cnt = ax.own.cnt;
-            peer_ax->peer.overflow = ax.own.overflow;
+            peer_ax->fl.peer_cnt = ax.fl.cnt;
+            peer_ax->fl.peer_overflow = ax.fl.overflow;
         }
-    }
+    };
+
+    scan_range(0, my_pad, L, false);
+    if (!leader) ship_list();
     cluster.sync();// CS2
     stamp();       // 1: candidate lists at the leader
 
@@ -346,51 +460,147 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
     MinBuf mb{kEmptyMin, kEmptyMin, 0};
     float M = 0.f;
     if (leader) {
-        if (warp == 0) {
-            TopBuf tb{0, 0, 0, 0};
-            if (!ax.own.overflow && !ax.peer.overflow) {
-                for (int c = 0; c < ax.own.cnt; ++c) topbuf_insert(tb, lane, k, ax.own.key[c], ax.own.idx[c]);
-                for (int c = 0; c < ax.peer.cnt; ++c) topbuf_insert(tb, lane, k, ax.peer.key[c], ax.peer.idx[c]);
-            } else {
-                // more ties than the lists hold: stream the whole row
-                for (uint32_t b = 0; b < nblk; ++b) {
-                    const uint16_t *blk = b < nblk0 ? keys + b * kBlk : peer_keys + (b - nblk0) * kBlk;
-                    const uint32_t gbase = b < nblk0 ? b * kBlk : (uint32_t) kHalfElems + (b - nblk0) * kBlk;
-                    uint32_t kk[8];
-                    lds_keys(blk + lane * 8, kk);
-                    const uint32_t kth = __shfl_sync(0xffffffffu, (k - 1) < 32 ? tb.k0 : tb.k1, (k - 1) & 31);
-                    uint32_t mask = 0;
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) mask |= (kk[e] > kth ? 1u : 0u) << e;
-                    uint32_t any = __ballot_sync(0xffffffffu, mask != 0);
-                    while (any) {
-                        const int src = __ffs(any) - 1;
-                        const uint32_t smask = __shfl_sync(0xffffffffu, mask, src);
-                        const int e = __ffs(smask) - 1;
-                        uint32_t key = 0;
-#pragma unroll
-                        for (int t = 0; t < 8; ++t) {
-                            if (t == e) key = kk[t];
-                        }
-                        key = __shfl_sync(0xffffffffu, key, src);
-                        topbuf_insert(tb, lane, k, key, gbase + src * 8 + e);
-                        if (lane == src) mask &= mask - 1;
-                        any = __ballot_sync(0xffffffffu, mask != 0);
+        const int cnt0 = ax.fl.cnt, cnt1 = ax.fl.peer_cnt;
+        const int m = cnt0 + cnt1;
+        const bool list_ok = !ax.fl.overflow && !ax.fl.peer_overflow && m <= kThreads;// one thread per candidate
+        if (list_ok) {
+            // move the helper's entries up behind the leader's own: one list in index order
+            uint32_t mv_idx = 0;
+            uint16_t mv_key = 0;
+            if (tid < cnt1) {
+                mv_idx = ax.fl.idx[kFlatCap + tid];
+                mv_key = ax.fl.key[kFlatCap + tid];
+            }
+            if (tid == 0) ax.tie_groups = 0;
+            __syncthreads();
+            if (tid < cnt1) {
+                ax.fl.idx[cnt0 + tid] = mv_idx;
+                ax.fl.key[cnt0 + tid] = mv_key;
+            }
+            if (tid < kSlots) {
+                ax.top_key[tid] = 0;
+                ax.top_idx[tid] = 0;
+            }
+            __syncthreads();
+            SUBSTAMP();// s0: lists merged
+            // Rank every candidate: `greater` keys above it, `same` keys equal to it.
+            // A key that occurs once simply sits behind all larger keys.  Equal keys
+            // form a group that behaves like a queue under the reference's insertion
+            // cascade: an arriving equal key joins at the back (while the buffer has
+            // room above the smaller keys), an arriving larger key moves the front
+            // element to the back, or pushes it out when nothing smaller is left to
+            // evict.  Each such group is replayed over the candidates in index order
+            // by one warp; its final place is behind all larger keys.
+            if (tid < m) {
+                const uint32_t my_key = ax.fl.key[tid];
+                uint32_t greater = 0, same = 0;
+                bool seen_before = false;
+                for (int j = 0; j < m; ++j) {
+                    const uint32_t kj = ax.fl.key[j];
+                    greater += kj > my_key;
+                    same += kj == my_key;
+                    seen_before |= (kj == my_key) && j < tid;
+                }
+                if (same == 1) {
+                    if (greater < (uint32_t) k) {
+                        ax.top_key[greater] = my_key;
+                        ax.top_idx[greater] = ax.fl.idx[tid];
                     }
+                } else if (!seen_before && greater < (uint32_t) k) {
+                    const int g = atomicAdd(&ax.tie_groups, 1);// at most k groups start below rank k
+                    ax.tie_key[g] = my_key;
+                    ax.tie_greater[g] = greater;
+                    ax.tie_same[g] = same;
+                }
+            }
+            __syncthreads();
+            SUBSTAMP();// s1: ranks counted
+            for (int g = warp; g < ax.tie_groups; g += kWarps) {// warp-uniform replay of one group
+                const uint32_t gkey = ax.tie_key[g], cap = ax.tie_same[g];
+                uint16_t *q = ax.gbuf + ax.tie_greater[g];// this group's slots: [greater, greater + same)
+                uint32_t G = 0, sz = 0, head = 0;
+                for (int j = 0; j < m; ++j) {
+                    const uint32_t kj = ax.fl.key[j];
+                    if (kj > gkey) {
+                        ++G;
+                        if (sz > 0) {
+                            if (G + sz > (uint32_t) k) {// nothing smaller left to evict: the front leaves
+                                head = head + 1 == cap ? 0 : head + 1;
+                                --sz;
+                            } else if (sz > 1) {// front moves to the back
+                                if (sz < cap) {
+                                    uint32_t tail = head + sz;
+                                    if (tail >= cap) tail -= cap;
+                                    if (lane == 0) q[tail] = q[head];
+                                    __syncwarp();
+                                }
+                                head = head + 1 == cap ? 0 : head + 1;
+                            }
+                        }
+                    } else if (kj == gkey) {
+                        if (G + sz < (uint32_t) k) {
+                            uint32_t tail = head + sz;
+                            if (tail >= cap) tail -= cap;
+                            if (lane == 0) q[tail] = (uint16_t) j;
+                            __syncwarp();
+                            ++sz;
+                        }
+                    }
+                }
+                __syncwarp();
+                for (uint32_t t = lane; t < sz; t += 32) {// G < k whenever sz > 0
+                    uint32_t at = head + t;
+                    if (at >= cap) at -= cap;
+                    ax.top_key[G + t] = gkey;
+                    ax.top_idx[G + t] = ax.fl.idx[q[at]];
+                }
+            }
+            __syncthreads();
+        } else if (warp == 0) {
+            // more ties than the lists hold: stream the whole row through the warp-resident buffer
+            TopBuf tb{0, 0, 0, 0};
+            for (uint32_t b = 0; b < nblk; ++b) {
+                const uint16_t *blk = b < nblk0 ? raw + b * kBlk : peer_raw + (b - nblk0) * kBlk;
+                const uint32_t gbase = b < nblk0 ? b * kBlk : (uint32_t) kHalfElems + (b - nblk0) * kBlk;
+                uint32_t w[4], kk[8];
+                lds_raw(blk + lane * 8, w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) kk[e] = half_at(w, e) == kPad ? 0u : key_of(half_at(w, e));
+                const uint32_t kth = __shfl_sync(0xffffffffu, (k - 1) < 32 ? tb.k0 : tb.k1, (k - 1) & 31);
+                uint32_t mask = 0;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) mask |= (kk[e] > kth ? 1u : 0u) << e;
+                uint32_t any = __ballot_sync(0xffffffffu, mask != 0);
+                while (any) {
+                    const int src = __ffs(any) - 1;
+                    const uint32_t smask = __shfl_sync(0xffffffffu, mask, src);
+                    const int e = __ffs(smask) - 1;
+                    uint32_t key = 0;
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) {
+                        if (t == e) key = kk[t];
+                    }
+                    key = __shfl_sync(0xffffffffu, key, src);
+                    topbuf_insert(tb, lane, k, key, gbase + src * 8 + e);
+                    if (lane == src) mask &= mask - 1;
+                    any = __ballot_sync(0xffffffffu, mask != 0);
                 }
             }
             ax.top_key[lane] = tb.k0;
             ax.top_key[lane + 32] = tb.k1;
             ax.top_idx[lane] = tb.i0;
             ax.top_idx[lane + 32] = tb.i1;
-            __syncwarp();
+        }
+        __syncthreads();
+        SUBSTAMP();// s2: top-k placed
+        if (warp == 0) {
             const float Mw = val_of(ax.top_key[0]);
             for (int i = lane; i < k; i += 32) ax.top_term[i] = term_of(val_of(ax.top_key[i]), Mw, T);
             __syncwarp();
             if (lane == 0) {
-                float s = 0.f;
-                for (int i = 0; i < k; ++i) s = __fadd_rn(s, ax.top_term[i]);
-                ax.mail.s_base = s;
+                float sk = 0.f;
+                for (int i = 0; i < k; ++i) sk = __fadd_rn(sk, ax.top_term[i]);
+                ax.mail.s_base = sk;
                 ax.mail.pos_base = (uint32_t) k;
                 ax.mail.mkey = ax.top_key[0];
                 ax.mail.done = (uint32_t) k >= n;
@@ -398,57 +608,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         }
         __syncthreads();
         stamp();// 2: top-k in order, top-k terms summed
-        M = val_of(ax.mail.mkey);
 
         if ((uint32_t) k < n) {
             if (warp == 0) {
-                if (lane < k) mb.v0 = keys[lane];
-                if (lane + 32 < k) mb.v1 = keys[lane + 32];
-                mb.tau = __reduce_min_sync(0xffffffffu, min(mb.v0, mb.v1));
+                minbuf_init(mb, lane, k, raw);
+                if (lane == 0) ax.mail.tau_mid = mb.tau();
             }
-            const uint32_t head_blocks = min(nblk0, 8u);
-            if (warp == 0) {
-                for (uint32_t b = 0; b < head_blocks; ++b) {
-                    records_direct_block(keys + b * kBlk, b == 0 ? (uint32_t) k : 0u, lane, mb);
-                }
-                if (lane == 0) ax.mail.tau_mid = mb.tau;
-            }
-            uint32_t t_begin = head_blocks;
-            while (t_begin < nblk0) {
-                const uint32_t t_end = min(nblk0, t_begin * 2);
-                if (tid < kWarps) ax.wl.cnt[tid] = 0;
-                if (tid == 0) ax.wl.overflow = 0;
-                __syncthreads();
-                scan_blocks(t_begin, t_end, ax.mail.tau_mid, true);
-                __syncthreads();
+            __syncthreads();
+            // tiles [k,256) [256,1024) [1024,4096) ... each four times the previous end:
+            // about 3k flagged elements per tile, of which k*ln(4) are records
+            uint32_t t_begin = (uint32_t) k;
+            uint32_t t_end = min(n0, (uint32_t) kBlk);
+            while (t_begin < n0) {
+                scan_range(t_begin, t_end, ax.mail.tau_mid, true);
                 if (warp == 0) {
-                    if (!ax.wl.overflow) {
-                        for (int w = 0; w < kWarps; ++w) {
-                            const int cnt = ax.wl.cnt[w];
-                            for (int c = 0; c < cnt; ++c) {
-                                const uint32_t key = ax.wl.key[w][c];
-                                if (key > mb.tau) {
-                                    if (lane == 0) keys[ax.wl.idx[w][c]] = (uint16_t) mb.tau;
-                                    minbuf_replace(mb, lane, key);
-                                }
-                            }
-                        }
+                    if (!ax.fl.overflow) {
+                        replay_list(ax.fl, 0, ax.fl.cnt, raw, 0u, lane, mb);
                     } else {
-                        for (uint32_t b = t_begin; b < t_end; ++b) records_direct_block(keys + b * kBlk, 0u, lane, mb);
+                        for (uint32_t b = t_begin / kBlk; b * kBlk < t_end; ++b) {
+                            records_direct_block(raw + b * kBlk, b * kBlk < t_begin ? t_begin - b * kBlk : 0u, lane, mb);
+                        }
                     }
-                    if (lane == 0) ax.mail.tau_mid = mb.tau;
+                    if (lane == 0) ax.mail.tau_mid = mb.tau();
                 }
-                t_begin = t_end;
                 __syncthreads();
+                t_begin = t_end;
+                t_end = min(n0, t_end * 4);
             }
         }
-        __syncthreads();
         if (tid == 0) {// hand the helper what it needs
             peer_ax->mail.tau_mid = ax.mail.tau_mid;
             peer_ax->mail.mkey = ax.mail.mkey;
             peer_ax->mail.s_base = ax.mail.s_base;
             peer_ax->mail.pos_base = ax.mail.pos_base;
             peer_ax->mail.done = ax.mail.done;
+            ax.fl.peer_cnt = 0;
+            ax.fl.peer_overflow = 0;
         }
     }
     cluster.sync();// CS3
@@ -456,36 +651,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
 
     // ---- P4 (helper): elements of its half above the running k-th value -----------------
     if (!leader && my_n > 0 && !ax.mail.done) {
-        if (tid < kWarps) ax.wl.cnt[tid] = 0;
-        if (tid == 0) ax.wl.overflow = 0;
-        __syncthreads();
-        scan_blocks(0, my_nblk, ax.mail.tau_mid, true);
-        __syncthreads();
-        if (warp == 0) flatten(ax.wl, ax.own, lane);
-        __syncthreads();
-        for (int i = tid; i < ax.own.cnt; i += kThreads) {
-            peer_ax->peer.idx[i] = ax.own.idx[i];
-            peer_ax->peer.key[i] = ax.own.key[i];
-        }
-        if (tid == 0) {
-            peer_ax->peer.cnt = ax.own.cnt;
-            peer_ax->peer.overflow = ax.own.overflow;
-        }
+        scan_range(0, my_pad, ax.mail.tau_mid, true);
+        ship_list();
     }
     cluster.sync();// CS4
 
     // ---- P5 (leader, warp 0): records of the helper half -------------------------------
     if (leader && warp == 0 && n > n0 && !ax.mail.done) {
-        if (!ax.peer.overflow) {
-            for (int c = 0; c < ax.peer.cnt; ++c) {
-                const uint32_t key = ax.peer.key[c];
-                if (key > mb.tau) {
-                    if (lane == 0) peer_keys[ax.peer.idx[c] - (uint32_t) kHalfElems] = (uint16_t) mb.tau;
-                    minbuf_replace(mb, lane, key);
-                }
-            }
+        if (!ax.fl.peer_overflow) {
+            replay_list(ax.fl, kFlatCap, ax.fl.peer_cnt, peer_raw, (uint32_t) kHalfElems, lane, mb);
         } else {
-            for (uint32_t b = 0; b < nblk - nblk0; ++b) records_direct_block(peer_keys + b * kBlk, 0u, lane, mb);
+            for (uint32_t b = 0; b < nblk - nblk0; ++b) records_direct_block(peer_raw + b * kBlk, 0u, lane, mb);
         }
     }
     cluster.sync();// CS5
@@ -500,10 +676,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         const float s_base = ax.mail.s_base;
         const uint32_t pos = ax.mail.pos_base;
         const int e0 = (int) ((__float_as_uint(s_base) >> 23) & 0xFFu);
-        const float scale = __uint_as_float((uint32_t) (151 - e0 + 127) << 23);// 2 / ulp(s_base), a power of two
-        const float cut = -2.0f - (float) (151 - e0);                          // z < 1/4: no contribution at any level
-        const float band = 6.0e-6f;                                            // > 2^-17.5, relative error bound of z
-        const uint32_t gb_first = pos / kBlk;                                  // first global block still to sum
+        // z = 2 * term / ulp(s_base) = 2^((v - M) * log2(e) / T + shift); the argument stays below 32
+        // in magnitude, so its rounding and the SFU's error keep z within 2^-17.5 (relative) of the truth
+        const float shift = (float) (151 - e0);
+        const float band = 6.0e-6f;
+        const uint32_t gb_first = pos / kBlk;// first global block still to sum
         const uint32_t lb_first = leader ? gb_first : (gb_first > nblk0 ? gb_first - nblk0 : 0u);
         // block b of the local half is global block b (+ nblk0 for the helper)
         const uint32_t goff = leader ? 0u : nblk0;
@@ -519,22 +696,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             const uint32_t span = (cntb + kWarps - 1) / kWarps;
             const uint32_t b0 = lb_first + warp * span, b1 = min(my_nblk, b0 + span);
             for (uint32_t b = b0; b < b1; ++b) {
-                uint32_t kk[8];
-                lds_keys(keys + b * kBlk + lane * 8, kk);
-                uint32_t F = 0, Bp = 0;
+                // 1. which of the block's elements can contribute at all (z >= 1/4)?  Their
+                //    in-block indices are packed into this warp's queue, so that step 2 runs
+                //    with every lane busy although typically well under half the elements qualify.
+                uint32_t w[4];
+                lds_raw(raw + b * kBlk + lane * 8, w);
+                const bool partial = my_base + b * kBlk < pos;// only the round's first block
+                uint32_t mask = 0;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const uint32_t gpos = my_base + b * kBlk + lane * 8 + e;
-                    if (kk[e] == 0 || gpos < pos) continue;
-                    const float v = val_of(kk[e]);
-                    const float arg = __fmul_rn(__fsub_rn(v, M), A);
-                    if (arg < cut) continue;
-                    const float z = fast_exp2(arg) * scale;
+                    const float v = f16_to_f32(half_at(w, e));
+                    const bool in = fmaf(__fsub_rn(v, M), A, shift) >= -2.0f;// false for padding (-inf)
+                    const bool skip = partial && my_base + b * kBlk + lane * 8 + e < pos;
+                    mask |= ((in && !skip) ? 1u : 0u) << e;
+                }
+                const int cnt = __popc(mask);
+                int pre = cnt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, pre, o);
+                    if (lane >= o) pre += t;
+                }
+                const int total = __shfl_sync(0xffffffffu, pre, 31);
+                if (total == 0) continue;
+                {
+                    int at = pre - cnt;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        if (mask & (1u << e)) ax.relq[warp][at++] = (uint8_t) (lane * 8 + e);
+                    }
+                }
+                __syncwarp();
+                // 2. dense evaluation
+                uint32_t F = 0, Bp = 0;
+                for (int i = lane; i < total; i += 32) {
+                    const uint32_t eidx = ax.relq[warp][i];
+                    const float v = f16_to_f32(raw[b * kBlk + eidx]);
+                    const float z = fast_exp2(fmaf(__fsub_rn(v, M), A, shift));
                     const float fz = floorf(z);
-                    const float fr = z - fz;
-                    if (fminf(fr, 1.0f - fr) <= z * band || z >= 1048576.0f) {
+                    if (fabsf(z - fz - 0.5f) >= 0.5f - z * band || z >= 1048576.0f) {
                         const int slot = atomicAdd(&ax.unc_cnt, 1);
-                        if (slot < kUncCap) ax.unc[slot] = b * kBlk + lane * 8 + e;
+                        if (slot < kUncCap) ax.unc[slot] = b * kBlk + eidx;
                         else exact_contrib(ax, b + goff, v, M, T, e0);// list full: settle it here
                     } else {
                         const uint32_t f = (uint32_t) fz;
@@ -542,10 +744,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                         Bp += ((f & 15u) * 0x00204081u) & 0x01010101u;// bit i of f -> byte i
                     }
                 }
+                __syncwarp();
                 F = __reduce_add_sync(0xffffffffu, F);
                 const uint32_t lo = __reduce_add_sync(0xffffffffu, Bp & 0x00FF00FFu);       // bits 0 and 2
                 const uint32_t hi = __reduce_add_sync(0xffffffffu, (Bp >> 8) & 0x00FF00FFu);// bits 1 and 3
-                if (lane == 0) {
+                if (lane == 0 && F != 0) {
                     const uint32_t B0 = lo & 0xFFFFu, B2 = lo >> 16, B1 = hi & 0xFFFFu, B3 = hi >> 16;
                     // sum over elements of round(f_exact / 2^(d+1)) = sum (f >> (d+1)) + sum bit_d(f)
                     // (added, not stored: exact contributions of this block may already be there)
@@ -557,11 +760,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             }
         }
         __syncthreads();
+        SUBSTAMP();// s3: block sums (approximate path)
         {// exact re-evaluation of the uncertain elements, densely
             const int cnt = min(ax.unc_cnt, kUncCap);
             for (int i = tid; i < cnt; i += kThreads) {
                 const uint32_t lp = ax.unc[i];
-                exact_contrib(ax, lp / kBlk + goff, val_of(keys[lp]), M, T, e0);
+                exact_contrib(ax, lp / kBlk + goff, f16_to_f32(raw[lp]), M, T, e0);
             }
         }
         __syncthreads();
@@ -573,7 +777,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 peer_ax->tie[g] = ax.tie[g];
             }
         }
+        SUBSTAMP();// s4: exact path done
         cluster.sync();// CS6
+        SUBSTAMP();// s5: after barrier
         if (leader && warp == 0) {
             uint32_t m = (__float_as_uint(s_base) & 0x7FFFFFu) | 0x800000u;
             int level = 0;
@@ -582,9 +788,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             uint32_t b0 = gb_first;
             while (b0 < nblk) {
                 const uint32_t b = b0 + lane;
-                const uint32_t raw = b < nblk ? ax.C[level][b] : 0u;
+                const uint32_t rawc = b < nblk ? ax.C[level][b] : 0u;
                 const bool tied = b < nblk && ((ax.tie[b] >> level) & 1u);
-                uint32_t inc = min(raw, 1u << 25);// >= 2^24 is a carry by itself; keeps the scan in 32 bits
+                uint32_t inc = min(rawc, 1u << 25);// >= 2^24 is a carry by itself; keeps the scan in 32 bits
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
                     const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
@@ -601,18 +807,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 const uint32_t eb = b0 + l;// replay this block with real fp32 additions
                 float s_new = __uint_as_float((uint32_t) (e0 + level - 23) << 23) * (float) m;
                 {
-                    const uint16_t *blk = eb < nblk0 ? keys + eb * kBlk : peer_keys + (eb - nblk0) * kBlk;
+                    const uint16_t *blk = eb < nblk0 ? raw + eb * kBlk : peer_raw + (eb - nblk0) * kBlk;
                     const uint32_t gbase = eb < nblk0 ? eb * kBlk : (uint32_t) kHalfElems + (eb - nblk0) * kBlk;
-                    uint32_t kk[8];
-                    lds_keys(blk + lane * 8, kk);
+                    uint32_t w[4];
+                    lds_raw(blk + lane * 8, w);
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         const uint32_t j = gbase + lane * 8 + e;
-                        ax.blk_terms[lane * 8 + e] = (kk[e] == 0 || j < pos) ? 0.f : term_of(val_of(kk[e]), M, T);
+                        const uint16_t h = half_at(w, e);
+                        ax.blk_terms[lane * 8 + e] = (h == kPad || j < pos) ? 0.f : term_of(f16_to_f32(h), M, T);
                     }
                     __syncwarp();
                     if (lane == 0) {
-                        for (int i = 0; i < kBlk; ++i) s_new = __fadd_rn(s_new, ax.blk_terms[i]);
+                        for (int i0 = 0; i0 < kBlk; i0 += 16) {
+                            float t16[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) t16[i] = ax.blk_terms[i0 + i];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) s_new = __fadd_rn(s_new, t16[i]);
+                        }
                     }
                     s_new = __shfl_sync(0xffffffffu, s_new, 0);
                 }
@@ -638,6 +851,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 peer_ax->mail.done = again ? 0 : 1;
             }
         }
+        SUBSTAMP();// s6: walk done
         cluster.sync();// CS7
     }
     stamp();// 5: denominator
