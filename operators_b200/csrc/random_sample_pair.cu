@@ -258,13 +258,15 @@ __device__ __forceinline__ void replay_list(const FlatList &fl, int first, int c
 #pragma unroll
         for (int i = 0; i < kBatch; ++i) kb[i] = c0 + i < count ? (uint32_t) fl.key[first + c0 + i] << 6 : 0u;
         const uint32_t my_idx = (lane < kBatch && c0 + lane < count) ? fl.idx[first + c0 + lane] : 0u;
+        uint32_t my_tau = kEmptyMin;// lane i remembers the value its entry is replaced by; stored after the batch
 #pragma unroll
         for (int i = 0; i < kBatch; ++i) {
             if (kb[i] > m.p) {// key > tau, uniform across the warp
-                if (lane == i) dst[my_idx - pos_offset] = half_of_key(m.tau());
+                if (lane == i) my_tau = m.tau();
                 minbuf_replace(m, lane, kb[i]);
             }
         }
+        if (my_tau != kEmptyMin) dst[my_idx - pos_offset] = half_of_key(my_tau);
     }
 }
 
