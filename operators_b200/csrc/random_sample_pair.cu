@@ -35,7 +35,7 @@ namespace {
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr int kBlk = 256;
-constexpr int kListCap = 64;      // per-warp ordered list
+constexpr int kListCap = 128;     // per-warp ordered list
 constexpr int kFlatCap = 1024;    // per-CTA ordered list (candidates, flagged records)
 constexpr int kHalfElems = 65536; // elements held by one CTA
 constexpr int kMaxBlk = 2 * kHalfElems / kBlk;
@@ -43,6 +43,11 @@ constexpr int kLevels = 4;
 constexpr int kUncCap = 6144;
 constexpr int kMaxRounds = 6;     // 6 x 4 binades covers any sum of <= 2^17 terms <= 1
 constexpr int kTieGroups = 64;
+// Record segments of the leader half end at these positions; the helper half is one more segment.
+// Each boundary's prefix is covered by whole per-thread load slots: thread t's first vector is elements
+// [8t, 8t+8), its first two vectors lie below 16384, all eight below 65536.
+constexpr int kBounds = 5;
+__device__ __constant__ uint32_t kBoundPos[kBounds] = {512u, 1024u, 4096u, 16384u, 65536u};
 constexpr uint32_t kEmptyMin = 0xFFFFFFFFu;
 constexpr uint16_t kPad = 0xFC00u;// fp16 -inf: never a candidate, contributes nothing
 
@@ -85,6 +90,9 @@ struct Aux {
     float blk_terms[kBlk];
     uint32_t C[kLevels][kMaxBlk];// integer block sums per binade level
     uint32_t tie[kMaxBlk];       // bit d: block holds an exact half-way case at level d
+    uint32_t LB[kBounds];        // lower bound of the k-th largest key of the prefix that ends at boundary b
+    uint32_t seg_tau[kBounds + 1];       // exact k-th largest key at the start of segment i
+    uint32_t state[kBounds + 1][kSlots]; // the k largest keys at the start of segment i (slot order irrelevant)
     uint8_t relq[kWarps][kBlk];  // per warp: in-block indices of the elements that can contribute
     uint32_t unc[kUncCap];       // positions (local) to re-evaluate exactly
     int unc_cnt;
@@ -152,7 +160,7 @@ __device__ __forceinline__ void warp_append(WarpLists &wl, int warp, int lane, u
 
 // Warp lists -> this CTA's part of the ordered list.  All threads of the CTA
 // call it (it contains CTA barriers).
-__device__ __forceinline__ void flatten(WarpLists &wl, FlatList &fl, int tid) {
+__device__ __forceinline__ void flatten(WarpLists &wl, FlatList &fl, int tid, int cap = kFlatCap) {
     __shared__ int s_off[kWarps];
     if (tid < 32) {// kWarps == 32: one lane per warp list
         const int c = wl.cnt[tid];
@@ -164,7 +172,7 @@ __device__ __forceinline__ void flatten(WarpLists &wl, FlatList &fl, int tid) {
         }
         s_off[tid] = pre - c;
         if (tid == 31) {
-            const bool over = wl.overflow != 0 || pre > kFlatCap;
+            const bool over = wl.overflow != 0 || pre > cap;
             fl.cnt = over ? 0 : pre;
             fl.overflow = over ? 1 : 0;
         }
@@ -194,6 +202,11 @@ struct MinBuf {
 __device__ __forceinline__ void minbuf_init(MinBuf &m, int lane, int k, const uint16_t *first_raw) {
     m.v0 = lane < k ? (key_of(first_raw[lane]) << 6) | (uint32_t) lane : kEmptyMin;
     m.v1 = lane + 32 < k ? (key_of(first_raw[lane + 32]) << 6) | (uint32_t) (lane + 32) : kEmptyMin;
+    m.p = __reduce_min_sync(0xffffffffu, min(m.v0, m.v1));
+}
+__device__ __forceinline__ void minbuf_init_keys(MinBuf &m, int lane, int k, const uint32_t *keys) {
+    m.v0 = lane < k ? (keys[lane] << 6) | (uint32_t) lane : kEmptyMin;
+    m.v1 = lane + 32 < k ? (keys[lane + 32] << 6) | (uint32_t) (lane + 32) : kEmptyMin;
     m.p = __reduce_min_sync(0xffffffffu, min(m.v0, m.v1));
 }
 // Replace the smallest held key by the key in `key_shl6` (= key << 6, known to
@@ -340,7 +353,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
 
     // ---- P1: this CTA's half of the row -> shared memory; per-thread maxima --------------
     const bool in_aligned = (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
-    __half2 tmax2 = h2_of(0xFC00FC00u);
+    __half2 tmax2 = h2_of(0xFC00FC00u), m0_2 = tmax2, mA_2 = tmax2;// running maximum; after 1 and after 2 vectors
     constexpr int kInFlight = 8;
     for (uint32_t base0 = tid * 8; base0 < my_pad; base0 += kThreads * 8 * kInFlight) {
         uint4 ld[kInFlight];
@@ -364,30 +377,54 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             }
             *reinterpret_cast<uint4 *>(raw + base) = ld[u];
             tmax2 = __hmax2(tmax2, __hmax2(__hmax2(h2_of(ld[u].x), h2_of(ld[u].y)), __hmax2(h2_of(ld[u].z), h2_of(ld[u].w))));
+            if (u == 0) m0_2 = tmax2;
+            if (u <= 1) mA_2 = tmax2;
         }
     }
-    // thread maximum as an order-preserving key (0 when the thread saw nothing but padding)
-    uint32_t tmax = 0;
+    // Per-thread maxima as order-preserving keys (0 = nothing but padding), entered into one array per
+    // boundary: x_b[t] is the maximum of the part of thread t's data that lies below boundary b.  The
+    // k-th largest entry of x_b is a lower bound of the k-th largest key of that prefix, because k
+    // different elements of the prefix are at least that large.  One warp per boundary finds it.
+    auto key_of_max = [](const __half2 m2) -> uint32_t {
+        const uint16_t hb = __half_as_ushort(__hmax(__low2half(m2), __high2half(m2)));
+        return hb == kPad ? 0u : key_of(hb);
+    };
+    const uint32_t tmax = key_of_max(tmax2);
     {
-        const __half hm = __hmax(__low2half(tmax2), __high2half(tmax2));
-        const uint16_t hb = __half_as_ushort(hm);
-        tmax = hb == kPad ? 0u : key_of(hb);
-    }
-    // local lower bound of the k-th largest key: k-th largest per-thread maximum
-    uint32_t L_mine = 0;
-    {
-        const int have = __syncthreads_count(tmax >= 1);
-        if (have > 0) {// uniform
-            const int need = k < have ? k : have;
-            uint32_t lo = 1, hi = 65535;
-            while (lo < hi) {
-                const uint32_t mid = (lo + hi + 1) >> 1;
-                if (__syncthreads_count(tmax >= mid) >= need) lo = mid;
-                else hi = mid - 1;
+        uint16_t *xs = reinterpret_cast<uint16_t *>(ax.unc);// [kBounds][kThreads], free until the denominator
+        const uint32_t k0 = key_of_max(m0_2);
+        xs[0 * kThreads + tid] = (uint16_t) (tid < 64 ? k0 : 0u);
+        xs[1 * kThreads + tid] = (uint16_t) (tid < 128 ? k0 : 0u);
+        xs[2 * kThreads + tid] = (uint16_t) (tid < 512 ? k0 : 0u);
+        xs[3 * kThreads + tid] = (uint16_t) key_of_max(mA_2);
+        xs[4 * kThreads + tid] = (uint16_t) tmax;
+        __syncthreads();
+        if (warp < kBounds) {
+            const uint16_t *x = xs + warp * kThreads;
+            const int nx = warp == 0 ? 64 : warp == 1 ? 128 : warp == 2 ? 512 : kThreads;// entries that can be non-zero
+            int have = 0;
+            for (int i = lane; i < nx; i += 32) have += x[i] != 0;
+            have = __reduce_add_sync(0xffffffffu, have);
+            uint32_t lo = 0;
+            if (have > 0) {
+                const int need = k < have ? k : have;
+                uint32_t hi = 65535;
+                lo = 1;
+                while (lo < hi) {
+                    const uint32_t mid = (lo + hi + 1) >> 1;
+                    int c = 0;
+                    for (int i = lane; i < nx; i += 32) c += x[i] >= mid;
+                    c = __reduce_add_sync(0xffffffffu, c);
+                    if (c >= need) lo = mid;
+                    else hi = mid - 1;
+                }
+                if (have < k) lo = 1;
             }
-            L_mine = have < k ? 1u : lo;
+            if (lane == 0) ax.LB[warp] = lo;
         }
+        __syncthreads();
     }
+    const uint32_t L_mine = ax.LB[kBounds - 1];
     if (tid == 0) {
         peer_ax->mail.L_peer = L_mine;
         ax.fl.peer_cnt = 0;// the helper fills these in after the barrier
@@ -453,19 +490,125 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         }
     };
 
-    scan_range(0, my_pad, L, false);
-    if (!leader) ship_list();
+    // Leader half with one threshold per record segment ([.,512) [512,1024) [1024,4096) [4096,16384)
+    // [16384,65536)).  Every segment gets its own group of warps, in position order, so that the
+    // ordered lists stay short per warp although the early segments are dense in records:
+    // 8 + 8 warps take 64 elements each, then 4 warps x 3 blocks, 4 x 12 blocks, 8 x 24 blocks.
+    auto scan_segments = [&](uint32_t e_begin, const uint32_t *thr, bool strict, int cap) {
+        if (tid < kWarps) ax.wl.cnt[tid] = 0;
+        if (tid == 0) ax.wl.overflow = 0;
+        __syncthreads();
+        uint32_t r0, r1;
+        int seg;
+        if (warp < 8) {
+            seg = 0, r0 = 64u * warp, r1 = r0 + 64u;
+        } else if (warp < 16) {
+            seg = 1, r0 = 512u + 64u * (warp - 8), r1 = r0 + 64u;
+        } else if (warp < 20) {
+            seg = 2, r0 = 1024u + 768u * (warp - 16), r1 = r0 + 768u;
+        } else if (warp < 24) {
+            seg = 3, r0 = 4096u + 3072u * (warp - 20), r1 = r0 + 3072u;
+        } else {
+            seg = 4, r0 = 16384u + 6144u * (warp - 24), r1 = r0 + 6144u;
+        }
+        r1 = min(r1, n0);
+        const uint32_t tk = thr[seg];
+        const uint16_t th = tk < 0x0400u ? kPad : half_of_key(tk);
+        const __half2 thr2 = h2_of((uint32_t) th | ((uint32_t) th << 16));
+        if (r0 < r1) {
+            if (warp < 16) {
+                const uint32_t w2 = *reinterpret_cast<const uint32_t *>(raw + r0 + lane * 2);
+                const uint32_t mm = strict ? __hgt2_mask(h2_of(w2), thr2) : __hge2_mask(h2_of(w2), thr2);
+                const uint32_t j = r0 + lane * 2;
+                uint32_t mask = 0;
+                if ((mm & 1u) && j >= e_begin && j < r1) mask |= 1u;
+                if ((mm >> 16) && j + 1 >= e_begin && j + 1 < r1) mask |= 2u;
+                warp_append<2>(ax.wl, warp, lane, mask, &w2, r0);
+            } else {
+                for (uint32_t c = r0; c < r1; c += kBlk) {
+                    uint32_t w[4];
+                    lds_raw(raw + c + lane * 8, w);
+                    uint32_t mask = flag8(w, thr2, strict);
+                    const uint32_t first = c + lane * 8;
+                    if (first + 8 > r1) mask &= first >= r1 ? 0u : (1u << (r1 - first)) - 1u;
+                    warp_append<8>(ax.wl, warp, lane, mask, w, c);
+                }
+            }
+        }
+        __syncthreads();
+        flatten(ax.wl, ax.fl, tid, cap);
+    };
+
+    if (leader) {
+        scan_segments(0u, ax.LB, false, kFlatCap);// master list: per segment, everything >= the bound of the prefix it closes
+    } else {
+        scan_range(0, my_pad, L, false);
+        ship_list();
+    }
     cluster.sync();// CS2
     stamp();       // 1: candidate lists at the leader
 
     // ---- P3 (leader): exact top-k, records of the leader half --------------------------
     MinBuf mb{kEmptyMin, kEmptyMin, 0};
     float M = 0.f;
+    bool list_ok = false;
+    // state b + 1 (the k largest keys of the prefix that ends at boundary b) is wanted when a segment starts there
+    auto need_state = [&](int b) { return kBoundPos[b] < n0 || (kBoundPos[b] == n0 && n > n0); };
     if (leader) {
         const int cnt0 = ax.fl.cnt, cnt1 = ax.fl.peer_cnt;
-        const int m = cnt0 + cnt1;
-        const bool list_ok = !ax.fl.overflow && !ax.fl.peer_overflow && m <= kThreads;// one thread per candidate
+        list_ok = !ax.fl.overflow && !ax.fl.peer_overflow;
         if (list_ok) {
+            // Start states of the record segments, one warp per boundary: among the master entries
+            // below the boundary (a prefix of the list) the k largest keys are the k largest keys of
+            // that whole prefix of the row.  Their k-th largest is found by bisection on the key.
+            if ((uint32_t) k < n && warp < kBounds && need_state(warp)) {
+                const uint32_t P = kBoundPos[warp];
+                int nb = 0;
+                for (int i = lane; i < cnt0; i += 32) nb += ax.fl.idx[i] < P;
+                nb = __reduce_add_sync(0xffffffffu, nb);
+                uint32_t lo = max(ax.LB[warp], 1u), hi = 65535;
+                while (lo < hi) {
+                    const uint32_t mid = (lo + hi + 1) >> 1;
+                    int c = 0;
+                    for (int i = lane; i < nb; i += 32) c += ax.fl.key[i] >= mid;
+                    c = __reduce_add_sync(0xffffffffu, c);
+                    if (c >= k) lo = mid;
+                    else hi = mid - 1;
+                }
+                int filled = 0;
+                for (int i0 = 0; i0 < nb; i0 += 32) {
+                    const int i = i0 + lane;
+                    const uint32_t key = i < nb ? ax.fl.key[i] : 0u;
+                    const uint32_t hit = __ballot_sync(0xffffffffu, key > lo);
+                    if (key > lo) ax.state[warp + 1][filled + __popc(hit & ((1u << lane) - 1u))] = key;
+                    filled += __popc(hit);
+                }
+                for (int sl = filled + lane; sl < k; sl += 32) ax.state[warp + 1][sl] = lo;// copies of the k-th largest
+                if (lane == 0) ax.seg_tau[warp + 1] = lo;
+            }
+            __syncthreads();// the start states have been read off the master list
+            // keep only the candidates proper (key >= L): the ranking below is quadratic in the list length
+            if (warp == 0) {
+                int out = 0;
+                for (int i0 = 0; i0 < cnt0; i0 += 32) {// forward, in place: writes never pass the reads
+                    const int i = i0 + lane;
+                    const uint32_t key = i < cnt0 ? ax.fl.key[i] : 0u;
+                    const uint32_t idx = i < cnt0 ? ax.fl.idx[i] : 0u;
+                    const uint32_t hit = __ballot_sync(0xffffffffu, key >= L);
+                    __syncwarp();
+                    if (key >= L) {
+                        const int at = out + __popc(hit & ((1u << lane) - 1u));
+                        ax.fl.key[at] = (uint16_t) key;
+                        ax.fl.idx[at] = idx;
+                    }
+                    out += __popc(hit);
+                    __syncwarp();
+                }
+                if (lane == 0) ax.fl.cnt = out;
+            }
+            __syncthreads();
+            const int cnt0c = ax.fl.cnt;
+            const int m = cnt0c + cnt1;
             // move the helper's entries up behind the leader's own: one list in index order
             uint32_t mv_idx = 0;
             uint16_t mv_key = 0;
@@ -476,8 +619,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             if (tid == 0) ax.tie_groups = 0;
             __syncthreads();
             if (tid < cnt1) {
-                ax.fl.idx[cnt0 + tid] = mv_idx;
-                ax.fl.key[cnt0 + tid] = mv_key;
+                ax.fl.idx[cnt0c + tid] = mv_idx;
+                ax.fl.key[cnt0c + tid] = mv_key;
             }
             if (tid < kSlots) {
                 ax.top_key[tid] = 0;
@@ -493,20 +636,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             // element to the back, or pushes it out when nothing smaller is left to
             // evict.  Each such group is replayed over the candidates in index order
             // by one warp; its final place is behind all larger keys.
-            if (tid < m) {
-                const uint32_t my_key = ax.fl.key[tid];
+            for (int c = tid; c < m; c += kThreads) {// normally one candidate per thread, m ~ 100
+                const uint32_t my_key = ax.fl.key[c];
                 uint32_t greater = 0, same = 0;
                 bool seen_before = false;
                 for (int j = 0; j < m; ++j) {
                     const uint32_t kj = ax.fl.key[j];
                     greater += kj > my_key;
                     same += kj == my_key;
-                    seen_before |= (kj == my_key) && j < tid;
+                    seen_before |= (kj == my_key) && j < c;
                 }
                 if (same == 1) {
                     if (greater < (uint32_t) k) {
                         ax.top_key[greater] = my_key;
-                        ax.top_idx[greater] = ax.fl.idx[tid];
+                        ax.top_idx[greater] = ax.fl.idx[c];
                     }
                 } else if (!seen_before && greater < (uint32_t) k) {
                     const int g = atomicAdd(&ax.tie_groups, 1);// at most k groups start below rank k
@@ -614,59 +757,72 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         if ((uint32_t) k < n) {
             if (warp == 0) {
                 minbuf_init(mb, lane, k, raw);
-                if (lane == 0) ax.mail.tau_mid = mb.tau();
+                if (lane == 0) ax.seg_tau[0] = mb.tau();
+                if (!list_ok) {
+                    // slow path (candidate lists overflowed): one warp walks the leader half in order
+                    for (uint32_t b = 0; b < nblk0; ++b) records_direct_block(raw + b * kBlk, b == 0 ? (uint32_t) k : 0u, lane, mb);
+                    ax.state[kBounds][lane] = mb.v0 >> 6;
+                    ax.state[kBounds][lane + 32] = mb.v1 >> 6;
+                    if (lane == 0) ax.seg_tau[kBounds] = mb.tau();
+                }
             }
             __syncthreads();
-            // tiles [k,256) [256,1024) [1024,4096) ... each four times the previous end:
-            // about 3k flagged elements per tile, of which k*ln(4) are records
-            uint32_t t_begin = (uint32_t) k;
-            uint32_t t_end = min(n0, (uint32_t) kBlk);
-            while (t_begin < n0) {
-                scan_range(t_begin, t_end, ax.mail.tau_mid, true);
-                if (warp == 0) {
-                    if (!ax.fl.overflow) {
-                        replay_list(ax.fl, 0, ax.fl.cnt, raw, 0u, lane, mb);
-                    } else {
-                        for (uint32_t b = t_begin / kBlk; b * kBlk < t_end; ++b) {
-                            records_direct_block(raw + b * kBlk, b * kBlk < t_begin ? t_begin - b * kBlk : 0u, lane, mb);
-                        }
-                    }
-                    if (lane == 0) ax.mail.tau_mid = mb.tau();
-                }
-                __syncthreads();
-                t_begin = t_end;
-                t_end = min(n0, t_end * 4);
-            }
+            if (n > n0 && tid < kSlots) peer_ax->state[kBounds][tid] = ax.state[kBounds][tid];
         }
         if (tid == 0) {// hand the helper what it needs
-            peer_ax->mail.tau_mid = ax.mail.tau_mid;
+            peer_ax->seg_tau[kBounds] = ax.seg_tau[kBounds];
             peer_ax->mail.mkey = ax.mail.mkey;
             peer_ax->mail.s_base = ax.mail.s_base;
             peer_ax->mail.pos_base = ax.mail.pos_base;
             peer_ax->mail.done = ax.mail.done;
-            ax.fl.peer_cnt = 0;
-            ax.fl.peer_overflow = 0;
         }
     }
     cluster.sync();// CS3
-    stamp();       // 3: leader half patched
+    stamp();       // 3: start states known on both sides
 
-    // ---- P4 (helper): elements of its half above the running k-th value -----------------
-    if (!leader && my_n > 0 && !ax.mail.done) {
-        scan_range(0, my_pad, ax.mail.tau_mid, true);
-        ship_list();
-    }
-    cluster.sync();// CS4
-
-    // ---- P5 (leader, warp 0): records of the helper half -------------------------------
-    if (leader && warp == 0 && n > n0 && !ax.mail.done) {
-        if (!ax.fl.peer_overflow) {
-            replay_list(ax.fl, kFlatCap, ax.fl.peer_cnt, peer_raw, (uint32_t) kHalfElems, lane, mb);
-        } else {
-            for (uint32_t b = 0; b < nblk - nblk0; ++b) records_direct_block(peer_raw + b * kBlk, 0u, lane, mb);
+    // ---- P4: records.  Leader: its segments in parallel, one warp each.  Helper: its half. ----
+    if (leader && list_ok && (uint32_t) k < n) {
+        scan_segments((uint32_t) k, ax.seg_tau, true, 2 * kFlatCap);// the whole list area: nothing else uses it now// flagged: above the exact k-th largest at the segment start
+        if (!ax.fl.overflow) {
+            // segment i on warp i (the last one on warp 5): the long first segment keeps a scheduler to itself
+            const int sg = warp < kBounds - 1 ? warp : (warp == kBounds ? kBounds - 1 : -1);
+            if (sg >= 0) {
+                const uint32_t s_begin = sg == 0 ? (uint32_t) k : kBoundPos[sg - 1];
+                const uint32_t s_end = min(kBoundPos[sg], n0);
+                if (s_begin < s_end) {
+                    const int cnt = ax.fl.cnt;
+                    int first = 0, last = 0;
+                    for (int i = lane; i < cnt; i += 32) {
+                        const uint32_t p = ax.fl.idx[i];
+                        first += p < s_begin;
+                        last += p < s_end;
+                    }
+                    first = __reduce_add_sync(0xffffffffu, first);
+                    last = __reduce_add_sync(0xffffffffu, last);
+                    MinBuf sb;
+                    if (sg == 0) minbuf_init(sb, lane, k, raw);
+                    else minbuf_init_keys(sb, lane, k, ax.state[sg]);
+                    replay_list(ax.fl, first, last - first, raw, 0u, lane, sb);
+                }
+            }
+        } else if (warp == 0) {// flagged list overflowed: serial walk from the initial state
+            minbuf_init(mb, lane, k, raw);
+            for (uint32_t b = 0; b < nblk0; ++b) records_direct_block(raw + b * kBlk, b == 0 ? (uint32_t) k : 0u, lane, mb);
         }
     }
-    cluster.sync();// CS5
+    if (!leader && my_n > 0 && !ax.mail.done) {
+        scan_range(0, my_pad, ax.seg_tau[kBounds], true);
+        if (warp == 0) {
+            MinBuf hb;
+            minbuf_init_keys(hb, lane, k, ax.state[kBounds]);
+            if (!ax.fl.overflow) {
+                replay_list(ax.fl, 0, ax.fl.cnt, raw, (uint32_t) kHalfElems, lane, hb);
+            } else {
+                for (uint32_t b = 0; b < my_nblk; ++b) records_direct_block(raw + b * kBlk, 0u, lane, hb);
+            }
+        }
+    }
+    cluster.sync();// CS4
     stamp();       // 4: whole row patched
     M = val_of(ax.mail.mkey);
 
