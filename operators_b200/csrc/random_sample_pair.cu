@@ -26,6 +26,7 @@
 #include "random_sample_device.cuh"
 
 #include <cooperative_groups.h>
+#include <cstddef>
 
 namespace cg = cooperative_groups;
 using namespace b200;
@@ -35,7 +36,6 @@ namespace {
 constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr int kBlk = 256;
-constexpr int kListCap = 128;     // per-warp ordered list
 constexpr int kFlatCap = 1024;    // per-CTA ordered list (candidates, flagged records)
 constexpr int kHalfElems = 65536; // elements held by one CTA
 constexpr int kMaxBlk = 2 * kHalfElems / kBlk;
@@ -43,20 +43,27 @@ constexpr int kLevels = 4;
 constexpr int kUncCap = 6144;
 constexpr int kMaxRounds = 6;     // 6 x 4 binades covers any sum of <= 2^17 terms <= 1
 constexpr int kTieGroups = 64;
-// Record segments of the leader half end at these positions; the helper half is one more segment.
-// Each boundary's prefix is covered by whole per-thread load slots: thread t's first vector is elements
-// [8t, 8t+8), its first two vectors lie below 16384, all eight below 65536.
-constexpr int kBounds = 5;
-__device__ __constant__ uint32_t kBoundPos[kBounds] = {512u, 1024u, 4096u, 16384u, 65536u};
+// Record segments of the leader half end at these positions (each twice the one before, so every
+// segment holds about k flagged entries and 0.7 k records whatever its length); the helper half is
+// one more segment.  The k largest keys of a prefix that ends at one of the first kDirect boundaries
+// are found directly on the row; for the later boundaries they come from a candidate list whose
+// threshold is a lower bound taken from per-thread maxima.  Those prefixes are covered by whole
+// per-thread load slots: thread t's vector u is elements [8t + 8192u, 8t + 8192u + 8).
+constexpr int kBounds = 10;
+constexpr int kDirect = 5;
+__device__ __constant__ uint32_t kBoundPos[kBounds] = {128u, 256u, 512u, 1024u, 2048u, 4096u, 8192u, 16384u, 32768u, 65536u};
+// Scan assignment of the leader half: warp w looks at [kScanR0[w], kScanR0[w + 1]), which lies inside
+// segment kScanSeg[w].  Pieces shorter than 256 are cut into 64-element chunks, the others into
+// 256-element blocks (at most 16 per warp).
+__device__ __constant__ uint32_t kScanR0[kWarps + 1] = {
+    0u, 64u, 128u, 192u, 256u, 384u, 512u, 768u, 1024u, 1536u, 2048u, 3072u, 4096u, 6144u, 8192u, 12288u,
+    16384u, 20480u, 24576u, 28672u, 32768u, 36864u, 40960u, 45056u, 49152u, 53248u, 57344u, 61440u, 65536u,
+    65536u, 65536u, 65536u, 65536u};
+__device__ __constant__ uint8_t kScanSeg[kWarps] = {0, 0, 1, 1, 2, 2, 3, 3, 4, 4, 5, 5, 6, 6, 7, 7,
+                                                    8, 8, 8, 8, 9, 9, 9, 9, 9, 9, 9, 9, 9, 9, 9, 9};
 constexpr uint32_t kEmptyMin = 0xFFFFFFFFu;
 constexpr uint16_t kPad = 0xFC00u;// fp16 -inf: never a candidate, contributes nothing
 
-struct WarpLists {
-    uint32_t idx[kWarps][kListCap];
-    uint16_t key[kWarps][kListCap];
-    int cnt[kWarps];
-    int overflow;
-};
 // Ordered (index order) list of (position, key) pairs.  Slots [0, kFlatCap) hold
 // this CTA's entries; at the leader, slots [kFlatCap, 2*kFlatCap) receive the
 // helper's entries.
@@ -67,6 +74,8 @@ struct FlatList {
     int overflow; // own entries did not fit
     int peer_cnt; // leader: helper's entries
     int peer_overflow;
+    int wcnt[kWarps];          // entries found by each warp of the scan
+    int seg_first[kBounds + 1];// leader: list position of the first entry of segment i; [kBounds] = count
 };
 struct Mail {// written by the other CTA of the pair (the leader also fills its own copy)
     uint32_t L_peer;
@@ -77,7 +86,6 @@ struct Mail {// written by the other CTA of the pair (the leader also fills its 
     int done;
 };
 struct Aux {
-    WarpLists wl;
     FlatList fl;
     uint16_t gbuf[2 * kFlatCap];// top-k: per-key-group queues of candidate ordinals
     uint32_t tie_key[kTieGroups];
@@ -94,12 +102,13 @@ struct Aux {
     uint32_t seg_tau[kBounds + 1];       // exact k-th largest key at the start of segment i
     uint32_t state[kBounds + 1][kSlots]; // the k largest keys at the start of segment i (slot order irrelevant)
     uint8_t relq[kWarps][kBlk];  // per warp: in-block indices of the elements that can contribute
-    uint32_t unc[kUncCap];       // positions (local) to re-evaluate exactly
+    alignas(16) uint32_t unc[kUncCap];// positions (local) to re-evaluate exactly; before that, the per-thread maxima (read as 16-byte vectors)
     int unc_cnt;
     Mail mail;
 };
 
 constexpr size_t kSmemBytes = (size_t) kHalfElems * 2 + sizeof(Aux);
+static_assert(offsetof(Aux, unc) % 16 == 0 && (kHalfElems * 2) % 16 == 0, "vector loads from the maxima arrays");
 static_assert(kSmemBytes <= 227 * 1024, "row half + bookkeeping must fit one SM's shared memory");
 
 __device__ __forceinline__ uint16_t half_of_key(uint32_t key) {
@@ -110,83 +119,45 @@ __device__ __forceinline__ __half2 h2_of(uint32_t w) { return *reinterpret_cast<
 // 8 consecutive fp16 values (4 packed words) against a threshold: bit e of the
 // result is set when element e is > thr (strict) or >= thr.
 __device__ __forceinline__ uint32_t flag8(const uint32_t w[4], __half2 thr2, bool strict) {
-    uint32_t mask = 0;
+    uint32_t m[4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const uint32_t m = strict ? __hgt2_mask(h2_of(w[q]), thr2) : __hge2_mask(h2_of(w[q]), thr2);
-        mask |= ((m & 1u) << (2 * q)) | (((m >> 16) & 1u) << (2 * q + 1));
-    }
-    return mask;
+    for (int q = 0; q < 4; ++q) m[q] = strict ? __hgt2_mask(h2_of(w[q]), thr2) : __hge2_mask(h2_of(w[q]), thr2);
+    // element 2q -> bit 2q, element 2q+1 -> bit 16 + 2q + 1, then fold the upper half down
+    const uint32_t p = (m[0] & 0x00020001u) | (m[1] & 0x00080004u) | (m[2] & 0x00200010u) | (m[3] & 0x00800040u);
+    return (p | (p >> 16)) & 0xFFu;
 }
 __device__ __forceinline__ void lds_raw(const uint16_t *p, uint32_t w[4]) {
     const uint4 v = *reinterpret_cast<const uint4 *>(p);
     w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
 }
 __device__ __forceinline__ uint16_t half_at(const uint32_t *w, int e) { return (uint16_t) (w[e >> 1] >> ((e & 1) * 16)); }
-
-// Ordered append of the flagged elements a warp looked at (E consecutive
-// elements per lane held as packed fp16 words, lane-major order = index order).
-template<int E>
-__device__ __forceinline__ void warp_append(WarpLists &wl, int warp, int lane, uint32_t mask, const uint32_t *words,
-                                            uint32_t base_idx) {
-    const uint32_t any = __ballot_sync(0xffffffffu, mask != 0);
-    if (any == 0) return;
-    const int cnt = __popc(mask);
-    int pre = cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, pre, o);
-        if (lane >= o) pre += t;
-    }
-    const int total = __shfl_sync(0xffffffffu, pre, 31);
-    const int start = wl.cnt[warp];
-    if (start + total > kListCap) {
-        if (lane == 0) wl.overflow = 1;
-    } else {
-        int at = start + pre - cnt;
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-            if (mask & (1u << e)) {
-                wl.idx[warp][at] = base_idx + lane * E + e;
-                wl.key[warp][at] = (uint16_t) key_of(half_at(words, e));
-                ++at;
-            }
-        }
-    }
-    __syncwarp();
-    if (lane == 0) wl.cnt[warp] = min(start + total, kListCap + 1);
-    __syncwarp();
+__device__ __forceinline__ __half2 thr2_of_key(uint32_t key) {
+    // keys below 0x0400 lie under every fp16 value (0x0400 is -inf): compare with -inf then
+    const uint32_t th = key < 0x0400u ? kPad : half_of_key(key);
+    return h2_of(th | (th << 16));
 }
 
-// Warp lists -> this CTA's part of the ordered list.  All threads of the CTA
-// call it (it contains CTA barriers).
-__device__ __forceinline__ void flatten(WarpLists &wl, FlatList &fl, int tid, int cap = kFlatCap) {
-    __shared__ int s_off[kWarps];
-    if (tid < 32) {// kWarps == 32: one lane per warp list
-        const int c = wl.cnt[tid];
-        int pre = c;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int t = __shfl_up_sync(0xffffffffu, pre, o);
-            if (tid >= o) pre += t;
-        }
-        s_off[tid] = pre - c;
-        if (tid == 31) {
-            const bool over = wl.overflow != 0 || pre > cap;
-            fl.cnt = over ? 0 : pre;
-            fl.overflow = over ? 1 : 0;
-        }
+// How many of the n_vec8 * 8 fp16 values at p (shared memory, 16-byte aligned) are >= / > the threshold.
+// One warp; every lane gets the count.
+__device__ __forceinline__ int warp_count_f16(const uint16_t *p, int n_vec8, __half2 thr2, bool strict, int lane) {
+    int c = 0;
+    for (int v = lane; v < n_vec8; v += 32) {
+        uint32_t w[4];
+        lds_raw(p + v * 8, w);
+        c += __popc(flag8(w, thr2, strict));
     }
-    __syncthreads();
-    if (!fl.overflow) {
-        const int w = tid >> 5, lane = tid & 31;
-        const int c = wl.cnt[w], off = s_off[w];
-        for (int i = lane; i < c; i += 32) {
-            fl.idx[off + i] = wl.idx[w][i];
-            fl.key[off + i] = wl.key[w][i];
-        }
+    return __reduce_add_sync(0xffffffffu, c);
+}
+// Key of the k-th largest of those values (with multiplicity), by bisection on the key; 0x0400 (the key
+// of -inf) when fewer than k values lie above -inf.  One warp.
+__device__ __forceinline__ uint32_t warp_kth_largest_f16(const uint16_t *p, int n_vec8, int k, int lane) {
+    uint32_t lo = 0x0400u, hi = 0xFC00u;// keys of -inf and +inf
+    while (lo < hi) {
+        const uint32_t mid = (lo + hi + 1) >> 1;
+        if (warp_count_f16(p, n_vec8, thr2_of_key(mid), false, lane) >= k) lo = mid;
+        else hi = mid - 1;
     }
-    __syncthreads();
+    return lo;
 }
 
 // Running multiset of the k largest keys seen so far, 2 slots per lane.  Each
@@ -353,7 +324,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
 
     // ---- P1: this CTA's half of the row -> shared memory; per-thread maxima --------------
     const bool in_aligned = (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
-    __half2 tmax2 = h2_of(0xFC00FC00u), m0_2 = tmax2, mA_2 = tmax2;// running maximum; after 1 and after 2 vectors
+    __half2 tmax2 = h2_of(0xFC00FC00u), m0_2 = tmax2, mA_2 = tmax2, mB_2 = tmax2;// running maximum; after 1, 2 and 4 vectors
     constexpr int kInFlight = 8;
     for (uint32_t base0 = tid * 8; base0 < my_pad; base0 += kThreads * 8 * kInFlight) {
         uint4 ld[kInFlight];
@@ -379,48 +350,63 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             tmax2 = __hmax2(tmax2, __hmax2(__hmax2(h2_of(ld[u].x), h2_of(ld[u].y)), __hmax2(h2_of(ld[u].z), h2_of(ld[u].w))));
             if (u == 0) m0_2 = tmax2;
             if (u <= 1) mA_2 = tmax2;
+            if (u <= 3) mB_2 = tmax2;
         }
     }
-    // Per-thread maxima as order-preserving keys (0 = nothing but padding), entered into one array per
-    // boundary: x_b[t] is the maximum of the part of thread t's data that lies below boundary b.  The
+    // Per-thread maxima (fp16; -inf = nothing but padding), entered into one array per boundary from
+    // 4096 on: x_b[t] is the maximum of the part of thread t's data that lies below boundary b.  The
     // k-th largest entry of x_b is a lower bound of the k-th largest key of that prefix, because k
-    // different elements of the prefix are at least that large.  One warp per boundary finds it.
-    auto key_of_max = [](const __half2 m2) -> uint32_t {
-        const uint16_t hb = __half_as_ushort(__hmax(__low2half(m2), __high2half(m2)));
-        return hb == kPad ? 0u : key_of(hb);
-    };
-    const uint32_t tmax = key_of_max(tmax2);
+    // different elements of the prefix are at least that large.  One warp per boundary finds it; five
+    // more warps find the exact k largest keys of the short prefixes (128 .. 2048) on the row itself.
+    auto max_of = [](const __half2 m2) -> uint16_t { return __half_as_ushort(__hmax(__low2half(m2), __high2half(m2))); };
+    // state b + 1 (the k largest keys of the prefix that ends at boundary b) is wanted when a segment starts there
+    auto need_state = [&](int b) { return kBoundPos[b] < n0 || (kBoundPos[b] == n0 && n > n0); };
     {
-        uint16_t *xs = reinterpret_cast<uint16_t *>(ax.unc);// [kBounds][kThreads], free until the denominator
-        const uint32_t k0 = key_of_max(m0_2);
-        xs[0 * kThreads + tid] = (uint16_t) (tid < 64 ? k0 : 0u);
-        xs[1 * kThreads + tid] = (uint16_t) (tid < 128 ? k0 : 0u);
-        xs[2 * kThreads + tid] = (uint16_t) (tid < 512 ? k0 : 0u);
-        xs[3 * kThreads + tid] = (uint16_t) key_of_max(mA_2);
-        xs[4 * kThreads + tid] = (uint16_t) tmax;
+        uint16_t *xs = reinterpret_cast<uint16_t *>(ax.unc);// [kBounds - kDirect][kThreads], free until the denominator
+        const uint16_t x0 = max_of(m0_2);
+        xs[0 * kThreads + tid] = tid < 512 ? x0 : kPad;
+        xs[1 * kThreads + tid] = x0;
+        xs[2 * kThreads + tid] = max_of(mA_2);
+        xs[3 * kThreads + tid] = max_of(mB_2);
+        xs[4 * kThreads + tid] = max_of(tmax2);
         __syncthreads();
-        if (warp < kBounds) {
-            const uint16_t *x = xs + warp * kThreads;
-            const int nx = warp == 0 ? 64 : warp == 1 ? 128 : warp == 2 ? 512 : kThreads;// entries that can be non-zero
-            int have = 0;
-            for (int i = lane; i < nx; i += 32) have += x[i] != 0;
-            have = __reduce_add_sync(0xffffffffu, have);
-            uint32_t lo = 0;
-            if (have > 0) {
-                const int need = k < have ? k : have;
-                uint32_t hi = 65535;
-                lo = 1;
-                while (lo < hi) {
-                    const uint32_t mid = (lo + hi + 1) >> 1;
-                    int c = 0;
-                    for (int i = lane; i < nx; i += 32) c += x[i] >= mid;
-                    c = __reduce_add_sync(0xffffffffu, c);
-                    if (c >= need) lo = mid;
-                    else hi = mid - 1;
+        if (warp < kBounds - kDirect && (leader || warp == kBounds - kDirect - 1)) {
+            const uint32_t kth = warp_kth_largest_f16(xs + warp * kThreads, warp == 0 ? 64 : 128, k, lane);
+            if (lane == 0) ax.LB[kDirect + warp] = kth <= 0x0400u ? 1u : kth;// fewer than k threads hold data: everything
+        } else if (leader && warp >= kBounds - kDirect && warp < kBounds && (uint32_t) k < n &&
+                   need_state(warp - (kBounds - kDirect))) {
+            const int b = warp - (kBounds - kDirect);
+            const int nv = (int) (kBoundPos[b] / 8u);
+            const uint32_t tau = warp_kth_largest_f16(raw, nv, k, lane);
+            const __half2 t2 = thr2_of_key(tau);
+            uint32_t *st = ax.state[b + 1];
+            int filled = 0;
+            for (int v0 = 0; v0 < nv; v0 += 32) {
+                const int v = v0 + lane;
+                uint32_t m = 0;
+                if (v < nv) {
+                    uint32_t w[4];
+                    lds_raw(raw + v * 8, w);
+                    m = flag8(w, t2, true);
                 }
-                if (have < k) lo = 1;
+                if (__ballot_sync(0xffffffffu, m != 0) == 0) continue;
+                const int cnt = __popc(m);
+                int incl = cnt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                int at = filled + incl - cnt;
+                while (m) {// fewer than k keys lie above the k-th largest
+                    const int e = __ffs(m) - 1;
+                    m &= m - 1;
+                    st[at++] = key_of(raw[v * 8 + e]);
+                }
+                filled += __shfl_sync(0xffffffffu, incl, 31);
             }
-            if (lane == 0) ax.LB[warp] = lo;
+            for (int sl = filled + lane; sl < k; sl += 32) st[sl] = tau;// copies of the k-th largest
+            if (lane == 0) ax.seg_tau[b + 1] = tau;
         }
         __syncthreads();
     }
@@ -435,48 +421,104 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
     const uint32_t L = max(max(L_mine, ax.mail.L_peer), 1u);
 
     // ---- P2: candidates (key >= L), ordered --------------------------------------------
-    // Flag elements of [e_begin, e_end) of the LOCAL half against the key `thresh`
-    // into the per-warp ordered lists.  Short ranges are cut into 64-element
-    // pieces (one per warp, two elements per lane) so that the first,
-    // record-dense tiles neither overflow a warp's list nor leave most warps idle.
-    auto scan_range = [&](uint32_t e_begin, uint32_t e_end, uint32_t thresh, bool strict) {
-        if (tid < kWarps) ax.wl.cnt[tid] = 0;
-        if (tid == 0) ax.wl.overflow = 0;
-        __syncthreads();
-        // keys below 0x0400 lie under every fp16 value (0x0400 is -inf): compare with -inf then.
-        // Padding is -inf too, so positions at or beyond the real end are masked out by index.
-        const uint16_t th = thresh < 0x0400u ? kPad : half_of_key(thresh);
-        const __half2 thr2 = h2_of((uint32_t) th | ((uint32_t) th << 16));
-        e_end = min(e_end, my_n);
-        if (e_end <= e_begin) {
-            // nothing to scan
-        } else if (e_end - e_begin <= 2048u) {
-            const uint32_t base64 = e_begin & ~63u;
-            for (uint32_t c = base64 + warp * 64; c < e_end; c += kWarps * 64) {
-                const uint32_t w2 = *reinterpret_cast<const uint32_t *>(raw + c + lane * 2);
-                const uint32_t m = strict ? __hgt2_mask(h2_of(w2), thr2) : __hge2_mask(h2_of(w2), thr2);
-                const uint32_t j = c + lane * 2;
-                uint32_t mask = 0;
-                if ((m & 1u) && j >= e_begin && j < e_end) mask |= 1u;
-                if ((m >> 16) && j + 1 >= e_begin && j + 1 < e_end) mask |= 2u;
-                warp_append<2>(ax.wl, warp, lane, mask, &w2, my_base + c);
+    // Ordered list of the elements of this warp's piece [r0, r1) of the LOCAL half that lie above
+    // (strict) or at or above the key `tk`, positions below e_begin left out.  Two passes: every
+    // warp flags its piece into registers (one byte per 256-element block or 64-element chunk) and
+    // counts; after one CTA barrier each warp knows where its entries go and writes them in index
+    // order.  All threads of the CTA call it; `cap` is the room in the list.
+    auto scan_ordered = [&](uint32_t r0, uint32_t r1, uint32_t e_begin, uint32_t tk, bool strict, int cap) {
+        const __half2 thr2 = thr2_of_key(tk);
+        const bool fine = r1 - r0 < (uint32_t) kBlk;// whole pieces are multiples of 64 or of 256
+        r1 = min(r1, my_n);                         // padding beyond the real end is never listed
+        uint32_t pm[4] = {0u, 0u, 0u, 0u};         // flags of piece i: byte i & 3 of pm[i >> 2]
+        if (r0 < r1) {
+            if (fine) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const uint32_t c = r0 + 64u * i;
+                    if (c < r1) {
+                        const uint32_t w2 = *reinterpret_cast<const uint32_t *>(raw + c + lane * 2);
+                        const uint32_t mm = strict ? __hgt2_mask(h2_of(w2), thr2) : __hge2_mask(h2_of(w2), thr2);
+                        const uint32_t j = c + lane * 2;
+                        uint32_t mask = 0;
+                        if ((mm & 1u) && j >= e_begin && j < r1) mask |= 1u;
+                        if ((mm >> 16) && j + 1 >= e_begin && j + 1 < r1) mask |= 2u;
+                        pm[0] |= mask << (8 * i);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t c = r0 + (uint32_t) kBlk * i;
+                    if (c < r1) {
+                        uint32_t w[4];
+                        lds_raw(raw + c + lane * 8, w);
+                        uint32_t mask = flag8(w, thr2, strict);
+                        const uint32_t first = c + lane * 8;
+                        if (first + 8 > r1) mask &= first >= r1 ? 0u : (1u << (r1 - first)) - 1u;
+                        if (first < e_begin) mask &= first + 8 <= e_begin ? 0u : ~((1u << (e_begin - first)) - 1u);
+                        pm[i >> 2] |= mask << (8 * (i & 3));
+                    }
+                }
             }
-        } else {// whole 256-element blocks, a contiguous span of blocks per warp
-            const uint32_t bb = e_begin / kBlk, be = (e_end + kBlk - 1) / kBlk;
-            const uint32_t span = (be - bb + kWarps - 1) / kWarps;
-            const uint32_t b0 = bb + warp * span, b1 = min(be, b0 + span);
-            for (uint32_t b = b0; b < b1; ++b) {
-                uint32_t w[4];
-                lds_raw(raw + b * kBlk + lane * 8, w);
-                uint32_t mask = flag8(w, thr2, strict);
-                const uint32_t first = b * kBlk + lane * 8;// drop positions outside [e_begin, e_end)
-                if (first + 8 > e_end) mask &= first >= e_end ? 0u : (1u << (e_end - first)) - 1u;
-                if (first < e_begin) mask &= first + 8 <= e_begin ? 0u : ~((1u << (e_begin - first)) - 1u);
-                warp_append<8>(ax.wl, warp, lane, mask, w, my_base + b * kBlk);
+        }
+        const int mine = __popc(pm[0]) + __popc(pm[1]) + __popc(pm[2]) + __popc(pm[3]);
+        const int wtot = __reduce_add_sync(0xffffffffu, mine);
+        if (lane == 0) ax.fl.wcnt[warp] = wtot;
+        __syncthreads();
+        const int c_l = ax.fl.wcnt[lane];// kWarps == 32: one lane per warp
+        int at = __reduce_add_sync(0xffffffffu, lane < warp ? c_l : 0);
+        const int tot = __reduce_add_sync(0xffffffffu, c_l);
+        const bool over = tot > cap;
+        if (tid == 0) {
+            ax.fl.cnt = over ? 0 : tot;
+            ax.fl.overflow = over ? 1 : 0;
+            ax.fl.seg_first[kBounds] = tot;
+        }
+        if (leader && lane == 0 && (warp == 0 || kScanSeg[warp - 1] != kScanSeg[warp])) ax.fl.seg_first[kScanSeg[warp]] = at;
+        if (!over && wtot > 0) {
+            uint32_t nz = 0;// pieces in which this lane flagged something
+#pragma unroll
+            for (int i = 0; i < 16; ++i) nz |= ((pm[i >> 2] >> (8 * (i & 3))) & 0xFFu) ? 1u << i : 0u;
+            uint32_t todo = __reduce_or_sync(0xffffffffu, nz);
+            const int per_lane = fine ? 2 : 8;
+            while (todo) {
+                const int i = __ffs(todo) - 1;
+                todo &= todo - 1;
+                const uint32_t word = (i >> 2) == 0 ? pm[0] : (i >> 2) == 1 ? pm[1] : (i >> 2) == 2 ? pm[2] : pm[3];
+                uint32_t m = (word >> (8 * (i & 3))) & 0xFFu;
+                const uint32_t pos0 = r0 + (fine ? 64u : (uint32_t) kBlk) * i + lane * per_lane;
+                const uint32_t any = __ballot_sync(0xffffffffu, m != 0);
+                const uint32_t multi = __ballot_sync(0xffffffffu, (m & (m - 1)) != 0);
+                if (multi == 0) {// the usual case: at most one hit per lane
+                    if (m) {
+                        const int e = __ffs(m) - 1;
+                        const int q = at + __popc(any & ((1u << lane) - 1u));
+                        ax.fl.idx[q] = my_base + pos0 + e;
+                        ax.fl.key[q] = (uint16_t) key_of(raw[pos0 + e]);
+                    }
+                    at += __popc(any);
+                } else {
+                    const int cnt = __popc(m);
+                    int incl = cnt;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                        if (lane >= o) incl += t;
+                    }
+                    int q = at + incl - cnt;
+                    while (m) {
+                        const int e = __ffs(m) - 1;
+                        m &= m - 1;
+                        ax.fl.idx[q] = my_base + pos0 + e;
+                        ax.fl.key[q] = (uint16_t) key_of(raw[pos0 + e]);
+                        ++q;
+                    }
+                    at += __shfl_sync(0xffffffffu, incl, 31);
+                }
             }
         }
         __syncthreads();
-        flatten(ax.wl, ax.fl, tid);
     };
     // Helper: hand this CTA's list to the leader (second half of the leader's arrays).
     auto ship_list = [&]() {
@@ -489,60 +531,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             peer_ax->fl.peer_overflow = ax.fl.overflow;
         }
     };
-
-    // Leader half with one threshold per record segment ([.,512) [512,1024) [1024,4096) [4096,16384)
-    // [16384,65536)).  Every segment gets its own group of warps, in position order, so that the
-    // ordered lists stay short per warp although the early segments are dense in records:
-    // 8 + 8 warps take 64 elements each, then 4 warps x 3 blocks, 4 x 12 blocks, 8 x 24 blocks.
-    auto scan_segments = [&](uint32_t e_begin, const uint32_t *thr, bool strict, int cap) {
-        if (tid < kWarps) ax.wl.cnt[tid] = 0;
-        if (tid == 0) ax.wl.overflow = 0;
-        __syncthreads();
-        uint32_t r0, r1;
-        int seg;
-        if (warp < 8) {
-            seg = 0, r0 = 64u * warp, r1 = r0 + 64u;
-        } else if (warp < 16) {
-            seg = 1, r0 = 512u + 64u * (warp - 8), r1 = r0 + 64u;
-        } else if (warp < 20) {
-            seg = 2, r0 = 1024u + 768u * (warp - 16), r1 = r0 + 768u;
-        } else if (warp < 24) {
-            seg = 3, r0 = 4096u + 3072u * (warp - 20), r1 = r0 + 3072u;
-        } else {
-            seg = 4, r0 = 16384u + 6144u * (warp - 24), r1 = r0 + 6144u;
-        }
-        r1 = min(r1, n0);
-        const uint32_t tk = thr[seg];
-        const uint16_t th = tk < 0x0400u ? kPad : half_of_key(tk);
-        const __half2 thr2 = h2_of((uint32_t) th | ((uint32_t) th << 16));
-        if (r0 < r1) {
-            if (warp < 16) {
-                const uint32_t w2 = *reinterpret_cast<const uint32_t *>(raw + r0 + lane * 2);
-                const uint32_t mm = strict ? __hgt2_mask(h2_of(w2), thr2) : __hge2_mask(h2_of(w2), thr2);
-                const uint32_t j = r0 + lane * 2;
-                uint32_t mask = 0;
-                if ((mm & 1u) && j >= e_begin && j < r1) mask |= 1u;
-                if ((mm >> 16) && j + 1 >= e_begin && j + 1 < r1) mask |= 2u;
-                warp_append<2>(ax.wl, warp, lane, mask, &w2, r0);
-            } else {
-                for (uint32_t c = r0; c < r1; c += kBlk) {
-                    uint32_t w[4];
-                    lds_raw(raw + c + lane * 8, w);
-                    uint32_t mask = flag8(w, thr2, strict);
-                    const uint32_t first = c + lane * 8;
-                    if (first + 8 > r1) mask &= first >= r1 ? 0u : (1u << (r1 - first)) - 1u;
-                    warp_append<8>(ax.wl, warp, lane, mask, w, c);
-                }
-            }
-        }
-        __syncthreads();
-        flatten(ax.wl, ax.fl, tid, cap);
+    // Helper half: equal spans of whole blocks per warp (at most 8), one threshold.
+    auto scan_helper = [&](uint32_t tk, bool strict) {
+        const uint32_t span = ((my_nblk + kWarps - 1) / kWarps) * kBlk;
+        const uint32_t r0 = min(warp * span, my_pad);
+        scan_ordered(r0, min(r0 + span, my_pad), 0u, tk, strict, kFlatCap);
     };
 
     if (leader) {
-        scan_segments(0u, ax.LB, false, kFlatCap);// master list: per segment, everything >= the bound of the prefix it closes
+        // master list.  Segments below 2048: the candidates proper (key >= L); their start states are known.
+        // Later segments: everything >= the bound of the prefix the segment closes, for the start states.
+        const int sg = kScanSeg[warp];
+        scan_ordered(kScanR0[warp], kScanR0[warp + 1], 0u, sg < kDirect ? L : ax.LB[sg], false, kFlatCap);
     } else {
-        scan_range(0, my_pad, L, false);
+        scan_helper(L, false);
         ship_list();
     }
     cluster.sync();// CS2
@@ -552,38 +554,58 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
     MinBuf mb{kEmptyMin, kEmptyMin, 0};
     float M = 0.f;
     bool list_ok = false;
-    // state b + 1 (the k largest keys of the prefix that ends at boundary b) is wanted when a segment starts there
-    auto need_state = [&](int b) { return kBoundPos[b] < n0 || (kBoundPos[b] == n0 && n > n0); };
     if (leader) {
         const int cnt0 = ax.fl.cnt, cnt1 = ax.fl.peer_cnt;
         list_ok = !ax.fl.overflow && !ax.fl.peer_overflow;
         if (list_ok) {
-            // Start states of the record segments, one warp per boundary: among the master entries
-            // below the boundary (a prefix of the list) the k largest keys are the k largest keys of
-            // that whole prefix of the row.  Their k-th largest is found by bisection on the key.
-            if ((uint32_t) k < n && warp < kBounds && need_state(warp)) {
-                const uint32_t P = kBoundPos[warp];
-                int nb = 0;
-                for (int i = lane; i < cnt0; i += 32) nb += ax.fl.idx[i] < P;
-                nb = __reduce_add_sync(0xffffffffu, nb);
-                uint32_t lo = max(ax.LB[warp], 1u), hi = 65535;
+            // Start states of the segments from 4096 on, one warp per boundary: the k largest keys of
+            // the prefix are among the k largest of [0, 2048) (known) and the master entries of the
+            // segments in between, all of which hold everything at or above this boundary's bound.
+            // Their k-th largest is found by bisection on the key, with the keys in registers.
+            if ((uint32_t) k < n && warp >= kDirect && warp < kBounds && need_state(warp)) {
+                constexpr int kRegs = 14;
+                const int e0 = ax.fl.seg_first[kDirect], e1 = ax.fl.seg_first[warp + 1];
+                uint32_t kr[kRegs + 2];
+                kr[0] = lane < k ? ax.state[kDirect][lane] : 0u;
+                kr[1] = lane + 32 < k ? ax.state[kDirect][lane + 32] : 0u;
+#pragma unroll
+                for (int j = 0; j < kRegs; ++j) {
+                    const int i = e0 + lane + 32 * j;
+                    kr[2 + j] = i < e1 ? (uint32_t) ax.fl.key[i] : 0u;
+                }
+                const int e_rest = e0 + 32 * kRegs;// entries beyond the registers are read from the list
+                uint32_t lo = max(ax.LB[warp], 1u), hi = 0xFC00u;
                 while (lo < hi) {
                     const uint32_t mid = (lo + hi + 1) >> 1;
                     int c = 0;
-                    for (int i = lane; i < nb; i += 32) c += ax.fl.key[i] >= mid;
+#pragma unroll
+                    for (int j = 0; j < kRegs + 2; ++j) c += kr[j] >= mid;
+                    for (int i = e_rest + lane; i < e1; i += 32) c += ax.fl.key[i] >= mid;
                     c = __reduce_add_sync(0xffffffffu, c);
                     if (c >= k) lo = mid;
                     else hi = mid - 1;
                 }
-                int filled = 0;
-                for (int i0 = 0; i0 < nb; i0 += 32) {
-                    const int i = i0 + lane;
-                    const uint32_t key = i < nb ? ax.fl.key[i] : 0u;
-                    const uint32_t hit = __ballot_sync(0xffffffffu, key > lo);
-                    if (key > lo) ax.state[warp + 1][filled + __popc(hit & ((1u << lane) - 1u))] = key;
-                    filled += __popc(hit);
+                uint32_t *st = ax.state[warp + 1];
+                int mine = 0;
+#pragma unroll
+                for (int j = 0; j < kRegs + 2; ++j) mine += kr[j] > lo;
+                for (int i = e_rest + lane; i < e1; i += 32) mine += ax.fl.key[i] > lo;
+                int incl = mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += t;
                 }
-                for (int sl = filled + lane; sl < k; sl += 32) ax.state[warp + 1][sl] = lo;// copies of the k-th largest
+                int at = incl - mine;
+#pragma unroll
+                for (int j = 0; j < kRegs + 2; ++j) {
+                    if (kr[j] > lo) st[at++] = kr[j];
+                }
+                for (int i = e_rest + lane; i < e1; i += 32) {
+                    if (ax.fl.key[i] > lo) st[at++] = ax.fl.key[i];
+                }
+                const int filled = __shfl_sync(0xffffffffu, incl, 31);// < k
+                for (int sl = filled + lane; sl < k; sl += 32) st[sl] = lo;// copies of the k-th largest
                 if (lane == 0) ax.seg_tau[warp + 1] = lo;
             }
             __syncthreads();// the start states have been read off the master list
@@ -782,23 +804,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
 
     // ---- P4: records.  Leader: its segments in parallel, one warp each.  Helper: its half. ----
     if (leader && list_ok && (uint32_t) k < n) {
-        scan_segments((uint32_t) k, ax.seg_tau, true, 2 * kFlatCap);// the whole list area: nothing else uses it now// flagged: above the exact k-th largest at the segment start
+        // flagged: above the exact k-th largest at the segment start (the whole list area is free now)
+        scan_ordered(kScanR0[warp], kScanR0[warp + 1], (uint32_t) k, ax.seg_tau[kScanSeg[warp]], true, 2 * kFlatCap);
         if (!ax.fl.overflow) {
-            // segment i on warp i (the last one on warp 5): the long first segment keeps a scheduler to itself
-            const int sg = warp < kBounds - 1 ? warp : (warp == kBounds ? kBounds - 1 : -1);
-            if (sg >= 0) {
+            if (warp < kBounds) {// segment i on warp i
+                const int sg = warp;
                 const uint32_t s_begin = sg == 0 ? (uint32_t) k : kBoundPos[sg - 1];
-                const uint32_t s_end = min(kBoundPos[sg], n0);
-                if (s_begin < s_end) {
-                    const int cnt = ax.fl.cnt;
-                    int first = 0, last = 0;
-                    for (int i = lane; i < cnt; i += 32) {
-                        const uint32_t p = ax.fl.idx[i];
-                        first += p < s_begin;
-                        last += p < s_end;
-                    }
-                    first = __reduce_add_sync(0xffffffffu, first);
-                    last = __reduce_add_sync(0xffffffffu, last);
+                if (s_begin < n0) {
+                    const int first = ax.fl.seg_first[sg], last = ax.fl.seg_first[sg + 1];
                     MinBuf sb;
                     if (sg == 0) minbuf_init(sb, lane, k, raw);
                     else minbuf_init_keys(sb, lane, k, ax.state[sg]);
@@ -811,7 +824,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         }
     }
     if (!leader && my_n > 0 && !ax.mail.done) {
-        scan_range(0, my_pad, ax.seg_tau[kBounds], true);
+        scan_helper(ax.seg_tau[kBounds], true);
         if (warp == 0) {
             MinBuf hb;
             minbuf_init_keys(hb, lane, k, ax.state[kBounds]);
