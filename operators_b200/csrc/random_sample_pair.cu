@@ -47,10 +47,10 @@ constexpr int kTieGroups = 64;
 // segment holds about k flagged entries and 0.7 k records whatever its length); the helper half is
 // one more segment.  The k largest keys of a prefix that ends at one of the first kDirect boundaries
 // are found directly on the row; for the later boundaries they come from a candidate list whose
-// threshold is a lower bound taken from per-thread maxima.  Those prefixes are covered by whole
-// per-thread load slots: thread t's vector u is elements [8t + 8192u, 8t + 8192u + 8).
+// threshold is a lower bound taken from maxima of groups of threads.  Those prefixes are covered by
+// whole per-thread load slots: thread t's vector u is elements [8t + 8192u, 8t + 8192u + 8).
 constexpr int kBounds = 10;
-constexpr int kDirect = 5;
+constexpr int kDirect = 2;
 __device__ __constant__ uint32_t kBoundPos[kBounds] = {128u, 256u, 512u, 1024u, 2048u, 4096u, 8192u, 16384u, 32768u, 65536u};
 // Scan assignment of the leader half: warp w looks at [kScanR0[w], kScanR0[w + 1]), which lies inside
 // segment kScanSeg[w].  Pieces shorter than 256 are cut into 64-element chunks, the others into
@@ -87,14 +87,15 @@ struct Mail {// written by the other CTA of the pair (the leader also fills its 
 };
 struct Aux {
     FlatList fl;
-    uint16_t gbuf[2 * kFlatCap];// top-k: per-key-group queues of candidate ordinals
+    alignas(16) uint16_t gbuf[2 * kFlatCap];// start states: 256 fp16 values per boundary; then top-k: per-key-group queues of candidate ordinals
+    int state_ovf;                         // a boundary had more than 256 values to choose from
     uint32_t tie_key[kTieGroups];
     uint32_t tie_greater[kTieGroups];
     uint32_t tie_same[kTieGroups];
     int tie_groups;
     uint32_t top_key[kSlots];
     uint32_t top_idx[kSlots];
-    float top_term[kSlots];
+    alignas(16) float top_term[kSlots];
     float blk_terms[kBlk];
     uint32_t C[kLevels][kMaxBlk];// integer block sums per binade level
     uint32_t tie[kMaxBlk];       // bit d: block holds an exact half-way case at level d
@@ -137,27 +138,109 @@ __device__ __forceinline__ __half2 thr2_of_key(uint32_t key) {
     return h2_of(th | (th << 16));
 }
 
-// How many of the n_vec8 * 8 fp16 values at p (shared memory, 16-byte aligned) are >= / > the threshold.
-// One warp; every lane gets the count.
-__device__ __forceinline__ int warp_count_f16(const uint16_t *p, int n_vec8, __half2 thr2, bool strict, int lane) {
-    int c = 0;
-    for (int v = lane; v < n_vec8; v += 32) {
-        uint32_t w[4];
-        lds_raw(p + v * 8, w);
-        c += __popc(flag8(w, thr2, strict));
+// One warp holds n_vec8 * 8 fp16 values (shared memory at p, 16-byte aligned) in registers, NW packed
+// words per lane (NW * 64 >= n_vec8 * 8; missing ones are -inf), and bisects on them without touching
+// memory again.
+template<int NW>
+struct WarpVals {
+    uint32_t w[NW];
+    __device__ __forceinline__ void load(const uint16_t *p, int n_vec8, int lane) {
+#pragma unroll
+        for (int j = 0; j < NW / 4; ++j) {
+            const int v = lane + 32 * j;
+            uint4 q = make_uint4(0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u);
+            if (v < n_vec8) q = *reinterpret_cast<const uint4 *>(p + v * 8);
+            w[4 * j] = q.x, w[4 * j + 1] = q.y, w[4 * j + 2] = q.z, w[4 * j + 3] = q.w;
+        }
     }
-    return __reduce_add_sync(0xffffffffu, c);
-}
-// Key of the k-th largest of those values (with multiplicity), by bisection on the key; 0x0400 (the key
-// of -inf) when fewer than k values lie above -inf.  One warp.
-__device__ __forceinline__ uint32_t warp_kth_largest_f16(const uint16_t *p, int n_vec8, int k, int lane) {
-    uint32_t lo = 0x0400u, hi = 0xFC00u;// keys of -inf and +inf
-    while (lo < hi) {
-        const uint32_t mid = (lo + hi + 1) >> 1;
-        if (warp_count_f16(p, n_vec8, thr2_of_key(mid), false, lane) >= k) lo = mid;
-        else hi = mid - 1;
+    // this lane's count of values >= thr (or > thr)
+    __device__ __forceinline__ int count(__half2 thr2, bool strict) const {
+        int c = 0;
+#pragma unroll
+        for (int g = 0; g < NW; g += 16) {
+            uint32_t acc = 0;// word r of the group answers in bits r and 16 + r
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                if (g + r < NW) {
+                    const uint32_t m = strict ? __hgt2_mask(h2_of(w[g + r]), thr2) : __hge2_mask(h2_of(w[g + r]), thr2);
+                    acc |= m & (0x00010001u << r);
+                }
+            }
+            c += __popc(acc);
+        }
+        return c;
     }
-    return lo;
+    // this lane's counts of values >= each of three thresholds, in the low and high half of x and in y
+    __device__ __forceinline__ void count3(__half2 t1, __half2 t2, __half2 t3, uint32_t &x, uint32_t &y) const {
+        uint32_t c1 = 0, c2 = 0, c3 = 0;
+#pragma unroll
+        for (int g = 0; g < NW; g += 16) {
+            uint32_t a1 = 0, a2 = 0, a3 = 0;
+#pragma unroll
+            for (int r = 0; r < 16; ++r) {
+                if (g + r < NW) {
+                    const uint32_t sel = 0x00010001u << r;
+                    a1 |= __hge2_mask(h2_of(w[g + r]), t1) & sel;
+                    a2 |= __hge2_mask(h2_of(w[g + r]), t2) & sel;
+                    a3 |= __hge2_mask(h2_of(w[g + r]), t3) & sel;
+                }
+            }
+            c1 += __popc(a1), c2 += __popc(a2), c3 += __popc(a3);
+        }
+        x = c1 | (c2 << 16);
+        y = c3;
+    }
+    // Key of the k-th largest value (with multiplicity); 0x0400 (the key of -inf) when fewer than k
+    // values lie above -inf.  Four-way search: three thresholds per step, eight steps.
+    __device__ __forceinline__ uint32_t kth_largest(int k) const {
+        uint32_t lo = 0x0400u, hi = 0xFC00u;// keys of -inf and +inf
+        while (lo < hi) {
+            const uint32_t m2 = (lo + hi + 1) >> 1;// lo < m2 <= hi
+            const uint32_t m1 = (lo + m2) >> 1;    // lo <= m1 < m2
+            const uint32_t m3 = (m2 + hi + 1) >> 1;// m2 <= m3 <= hi
+            uint32_t x, y;
+            count3(thr2_of_key(m1), thr2_of_key(m2), thr2_of_key(m3), x, y);
+            x = __reduce_add_sync(0xffffffffu, x);// at most 2048 values: the halves do not carry
+            y = __reduce_add_sync(0xffffffffu, y);
+            const int c1 = (int) (x & 0xFFFFu), c2 = (int) (x >> 16), c3 = (int) y;
+            if (c3 >= k) lo = m3;
+            else if (c2 >= k) lo = m2, hi = m3 - 1;
+            else if (c1 >= k) lo = m1, hi = m2 - 1;
+            else hi = m1 - 1;// below lo when m1 == lo: ends the search with lo unchanged
+        }
+        return lo;
+    }
+    // The k largest keys into st[0, k): those above tau (fewer than k), then copies of tau.
+    __device__ __forceinline__ void k_largest(uint32_t tau, int k, uint32_t *st, int lane) const {
+        const __half2 t2 = thr2_of_key(tau);
+        const int mine = count(t2, true);
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        int at = incl - mine;
+#pragma unroll
+        for (int r = 0; r < NW; ++r) {
+            const uint32_t m = __hgt2_mask(h2_of(w[r]), t2);
+            if (m & 0xFFFFu) st[at++] = key_of((uint16_t) (w[r] & 0xFFFFu));
+            if (m >> 16) st[at++] = key_of((uint16_t) (w[r] >> 16));
+        }
+        const int filled = __shfl_sync(0xffffffffu, incl, 31);
+        for (int sl = filled + lane; sl < k; sl += 32) st[sl] = tau;
+    }
+};
+
+// Key of the k-th largest of up to 256 fp16 values (n_vec8 vectors of 8 at p); with st, also the k
+// largest keys into st[0, k).  One warp; one copy of the code for all the warps that call it.
+__device__ __noinline__ uint32_t kth_largest_256(const uint16_t *p, int n_vec8, int k, uint32_t *st) {
+    const int lane = threadIdx.x & 31;
+    WarpVals<4> v;
+    v.load(p, n_vec8, lane);
+    const uint32_t tau = v.kth_largest(k);
+    if (st != nullptr) v.k_largest(tau, k, st, lane);
+    return tau;
 }
 
 // Running multiset of the k largest keys seen so far, 2 slots per lane.  Each
@@ -194,7 +277,7 @@ __device__ __forceinline__ void minbuf_replace(MinBuf &m, int lane, uint32_t key
 // One warp walks a 256-element block (local or the peer's shared memory) in
 // index order and feeds every element above the running k-th largest value;
 // a record is overwritten with that value.  Slow path (list overflow only).
-__device__ __forceinline__ void records_direct_block(uint16_t *blk, uint32_t first_in_blk, int lane, MinBuf &m) {
+__device__ __noinline__ void records_direct_block(uint16_t *blk, uint32_t first_in_blk, int lane, MinBuf &m) {
     uint32_t w[4], keys[8];
     lds_raw(blk + lane * 8, w);
 #pragma unroll
@@ -234,7 +317,7 @@ __device__ __forceinline__ void records_direct_block(uint16_t *blk, uint32_t fir
 // `dst` (positions are taken relative to `pos_offset`).  Sixteen keys at a time
 // are read into registers of every lane, so the only serial dependency between
 // entries is the running value itself (one warp-wide minimum per record).
-__device__ __forceinline__ void replay_list(const FlatList &fl, int first, int count, uint16_t *dst,
+__device__ __noinline__ void replay_list(const FlatList &fl, int first, int count, uint16_t *dst,
                                             uint32_t pos_offset, int lane, MinBuf &m) {
     constexpr int kBatch = 16;
     for (int c0 = 0; c0 < count; c0 += kBatch) {
@@ -254,9 +337,12 @@ __device__ __forceinline__ void replay_list(const FlatList &fl, int first, int c
     }
 }
 
+// exp in double precision is some hundred instructions: one copy, called.
+__device__ __noinline__ float term_exact(float v, float M, float T) { return term_of(v, M, T); }
+
 // Exact contribution of one term to the block sums of all levels.
-__device__ __forceinline__ void exact_contrib(Aux &ax, uint32_t blk, float v, float M, float T, int e0) {
-    const uint32_t tb = __float_as_uint(term_of(v, M, T));
+__device__ __noinline__ void exact_contrib(Aux &ax, uint32_t blk, float v, float M, float T, int e0) {
+    const uint32_t tb = __float_as_uint(term_exact(v, M, T));
     int e_t = (int) ((tb >> 23) & 0xFFu);
     uint32_t man = tb & 0x7FFFFFu;
     if (e_t == 0) e_t = 1;
@@ -325,87 +411,81 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
     // ---- P1: this CTA's half of the row -> shared memory; per-thread maxima --------------
     const bool in_aligned = (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
     __half2 tmax2 = h2_of(0xFC00FC00u), m0_2 = tmax2, mA_2 = tmax2, mB_2 = tmax2;// running maximum; after 1, 2 and 4 vectors
+    auto max4 = [](const uint4 q) { return __hmax2(__hmax2(h2_of(q.x), h2_of(q.y)), __hmax2(h2_of(q.z), h2_of(q.w))); };
     constexpr int kInFlight = 8;
-    for (uint32_t base0 = tid * 8; base0 < my_pad; base0 += kThreads * 8 * kInFlight) {
+    for (uint32_t base0 = tid * 8; base0 < my_pad; base0 += kThreads * 8 * kInFlight) {// whole aligned vectors
         uint4 ld[kInFlight];
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
             const uint32_t base = base0 + u * kThreads * 8;
+            ld[u] = make_uint4(0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u);
             if (in_aligned && base + 8 <= my_n) ld[u] = ld_stream(logits + base);
         }
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
             const uint32_t base = base0 + u * kThreads * 8;
-            if (base >= my_pad) break;
-            if (!(in_aligned && base + 8 <= my_n)) {// ragged end or unaligned row: element-wise, padded with -inf
-                uint16_t h[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) h[e] = base + e < my_n ? logits[base + e] : kPad;
-                ld[u].x = h[0] | ((uint32_t) h[1] << 16);
-                ld[u].y = h[2] | ((uint32_t) h[3] << 16);
-                ld[u].z = h[4] | ((uint32_t) h[5] << 16);
-                ld[u].w = h[6] | ((uint32_t) h[7] << 16);
+            if (base < my_pad) {
+                *reinterpret_cast<uint4 *>(raw + base) = ld[u];
+                tmax2 = __hmax2(tmax2, max4(ld[u]));
             }
-            *reinterpret_cast<uint4 *>(raw + base) = ld[u];
-            tmax2 = __hmax2(tmax2, __hmax2(__hmax2(h2_of(ld[u].x), h2_of(ld[u].y)), __hmax2(h2_of(ld[u].z), h2_of(ld[u].w))));
             if (u == 0) m0_2 = tmax2;
-            if (u <= 1) mA_2 = tmax2;
-            if (u <= 3) mB_2 = tmax2;
+            if (u == 1) mA_2 = tmax2;
+            if (u == 3) mB_2 = tmax2;
         }
     }
-    // Per-thread maxima (fp16; -inf = nothing but padding), entered into one array per boundary from
-    // 4096 on: x_b[t] is the maximum of the part of thread t's data that lies below boundary b.  The
-    // k-th largest entry of x_b is a lower bound of the k-th largest key of that prefix, because k
-    // different elements of the prefix are at least that large.  One warp per boundary finds it; five
-    // more warps find the exact k largest keys of the short prefixes (128 .. 2048) on the row itself.
-    auto max_of = [](const __half2 m2) -> uint16_t { return __half_as_ushort(__hmax(__low2half(m2), __high2half(m2))); };
+    if (!in_aligned || (my_n & 7u)) {// ragged end or unaligned row: those vectors again, element-wise, padded with -inf
+#pragma unroll 1
+        for (uint32_t base = tid * 8; base < my_pad; base += kThreads * 8) {
+            if (in_aligned && base + 8 <= my_n) continue;
+            uint16_t h[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) h[e] = base + e < my_n ? logits[base + e] : kPad;
+            const uint4 q = make_uint4(h[0] | ((uint32_t) h[1] << 16), h[2] | ((uint32_t) h[3] << 16),
+                                       h[4] | ((uint32_t) h[5] << 16), h[6] | ((uint32_t) h[7] << 16));
+            *reinterpret_cast<uint4 *>(raw + base) = q;
+            const __half2 vm = max4(q);
+            const uint32_t u = base / (kThreads * 8);
+            tmax2 = __hmax2(tmax2, vm);
+            if (u == 0) m0_2 = __hmax2(m0_2, vm);
+            if (u <= 1) mA_2 = __hmax2(mA_2, vm);
+            if (u <= 3) mB_2 = __hmax2(mB_2, vm);
+        }
+    }
+    // Maxima of disjoint groups of elements (fp16; -inf = nothing but padding), at most 256 per
+    // boundary from 512 on: x_b[g] is the maximum of the part of group g that lies below boundary b
+    // (a group is one thread's slots, or two or four neighbouring threads').  The k-th largest entry
+    // of x_b is a lower bound of the k-th largest key of that prefix, because k different elements
+    // of the prefix are at least that large.  One warp per boundary finds it; two more warps find
+    // the exact k largest keys of the prefixes 128 and 256 on the row itself.
     // state b + 1 (the k largest keys of the prefix that ends at boundary b) is wanted when a segment starts there
     auto need_state = [&](int b) { return kBoundPos[b] < n0 || (kBoundPos[b] == n0 && n > n0); };
     {
-        uint16_t *xs = reinterpret_cast<uint16_t *>(ax.unc);// [kBounds - kDirect][kThreads], free until the denominator
-        const uint16_t x0 = max_of(m0_2);
-        xs[0 * kThreads + tid] = tid < 512 ? x0 : kPad;
-        xs[1 * kThreads + tid] = x0;
-        xs[2 * kThreads + tid] = max_of(mA_2);
-        xs[3 * kThreads + tid] = max_of(mB_2);
-        xs[4 * kThreads + tid] = max_of(tmax2);
+        uint16_t *xs = reinterpret_cast<uint16_t *>(ax.unc);// [kBounds - kDirect][256], free until the denominator
+        auto one = [](const __half2 m2) { return __hmax(__low2half(m2), __high2half(m2)); };
+        const __half x0 = one(m0_2);
+        __half2 p01 = __halves2half2(x0, one(mA_2)), p23 = __halves2half2(one(mB_2), one(tmax2));
+        const __half2 q01 = __hmax2(p01, __shfl_xor_sync(0xffffffffu, p01, 1));
+        p01 = __hmax2(q01, __shfl_xor_sync(0xffffffffu, q01, 2));// maxima over four neighbouring threads
+        p23 = __hmax2(p23, __shfl_xor_sync(0xffffffffu, p23, 1));
+        p23 = __hmax2(p23, __shfl_xor_sync(0xffffffffu, p23, 2));
+        if (tid < 64) xs[0 * 256 + tid] = __half_as_ushort(x0); // below 512
+        if (tid < 128) xs[1 * 256 + tid] = __half_as_ushort(x0);// below 1024
+        if (tid < 256) xs[2 * 256 + tid] = __half_as_ushort(x0);// below 2048
+        if (tid < 512 && !(tid & 1)) xs[3 * 256 + (tid >> 1)] = __half_as_ushort(__low2half(q01));// below 4096
+        if (!(tid & 3)) {
+            xs[4 * 256 + (tid >> 2)] = __half_as_ushort(__low2half(p01)); // below 8192
+            xs[5 * 256 + (tid >> 2)] = __half_as_ushort(__high2half(p01));// below 16384
+            xs[6 * 256 + (tid >> 2)] = __half_as_ushort(__low2half(p23)); // below 32768
+            xs[7 * 256 + (tid >> 2)] = __half_as_ushort(__high2half(p23));// all
+        }
         __syncthreads();
         if (warp < kBounds - kDirect && (leader || warp == kBounds - kDirect - 1)) {
-            const uint32_t kth = warp_kth_largest_f16(xs + warp * kThreads, warp == 0 ? 64 : 128, k, lane);
-            if (lane == 0) ax.LB[kDirect + warp] = kth <= 0x0400u ? 1u : kth;// fewer than k threads hold data: everything
+            const uint32_t kth = kth_largest_256(xs + warp * 256, warp == 0 ? 8 : warp == 1 ? 16 : 32, k, nullptr);
+            if (lane == 0) ax.LB[kDirect + warp] = kth <= 0x0400u ? 1u : kth;// fewer than k groups hold data: everything
         } else if (leader && warp >= kBounds - kDirect && warp < kBounds && (uint32_t) k < n &&
                    need_state(warp - (kBounds - kDirect))) {
             const int b = warp - (kBounds - kDirect);
-            const int nv = (int) (kBoundPos[b] / 8u);
-            const uint32_t tau = warp_kth_largest_f16(raw, nv, k, lane);
-            const __half2 t2 = thr2_of_key(tau);
-            uint32_t *st = ax.state[b + 1];
-            int filled = 0;
-            for (int v0 = 0; v0 < nv; v0 += 32) {
-                const int v = v0 + lane;
-                uint32_t m = 0;
-                if (v < nv) {
-                    uint32_t w[4];
-                    lds_raw(raw + v * 8, w);
-                    m = flag8(w, t2, true);
-                }
-                if (__ballot_sync(0xffffffffu, m != 0) == 0) continue;
-                const int cnt = __popc(m);
-                int incl = cnt;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int t = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += t;
-                }
-                int at = filled + incl - cnt;
-                while (m) {// fewer than k keys lie above the k-th largest
-                    const int e = __ffs(m) - 1;
-                    m &= m - 1;
-                    st[at++] = key_of(raw[v * 8 + e]);
-                }
-                filled += __shfl_sync(0xffffffffu, incl, 31);
-            }
-            for (int sl = filled + lane; sl < k; sl += 32) st[sl] = tau;// copies of the k-th largest
+            const uint32_t tau = kth_largest_256(raw, (int) (kBoundPos[b] / 8u), k, ax.state[b + 1]);
             if (lane == 0) ax.seg_tau[b + 1] = tau;
         }
         __syncthreads();
@@ -413,6 +493,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
     const uint32_t L_mine = ax.LB[kBounds - 1];
     if (tid == 0) {
         peer_ax->mail.L_peer = L_mine;
+        ax.state_ovf = 0;
         ax.fl.peer_cnt = 0;// the helper fills these in after the barrier
         ax.fl.peer_overflow = 0;
     }
@@ -539,7 +620,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
     };
 
     if (leader) {
-        // master list.  Segments below 2048: the candidates proper (key >= L); their start states are known.
+        // master list.  Segments below 256: the candidates proper (key >= L); their start states are known.
         // Later segments: everything >= the bound of the prefix the segment closes, for the start states.
         const int sg = kScanSeg[warp];
         scan_ordered(kScanR0[warp], kScanR0[warp + 1], 0u, sg < kDirect ? L : ax.LB[sg], false, kFlatCap);
@@ -557,97 +638,75 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
     if (leader) {
         const int cnt0 = ax.fl.cnt, cnt1 = ax.fl.peer_cnt;
         list_ok = !ax.fl.overflow && !ax.fl.peer_overflow;
+        if (list_ok && (uint32_t) k < n && warp >= kDirect && warp < kBounds && need_state(warp)) {
+            // Start states of the segments from 512 on, one warp per boundary: the k largest keys of
+            // the prefix are among the k largest of [0, 256) (known) and those master entries of the
+            // segments in between that reach this boundary's bound (about k of them).  They are put
+            // side by side as fp16 values and the selection that found the bounds runs on them.
+            uint16_t *sc = ax.gbuf + (warp - kDirect) * 256;
+            const int e0 = ax.fl.seg_first[kDirect], e1 = ax.fl.seg_first[warp + 1];
+            const uint32_t lb = max(ax.LB[warp], 1u);
+            for (int i = lane; i < 256; i += 32) sc[i] = kPad;
+            __syncwarp();
+            if (lane < k) sc[lane] = half_of_key(ax.state[kDirect][lane]);
+            if (lane + 32 < k) sc[lane + 32] = half_of_key(ax.state[kDirect][lane + 32]);
+            int fill = k;
+#pragma unroll 1
+            for (int i0 = e0; i0 < e1; i0 += 32) {
+                const int i = i0 + lane;
+                const uint32_t key = i < e1 ? (uint32_t) ax.fl.key[i] : 0u;
+                const uint32_t hit = __ballot_sync(0xffffffffu, key >= lb);
+                const int at = fill + __popc(hit & ((1u << lane) - 1u));
+                if (key >= lb && at < 256) sc[at] = half_of_key(key);
+                fill += __popc(hit);
+            }
+            __syncwarp();
+            if (fill > 256) {
+                if (lane == 0) ax.state_ovf = 1;
+            } else {
+                const uint32_t tau = kth_largest_256(sc, 32, k, ax.state[warp + 1]);
+                if (lane == 0) ax.seg_tau[warp + 1] = tau;
+            }
+        }
+        __syncthreads();// the start states have been read off the master list
+        if (ax.state_ovf) list_ok = false;
         if (list_ok) {
-            // Start states of the segments from 4096 on, one warp per boundary: the k largest keys of
-            // the prefix are among the k largest of [0, 2048) (known) and the master entries of the
-            // segments in between, all of which hold everything at or above this boundary's bound.
-            // Their k-th largest is found by bisection on the key, with the keys in registers.
-            if ((uint32_t) k < n && warp >= kDirect && warp < kBounds && need_state(warp)) {
-                constexpr int kRegs = 14;
-                const int e0 = ax.fl.seg_first[kDirect], e1 = ax.fl.seg_first[warp + 1];
-                uint32_t kr[kRegs + 2];
-                kr[0] = lane < k ? ax.state[kDirect][lane] : 0u;
-                kr[1] = lane + 32 < k ? ax.state[kDirect][lane + 32] : 0u;
-#pragma unroll
-                for (int j = 0; j < kRegs; ++j) {
-                    const int i = e0 + lane + 32 * j;
-                    kr[2 + j] = i < e1 ? (uint32_t) ax.fl.key[i] : 0u;
-                }
-                const int e_rest = e0 + 32 * kRegs;// entries beyond the registers are read from the list
-                uint32_t lo = max(ax.LB[warp], 1u), hi = 0xFC00u;
-                while (lo < hi) {
-                    const uint32_t mid = (lo + hi + 1) >> 1;
-                    int c = 0;
-#pragma unroll
-                    for (int j = 0; j < kRegs + 2; ++j) c += kr[j] >= mid;
-                    for (int i = e_rest + lane; i < e1; i += 32) c += ax.fl.key[i] >= mid;
-                    c = __reduce_add_sync(0xffffffffu, c);
-                    if (c >= k) lo = mid;
-                    else hi = mid - 1;
-                }
-                uint32_t *st = ax.state[warp + 1];
-                int mine = 0;
-#pragma unroll
-                for (int j = 0; j < kRegs + 2; ++j) mine += kr[j] > lo;
-                for (int i = e_rest + lane; i < e1; i += 32) mine += ax.fl.key[i] > lo;
-                int incl = mine;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int t = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += t;
-                }
-                int at = incl - mine;
-#pragma unroll
-                for (int j = 0; j < kRegs + 2; ++j) {
-                    if (kr[j] > lo) st[at++] = kr[j];
-                }
-                for (int i = e_rest + lane; i < e1; i += 32) {
-                    if (ax.fl.key[i] > lo) st[at++] = ax.fl.key[i];
-                }
-                const int filled = __shfl_sync(0xffffffffu, incl, 31);// < k
-                for (int sl = filled + lane; sl < k; sl += 32) st[sl] = lo;// copies of the k-th largest
-                if (lane == 0) ax.seg_tau[warp + 1] = lo;
+            // keep only the candidates proper (key >= L): the ranking below is quadratic in the list length.
+            // One entry per thread, read before the barrier and written to its new place after it; the
+            // helper's entries move up behind the leader's own: one list in index order.
+            uint32_t my_idx = 0, my_key = 0, mv_idx = 0, mv_key = 0;
+            bool keep = false;
+            if (tid < cnt0) {
+                my_key = ax.fl.key[tid];
+                my_idx = ax.fl.idx[tid];
+                keep = my_key >= L;
             }
-            __syncthreads();// the start states have been read off the master list
-            // keep only the candidates proper (key >= L): the ranking below is quadratic in the list length
-            if (warp == 0) {
-                int out = 0;
-                for (int i0 = 0; i0 < cnt0; i0 += 32) {// forward, in place: writes never pass the reads
-                    const int i = i0 + lane;
-                    const uint32_t key = i < cnt0 ? ax.fl.key[i] : 0u;
-                    const uint32_t idx = i < cnt0 ? ax.fl.idx[i] : 0u;
-                    const uint32_t hit = __ballot_sync(0xffffffffu, key >= L);
-                    __syncwarp();
-                    if (key >= L) {
-                        const int at = out + __popc(hit & ((1u << lane) - 1u));
-                        ax.fl.key[at] = (uint16_t) key;
-                        ax.fl.idx[at] = idx;
-                    }
-                    out += __popc(hit);
-                    __syncwarp();
-                }
-                if (lane == 0) ax.fl.cnt = out;
-            }
-            __syncthreads();
-            const int cnt0c = ax.fl.cnt;
-            const int m = cnt0c + cnt1;
-            // move the helper's entries up behind the leader's own: one list in index order
-            uint32_t mv_idx = 0;
-            uint16_t mv_key = 0;
             if (tid < cnt1) {
                 mv_idx = ax.fl.idx[kFlatCap + tid];
                 mv_key = ax.fl.key[kFlatCap + tid];
             }
+            const uint32_t hit = __ballot_sync(0xffffffffu, keep);
+            if (lane == 0) ax.fl.wcnt[warp] = __popc(hit);
             if (tid == 0) ax.tie_groups = 0;
-            __syncthreads();
-            if (tid < cnt1) {
-                ax.fl.idx[cnt0c + tid] = mv_idx;
-                ax.fl.key[cnt0c + tid] = mv_key;
-            }
             if (tid < kSlots) {
                 ax.top_key[tid] = 0;
                 ax.top_idx[tid] = 0;
             }
+            __syncthreads();
+            const int c_l = ax.fl.wcnt[lane];
+            const int off = __reduce_add_sync(0xffffffffu, lane < warp ? c_l : 0);
+            const int cnt0c = __reduce_add_sync(0xffffffffu, c_l);
+            const int m = cnt0c + cnt1;
+            if (keep) {
+                const int at = off + __popc(hit & ((1u << lane) - 1u));
+                ax.fl.key[at] = (uint16_t) my_key;
+                ax.fl.idx[at] = my_idx;
+            }
+            if (tid < cnt1) {
+                ax.fl.idx[cnt0c + tid] = mv_idx;
+                ax.fl.key[cnt0c + tid] = (uint16_t) mv_key;
+            }
+            if (tid == 0) ax.fl.cnt = cnt0c;
             __syncthreads();
             SUBSTAMP();// s0: lists merged
             // Rank every candidate: `greater` keys above it, `same` keys equal to it.
@@ -686,30 +745,38 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 const uint32_t gkey = ax.tie_key[g], cap = ax.tie_same[g];
                 uint16_t *q = ax.gbuf + ax.tie_greater[g];// this group's slots: [greater, greater + same)
                 uint32_t G = 0, sz = 0, head = 0;
-                for (int j = 0; j < m; ++j) {
-                    const uint32_t kj = ax.fl.key[j];
-                    if (kj > gkey) {
-                        ++G;
-                        if (sz > 0) {
-                            if (G + sz > (uint32_t) k) {// nothing smaller left to evict: the front leaves
-                                head = head + 1 == cap ? 0 : head + 1;
-                                --sz;
-                            } else if (sz > 1) {// front moves to the back
-                                if (sz < cap) {
-                                    uint32_t tail = head + sz;
-                                    if (tail >= cap) tail -= cap;
-                                    if (lane == 0) q[tail] = q[head];
-                                    __syncwarp();
+                // 32 candidates at a time; only those at or above the group's key are events
+                for (int j0 = 0; j0 < m; j0 += 32) {
+                    const uint32_t kj = j0 + lane < m ? (uint32_t) ax.fl.key[j0 + lane] : 0u;
+                    const uint32_t gt = __ballot_sync(0xffffffffu, kj > gkey);
+                    const uint32_t eq = __ballot_sync(0xffffffffu, kj == gkey);
+                    if (eq == 0 && sz == 0) {// nothing queued, nothing joins: the larger keys only count
+                        G += __popc(gt);
+                        continue;
+                    }
+                    uint32_t ev = gt | eq;
+                    while (ev) {
+                        const int bpos = __ffs(ev) - 1;
+                        ev &= ev - 1;
+                        if ((gt >> bpos) & 1u) {
+                            ++G;
+                            if (sz > 0) {
+                                if (G + sz > (uint32_t) k) {// nothing smaller left to evict: the front leaves
+                                    head = head + 1 == cap ? 0 : head + 1;
+                                    --sz;
+                                } else if (sz > 1) {// front moves to the back
+                                    if (sz < cap) {
+                                        uint32_t tail = head + sz;
+                                        if (tail >= cap) tail -= cap;
+                                        if (lane == 0) q[tail] = q[head];
+                                    }
+                                    head = head + 1 == cap ? 0 : head + 1;
                                 }
-                                head = head + 1 == cap ? 0 : head + 1;
                             }
-                        }
-                    } else if (kj == gkey) {
-                        if (G + sz < (uint32_t) k) {
+                        } else if (G + sz < (uint32_t) k) {
                             uint32_t tail = head + sz;
                             if (tail >= cap) tail -= cap;
-                            if (lane == 0) q[tail] = (uint16_t) j;
-                            __syncwarp();
+                            if (lane == 0) q[tail] = (uint16_t) (j0 + bpos);
                             ++sz;
                         }
                     }
@@ -760,35 +827,46 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         }
         __syncthreads();
         SUBSTAMP();// s2: top-k placed
-        if (warp == 0) {
-            const float Mw = val_of(ax.top_key[0]);
-            for (int i = lane; i < k; i += 32) ax.top_term[i] = term_of(val_of(ax.top_key[i]), Mw, T);
-            __syncwarp();
-            if (lane == 0) {
-                float sk = 0.f;
-                for (int i = 0; i < k; ++i) sk = __fadd_rn(sk, ax.top_term[i]);
-                ax.mail.s_base = sk;
-                ax.mail.pos_base = (uint32_t) k;
-                ax.mail.mkey = ax.top_key[0];
-                ax.mail.done = (uint32_t) k >= n;
+        if (warp < 2) {// exact terms of the top-k, one per thread
+            const int i = tid;
+            if (i < k) ax.top_term[i] = term_exact(val_of(ax.top_key[i]), val_of(ax.top_key[0]), T);
+        } else if (warp == 2 && (uint32_t) k < n && list_ok) {// meanwhile: the k-th largest of the first k elements
+            MinBuf fb;
+            minbuf_init(fb, lane, k, raw);
+            if (lane == 0) ax.seg_tau[0] = fb.tau();
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float sk = 0.f;// the reference's order: one addition after the other
+#pragma unroll 1
+            for (int i0 = 0; i0 < k; i0 += 4) {
+                const float4 q = *reinterpret_cast<const float4 *>(&ax.top_term[i0]);
+                sk = __fadd_rn(sk, q.x);
+                if (i0 + 1 < k) sk = __fadd_rn(sk, q.y);
+                if (i0 + 2 < k) sk = __fadd_rn(sk, q.z);
+                if (i0 + 3 < k) sk = __fadd_rn(sk, q.w);
             }
+            ax.mail.s_base = sk;
+            ax.mail.pos_base = (uint32_t) k;
+            ax.mail.mkey = ax.top_key[0];
+            ax.mail.done = (uint32_t) k >= n;
         }
         __syncthreads();
         stamp();// 2: top-k in order, top-k terms summed
 
         if ((uint32_t) k < n) {
-            if (warp == 0) {
-                minbuf_init(mb, lane, k, raw);
-                if (lane == 0) ax.seg_tau[0] = mb.tau();
-                if (!list_ok) {
+            if (!list_ok) {
+                if (warp == 0) {
                     // slow path (candidate lists overflowed): one warp walks the leader half in order
+                    minbuf_init(mb, lane, k, raw);
+                    if (lane == 0) ax.seg_tau[0] = mb.tau();
                     for (uint32_t b = 0; b < nblk0; ++b) records_direct_block(raw + b * kBlk, b == 0 ? (uint32_t) k : 0u, lane, mb);
                     ax.state[kBounds][lane] = mb.v0 >> 6;
                     ax.state[kBounds][lane + 32] = mb.v1 >> 6;
                     if (lane == 0) ax.seg_tau[kBounds] = mb.tau();
                 }
+                __syncthreads();
             }
-            __syncthreads();
             if (n > n0 && tid < kSlots) peer_ax->state[kBounds][tid] = ax.state[kBounds][tid];
         }
         if (tid == 0) {// hand the helper what it needs
@@ -835,6 +913,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             }
         }
     }
+    __syncthreads();// idle warps wait here, at the CTA barrier, for the replaying ones
     cluster.sync();// CS4
     stamp();       // 4: whole row patched
     M = val_of(ax.mail.mkey);
@@ -986,7 +1065,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                     for (int e = 0; e < 8; ++e) {
                         const uint32_t j = gbase + lane * 8 + e;
                         const uint16_t h = half_at(w, e);
-                        ax.blk_terms[lane * 8 + e] = (h == kPad || j < pos) ? 0.f : term_of(f16_to_f32(h), M, T);
+                        ax.blk_terms[lane * 8 + e] = (h == kPad || j < pos) ? 0.f : term_exact(f16_to_f32(h), M, T);
                     }
                     __syncwarp();
                     if (lane == 0) {
@@ -1023,6 +1102,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             }
         }
         SUBSTAMP();// s6: walk done
+        __syncthreads();
         cluster.sync();// CS7
     }
     stamp();// 5: denominator
