@@ -102,7 +102,6 @@ struct Aux {
     uint32_t LB[kBounds];        // lower bound of the k-th largest key of the prefix that ends at boundary b
     uint32_t seg_tau[kBounds + 1];       // exact k-th largest key at the start of segment i
     uint32_t state[kBounds + 1][kSlots]; // the k largest keys at the start of segment i (slot order irrelevant)
-    uint8_t relq[kWarps][kBlk];  // per warp: in-block indices of the elements that can contribute
     alignas(16) uint32_t unc[kUncCap];// positions (local) to re-evaluate exactly; before that, the per-thread maxima (read as 16-byte vectors)
     int unc_cnt;
     Mail mail;
@@ -946,53 +945,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             const uint32_t span = (cntb + kWarps - 1) / kWarps;
             const uint32_t b0 = lb_first + warp * span, b1 = min(my_nblk, b0 + span);
             for (uint32_t b = b0; b < b1; ++b) {
-                // 1. which of the block's elements can contribute at all (z >= 1/4)?  Their
-                //    in-block indices are packed into this warp's queue, so that step 2 runs
-                //    with every lane busy although typically well under half the elements qualify.
+                // Every element is evaluated (no compaction: flagging, scanning and queueing the ones that
+                // can contribute costs as many issue slots as evaluating the others too).  z below 1 gives
+                // floor 0 and adds nothing; padding and far-away values give z = 0.
                 uint32_t w[4];
                 lds_raw(raw + b * kBlk + lane * 8, w);
+                const uint32_t gpos0 = my_base + b * kBlk + lane * 8;
                 const bool partial = my_base + b * kBlk < pos;// only the round's first block
-                uint32_t mask = 0;
+                uint32_t F = 0, Bp = 0, um = 0;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const float v = f16_to_f32(half_at(w, e));
-                    const bool in = fmaf(__fsub_rn(v, M), A, shift) >= -2.0f;// false for padding (-inf)
-                    const bool skip = partial && my_base + b * kBlk + lane * 8 + e < pos;
-                    mask |= ((in && !skip) ? 1u : 0u) << e;
-                }
-                const int cnt = __popc(mask);
-                int pre = cnt;
-#pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const int t = __shfl_up_sync(0xffffffffu, pre, o);
-                    if (lane >= o) pre += t;
-                }
-                const int total = __shfl_sync(0xffffffffu, pre, 31);
-                if (total == 0) continue;
-                {
-                    int at = pre - cnt;
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        if (mask & (1u << e)) ax.relq[warp][at++] = (uint8_t) (lane * 8 + e);
-                    }
-                }
-                __syncwarp();
-                // 2. dense evaluation
-                uint32_t F = 0, Bp = 0;
-                for (int i = lane; i < total; i += 32) {
-                    const uint32_t eidx = ax.relq[warp][i];
-                    const float v = f16_to_f32(raw[b * kBlk + eidx]);
-                    const float z = fast_exp2(fmaf(__fsub_rn(v, M), A, shift));
+                    float arg = fmaf(__fsub_rn(v, M), A, shift);
+                    if (partial && gpos0 + e < pos) arg = -1000.f;// already in the running sum
+                    const float z = fast_exp2(arg);
                     const float fz = floorf(z);
-                    if (fabsf(z - fz - 0.5f) >= 0.5f - z * band || z >= 1048576.0f) {
-                        const int slot = atomicAdd(&ax.unc_cnt, 1);
-                        if (slot < kUncCap) ax.unc[slot] = b * kBlk + eidx;
-                        else exact_contrib(ax, b + goff, v, M, T, e0);// list full: settle it here
-                    } else {
+                    // sure when z keeps z * band away from the integers on both sides (never for z >= 0.5 / band)
+                    if (fabsf(z - fz - 0.5f) <= fmaf(-z, band, 0.5f)) {
                         const uint32_t f = (uint32_t) fz;
                         F += f;
                         Bp += ((f & 15u) * 0x00204081u) & 0x01010101u;// bit i of f -> byte i
+                    } else {
+                        um |= 1u << e;
                     }
+                }
+                while (um) {// rare: near an integer, or large
+                    const int e = __ffs(um) - 1;
+                    um &= um - 1;
+                    const int slot = atomicAdd(&ax.unc_cnt, 1);
+                    if (slot < kUncCap) ax.unc[slot] = b * kBlk + lane * 8 + e;
+                    else exact_contrib(ax, b + goff, f16_to_f32(raw[b * kBlk + lane * 8 + e]), M, T, e0);// list full: settle it here
                 }
                 __syncwarp();
                 F = __reduce_add_sync(0xffffffffu, F);
