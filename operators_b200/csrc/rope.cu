@@ -35,36 +35,48 @@ struct RoPEDesc {
 // ALIGNED says whether a slice may be moved with a single V*2-byte access.
 template<int V, bool ALIGNED>
 struct Slice {
-    uint16_t h[V];
+    uint32_t w[V / 2];// V / 2 packed pairs
     __device__ __forceinline__ void load(const uint16_t *p) {
         if (ALIGNED && V == 8) {
-            *reinterpret_cast<uint4 *>(h) = ld_stream(p);
-        } else if (ALIGNED && V == 2) {
-            *reinterpret_cast<uint32_t *>(h) = *reinterpret_cast<const uint32_t *>(p);
+            const uint4 q = ld_stream(p);
+            w[0] = q.x, w[V / 2 > 1 ? 1 : 0] = q.y, w[V / 2 > 2 ? 2 : 0] = q.z, w[V / 2 > 3 ? 3 : 0] = q.w;
+        } else if (ALIGNED) {
+#pragma unroll
+            for (int e = 0; e < V / 2; ++e) w[e] = reinterpret_cast<const uint32_t *>(p)[e];
         } else {
 #pragma unroll
-            for (int e = 0; e < V; ++e) h[e] = p[e];
+            for (int e = 0; e < V / 2; ++e) w[e] = (uint32_t) p[2 * e] | ((uint32_t) p[2 * e + 1] << 16);
         }
     }
     __device__ __forceinline__ void store(uint16_t *p) const {
         if (ALIGNED && V == 8) {
-            st_stream(p, *reinterpret_cast<const uint4 *>(h));
-        } else if (ALIGNED && V == 2) {
-            *reinterpret_cast<uint32_t *>(p) = *reinterpret_cast<const uint32_t *>(h);
+            st_stream(p, make_uint4(w[0], w[V / 2 > 1 ? 1 : 0], w[V / 2 > 2 ? 2 : 0], w[V / 2 > 3 ? 3 : 0]));
+        } else if (ALIGNED) {
+#pragma unroll
+            for (int e = 0; e < V / 2; ++e) reinterpret_cast<uint32_t *>(p)[e] = w[e];
         } else {
 #pragma unroll
-            for (int e = 0; e < V; ++e) p[e] = h[e];
+            for (int e = 0; e < V / 2; ++e) {
+                p[2 * e] = (uint16_t) w[e];
+                p[2 * e + 1] = (uint16_t) (w[e] >> 16);
+            }
         }
     }
 };
 
-constexpr int kHeadsInFlight = 4;// measured at [4096,32,128]: 4 -> 23 us, 2 -> 27 us, 8 -> 29 us
+#ifndef ROPE_HIF
+#define ROPE_HIF 4
+#endif
+#ifndef ROPE_MINB
+#define ROPE_MINB 4
+#endif
+constexpr int kHeadsInFlight = ROPE_HIF;// measured at [4096,32,128]: 4 -> 23 us, 2 -> 27 us, 8 -> 29 us
 
 // Block = tokens_per_cta x threads_per_token.  threads_per_token is a multiple
 // of slices_per_head, so a thread's slice index within the head never changes
 // while it strides over (head, slice) items: its table values load once.
 template<int V, bool ALIGNED>
-__global__ void rope_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table,
+__global__ void __launch_bounds__(256, ROPE_MINB) rope_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table,
                             uint64_t seq_len, uint32_t nhead, uint32_t dim, int64_t stride_0, int64_t stride_1,
                             uint32_t threads_per_token, uint32_t slices_per_head) {
     const uint32_t tok_in_cta = threadIdx.x / threads_per_token;
@@ -115,11 +127,10 @@ __global__ void rope_kernel(uint16_t *t, const uint64_t *pos_ids, const float *s
                     if (hh < nhead) {
 #pragma unroll
                         for (int k = 0; k < V / 2; ++k) {
-                            const float a = f16_to_f32(x[u].h[2 * k]), b = f16_to_f32(x[u].h[2 * k + 1]);
-                            const float r0 = __fsub_rn(__fmul_rn(a, cs[2 * k]), __fmul_rn(b, sn[2 * k]));
-                            const float r1 = __fadd_rn(__fmul_rn(a, sn[2 * k + 1]), __fmul_rn(b, cs[2 * k + 1]));
-                            x[u].h[2 * k] = f32_to_f16_ref(r0);
-                            x[u].h[2 * k + 1] = f32_to_f16_ref(r1);
+                            const float2 ab = unpack2(x[u].w[k]);
+                            const float r0 = __fsub_rn(__fmul_rn(ab.x, cs[2 * k]), __fmul_rn(ab.y, sn[2 * k]));
+                            const float r1 = __fadd_rn(__fmul_rn(ab.x, sn[2 * k + 1]), __fmul_rn(ab.y, cs[2 * k + 1]));
+                            x[u].w[k] = pack2_ref(r0, r1);// both halves with one truncating conversion
                         }
                         x[u].store(base + (int64_t) hh * stride_1);
                     }
@@ -205,14 +216,14 @@ INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *
     const uint32_t V = v8 ? 8 : 2;
     const uint32_t slices = dim / V;
     // threads per token: a multiple of `slices`, about (items / kHeadsInFlight)
-    // so that every thread has a full set of loads in flight, capped at 1024.
+    // so that every thread has a full set of loads in flight, capped at 256 (the kernel's launch bound).
     uint32_t heads_per_pass = (nhead + kHeadsInFlight - 1) / kHeadsInFlight;
     uint32_t tpt = slices * heads_per_pass;
-    while (tpt > 1024 && heads_per_pass > 1) {
+    while (tpt > 256 && heads_per_pass > 1) {
         heads_per_pass = (heads_per_pass + 1) / 2;
         tpt = slices * heads_per_pass;
     }
-    if (tpt > 1024) tpt = 1024;// more slices per head than a CTA has threads
+    if (tpt > 256) tpt = 256;// more slices per head than a CTA has threads
     uint32_t tokens_per_cta = 1, threads = tpt;
     if (tpt < 256) {
         tokens_per_cta = 256 / tpt;

@@ -377,3 +377,47 @@ def test_vocab_sharded_overflow_is_reported(cuda_lib):
         s = VocabShardedSampler(lib, handle, op, 4096, 0, 1)
         with pytest.raises(RuntimeError):
             s.sample(res, logits, torch.rand(4, device=DEV), 0.9, 20, 1.0)
+
+
+# ---- host buffers through the three-stream staging ---------------------------------
+def test_staged_pipeline_host_buffers(oracle, cuda_lib):
+    """Add (out of place) and RoPE (in place) fed from pinned host tensors through StagedPipeline,
+    three passes in a row with fresh host inputs each time: every pass must return that pass's
+    results (the event chain keeps uploads from overtaking the previous pass's downloads)."""
+    from operators_b200.staging import Stage, StagedPipeline
+
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(77)
+    n_tok, nh, dh = 257, 4, 64
+    a_h = torch.zeros((1 << 16,), dtype=torch.float16).pin_memory()
+    b_h = torch.zeros_like(a_h).pin_memory()
+    c_h = torch.zeros_like(a_h).pin_memory()
+    t_h = torch.zeros((n_tok, nh, dh), dtype=torch.float16).pin_memory()
+    t_out = torch.zeros_like(t_h).pin_memory()
+    pos = torch.arange(n_tok, dtype=torch.int64)
+    sin, cos = ops.sin_cos_table(n_tok, dh)
+    a_d, b_d, c_d, t_d = (x.to(DEV) for x in (a_h, b_h, c_h, t_h))
+    pos_d, sin_d, cos_d = pos.to(DEV), sin.to(DEV), cos.to(DEV)
+    add_op = ops.AddOp(lib, handle, c_d, a_d, b_d)
+    rope_op = ops.RoPEOp(lib, handle, t_d, pos_d, sin_d, cos_d)
+    pipe = StagedPipeline([
+        Stage("add", [(a_d, a_h), (b_d, b_h)], lambda s: add_op(c_d, a_d, b_d, s), [(c_d, c_h)]),
+        Stage("rope", [(t_d, t_h)], lambda s: rope_op(t_d, pos_d, sin_d, cos_d, s), [(t_d, t_out)]),
+    ], DEV)
+    for it in range(3):
+        a = torch.randn(a_h.shape, generator=g).half()
+        b = torch.randn(a_h.shape, generator=g).half()
+        t = torch.randn(t_h.shape, generator=g).half()
+        pipe.synchronize()  # the host buffers are read asynchronously: refill them only when idle
+        a_h.copy_(a), b_h.copy_(b), t_h.copy_(t)
+        pipe.run()
+        pipe.synchronize()
+        want_c = oracle.add(a.numpy(), b.numpy())
+        want_t = oracle.rope(t.numpy().copy(), pos.numpy().astype(np.uint64), sin.numpy(), cos.numpy())
+        assert np.array_equal(c_h.numpy().view(np.uint16), want_c.view(np.uint16)), it
+        assert np.array_equal(t_out.numpy().view(np.uint16), want_t.view(np.uint16)), it
+    # back-to-back passes without waiting in between: the last pass's results are the ones left
+    pipe.run()
+    pipe.run()
+    pipe.synchronize()
+    assert np.array_equal(t_out.numpy().view(np.uint16), want_t.view(np.uint16))
