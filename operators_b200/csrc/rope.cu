@@ -11,12 +11,19 @@
 // the reference the table row offset is p * dh (the table's own row stride is
 // not used) and p is not range-checked.
 //
-// HBM-bound: t is read and written once; a token's two table rows are read
-// from HBM once and shared by all its heads.  Thread -> (token, slice of the
-// head dimension); the thread keeps its slice of the sin/cos rows in registers
-// and walks over the heads with several 128-bit loads in flight.
+// t is read and written once; a token's two table rows are read from HBM once
+// and shared by all its heads.  Two kernels:
+//  * rope_pipeline_kernel (rope_pipeline.cuh): contiguous token rows go through
+//    shared memory with bulk asynchronous copies, persistent CTAs, no CTA
+//    barrier in the loop.  Taken whenever the layout allows it.
+//  * rope_kernel (below): any strides.  Thread -> (token, slice of the head
+//    dimension); the thread keeps its slice of the sin/cos rows in registers
+//    and walks over the heads with several 128-bit loads in flight.  The
+//    environment variable INFINIOP_ROPE_KERNEL (any value) forces this one.
 #include "common.cuh"
+#include "rope_pipeline.cuh"
 
+#include <cstdlib>
 #include <new>
 
 using namespace b200;
@@ -27,6 +34,7 @@ struct RoPEDesc {
     Device device;
     int device_id;
     int sm_count;
+    int max_smem_optin;
     uint64_t seq_len, nhead, dim;
     int64_t stride_0, stride_1;
 };
@@ -64,19 +72,13 @@ struct Slice {
     }
 };
 
-#ifndef ROPE_HIF
-#define ROPE_HIF 4
-#endif
-#ifndef ROPE_MINB
-#define ROPE_MINB 4
-#endif
-constexpr int kHeadsInFlight = ROPE_HIF;// measured at [4096,32,128]: 4 -> 23 us, 2 -> 27 us, 8 -> 29 us
+constexpr int kHeadsInFlight = 4;// measured at [4096,32,128]: 4 -> 23 us, 2 -> 27 us, 8 -> 29 us
 
 // Block = tokens_per_cta x threads_per_token.  threads_per_token is a multiple
 // of slices_per_head, so a thread's slice index within the head never changes
 // while it strides over (head, slice) items: its table values load once.
 template<int V, bool ALIGNED>
-__global__ void __launch_bounds__(256, ROPE_MINB) rope_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table,
+__global__ void __launch_bounds__(256, 4) rope_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table,
                             uint64_t seq_len, uint32_t nhead, uint32_t dim, int64_t stride_0, int64_t stride_1,
                             uint32_t threads_per_token, uint32_t slices_per_head) {
     const uint32_t tok_in_cta = threadIdx.x / threads_per_token;
@@ -177,7 +179,7 @@ INFINIOP_API infiniopStatus_t infiniopCreateRoPEDescriptor(infiniopHandle_t hand
 
     auto *h = reinterpret_cast<Handle *>(handle);
     auto *d = new (std::nothrow)
-        RoPEDesc{DevNvGpu, h->device_id, h->sm_count, seq_len, nhead, dim, t->strides[0], t->strides[1]};
+        RoPEDesc{DevNvGpu, h->device_id, h->sm_count, h->max_smem_optin, seq_len, nhead, dim, t->strides[0], t->strides[1]};
     if (d == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
     *desc_ptr = reinterpret_cast<infiniopRoPEDescriptor_t>(d);
     return STATUS_SUCCESS;
@@ -212,6 +214,37 @@ INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *
     // and of both tables (dh % 8 == 0 makes p*dh*4 a multiple of 32 bytes).
     const bool v8 = dim % 8 == 0 && d->stride_0 % 8 == 0 && d->stride_1 % 8 == 0 && aligned16(t) &&
                     aligned16(sin_table) && aligned16(cos_table);
+    // Contiguous token rows of a size that leaves room for a few stages: the bulk-copy pipeline.
+    if (v8 && d->stride_1 == (int64_t) dim && d->seq_len <= 0xFFFFFFFFull && getenv("INFINIOP_ROPE_KERNEL") == nullptr) {
+        namespace rp = rope_pipe;
+        rp::Plan plan;
+        plan.row_bytes = nhead * dim * 2u;
+        plan.tab_bytes = dim * 4u;
+        plan.stage_bytes = (plan.row_bytes + 2u * plan.tab_bytes + 127u) & ~127u;
+        plan.slices = dim / 8u;
+        plan.row_vecs = plan.row_bytes / 16u;
+        const uint64_t overflow_guard = (uint64_t) nhead * dim * 2ull;
+        const uint32_t grid = (uint32_t) (d->seq_len < (uint64_t) d->sm_count ? d->seq_len : (uint64_t) d->sm_count);
+        plan.grid = grid;
+        plan.smem_bytes = (size_t) rp::kTotalStages * plan.stage_bytes;
+        const uint64_t per_group = (d->seq_len + (uint64_t) grid * rp::kGroups - 1) / ((uint64_t) grid * rp::kGroups);
+        if (overflow_guard == plan.row_bytes && plan.smem_bytes + 1024 <= (size_t) d->max_smem_optin && 32u % plan.slices == 0 &&
+            per_group <= (uint64_t) rp::kMaxTokensPerGroup) {
+            static thread_local int configured_dev = -1, configured_bytes = 0;
+            if (configured_dev != d->device_id || configured_bytes < (int) plan.smem_bytes) {
+                if (cudaFuncSetAttribute(rp::rope_pipeline_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int) plan.smem_bytes) != cudaSuccess) {
+                    cudaGetLastError();
+                    return STATUS_EXECUTION_FAILED;
+                }
+                configured_dev = d->device_id;
+                configured_bytes = (int) plan.smem_bytes;
+            }
+            rp::rope_pipeline_kernel<<<grid, rp::kThreads, plan.smem_bytes, st>>>(tp, pp, sp, cp, (uint32_t) d->seq_len, dim,
+                                                                              d->stride_0, plan);
+            return check_launch("rope_pipeline");
+        }
+    }
     const bool v2_aligned = d->stride_0 % 2 == 0 && d->stride_1 % 2 == 0 && aligned4(t);
     const uint32_t V = v8 ? 8 : 2;
     const uint32_t slices = dim / V;
