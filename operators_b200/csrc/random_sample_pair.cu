@@ -77,6 +77,14 @@ struct FlatList {
     int wcnt[kWarps];          // entries found by each warp of the scan
     int seg_first[kBounds + 1];// leader: list position of the first entry of segment i; [kBounds] = count
 };
+// Records to replay: the entries of the ordered list that lie above the k-th largest key at the start
+// of their segment, in index order.
+struct RecList {
+    uint32_t idx[kFlatCap];
+    uint16_t key[kFlatCap];
+    int cnt;
+    int seg_first[kBounds + 1];// leader: position of the first entry of segment i; [kBounds] = count
+};
 struct Mail {// written by the other CTA of the pair (the leader also fills its own copy)
     uint32_t L_peer;
     uint32_t tau_mid;
@@ -87,8 +95,10 @@ struct Mail {// written by the other CTA of the pair (the leader also fills its 
 };
 struct Aux {
     FlatList fl;
+    RecList rl;
     alignas(16) uint16_t gbuf[2 * kFlatCap];// start states: 256 fp16 values per boundary; then top-k: per-key-group queues of candidate ordinals
     int state_ovf;                         // a boundary had more than 256 values to choose from
+    int wcnt_r[kWarps], wcnt_h[kWarps];    // per-warp counts of the list compaction (records, helper's candidates)
     uint32_t tie_key[kTieGroups];
     uint32_t tie_greater[kTieGroups];
     uint32_t tie_same[kTieGroups];
@@ -316,14 +326,14 @@ __device__ __noinline__ void records_direct_block(uint16_t *blk, uint32_t first_
 // `dst` (positions are taken relative to `pos_offset`).  Sixteen keys at a time
 // are read into registers of every lane, so the only serial dependency between
 // entries is the running value itself (one warp-wide minimum per record).
-__device__ __noinline__ void replay_list(const FlatList &fl, int first, int count, uint16_t *dst,
-                                            uint32_t pos_offset, int lane, MinBuf &m) {
+__device__ __noinline__ void replay_list(const uint16_t *keys, const uint32_t *idx, int count, uint16_t *dst,
+                                         uint32_t pos_offset, int lane, MinBuf &m) {
     constexpr int kBatch = 16;
     for (int c0 = 0; c0 < count; c0 += kBatch) {
         uint32_t kb[kBatch];// key << 6
 #pragma unroll
-        for (int i = 0; i < kBatch; ++i) kb[i] = c0 + i < count ? (uint32_t) fl.key[first + c0 + i] << 6 : 0u;
-        const uint32_t my_idx = (lane < kBatch && c0 + lane < count) ? fl.idx[first + c0 + lane] : 0u;
+        for (int i = 0; i < kBatch; ++i) kb[i] = c0 + i < count ? (uint32_t) keys[c0 + i] << 6 : 0u;
+        const uint32_t my_idx = (lane < kBatch && c0 + lane < count) ? idx[c0 + lane] : 0u;
         uint32_t my_tau = kEmptyMin;// lane i remembers the value its entry is replaced by; stored after the batch
 #pragma unroll
         for (int i = 0; i < kBatch; ++i) {
@@ -486,6 +496,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             const int b = warp - (kBounds - kDirect);
             const uint32_t tau = kth_largest_256(raw, (int) (kBoundPos[b] / 8u), k, ax.state[b + 1]);
             if (lane == 0) ax.seg_tau[b + 1] = tau;
+        } else if (leader && warp == kBounds && (uint32_t) k < n) {// the k-th largest of the first k elements
+            MinBuf fb;
+            minbuf_init(fb, lane, k, raw);
+            if (lane == 0) ax.seg_tau[0] = fb.tau();
         }
         __syncthreads();
     }
@@ -618,13 +632,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         scan_ordered(r0, min(r0 + span, my_pad), 0u, tk, strict, kFlatCap);
     };
 
+    // One ordered list per CTA serves three purposes, so a segment's threshold is the lowest of what they
+    // need: the candidates for the top-k (key >= L), the keys a later start state is chosen from (at or
+    // above that boundary's bound), and the records to replay (above the k-th largest key at the START of
+    // the segment, known exactly for the first segments and bounded from below by that boundary's bound
+    // for the later ones).  The records are filtered out of the list later instead of scanning the row again.
+    const bool want_records = (uint32_t) k < n;
     if (leader) {
-        // master list.  Segments below 256: the candidates proper (key >= L); their start states are known.
-        // Later segments: everything >= the bound of the prefix the segment closes, for the start states.
         const int sg = kScanSeg[warp];
-        scan_ordered(kScanR0[warp], kScanR0[warp + 1], 0u, sg < kDirect ? L : ax.LB[sg], false, kFlatCap);
+        uint32_t thr = L;
+        if (want_records) {
+            if (sg < kDirect) thr = min(L, ax.seg_tau[sg] + 1u);
+            else if (sg == kDirect) thr = min(ax.seg_tau[sg] + 1u, ax.LB[sg]);
+            else thr = ax.LB[sg - 1];
+        }
+        scan_ordered(kScanR0[warp], kScanR0[warp + 1], 0u, thr, false, kFlatCap);
     } else {
-        scan_helper(L, false);
+        // the leader's bound for its whole half is a lower bound of the k-th largest key where this half starts
+        scan_helper(want_records ? min(L, max(ax.mail.L_peer, 1u)) : L, false);
         ship_list();
     }
     cluster.sync();// CS2
@@ -670,42 +695,71 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         __syncthreads();// the start states have been read off the master list
         if (ax.state_ovf) list_ok = false;
         if (list_ok) {
-            // keep only the candidates proper (key >= L): the ranking below is quadratic in the list length.
-            // One entry per thread, read before the barrier and written to its new place after it; the
-            // helper's entries move up behind the leader's own: one list in index order.
+            // Out of the ordered lists: the candidates proper (key >= L; the ranking below is quadratic in
+            // their number), the helper's behind the leader's own, in place; and the records to replay
+            // (key above the k-th largest at the start of the entry's segment), into their own list.  One
+            // entry per thread, read before the barrier and written to its new place after it.
             uint32_t my_idx = 0, my_key = 0, mv_idx = 0, mv_key = 0;
-            bool keep = false;
+            bool keep = false, rec = false, keep_h = false;
             if (tid < cnt0) {
                 my_key = ax.fl.key[tid];
                 my_idx = ax.fl.idx[tid];
                 keep = my_key >= L;
+                const int sg = my_idx < 128u ? 0 : 25 - __clz(my_idx);// segment i ends at 128 << i
+                rec = want_records && my_idx >= (uint32_t) k && my_key > ax.seg_tau[sg];
             }
             if (tid < cnt1) {
                 mv_idx = ax.fl.idx[kFlatCap + tid];
                 mv_key = ax.fl.key[kFlatCap + tid];
+                keep_h = mv_key >= L;
             }
-            const uint32_t hit = __ballot_sync(0xffffffffu, keep);
-            if (lane == 0) ax.fl.wcnt[warp] = __popc(hit);
+            const uint32_t hit = __ballot_sync(0xffffffffu, keep), hit_r = __ballot_sync(0xffffffffu, rec);
+            const uint32_t hit_h = __ballot_sync(0xffffffffu, keep_h);
+            if (lane == 0) {
+                ax.fl.wcnt[warp] = __popc(hit);
+                ax.wcnt_r[warp] = __popc(hit_r);
+                ax.wcnt_h[warp] = __popc(hit_h);
+            }
             if (tid == 0) ax.tie_groups = 0;
             if (tid < kSlots) {
                 ax.top_key[tid] = 0;
                 ax.top_idx[tid] = 0;
             }
             __syncthreads();
-            const int c_l = ax.fl.wcnt[lane];
+            const int c_l = ax.fl.wcnt[lane], r_l = ax.wcnt_r[lane], h_l = ax.wcnt_h[lane];
             const int off = __reduce_add_sync(0xffffffffu, lane < warp ? c_l : 0);
             const int cnt0c = __reduce_add_sync(0xffffffffu, c_l);
-            const int m = cnt0c + cnt1;
+            const int off_r = __reduce_add_sync(0xffffffffu, lane < warp ? r_l : 0);
+            const int cnt_r = __reduce_add_sync(0xffffffffu, r_l);
+            const int off_h = __reduce_add_sync(0xffffffffu, lane < warp ? h_l : 0);
+            const int cnt1c = __reduce_add_sync(0xffffffffu, h_l);
+            const int m = cnt0c + cnt1c;
+            const uint32_t below = (1u << lane) - 1u;
             if (keep) {
-                const int at = off + __popc(hit & ((1u << lane) - 1u));
+                const int at = off + __popc(hit & below);
                 ax.fl.key[at] = (uint16_t) my_key;
                 ax.fl.idx[at] = my_idx;
             }
-            if (tid < cnt1) {
-                ax.fl.idx[cnt0c + tid] = mv_idx;
-                ax.fl.key[cnt0c + tid] = (uint16_t) mv_key;
+            if (keep_h) {
+                const int at = cnt0c + off_h + __popc(hit_h & below);
+                ax.fl.idx[at] = mv_idx;
+                ax.fl.key[at] = (uint16_t) mv_key;
             }
-            if (tid == 0) ax.fl.cnt = cnt0c;
+            const int at_r = off_r + __popc(hit_r & below);// records before this entry
+            if (rec) {
+                ax.rl.key[at_r] = (uint16_t) my_key;
+                ax.rl.idx[at_r] = my_idx;
+            }
+            // where each segment's records start: the list position of the segment's first entry, translated
+            for (int sg = 0; sg <= kBounds; ++sg) {
+                const int p0 = ax.fl.seg_first[sg];
+                if (p0 == tid && tid < cnt0) ax.rl.seg_first[sg] = at_r;
+                if (p0 >= cnt0 && tid == 0) ax.rl.seg_first[sg] = cnt_r;
+            }
+            if (tid == 0) {
+                ax.fl.cnt = cnt0c;
+                ax.rl.cnt = cnt_r;
+            }
             __syncthreads();
             SUBSTAMP();// s0: lists merged
             // Rank every candidate: `greater` keys above it, `same` keys equal to it.
@@ -829,10 +883,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         if (warp < 2) {// exact terms of the top-k, one per thread
             const int i = tid;
             if (i < k) ax.top_term[i] = term_exact(val_of(ax.top_key[i]), val_of(ax.top_key[0]), T);
-        } else if (warp == 2 && (uint32_t) k < n && list_ok) {// meanwhile: the k-th largest of the first k elements
-            MinBuf fb;
-            minbuf_init(fb, lane, k, raw);
-            if (lane == 0) ax.seg_tau[0] = fb.tau();
         }
         __syncthreads();
         if (tid == 0) {
@@ -881,32 +931,49 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
 
     // ---- P4: records.  Leader: its segments in parallel, one warp each.  Helper: its half. ----
     if (leader && list_ok && (uint32_t) k < n) {
-        // flagged: above the exact k-th largest at the segment start (the whole list area is free now)
-        scan_ordered(kScanR0[warp], kScanR0[warp + 1], (uint32_t) k, ax.seg_tau[kScanSeg[warp]], true, 2 * kFlatCap);
-        if (!ax.fl.overflow) {
-            if (warp < kBounds) {// segment i on warp i
-                const int sg = warp;
-                const uint32_t s_begin = sg == 0 ? (uint32_t) k : kBoundPos[sg - 1];
-                if (s_begin < n0) {
-                    const int first = ax.fl.seg_first[sg], last = ax.fl.seg_first[sg + 1];
-                    MinBuf sb;
-                    if (sg == 0) minbuf_init(sb, lane, k, raw);
-                    else minbuf_init_keys(sb, lane, k, ax.state[sg]);
-                    replay_list(ax.fl, first, last - first, raw, 0u, lane, sb);
-                }
+        if (warp < kBounds) {// segment i on warp i
+            const int sg = warp;
+            const uint32_t s_begin = sg == 0 ? (uint32_t) k : kBoundPos[sg - 1];
+            if (s_begin < n0) {
+                const int first = ax.rl.seg_first[sg], last = ax.rl.seg_first[sg + 1];
+                MinBuf sb;
+                if (sg == 0) minbuf_init(sb, lane, k, raw);
+                else minbuf_init_keys(sb, lane, k, ax.state[sg]);
+                replay_list(ax.rl.key + first, ax.rl.idx + first, last - first, raw, 0u, lane, sb);
             }
-        } else if (warp == 0) {// flagged list overflowed: serial walk from the initial state
-            minbuf_init(mb, lane, k, raw);
-            for (uint32_t b = 0; b < nblk0; ++b) records_direct_block(raw + b * kBlk, b == 0 ? (uint32_t) k : 0u, lane, mb);
         }
     }
     if (!leader && my_n > 0 && !ax.mail.done) {
-        scan_helper(ax.seg_tau[kBounds], true);
+        const bool have_list = !ax.fl.overflow;
+        if (have_list) {
+            // the records among this half's list entries: above the k-th largest key of the leader half
+            const int cnt = ax.fl.cnt;
+            uint32_t my_idx = 0, my_key = 0;
+            bool rec = false;
+            if (tid < cnt) {
+                my_key = ax.fl.key[tid];
+                my_idx = ax.fl.idx[tid];
+                rec = my_key > ax.seg_tau[kBounds];
+            }
+            const uint32_t hit_r = __ballot_sync(0xffffffffu, rec);
+            if (lane == 0) ax.wcnt_r[warp] = __popc(hit_r);
+            __syncthreads();
+            const int r_l = ax.wcnt_r[lane];
+            const int off_r = __reduce_add_sync(0xffffffffu, lane < warp ? r_l : 0);
+            const int cnt_r = __reduce_add_sync(0xffffffffu, r_l);
+            if (rec) {
+                const int at = off_r + __popc(hit_r & ((1u << lane) - 1u));
+                ax.rl.key[at] = (uint16_t) my_key;
+                ax.rl.idx[at] = my_idx;
+            }
+            if (tid == 0) ax.rl.cnt = cnt_r;
+            __syncthreads();
+        }
         if (warp == 0) {
             MinBuf hb;
             minbuf_init_keys(hb, lane, k, ax.state[kBounds]);
-            if (!ax.fl.overflow) {
-                replay_list(ax.fl, 0, ax.fl.cnt, raw, (uint32_t) kHalfElems, lane, hb);
+            if (have_list) {
+                replay_list(ax.rl.key, ax.rl.idx, ax.rl.cnt, raw, (uint32_t) kHalfElems, lane, hb);
             } else {
                 for (uint32_t b = 0; b < my_nblk; ++b) records_direct_block(raw + b * kBlk, 0u, lane, hb);
             }
