@@ -803,33 +803,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                     const uint32_t kj = j0 + lane < m ? (uint32_t) ax.fl.key[j0 + lane] : 0u;
                     const uint32_t gt = __ballot_sync(0xffffffffu, kj > gkey);
                     const uint32_t eq = __ballot_sync(0xffffffffu, kj == gkey);
-                    if (eq == 0 && sz == 0) {// nothing queued, nothing joins: the larger keys only count
-                        G += __popc(gt);
-                        continue;
-                    }
-                    uint32_t ev = gt | eq;
-                    while (ev) {
-                        const int bpos = __ffs(ev) - 1;
-                        ev &= ev - 1;
-                        if ((gt >> bpos) & 1u) {
-                            ++G;
+                    // Larger keys between two equal ones act as a run: the first `room` of them (while the
+                    // buffer still holds smaller keys to evict) each move the front of the queue to the back,
+                    // the others each push the front out.  r rotations of a queue of sz are r mod sz rotations.
+                    uint32_t rest = gt, e = eq;
+                    while (true) {
+                        const int nb = e ? __ffs(e) - 1 : 32;// next equal key in this chunk
+                        const uint32_t upto = nb < 32 ? (1u << nb) - 1u : 0xFFFFFFFFu;
+                        const uint32_t r = __popc(rest & upto);
+                        rest &= ~upto;
+                        if (r > 0) {
                             if (sz > 0) {
-                                if (G + sz > (uint32_t) k) {// nothing smaller left to evict: the front leaves
-                                    head = head + 1 == cap ? 0 : head + 1;
-                                    --sz;
-                                } else if (sz > 1) {// front moves to the back
-                                    if (sz < cap) {
-                                        uint32_t tail = head + sz;
-                                        if (tail >= cap) tail -= cap;
-                                        if (lane == 0) q[tail] = q[head];
+                                const uint32_t room = (uint32_t) k - (G + sz);// invariant: G + sz <= k
+                                const uint32_t rot = r < room ? r : room;
+                                uint32_t pops = r - rot;
+                                if (sz > 1 && rot > 0) {
+                                    const uint32_t rr = rot % sz;
+                                    if (sz == cap) {// full ring: turning it is moving the head
+                                        head += rr;
+                                        if (head >= cap) head -= cap;
+                                    } else {
+                                        for (uint32_t i = 0; i < rr; ++i) {
+                                            uint32_t tail = head + sz;
+                                            if (tail >= cap) tail -= cap;
+                                            if (lane == 0) q[tail] = q[head];
+                                            head = head + 1 == cap ? 0 : head + 1;
+                                        }
                                     }
-                                    head = head + 1 == cap ? 0 : head + 1;
                                 }
+                                if (pops > sz) pops = sz;
+                                head += pops;
+                                if (head >= cap) head -= cap;
+                                sz -= pops;
                             }
-                        } else if (G + sz < (uint32_t) k) {
+                            G += r;
+                        }
+                        if (!e) break;
+                        e &= e - 1;
+                        if (G + sz < (uint32_t) k) {// the equal key joins at the back
                             uint32_t tail = head + sz;
                             if (tail >= cap) tail -= cap;
-                            if (lane == 0) q[tail] = (uint16_t) (j0 + bpos);
+                            if (lane == 0) q[tail] = (uint16_t) (j0 + nb);
                             ++sz;
                         }
                     }
