@@ -106,7 +106,8 @@ struct Aux {
     uint32_t top_key[kSlots];
     uint32_t top_idx[kSlots];
     alignas(16) float top_term[kSlots];
-    float blk_terms[kBlk];
+    alignas(16) float blk_terms[kBlk];
+    uint32_t walk_event;                   // block to replay with real additions, or none
     uint32_t C[kLevels][kMaxBlk];// integer block sums per binade level
     uint32_t tie[kMaxBlk];       // bit d: block holds an exact half-way case at level d
     uint32_t LB[kBounds];        // lower bound of the k-th largest key of the prefix that ends at boundary b
@@ -1093,75 +1094,85 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         SUBSTAMP();// s4: exact path done
         cluster.sync();// CS6
         SUBSTAMP();// s5: after barrier
-        if (leader && warp == 0) {
+        if (leader) {
+            // Warp 0 walks over the block sums; where the running sum may change binade (or a block holds a
+            // half-way case) the block is replayed with real fp32 additions: the whole CTA evaluates its 256
+            // exact terms, one per thread, thread 0 adds them in order, warp 0 walks on.
+            constexpr uint32_t kNoEvent = 0xFFFFFFFFu;
             uint32_t m = (__float_as_uint(s_base) & 0x7FFFFFu) | 0x800000u;
             int level = 0;
-            bool again = false;
+            bool again = false, stop = false;
             float s_cur = s_base;
             uint32_t b0 = gb_first;
-            while (b0 < nblk) {
-                const uint32_t b = b0 + lane;
-                const uint32_t rawc = b < nblk ? ax.C[level][b] : 0u;
-                const bool tied = b < nblk && ((ax.tie[b] >> level) & 1u);
-                uint32_t inc = min(rawc, 1u << 25);// >= 2^24 is a carry by itself; keeps the scan in 32 bits
+            while (true) {
+                if (warp == 0) {
+                    uint32_t eb = kNoEvent;
+                    while (!stop && b0 < nblk) {
+                        const uint32_t b = b0 + lane;
+                        const uint32_t rawc = b < nblk ? ax.C[level][b] : 0u;
+                        const bool tied = b < nblk && ((ax.tie[b] >> level) & 1u);
+                        uint32_t inc = min(rawc, 1u << 25);// >= 2^24 is a carry by itself; keeps the scan in 32 bits
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
-                    if (lane >= o) inc += t;
-                }
-                const uint32_t evm = __ballot_sync(0xffffffffu, tied || (m + inc >= (1u << 24)));
-                if (evm == 0) {
-                    m += __shfl_sync(0xffffffffu, inc, 31);
-                    b0 += 32;
-                    continue;
-                }
-                const int l = __ffs(evm) - 1;
-                m += l == 0 ? 0u : __shfl_sync(0xffffffffu, inc, l - 1);
-                const uint32_t eb = b0 + l;// replay this block with real fp32 additions
-                float s_new = __uint_as_float((uint32_t) (e0 + level - 23) << 23) * (float) m;
-                {
-                    const uint16_t *blk = eb < nblk0 ? raw + eb * kBlk : peer_raw + (eb - nblk0) * kBlk;
-                    const uint32_t gbase = eb < nblk0 ? eb * kBlk : (uint32_t) kHalfElems + (eb - nblk0) * kBlk;
-                    uint32_t w[4];
-                    lds_raw(blk + lane * 8, w);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const uint32_t j = gbase + lane * 8 + e;
-                        const uint16_t h = half_at(w, e);
-                        ax.blk_terms[lane * 8 + e] = (h == kPad || j < pos) ? 0.f : term_exact(f16_to_f32(h), M, T);
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+                            if (lane >= o) inc += t;
+                        }
+                        const uint32_t evm = __ballot_sync(0xffffffffu, tied || (m + inc >= (1u << 24)));
+                        if (evm == 0) {
+                            m += __shfl_sync(0xffffffffu, inc, 31);
+                            b0 += 32;
+                            continue;
+                        }
+                        const int l = __ffs(evm) - 1;
+                        m += l == 0 ? 0u : __shfl_sync(0xffffffffu, inc, l - 1);
+                        eb = b0 + l;
+                        break;
                     }
-                    __syncwarp();
+                    if (lane == 0) ax.walk_event = eb;
+                }
+                __syncthreads();
+                const uint32_t eb = ax.walk_event;
+                if (eb == kNoEvent) break;
+                if (tid < kBlk) {
+                    const uint16_t *blk = eb < nblk0 ? raw + eb * kBlk : peer_raw + (eb - nblk0) * kBlk;
+                    const uint32_t j = (eb < nblk0 ? eb * kBlk : (uint32_t) kHalfElems + (eb - nblk0) * kBlk) + tid;
+                    const uint16_t h = blk[tid];
+                    ax.blk_terms[tid] = (h == kPad || j < pos) ? 0.f : term_exact(f16_to_f32(h), M, T);
+                }
+                __syncthreads();
+                if (warp == 0) {
+                    float s_new = __uint_as_float((uint32_t) (e0 + level - 23) << 23) * (float) m;
                     if (lane == 0) {
-                        for (int i0 = 0; i0 < kBlk; i0 += 16) {
-                            float t16[16];
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) t16[i] = ax.blk_terms[i0 + i];
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) s_new = __fadd_rn(s_new, t16[i]);
+#pragma unroll 2
+                        for (int i0 = 0; i0 < kBlk; i0 += 4) {
+                            const float4 q = *reinterpret_cast<const float4 *>(&ax.blk_terms[i0]);
+                            s_new = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s_new, q.x), q.y), q.z), q.w);
                         }
                     }
                     s_new = __shfl_sync(0xffffffffu, s_new, 0);
-                }
-                s_cur = s_new;
-                const int es = (int) ((__float_as_uint(s_new) >> 23) & 0xFFu);
-                level = es - e0;
-                m = (__float_as_uint(s_new) & 0x7FFFFFu) | 0x800000u;
-                b0 = eb + 1;
-                if (level >= kLevels) {
-                    again = b0 < nblk;
-                    break;
+                    s_cur = s_new;
+                    const int es = (int) ((__float_as_uint(s_new) >> 23) & 0xFFu);
+                    level = es - e0;
+                    m = (__float_as_uint(s_new) & 0x7FFFFFu) | 0x800000u;
+                    b0 = eb + 1;
+                    if (level >= kLevels) {
+                        again = b0 < nblk;
+                        stop = true;
+                    }
                 }
             }
-            if (b0 >= nblk && level < kLevels) {
-                s_cur = __uint_as_float((uint32_t) (e0 + level - 23) << 23) * (float) m;
-            }
-            if (lane == 0) {
-                ax.mail.s_base = s_cur;
-                ax.mail.pos_base = b0 * kBlk;
-                ax.mail.done = again ? 0 : 1;
-                peer_ax->mail.s_base = s_cur;
-                peer_ax->mail.pos_base = b0 * kBlk;
-                peer_ax->mail.done = again ? 0 : 1;
+            if (warp == 0) {
+                if (b0 >= nblk && level < kLevels) {
+                    s_cur = __uint_as_float((uint32_t) (e0 + level - 23) << 23) * (float) m;
+                }
+                if (lane == 0) {
+                    ax.mail.s_base = s_cur;
+                    ax.mail.pos_base = b0 * kBlk;
+                    ax.mail.done = again ? 0 : 1;
+                    peer_ax->mail.s_base = s_cur;
+                    peer_ax->mail.pos_base = b0 * kBlk;
+                    peer_ax->mail.done = again ? 0 : 1;
+                }
             }
         }
         SUBSTAMP();// s6: walk done
