@@ -49,6 +49,7 @@ constexpr int kTieGroups = 64;
 // are found directly on the row; for the later boundaries they come from a candidate list whose
 // threshold is a lower bound taken from maxima of groups of threads.  Those prefixes are covered by
 // whole per-thread load slots: thread t's vector u is elements [8t + 8192u, 8t + 8192u + 8).
+constexpr int kWalkWarps = kMaxBlk / 32;// the walk looks at all block sums at once, 32 per warp
 constexpr int kBounds = 10;
 constexpr int kDirect = 2;
 __device__ __constant__ uint32_t kBoundPos[kBounds] = {128u, 256u, 512u, 1024u, 2048u, 4096u, 8192u, 16384u, 32768u, 65536u};
@@ -108,6 +109,9 @@ struct Aux {
     alignas(16) float top_term[kSlots];
     alignas(16) float blk_terms[kBlk];
     uint32_t walk_event;                   // block to replay with real additions, or none
+    uint32_t walk_tot[kWalkWarps], walk_m[kWalkWarps];
+    int walk_ev[kWalkWarps];
+    float walk_s;
     uint32_t C[kLevels][kMaxBlk];// integer block sums per binade level
     uint32_t tie[kMaxBlk];       // bit d: block holds an exact half-way case at level d
     uint32_t LB[kBounds];        // lower bound of the k-th largest key of the prefix that ends at boundary b
@@ -1095,9 +1099,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         cluster.sync();// CS6
         SUBSTAMP();// s5: after barrier
         if (leader) {
-            // Warp 0 walks over the block sums; where the running sum may change binade (or a block holds a
-            // half-way case) the block is replayed with real fp32 additions: the whole CTA evaluates its 256
-            // exact terms, one per thread, thread 0 adds them in order, warp 0 walks on.
+            // The walk over the block sums; where the running sum may change binade (or a block holds a
+            // half-way case) the block is replayed with real fp32 additions: the CTA evaluates its 256
+            // exact terms, one per thread, thread 0 adds them in order, the walk goes on behind the block.
             constexpr uint32_t kNoEvent = 0xFFFFFFFFu;
             uint32_t m = (__float_as_uint(s_base) & 0x7FFFFFu) | 0x800000u;
             int level = 0;
@@ -1105,30 +1109,49 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             float s_cur = s_base;
             uint32_t b0 = gb_first;
             while (true) {
-                if (warp == 0) {
-                    uint32_t eb = kNoEvent;
-                    while (!stop && b0 < nblk) {
-                        const uint32_t b = b0 + lane;
-                        const uint32_t rawc = b < nblk ? ax.C[level][b] : 0u;
-                        const bool tied = b < nblk && ((ax.tie[b] >> level) & 1u);
-                        uint32_t inc = min(rawc, 1u << 25);// >= 2^24 is a carry by itself; keeps the scan in 32 bits
+                // One pass over all remaining blocks, 32 per warp: scan inside the warp, chain the warps'
+                // totals, find the first block where the sum may carry (or that holds a half-way case).
+                {
+                    const uint32_t b = b0 + 32u * warp + lane;
+                    const bool live = warp < kWalkWarps && b < nblk;
+                    const uint32_t rawc = live ? ax.C[level][b] : 0u;
+                    const bool tied = live && ((ax.tie[b] >> level) & 1u);
+                    uint32_t inc = min(rawc, 1u << 25);// >= 2^24 is a carry by itself; keeps the sums in 32 bits
 #pragma unroll
-                        for (int o = 1; o < 32; o <<= 1) {
-                            const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
-                            if (lane >= o) inc += t;
-                        }
-                        const uint32_t evm = __ballot_sync(0xffffffffu, tied || (m + inc >= (1u << 24)));
-                        if (evm == 0) {
-                            m += __shfl_sync(0xffffffffu, inc, 31);
-                            b0 += 32;
-                            continue;
-                        }
-                        const int l = __ffs(evm) - 1;
-                        m += l == 0 ? 0u : __shfl_sync(0xffffffffu, inc, l - 1);
-                        eb = b0 + l;
-                        break;
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+                        if (lane >= o) inc += t;
                     }
-                    if (lane == 0) ax.walk_event = eb;
+                    inc = min(inc, 1u << 25);
+                    if (warp < kWalkWarps && lane == 31) ax.walk_tot[warp] = inc;
+                    __syncthreads();
+                    const uint32_t t_l = lane < kWalkWarps ? ax.walk_tot[lane] : 0u;// at most 16 x 2^25
+                    const uint32_t before = __reduce_add_sync(0xffffffffu, lane < warp ? t_l : 0u);
+                    const uint32_t all = __reduce_add_sync(0xffffffffu, t_l);
+                    const uint32_t m_start = m + min(before, 1u << 25);
+                    const uint32_t evm = __ballot_sync(0xffffffffu, tied || (live && m_start + inc >= (1u << 24)));
+                    if (warp < kWalkWarps && lane == 0) {
+                        const int l = evm ? __ffs(evm) - 1 : -1;
+                        ax.walk_ev[warp] = l;
+                    }
+                    const int l = evm ? __ffs(evm) - 1 : 0;
+                    const uint32_t m_at = m_start + (l == 0 ? 0u : __shfl_sync(0xffffffffu, inc, l - 1));
+                    if (warp < kWalkWarps && lane == 0) ax.walk_m[warp] = m_at;
+                    __syncthreads();
+                    // every thread: the first warp with an event
+                    const int ev_l = lane < kWalkWarps ? ax.walk_ev[lane] : -1;
+                    const uint32_t has = __ballot_sync(0xffffffffu, ev_l >= 0);
+                    if (stop || b0 >= nblk || has == 0) {
+                        if (!stop && b0 < nblk) {// walked to the end without an event
+                            m += all;
+                            b0 = nblk;
+                        }
+                        if (tid == 0) ax.walk_event = kNoEvent;
+                    } else {
+                        const int w = __ffs(has) - 1;
+                        m = ax.walk_m[w];
+                        if (tid == 0) ax.walk_event = b0 + 32u * w + (uint32_t) ax.walk_ev[w];
+                    }
                 }
                 __syncthreads();
                 const uint32_t eb = ax.walk_event;
@@ -1140,16 +1163,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                     ax.blk_terms[tid] = (h == kPad || j < pos) ? 0.f : term_exact(f16_to_f32(h), M, T);
                 }
                 __syncthreads();
-                if (warp == 0) {
+                if (tid == 0) {
                     float s_new = __uint_as_float((uint32_t) (e0 + level - 23) << 23) * (float) m;
-                    if (lane == 0) {
 #pragma unroll 2
-                        for (int i0 = 0; i0 < kBlk; i0 += 4) {
-                            const float4 q = *reinterpret_cast<const float4 *>(&ax.blk_terms[i0]);
-                            s_new = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s_new, q.x), q.y), q.z), q.w);
-                        }
+                    for (int i0 = 0; i0 < kBlk; i0 += 4) {
+                        const float4 q = *reinterpret_cast<const float4 *>(&ax.blk_terms[i0]);
+                        s_new = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s_new, q.x), q.y), q.z), q.w);
                     }
-                    s_new = __shfl_sync(0xffffffffu, s_new, 0);
+                    ax.walk_s = s_new;
+                }
+                __syncthreads();
+                {// every thread keeps the walk's state
+                    const float s_new = ax.walk_s;
                     s_cur = s_new;
                     const int es = (int) ((__float_as_uint(s_new) >> 23) & 0xFFu);
                     level = es - e0;
