@@ -1005,7 +1005,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
 
     // ---- denominator rounds -------------------------------------------------------------
     const float A = kLog2e / T;
-    int rounds = 0;
+    int rounds = 0, replays = 0, unsure = 0;
     for (int round = 0; round < kMaxRounds && !ax.mail.done; ++round) {
         ++rounds;
         const float s_base = ax.mail.s_base;
@@ -1081,6 +1081,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         SUBSTAMP();// s3: block sums (approximate path)
         {// exact re-evaluation of the uncertain elements, densely
             const int cnt = min(ax.unc_cnt, kUncCap);
+            unsure += ax.unc_cnt;
             for (int i = tid; i < cnt; i += kThreads) {
                 const uint32_t lp = ax.unc[i];
                 exact_contrib(ax, lp / kBlk + goff, f16_to_f32(raw[lp]), M, T, e0);
@@ -1156,6 +1157,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 __syncthreads();
                 const uint32_t eb = ax.walk_event;
                 if (eb == kNoEvent) break;
+                ++replays;
                 if (tid < kBlk) {
                     const uint16_t *blk = eb < nblk0 ? raw + eb * kBlk : peer_raw + (eb - nblk0) * kBlk;
                     const uint32_t j = (eb < nblk0 ? eb * kBlk : (uint32_t) kHalfElems + (eb - nblk0) * kBlk) + tid;
@@ -1165,10 +1167,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 __syncthreads();
                 if (tid == 0) {
                     float s_new = __uint_as_float((uint32_t) (e0 + level - 23) << 23) * (float) m;
-#pragma unroll 2
-                    for (int i0 = 0; i0 < kBlk; i0 += 4) {
-                        const float4 q = *reinterpret_cast<const float4 *>(&ax.blk_terms[i0]);
-                        s_new = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s_new, q.x), q.y), q.z), q.w);
+                    const float4 *t4 = reinterpret_cast<const float4 *>(ax.blk_terms);
+                    float4 q[4] = {t4[0], t4[1], t4[2], t4[3]};// the loads run ahead of the chain of additions
+#pragma unroll 1
+                    for (int i0 = 0; i0 < kBlk / 4; i0 += 4) {
+                        float4 nx[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) nx[u] = t4[min(i0 + 4 + u, kBlk / 4 - 1)];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            s_new = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(s_new, q[u].x), q[u].y), q[u].z), q[u].w);
+                            q[u] = nx[u];
+                        }
                     }
                     ax.walk_s = s_new;
                 }
@@ -1220,6 +1230,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                     dbg[1 + kSlots + i] = ax.top_term[i];
                 }
                 dbg[129 + 15] = (float) rounds;
+                dbg[129 + 14] = (float) replays;
+                dbg[129 + 13] = (float) unsure;
             }
             pick_from_topk(ax.top_term, ax.top_idx, k, a.topp, random_val, a.result + (int64_t) row * a.result_stride);
         }
