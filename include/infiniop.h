@@ -180,6 +180,22 @@ INFINIOP_API infiniopStatus_t infiniopAdd(infiniopAddDescriptor_t desc, void *c,
                                           void *stream);
 INFINIOP_API infiniopStatus_t infiniopDestroyAddDescriptor(infiniopAddDescriptor_t desc);
 
+/* ---- rearrange: include/ops/rearrange/rearrange.h:7-20 --------------------- *
+ * dst[..] = src[..] between two views of equal shape and element type whose
+ * innermost stride is 1; outer strides are arbitrary.  Bytes are copied, any
+ * DataLayout.  Up to 8 dimensions (the reference's nv-gpu code: 3). */
+typedef struct RearrangeDescriptor {
+    Device device;
+} RearrangeDescriptor;
+typedef RearrangeDescriptor *infiniopRearrangeDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateRearrangeDescriptor(infiniopHandle_t handle,
+                                                                infiniopRearrangeDescriptor_t *desc_ptr,
+                                                                infiniopTensorDescriptor_t dst,
+                                                                infiniopTensorDescriptor_t src);
+INFINIOP_API infiniopStatus_t infiniopRearrange(infiniopRearrangeDescriptor_t desc, void *dst, void const *src,
+                                                void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyRearrangeDescriptor(infiniopRearrangeDescriptor_t desc);
+
 /* ---- causal softmax: include/ops/causal_softmax/causal_softmax.h:7-25 ----- *
  * In place on fp16 [.., seq_len, total_seq_len] (2-D or 3-D, unit last
  * stride): row i keeps columns j <= total_seq_len - seq_len + i, the rest

@@ -38,6 +38,9 @@ def _declare(lib):
         "infiniopCreateAddDescriptor": [H, POINTER(D), T, T, T],
         "infiniopAdd": [D, c_void_p, c_void_p, c_void_p, c_void_p],
         "infiniopDestroyAddDescriptor": [D],
+        "infiniopCreateRearrangeDescriptor": [H, POINTER(D), T, T],
+        "infiniopRearrange": [D, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroyRearrangeDescriptor": [D],
         "infiniopCreateCausalSoftmaxDescriptor": [H, POINTER(D), T],
         "infiniopGetCausalSoftmaxWorkspaceSize": [D, POINTER(c_uint64)],
         "infiniopCausalSoftmax": [D, c_void_p, c_uint64, c_void_p, c_void_p],
@@ -187,6 +190,19 @@ class AddOp(_Op):
         super().destroy()
 
 
+class RearrangeOp(_Op):
+    """dst[...] = src[...] between two views of equal shape and dtype (reference operatorspy/tests/rearrange.py)."""
+    _destroy = "infiniopDestroyRearrangeDescriptor"
+
+    def __init__(self, lib, handle, dst, src):
+        super().__init__(lib, handle)
+        dt, st = self._t(dst), self._t(src)
+        check_error(lib.infiniopCreateRearrangeDescriptor(handle, ctypes.byref(self.desc), dt.descriptor, st.descriptor))
+
+    def __call__(self, dst, src, stream=None):
+        check_error(self.lib.infiniopRearrange(self.desc, dst.data_ptr(), src.data_ptr(), _stream_ptr(stream)))
+
+
 class CausalSoftmaxOp(_Op):
     _destroy, _wsize = "infiniopDestroyCausalSoftmaxDescriptor", "infiniopGetCausalSoftmaxWorkspaceSize"
 
@@ -269,6 +285,11 @@ def swiglu(lib, handle, c, a, b, stream=None):
 def add(lib, handle, c, a, b, stream=None):
     with AddOp(lib, handle, c, a, b) as op:
         op(c, a, b, stream)
+
+
+def rearrange(lib, handle, dst, src, stream=None):
+    with RearrangeOp(lib, handle, dst, src) as op:
+        op(dst, src, stream)
 
 
 def causal_softmax(lib, handle, y, stream=None):

@@ -49,6 +49,7 @@ def lib():
         L.oracle_rope_f16.argtypes = [vp, vp, vp, vp, u64, u64, u64, i64, i64]
         L.oracle_swiglu_f16.argtypes = [vp, vp, vp, u64, u64, i64, i64, i64]
         L.oracle_add.argtypes = [vp, vp, vp, ci, u64, vp, vp, vp]
+        L.oracle_rearrange.argtypes = [vp, vp, u64, u64, vp, vp, vp]
         L.oracle_causal_softmax_f16.argtypes = [vp, u64, u64, u64, i64, i64, i64]
         L.oracle_random_sample_f16.argtypes = [vp, vp, vp, ci, cf, cf, ci, cf]
         L.oracle_random_sample_workspace.argtypes, L.oracle_random_sample_workspace.restype = [ci], u64
@@ -153,6 +154,20 @@ def add(a, b):
     lib().oracle_add(_ptr(out), _ptr(a), _ptr(b), int(is_f16), nd, ctypes.addressof(cshape),
                      ctypes.addressof(sa), ctypes.addressof(sb))
     return out
+
+
+def rearrange(dst, src):
+    """dst[...] = src[...]: numpy views of equal shape and itemsize with unit innermost stride (the arrays' own
+    strides are used, so pass the strided views themselves).  src/ops/rearrange/cpu/rearrange_cpu.cc:70-100."""
+    assert dst.shape == src.shape and dst.itemsize == src.itemsize and dst.ndim >= 1
+    nd = dst.ndim
+    sd, ss = _elem_strides(dst), _elem_strides(src)
+    assert sd[-1] == 1 and ss[-1] == 1
+    cshape = (ctypes.c_uint64 * nd)(*dst.shape)
+    csd, css = (ctypes.c_int64 * nd)(*sd), (ctypes.c_int64 * nd)(*ss)
+    lib().oracle_rearrange(dst.ctypes.data, src.ctypes.data, dst.itemsize, nd, ctypes.addressof(cshape),
+                           ctypes.addressof(csd), ctypes.addressof(css))
+    return dst
 
 
 def causal_softmax(y):

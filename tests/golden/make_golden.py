@@ -93,6 +93,22 @@ def main():
     out["rs_rows"] = np.concatenate(rs_rows)
     out["rs_idx"] = np.array(rs_idx, np.int64)
 
+    # rearrange (two of the reference's own cases, reference operatorspy/tests/rearrange.py:111-112): the
+    # source view's whole storage, and the destination storage the reference leaves (gaps stay zero)
+    from operators_b200 import rearrange_tensor
+
+    for tag, shape, s_src, s_dst in (("a", (2, 4, 32), None, (256, 64, 1)), ("b", (32, 6, 64), (64, 2560, 1), None)):
+        x = torch.rand(shape, generator=g).half()
+        y = torch.zeros(shape, dtype=torch.float16)
+        if s_src is not None:
+            x = rearrange_tensor(x, s_src)
+        if s_dst is not None:
+            y = rearrange_tensor(y, s_dst)
+        ops.rearrange(lib, h, y, x)
+        storage = lambda t: torch.as_strided(t, (sum(st * (sz - 1) for st, sz in zip(t.stride(), t.shape)) + 1,), (1,))
+        out["rearrange_src_" + tag], out["rearrange_dst_" + tag] = bits(storage(x)), bits(storage(y))
+        out["rearrange_meta_" + tag] = np.array([shape, x.stride(), y.stride()], np.int64)
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "hot_path_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

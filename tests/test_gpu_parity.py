@@ -421,3 +421,66 @@ def test_staged_pipeline_host_buffers(oracle, cuda_lib):
     pipe.run()
     pipe.synchronize()
     assert np.array_equal(t_out.numpy().view(np.uint16), want_t.view(np.uint16))
+
+
+# ---- rearrange -------------------------------------------------------------------
+REARRANGE_GPU_CASES = [
+    # the reference's own cases (reference operatorspy/tests/rearrange.py:109-117)
+    (((2, 4, 32), None), ((2, 4, 32), (256, 64, 1)), torch.float16),
+    (((32, 6, 64), (64, 2560, 1)), ((32, 6, 64), None), torch.float16),
+    (((4, 6, 64), (64, 2560, 1)), ((4, 6, 64), (131072, 64, 1)), torch.float16),
+    (((1, 32, 64), (2048, 64, 1)), ((1, 32, 64), (2048, 64, 1)), torch.float16),
+    (((32, 1, 64), (64, 2560, 1)), ((32, 1, 64), (64, 64, 1)), torch.float16),
+    (((4, 1, 64), (64, 2560, 1)), ((4, 1, 64), (64, 11264, 1)), torch.float16),
+    # other ranks, element sizes and alignments
+    (((77,), None), ((77,), None), torch.float16),
+    (((5, 33), (40, 1)), ((5, 33), None), torch.float32),
+    (((3, 7), (9, 1)), ((3, 7), (11, 1)), torch.uint8),
+    (((2, 3, 4, 8), None), ((2, 3, 4, 8), (200, 50, 10, 1)), torch.float16),
+    (((2, 3, 4, 5, 6), (1000, 300, 70, 12, 1)), ((2, 3, 4, 5, 6), None), torch.float64),
+    # KV-cache write: 32 heads x 128 of 64 new tokens into a [heads, max_seq, 128] cache, and a decode-sized q
+    (((64, 32, 128), None), ((64, 32, 128), (128, 4096 * 128, 1)), torch.float16),
+    (((1024, 32, 128), (128, 1024 * 128, 1)), ((1024, 32, 128), None), torch.float16),
+]
+
+
+@pytest.mark.parametrize("src_spec,dst_spec,dtype", REARRANGE_GPU_CASES)
+def test_rearrange(oracle, cuda_lib, src_spec, dst_spec, dtype):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(9)
+    x = (torch.rand(src_spec[0], generator=g) * 200).to(dtype)
+    if src_spec[1] is not None:
+        x = rearrange_tensor(x, src_spec[1])
+    make_dst = lambda: (torch.full(dst_spec[0], 7, dtype=dtype) if dst_spec[1] is None
+                        else rearrange_tensor(torch.full(dst_spec[0], 7, dtype=dtype), dst_spec[1]))
+    want = make_dst()
+    oracle.rearrange(want.numpy(), x.numpy())
+    storage = lambda t: torch.as_strided(t, (sum(st * (sz - 1) for st, sz in zip(t.stride(), t.shape)) + 1,), (1,))
+    xd_store, yd_store = storage(x).to(DEV), storage(make_dst()).to(DEV)
+    xd = torch.as_strided(xd_store, x.shape, x.stride())
+    yd = torch.as_strided(yd_store, want.shape, want.stride())
+    ops.rearrange(lib, handle, yd, xd)
+    torch.cuda.synchronize()
+    # the whole destination storage: the copied rows and the untouched gaps between them
+    assert torch.equal(yd_store.cpu(), storage(want))
+
+
+def test_rearrange_unaligned_base_and_status(cuda_lib):
+    lib, handle = cuda_lib
+    src = torch.arange(4 * 64 + 1, dtype=torch.float16, device=DEV)
+    dst = torch.zeros(4 * 80 + 1, dtype=torch.float16, device=DEV)
+    xs, yd = torch.as_strided(src, (4, 64), (64, 1), 1), torch.as_strided(dst, (4, 64), (80, 1), 1)
+    ops.rearrange(lib, handle, yd, xs)
+    torch.cuda.synchronize()
+    assert torch.equal(yd.cpu(), xs.cpu()) and dst[0].item() == 0 and dst[65:81].abs().sum().item() == 0
+    bad = [
+        (torch.zeros((4, 8), dtype=torch.float16, device=DEV), torch.zeros((4, 8), dtype=torch.float32, device=DEV), 3),
+        (torch.zeros((4, 8), dtype=torch.float16, device=DEV), torch.zeros((4, 9), dtype=torch.float16, device=DEV), 4),
+        (torch.zeros((4, 8), dtype=torch.float16, device=DEV), torch.zeros((2, 4, 8), dtype=torch.float16, device=DEV), 4),
+        (torch.zeros((4, 8), dtype=torch.float16, device=DEV),
+         torch.as_strided(torch.zeros(64, dtype=torch.float16, device=DEV), (4, 8), (16, 2)), 5),
+    ]
+    for d, s, code in bad:
+        with pytest.raises(Exception) as e:
+            ops.rearrange(lib, handle, d, s)
+        assert str(code) in str(e.value)

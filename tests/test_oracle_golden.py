@@ -35,6 +35,16 @@ def test_add(oracle):
     assert np.array_equal(got.view(np.uint32), G["add32_c"].view(np.uint32))
 
 
+def test_rearrange(oracle):
+    for tag in ("a", "b"):
+        shape, s_src, s_dst = (tuple(int(v) for v in row) for row in G["rearrange_meta_" + tag])
+        src_store = G["rearrange_src_" + tag].copy()
+        dst_store = np.zeros_like(G["rearrange_dst_" + tag])
+        view = lambda store, strides: np.lib.stride_tricks.as_strided(store, shape, tuple(2 * st for st in strides))
+        oracle.rearrange(view(dst_store, s_dst), view(src_store, s_src))
+        assert np.array_equal(dst_store, G["rearrange_dst_" + tag]), tag
+
+
 def test_causal_softmax(oracle):
     y = G["softmax_in"].copy()
     oracle.causal_softmax(y)

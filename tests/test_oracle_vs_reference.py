@@ -10,6 +10,7 @@ import pytest
 import torch
 
 from operators_b200 import ops
+from operators_b200.utils import rearrange_tensor
 
 
 def _bits(t):
@@ -87,6 +88,36 @@ def test_add(oracle, ref_cpu, shapes, dtype):
         assert np.array_equal(mine.view(np.uint16).reshape(cs), _bits(c).reshape(cs))
     else:
         assert np.array_equal(mine.reshape(cs), c.numpy())
+
+
+# the reference's own cases (reference operatorspy/tests/rearrange.py:109-117) plus 1-D, 2-D, 4-D and fp32
+REARRANGE_CASES = [
+    (((2, 4, 32), None), ((2, 4, 32), (256, 64, 1)), torch.float16),
+    (((32, 6, 64), (64, 2560, 1)), ((32, 6, 64), None), torch.float16),
+    (((4, 6, 64), (64, 2560, 1)), ((4, 6, 64), (131072, 64, 1)), torch.float16),
+    (((1, 32, 64), (2048, 64, 1)), ((1, 32, 64), (2048, 64, 1)), torch.float16),
+    (((32, 1, 64), (64, 2560, 1)), ((32, 1, 64), (64, 64, 1)), torch.float16),
+    (((4, 1, 64), (64, 2560, 1)), ((4, 1, 64), (64, 11264, 1)), torch.float16),
+    (((77,), None), ((77,), None), torch.float16),
+    (((5, 33), (40, 1)), ((5, 33), None), torch.float32),
+    (((2, 3, 4, 8), None), ((2, 3, 4, 8), None), torch.float16),
+]
+
+
+@pytest.mark.parametrize("src_spec,dst_spec,dtype", REARRANGE_CASES)
+def test_rearrange(oracle, ref_cpu, src_spec, dst_spec, dtype):
+    lib, handle = ref_cpu
+    g = torch.Generator().manual_seed(9)
+    x = torch.rand(src_spec[0], generator=g).to(dtype)
+    y = torch.zeros(dst_spec[0], dtype=dtype)
+    if src_spec[1] is not None:
+        x = rearrange_tensor(x, src_spec[1])
+    if dst_spec[1] is not None:
+        y = rearrange_tensor(y, dst_spec[1])
+    y2 = y.clone() if dst_spec[1] is None else rearrange_tensor(torch.zeros(dst_spec[0], dtype=dtype), dst_spec[1])
+    ops.rearrange(lib, handle, y, x)
+    oracle.rearrange(y2.numpy(), x.numpy())
+    assert torch.equal(y, x) and torch.equal(y2, y)
 
 
 @pytest.mark.parametrize("shape", [(32, 20, 512), (5, 64), (2, 7, 7), (3, 1, 9)])
