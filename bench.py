@@ -259,6 +259,26 @@ def run_b200(args):
             fn(sptr)
     barrier()
 
+    # One step captured into a CUDA graph (the entry points neither allocate nor synchronise, so they can be
+    # captured as they are); the timed region replays it K times.  Plain launches if capture is unavailable.
+    graph = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(stream)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _, fn in calls:
+                    fn(torch.cuda.current_stream().cuda_stream)
+            stream.wait_stream(side)
+            g.replay()
+            torch.cuda.synchronize()
+            graph = g
+        except Exception as exc:  # noqa: BLE001
+            print("bench: CUDA graph capture failed (%s); timing plain launches" % exc, file=sys.stderr)
+            torch.cuda.synchronize()
+    barrier()
+
     # ---- timed region: exactly K steps between two device events, nothing else on the stream ----
     clocks = ClockSampler(local)
     clocks.start()
@@ -266,11 +286,13 @@ def run_b200(args):
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_begin.record(stream)
     for k in range(args.steps):
-        for _, fn in calls:
-            fn(sptr)
+        if graph is not None:
+            graph.replay()
+        else:
+            for _, fn in calls:
+                fn(sptr)
     t_end.record(stream)
     barrier()
-    clk = clocks.stop()
     ms_per_step = t_begin.elapsed_time(t_end) / args.steps
 
     # ---- the same K steps again with an event after every operator: the per-operator breakdown ----
@@ -283,6 +305,7 @@ def run_b200(args):
             fn(sptr)
             ev[k][i + 1].record(stream)
     barrier()
+    clk = clocks.stop()  # sampled over both passes: the same kernels under the same load
     per_op_ms = {name: sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(args.steps)) / args.steps
                  for i, (name, _) in enumerate(calls)}
 
@@ -384,7 +407,9 @@ def run_b200(args):
                                "random_sample[64,128256] T0.8 k50 p0.9",
                    "bytes_per_step": step_bytes, "sharding": "rows per GPU fixed (weak), no collective",
                    "l2": "step working set 1.25 GB > 126 MB L2; every operator's buffers were last touched a full step earlier",
-                   "random_sample": "batched extension entry, one launch for 64 rows"},
+                   "random_sample": "batched extension entry, one launch for 64 rows",
+                   "launch": ("one step captured in a CUDA graph, replayed K times" if graph is not None
+                              else "plain launches on one stream")},
         "ops": ops_out,
         "sample_tokens_per_s": ops_out["random_sample"]["tokens_per_s"],
         "e2e": {"value": round(step_bytes * world / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
@@ -556,6 +581,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
+    ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of a CUDA graph of the step")
     ap.add_argument("--only", choices=OPS, help="launch a single operator at its configuration (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
