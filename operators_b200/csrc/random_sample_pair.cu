@@ -1045,10 +1045,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                     float arg = fmaf(__fsub_rn(v, M), A, shift);
                     if (partial && gpos0 + e < pos) arg = -1000.f;// already in the running sum
                     const float z = fast_exp2(arg);
-                    const float fz = floorf(z);
+                    // floor(z) without the conversion unit (ex2 already keeps it busy): adding 2^23 rounding
+                    // down leaves floor(z) in the mantissa; z beyond 2^22 is never "sure" anyway
+                    const float t23 = __fadd_rd(fminf(z, 4194304.0f), 8388608.0f);
+                    const float fz = t23 - 8388608.0f;
                     // sure when z keeps z * band away from the integers on both sides (never for z >= 0.5 / band)
                     if (fabsf(z - fz - 0.5f) <= fmaf(-z, band, 0.5f)) {
-                        const uint32_t f = (uint32_t) fz;
+                        const uint32_t f = __float_as_uint(t23) & 0x7FFFFFu;
                         F += f;
                         Bp += ((f & 15u) * 0x00204081u) & 0x01010101u;// bit i of f -> byte i
                     } else {
