@@ -206,8 +206,19 @@ struct WarpVals {
     }
     // Key of the k-th largest value (with multiplicity); 0x0400 (the key of -inf) when fewer than k
     // values lie above -inf.  Four-way search: three thresholds per step, eight steps.
-    __device__ __forceinline__ uint32_t kth_largest(int k) const {
-        uint32_t lo = 0x0400u, hi = 0xFC00u;// keys of -inf and +inf
+    __device__ __forceinline__ uint32_t kth_largest(int k, uint32_t lo_hint) const {
+        // the search runs between the smallest value (or a bound the caller knows to have k values at or
+        // above it) and the largest one: a few hundred to a few thousand keys instead of all 63488
+        __half2 mn2 = h2_of(w[0]), mx2 = mn2;
+#pragma unroll
+        for (int r = 1; r < NW; ++r) {
+            mn2 = __hmin2(mn2, h2_of(w[r]));
+            mx2 = __hmax2(mx2, h2_of(w[r]));
+        }
+        const uint32_t kmin = key_of(__half_as_ushort(__hmin(__low2half(mn2), __high2half(mn2))));
+        const uint32_t kmax = key_of(__half_as_ushort(__hmax(__low2half(mx2), __high2half(mx2))));
+        uint32_t lo = max(max(__reduce_min_sync(0xffffffffu, kmin), lo_hint), 0x0400u);
+        uint32_t hi = max(__reduce_max_sync(0xffffffffu, kmax), lo);
         while (lo < hi) {
             const uint32_t m2 = (lo + hi + 1) >> 1;// lo < m2 <= hi
             const uint32_t m1 = (lo + m2) >> 1;    // lo <= m1 < m2
@@ -247,12 +258,12 @@ struct WarpVals {
 };
 
 // Key of the k-th largest of up to 256 fp16 values (n_vec8 vectors of 8 at p); with st, also the k
-// largest keys into st[0, k).  One warp; one copy of the code for all the warps that call it.
-__device__ __noinline__ uint32_t kth_largest_256(const uint16_t *p, int n_vec8, int k, uint32_t *st) {
+// largest keys into st[0, k).  lo_hint: a key known to have at least k values at or above it (or 0).  One warp; one copy of the code for all the warps that call it.
+__device__ __noinline__ uint32_t kth_largest_256(const uint16_t *p, int n_vec8, int k, uint32_t *st, uint32_t lo_hint) {
     const int lane = threadIdx.x & 31;
     WarpVals<4> v;
     v.load(p, n_vec8, lane);
-    const uint32_t tau = v.kth_largest(k);
+    const uint32_t tau = v.kth_largest(k, lo_hint);
     if (st != nullptr) v.k_largest(tau, k, st, lane);
     return tau;
 }
@@ -494,12 +505,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         }
         __syncthreads();
         if (warp < kBounds - kDirect && (leader || warp == kBounds - kDirect - 1)) {
-            const uint32_t kth = kth_largest_256(xs + warp * 256, warp == 0 ? 8 : warp == 1 ? 16 : 32, k, nullptr);
+            const uint32_t kth = kth_largest_256(xs + warp * 256, warp == 0 ? 8 : warp == 1 ? 16 : 32, k, nullptr, 0u);
             if (lane == 0) ax.LB[kDirect + warp] = kth <= 0x0400u ? 1u : kth;// fewer than k groups hold data: everything
         } else if (leader && warp >= kBounds - kDirect && warp < kBounds && (uint32_t) k < n &&
                    need_state(warp - (kBounds - kDirect))) {
             const int b = warp - (kBounds - kDirect);
-            const uint32_t tau = kth_largest_256(raw, (int) (kBoundPos[b] / 8u), k, ax.state[b + 1]);
+            const uint32_t tau = kth_largest_256(raw, (int) (kBoundPos[b] / 8u), k, ax.state[b + 1], 0u);
             if (lane == 0) ax.seg_tau[b + 1] = tau;
         } else if (leader && warp == kBounds && (uint32_t) k < n) {// the k-th largest of the first k elements
             MinBuf fb;
@@ -693,7 +704,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             if (fill > 256) {
                 if (lane == 0) ax.state_ovf = 1;
             } else {
-                const uint32_t tau = kth_largest_256(sc, 32, k, ax.state[warp + 1]);
+                const uint32_t tau = kth_largest_256(sc, 32, k, ax.state[warp + 1], lb);
                 if (lane == 0) ax.seg_tau[warp + 1] = tau;
             }
         }
