@@ -9,18 +9,23 @@
 //
 //  * The row is read from HBM exactly once and kept in shared memory as the
 //    fp16 bit patterns it came as: the leader CTA holds elements [0, 65536), the
-//    helper the rest.  Every later step (candidate search, record patches, block sums)
-//    runs on shared memory; the two CTAs exchange a few hundred bytes through
-//    distributed shared memory and meet at hardware cluster barriers (no
-//    flag spinning anywhere).
+//    helper the rest.  Every later step runs on shared memory; the two CTAs
+//    exchange lists, thresholds and block sums through distributed shared
+//    memory and meet at hardware cluster barriers (no flag spinning anywhere).
+//  * The serial parts are cut into pieces that run side by side.  The record
+//    chain is split into segments that end at 128, 256, ..., 65536 (and the
+//    helper half); the k largest keys at each boundary come from a selection
+//    over about 2k values (lower bounds from maxima of thread groups decide
+//    which values), one warp per boundary; one ordered list per half, built by
+//    a single scan, feeds the top-k candidates, those selections and the records.
 //  * The denominator is formed for FOUR binades of the running sum at once:
 //    per element z = 2*term/ulp0 comes from the special-function unit
 //    (ex2.approx), floor(z) gives round-to-nearest(term/ulp_d) for d = 0..3 with
 //    shifts, and only elements whose z lies within the approximation's error
 //    band of an integer (or that are very large) are re-evaluated exactly with
 //    a double-precision exp, densely, by the whole CTA.  The walk over the
-//    256-element block sums switches level when the running sum carries into
-//    the next binade, after replaying that one block with real fp32 additions.
+//    256-element block sums looks at all of them at once and replays, with real
+//    fp32 additions, each block in which the running sum may change binade.
 #include "common.cuh"
 #include "random_sample.cuh"
 #include "random_sample_device.cuh"
@@ -421,17 +426,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         }
         ++stamp_i;
     };
-#ifdef RS_TILE_STAMPS
-    int sub_i = 0;
-#define SUBSTAMP()                                                                                            \
-    do {                                                                                                      \
-        if (a.debug && leader && tid == 0 && sub_i < 9)                                                       \
-            a.debug[(int64_t) row * kDebugStride + 135 + sub_i] = (float) (clock64() - t_entry);              \
-        ++sub_i;                                                                                              \
-    } while (0)
-#else
-#define SUBSTAMP() do {} while (0)
-#endif
 
     // ---- P1: this CTA's half of the row -> shared memory; per-thread maxima --------------
     const bool in_aligned = (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
@@ -777,7 +771,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 ax.rl.cnt = cnt_r;
             }
             __syncthreads();
-            SUBSTAMP();// s0: lists merged
             // Rank every candidate: `greater` keys above it, `same` keys equal to it.
             // A key that occurs once simply sits behind all larger keys.  Equal keys
             // form a group that behaves like a queue under the reference's insertion
@@ -809,7 +802,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 }
             }
             __syncthreads();
-            SUBSTAMP();// s1: ranks counted
             for (int g = warp; g < ax.tie_groups; g += kWarps) {// warp-uniform replay of one group
                 const uint32_t gkey = ax.tie_key[g], cap = ax.tie_same[g];
                 uint16_t *q = ax.gbuf + ax.tie_greater[g];// this group's slots: [greater, greater + same)
@@ -909,7 +901,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             ax.top_idx[lane + 32] = tb.i1;
         }
         __syncthreads();
-        SUBSTAMP();// s2: top-k placed
         if (warp < 2) {// exact terms of the top-k, one per thread
             const int i = tid;
             if (i < k) ax.top_term[i] = term_exact(val_of(ax.top_key[i]), val_of(ax.top_key[0]), T);
@@ -1092,7 +1083,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             }
         }
         __syncthreads();
-        SUBSTAMP();// s3: block sums (approximate path)
         {// exact re-evaluation of the uncertain elements, densely
             const int cnt = min(ax.unc_cnt, kUncCap);
             unsure += ax.unc_cnt;
@@ -1110,9 +1100,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 peer_ax->tie[g] = ax.tie[g];
             }
         }
-        SUBSTAMP();// s4: exact path done
         cluster.sync();// CS6
-        SUBSTAMP();// s5: after barrier
         if (leader) {
             // The walk over the block sums; where the running sum may change binade (or a block holds a
             // half-way case) the block is replayed with real fp32 additions: the CTA evaluates its 256
@@ -1224,7 +1212,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 }
             }
         }
-        SUBSTAMP();// s6: walk done
         __syncthreads();
         cluster.sync();// CS7
     }
