@@ -484,3 +484,57 @@ def test_rearrange_unaligned_base_and_status(cuda_lib):
         with pytest.raises(Exception) as e:
             ops.rearrange(lib, handle, d, s)
         assert str(code) in str(e.value)
+
+
+# ---- stream capture ------------------------------------------------------------------
+def test_entry_points_capture_into_a_cuda_graph(oracle, cuda_lib):
+    """bench.py times a CUDA graph of the step: the compute entry points must neither allocate nor
+    synchronise.  SwiGLU, Add, RoPE, causal softmax and batched sampling are captured on a side stream
+    (after one eager call each, which performs the one-time per-device kernel attribute set-up), the graph is
+    replayed on fresh inputs, and the results are those of the oracle."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(123)
+    a = torch.randn((64, 256), generator=g).half()
+    b = torch.randn((64, 256), generator=g).half()
+    t = torch.randn((40, 8, 64), generator=g).half()
+    pos = torch.arange(40, dtype=torch.int64)
+    sin, cos = ops.sin_cos_table(40, 64)
+    y = (torch.randn((3, 16, 64), generator=g) * 2).half()
+    logits = (torch.randn((4, 5000), generator=g) * 3).half()
+    u = torch.rand(4, generator=g)
+    ad, bd, td, yd, ld, ud = (x.to(DEV) for x in (a, b, t, y, logits, u))
+    posd, sind, cosd = pos.to(DEV), sin.to(DEV), cos.to(DEV)
+    cd, sd = torch.zeros_like(ad), torch.zeros_like(ad)
+    res = torch.zeros(4, dtype=torch.int64, device=DEV)
+    swi, add = ops.SwiGLUOp(lib, handle, sd, ad, bd), ops.AddOp(lib, handle, cd, ad, bd)
+    rope, sm = ops.RoPEOp(lib, handle, td, posd, sind, cosd), ops.CausalSoftmaxOp(lib, handle, yd)
+    rs = ops.RandomSampleOp(lib, handle, res[:1], ld[0])
+
+    def step(s):
+        swi(sd, ad, bd, s)
+        add(cd, ad, bd, s)
+        rope(td, posd, sind, cosd, s)
+        sm(yd, s)
+        rs.batch(res, ld, ud, 0.9, 20, 0.8, s)
+
+    step(None)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step(torch.cuda.current_stream().cuda_stream)
+    # fresh contents in the captured buffers, then two replays of the in-place operators' inputs
+    td.copy_(t.to(DEV))
+    yd.copy_(y.to(DEV))
+    cd.zero_(), sd.zero_(), res.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(cd).reshape(64, 256), oracle.add(a.numpy(), b.numpy()).view(np.uint16))
+    want_t = oracle.rope(t.numpy().copy(), pos.numpy().astype(np.uint64), sin.numpy(), cos.numpy())
+    assert np.array_equal(_bits(td).reshape(40, 8, 64), want_t.view(np.uint16))
+    got_s, want_s = sd.cpu().float().numpy(), oracle.swiglu(a.numpy(), b.numpy()).astype(np.float32)
+    assert np.allclose(got_s, want_s, atol=1e-3, rtol=1e-3)
+    got_y, want_y = yd.cpu().float().numpy(), oracle.causal_softmax(y.numpy().copy()).astype(np.float32)
+    assert np.allclose(got_y, want_y, atol=2e-3, rtol=2e-3)
+    for r in range(4):
+        assert int(res[r]) == oracle.random_sample(logits[r].numpy(), float(u[r]), 0.9, 20, 0.8)
