@@ -6,8 +6,9 @@
 // Arithmetic follows the CPU backend (src/ops/rms_norm/cpu/rms_norm_cpu.cc:
 // 63-85): fp32 sum of squares, the scale k = (ss/d + eps)^-1/2 and the product
 // k * x * w evaluated in DOUBLE, one rounding to fp32, then the reference's
-// truncating fp32 -> fp16 conversion.  The only departure is the order of the
-// fp32 sum of squares (tree instead of sequential).
+// truncating fp32 -> fp16 conversion.  Departures: the order of the fp32 sum
+// of squares (tree instead of sequential), and in the register kernel the
+// product is formed in two-float arithmetic on the fp32 pipe (see rms_prod).
 //
 // HBM-bound, 4 bytes per element.  A row lives in registers between the
 // reduction and the scaling pass, so x is read from HBM exactly once: each
@@ -49,6 +50,31 @@ __device__ __forceinline__ uint16_t rms_out(double k, uint16_t x, double w) {
     return f32_to_f16_ref(__double2float_rn(__dmul_rn(__dmul_rn(k, h2d(x)), w)));
 }
 
+// The same product on the fp32 pipe (double conversions and multiplies run at a fraction of the fp32 rate
+// and would bound the kernel on long inputs): k = k_hi + k_lo as two floats, x * w = p + pe with pe the
+// exact residual of the fp32 product (zero for an fp16 weight: 11 + 11 significant bits), and
+//   k * x * w = k_hi * p + (k_hi * pe + k_lo * p) + O(2^-48)
+// summed smallest first and rounded to fp32 once.  It differs from the double product rounded to fp32
+// only when that product lies within 2^-46 (relative) of an fp32 rounding boundary.
+struct ScaleF2 {
+    float hi, lo;
+};
+__device__ __forceinline__ ScaleF2 split_scale(double k) {
+    ScaleF2 s;
+    s.hi = __double2float_rn(k);
+    s.lo = __double2float_rn(k - (double) s.hi);
+    return s;
+}
+template<bool W_F16>
+__device__ __forceinline__ float rms_prod(ScaleF2 k, float x, float w) {
+    const float p = __fmul_rn(x, w);
+    const float t = __fmul_rn(k.hi, p);
+    float c = __fmaf_rn(k.hi, p, -t);// exact residual of k_hi * p
+    c = __fmaf_rn(k.lo, p, c);
+    if (!W_F16) c = __fmaf_rn(k.hi, __fmaf_rn(x, w, -p), c);
+    return __fadd_rn(t, c);
+}
+
 // VPT vectors (8 halves each) per thread; CTA_ROW: the whole CTA owns one row,
 // otherwise each warp owns one row.
 template<int VPT, bool W_F16, bool CTA_ROW>
@@ -87,26 +113,32 @@ __global__ void rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void 
             }
         }
         ss = CTA_ROW ? cta_reduce<false>(ss, red) : warp_sum(ss);
-        const double k = rms_scale(ss, d, eps);
+        const ScaleF2 k = split_scale(rms_scale(ss, d, eps));
         uint16_t *yr = y + (int64_t) row * stride_y;
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
             const uint32_t j = t + u * group;
             if (j < vecs) {
-                const uint16_t *hx = reinterpret_cast<const uint16_t *>(&v[u]);
+                const uint32_t *px = reinterpret_cast<const uint32_t *>(&v[u]);
                 uint4 out;
-                uint16_t *ho = reinterpret_cast<uint16_t *>(&out);
+                uint32_t *po = reinterpret_cast<uint32_t *>(&out);
                 if (W_F16) {
                     const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(w) + j);
-                    const uint16_t *hw = reinterpret_cast<const uint16_t *>(&wv);
+                    const uint32_t *pw = reinterpret_cast<const uint32_t *>(&wv);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) ho[e] = rms_out(k, hx[e], h2d(hw[e]));
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 xf = unpack2(px[e]), wf = unpack2(pw[e]);
+                        po[e] = pack2_ref(rms_prod<true>(k, xf.x, wf.x), rms_prod<true>(k, xf.y, wf.y));
+                    }
                 } else {
                     const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * j);
                     const float4 w1 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * j + 1);
                     const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) ho[e] = rms_out(k, hx[e], (double) wf[e]);
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 xf = unpack2(px[e]);
+                        po[e] = pack2_ref(rms_prod<false>(k, xf.x, wf[2 * e]), rms_prod<false>(k, xf.y, wf[2 * e + 1]));
+                    }
                 }
                 st_stream(yr + (uint64_t) j * 8, out);
             }
