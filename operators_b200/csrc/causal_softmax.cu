@@ -15,6 +15,7 @@
 // once; masked tails are never read.  A row lives in registers between the
 // three steps (max, exp+sum, scale), owned by one warp or one CTA.
 #include "common.cuh"
+#include "fastdiv.h"
 
 #include <new>
 
@@ -45,8 +46,8 @@ __device__ __forceinline__ uint64_t visible_cols(uint64_t i, uint64_t seq_len, u
 // evaluation instead; measured, that is the faster of the two on B200.)
 template<int VPT, bool CTA_ROW>
 __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total,
-                                           uint32_t vecs, int64_t stride_b, int64_t stride_i) {
-    __shared__ float red[32];
+                                           uint32_t vecs, int64_t stride_b, int64_t stride_i, FastDiv seq_div) {
+    __shared__ float red_m[32], red_s[32];// one slot array per reduction of a row: one barrier each
     const int lane = threadIdx.x & 31;
     const uint32_t group = CTA_ROW ? blockDim.x : 32;
     const uint32_t t = CTA_ROW ? threadIdx.x : lane;
@@ -56,7 +57,14 @@ __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t 
     constexpr uint32_t kNegInf2 = 0xFC00FC00u;// two fp16 -inf
 
     for (uint64_t row = row0; row < rows; row += row_step) {
-        const uint64_t b = row / seq_len, i = row - b * seq_len;
+        uint64_t b, i;
+        if (rows <= 0xFFFFFFFFull) {// the usual case: one multiply-high instead of a 64-bit division
+            uint32_t q, r;
+            seq_div.divmod((uint32_t) row, q, r);
+            b = q, i = r;
+        } else {
+            b = row / seq_len, i = row - b * seq_len;
+        }
         uint16_t *yr = y + (int64_t) b * stride_b + (int64_t) i * stride_i;
         const uint32_t vis = (uint32_t) visible_cols(i, seq_len, total);
 
@@ -83,7 +91,7 @@ __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t 
             for (int k = 0; k < 4; ++k) m2 = __hmax2(m2, *reinterpret_cast<const __half2 *>(&p[k]));
         }
         float m = fmaxf(__low2float(m2), __high2float(m2));
-        m = CTA_ROW ? cta_reduce<true>(m, red) : warp_max(m);
+        m = CTA_ROW ? cta_reduce_alt<true>(m, red_m) : warp_max(m);
         // exp(x - m) = 2^(x*log2e - m*log2e); the rounding of m*log2e is common to
         // the whole row and cancels in the quotient.
         const float mk = -m * kLog2e;
@@ -98,7 +106,7 @@ __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t 
                 s += fast_exp2(fmaf(f.y, kLog2e, mk));
             }
         }
-        s = CTA_ROW ? cta_reduce<false>(s, red) : warp_sum(s);
+        s = CTA_ROW ? cta_reduce_alt<false>(s, red_s) : warp_sum(s);
         const float r = __frcp_rn(s);
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
@@ -154,17 +162,18 @@ template<int VPT>
 void launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uint32_t vecs, uint16_t *y,
                  cudaStream_t st) {
     const uint64_t rows = d->batch * d->seq_len;
+    const FastDiv seq_div(d->seq_len <= 0xFFFFFFFFull && d->seq_len > 0 ? (uint32_t) d->seq_len : 1u);
     if (cta_row) {
         const uint64_t cap = 0x7FFFFFFFull;// one CTA per row; rows beyond 2^31 loop
         const uint32_t grid = (uint32_t) (rows < cap ? rows : cap);
         causal_softmax_regs_kernel<VPT, true>
-            <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i);
+            <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
     } else {
         const uint64_t ctas = (rows + 7) / 8;
         const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
         causal_softmax_regs_kernel<VPT, false>
-            <<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i);
+            <<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
     }
 }
 

@@ -149,4 +149,18 @@ __device__ __forceinline__ float cta_reduce(float v, float *slot) {
     return r;
 }
 
+// The same with a single barrier: the caller alternates between two slots (e.g. one for a row's maximum,
+// one for its sum), so a slot is written again only after a later barrier has been passed by every reader.
+template<bool IS_MAX>
+__device__ __forceinline__ float cta_reduce_alt(float v, float *slot) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = IS_MAX ? warp_max(v) : warp_sum(v);
+    if (nwarps == 1) return v;
+    if (lane == 0) slot[warp] = v;
+    __syncthreads();
+    float r = slot[0];
+    for (int w = 1; w < nwarps; ++w) r = IS_MAX ? fmaxf(r, slot[w]) : r + slot[w];
+    return r;
+}
+
 }// namespace b200

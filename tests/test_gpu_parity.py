@@ -59,7 +59,11 @@ def test_rms_norm(oracle, cuda_lib, shape, stride, w_dtype):
 @pytest.mark.parametrize("shape,strides", [((1, 32, 128), None), ((1, 32, 64), None), ((4, 1, 32), None),
                                            ((3, 32, 128), (8000, 200, 1)), ((64, 32, 128), None),
                                            ((5, 3, 6), None), ((5, 3, 6), (37, 7, 1)), ((7, 5, 96), None),
-                                           ((2, 2, 4096), None), ((9, 40, 128), (40 * 256, 256, 1))])
+                                           ((2, 2, 4096), None), ((9, 40, 128), (40 * 256, 256, 1)),
+                                           # bulk-copy pipeline: rings reused several times, ragged token counts,
+                                           # one token, more tokens than the pipeline takes (-> strided kernel)
+                                           ((9000, 8, 64), None), ((1187, 32, 128), None), ((33, 4, 256), None),
+                                           ((40000, 2, 32), None), ((300, 16, 8), None)])
 def test_rope(oracle, cuda_lib, shape, strides):
     lib, handle = cuda_lib
     g = torch.Generator().manual_seed(2)
