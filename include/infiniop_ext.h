@@ -29,8 +29,9 @@ INFINIOP_API infiniopStatus_t infiniopRandomSampleBatch(infiniopRandomSampleDesc
  * Same as infiniopRandomSampleBatch, additionally writing a per-row trace to
  * `trace` (device, 145 fp32 per row): [0] the fp32 softmax denominator,
  * [1..64] the selected top-k indices (as bit patterns), [65..128] their
- * truncated probabilities, [129..143] SM cycle counts at the kernel's phase
- * boundaries, [144] the number of passes the denominator took.  Used by the parity tests to compare intermediate
+ * truncated probabilities, [129..134] SM cycle counts at the kernel's phase
+ * boundaries, [141..143] (shared-memory kernel) blocks replayed on integers, elements settled by the exact path,
+ * blocks replayed in all, [144] the number of passes the denominator took.  Used by the parity tests to compare intermediate
  * values with the CPU oracle, not only the final index.
  */
 INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchTrace(infiniopRandomSampleDescriptor_t desc, void *workspace,

@@ -117,6 +117,7 @@ struct Aux {
     uint32_t walk_tot[kWalkWarps], walk_m[kWalkWarps];
     int walk_ev[kWalkWarps];
     float walk_s;
+    uint32_t tie_excl[kBlk], tie_c[kBlk];  // integer replay of a block: prefix and own contribution per element
     uint32_t C[kLevels][kMaxBlk];// integer block sums per binade level
     uint32_t tie[kMaxBlk];       // bit d: block holds an exact half-way case at level d
     uint32_t LB[kBounds];        // lower bound of the k-th largest key of the prefix that ends at boundary b
@@ -391,6 +392,23 @@ __device__ __noinline__ void exact_contrib(Aux &ax, uint32_t blk, float v, float
         if (sh > 0 && rem == half) ties |= 1u << d;
     }
     if (ties) atomicOr(&ax.tie[blk], ties);
+}
+
+// The same split for one level: what the term adds to the mantissa of a running sum whose ulp is
+// 2^(e0 + level - 150), and whether it lies exactly half-way (then the addition rounds to even).
+__device__ __forceinline__ void exact_at_level(float term, int e0, int level, uint32_t &c, bool &tie) {
+    const uint32_t tb = __float_as_uint(term);
+    int e_t = (int) ((tb >> 23) & 0xFFu);
+    uint32_t man = tb & 0x7FFFFFu;
+    if (e_t == 0) e_t = 1;
+    else man |= 0x800000u;
+    const int sh = e0 + level - e_t;
+    c = 0, tie = false;
+    if (man == 0 || sh >= 25) return;
+    const uint32_t rem = man & ((1u << sh) - 1u);
+    const uint32_t half = sh > 0 ? 1u << (sh - 1) : 0u;
+    c = (man >> sh) + ((sh > 0 && rem > half) ? 1u : 0u);
+    tie = sh > 0 && rem == half;
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomSampleArgs a) {
@@ -1007,7 +1025,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
 
     // ---- denominator rounds -------------------------------------------------------------
     const float A = kLog2e / T;
-    int rounds = 0, replays = 0, unsure = 0;
+    int rounds = 0, replays = 0, int_replays = 0, unsure = 0;
     for (int round = 0; round < kMaxRounds && !ax.mail.done; ++round) {
         ++rounds;
         const float s_base = ax.mail.s_base;
@@ -1160,6 +1178,65 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 const uint32_t eb = ax.walk_event;
                 if (eb == kNoEvent) break;
                 ++replays;
+                // A block that only holds half-way cases (the sum stays inside its binade whatever they round
+                // to) is replayed on integers: every element's contribution to the mantissa at this level
+                // (from the fast path where that is sure, from the exact term otherwise) is independent of the
+                // running value except for the half-way ones, which round to even; those are settled in index
+                // order from the prefix sums.  A block in which the sum may carry takes the fp32 replay below.
+                if (m + min(ax.C[level][eb], 1u << 25) + (uint32_t) kBlk < (1u << 24)) {
+                    ++int_replays;
+                    uint32_t c = 0;
+                    bool tie = false;
+                    if (tid < kBlk) {
+                        const uint16_t *blk = eb < nblk0 ? raw + eb * kBlk : peer_raw + (eb - nblk0) * kBlk;
+                        const uint32_t j = (eb < nblk0 ? eb * kBlk : (uint32_t) kHalfElems + (eb - nblk0) * kBlk) + tid;
+                        const uint16_t h = blk[tid];
+                        if (h != kPad && j >= pos) {
+                            const float v = f16_to_f32(h);
+                            const float z = fast_exp2(fmaf(__fsub_rn(v, M), A, shift));
+                            const float t23 = __fadd_rd(fminf(z, 4194304.0f), 8388608.0f);
+                            const float fz = t23 - 8388608.0f;
+                            if (fabsf(z - fz - 0.5f) <= fmaf(-z, band, 0.5f)) {// the same test as in the block sums
+                                c = ((__float_as_uint(t23) & 0x7FFFFFu) + (1u << level)) >> (level + 1);
+                            } else {
+                                exact_at_level(term_exact(v, M, T), e0, level, c, tie);
+                            }
+                        }
+                    }
+                    uint32_t incl = c;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) {
+                        const uint32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+                        if (lane >= o) incl += t;
+                    }
+                    const uint32_t tmask = __ballot_sync(0xffffffffu, tie);
+                    if (tid < kBlk) {
+                        ax.tie_excl[tid] = incl - c;
+                        ax.tie_c[tid] = c;
+                        if (lane == 31) ax.walk_tot[warp] = incl;
+                        if (lane == 0) ax.walk_ev[warp] = (int) tmask;
+                    }
+                    __syncthreads();
+                    if (tid == 0) {
+                        uint32_t run = m, adj = 0;// run: mantissa before the current warp's 32 elements, ties not counted
+                        for (int w = 0; w < kBlk / 32; ++w) {
+                            uint32_t tm = (uint32_t) ax.walk_ev[w];
+                            while (tm) {
+                                const int l = __ffs(tm) - 1;
+                                tm &= tm - 1;
+                                const int i = w * 32 + l;
+                                // exact value: before + c + 1/2; it rounds up when before + c is odd
+                                adj += (run + ax.tie_excl[i] + adj + ax.tie_c[i]) & 1u;
+                            }
+                            run += ax.walk_tot[w];
+                        }
+                        ax.walk_m[0] = run + adj;
+                    }
+                    __syncthreads();
+                    m = ax.walk_m[0];
+                    b0 = eb + 1;
+                    continue;
+                }
                 if (tid < kBlk) {
                     const uint16_t *blk = eb < nblk0 ? raw + eb * kBlk : peer_raw + (eb - nblk0) * kBlk;
                     const uint32_t j = (eb < nblk0 ? eb * kBlk : (uint32_t) kHalfElems + (eb - nblk0) * kBlk) + tid;
@@ -1233,6 +1310,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 dbg[129 + 15] = (float) rounds;
                 dbg[129 + 14] = (float) replays;
                 dbg[129 + 13] = (float) unsure;
+                dbg[129 + 12] = (float) int_replays;
             }
             pick_from_topk(ax.top_term, ax.top_idx, k, a.topp, random_val, a.result + (int64_t) row * a.result_stride);
         }
