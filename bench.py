@@ -224,6 +224,28 @@ def run_b200(args):
     lib = open_lib(os.path.join(ROOT, "operators_b200", "lib"))
     handle = create_handle(lib, DeviceEnum.DEVICE_CUDA, local)
 
+    if args.only == "rearrange":  # not part of the step: the permute on the way out of attention, for ncu captures
+        from operators_b200 import ops as _ops
+
+        src = torch.randn((ROPE_T, ROPE_H, ROPE_DH), device=dev).half()
+        dst = torch.as_strided(torch.empty(ROPE_T * ROPE_H * ROPE_DH, device=dev, dtype=torch.float16),
+                               (ROPE_T, ROPE_H, ROPE_DH), (ROPE_DH, ROPE_T * ROPE_DH, 1))  # [heads, tokens, dh] storage
+        op = _ops.RearrangeOp(lib, handle, dst, src)
+        for _ in range(args.warmup):
+            op(dst, src)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            op(dst, src)
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        nbytes = 2 * src.numel() * 2
+        print(json.dumps({"only": "rearrange", "shape": list(src.shape), "ms": round(ms, 5),
+                          "gbs": round(nbytes / ms / 1e6, 1),
+                          "note": "back-to-back launches of one operator; not a bench value"}))
+        return
     inputs = make_inputs(1000 + rank, only=args.only)
     step = DecodeStep(lib, handle, dev, inputs)
     calls = step.calls()
@@ -613,7 +635,8 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of a CUDA graph of the step")
-    ap.add_argument("--only", choices=OPS, help="launch a single operator at its configuration (for ncu captures)")
+    ap.add_argument("--only", choices=OPS + ["rearrange"],
+                    help="launch a single operator at its configuration (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
