@@ -36,7 +36,7 @@ struct RandomSampleArgs {
     float *debug;
 };
 
-// Shared-memory resident two-CTA form (random_sample_pair.cu): sampling branch, voc <= 131072.
+// Shared-memory resident cluster form (random_sample_pair.cu): sampling branch, voc <= 262144.
 bool random_sample_pair_supported(int voc);
 infiniopStatus_t random_sample_pair_launch(const RandomSampleArgs &args, int rows, cudaStream_t stream);
 

@@ -1,5 +1,6 @@
 // Random sample, shared-memory resident form: a thread-block cluster of two
-// CTAs owns one row of up to 131072 logits.
+// CTAs owns one row of up to 131072 logits, a cluster of four a row of up to
+// 262144 (the cluster size is a launch attribute; the kernel reads it).
 //
 // Same result as random_sample_kernel (random_sample.cu), i.e. the index the
 // reference CPU backend returns (src/ops/random_sample/cpu/random_sample.cc:
@@ -8,8 +9,8 @@
 // sum).  What differs is where the row lives and how the work is spread:
 //
 //  * The row is read from HBM exactly once and kept in shared memory as the
-//    fp16 bit patterns it came as: the leader CTA holds elements [0, 65536), the
-//    helper the rest.  Every later step runs on shared memory; the two CTAs
+//    fp16 bit patterns it came as: CTA r holds elements [65536 r, 65536 (r + 1));
+//    CTA 0 leads, the others help.  Every later step runs on shared memory; the two CTAs
 //    exchange lists, thresholds and block sums through distributed shared
 //    memory and meet at hardware cluster barriers (no flag spinning anywhere).
 //  * The serial parts are cut into pieces that run side by side.  The record
@@ -43,7 +44,8 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kBlk = 256;
 constexpr int kFlatCap = 1024;    // per-CTA ordered list (candidates, flagged records)
 constexpr int kHalfElems = 65536; // elements held by one CTA
-constexpr int kMaxBlk = 2 * kHalfElems / kBlk;
+constexpr int kMaxRanks = 4;       // CTAs per cluster: 2 up to 131072 logits, 4 up to 262144
+constexpr int kMaxBlk = kMaxRanks * kHalfElems / kBlk;
 constexpr int kLevels = 4;
 constexpr int kUncCap = 6144;
 constexpr int kMaxRounds = 6;     // 6 x 4 binades covers any sum of <= 2^17 terms <= 1
@@ -78,7 +80,7 @@ struct FlatList {
     uint16_t key[2 * kFlatCap];
     int cnt;      // own entries
     int overflow; // own entries did not fit
-    int peer_cnt; // leader: helper's entries
+    int peer_cnt[kMaxRanks - 1];// leader: entries of helper 1, 2, 3 (each in its own share of the upper slots)
     int peer_overflow;
     int wcnt[kWarps];          // entries found by each warp of the scan
     int seg_first[kBounds + 1];// leader: list position of the first entry of segment i; [kBounds] = count
@@ -92,8 +94,7 @@ struct RecList {
     int seg_first[kBounds + 1];// leader: position of the first entry of segment i; [kBounds] = count
 };
 struct Mail {// written by the other CTA of the pair (the leader also fills its own copy)
-    uint32_t L_peer;
-    uint32_t tau_mid;
+    uint32_t L_of[kMaxRanks];// every CTA's lower bound of the k-th largest key of its own part
     uint32_t mkey;
     float s_base;
     uint32_t pos_base;
@@ -411,26 +412,29 @@ __device__ __forceinline__ void exact_at_level(float term, int e0, int level, ui
     tie = sh > 0 && rem == half;
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomSampleArgs a) {
+__global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomSampleArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint16_t *raw = reinterpret_cast<uint16_t *>(smem_raw);// this CTA's half of the row, fp16 bit patterns
     Aux &ax = *reinterpret_cast<Aux *>(smem_raw + (size_t) kHalfElems * 2);
     cg::cluster_group cluster = cg::this_cluster();
-    const unsigned rank = cluster.block_rank();
+    // CTA `rank` of the cluster holds elements [rank * 65536, (rank + 1) * 65536) of the row; rank 0 leads.
+    const unsigned rank = cluster.block_rank(), R = cluster.num_blocks();
     const bool leader = rank == 0;
-    uint16_t *peer_raw = cluster.map_shared_rank(raw, rank ^ 1u);
-    Aux *peer_ax = cluster.map_shared_rank(&ax, rank ^ 1u);
+    // the same objects in another CTA of the cluster (one address-mapping instruction each time)
+    auto ax_of = [&](unsigned r) -> Aux * { return cluster.map_shared_rank(&ax, r); };
+    Aux *lead_ax = ax_of(0);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int row = blockIdx.x >> 1;
+    const int row = blockIdx.x / R;
     const uint32_t n = (uint32_t) a.voc;
-    const uint32_t n0 = min(n, (uint32_t) kHalfElems);           // leader's elements
-    const uint32_t my_base = leader ? 0u : (uint32_t) kHalfElems;// helper starts at 65536 (only used when n > 65536)
-    const uint32_t my_n = leader ? n0 : n - n0;
+    const uint32_t n0 = min(n, (uint32_t) kHalfElems);// leader's elements
+    const uint32_t my_base = rank * (uint32_t) kHalfElems;
+    const uint32_t my_n = n > my_base ? min(n - my_base, (uint32_t) kHalfElems) : 0u;
     const uint32_t my_nblk = (my_n + kBlk - 1) / kBlk;
     const uint32_t my_pad = my_nblk * kBlk;
     const uint32_t nblk0 = (n0 + kBlk - 1) / kBlk;
-    const uint32_t nblk = nblk0 + (n - n0 + kBlk - 1) / kBlk;
+    const uint32_t nblk = (n + kBlk - 1) / kBlk;// every part before the last is full: block g lives in CTA g / 256
+    const uint32_t ranks_used = (n + kHalfElems - 1) / kHalfElems;// CTAs that hold data
     const uint16_t *logits = a.logits + (int64_t) row * a.logits_stride + my_base;
     const float random_val = a.random_vals ? a.random_vals[row] : a.random_val;
     const float T = a.temperature;
@@ -443,6 +447,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             a.debug[(int64_t) row * kDebugStride + 129 + stamp_i] = (float) (clock64() - t_entry);
         }
         ++stamp_i;
+    };
+
+    auto block_ptr = [&](uint32_t g) -> const uint16_t * {
+        return cluster.map_shared_rank(raw, g >> 8) + (g & 255u) * kBlk;
     };
 
     // ---- P1: this CTA's half of the row -> shared memory; per-thread maxima --------------
@@ -532,15 +540,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         __syncthreads();
     }
     const uint32_t L_mine = ax.LB[kBounds - 1];
+    if (tid < (int) R) ax_of((unsigned) tid)->mail.L_of[rank] = my_n > 0 ? L_mine : 0u;
     if (tid == 0) {
-        peer_ax->mail.L_peer = L_mine;
         ax.state_ovf = 0;
-        ax.fl.peer_cnt = 0;// the helper fills these in after the barrier
+        for (int h = 0; h < kMaxRanks - 1; ++h) ax.fl.peer_cnt[h] = 0;// the helpers fill these in after the barrier
         ax.fl.peer_overflow = 0;
     }
     cluster.sync();// CS1
     stamp();       // 0: row resident
-    const uint32_t L = max(max(L_mine, ax.mail.L_peer), 1u);
+    uint32_t L = 1u, L_before = 0u;// L_before: a lower bound of the k-th largest key of everything before this part
+    for (unsigned r = 0; r < R; ++r) {
+        L = max(L, ax.mail.L_of[r]);
+        if (r < rank) L_before = max(L_before, ax.mail.L_of[r]);
+    }
 
     // ---- P2: candidates (key >= L), ordered --------------------------------------------
     // Ordered list of the elements of this warp's piece [r0, r1) of the LOCAL half that lie above
@@ -642,22 +654,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         }
         __syncthreads();
     };
-    // Helper: hand this CTA's list to the leader (second half of the leader's arrays).
+    // Helpers: hand this CTA's list to the leader.  The upper half of the leader's arrays is divided evenly
+    // among the helpers, in rank (= index) order; a helper keeps its list within its share.
+    const int helper_cap = kFlatCap / (int) (R > 1 ? R - 1 : 1);
     auto ship_list = [&]() {
+        const int at = kFlatCap + (int) (rank - 1) * helper_cap;
         for (int i = tid; i < ax.fl.cnt; i += kThreads) {
-            peer_ax->fl.idx[kFlatCap + i] = ax.fl.idx[i];
-            peer_ax->fl.key[kFlatCap + i] = ax.fl.key[i];
+            lead_ax->fl.idx[at + i] = ax.fl.idx[i];
+            lead_ax->fl.key[at + i] = ax.fl.key[i];
         }
         if (tid == 0) {
-            peer_ax->fl.peer_cnt = ax.fl.cnt;
-            peer_ax->fl.peer_overflow = ax.fl.overflow;
+            lead_ax->fl.peer_cnt[rank - 1] = ax.fl.cnt;
+            if (ax.fl.overflow) lead_ax->fl.peer_overflow = 1;
         }
     };
-    // Helper half: equal spans of whole blocks per warp (at most 8), one threshold.
+    // Helper part: equal spans of whole blocks per warp (at most 8), one threshold.
     auto scan_helper = [&](uint32_t tk, bool strict) {
         const uint32_t span = ((my_nblk + kWarps - 1) / kWarps) * kBlk;
         const uint32_t r0 = min(warp * span, my_pad);
-        scan_ordered(r0, min(r0 + span, my_pad), 0u, tk, strict, kFlatCap);
+        scan_ordered(r0, min(r0 + span, my_pad), 0u, tk, strict, helper_cap);
     };
 
     // One ordered list per CTA serves three purposes, so a segment's threshold is the lowest of what they
@@ -676,8 +691,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         }
         scan_ordered(kScanR0[warp], kScanR0[warp + 1], 0u, thr, false, kFlatCap);
     } else {
-        // the leader's bound for its whole half is a lower bound of the k-th largest key where this half starts
-        scan_helper(want_records ? min(L, max(ax.mail.L_peer, 1u)) : L, false);
+        // the bounds of the parts before this one are lower bounds of the k-th largest key where this part starts
+        scan_helper(want_records ? min(L, max(L_before, 1u)) : L, false);
         ship_list();
     }
     cluster.sync();// CS2
@@ -688,7 +703,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
     float M = 0.f;
     bool list_ok = false;
     if (leader) {
-        const int cnt0 = ax.fl.cnt, cnt1 = ax.fl.peer_cnt;
+        const int cnt0 = ax.fl.cnt;
+        const int c_h0 = ax.fl.peer_cnt[0], c_h1 = ax.fl.peer_cnt[1], c_h2 = ax.fl.peer_cnt[2];
+        const int cnt1 = c_h0 + c_h1 + c_h2;// the helpers' entries, taken in rank order
         list_ok = !ax.fl.overflow && !ax.fl.peer_overflow;
         if (list_ok && (uint32_t) k < n && warp >= kDirect && warp < kBounds && need_state(warp)) {
             // Start states of the segments from 512 on, one warp per boundary: the k largest keys of
@@ -737,8 +754,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 rec = want_records && my_idx >= (uint32_t) k && my_key > ax.seg_tau[sg];
             }
             if (tid < cnt1) {
-                mv_idx = ax.fl.idx[kFlatCap + tid];
-                mv_key = ax.fl.key[kFlatCap + tid];
+                const int slot = tid < c_h0 ? kFlatCap + tid
+                                            : tid < c_h0 + c_h1 ? kFlatCap + helper_cap + (tid - c_h0)
+                                                                : kFlatCap + 2 * helper_cap + (tid - c_h0 - c_h1);
+                mv_idx = ax.fl.idx[slot];
+                mv_key = ax.fl.key[slot];
                 keep_h = mv_key >= L;
             }
             const uint32_t hit = __ballot_sync(0xffffffffu, keep), hit_r = __ballot_sync(0xffffffffu, rec);
@@ -887,8 +907,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             // more ties than the lists hold: stream the whole row through the warp-resident buffer
             TopBuf tb{0, 0, 0, 0};
             for (uint32_t b = 0; b < nblk; ++b) {
-                const uint16_t *blk = b < nblk0 ? raw + b * kBlk : peer_raw + (b - nblk0) * kBlk;
-                const uint32_t gbase = b < nblk0 ? b * kBlk : (uint32_t) kHalfElems + (b - nblk0) * kBlk;
+                const uint16_t *blk = block_ptr(b);
+                const uint32_t gbase = b * kBlk;
                 uint32_t w[4], kk[8];
                 lds_raw(blk + lane * 8, w);
 #pragma unroll
@@ -955,71 +975,82 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                 }
                 __syncthreads();
             }
-            if (n > n0 && tid < kSlots) peer_ax->state[kBounds][tid] = ax.state[kBounds][tid];
+            if (n > n0 && tid < kSlots) ax_of(1u)->state[kBounds][tid] = ax.state[kBounds][tid];// where part 1 starts
         }
-        if (tid == 0) {// hand the helper what it needs
-            peer_ax->seg_tau[kBounds] = ax.seg_tau[kBounds];
-            peer_ax->mail.mkey = ax.mail.mkey;
-            peer_ax->mail.s_base = ax.mail.s_base;
-            peer_ax->mail.pos_base = ax.mail.pos_base;
-            peer_ax->mail.done = ax.mail.done;
+        if (tid == 0 && R > 1) ax_of(1u)->seg_tau[kBounds] = ax.seg_tau[kBounds];
+        if (tid >= 1 && tid < (int) R) {// hand every helper what it needs
+            ax_of((unsigned) tid)->mail.mkey = ax.mail.mkey;
+            ax_of((unsigned) tid)->mail.s_base = ax.mail.s_base;
+            ax_of((unsigned) tid)->mail.pos_base = ax.mail.pos_base;
+            ax_of((unsigned) tid)->mail.done = ax.mail.done;
         }
     }
     cluster.sync();// CS3
-    stamp();       // 3: start states known on both sides
+    stamp();       // 3: start states known at the leader and the first helper
 
-    // ---- P4: records.  Leader: its segments in parallel, one warp each.  Helper: its half. ----
-    if (leader && list_ok && (uint32_t) k < n) {
-        if (warp < kBounds) {// segment i on warp i
-            const int sg = warp;
-            const uint32_t s_begin = sg == 0 ? (uint32_t) k : kBoundPos[sg - 1];
-            if (s_begin < n0) {
-                const int first = ax.rl.seg_first[sg], last = ax.rl.seg_first[sg + 1];
-                MinBuf sb;
-                if (sg == 0) minbuf_init(sb, lane, k, raw);
-                else minbuf_init_keys(sb, lane, k, ax.state[sg]);
-                replay_list(ax.rl.key + first, ax.rl.idx + first, last - first, raw, 0u, lane, sb);
+    // ---- P4: records.  Leader: its segments in parallel, one warp each.  Helpers: one after the other, ----
+    // each from the k largest keys its predecessor ends with (the leader's for the first helper), which it
+    // hands on in turn.  One cluster barrier per helper that holds data (at least one).
+    const unsigned p4_rounds = ranks_used > 2u ? ranks_used - 1u : 1u;
+    for (unsigned turn = 1; turn <= p4_rounds; ++turn) {
+        if (leader && turn == 1 && list_ok && (uint32_t) k < n) {
+            if (warp < kBounds) {// segment i on warp i
+                const int sg = warp;
+                const uint32_t s_begin = sg == 0 ? (uint32_t) k : kBoundPos[sg - 1];
+                if (s_begin < n0) {
+                    const int first = ax.rl.seg_first[sg], last = ax.rl.seg_first[sg + 1];
+                    MinBuf sb;
+                    if (sg == 0) minbuf_init(sb, lane, k, raw);
+                    else minbuf_init_keys(sb, lane, k, ax.state[sg]);
+                    replay_list(ax.rl.key + first, ax.rl.idx + first, last - first, raw, 0u, lane, sb);
+                }
             }
         }
-    }
-    if (!leader && my_n > 0 && !ax.mail.done) {
-        const bool have_list = !ax.fl.overflow;
-        if (have_list) {
-            // the records among this half's list entries: above the k-th largest key of the leader half
-            const int cnt = ax.fl.cnt;
-            uint32_t my_idx = 0, my_key = 0;
-            bool rec = false;
-            if (tid < cnt) {
-                my_key = ax.fl.key[tid];
-                my_idx = ax.fl.idx[tid];
-                rec = my_key > ax.seg_tau[kBounds];
-            }
-            const uint32_t hit_r = __ballot_sync(0xffffffffu, rec);
-            if (lane == 0) ax.wcnt_r[warp] = __popc(hit_r);
-            __syncthreads();
-            const int r_l = ax.wcnt_r[lane];
-            const int off_r = __reduce_add_sync(0xffffffffu, lane < warp ? r_l : 0);
-            const int cnt_r = __reduce_add_sync(0xffffffffu, r_l);
-            if (rec) {
-                const int at = off_r + __popc(hit_r & ((1u << lane) - 1u));
-                ax.rl.key[at] = (uint16_t) my_key;
-                ax.rl.idx[at] = my_idx;
-            }
-            if (tid == 0) ax.rl.cnt = cnt_r;
-            __syncthreads();
-        }
-        if (warp == 0) {
-            MinBuf hb;
-            minbuf_init_keys(hb, lane, k, ax.state[kBounds]);
+        if (rank == turn && my_n > 0 && !ax.mail.done) {
+            const bool have_list = !ax.fl.overflow;
             if (have_list) {
-                replay_list(ax.rl.key, ax.rl.idx, ax.rl.cnt, raw, (uint32_t) kHalfElems, lane, hb);
-            } else {
-                for (uint32_t b = 0; b < my_nblk; ++b) records_direct_block(raw + b * kBlk, 0u, lane, hb);
+                // the records among this part's list entries: above the k-th largest key of everything before it
+                const int cnt = ax.fl.cnt;
+                uint32_t my_idx = 0, my_key = 0;
+                bool rec = false;
+                if (tid < cnt) {
+                    my_key = ax.fl.key[tid];
+                    my_idx = ax.fl.idx[tid];
+                    rec = my_key > ax.seg_tau[kBounds];
+                }
+                const uint32_t hit_r = __ballot_sync(0xffffffffu, rec);
+                if (lane == 0) ax.wcnt_r[warp] = __popc(hit_r);
+                __syncthreads();
+                const int r_l = ax.wcnt_r[lane];
+                const int off_r = __reduce_add_sync(0xffffffffu, lane < warp ? r_l : 0);
+                const int cnt_r = __reduce_add_sync(0xffffffffu, r_l);
+                if (rec) {
+                    const int at = off_r + __popc(hit_r & ((1u << lane) - 1u));
+                    ax.rl.key[at] = (uint16_t) my_key;
+                    ax.rl.idx[at] = my_idx;
+                }
+                if (tid == 0) ax.rl.cnt = cnt_r;
+                __syncthreads();
+            }
+            if (warp == 0) {
+                MinBuf hb;
+                minbuf_init_keys(hb, lane, k, ax.state[kBounds]);
+                if (have_list) {
+                    replay_list(ax.rl.key, ax.rl.idx, ax.rl.cnt, raw, my_base, lane, hb);
+                } else {
+                    for (uint32_t b = 0; b < my_nblk; ++b) records_direct_block(raw + b * kBlk, 0u, lane, hb);
+                }
+                if (rank + 1 < ranks_used) {// the next part starts from what this one ends with
+                    Aux *next = ax_of(rank + 1);
+                    next->state[kBounds][lane] = hb.v0 >> 6;
+                    next->state[kBounds][lane + 32] = hb.v1 >> 6;
+                    if (lane == 0) next->seg_tau[kBounds] = hb.tau();
+                }
             }
         }
+        __syncthreads();// idle warps wait here, at the CTA barrier, for the replaying ones
+        cluster.sync();// CS4 (one per turn)
     }
-    __syncthreads();// idle warps wait here, at the CTA barrier, for the replaying ones
-    cluster.sync();// CS4
     stamp();       // 4: whole row patched
     M = val_of(ax.mail.mkey);
 
@@ -1036,9 +1067,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
         const float shift = (float) (151 - e0);
         const float band = 6.0e-6f;
         const uint32_t gb_first = pos / kBlk;// first global block still to sum
-        const uint32_t lb_first = leader ? gb_first : (gb_first > nblk0 ? gb_first - nblk0 : 0u);
-        // block b of the local half is global block b (+ nblk0 for the helper)
-        const uint32_t goff = leader ? 0u : nblk0;
+        // block b of this CTA's part is global block b + 256 * rank
+        const uint32_t goff = rank * (uint32_t) (kHalfElems / kBlk);
+        const uint32_t lb_first = gb_first > goff ? min(gb_first - goff, my_nblk) : 0u;
         if (tid == 0) ax.unc_cnt = 0;
         for (uint32_t i = lb_first + tid; i < my_nblk; i += kThreads) {
 #pragma unroll
@@ -1114,8 +1145,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
             for (uint32_t i = tid; i < my_nblk; i += kThreads) {
                 const uint32_t g = i + goff;
 #pragma unroll
-                for (int d = 0; d < kLevels; ++d) peer_ax->C[d][g] = ax.C[d][g];
-                peer_ax->tie[g] = ax.tie[g];
+                for (int d = 0; d < kLevels; ++d) lead_ax->C[d][g] = ax.C[d][g];
+                lead_ax->tie[g] = ax.tie[g];
             }
         }
         cluster.sync();// CS6
@@ -1188,8 +1219,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                     uint32_t c = 0;
                     bool tie = false;
                     if (tid < kBlk) {
-                        const uint16_t *blk = eb < nblk0 ? raw + eb * kBlk : peer_raw + (eb - nblk0) * kBlk;
-                        const uint32_t j = (eb < nblk0 ? eb * kBlk : (uint32_t) kHalfElems + (eb - nblk0) * kBlk) + tid;
+                        const uint16_t *blk = block_ptr(eb);
+                        const uint32_t j = eb * kBlk + tid;
                         const uint16_t h = blk[tid];
                         if (h != kPad && j >= pos) {
                             const float v = f16_to_f32(h);
@@ -1238,8 +1269,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                     continue;
                 }
                 if (tid < kBlk) {
-                    const uint16_t *blk = eb < nblk0 ? raw + eb * kBlk : peer_raw + (eb - nblk0) * kBlk;
-                    const uint32_t j = (eb < nblk0 ? eb * kBlk : (uint32_t) kHalfElems + (eb - nblk0) * kBlk) + tid;
+                    const uint16_t *blk = block_ptr(eb);
+                    const uint32_t j = eb * kBlk + tid;
                     const uint16_t h = blk[tid];
                     ax.blk_terms[tid] = (h == kPad || j < pos) ? 0.f : term_exact(f16_to_f32(h), M, T);
                 }
@@ -1283,9 +1314,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
                     ax.mail.s_base = s_cur;
                     ax.mail.pos_base = b0 * kBlk;
                     ax.mail.done = again ? 0 : 1;
-                    peer_ax->mail.s_base = s_cur;
-                    peer_ax->mail.pos_base = b0 * kBlk;
-                    peer_ax->mail.done = again ? 0 : 1;
+                    for (unsigned r = 1; r < R; ++r) {
+                        ax_of(r)->mail.s_base = s_cur;
+                        ax_of(r)->mail.pos_base = b0 * kBlk;
+                        ax_of(r)->mail.done = again ? 0 : 1;
+                    }
                 }
             }
         }
@@ -1321,8 +1354,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) random_
 
 namespace b200 {
 
-// Sampling branch for rows of at most 131072 logits and topk <= 64.
-bool random_sample_pair_supported(int voc) { return voc >= 1 && voc <= 2 * kHalfElems; }
+// Sampling branch for rows of at most 262144 logits and topk <= 64: a cluster of two CTAs per row up to
+// 131072 logits, of four beyond.
+bool random_sample_pair_supported(int voc) { return voc >= 1 && voc <= kMaxRanks * kHalfElems; }
 
 infiniopStatus_t random_sample_pair_launch(const RandomSampleArgs &a, int rows, cudaStream_t st) {
     static thread_local int configured_dev = -1;
@@ -1336,7 +1370,20 @@ infiniopStatus_t random_sample_pair_launch(const RandomSampleArgs &a, int rows, 
         }
         configured_dev = dev;
     }
-    random_sample_pair_kernel<<<2 * rows, kThreads, kSmemBytes, st>>>(a);
+    const unsigned ranks = a.voc > 2 * kHalfElems ? 4u : 2u;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ranks * (unsigned) rows);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, random_sample_pair_kernel, a);
     return check_launch("random_sample_pair");
 }
 

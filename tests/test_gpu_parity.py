@@ -210,7 +210,7 @@ def test_random_sample_single_row_abi(oracle, cuda_lib, voc, u, topp, topk, temp
 @pytest.fixture(params=["shared", "global"])
 def sampler_kernel(request, monkeypatch):
     """Both sampling kernels: the shared-memory resident pair kernel (default for
-    voc <= 131072) and the global-memory kernel (any voc)."""
+    voc <= 262144; clusters of two or four CTAs) and the global-memory kernel (any voc)."""
     if request.param == "global":
         monkeypatch.setenv("INFINIOP_RANDOM_SAMPLE_KERNEL", "global")
     else:
@@ -220,6 +220,8 @@ def sampler_kernel(request, monkeypatch):
 
 @pytest.mark.parametrize("voc,rows,topp,topk,temp,dist", [
     (128256, 64, 0.9, 50, 0.8, "normal3"), (131072, 8, 0.9, 64, 1.0, "normal3"), (200000, 6, 0.9, 50, 0.8, "normal3"),
+    (131073, 5, 0.9, 50, 1.0, "normal3"), (151936, 6, 0.9, 50, 1.3, "normal3"), (262144, 3, 0.9, 64, 0.8, "uniform"),
+    (262145, 2, 0.9, 50, 0.8, "normal3"), (196608, 3, 0.9, 50, 1.0, "coarse"), (256000, 3, 0.9, 50, 1.0, "ascending"),
     (65536, 8, 0.9, 50, 0.8, "normal3"), (65537, 8, 0.9, 50, 1.3, "uniform"), (70000, 4, 0.9, 50, 1.0, "ascending"),
     (100000, 4, 0.95, 33, 0.6, "coarse"), (128256, 4, 0.9, 50, 1.0, "constant"), (128256, 6, 0.9, 50, 5.0, "normal3"), (32000, 96, 0.8, 50, 1.0, "uniform"), (32000, 64, 1.0, 25, 1.0, "uniform"),
     (16384, 64, 0.85, 10, 2.0, "normal3"), (5000, 200, 0.95, 64, 0.3, "normal3"), (777, 50, 0.9, 7, 1.0, "coarse"),
