@@ -592,9 +592,15 @@ def cpu_baseline(sample_seconds=20.0):
     reps = 3
     secs = sum(cpu_step(kind, lib, handle, inputs, threads) for _ in range(reps)) / reps
     nbytes = sum(sample_bytes(inputs).values())
+    # the reference as shipped is single-threaded: the same step over an eighth of the rows on one thread
+    small = make_inputs(1000, rows_fraction=0.125)
+    secs1 = cpu_step(kind, lib, handle, small, 1)
+    nbytes1 = sum(sample_bytes(small).values())
     return {"value": round(nbytes / secs / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": kind,
             "sample": "mean of %d steps over %.3g of the rows of every operator (%d bytes per step, %.2f s per step on %d "
-                      "threads)" % (reps, fraction, nbytes, secs, threads)}
+                      "threads)" % (reps, fraction, nbytes, secs, threads),
+            "one_core": {"value": round(nbytes1 / secs1 / 1e9, 3), "unit": "GB/s",
+                         "sample": "one step over 0.125 of the rows (%d bytes) in %.2f s on 1 thread" % (nbytes1, secs1)}}
 
 
 def run_reference(args):
