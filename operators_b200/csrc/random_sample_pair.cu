@@ -50,9 +50,9 @@ constexpr int kLevels = 4;
 constexpr int kUncCap = 6144;
 constexpr int kMaxRounds = 6;     // 6 x 4 binades covers any sum of <= 2^17 terms <= 1
 constexpr int kTieGroups = 64;
-// Record segments of the leader half end at these positions (each twice the one before, so every
-// segment holds about k flagged entries and 0.7 k records whatever its length); the helper half is
-// one more segment.  The k largest keys of a prefix that ends at one of the first kDirect boundaries
+// Record segments of the leader's part end at these positions (each twice the one before, so every
+// segment holds about k flagged entries and 0.7 k records whatever its length); every helper's part
+// is one more segment.  The k largest keys of a prefix that ends at one of the first kDirect boundaries
 // are found directly on the row; for the later boundaries they come from a candidate list whose
 // threshold is a lower bound taken from maxima of groups of threads.  Those prefixes are covered by
 // whole per-thread load slots: thread t's vector u is elements [8t + 8192u, 8t + 8192u + 8).
@@ -60,7 +60,7 @@ constexpr int kWalkWarps = kMaxBlk / 32;// the walk looks at all block sums at o
 constexpr int kBounds = 10;
 constexpr int kDirect = 2;
 __device__ __constant__ uint32_t kBoundPos[kBounds] = {128u, 256u, 512u, 1024u, 2048u, 4096u, 8192u, 16384u, 32768u, 65536u};
-// Scan assignment of the leader half: warp w looks at [kScanR0[w], kScanR0[w + 1]), which lies inside
+// Scan assignment of the leader's part: warp w looks at [kScanR0[w], kScanR0[w + 1]), which lies inside
 // segment kScanSeg[w].  Pieces shorter than 256 are cut into 64-element chunks, the others into
 // 256-element blocks (at most 16 per warp).
 __device__ __constant__ uint32_t kScanR0[kWarps + 1] = {
@@ -93,7 +93,7 @@ struct RecList {
     int cnt;
     int seg_first[kBounds + 1];// leader: position of the first entry of segment i; [kBounds] = count
 };
-struct Mail {// written by the other CTA of the pair (the leader also fills its own copy)
+struct Mail {// written by other CTAs of the cluster (the leader also fills its own copy)
     uint32_t L_of[kMaxRanks];// every CTA's lower bound of the k-th largest key of its own part
     uint32_t mkey;
     float s_base;
@@ -414,7 +414,7 @@ __device__ __forceinline__ void exact_at_level(float term, int e0, int level, ui
 
 __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomSampleArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint16_t *raw = reinterpret_cast<uint16_t *>(smem_raw);// this CTA's half of the row, fp16 bit patterns
+    uint16_t *raw = reinterpret_cast<uint16_t *>(smem_raw);// this CTA's part of the row, fp16 bit patterns
     Aux &ax = *reinterpret_cast<Aux *>(smem_raw + (size_t) kHalfElems * 2);
     cg::cluster_group cluster = cg::this_cluster();
     // CTA `rank` of the cluster holds elements [rank * 65536, (rank + 1) * 65536) of the row; rank 0 leads.
@@ -453,7 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomS
         return cluster.map_shared_rank(raw, g >> 8) + (g & 255u) * kBlk;
     };
 
-    // ---- P1: this CTA's half of the row -> shared memory; per-thread maxima --------------
+    // ---- P1: this CTA's part of the row -> shared memory; per-thread maxima --------------
     const bool in_aligned = (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
     __half2 tmax2 = h2_of(0xFC00FC00u), m0_2 = tmax2, mA_2 = tmax2, mB_2 = tmax2;// running maximum; after 1, 2 and 4 vectors
     auto max4 = [](const uint4 q) { return __hmax2(__hmax2(h2_of(q.x), h2_of(q.y)), __hmax2(h2_of(q.z), h2_of(q.w))); };
@@ -698,7 +698,7 @@ __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomS
     cluster.sync();// CS2
     stamp();       // 1: candidate lists at the leader
 
-    // ---- P3 (leader): exact top-k, records of the leader half --------------------------
+    // ---- P3 (leader): exact top-k, start states of its record segments -----------------
     MinBuf mb{kEmptyMin, kEmptyMin, 0};
     float M = 0.f;
     bool list_ok = false;
@@ -741,7 +741,7 @@ __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomS
         if (ax.state_ovf) list_ok = false;
         if (list_ok) {
             // Out of the ordered lists: the candidates proper (key >= L; the ranking below is quadratic in
-            // their number), the helper's behind the leader's own, in place; and the records to replay
+            // their number), the helpers' behind the leader's own, in place; and the records to replay
             // (key above the k-th largest at the start of the entry's segment), into their own list.  One
             // entry per thread, read before the barrier and written to its new place after it.
             uint32_t my_idx = 0, my_key = 0, mv_idx = 0, mv_key = 0;
@@ -965,7 +965,7 @@ __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomS
         if ((uint32_t) k < n) {
             if (!list_ok) {
                 if (warp == 0) {
-                    // slow path (candidate lists overflowed): one warp walks the leader half in order
+                    // slow path (candidate lists overflowed): one warp walks the leader's part in order
                     minbuf_init(mb, lane, k, raw);
                     if (lane == 0) ax.seg_tau[0] = mb.tau();
                     for (uint32_t b = 0; b < nblk0; ++b) records_direct_block(raw + b * kBlk, b == 0 ? (uint32_t) k : 0u, lane, mb);
@@ -1141,7 +1141,7 @@ __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomS
             }
         }
         __syncthreads();
-        if (!leader) {// ship the helper's block sums to the leader
+        if (!leader) {// ship this helper's block sums to the leader
             for (uint32_t i = tid; i < my_nblk; i += kThreads) {
                 const uint32_t g = i + goff;
 #pragma unroll
