@@ -48,7 +48,7 @@ constexpr int kMaxRanks = 4;       // CTAs per cluster: 2 up to 131072 logits, 4
 constexpr int kMaxBlk = kMaxRanks * kHalfElems / kBlk;
 constexpr int kLevels = 4;
 constexpr int kUncCap = 6144;
-constexpr int kMaxRounds = 6;     // 6 x 4 binades covers any sum of <= 2^17 terms <= 1
+constexpr int kMaxRounds = 6;     // 6 x 4 binades covers any sum of <= 2^18 terms <= 1 (18 binades above 1)
 constexpr int kTieGroups = 64;
 // Record segments of the leader's part end at these positions (each twice the one before, so every
 // segment holds about k flagged entries and 0.7 k records whatever its length); every helper's part
