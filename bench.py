@@ -328,8 +328,9 @@ def run_b200(args):
             ev[k][i + 1].record(stream)
     barrier()
     clk = clocks.stop()  # sampled over both passes: the same kernels under the same load
-    per_op_ms = {name: sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(args.steps)) / args.steps
-                 for i, (name, _) in enumerate(calls)}
+    per_op_all = {name: sorted(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(args.steps))
+                  for i, (name, _) in enumerate(calls)}
+    per_op_ms = {name: sum(v) / len(v) for name, v in per_op_all.items()}
 
     # ---- RMSNorm at a size that can load the memory system (the configuration above is 135 KB: launch latency) ----
     # rank 0 only, outside every timed region above; 36 launches over three rotating [65536, 2048] buffers
@@ -439,7 +440,9 @@ def run_b200(args):
     ops_out = {}
     for o in OPS:
         gbs = ALGO_BYTES[o] * world / (per_op_ms[o] * 1e-3) / 1e9
-        ops_out[o] = {"bytes": ALGO_BYTES[o], "ms": round(per_op_ms[o], 5), "gbs": round(gbs, 1),
+        ops_out[o] = {"bytes": ALGO_BYTES[o], "ms": round(per_op_ms[o], 5),
+                      "ms_median": round(per_op_all[o][len(per_op_all[o]) // 2], 5), "ms_best": round(per_op_all[o][0], 5),
+                      "gbs": round(gbs, 1),
                       "frac_of_%s_peak" % peak_kind: round(gbs / world / peak, 4),
                       "frac_of_8TBs": round(gbs / world / NOMINAL_HBM_GBS, 4)}
     ops_out["random_sample"]["tokens_per_s"] = round(RS_B * world / (per_op_ms["random_sample"] * 1e-3), 1)
