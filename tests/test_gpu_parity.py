@@ -169,7 +169,8 @@ def test_add_unaligned_views(oracle, cuda_lib):
 # ---- causal softmax --------------------------------------------------------------
 @pytest.mark.parametrize("shape,strides", [((32, 20, 512), None), ((32, 20, 512), (20480, 1024, 1)), ((5, 64), None),
                                            ((2, 7, 7), None), ((3, 1, 9), None), ((2, 128, 4096), None),
-                                           ((4, 33, 1000), None), ((1, 3, 20000), None), ((2, 2, 70000), None)])
+                                           ((4, 33, 1000), None), ((1, 3, 20000), None), ((2, 2, 70000), None),
+                                           ((8, 64, 16384), None), ((600, 1, 16384), None)])
 def test_causal_softmax(oracle, cuda_lib, shape, strides):
     lib, handle = cuda_lib
     g = torch.Generator().manual_seed(5)
