@@ -62,8 +62,8 @@ def test_rms_norm(oracle, cuda_lib, shape, stride, w_dtype):
                                            ((2, 2, 4096), None), ((9, 40, 128), (40 * 256, 256, 1)),
                                            # bulk-copy pipeline: rings reused several times, ragged token counts,
                                            # one token, more tokens than the pipeline takes (-> strided kernel)
-                                           ((9000, 8, 64), None), ((1187, 32, 128), None), ((33, 4, 256), None),
-                                           ((40000, 2, 32), None), ((300, 16, 8), None)])
+                                           ((9000, 32, 64), None), ((1187, 32, 128), None), ((33, 8, 256), None),
+                                           ((9000, 8, 64), None), ((40000, 64, 32), None), ((300, 16, 8), None)])
 def test_rope(oracle, cuda_lib, shape, strides):
     lib, handle = cuda_lib
     g = torch.Generator().manual_seed(2)
