@@ -14,8 +14,10 @@
 // reference cudaMallocs three stride arrays per descriptor, add.cc:48-54;
 // nothing is allocated on the device here).
 #include "common.cuh"
+#include "fastdiv.h"
 
 #include <new>
+#include <type_traits>
 
 using namespace b200;
 
@@ -125,6 +127,62 @@ __global__ void __launch_bounds__(kThreads)
             reinterpret_cast<float *>(c)[i] =
                 __fadd_rn(reinterpret_cast<const float *>(a)[oa], reinterpret_cast<const float *>(b)[ob]);
         }
+    }
+}
+
+// Broadcast patterns whose innermost collapsed axis is walked with stride 1 or 0 by both operands and
+// is a whole number of 128-bit vectors long: one vector of c per thread and step; the vector's multi-index
+// is rebuilt once (multiply-high dividers, the innermost extent counted in vectors), an operand that does
+// not span the innermost axis contributes one replicated element.  Everything else (odd extents,
+// unaligned bases) stays on add_general_kernel.
+struct VecDims {
+    int ndim;
+    FastDiv div[kMaxDims];// extents, the innermost one in vectors
+    int64_t sa[kMaxDims]; // strides in elements; for the innermost axis per vector (V or 0)
+    int64_t sb[kMaxDims];
+    bool a_inner, b_inner;// operand spans the innermost axis
+};
+
+template<bool F16>
+__global__ void __launch_bounds__(kThreads)
+    add_bcast_vec_kernel(void *c, const void *a, const void *b, uint32_t total_vecs, VecDims dims) {
+    constexpr int V = F16 ? 8 : 4;
+    using E = typename std::conditional<F16, uint16_t, uint32_t>::type;
+    const E *ae = reinterpret_cast<const E *>(a), *be = reinterpret_cast<const E *>(b);
+    uint4 *cv = reinterpret_cast<uint4 *>(c);
+    const uint32_t base = blockIdx.x * (kThreads * kUnroll) + threadIdx.x;
+    uint4 x[kUnroll], y[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        const uint32_t v = base + u * kThreads;
+        if (v < total_vecs) {
+            uint32_t rem = v;
+            int64_t oa = 0, ob = 0;
+            for (int ax = dims.ndim - 1; ax >= 0; --ax) {
+                uint32_t q, idx;
+                dims.div[ax].divmod(rem, q, idx);
+                oa += (int64_t) idx * dims.sa[ax];
+                ob += (int64_t) idx * dims.sb[ax];
+                rem = q;
+            }
+            if (dims.a_inner) {
+                x[u] = ld_stream(ae + oa);
+            } else {
+                const uint32_t e = F16 ? (uint32_t) ae[oa] * 0x00010001u : (uint32_t) ae[oa];
+                x[u] = make_uint4(e, e, e, e);
+            }
+            if (dims.b_inner) {
+                y[u] = ld_stream(be + ob);
+            } else {
+                const uint32_t e = F16 ? (uint32_t) be[ob] * 0x00010001u : (uint32_t) be[ob];
+                y[u] = make_uint4(e, e, e, e);
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+        const uint32_t v = base + u * kThreads;
+        if (v < total_vecs) st_stream(cv + v, add_vec<F16>(x[u], y[u]));
     }
 }
 
@@ -246,6 +304,32 @@ INFINIOP_API infiniopStatus_t infiniopAdd(infiniopAddDescriptor_t desc, void *c,
             add_flat_kernel<false><<<(uint32_t) grid, kThreads, 0, st>>>(c, a, b, vecs, d->total);
         }
         return check_launch("add");
+    }
+    if (d->broadcast && d->dims.ndim >= 1 && aligned16(c) && aligned16(a) && aligned16(b)) {
+        const BroadcastDims &bd = d->dims;
+        const int in = bd.ndim - 1;
+        const uint32_t V = d->is_f16 ? 8u : 4u;
+        bool ok = bd.shape[in] % V == 0 && (bd.sa[in] == 0 || bd.sa[in] == 1) && (bd.sb[in] == 0 || bd.sb[in] == 1) &&
+                  d->total / V <= 0xFFFFFFFFull;
+        VecDims vd;
+        vd.ndim = bd.ndim;
+        vd.a_inner = bd.sa[in] == 1;
+        vd.b_inner = bd.sb[in] == 1;
+        for (int ax = 0; ax < bd.ndim && ok; ++ax) {
+            const bool inner = ax == in;
+            vd.div[ax] = FastDiv(inner ? bd.shape[ax] / V : bd.shape[ax]);
+            vd.sa[ax] = inner ? bd.sa[ax] * (int64_t) V : bd.sa[ax];
+            vd.sb[ax] = inner ? bd.sb[ax] * (int64_t) V : bd.sb[ax];
+            // vector loads of an operand that spans the innermost axis need every outer step to keep 16-byte alignment
+            if (!inner && ((vd.a_inner && bd.sa[ax] % V != 0) || (vd.b_inner && bd.sb[ax] % V != 0))) ok = false;
+        }
+        if (ok) {
+            const uint32_t vecs = (uint32_t) (d->total / V);
+            const uint32_t tiles = (vecs + kThreads * kUnroll - 1) / (kThreads * kUnroll);
+            if (d->is_f16) add_bcast_vec_kernel<true><<<tiles, kThreads, 0, st>>>(c, a, b, vecs, vd);
+            else add_bcast_vec_kernel<false><<<tiles, kThreads, 0, st>>>(c, a, b, vecs, vd);
+            return check_launch("add");
+        }
     }
     // Broadcast, or flat tensors at addresses that are not 16-byte aligned.
     uint64_t blocks = (d->total + kThreads - 1) / kThreads;

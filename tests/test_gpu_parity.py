@@ -119,7 +119,12 @@ def test_swiglu_fused_gate_up_halves(oracle, cuda_lib):
 @pytest.mark.parametrize("shapes", [((), (), ()), ((3, 3), (3, 3), (3, 3)), ((2, 20, 3), (2, 1, 3), (2, 20, 3)),
                                     ((32, 20, 512), (32, 20, 512), (32, 20, 512)), ((4, 5, 6), (6,), (4, 5, 6)),
                                     ((3, 1, 7), (1, 5, 1), (3, 5, 7)), ((1000003,), (1000003,), (1000003,)),
-                                    ((2, 3, 4, 5), (5,), (2, 3, 4, 5)), ((32, 64, 28, 28), (32, 64, 28, 28), (32, 64, 28, 28))])
+                                    ((2, 3, 4, 5), (5,), (2, 3, 4, 5)), ((32, 64, 28, 28), (32, 64, 28, 28), (32, 64, 28, 28)),
+                                    # broadcasts whose innermost axis is whole vectors (the vectorised broadcast kernel)
+                                    ((64, 4096), (4096,), (64, 4096)), ((64, 1), (64, 4096), (64, 4096)),
+                                    ((4, 8, 256), (4, 1, 256), (4, 8, 256)), ((16, 1, 64), (1, 8, 64), (16, 8, 64)),
+                                    ((3, 5, 1, 16), (5, 7, 16), (3, 5, 7, 16)), ((2, 1, 1), (1, 3, 24), (2, 3, 24)),
+                                    ((1, 40), (9, 1), (9, 40)), ((300, 8), (8,), (300, 8))])
 def test_add(oracle, cuda_lib, shapes, dtype):
     lib, handle = cuda_lib
     as_, bs, cs = shapes
