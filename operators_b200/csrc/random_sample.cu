@@ -39,6 +39,8 @@
 #include "random_sample.cuh"
 #include "random_sample_device.cuh"
 
+#include <cooperative_groups.h>
+
 #include <cstdlib>
 #include <new>
 
@@ -523,6 +525,103 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 namespace b200 {
 
+}// namespace b200
+
+namespace {
+
+// Argmax branch (topp == 0 or topk <= 1; reference random_sample.cc:130-153: the first index among
+// equal maxima) for rows that start on a 16-byte boundary.  A cluster of two CTAs per row, each streams
+// one half with eight 128-bit loads in flight per thread; a thread only keeps the largest value it has
+// seen (packed fp16 maxima) and the first vector that reached it, so the pass costs about one
+// instruction per element; the winning vector is looked at again to name the element.
+constexpr int kArgmaxThreads = 512;
+
+__device__ __forceinline__ unsigned long long shfl_max_u64(unsigned long long v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+        v = other > v ? other : v;
+    }
+    return v;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kArgmaxThreads) random_sample_argmax_kernel(RandomSampleArgs a) {
+    namespace cg = cooperative_groups;
+    __shared__ unsigned long long red[kArgmaxThreads / 32];
+    __shared__ unsigned long long peer_best;
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank = cluster.block_rank();
+    const int row = blockIdx.x >> 1, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint16_t *logits = a.logits + (int64_t) row * a.logits_stride;
+    const uint32_t n = (uint32_t) a.voc, nvec = (n + 7) / 8;   // the last vector may be ragged
+    const uint32_t half = (nvec + 1) / 2;
+    const uint32_t v_begin = rank == 0 ? 0u : half, v_end = rank == 0 ? half : nvec;
+
+    uint32_t best_key = 0, best_vec = 0xFFFFFFFFu;// key 0: nothing seen
+    constexpr int kInFlight = 8;
+    for (uint32_t v0 = v_begin + tid; v0 < v_end; v0 += kArgmaxThreads * kInFlight) {
+        uint4 q[kInFlight];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            const uint32_t v = v0 + u * kArgmaxThreads;
+            q[u] = make_uint4(0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u);
+            if (v < v_end) {
+                if (v * 8 + 8 <= n) {
+                    q[u] = ld_stream(logits + (uint64_t) v * 8);
+                } else {// ragged end of the row: element-wise, padded with -inf (never wins over a real element before it)
+                    uint16_t h[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) h[e] = v * 8 + e < n ? logits[(uint64_t) v * 8 + e] : (uint16_t) 0xFC00;
+                    q[u] = make_uint4(h[0] | ((uint32_t) h[1] << 16), h[2] | ((uint32_t) h[3] << 16),
+                                      h[4] | ((uint32_t) h[5] << 16), h[6] | ((uint32_t) h[7] << 16));
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+            const uint32_t v = v0 + u * kArgmaxThreads;
+            if (v < v_end) {
+                const __half2 m2 = __hmax2(__hmax2(*reinterpret_cast<const __half2 *>(&q[u].x), *reinterpret_cast<const __half2 *>(&q[u].y)),
+                                           __hmax2(*reinterpret_cast<const __half2 *>(&q[u].z), *reinterpret_cast<const __half2 *>(&q[u].w)));
+                const uint32_t key = key_of(__half_as_ushort(__hmax(__low2half(m2), __high2half(m2))));
+                if (key > best_key) {// strictly larger: the first vector that reaches the maximum stays
+                    best_key = key;
+                    best_vec = v;
+                }
+            }
+        }
+    }
+    // (key, lowest vector) -> one 64-bit value whose maximum is the answer
+    unsigned long long best = ((unsigned long long) best_key << 32) | (0xFFFFFFFFu - best_vec);
+    best = shfl_max_u64(best);
+    if (lane == 0) red[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < kArgmaxThreads / 32 ? red[lane] : 0ull;
+        best = shfl_max_u64(best);
+        if (rank == 1 && lane == 0) *cluster.map_shared_rank(&peer_best, 0) = best;
+    }
+    cluster.sync();
+    if (rank == 0 && warp == 0) {
+        const unsigned long long other = peer_best;
+        if (other > best) best = other;
+        const uint32_t key = (uint32_t) (best >> 32), vec = 0xFFFFFFFFu - (uint32_t) (best & 0xFFFFFFFFu);
+        // the first element of that vector whose key is the maximum
+        uint32_t pos = 0xFFFFFFFFu;
+        if (lane < 8) {
+            const uint32_t i = vec * 8 + lane;
+            if (i < n && key_of(logits[i]) == key) pos = i;
+        }
+        pos = __reduce_min_sync(0xffffffffu, pos);
+        if (pos == 0xFFFFFFFFu) pos = 0;// only a row of NaNs gets here; the reference answers 0 for it
+        if (lane == 0) a.result[(int64_t) row * a.result_stride] = pos;
+    }
+}
+
+}// namespace
+
+namespace b200 {
+
 uint64_t random_sample_work_pitch(int voc) { return ((uint64_t) voc + kBlk - 1) / kBlk * kBlk; }
 
 uint64_t random_sample_workspace_bytes(int voc, int rows) {
@@ -550,6 +649,10 @@ infiniopStatus_t random_sample_launch(const RandomSampleArgs &args_in, int rows,
         if (workspace_size < random_sample_workspace_bytes(a.voc, rows)) return STATUS_INSUFFICIENT_WORKSPACE;
         a.work = reinterpret_cast<uint16_t *>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t) 255);
         a.work_pitch = (int64_t) random_sample_work_pitch(a.voc);
+    }
+    if (!sampling && aligned16(a.logits) && a.logits_stride % 8 == 0 && a.voc >= 1) {
+        random_sample_argmax_kernel<<<2 * rows, kArgmaxThreads, 0, st>>>(a);
+        return check_launch("random_sample_argmax");
     }
     const uint32_t nblk = (uint32_t) ((a.voc + kBlk - 1) / kBlk);
     const size_t smem = sizeof(Shared) + (size_t) nblk * sizeof(uint32_t);

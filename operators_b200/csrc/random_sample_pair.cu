@@ -1354,8 +1354,8 @@ __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomS
 
 namespace b200 {
 
-// Sampling branch for rows of at most 262144 logits and topk <= 64: a cluster of two CTAs per row up to
-// 131072 logits, of four beyond.
+// Sampling branch for rows of at most 262144 logits and topk <= 64: one CTA per row up to 65536 logits, a
+// cluster of two up to 131072, of four beyond.
 bool random_sample_pair_supported(int voc) { return voc >= 1 && voc <= kMaxRanks * kHalfElems; }
 
 infiniopStatus_t random_sample_pair_launch(const RandomSampleArgs &a, int rows, cudaStream_t st) {
@@ -1370,7 +1370,8 @@ infiniopStatus_t random_sample_pair_launch(const RandomSampleArgs &a, int rows, 
         }
         configured_dev = dev;
     }
-    const unsigned ranks = a.voc > 2 * kHalfElems ? 4u : 2u;
+    // one CTA per row while the row fits it: a second one would only occupy an SM another row could use
+    const unsigned ranks = a.voc > 2 * kHalfElems ? 4u : a.voc > kHalfElems ? 2u : 1u;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ranks * (unsigned) rows);
     cfg.blockDim = dim3(kThreads);

@@ -286,6 +286,48 @@ def test_random_sample_argmax_ties(oracle, cuda_lib):
     assert int(res[0]) == 77 == oracle.random_sample(logits.numpy(), 0.5, 0.0, 5, 1.0)
 
 
+@pytest.mark.parametrize("voc,rows,pitch", [(128256, 64, 128256), (32000, 33, 32000), (1, 3, 8), (7, 5, 8), (8, 4, 8),
+                                            (9, 4, 16), (4097, 9, 4104), (151937, 3, 151944), (5000, 6, 5003),
+                                            (262147, 2, 262152)])
+@pytest.mark.parametrize("dist", ["normal3", "coarse", "neg_inf", "late_tie"])
+def test_random_sample_argmax_batch(oracle, cuda_lib, voc, rows, pitch, dist):
+    """Greedy decoding (top-p 0 or top-k 1): the first index of the row maximum, as the
+    reference's strict-greater scan finds it; rows that end inside a 16-byte vector, rows
+    whose pitch keeps them 16-byte aligned and rows whose pitch does not."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(voc + rows)
+    if dist == "normal3":
+        logits = (torch.randn((rows, voc), generator=g) * 3).half()
+    elif dist == "coarse":
+        logits = torch.randint(-3, 4, (rows, voc), generator=g).half()
+    elif dist == "neg_inf":
+        logits = torch.full((rows, voc), float("-inf")).half()
+        if voc > 2:
+            logits[1::2, voc - 1] = -7.0  # a single finite value at the ragged end of every second row
+    else:  # the maximum appears in both halves of the row and as the last element
+        logits = (torch.rand((rows, voc), generator=g) - 2).half()
+        for r in range(rows):
+            logits[r, [min(voc - 1, voc // 2 + r), voc - 1]] = 5.0
+            if r % 2 and voc > 4:
+                logits[r, voc // 4] = 5.0
+        logits[:, 0] = -0.0
+    store = torch.zeros((rows, pitch), dtype=torch.float16, device=DEV)
+    store[:, :voc] = logits.to(DEV)
+    ld = store[:, :voc]
+    u = torch.rand(rows, generator=g).to(DEV)
+    want = [oracle.random_sample(logits[r].numpy(), 0.5, 0.0, 5, 1.0) for r in range(rows)]
+    for topp, topk in ((0.0, 5), (0.9, 1)):
+        res = torch.full((rows,), 999, dtype=torch.int64, device=DEV)
+        with ops.RandomSampleOp(lib, handle, res[:1], ld[0]) as op:
+            op.batch(res, ld, u, topp, topk, 1.0)
+            torch.cuda.synchronize()
+        assert res.cpu().tolist() == want
+    one = torch.full((1,), 999, dtype=torch.int64, device=DEV)
+    ops.random_sample(lib, handle, one, ld[rows - 1], 0.5, 0.0, 5, 1.0)
+    torch.cuda.synchronize()
+    assert int(one[0]) == want[rows - 1]
+
+
 # ---- descriptor validation: same status codes as the reference ------------------------
 def test_status_codes(cuda_lib):
     import ctypes
