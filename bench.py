@@ -246,6 +246,68 @@ def run_b200(args):
                           "gbs": round(nbytes / ms / 1e6, 1),
                           "note": "back-to-back launches of one operator; not a bench value"}))
         return
+    if args.only == "add_rms_norm":  # not part of the step: the fused residual form beside the two calls it replaces
+        from operators_b200 import ops as _ops
+
+        shape = (ADD_T, ADD_D)
+        a = torch.randn(shape, device=dev).half()
+        b = torch.randn(shape, device=dev).half()
+        w = torch.rand(shape[1], device=dev).half()
+        total, y = torch.empty_like(a), torch.empty_like(a)
+        fused = _ops.AddRMSNormOp(lib, handle, y, total, a, b, w)
+        add_op, norm_op = _ops.AddOp(lib, handle, total, a, b), _ops.RMSNormOp(lib, handle, y, total, w)
+
+        def timed(fn):
+            for _ in range(args.warmup):
+                fn()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(args.steps):
+                fn()
+            t1.record()
+            torch.cuda.synchronize()
+            return t0.elapsed_time(t1) / args.steps
+
+        ms_fused = timed(lambda: fused(y, total, a, b, w))
+        ms_pair = timed(lambda: (add_op(total, a, b), norm_op(y, total, w)))
+        nbytes = 4 * a.numel() * 2 + w.numel() * 2  # a, b read; sum, y written (268 MB per launch: larger than L2)
+        print(json.dumps({"only": "add_rms_norm", "shape": list(shape), "ms": round(ms_fused, 5),
+                          "gbs": round(nbytes / ms_fused / 1e6, 1), "ms_add_then_rms_norm": round(ms_pair, 5),
+                          "note": "back-to-back launches of one operator; not a bench value"}))
+        return
+    if args.only == "rope_rearrange":  # not part of the step: K rotated into the cache beside the two calls it replaces
+        from operators_b200 import ops as _ops
+
+        tokens, kv_heads, dh, cache_len = 4 * ROPE_T, 8, ROPE_DH, 4 * ROPE_T
+        qkv = torch.randn((tokens, (ROPE_H + 2 * kv_heads) * dh), device=dev).half()
+        k = qkv[:, ROPE_H * dh:(ROPE_H + kv_heads) * dh].view(tokens, kv_heads, dh)  # the K slice of a qkv row
+        pos = torch.arange(tokens, device=dev, dtype=torch.int64)
+        sin, cos = _ops.sin_cos_table(tokens, dh, device=dev)
+        cache = torch.zeros((kv_heads, cache_len, dh), device=dev, dtype=torch.float16)
+        dst = cache.permute(1, 0, 2)
+        fused = _ops.RoPERearrangeOp(lib, handle, dst, k, pos, sin, cos)
+        rope_op, copy_op = _ops.RoPEOp(lib, handle, k, pos, sin, cos), _ops.RearrangeOp(lib, handle, dst, k)
+
+        def timed(fn):
+            for _ in range(args.warmup):
+                fn()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(args.steps):
+                fn()
+            t1.record()
+            torch.cuda.synchronize()
+            return t0.elapsed_time(t1) / args.steps
+
+        ms_fused = timed(lambda: fused(dst, k, pos, sin, cos))
+        ms_pair = timed(lambda: (rope_op(k, pos, sin, cos), copy_op(dst, k)))
+        nbytes = 2 * k.numel() * 2 + 2 * sin.numel() * 4 + pos.numel() * 8
+        print(json.dumps({"only": "rope_rearrange", "shape": list(k.shape), "ms": round(ms_fused, 5),
+                          "gbs": round(nbytes / ms_fused / 1e6, 1), "ms_rope_then_rearrange": round(ms_pair, 5),
+                          "note": "back-to-back launches of one operator on L2-sized data; not a bench value"}))
+        return
     inputs = make_inputs(1000 + rank, only=args.only)
     step = DecodeStep(lib, handle, dev, inputs)
     calls = step.calls()
@@ -675,7 +737,7 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of a CUDA graph of the step")
-    ap.add_argument("--only", choices=OPS + ["rearrange"],
+    ap.add_argument("--only", choices=OPS + ["rearrange", "add_rms_norm", "rope_rearrange"],
                     help="launch a single operator at its configuration (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

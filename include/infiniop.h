@@ -150,6 +150,31 @@ INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *
                                            void const *cos_table, void *stream);
 INFINIOP_API infiniopStatus_t infiniopDestroyRoPEDescriptor(infiniopRoPEDescriptor_t desc);
 
+/* ---- RoPE written to a second view (NO counterpart in the reference) ------- *
+ * dst[i, j, :] = the rotation infiniopRoPE applies to src[i, j, :]; src is not
+ * modified.  dst and src: fp16 [tokens, heads, dh] views with unit innermost
+ * stride and otherwise free strides, so dst can be the rows of a K cache
+ * [heads, max_seq, dh] at the tokens' positions.  Bit for bit what infiniopRoPE
+ * followed by infiniopRearrange writes (the reference reaches it through
+ * include/ops/rotary_embedding/rotary_embedding.h:10-30 and the rearrange of k
+ * into k_cache in src/ops/attention/operator.cc:87-91).  dst and src must not
+ * overlap. */
+typedef struct RoPEDescriptor *infiniopRoPERearrangeDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateRoPERearrangeDescriptor(infiniopHandle_t handle,
+                                                                    infiniopRoPERearrangeDescriptor_t *desc_ptr,
+                                                                    infiniopTensorDescriptor_t dst,
+                                                                    infiniopTensorDescriptor_t src,
+                                                                    infiniopTensorDescriptor_t pos_ids,
+                                                                    infiniopTensorDescriptor_t sin_table,
+                                                                    infiniopTensorDescriptor_t cos_table);
+INFINIOP_API infiniopStatus_t infiniopGetRoPERearrangeWorkspaceSize(infiniopRoPERearrangeDescriptor_t desc,
+                                                                    uint64_t *size);
+INFINIOP_API infiniopStatus_t infiniopRoPERearrange(infiniopRoPERearrangeDescriptor_t desc, void *workspace,
+                                                    uint64_t workspace_size, void *dst, void const *src,
+                                                    void const *pos_ids, void const *sin_table,
+                                                    void const *cos_table, void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyRoPERearrangeDescriptor(infiniopRoPERearrangeDescriptor_t desc);
+
 /* ---- SwiGLU: include/ops/swiglu/swiglu.h:7-25 ----------------------------- *
  * c = a * silu(b), 2-D fp16, unit column stride, free row strides; c may alias
  * a or b.  No workspace entry point exists for this operator. */
@@ -195,6 +220,32 @@ INFINIOP_API infiniopStatus_t infiniopCreateRearrangeDescriptor(infiniopHandle_t
 INFINIOP_API infiniopStatus_t infiniopRearrange(infiniopRearrangeDescriptor_t desc, void *dst, void const *src,
                                                 void *stream);
 INFINIOP_API infiniopStatus_t infiniopDestroyRearrangeDescriptor(infiniopRearrangeDescriptor_t desc);
+
+/* ---- fused residual add + RMSNorm (NO counterpart in the reference) -------- *
+ * sum = a + b as infiniopAdd forms it, y = RMSNorm(sum) * w as infiniopRMSNorm
+ * forms it, in one pass: the sum is bit for bit that of infiniopAdd, y is what
+ * infiniopRMSNorm makes of it (up to the grouping of the fp32 sum of squares),
+ * and the sum is not read back from memory.  y, sum, a, b: 2-D fp16 of one shape, unit
+ * column stride, free row strides, no broadcasting; w 1-D fp16 or fp32.  `sum`
+ * may be `a` or `b` (residual updated in place); `y` must not overlap `sum`.
+ * The reference's callers reach the same result through
+ * include/ops/add/add.h:13-25 followed by include/ops/rms_norm/rms_norm.h:13-26. */
+typedef struct AddRMSNormDescriptor {
+    Device device;
+} AddRMSNormDescriptor;
+typedef AddRMSNormDescriptor *infiniopAddRMSNormDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateAddRMSNormDescriptor(infiniopHandle_t handle,
+                                                                 infiniopAddRMSNormDescriptor_t *desc_ptr,
+                                                                 infiniopTensorDescriptor_t y_desc,
+                                                                 infiniopTensorDescriptor_t sum_desc,
+                                                                 infiniopTensorDescriptor_t a_desc,
+                                                                 infiniopTensorDescriptor_t b_desc,
+                                                                 infiniopTensorDescriptor_t w_desc, float epsilon);
+INFINIOP_API infiniopStatus_t infiniopGetAddRMSNormWorkspaceSize(infiniopAddRMSNormDescriptor_t desc, uint64_t *size);
+INFINIOP_API infiniopStatus_t infiniopAddRMSNorm(infiniopAddRMSNormDescriptor_t desc, void *workspace,
+                                                 uint64_t workspace_size, void *y, void *sum, void const *a,
+                                                 void const *b, void const *w, void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyAddRMSNormDescriptor(infiniopAddRMSNormDescriptor_t desc);
 
 /* ---- causal softmax: include/ops/causal_softmax/causal_softmax.h:7-25 ----- *
  * In place on fp16 [.., seq_len, total_seq_len] (2-D or 3-D, unit last

@@ -16,6 +16,13 @@
 // (shuffle reduction only) or by one CTA (shuffles + one shared-memory step).
 // Rows that are not 16-byte aligned, or longer than 64 Ki elements, take the
 // two-pass scalar kernel.
+//
+// The same kernels serve the fused residual form (infiniopAddRMSNorm, which the
+// reference does not have): x = a + b with the Add operator's arithmetic
+// (src/ops/add/cpu/add_cpu.cc:82-83: exact fp32 sum, truncated to fp16) is
+// formed in registers, written out once as the new residual and normalised
+// without being read back: 8 bytes per element instead of the 10 of Add
+// followed by RMSNorm.
 #include "common.cuh"
 
 #include <new>
@@ -32,7 +39,29 @@ struct RMSNormDesc {
     int64_t stride_y, stride_x;
     bool w_f16;
     float epsilon;
+    bool fused;                 // x = a + b, written to `sum`
+    int64_t stride_b, stride_sum;
 };
+
+// Second operand and destination of the sum in the fused form.
+struct Residual {
+    const uint16_t *b;
+    uint16_t *sum;
+    int64_t stride_b, stride_sum;
+};
+
+__device__ __forceinline__ uint4 add_vec_f16(uint4 x, uint4 y) {
+    uint4 r;
+    const uint32_t *px = reinterpret_cast<const uint32_t *>(&x);
+    const uint32_t *py = reinterpret_cast<const uint32_t *>(&y);
+    uint32_t *pr = reinterpret_cast<uint32_t *>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 fx = unpack2(px[k]), fy = unpack2(py[k]);
+        pr[k] = pack2_ref(__fadd_rn(fx.x, fy.x), __fadd_rn(fx.y, fy.y));
+    }
+    return r;
+}
 
 __device__ __forceinline__ double h2d(uint16_t h) {
     double r;
@@ -77,9 +106,9 @@ __device__ __forceinline__ float rms_prod(ScaleF2 k, float x, float w) {
 
 // VPT vectors (8 halves each) per thread; CTA_ROW: the whole CTA owns one row,
 // otherwise each warp owns one row.
-template<int VPT, bool W_F16, bool CTA_ROW>
+template<int VPT, bool W_F16, bool CTA_ROW, bool FUSED>
 __global__ void rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs,
-                                     uint64_t d, int64_t stride_y, int64_t stride_x, float eps) {
+                                     uint64_t d, int64_t stride_y, int64_t stride_x, float eps, Residual res) {
     __shared__ float red[32];
     const int lane = threadIdx.x & 31;
     const uint32_t group = CTA_ROW ? blockDim.x : 32;
@@ -98,6 +127,24 @@ __global__ void rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void 
         for (int u = 0; u < VPT; ++u) {
             const uint32_t j = t + u * group;
             if (j < vecs) v[u] = ld_stream(xr + (uint64_t) j * 8);
+        }
+        if (FUSED) {
+            const uint16_t *br = res.b + (int64_t) row * res.stride_b;
+            uint16_t *sr = res.sum + (int64_t) row * res.stride_sum;
+            uint4 o[VPT];
+#pragma unroll
+            for (int u = 0; u < VPT; ++u) {
+                const uint32_t j = t + u * group;
+                if (j < vecs) o[u] = ld_stream(br + (uint64_t) j * 8);
+            }
+#pragma unroll
+            for (int u = 0; u < VPT; ++u) {
+                const uint32_t j = t + u * group;
+                if (j < vecs) {
+                    v[u] = add_vec_f16(v[u], o[u]);
+                    st_stream(sr + (uint64_t) j * 8, v[u]);
+                }
+            }
         }
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
@@ -148,17 +195,29 @@ __global__ void rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void 
 
 // Any alignment, any d: one CTA per row, two passes over x (the second one is
 // served by L2).
-template<bool W_F16>
+template<bool W_F16, bool FUSED>
 __global__ void rms_norm_generic_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint64_t d,
-                                        int64_t stride_y, int64_t stride_x, float eps) {
+                                        int64_t stride_y, int64_t stride_x, float eps, Residual res) {
     __shared__ float red[32];
     for (uint64_t row = blockIdx.x; row < n; row += gridDim.x) {
         const uint16_t *xr = x + (int64_t) row * stride_x;
         uint16_t *yr = y + (int64_t) row * stride_y;
         float ss = 0.f;
-        for (uint64_t j = threadIdx.x; j < d; j += blockDim.x) {
-            const float f = f16_to_f32(xr[j]);
-            ss = fmaf(f, f, ss);
+        if (FUSED) {// the sum is written here and read back below by the thread that wrote it
+            const uint16_t *br = res.b + (int64_t) row * res.stride_b;
+            uint16_t *sr = res.sum + (int64_t) row * res.stride_sum;
+            for (uint64_t j = threadIdx.x; j < d; j += blockDim.x) {
+                const uint16_t h = f32_to_f16_ref(__fadd_rn(f16_to_f32(xr[j]), f16_to_f32(br[j])));
+                sr[j] = h;
+                const float f = f16_to_f32(h);
+                ss = fmaf(f, f, ss);
+            }
+            xr = sr;
+        } else {
+            for (uint64_t j = threadIdx.x; j < d; j += blockDim.x) {
+                const float f = f16_to_f32(xr[j]);
+                ss = fmaf(f, f, ss);
+            }
         }
         ss = cta_reduce<false>(ss, red);
         const double k = rms_scale(ss, d, eps);
@@ -171,34 +230,88 @@ __global__ void rms_norm_generic_kernel(uint16_t *y, const uint16_t *x, const vo
     }
 }
 
-template<int VPT, bool W_F16>
+template<int VPT, bool W_F16, bool FUSED>
 void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t vecs, void *y, const void *x,
-                 const void *w, cudaStream_t st) {
+                 const void *w, Residual res, cudaStream_t st) {
     auto *yp = reinterpret_cast<uint16_t *>(y);
     auto *xp = reinterpret_cast<const uint16_t *>(x);
     if (cta_row) {
         const uint64_t cap = 0x7FFFFFFFull;// one CTA per row; rows beyond 2^31 loop
         const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap);
-        rms_norm_regs_kernel<VPT, W_F16, true>
-            <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon);
+        rms_norm_regs_kernel<VPT, W_F16, true, FUSED>
+            <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
     } else {
         const uint64_t ctas = (d->n + 7) / 8;
         const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-        rms_norm_regs_kernel<VPT, W_F16, false>
-            <<<grid, 256, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon);
+        rms_norm_regs_kernel<VPT, W_F16, false, FUSED>
+            <<<grid, 256, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
     }
 }
 
-template<bool W_F16>
+template<bool W_F16, bool FUSED>
 void dispatch_regs(const RMSNormDesc *d, int vpt, bool cta_row, uint32_t threads, uint32_t vecs, void *y,
-                   const void *x, const void *w, cudaStream_t st) {
+                   const void *x, const void *w, Residual res, cudaStream_t st) {
     switch (vpt) {
-        case 1: launch_regs<1, W_F16>(d, cta_row, threads, vecs, y, x, w, st); break;
-        case 2: launch_regs<2, W_F16>(d, cta_row, threads, vecs, y, x, w, st); break;
-        case 4: launch_regs<4, W_F16>(d, cta_row, threads, vecs, y, x, w, st); break;
-        default: launch_regs<8, W_F16>(d, cta_row, threads, vecs, y, x, w, st); break;
+        case 1: launch_regs<1, W_F16, FUSED>(d, cta_row, threads, vecs, y, x, w, res, st); break;
+        case 2: launch_regs<2, W_F16, FUSED>(d, cta_row, threads, vecs, y, x, w, res, st); break;
+        case 4: launch_regs<4, W_F16, FUSED>(d, cta_row, threads, vecs, y, x, w, res, st); break;
+        default: launch_regs<8, W_F16, FUSED>(d, cta_row, threads, vecs, y, x, w, res, st); break;
     }
+}
+
+// Kernel choice and launch for both forms; `b` and `sum` are null for the plain one.
+template<bool FUSED>
+infiniopStatus_t run(const RMSNormDesc *d, void *y, const void *x, const void *w, const void *b, void *sum,
+                     cudaStream_t st) {
+    const Residual res{reinterpret_cast<const uint16_t *>(b), reinterpret_cast<uint16_t *>(sum), d->stride_b,
+                       d->stride_sum};
+    bool vec_ok = d->d % 8 == 0 && d->d / 8 <= 8192 && d->stride_x % 8 == 0 && d->stride_y % 8 == 0 &&
+                  aligned16(y) && aligned16(x) && aligned16(w);
+    // the fused form holds two operands per vector: rows of up to 4096 vectors (4 per thread), longer ones go the scalar way
+    if (FUSED) {
+        vec_ok = vec_ok && d->d / 8 <= 4096 && d->stride_b % 8 == 0 && d->stride_sum % 8 == 0 && aligned16(b) &&
+                 aligned16(sum);
+    }
+    if (vec_ok) {
+        const uint32_t vecs = (uint32_t) (d->d / 8);
+        // Enough rows to fill the GPU: favour bytes in flight per thread (8
+        // vectors each, a warp per row when the row fits).  Few rows: favour
+        // latency, spread each row over as many threads as it has vectors.
+        const bool big = d->n * (uint64_t) vecs >= (1u << 20);
+        int vpt;
+        bool cta_row;
+        uint32_t threads = 256;
+        if (big && vecs <= (FUSED ? 128u : 256u)) {// the fused form holds two operands: half the vectors per thread
+            cta_row = false;
+            const uint32_t need = (vecs + 31) / 32;
+            vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+        } else {
+            cta_row = true;
+            const uint32_t min_vpt = (vecs + 1023) / 1024;
+            // measured on [32768, 4096] / [16384, 8192] / [8192, 16384]: 4 vectors per thread 0.88 / 0.87 / 0.81 of the
+            // copy bandwidth, 8 vectors 0.79 / 0.78 / 0.70, 2 vectors 0.75 / 0.71 / 0.59
+            uint32_t want = big ? (FUSED ? 2 : 4) : min_vpt;
+            if (want < min_vpt) want = min_vpt;
+            vpt = want <= 1 ? 1 : want <= 2 ? 2 : want <= 4 ? 4 : 8;
+            threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;
+        }
+        if (d->w_f16) dispatch_regs<true, FUSED>(d, vpt, cta_row, threads, vecs, y, x, w, res, st);
+        else dispatch_regs<false, FUSED>(d, vpt, cta_row, threads, vecs, y, x, w, res, st);
+        return check_launch("rms_norm");
+    }
+    const uint64_t cap = (uint64_t) d->sm_count * 8;
+    const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap);
+    auto *yp = reinterpret_cast<uint16_t *>(y);
+    auto *xp = reinterpret_cast<const uint16_t *>(x);
+    if (d->w_f16) {
+        rms_norm_generic_kernel<true, FUSED>
+            <<<grid, 256, 0, st>>>(yp, xp, w, d->n, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+    } else {
+        rms_norm_generic_kernel<false, FUSED>
+            <<<grid, 256, 0, st>>>(yp, xp, w, d->n, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+    }
+    return check_launch("rms_norm");
 }
 
 }// namespace
@@ -225,7 +338,7 @@ INFINIOP_API infiniopStatus_t infiniopCreateRMSNormDescriptor(infiniopHandle_t h
     auto *h = reinterpret_cast<Handle *>(handle);
     auto *r = new (std::nothrow) RMSNormDesc{DevNvGpu, h->device_id,         h->sm_count,           n,
                                              d,        y_desc->strides[0],   x_desc->strides[0],    dt_eq(w_desc->dt, F16),
-                                             epsilon};
+                                             epsilon,  false,                0,                     0};
     if (r == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
     *desc_ptr = reinterpret_cast<infiniopRMSNormDescriptor_t>(r);
     return STATUS_SUCCESS;
@@ -246,52 +359,84 @@ INFINIOP_API infiniopStatus_t infiniopRMSNorm(infiniopRMSNormDescriptor_t desc, 
     if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
     if (y == nullptr || x == nullptr || w == nullptr) return STATUS_BAD_PARAM;
     auto *d = reinterpret_cast<RMSNormDesc *>(desc);
+    if (d->fused) return STATUS_BAD_PARAM;// a descriptor of the fused form
     if (d->n == 0 || d->d == 0) return STATUS_SUCCESS;
     DeviceGuard guard(d->device_id);
     auto st = reinterpret_cast<cudaStream_t>(stream);
-
-    const bool vec_ok = d->d % 8 == 0 && d->d / 8 <= 8192 && d->stride_x % 8 == 0 && d->stride_y % 8 == 0 &&
-                        aligned16(y) && aligned16(x) && aligned16(w);
-    if (vec_ok) {
-        const uint32_t vecs = (uint32_t) (d->d / 8);
-        // Enough rows to fill the GPU: favour bytes in flight per thread (8
-        // vectors each, a warp per row when the row fits).  Few rows: favour
-        // latency, spread each row over as many threads as it has vectors.
-        const bool big = d->n * (uint64_t) vecs >= (1u << 20);
-        int vpt;
-        bool cta_row;
-        uint32_t threads = 256;
-        if (big && vecs <= 256) {
-            cta_row = false;
-            const uint32_t need = (vecs + 31) / 32;
-            vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
-        } else {
-            cta_row = true;
-            const uint32_t min_vpt = (vecs + 1023) / 1024;
-            // measured on [32768, 4096] / [16384, 8192] / [8192, 16384]: 4 vectors per thread 0.88 / 0.87 / 0.81 of the
-            // copy bandwidth, 8 vectors 0.79 / 0.78 / 0.70, 2 vectors 0.75 / 0.71 / 0.59
-            uint32_t want = big ? 4 : min_vpt;
-            if (want < min_vpt) want = min_vpt;
-            vpt = want <= 1 ? 1 : want <= 2 ? 2 : want <= 4 ? 4 : 8;
-            threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;
-        }
-        if (d->w_f16) dispatch_regs<true>(d, vpt, cta_row, threads, vecs, y, x, w, st);
-        else dispatch_regs<false>(d, vpt, cta_row, threads, vecs, y, x, w, st);
-        return check_launch("rms_norm");
-    }
-    const uint64_t cap = (uint64_t) d->sm_count * 8;
-    const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap);
-    auto *yp = reinterpret_cast<uint16_t *>(y);
-    auto *xp = reinterpret_cast<const uint16_t *>(x);
-    if (d->w_f16) {
-        rms_norm_generic_kernel<true><<<grid, 256, 0, st>>>(yp, xp, w, d->n, d->d, d->stride_y, d->stride_x, d->epsilon);
-    } else {
-        rms_norm_generic_kernel<false><<<grid, 256, 0, st>>>(yp, xp, w, d->n, d->d, d->stride_y, d->stride_x, d->epsilon);
-    }
-    return check_launch("rms_norm");
+    return run<false>(d, y, x, w, nullptr, nullptr, st);
 }
 
 INFINIOP_API infiniopStatus_t infiniopDestroyRMSNormDescriptor(infiniopRMSNormDescriptor_t desc) {
+    if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    delete reinterpret_cast<RMSNormDesc *>(desc);
+    return STATUS_SUCCESS;
+}
+
+// ---- fused residual form: sum = a + b, y = RMSNorm(sum) * w (no counterpart in the reference) ----------------
+INFINIOP_API infiniopStatus_t infiniopCreateAddRMSNormDescriptor(infiniopHandle_t handle,
+                                                                 infiniopAddRMSNormDescriptor_t *desc_ptr,
+                                                                 infiniopTensorDescriptor_t y_desc,
+                                                                 infiniopTensorDescriptor_t sum_desc,
+                                                                 infiniopTensorDescriptor_t a_desc,
+                                                                 infiniopTensorDescriptor_t b_desc,
+                                                                 infiniopTensorDescriptor_t w_desc, float epsilon) {
+    if (handle == nullptr || handle->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (desc_ptr == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    if (y_desc == nullptr || sum_desc == nullptr || a_desc == nullptr || b_desc == nullptr || w_desc == nullptr) {
+        return STATUS_BAD_PARAM;
+    }
+    // the checks of the RMSNorm descriptor, applied to all four row tensors; no broadcasting
+    infiniopTensorDescriptor_t rows[4] = {y_desc, sum_desc, a_desc, b_desc};
+    for (auto *t : rows) {
+        if (t->ndim != 2) return STATUS_BAD_TENSOR_SHAPE;
+    }
+    if (w_desc->ndim != 1) return STATUS_BAD_TENSOR_SHAPE;
+    const uint64_t n = y_desc->shape[0], d = y_desc->shape[1];
+    for (auto *t : rows) {
+        if (t->shape[0] != n || t->shape[1] != d) return STATUS_BAD_TENSOR_SHAPE;
+    }
+    if (w_desc->shape[0] != d) return STATUS_BAD_TENSOR_SHAPE;
+    for (auto *t : rows) {
+        if (!dt_eq(t->dt, F16)) return STATUS_BAD_TENSOR_DTYPE;
+    }
+    if (!dt_eq(w_desc->dt, F16) && !dt_eq(w_desc->dt, F32)) return STATUS_BAD_TENSOR_DTYPE;
+    for (auto *t : rows) {
+        if (t->strides[1] != 1) return STATUS_BAD_TENSOR_STRIDES;
+    }
+    if (w_desc->strides[0] != 1) return STATUS_BAD_TENSOR_STRIDES;
+
+    auto *h = reinterpret_cast<Handle *>(handle);
+    auto *r = new (std::nothrow) RMSNormDesc{DevNvGpu, h->device_id,        h->sm_count,          n,
+                                             d,        y_desc->strides[0],  a_desc->strides[0],   dt_eq(w_desc->dt, F16),
+                                             epsilon,  true,                b_desc->strides[0],   sum_desc->strides[0]};
+    if (r == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    *desc_ptr = reinterpret_cast<infiniopAddRMSNormDescriptor_t>(r);
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopGetAddRMSNormWorkspaceSize(infiniopAddRMSNormDescriptor_t desc, uint64_t *size) {
+    if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (size == nullptr) return STATUS_BAD_PARAM;
+    *size = 0;
+    return STATUS_SUCCESS;
+}
+
+// `sum` may be `a` or `b` (the residual updated in place); `y` must not overlap `sum`.
+INFINIOP_API infiniopStatus_t infiniopAddRMSNorm(infiniopAddRMSNormDescriptor_t desc, void *workspace,
+                                                 uint64_t workspace_size, void *y, void *sum, void const *a,
+                                                 void const *b, void const *w, void *stream) {
+    (void) workspace;
+    (void) workspace_size;
+    if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (y == nullptr || sum == nullptr || a == nullptr || b == nullptr || w == nullptr) return STATUS_BAD_PARAM;
+    auto *d = reinterpret_cast<RMSNormDesc *>(desc);
+    if (!d->fused) return STATUS_BAD_PARAM;
+    if (d->n == 0 || d->d == 0) return STATUS_SUCCESS;
+    DeviceGuard guard(d->device_id);
+    return run<true>(d, y, a, w, b, sum, reinterpret_cast<cudaStream_t>(stream));
+}
+
+INFINIOP_API infiniopStatus_t infiniopDestroyAddRMSNormDescriptor(infiniopAddRMSNormDescriptor_t desc) {
     if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
     delete reinterpret_cast<RMSNormDesc *>(desc);
     return STATUS_SUCCESS;

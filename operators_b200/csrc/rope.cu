@@ -20,6 +20,12 @@
 //    dimension); the thread keeps its slice of the sin/cos rows in registers
 //    and walks over the heads with several 128-bit loads in flight.  The
 //    environment variable INFINIOP_ROPE_KERNEL (any value) forces this one.
+//
+// rope_kernel also serves infiniopRoPERearrange (not in the reference): the
+// rotated values of `src` are written to a second view `dst` of the same shape
+// with its own strides, e.g. the rows of the K cache at the tokens' positions,
+// so the rotation and the cache write (reference src/ops/attention/operator.cc:
+// 87-91: a rearrange of k into k_cache) cost one pass over k instead of two.
 #include "common.cuh"
 #include "rope_pipeline.cuh"
 
@@ -37,6 +43,8 @@ struct RoPEDesc {
     int max_smem_optin;
     uint64_t seq_len, nhead, dim;
     int64_t stride_0, stride_1;
+    bool to_dst;                 // RoPERearrange: rotated values go to a second view
+    int64_t dstride_0, dstride_1;
 };
 
 // One slice = V halves of one head (V = 8: a 128-bit vector, V = 2: one pair).
@@ -78,9 +86,9 @@ constexpr int kHeadsInFlight = 4;// measured at [4096,32,128]: 4 -> 23 us, 2 -> 
 // of slices_per_head, so a thread's slice index within the head never changes
 // while it strides over (head, slice) items: its table values load once.
 template<int V, bool ALIGNED>
-__global__ void __launch_bounds__(256, 4) rope_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table,
+__global__ void __launch_bounds__(256, 4) rope_kernel(uint16_t *dst, const uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table,
                             uint64_t seq_len, uint32_t nhead, uint32_t dim, int64_t stride_0, int64_t stride_1,
-                            uint32_t threads_per_token, uint32_t slices_per_head) {
+                            int64_t dstride_0, int64_t dstride_1, uint32_t threads_per_token, uint32_t slices_per_head) {
     const uint32_t tok_in_cta = threadIdx.x / threads_per_token;
     const uint32_t lt = threadIdx.x - tok_in_cta * threads_per_token;
     const uint32_t tokens_per_cta = blockDim.x / threads_per_token;
@@ -97,7 +105,8 @@ __global__ void __launch_bounds__(256, 4) rope_kernel(uint16_t *t, const uint64_
          tok += (uint64_t) gridDim.x * tokens_per_cta) {
         const uint64_t p = pos_ids[tok];
         for (uint32_t slice = slice0; slice < slices_per_head; slice += slice_step) {
-            uint16_t *base = t + (int64_t) tok * stride_0 + slice * V;
+            const uint16_t *base = t + (int64_t) tok * stride_0 + slice * V;
+            uint16_t *out = dst + (int64_t) tok * dstride_0 + slice * V;
             // First group of heads goes in flight before the position id is
             // needed: the pos -> table-address -> table-load chain then overlaps
             // with the loads of t instead of preceding them.
@@ -134,7 +143,7 @@ __global__ void __launch_bounds__(256, 4) rope_kernel(uint16_t *t, const uint64_
                             const float r1 = __fadd_rn(__fmul_rn(ab.x, sn[2 * k + 1]), __fmul_rn(ab.y, cs[2 * k + 1]));
                             x[u].w[k] = pack2_ref(r0, r1);// both halves with one truncating conversion
                         }
-                        x[u].store(base + (int64_t) hh * stride_1);
+                        x[u].store(out + (int64_t) hh * dstride_1);
                     }
                 }
                 // next group of heads for this thread, if any
@@ -179,7 +188,8 @@ INFINIOP_API infiniopStatus_t infiniopCreateRoPEDescriptor(infiniopHandle_t hand
 
     auto *h = reinterpret_cast<Handle *>(handle);
     auto *d = new (std::nothrow)
-        RoPEDesc{DevNvGpu, h->device_id, h->sm_count, h->max_smem_optin, seq_len, nhead, dim, t->strides[0], t->strides[1]};
+        RoPEDesc{DevNvGpu, h->device_id, h->sm_count, h->max_smem_optin, seq_len, nhead, dim, t->strides[0], t->strides[1],
+                 false,    0,            0};
     if (d == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
     *desc_ptr = reinterpret_cast<infiniopRoPEDescriptor_t>(d);
     return STATUS_SUCCESS;
@@ -192,19 +202,15 @@ INFINIOP_API infiniopStatus_t infiniopGetRoPEWorkspaceSize(infiniopRoPEDescripto
     return STATUS_SUCCESS;
 }
 
-INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *workspace, uint64_t workspace_size,
-                                           void *t, void const *pos_ids, void const *sin_table,
-                                           void const *cos_table, void *stream) {
-    (void) workspace;
-    (void) workspace_size;
-    if (desc == nullptr) return STATUS_BAD_DEVICE;
-    auto *d = reinterpret_cast<RoPEDesc *>(desc);
-    if (d->device != DevNvGpu) return STATUS_BAD_DEVICE;
-    if (t == nullptr || pos_ids == nullptr || sin_table == nullptr || cos_table == nullptr) return STATUS_BAD_PARAM;
-    if (d->seq_len == 0 || d->nhead == 0 || d->dim == 0) return STATUS_SUCCESS;
-    DeviceGuard guard(d->device_id);
-    auto st = reinterpret_cast<cudaStream_t>(stream);
-    auto *tp = reinterpret_cast<uint16_t *>(t);
+namespace {
+
+// Kernel choice and launch; `out` is `t` itself for the in-place operator.
+infiniopStatus_t run(const RoPEDesc *d, void *out, const void *t, void const *pos_ids, void const *sin_table,
+                     void const *cos_table, cudaStream_t st) {
+    const bool in_place = !d->to_dst;
+    const int64_t dstride_0 = in_place ? d->stride_0 : d->dstride_0, dstride_1 = in_place ? d->stride_1 : d->dstride_1;
+    auto *tp = reinterpret_cast<uint16_t *>(const_cast<void *>(t));
+    auto *op = reinterpret_cast<uint16_t *>(out);
     auto *pp = reinterpret_cast<const uint64_t *>(pos_ids);
     auto *sp = reinterpret_cast<const float *>(sin_table);
     auto *cp = reinterpret_cast<const float *>(cos_table);
@@ -213,9 +219,11 @@ INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *
     // Widest slice the layout allows: 8 halves need 16-byte aligned rows of t
     // and of both tables (dh % 8 == 0 makes p*dh*4 a multiple of 32 bytes).
     const bool v8 = dim % 8 == 0 && d->stride_0 % 8 == 0 && d->stride_1 % 8 == 0 && aligned16(t) &&
-                    aligned16(sin_table) && aligned16(cos_table);
+                    dstride_0 % 8 == 0 && dstride_1 % 8 == 0 && aligned16(out) && aligned16(sin_table) &&
+                    aligned16(cos_table);
     // Contiguous token rows of a size that leaves room for a few stages: the bulk-copy pipeline.
-    if (v8 && d->stride_1 == (int64_t) dim && d->seq_len <= 0xFFFFFFFFull && getenv("INFINIOP_ROPE_KERNEL") == nullptr) {
+    if (in_place && v8 && d->stride_1 == (int64_t) dim && d->seq_len <= 0xFFFFFFFFull &&
+        getenv("INFINIOP_ROPE_KERNEL") == nullptr) {
         namespace rp = rope_pipe;
         rp::Plan plan;
         plan.row_bytes = nhead * dim * 2u;
@@ -248,7 +256,8 @@ INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *
             return check_launch("rope_pipeline");
         }
     }
-    const bool v2_aligned = d->stride_0 % 2 == 0 && d->stride_1 % 2 == 0 && aligned4(t);
+    const bool v2_aligned = d->stride_0 % 2 == 0 && d->stride_1 % 2 == 0 && aligned4(t) && dstride_0 % 2 == 0 &&
+                            dstride_1 % 2 == 0 && aligned4(out);
     const uint32_t V = v8 ? 8 : 2;
     const uint32_t slices = dim / V;
     // threads per token: a multiple of `slices`, about (items / kHeadsInFlight)
@@ -269,16 +278,104 @@ INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *
     const uint64_t cap = 0x7FFFFFFFull;// one CTA per token group; more tokens than that loop
     const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
     if (v8) {
-        rope_kernel<8, true><<<grid, threads, 0, st>>>(tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1, tpt, slices);
+        rope_kernel<8, true><<<grid, threads, 0, st>>>(op, tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1,
+                                                        dstride_0, dstride_1, tpt, slices);
     } else if (v2_aligned) {
-        rope_kernel<2, true><<<grid, threads, 0, st>>>(tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1, tpt, slices);
+        rope_kernel<2, true><<<grid, threads, 0, st>>>(op, tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1,
+                                                        dstride_0, dstride_1, tpt, slices);
     } else {
-        rope_kernel<2, false><<<grid, threads, 0, st>>>(tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1, tpt, slices);
+        rope_kernel<2, false><<<grid, threads, 0, st>>>(op, tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1,
+                                                        dstride_0, dstride_1, tpt, slices);
     }
     return check_launch("rope");
 }
 
+}// namespace
+
+INFINIOP_API infiniopStatus_t infiniopRoPE(infiniopRoPEDescriptor_t desc, void *workspace, uint64_t workspace_size,
+                                           void *t, void const *pos_ids, void const *sin_table,
+                                           void const *cos_table, void *stream) {
+    (void) workspace;
+    (void) workspace_size;
+    if (desc == nullptr) return STATUS_BAD_DEVICE;
+    auto *d = reinterpret_cast<RoPEDesc *>(desc);
+    if (d->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (t == nullptr || pos_ids == nullptr || sin_table == nullptr || cos_table == nullptr) return STATUS_BAD_PARAM;
+    if (d->to_dst) return STATUS_BAD_PARAM;// a descriptor of infiniopRoPERearrange
+    if (d->seq_len == 0 || d->nhead == 0 || d->dim == 0) return STATUS_SUCCESS;
+    DeviceGuard guard(d->device_id);
+    return run(d, t, t, pos_ids, sin_table, cos_table, reinterpret_cast<cudaStream_t>(stream));
+}
+
 INFINIOP_API infiniopStatus_t infiniopDestroyRoPEDescriptor(infiniopRoPEDescriptor_t desc) {
+    if (desc == nullptr) return STATUS_BAD_DEVICE;
+    delete reinterpret_cast<RoPEDesc *>(desc);
+    return STATUS_SUCCESS;
+}
+
+// ---- rotation written to a second view (no counterpart in the reference) ----------------------------------
+INFINIOP_API infiniopStatus_t infiniopCreateRoPERearrangeDescriptor(infiniopHandle_t handle,
+                                                                    infiniopRoPERearrangeDescriptor_t *desc_ptr,
+                                                                    infiniopTensorDescriptor_t dst,
+                                                                    infiniopTensorDescriptor_t src,
+                                                                    infiniopTensorDescriptor_t pos_ids,
+                                                                    infiniopTensorDescriptor_t sin_table,
+                                                                    infiniopTensorDescriptor_t cos_table) {
+    if (handle == nullptr || handle->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (desc_ptr == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
+    if (dst == nullptr) return STATUS_BAD_PARAM;
+    // `src` passes the checks of the in-place operator; `dst` must be a view of the same shape and type
+    infiniopRoPEDescriptor_t made = nullptr;
+    const infiniopStatus_t status = infiniopCreateRoPEDescriptor(handle, &made, src, pos_ids, sin_table, cos_table);
+    if (status != STATUS_SUCCESS) return status;
+    auto *d = reinterpret_cast<RoPEDesc *>(made);
+    infiniopStatus_t bad = STATUS_SUCCESS;
+    if (dst->ndim != 3 || dst->shape[0] != d->seq_len || dst->shape[1] != d->nhead || dst->shape[2] != d->dim) {
+        bad = STATUS_BAD_TENSOR_SHAPE;
+    } else if (dst->strides[2] != 1) {
+        bad = STATUS_BAD_TENSOR_STRIDES;
+    } else if (!dt_eq(dst->dt, F16)) {
+        bad = STATUS_BAD_TENSOR_DTYPE;
+    }
+    if (bad != STATUS_SUCCESS) {
+        delete d;
+        return bad;
+    }
+    d->to_dst = true;
+    d->dstride_0 = dst->strides[0];
+    d->dstride_1 = dst->strides[1];
+    *desc_ptr = reinterpret_cast<infiniopRoPERearrangeDescriptor_t>(d);
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopGetRoPERearrangeWorkspaceSize(infiniopRoPERearrangeDescriptor_t desc,
+                                                                    uint64_t *size) {
+    if (desc == nullptr) return STATUS_BAD_DEVICE;
+    if (size == nullptr) return STATUS_BAD_PARAM;
+    *size = 0;
+    return STATUS_SUCCESS;
+}
+
+// `dst` and `src` must not overlap unless they are the same view (then this is infiniopRoPE).
+INFINIOP_API infiniopStatus_t infiniopRoPERearrange(infiniopRoPERearrangeDescriptor_t desc, void *workspace,
+                                                    uint64_t workspace_size, void *dst, void const *src,
+                                                    void const *pos_ids, void const *sin_table,
+                                                    void const *cos_table, void *stream) {
+    (void) workspace;
+    (void) workspace_size;
+    if (desc == nullptr) return STATUS_BAD_DEVICE;
+    auto *d = reinterpret_cast<RoPEDesc *>(desc);
+    if (d->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (dst == nullptr || src == nullptr || pos_ids == nullptr || sin_table == nullptr || cos_table == nullptr) {
+        return STATUS_BAD_PARAM;
+    }
+    if (!d->to_dst) return STATUS_BAD_PARAM;
+    if (d->seq_len == 0 || d->nhead == 0 || d->dim == 0) return STATUS_SUCCESS;
+    DeviceGuard guard(d->device_id);
+    return run(d, dst, src, pos_ids, sin_table, cos_table, reinterpret_cast<cudaStream_t>(stream));
+}
+
+INFINIOP_API infiniopStatus_t infiniopDestroyRoPERearrangeDescriptor(infiniopRoPERearrangeDescriptor_t desc) {
     if (desc == nullptr) return STATUS_BAD_DEVICE;
     delete reinterpret_cast<RoPEDesc *>(desc);
     return STATUS_SUCCESS;

@@ -41,6 +41,14 @@ def _declare(lib):
         "infiniopCreateRearrangeDescriptor": [H, POINTER(D), T, T],
         "infiniopRearrange": [D, c_void_p, c_void_p, c_void_p],
         "infiniopDestroyRearrangeDescriptor": [D],
+        "infiniopCreateRoPERearrangeDescriptor": [H, POINTER(D), T, T, T, T, T],
+        "infiniopGetRoPERearrangeWorkspaceSize": [D, POINTER(c_uint64)],
+        "infiniopRoPERearrange": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroyRoPERearrangeDescriptor": [D],
+        "infiniopCreateAddRMSNormDescriptor": [H, POINTER(D), T, T, T, T, T, c_float],
+        "infiniopGetAddRMSNormWorkspaceSize": [D, POINTER(c_uint64)],
+        "infiniopAddRMSNorm": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroyAddRMSNormDescriptor": [D],
         "infiniopCreateCausalSoftmaxDescriptor": [H, POINTER(D), T],
         "infiniopGetCausalSoftmaxWorkspaceSize": [D, POINTER(c_uint64)],
         "infiniopCausalSoftmax": [D, c_void_p, c_uint64, c_void_p, c_void_p],
@@ -140,6 +148,24 @@ class RMSNormOp(_Op):
                                              x.data_ptr(), w.data_ptr(), _stream_ptr(stream)))
 
 
+class AddRMSNormOp(_Op):
+    """sum = a + b, y = RMSNorm(sum) * w in one pass (an addition of this library: what the
+    reference's callers get from its Add followed by its RMSNorm)."""
+    _destroy, _wsize = "infiniopDestroyAddRMSNormDescriptor", "infiniopGetAddRMSNormWorkspaceSize"
+
+    def __init__(self, lib, handle, y, total, a, b, w, epsilon=1e-5):
+        super().__init__(lib, handle)
+        ts = [self._t(x) for x in (y, total, a, b, w)]
+        check_error(lib.infiniopCreateAddRMSNormDescriptor(handle, ctypes.byref(self.desc),
+                                                           *[t.descriptor for t in ts], epsilon))
+        self._make_workspace(y.device)
+
+    def __call__(self, y, total, a, b, w, stream=None):
+        check_error(self.lib.infiniopAddRMSNorm(self.desc, self._ws_ptr(), self.workspace_size, y.data_ptr(),
+                                                total.data_ptr(), a.data_ptr(), b.data_ptr(), w.data_ptr(),
+                                                _stream_ptr(stream)))
+
+
 class RoPEOp(_Op):
     _destroy, _wsize = "infiniopDestroyRoPEDescriptor", "infiniopGetRoPEWorkspaceSize"
 
@@ -156,6 +182,26 @@ class RoPEOp(_Op):
         check_error(self.lib.infiniopRoPE(self.desc, self._ws_ptr(), self.workspace_size, t.data_ptr(),
                                           pos_ids.data_ptr(), sin_table.data_ptr(), cos_table.data_ptr(),
                                           _stream_ptr(stream)))
+
+
+class RoPERearrangeOp(_Op):
+    """dst = RoPE(src) with dst a second view of the same shape (e.g. rows of the K cache); an
+    addition of this library: the reference's RoPE followed by its rearrange."""
+    _destroy, _wsize = "infiniopDestroyRoPERearrangeDescriptor", "infiniopGetRoPERearrangeWorkspaceSize"
+
+    def __init__(self, lib, handle, dst, src, pos_ids, sin_table, cos_table):
+        super().__init__(lib, handle)
+        dt, st_, pt = self._t(dst), self._t(src), self._t(pos_ids, U64)
+        sn, cs = self._t(sin_table), self._t(cos_table)
+        check_error(lib.infiniopCreateRoPERearrangeDescriptor(handle, ctypes.byref(self.desc), dt.descriptor,
+                                                              st_.descriptor, pt.descriptor, sn.descriptor,
+                                                              cs.descriptor))
+        self._make_workspace(dst.device)
+
+    def __call__(self, dst, src, pos_ids, sin_table, cos_table, stream=None):
+        check_error(self.lib.infiniopRoPERearrange(self.desc, self._ws_ptr(), self.workspace_size, dst.data_ptr(),
+                                                   src.data_ptr(), pos_ids.data_ptr(), sin_table.data_ptr(),
+                                                   cos_table.data_ptr(), _stream_ptr(stream)))
 
 
 class SwiGLUOp(_Op):
@@ -266,6 +312,16 @@ class RandomSampleOp(_Op):
 
 
 # ---- one-shot forms ----------------------------------------------------------
+
+def rope_rearrange(lib, handle, dst, src, pos_ids, sin_table, cos_table, stream=None):
+    with RoPERearrangeOp(lib, handle, dst, src, pos_ids, sin_table, cos_table) as op:
+        op(dst, src, pos_ids, sin_table, cos_table, stream)
+
+
+def add_rms_norm(lib, handle, y, total, a, b, w, epsilon=1e-5, stream=None):
+    with AddRMSNormOp(lib, handle, y, total, a, b, w, epsilon) as op:
+        op(y, total, a, b, w, stream)
+
 
 def rms_norm(lib, handle, y, x, w, epsilon=1e-5, stream=None):
     with RMSNormOp(lib, handle, y, x, w, epsilon) as op:

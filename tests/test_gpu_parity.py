@@ -55,6 +55,69 @@ def test_rms_norm(oracle, cuda_lib, shape, stride, w_dtype):
     assert _few(mism, x.numel(), 0.02)  # only the order of the fp32 sum of squares differs
 
 
+# ---- fused residual add + RMSNorm (an addition of this library) ----------------------
+@pytest.mark.parametrize("w_dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("in_place", [False, True])
+@pytest.mark.parametrize("shape,stride", [((16, 2048), None), ((16, 2048), 4096), ((5, 33), None), ((1, 8), None),
+                                          ((700, 4096), None), ((2048, 2048), None), ((3, 16384), None),
+                                          ((2, 70000), None), ((9, 264), 272), ((4100, 1024), None),
+                                          ((600, 8192), None), ((40, 40000), None)])
+def test_add_rms_norm(oracle, cuda_lib, shape, stride, in_place, w_dtype):
+    """The sum is the Add operator's, bit for bit; the normalised rows are the
+    oracle's RMSNorm of that sum within the fp16 tolerance, and what this library's
+    Add followed by its RMSNorm write up to the grouping of the sum of squares."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(11)
+    a = (torch.rand(shape, generator=g) * 2 - 1).half()
+    b = (torch.randn(shape, generator=g) * 0.5).half()
+    w = (torch.rand(shape[1], generator=g) * 2 - 1).to(w_dtype)
+    want_sum = oracle.add(a.numpy(), b.numpy())
+    want_y = oracle.rms_norm(want_sum, w.numpy(), 1e-5)
+    ad, bd, wd = a.to(DEV), b.to(DEV), w.to(DEV)
+    yd = torch.full(shape, 7.0, dtype=torch.float16, device=DEV)
+    sd = torch.full(shape, 9.0, dtype=torch.float16, device=DEV)
+    # the two calls the fusion replaces, on contiguous copies (Add wants contiguous operands)
+    s2, y2 = torch.empty_like(ad), torch.empty_like(ad)
+    ops.add(lib, handle, s2, ad, bd)
+    ops.rms_norm(lib, handle, y2, s2, wd, 1e-5)
+    if stride is not None:
+        ad, bd, yd, sd = (rearrange_tensor(t, (stride, 1)) for t in (ad, bd, yd, sd))
+    if in_place:
+        sd = ad
+    ops.add_rms_norm(lib, handle, yd, sd, ad, bd, wd, 1e-5)
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(sd).reshape(shape), want_sum.view(np.uint16).reshape(shape))
+    assert np.array_equal(_bits(bd).reshape(shape), b.numpy().view(np.uint16))
+    mism = _close(_bits(yd).reshape(shape), want_y, 1e-3, 1e-3)
+    assert _few(mism, a.numel(), 0.02)
+    # against the two calls only the grouping of the fp32 sum of squares may differ
+    assert _few(int((_bits(yd).reshape(-1) != _bits(y2).reshape(-1)).sum()), a.numel(), 0.002)
+
+
+def test_add_rms_norm_status_codes(cuda_lib):
+    from operators_b200 import InfiniopError
+
+    lib, handle = cuda_lib
+    h = torch.zeros((4, 8), dtype=torch.float16, device=DEV)
+    f = torch.zeros((4, 8), dtype=torch.float32, device=DEV)
+
+    def status(fn):
+        with pytest.raises(InfiniopError) as e:
+            fn()
+        return e.value.status
+
+    assert status(lambda: ops.AddRMSNormOp(lib, handle, h, h, h, h[:2], h[0])) == 4
+    assert status(lambda: ops.AddRMSNormOp(lib, handle, h, h, h, h, h[0, :4])) == 4
+    assert status(lambda: ops.AddRMSNormOp(lib, handle, h, h, f, h, h[0])) == 3
+    assert status(lambda: ops.AddRMSNormOp(lib, handle, h, h[:, ::2], h[:, ::2], h[:, ::2], h[0, ::2])) == 4
+    assert status(lambda: ops.AddRMSNormOp(lib, handle, h[:, ::2], h[:, ::2], h[:, ::2], h[:, ::2], h[0, :4])) == 5
+    with ops.AddRMSNormOp(lib, handle, h, h, h, h, h[0]) as op:  # a descriptor of one form is refused by the other call
+        assert lib.infiniopRMSNorm(op.desc, None, 0, h.data_ptr(), h.data_ptr(), h.data_ptr(), None) == 2
+    with ops.RMSNormOp(lib, handle, h, h, h[0]) as op:
+        assert lib.infiniopAddRMSNorm(op.desc, None, 0, h.data_ptr(), h.data_ptr(), h.data_ptr(), h.data_ptr(),
+                                      h.data_ptr(), None) == 2
+
+
 # ---- RoPE (bit-exact) ----------------------------------------------------------
 @pytest.mark.parametrize("shape,strides", [((1, 32, 128), None), ((1, 32, 64), None), ((4, 1, 32), None),
                                            ((3, 32, 128), (8000, 200, 1)), ((64, 32, 128), None),
@@ -77,6 +140,65 @@ def test_rope(oracle, cuda_lib, shape, strides):
     ops.rope(lib, handle, td, pos.to(DEV), sin.to(DEV), cos.to(DEV))
     torch.cuda.synchronize()
     assert np.array_equal(_bits(td).reshape(shape), want.view(np.uint16))
+
+
+# ---- RoPE written into a second view, e.g. the K cache (an addition of this library; bit-exact) -------
+@pytest.mark.parametrize("tokens,heads,dh,src_strides,cache_len,first", [
+    (1, 8, 128, None, 64, 17), (7, 8, 128, None, 64, 50), (64, 8, 128, (40 * 128, 128, 1), 4096, 1000),
+    (5, 3, 6, None, 9, 2), (5, 3, 6, (37, 7, 1), 16, 0), (300, 4, 64, None, 300, 0),
+    (2048, 8, 128, (48 * 128, 128, 1), 4096, 2048), (33, 2, 256, None, 40, 3)])
+def test_rope_rearrange_into_cache(oracle, cuda_lib, tokens, heads, dh, src_strides, cache_len, first):
+    """k[tokens, heads, dh] (possibly a slice of a wider qkv row) is rotated and lands in
+    cache[heads, cache_len, dh] at rows first .. first+tokens; k itself and every other
+    byte of the cache stay as they were."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(12)
+    k = torch.randn((tokens, heads, dh), generator=g).half()
+    pos = torch.arange(first, first + tokens, dtype=torch.int64)
+    sin, cos = ops.sin_cos_table(first + tokens, dh)
+    want = oracle.rope(k.numpy().copy(), pos.numpy().astype(np.uint64), sin.numpy(), cos.numpy())
+    kd = k.to(DEV)
+    if src_strides is not None:
+        kd = rearrange_tensor(kd, src_strides)
+    cache = torch.full((heads, cache_len, dh), 3.0, dtype=torch.float16, device=DEV)
+    dst = cache[:, first:first + tokens, :].permute(1, 0, 2)  # [tokens, heads, dh] view of the cache rows
+    ops.rope_rearrange(lib, handle, dst, kd, pos.to(DEV), sin.to(DEV), cos.to(DEV))
+    torch.cuda.synchronize()
+    expect = np.full((heads, cache_len, dh), np.float16(3.0)).view(np.uint16)
+    expect[:, first:first + tokens, :] = want.view(np.uint16).transpose(1, 0, 2)
+    assert np.array_equal(_bits(cache), expect)
+    assert np.array_equal(_bits(kd).reshape(k.shape), k.numpy().view(np.uint16))
+    # the two calls it replaces write the same bytes
+    cache2 = torch.full((heads, cache_len, dh), 3.0, dtype=torch.float16, device=DEV)
+    k2 = kd.clone()
+    ops.rope(lib, handle, k2, pos.to(DEV), sin.to(DEV), cos.to(DEV))
+    ops.rearrange(lib, handle, cache2[:, first:first + tokens, :].permute(1, 0, 2), k2)
+    torch.cuda.synchronize()
+    assert torch.equal(cache, cache2)
+
+
+def test_rope_rearrange_status_codes(cuda_lib):
+    from operators_b200 import InfiniopError
+
+    lib, handle = cuda_lib
+    t = torch.zeros((4, 2, 8), dtype=torch.float16, device=DEV)
+    pos = torch.zeros(4, dtype=torch.int64, device=DEV)
+    tab = torch.zeros((8, 8), dtype=torch.float32, device=DEV)
+
+    def status(fn):
+        with pytest.raises(InfiniopError) as e:
+            fn()
+        return e.value.status
+
+    assert status(lambda: ops.RoPERearrangeOp(lib, handle, t[:3], t, pos, tab, tab)) == 4
+    assert status(lambda: ops.RoPERearrangeOp(lib, handle, t.float(), t, pos, tab, tab)) == 3
+    assert status(lambda: ops.RoPERearrangeOp(lib, handle, t[:, :, ::2], t[:, :, :4], pos, tab[:, :4], tab[:, :4])) == 5
+    assert status(lambda: ops.RoPERearrangeOp(lib, handle, t, t, pos[:3], tab, tab)) == 4
+    with ops.RoPERearrangeOp(lib, handle, t, t.clone(), pos, tab, tab) as op:
+        assert lib.infiniopRoPE(op.desc, None, 0, t.data_ptr(), pos.data_ptr(), tab.data_ptr(), tab.data_ptr(), None) == 2
+    with ops.RoPEOp(lib, handle, t, pos, tab, tab) as op:
+        assert lib.infiniopRoPERearrange(op.desc, None, 0, t.data_ptr(), t.data_ptr(), pos.data_ptr(), tab.data_ptr(),
+                                         tab.data_ptr(), None) == 2
 
 
 # ---- SwiGLU ------------------------------------------------------------------
