@@ -308,6 +308,32 @@ def run_b200(args):
                           "gbs": round(nbytes / ms_fused / 1e6, 1), "ms_rope_then_rearrange": round(ms_pair, 5),
                           "note": "back-to-back launches of one operator on L2-sized data; not a bench value"}))
         return
+    if args.only == "attention":  # not part of the step: one decoding token over a long KV cache
+        from operators_b200 import ops as _ops
+
+        nh, nkvh, dh, pos = 32, 8, ROPE_DH, 65535  # 268 MB of K and V rows per call: larger than L2
+        q = torch.randn((nh, 1, dh), device=dev).half()
+        k = torch.randn((nkvh, 1, dh), device=dev).half()
+        v = torch.randn((nkvh, 1, dh), device=dev).half()
+        k_cache = torch.randn((nkvh, pos + 1, dh), device=dev).half()
+        v_cache = torch.randn((nkvh, pos + 1, dh), device=dev).half()
+        out = torch.empty((1, nh, dh), device=dev, dtype=torch.float16)
+        op = _ops.AttentionOp(lib, handle, out, q, k, v, k_cache, v_cache, pos)
+        for _ in range(args.warmup):
+            op(out, q, k, v, k_cache, v_cache)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            op(out, q, k, v, k_cache, v_cache)
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / args.steps
+        nbytes = 2 * nkvh * (pos + 1) * dh * 2
+        print(json.dumps({"only": "attention", "q_heads": nh, "kv_heads": nkvh, "head_dim": dh, "cached_tokens": pos + 1,
+                          "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "launches_per_call": 3,
+                          "note": "back-to-back calls of one operator; bytes = K and V rows read once; not a bench value"}))
+        return
     inputs = make_inputs(1000 + rank, only=args.only)
     step = DecodeStep(lib, handle, dev, inputs)
     calls = step.calls()
@@ -737,7 +763,7 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
     ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of a CUDA graph of the step")
-    ap.add_argument("--only", choices=OPS + ["rearrange", "add_rms_norm", "rope_rearrange"],
+    ap.add_argument("--only", choices=OPS + ["rearrange", "add_rms_norm", "rope_rearrange", "attention"],
                     help="launch a single operator at its configuration (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

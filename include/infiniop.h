@@ -247,6 +247,31 @@ INFINIOP_API infiniopStatus_t infiniopAddRMSNorm(infiniopAddRMSNormDescriptor_t 
                                                  void const *b, void const *w, void *stream);
 INFINIOP_API infiniopStatus_t infiniopDestroyAddRMSNormDescriptor(infiniopAddRMSNormDescriptor_t desc);
 
+/* ---- attention: include/ops/attention/attention.h:9-37 --------------------- *
+ * k, v[n_kv_head, seq, dh] are written to k_cache, v_cache[n_kv_head, buf, dh]
+ * at rows pos .. pos+seq; out[seq, n_q_head, dh] (contiguous) = causal attention
+ * of q[n_q_head, seq, dh] over rows 0 .. pos+seq of the caches, scores scaled
+ * by 1/sqrt(dh).  fp16, unit innermost strides, dh <= 256.  `pos` is part of
+ * the descriptor, as in the reference.  The workspace must hold the reported
+ * size, else STATUS_MEMORY_NOT_ALLOCATED. */
+typedef struct AttentionDescriptor {
+    Device device;
+} AttentionDescriptor;
+typedef AttentionDescriptor *infiniopAttentionDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateAttentionDescriptor(infiniopHandle_t handle,
+                                                                infiniopAttentionDescriptor_t *desc_ptr,
+                                                                infiniopTensorDescriptor_t out_desc,
+                                                                infiniopTensorDescriptor_t q_desc,
+                                                                infiniopTensorDescriptor_t k_desc,
+                                                                infiniopTensorDescriptor_t v_desc,
+                                                                infiniopTensorDescriptor_t k_cache_desc,
+                                                                infiniopTensorDescriptor_t v_cache_desc, uint64_t pos);
+INFINIOP_API infiniopStatus_t infiniopGetAttentionWorkspaceSize(infiniopAttentionDescriptor_t desc, uint64_t *size);
+INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t desc, void *workspace,
+                                                uint64_t workspace_size, void *out, void const *q, void const *k,
+                                                void const *v, void *k_cache, void *v_cache, void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyAttentionDescriptor(infiniopAttentionDescriptor_t desc);
+
 /* ---- causal softmax: include/ops/causal_softmax/causal_softmax.h:7-25 ----- *
  * In place on fp16 [.., seq_len, total_seq_len] (2-D or 3-D, unit last
  * stride): row i keeps columns j <= total_seq_len - seq_len + i, the rest

@@ -41,6 +41,10 @@ def _declare(lib):
         "infiniopCreateRearrangeDescriptor": [H, POINTER(D), T, T],
         "infiniopRearrange": [D, c_void_p, c_void_p, c_void_p],
         "infiniopDestroyRearrangeDescriptor": [D],
+        "infiniopCreateAttentionDescriptor": [H, POINTER(D), T, T, T, T, T, T, c_uint64],
+        "infiniopGetAttentionWorkspaceSize": [D, POINTER(c_uint64)],
+        "infiniopAttention": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroyAttentionDescriptor": [D],
         "infiniopCreateRoPERearrangeDescriptor": [H, POINTER(D), T, T, T, T, T],
         "infiniopGetRoPERearrangeWorkspaceSize": [D, POINTER(c_uint64)],
         "infiniopRoPERearrange": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -184,6 +188,25 @@ class RoPEOp(_Op):
                                           _stream_ptr(stream)))
 
 
+class AttentionOp(_Op):
+    """out[seq, n_q_head, dh] = attention of q[n_q_head, seq, dh] over the caches after k, v[n_kv_head, seq, dh]
+    are written to their rows pos .. pos+seq (reference operatorspy/tests/attention.py; the position is part of
+    the descriptor, as in the reference)."""
+    _destroy, _wsize = "infiniopDestroyAttentionDescriptor", "infiniopGetAttentionWorkspaceSize"
+
+    def __init__(self, lib, handle, out, q, k, v, k_cache, v_cache, pos):
+        super().__init__(lib, handle)
+        ts = [self._t(x) for x in (out, q, k, v, k_cache, v_cache)]
+        check_error(lib.infiniopCreateAttentionDescriptor(handle, ctypes.byref(self.desc),
+                                                          *[t.descriptor for t in ts], int(pos)))
+        self._make_workspace(out.device)
+
+    def __call__(self, out, q, k, v, k_cache, v_cache, stream=None):
+        check_error(self.lib.infiniopAttention(self.desc, self._ws_ptr(), self.workspace_size, out.data_ptr(),
+                                               q.data_ptr(), k.data_ptr(), v.data_ptr(), k_cache.data_ptr(),
+                                               v_cache.data_ptr(), _stream_ptr(stream)))
+
+
 class RoPERearrangeOp(_Op):
     """dst = RoPE(src) with dst a second view of the same shape (e.g. rows of the K cache); an
     addition of this library: the reference's RoPE followed by its rearrange."""
@@ -312,6 +335,11 @@ class RandomSampleOp(_Op):
 
 
 # ---- one-shot forms ----------------------------------------------------------
+
+def attention(lib, handle, out, q, k, v, k_cache, v_cache, pos, stream=None):
+    with AttentionOp(lib, handle, out, q, k, v, k_cache, v_cache, pos) as op:
+        op(out, q, k, v, k_cache, v_cache, stream)
+
 
 def rope_rearrange(lib, handle, dst, src, pos_ids, sin_table, cos_table, stream=None):
     with RoPERearrangeOp(lib, handle, dst, src, pos_ids, sin_table, cos_table) as op:

@@ -51,6 +51,7 @@ def lib():
         L.oracle_add.argtypes = [vp, vp, vp, ci, u64, vp, vp, vp]
         L.oracle_rearrange.argtypes = [vp, vp, u64, u64, vp, vp, vp]
         L.oracle_causal_softmax_f16.argtypes = [vp, u64, u64, u64, i64, i64, i64]
+        L.oracle_matmul_f16.argtypes, L.oracle_matmul_f16.restype = [vp, vp, vp, cf, u64, u64, u64, u64, vp, vp, vp], None
         L.oracle_random_sample_f16.argtypes = [vp, vp, vp, ci, cf, cf, ci, cf]
         L.oracle_random_sample_workspace.argtypes, L.oracle_random_sample_workspace.restype = [ci], u64
         L.oracle_random_sample_trace.argtypes = [vp, vp, ci, ci, cf, vp, vp, vp, vp]
@@ -180,6 +181,43 @@ def causal_softmax(y):
         batch, sb = yu.shape[0], s[0]
     lib().oracle_causal_softmax_f16(_ptr(yu), batch, yu.shape[-2], yu.shape[-1], sb, s[-2], s[-1])
     return y
+
+
+def matmul(a, b, alpha=1.0):
+    """fp16 [batch, m, k] x [batch, k, n] -> contiguous fp16 [batch, m, n] (the arrays' own strides are used).
+    src/ops/matmul/cpu/matmul_cpu.cc:44-78 with beta = 0."""
+    au, bu = _u16(a), _u16(b)
+    assert au.ndim == 3 and bu.ndim == 3 and au.shape[0] == bu.shape[0] and au.shape[2] == bu.shape[1]
+    c = np.zeros((au.shape[0], au.shape[1], bu.shape[2]), np.uint16)
+    sc, sa, sb = ((ctypes.c_int64 * 3)(*_elem_strides(x)) for x in (c, au, bu))
+    lib().oracle_matmul_f16(_ptr(c), _ptr(au), _ptr(bu), float(alpha), au.shape[0], au.shape[1], bu.shape[2],
+                            au.shape[2], ctypes.addressof(sc), ctypes.addressof(sa), ctypes.addressof(sb))
+    return c.view(np.float16)
+
+
+def attention(q, k, v, k_cache, v_cache, pos):
+    """The attention composite, src/ops/attention/operator.cc:30-305, step by step with the
+    operators above: k and v copied into the caches at row `pos`, q made contiguous,
+    qk = matmul(q, full_k^T) * 1/sqrt(dh) with the q heads of one kv head stacked as rows,
+    causal softmax in place, matmul with full_v, rows permuted to out[seq, n_q_head, dh].
+    q [n_q_head, seq, dh], k and v [n_kv_head, seq, dh], caches [n_kv_head, buf_len, dh]
+    (numpy fp16 views, unit innermost stride); the caches are updated in place."""
+    nh, seq, dh = q.shape
+    nkvh = k.shape[0]
+    assert nh % nkvh == 0 and k.shape == v.shape == (nkvh, seq, dh)
+    group, total = nh // nkvh, seq + pos
+    rearrange(k_cache[:, pos:total, :], k)
+    rearrange(v_cache[:, pos:total, :], v)
+    qc = np.zeros(q.shape, np.float16)
+    rearrange(qc, q)
+    alpha = np.float32(1 / np.sqrt(np.float64(dh)))  # `float qk_alpha = 1 / sqrt(head_dim)`, operator.cc:136
+    qk = matmul(qc.reshape(nkvh, group * seq, dh), k_cache[:, :total, :].transpose(0, 2, 1), alpha)
+    qk = qk.reshape(nh, seq, total)
+    causal_softmax(qk)
+    temp = matmul(qk.reshape(nkvh, group * seq, total), v_cache[:, :total, :])
+    out = np.zeros((seq, nh, dh), np.float16)
+    rearrange(out, temp.reshape(nh, seq, dh).transpose(1, 0, 2))
+    return out
 
 
 def random_sample(logits, random_val, topp, topk, temperature, previous=0):

@@ -40,7 +40,7 @@ def test_reference_symbol_set(lib):
     ref = ["infiniopCreateHandle", "infiniopDestroyHandle", "infiniopCreateTensorDescriptor",
            "infiniopDestroyTensorDescriptor"]
     for op, ws in (("RMSNorm", True), ("RoPE", True), ("SwiGLU", False), ("Add", False), ("CausalSoftmax", True),
-                   ("RandomSample", True), ("Rearrange", False)):
+                   ("RandomSample", True), ("Rearrange", False), ("Attention", True)):
         ref += ["infiniopCreate%sDescriptor" % op, "infiniop%s" % op, "infiniopDestroy%sDescriptor" % op]
         if ws:
             ref.append("infiniopGet%sWorkspaceSize" % op)

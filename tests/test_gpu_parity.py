@@ -450,6 +450,96 @@ def test_random_sample_argmax_batch(oracle, cuda_lib, voc, rows, pitch, dist):
     assert int(one[0]) == want[rows - 1]
 
 
+# ---- attention over a KV cache (the reference's composite) ---------------------------------------------
+ATTENTION_CASES = [
+    # the reference's own three cases (operatorspy/tests/attention.py:310-357): prefill, decode, small
+    (32, 4, 5, 64, 0, 2048, (64, 2560, 1), (64, 11264, 1)),
+    (32, 4, 1, 64, 3, 2048, (64, 2560, 1), (64, 11264, 1)),
+    (8, 4, 2, 16, 1, 8, None, None),
+    # decoding over long caches: groups of 4 and 8 q heads, one q head per kv head, one kv head for all
+    (32, 8, 1, 128, 4095, 4096, None, None),
+    (64, 8, 1, 128, 9000, 9001, None, None),
+    (16, 16, 1, 128, 2500, 4096, None, None),
+    (8, 1, 1, 64, 700, 1024, None, None),
+    (2, 1, 1, 256, 300, 512, None, None),
+    # head sizes that are not a power of two / not whole vectors, odd strides
+    (12, 4, 1, 80, 130, 256, None, None),
+    (6, 2, 3, 20, 9, 32, None, None),
+    (8, 4, 2, 64, 17, 64, (67, 1000, 1), (69, 9000, 1)),
+    (4, 2, 1, 8, 5, 16, None, None),
+    # prefill: several row tiles per kv head, with and without a prefix in the cache
+    (8, 2, 37, 64, 0, 64, None, None),
+    (8, 4, 19, 128, 11, 64, (128, 8 * 128, 1), None),
+    (3, 3, 70, 32, 2100, 2200, None, None),
+]
+
+
+@pytest.mark.parametrize("nh,nkvh,seq,dh,pos,buf_len,qkv_strides,cache_strides", ATTENTION_CASES)
+def test_attention(oracle, cuda_lib, nh, nkvh, seq, dh, pos, buf_len, qkv_strides, cache_strides):
+    """out within the fp16 tolerance of the oracle's composite (only the grouping of fp32 sums
+    differs, so most elements are the same bit pattern); both caches byte for byte,
+    rows outside pos .. pos+seq untouched."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(21)
+    q = torch.randn((nh, seq, dh), generator=g).half()
+    k = torch.randn((nkvh, seq, dh), generator=g).half()
+    v = torch.randn((nkvh, seq, dh), generator=g).half()
+    k_cache = torch.randn((nkvh, buf_len, dh), generator=g).half()
+    v_cache = torch.randn((nkvh, buf_len, dh), generator=g).half()
+    if qkv_strides is not None:
+        q, k, v = (rearrange_tensor(t, qkv_strides) for t in (q, k, v))
+    if cache_strides is not None:
+        k_cache, v_cache = (rearrange_tensor(t, cache_strides) for t in (k_cache, v_cache))
+
+    def dev(t):  # same strides on the device
+        st = t.stride()
+        return rearrange_tensor(t.to(DEV), st) if not t.is_contiguous() else t.to(DEV)
+
+    qd, kd, vd, kcd, vcd = (dev(t) for t in (q, k, v, k_cache, v_cache))
+    out = torch.full((seq, nh, dh), 7.0, dtype=torch.float16, device=DEV)
+    with ops.AttentionOp(lib, handle, out, qd, kd, vd, kcd, vcd, pos) as op:
+        op.workspace.fill_(0xAB)  # the workspace arrives with arbitrary contents
+        op(out, qd, kd, vd, kcd, vcd)
+        torch.cuda.synchronize()
+        first = out.clone()
+        op(out, qd, kd, vd, kcd, vcd)  # same descriptor and workspace again
+        torch.cuda.synchronize()
+    want = oracle.attention(q.numpy(), k.numpy(), v.numpy(), k_cache.numpy(), v_cache.numpy(), pos)
+    assert torch.equal(first, out)
+    mism = _close(_bits(out).reshape(want.shape), want, 1e-3, 1e-3)
+    # sums of thousands of terms of both signs: a different grouping moves the last bit of more elements than elsewhere
+    assert _few(mism, want.size, 0.25)
+    assert torch.equal(kcd.cpu(), k_cache) and torch.equal(vcd.cpu(), v_cache)  # the oracle updated the host caches
+
+
+def test_attention_status_codes(cuda_lib):
+    from operators_b200 import InfiniopError
+
+    lib, handle = cuda_lib
+
+    def h(*shape):
+        return torch.zeros(shape, dtype=torch.float16, device=DEV)
+
+    def status(fn):
+        with pytest.raises(InfiniopError) as e:
+            fn()
+        return e.value.status
+
+    out, q, k, v, kc, vc = h(2, 8, 16), h(8, 2, 16), h(4, 2, 16), h(4, 2, 16), h(4, 8, 16), h(4, 8, 16)
+    assert status(lambda: ops.AttentionOp(lib, handle, out[0], q, k, v, kc, vc, 1)) == 4       # ndim
+    assert status(lambda: ops.AttentionOp(lib, handle, out[:, :, ::2], q[:, :, :8], k[:, :, :8], v[:, :, :8],
+                                          kc[:, :, :8], vc[:, :, :8], 1)) == 5               # out not contiguous
+    assert status(lambda: ops.AttentionOp(lib, handle, out, q, k, v, kc, vc, 7)) == 2           # cache too short
+    assert status(lambda: ops.AttentionOp(lib, handle, out, q, k[:3], v, kc, vc, 1)) == 2       # k and v disagree
+    assert status(lambda: ops.AttentionOp(lib, handle, h(2, 6, 16), h(6, 2, 16), k, v, kc, vc, 1)) == 2  # 6 % 4 != 0
+    assert status(lambda: ops.AttentionOp(lib, handle, out.float(), q, k, v, kc, vc, 1)) == 3
+    with ops.AttentionOp(lib, handle, out, q, k, v, kc, vc, 1) as op:
+        assert op.workspace_size > 0
+        assert lib.infiniopAttention(op.desc, op.workspace.data_ptr(), op.workspace_size - 1, out.data_ptr(),
+                                     q.data_ptr(), k.data_ptr(), v.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                     None) == 6                                               # workspace too small
+
+
 # ---- descriptor validation: same status codes as the reference ------------------------
 def test_status_codes(cuda_lib):
     import ctypes

@@ -120,6 +120,46 @@ def test_rearrange(oracle, ref_cpu, src_spec, dst_spec, dtype):
     assert torch.equal(y, x) and torch.equal(y2, y)
 
 
+# the reference's three attention cases (operatorspy/tests/attention.py:310-357) and two more
+ATTENTION_CASES = [
+    (32, 4, 5, 64, 0, 2048, (64, 2560, 1), (64, 11264, 1)),
+    (32, 4, 1, 64, 3, 2048, (64, 2560, 1), (64, 11264, 1)),
+    (8, 4, 2, 16, 1, 8, None, None),
+    (8, 8, 3, 32, 40, 64, None, None),
+    (12, 2, 1, 128, 200, 256, None, None),
+]
+
+
+def make_attention_inputs(nh, nkvh, seq, dh, pos, buf_len, qkv_strides, cache_strides, seed=21):
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.rand((nh, seq, dh), generator=g) * 0.1).half()
+    k = (torch.rand((nkvh, seq, dh), generator=g) * 0.1).half()
+    v = (torch.rand((nkvh, seq, dh), generator=g) * 0.1).half()
+    k_cache = (torch.rand((nkvh, buf_len, dh), generator=g) * 0.1).half()
+    v_cache = (torch.rand((nkvh, buf_len, dh), generator=g) * 0.1).half()
+    if qkv_strides is not None:
+        q, k, v = (rearrange_tensor(t, qkv_strides) for t in (q, k, v))
+    if cache_strides is not None:
+        k_cache, v_cache = (rearrange_tensor(t, cache_strides) for t in (k_cache, v_cache))
+    return q, k, v, k_cache, v_cache
+
+
+@pytest.mark.parametrize("nh,nkvh,seq,dh,pos,buf_len,qkv_strides,cache_strides", ATTENTION_CASES)
+def test_attention(oracle, ref_cpu, nh, nkvh, seq, dh, pos, buf_len, qkv_strides, cache_strides):
+    """The composite of the reference CPU build (rearranges, two matmuls, causal softmax) and the
+    oracle's step-by-step restatement write the same bits to out and to both caches."""
+    lib, handle = ref_cpu
+    q, k, v, k_cache, v_cache = make_attention_inputs(nh, nkvh, seq, dh, pos, buf_len, qkv_strides, cache_strides)
+    kc2, vc2 = k_cache.clone(), v_cache.clone()
+    if cache_strides is not None:
+        kc2, vc2 = rearrange_tensor(kc2, cache_strides), rearrange_tensor(vc2, cache_strides)
+    out = torch.zeros((seq, nh, dh), dtype=torch.float16)
+    ops.attention(lib, handle, out, q, k, v, k_cache, v_cache, pos)
+    mine = oracle.attention(q.numpy(), k.numpy(), v.numpy(), kc2.numpy(), vc2.numpy(), pos)
+    assert np.array_equal(mine.view(np.uint16), _bits(out).reshape(out.shape))
+    assert torch.equal(kc2, k_cache) and torch.equal(vc2, v_cache)
+
+
 @pytest.mark.parametrize("shape", [(32, 20, 512), (5, 64), (2, 7, 7), (3, 1, 9)])
 def test_causal_softmax(oracle, ref_cpu, shape):
     lib, handle = ref_cpu
