@@ -36,6 +36,7 @@
 #include "common.cuh"
 
 #include <cmath>
+#include <cstdlib>
 #include <new>
 
 using namespace b200;
@@ -205,6 +206,60 @@ __device__ __forceinline__ bool arrive_last(uint32_t *counter, uint32_t expected
     return last;
 }
 
+// After the chunk's scores stand in shared memory ([RT][pitch] floats): scores to the workspace, the chunk's
+// row maxima and exp-sums, and in the CTA that arrives last the rows' maxima and denominators.
+template<int RT>
+__device__ __forceinline__ void scores_epilogue(const AttnArgs &a, const Work<RT> &w, const float *smem, uint32_t pitch,
+                                                int *flag_ptr) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // per row: scores to the workspace, maximum and sum of exp(s - maximum) over the chunk; kWarps / RT warps share a row
+    constexpr uint32_t WPR = kWarps / RT;
+    __shared__ float part[2][kWarps];
+    const uint32_t r = warp / WPR, seg = warp % WPR;
+    const float *srow = smem + r * pitch;
+    float m = -INFINITY;
+    for (uint32_t j = seg * 32 + lane; j < w.n; j += WPR * 32) {
+        const float sc = srow[j];
+        m = fmaxf(m, sc);
+        a.scores[w.score_at(a, r, j)] = __half_as_ushort(__float2half_rz(sc));// exact: an fp16 value or -inf
+    }
+    m = warp_max(m);
+    if (lane == 0) part[0][warp] = m;
+    __syncthreads();
+    m = -INFINITY;
+#pragma unroll
+    for (uint32_t k = 0; k < WPR; ++k) m = fmaxf(m, part[0][r * WPR + k]);
+    float l = 0.f;
+    if (m > -INFINITY) {
+        for (uint32_t j = seg * 32 + lane; j < w.n; j += WPR * 32) l += expf(srow[j] - m);
+    }
+    l = warp_sum(l);
+    if (lane == 0) part[1][warp] = l;
+    __syncthreads();
+    if (seg == 0 && lane == 0) {
+        float total = 0.f;
+#pragma unroll
+        for (uint32_t k = 0; k < WPR; ++k) total += part[1][r * WPR + k];
+        __stcg(a.ml + w.slot(a) + r, make_float2(m, total));
+    }
+
+    // the last CTA of this (kv head, tile): row maximum and denominator over all chunks
+    if (!arrive_last(a.counters + w.h * a.row_tiles + w.tile, a.splits, flag_ptr)) return;
+    const uint64_t first = w.first_slot(a);
+    for (uint32_t r = warp; r < RT; r += kWarps) {
+        float big = -INFINITY;
+        for (uint32_t s = lane; s < a.splits; s += 32) big = fmaxf(big, __ldcg(a.ml + first + (uint64_t) s * RT + r).x);
+        big = warp_max(big);
+        float denom = 0.f;
+        for (uint32_t s = lane; s < a.splits; s += 32) {
+            const float2 ml = __ldcg(a.ml + first + (uint64_t) s * RT + r);
+            if (ml.x > -INFINITY) denom = fmaf(ml.y, expf(ml.x - big), denom);
+        }
+        denom = warp_sum(denom);
+        if (lane == 0) a.stat[(uint64_t) (w.h * a.row_tiles + w.tile) * RT + r] = make_float2(big, denom);
+    }
+}
+
 // ---- first kernel: scores = trunc16(alpha * q . k) of the chunk, row statistics ----------------------------
 template<int RT, int TPK, bool VEC>
 __global__ void __launch_bounds__(kThreads, 2) attention_scores_kernel(AttnArgs a) {
@@ -275,38 +330,36 @@ __global__ void __launch_bounds__(kThreads, 2) attention_scores_kernel(AttnArgs 
     }
     __syncthreads();
 
-    // per row: scores to the workspace, maximum and sum of exp(s - maximum) over the chunk
+    scores_epilogue<RT>(a, w, smem, pitch, &flag);
+}
+
+// After every warp's partial outputs stand in shared memory ([kWarps][RT][DHP] floats): their sum to the
+// workspace, and in the CTA that arrives last the sum over the chunks to `out`.
+template<int RT, int DHP>
+__device__ __forceinline__ void values_epilogue(const AttnArgs &a, const Work<RT> &w, const float *smem, int *flag_ptr) {
+    const uint32_t tid = threadIdx.x;
     const uint64_t slot = w.slot(a);
-    for (uint32_t r = warp; r < RT; r += kWarps) {
-        float m = -INFINITY;
-        for (uint32_t j = lane; j < w.n; j += 32) {
-            const float s = smem[r * pitch + j];
-            m = fmaxf(m, s);
-            a.scores[w.score_at(a, r, j)] = __half_as_ushort(__float2half_rz(s));// exact: s is an fp16 value or -inf
+    for (uint32_t o = tid; o < RT * DHP; o += kThreads) {
+        const uint32_t r = o / DHP, d = o - r * DHP;
+        if (d < a.dh) {
+            float s = 0.f;
+#pragma unroll
+            for (int wp = 0; wp < kWarps; ++wp) s += smem[(wp * RT + r) * DHP + d];
+            __stcg(a.acc + (slot + r) * a.dh + d, s);
         }
-        m = warp_max(m);
-        float l = 0.f;
-        if (m > -INFINITY) {
-            for (uint32_t j = lane; j < w.n; j += 32) l += expf(smem[r * pitch + j] - m);
-        }
-        l = warp_sum(l);
-        if (lane == 0) __stcg(a.ml + slot + r, make_float2(m, l));
     }
 
-    // the last CTA of this (kv head, tile): row maximum and denominator over all chunks
-    if (!arrive_last(a.counters + w.h * a.row_tiles + w.tile, a.splits, &flag)) return;
+    // the last CTA of this (kv head, tile) adds the chunks up, first chunk first
+    if (!arrive_last(a.counters + a.nkvh * a.row_tiles + w.h * a.row_tiles + w.tile, a.splits, flag_ptr)) return;
     const uint64_t first = w.first_slot(a);
-    for (uint32_t r = warp; r < RT; r += kWarps) {
-        float big = -INFINITY;
-        for (uint32_t s = lane; s < a.splits; s += 32) big = fmaxf(big, __ldcg(a.ml + first + (uint64_t) s * RT + r).x);
-        big = warp_max(big);
-        float denom = 0.f;
-        for (uint32_t s = lane; s < a.splits; s += 32) {
-            const float2 ml = __ldcg(a.ml + first + (uint64_t) s * RT + r);
-            if (ml.x > -INFINITY) denom = fmaf(ml.y, expf(ml.x - big), denom);
-        }
-        denom = warp_sum(denom);
-        if (lane == 0) a.stat[(uint64_t) (w.h * a.row_tiles + w.tile) * RT + r] = make_float2(big, denom);
+    for (uint32_t o = tid; o < RT * a.dh; o += kThreads) {
+        const uint32_t r = o / a.dh, d = o - r * a.dh;
+        const uint32_t row = w.tile * RT + r;
+        if (row >= w.rows_total) continue;
+        float sum = 0.f;
+        for (uint32_t s = 0; s < a.splits; ++s) sum += __ldcg(a.acc + (first + (uint64_t) s * RT + r) * a.dh + d);
+        const uint32_t g = row / a.seq, i = row - g * a.seq;
+        a.out[((uint64_t) i * a.nh + w.h * a.group + g) * a.dh + d] = f32_to_f16_ref(sum);
     }
 }
 
@@ -382,28 +435,233 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_kernel(AttnArgs 
         }
     }
     __syncthreads();
-    const uint64_t slot = w.slot(a);
-    for (uint32_t o = tid; o < RT * DHP; o += kThreads) {
-        const uint32_t r = o / DHP, d = o - r * DHP;
-        if (d < a.dh) {
-            float s = 0.f;
+    values_epilogue<RT, DHP>(a, w, smem, &flag);
+}
+
+// ---- the same two kernels with the dot products on the tensor cores ------------------------------------------
+// mma.sync m16n8k16 (fp16 operands, fp32 accumulation): the eight columns of the result are the tile's query
+// rows, so a kv head's rows cost the same whether one or eight q heads share them, and a lane needs one
+// instruction per 16 bytes of K or V instead of eight multiply-adds per query row.  Used for 16-byte aligned
+// rows with dh <= 128; nothing here is a GEMM-sized contraction, the kernels stay bound by the reads of K and V.
+//
+// A lane always loads 16 contiguous bytes of a cache row: lane = 4 * (row in a group of 8) + c, bytes
+// [32 dh-block + 8 c, +8) halves.  The contraction index of an mma is only a label, so for q . k the
+// four 32-bit registers of such a load serve as the k-pairs of two mmas directly, with q loaded the same way.
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// transpose of the 8 x 8 matrix of 16-bit values a warp holds one 32-bit register each of
+__device__ __forceinline__ uint32_t transpose8x8(uint32_t x) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+    return r;
+}
+
+// 16 cache rows (row0 + lane / 4 and eight further down) x NB blocks of 32 halves; rows >= n and columns >= dh read as zero
+template<int NB>
+__device__ __forceinline__ void load_rows16(uint4 (&lo)[NB], uint4 (&hi)[NB], const uint16_t *base, int64_t row_stride,
+                                            uint32_t row0, uint32_t n, uint32_t dh, uint32_t lane) {
+    const uint32_t j_lo = row0 + (lane >> 2), j_hi = j_lo + 8, c = lane & 3;
 #pragma unroll
-            for (int wp = 0; wp < kWarps; ++wp) s += smem[(wp * RT + r) * DHP + d];
-            __stcg(a.acc + (slot + r) * a.dh + d, s);
+    for (int blk = 0; blk < NB; ++blk) {
+        const uint32_t col = blk * 32 + c * 8;
+        lo[blk] = make_uint4(0, 0, 0, 0);
+        hi[blk] = make_uint4(0, 0, 0, 0);
+        if (col < dh) {
+            if (j_lo < n) lo[blk] = ld_stream(base + (int64_t) j_lo * row_stride + col);
+            if (j_hi < n) hi[blk] = ld_stream(base + (int64_t) j_hi * row_stride + col);
         }
     }
+}
 
-    // the last CTA of this (kv head, tile) adds the chunks up, first chunk first
-    if (!arrive_last(a.counters + a.nkvh * a.row_tiles + w.h * a.row_tiles + w.tile, a.splits, &flag)) return;
-    const uint64_t first = w.first_slot(a);
-    for (uint32_t o = tid; o < RT * a.dh; o += kThreads) {
-        const uint32_t r = o / a.dh, d = o - r * a.dh;
-        const uint32_t row = w.tile * RT + r;
-        if (row >= w.rows_total) continue;
-        float sum = 0.f;
-        for (uint32_t s = 0; s < a.splits; ++s) sum += __ldcg(a.acc + (first + (uint64_t) s * RT + r) * a.dh + d);
-        const uint32_t g = row / a.seq, i = row - g * a.seq;
-        a.out[((uint64_t) i * a.nh + w.h * a.group + g) * a.dh + d] = f32_to_f16_ref(sum);
+template<int RT, int NB>
+__global__ void __launch_bounds__(kThreads, 2) attention_scores_mma_kernel(AttnArgs a) {
+    extern __shared__ __align__(16) float smem[];// scores [RT][chunk + 1]
+    __shared__ int flag;
+    __shared__ int row_limit[8];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t kr = lane >> 2, c = lane & 3;
+    const uint32_t pitch = a.chunk + 1;
+    const Work<RT> w(a);
+    if (tid < 8) row_limit[tid] = tid < RT ? w.limit(a, w.tile * RT + tid) : -1;
+
+    // operand B: query row kr of the tile (zeros past the tile's rows)
+    uint4 qb[NB];
+#pragma unroll
+    for (int blk = 0; blk < NB; ++blk) qb[blk] = make_uint4(0, 0, 0, 0);
+    {
+        const uint32_t row = w.tile * RT + kr;
+        if (kr < RT && row < w.rows_total) {
+            const uint32_t g = row / a.seq, i = row - g * a.seq;
+            const uint16_t *qr = a.q + (int64_t) (w.h * a.group + g) * a.q_s0 + (int64_t) i * a.q_s1;
+#pragma unroll
+            for (int blk = 0; blk < NB; ++blk) {
+                const uint32_t col = blk * 32 + c * 8;
+                if (col < a.dh) qb[blk] = __ldg(reinterpret_cast<const uint4 *>(qr + col));
+            }
+        }
+    }
+    __syncthreads();
+
+    // a warp takes groups of 16 tokens; the next group's rows are in flight while this one is multiplied
+    const uint16_t *kbase = a.kc + (int64_t) w.h * a.kc_s0 + (int64_t) w.c0 * a.kc_s1;
+    const uint32_t groups = (w.n + 15) / 16;
+    uint4 lo[NB], hi[NB], nlo[NB], nhi[NB];
+    if (warp < groups) load_rows16<NB>(lo, hi, kbase, a.kc_s1, warp * 16, w.n, a.dh, lane);
+    for (uint32_t gi = warp; gi < groups; gi += kWarps) {
+        if (gi + kWarps < groups) load_rows16<NB>(nlo, nhi, kbase, a.kc_s1, (gi + kWarps) * 16, w.n, a.dh, lane);
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int blk = 0; blk < NB; ++blk) {
+            mma16816(d, lo[blk].x, hi[blk].x, lo[blk].y, hi[blk].y, qb[blk].x, qb[blk].y);
+            mma16816(d, lo[blk].z, hi[blk].z, lo[blk].w, hi[blk].w, qb[blk].z, qb[blk].w);
+        }
+        // d[0], d[1]: token gi * 16 + kr, rows 2c and 2c + 1; d[2], d[3]: eight tokens further down
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const uint32_t j = gi * 16 + kr + (v >= 2 ? 8 : 0), r = 2 * c + (v & 1);
+            if (r < RT && j < w.n) {
+                float sc = f16_to_f32(f32_to_f16_ref(__fmul_rn(a.alpha, d[v])));// as the first matmul stores it
+                if ((int) (w.c0 + j) > row_limit[r]) sc = -INFINITY;
+                smem[r * pitch + j] = sc;
+            }
+        }
+#pragma unroll
+        for (int blk = 0; blk < NB; ++blk) {
+            lo[blk] = nlo[blk];
+            hi[blk] = nhi[blk];
+        }
+    }
+    __syncthreads();
+    scores_epilogue<RT>(a, w, smem, pitch, &flag);
+}
+
+// out^T[d][row] = sum_j V[j][d] * p[row][j]: operand A is V transposed, 8 x 8 blocks at a time in registers;
+// operand B are the fp16 probabilities from shared memory.  Register t of a lane's 16-byte load holds columns
+// d = 32 blk + 8 (m / 2) + 2 t + m % 2 of the block's rows m after the transposition.
+template<int RT, int NB>
+__global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnArgs a) {
+    extern __shared__ __align__(16) float smem[];// fp16 probabilities [RT][chunk + 8], later the per-warp outputs
+    __shared__ int flag;
+    constexpr int DHP = NB * 32;
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t kr = lane >> 2, c = lane & 3;
+    const uint32_t pitch16 = a.chunk + 8;// in halves; rows land 4 banks apart
+    uint16_t *p16 = reinterpret_cast<uint16_t *>(smem);
+    const Work<RT> w(a);
+    const uint32_t groups = (w.n + 15) / 16;
+
+    // probabilities of the chunk: kWarps / RT warps per row, eight scores per lane and step
+    {
+        constexpr uint32_t WPR = kWarps / RT;
+        const uint32_t r = warp / WPR, seg = warp % WPR;
+        const float2 st = a.stat[(uint64_t) (w.h * a.row_tiles + w.tile) * RT + r];
+        const uint16_t *srow = a.scores + w.score_at(a, r, 0);// 16-byte aligned: chunk and pitch are multiples of 64
+        for (uint32_t j = (seg * 32 + lane) * 8; j < groups * 16; j += WPR * 256) {
+            const uint4 raw = __ldcs(reinterpret_cast<const uint4 *>(srow + j));
+            const uint16_t *sc16 = reinterpret_cast<const uint16_t *>(&raw);
+            uint32_t packed[4];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                uint32_t bits = 0;// masked entries and the padding of the last group are exact zeros
+                const float sc = f16_to_f32(sc16[e]);
+                if (j + e < w.n && sc > -INFINITY) bits = f32_to_f16_ref(__fdiv_rn(expf(sc - st.x), st.y));
+                packed[e >> 1] = (e & 1) ? (packed[e >> 1] | (bits << 16)) : bits;
+            }
+            *reinterpret_cast<uint4 *>(p16 + r * pitch16 + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+    }
+    __syncthreads();
+
+    float acc[NB][2][4];
+#pragma unroll
+    for (int blk = 0; blk < NB; ++blk) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) acc[blk][0][v] = acc[blk][1][v] = 0.f;
+    }
+    const uint16_t *vbase = a.vc + (int64_t) w.h * a.vc_s0 + (int64_t) w.c0 * a.vc_s1;
+    uint4 lo[NB], hi[NB], nlo[NB], nhi[NB];
+    if (warp < groups) load_rows16<NB>(lo, hi, vbase, a.vc_s1, warp * 16, w.n, a.dh, lane);
+    for (uint32_t gi = warp; gi < groups; gi += kWarps) {
+        if (gi + kWarps < groups) load_rows16<NB>(nlo, nhi, vbase, a.vc_s1, (gi + kWarps) * 16, w.n, a.dh, lane);
+        uint32_t b0 = 0, b1 = 0;// probabilities of row kr for tokens 2c, 2c+1 and eight further down
+        if (kr < RT) {
+            const uint16_t *pr = p16 + kr * pitch16 + gi * 16 + 2 * c;
+            b0 = *reinterpret_cast<const uint32_t *>(pr);
+            b1 = *reinterpret_cast<const uint32_t *>(pr + 8);
+        }
+#pragma unroll
+        for (int blk = 0; blk < NB; ++blk) {
+            mma16816(acc[blk][0], transpose8x8(lo[blk].x), transpose8x8(lo[blk].y), transpose8x8(hi[blk].x),
+                     transpose8x8(hi[blk].y), b0, b1);
+            mma16816(acc[blk][1], transpose8x8(lo[blk].z), transpose8x8(lo[blk].w), transpose8x8(hi[blk].z),
+                     transpose8x8(hi[blk].w), b0, b1);
+        }
+#pragma unroll
+        for (int blk = 0; blk < NB; ++blk) {
+            lo[blk] = nlo[blk];
+            hi[blk] = nhi[blk];
+        }
+    }
+    __syncthreads();// every warp is done with the probabilities
+#pragma unroll
+    for (int blk = 0; blk < NB; ++blk) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const uint32_t d = blk * 32 + (kr >> 1) * 8 + 2 * (2 * u + (v >> 1)) + (kr & 1), r = 2 * c + (v & 1);
+                if (r < RT) smem[(warp * RT + r) * DHP + d] = acc[blk][u][v];
+            }
+        }
+    }
+    __syncthreads();
+    values_epilogue<RT, DHP>(a, w, smem, &flag);
+}
+
+template<int RT, int NB>
+infiniopStatus_t launch_mma(const AttnDesc *d, const AttnArgs &args, cudaStream_t st) {
+    constexpr int DHP = NB * 32;
+    const size_t smem_scores = (size_t) RT * (d->chunk + 1) * sizeof(float);
+    size_t smem_values = (size_t) RT * (d->chunk + 8) * sizeof(uint16_t);
+    const size_t red = (size_t) kWarps * RT * DHP * sizeof(float);
+    if (red > smem_values) smem_values = red;
+    static thread_local int configured_dev = -1;
+    if (configured_dev != d->device_id) {
+        constexpr size_t most = (size_t) kMaxRows * (kMaxChunk + 1) * sizeof(float);
+        if (cudaFuncSetAttribute(attention_scores_mma_kernel<RT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int) most) != cudaSuccess ||
+            cudaFuncSetAttribute(attention_values_mma_kernel<RT, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int) most) != cudaSuccess) {
+            cudaGetLastError();
+            return STATUS_EXECUTION_FAILED;
+        }
+        configured_dev = d->device_id;
+    }
+    const dim3 grid(d->splits, d->nkvh, d->row_tiles);
+    attention_scores_mma_kernel<RT, NB><<<grid, kThreads, smem_scores, st>>>(args);
+    const infiniopStatus_t status = check_launch("attention scores");
+    if (status != STATUS_SUCCESS) return status;
+    attention_values_mma_kernel<RT, NB><<<grid, kThreads, smem_values, st>>>(args);
+    return check_launch("attention values");
+}
+
+template<int RT>
+infiniopStatus_t launch_mma_blocks(const AttnDesc *d, const AttnArgs &args, cudaStream_t st) {
+    if (d->dh <= 32) return launch_mma<RT, 1>(d, args, st);
+    if (d->dh <= 64) return launch_mma<RT, 2>(d, args, st);
+    return launch_mma<RT, 4>(d, args, st);
+}
+
+infiniopStatus_t launch_mma_rows(const AttnDesc *d, const AttnArgs &args, cudaStream_t st) {
+    switch (d->rt) {
+        case 1: return launch_mma_blocks<1>(d, args, st);
+        case 2: return launch_mma_blocks<2>(d, args, st);
+        case 4: return launch_mma_blocks<4>(d, args, st);
+        default: return launch_mma_blocks<8>(d, args, st);
     }
 }
 
@@ -603,6 +861,9 @@ INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t de
     else kv_append_kernel<false><<<(uint32_t) ctas, kThreads, 0, st>>>(a, n_counters);
     const infiniopStatus_t status = check_launch("attention kv append");
     if (status != STATUS_SUCCESS) return status;
+    // INFINIOP_ATTENTION_KERNEL (any value) forces the multiply-add kernels, which otherwise serve unaligned
+    // layouts and head sizes above 128
+    if (vec && d->dh <= 128 && getenv("INFINIOP_ATTENTION_KERNEL") == nullptr) return launch_mma_rows(d, a, st);
     return vec ? launch_rows<true>(d, a, st) : launch_rows<false>(d, a, st);
 }
 

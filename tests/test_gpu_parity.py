@@ -474,12 +474,17 @@ ATTENTION_CASES = [
 ]
 
 
+@pytest.mark.parametrize("kernels", ["tensor", "multiply_add"])
 @pytest.mark.parametrize("nh,nkvh,seq,dh,pos,buf_len,qkv_strides,cache_strides", ATTENTION_CASES)
-def test_attention(oracle, cuda_lib, nh, nkvh, seq, dh, pos, buf_len, qkv_strides, cache_strides):
+def test_attention(oracle, cuda_lib, monkeypatch, kernels, nh, nkvh, seq, dh, pos, buf_len, qkv_strides, cache_strides):
     """out within the fp16 tolerance of the oracle's composite (only the grouping of fp32 sums
     differs, so most elements are the same bit pattern); both caches byte for byte,
     rows outside pos .. pos+seq untouched."""
     lib, handle = cuda_lib
+    if kernels == "multiply_add":  # the kernels that otherwise serve unaligned layouts and dh > 128
+        monkeypatch.setenv("INFINIOP_ATTENTION_KERNEL", "fma")
+    else:
+        monkeypatch.delenv("INFINIOP_ATTENTION_KERNEL", raising=False)
     g = torch.Generator().manual_seed(21)
     q = torch.randn((nh, seq, dh), generator=g).half()
     k = torch.randn((nkvh, seq, dh), generator=g).half()
