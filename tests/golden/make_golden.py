@@ -109,6 +109,21 @@ def main():
         out["rearrange_src_" + tag], out["rearrange_dst_" + tag] = bits(storage(x)), bits(storage(y))
         out["rearrange_meta_" + tag] = np.array([shape, x.stride(), y.stride()], np.int64)
 
+    # attention composite (reference operatorspy/tests/attention.py): one decoding token over a prefix in the
+    # cache, and a short prefill; contiguous tensors.  Inputs, the output and both caches after the call.
+    for tag, nh, nkvh, seq, dh, pos, buf in (("decode", 8, 2, 1, 32, 37, 64), ("prefill", 6, 3, 4, 16, 0, 8)):
+        q = torch.randn((nh, seq, dh), generator=g).half()
+        k = torch.randn((nkvh, seq, dh), generator=g).half()
+        v = torch.randn((nkvh, seq, dh), generator=g).half()
+        kc = torch.randn((nkvh, buf, dh), generator=g).half()
+        vc = torch.randn((nkvh, buf, dh), generator=g).half()
+        for name, t in (("q", q), ("k", k), ("v", v), ("kc_in", kc), ("vc_in", vc)):
+            out["attn_%s_%s" % (name, tag)] = bits(t)
+        res = torch.zeros((seq, nh, dh), dtype=torch.float16)
+        ops.attention(lib, h, res, q, k, v, kc, vc, pos)
+        out["attn_out_" + tag], out["attn_kc_out_" + tag], out["attn_vc_out_" + tag] = bits(res), bits(kc), bits(vc)
+        out["attn_meta_" + tag] = np.array([nh, nkvh, seq, dh, pos, buf], np.int64)
+
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "hot_path_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -60,3 +60,15 @@ def test_random_sample(oracle):
         off += voc
         assert oracle.random_sample(row, float(np.float32(u)), float(np.float32(topp)), topk, float(np.float32(temp))) == want
     assert off == G["rs_rows"].size
+
+
+@pytest.mark.parametrize("tag", ["decode", "prefill"])
+def test_attention(oracle, tag):
+    nh, nkvh, seq, dh, pos, buf = (int(x) for x in G["attn_meta_" + tag])
+    f16 = lambda name, shape: G["attn_%s_%s" % (name, tag)].copy().view(np.float16).reshape(shape)
+    q, k, v = f16("q", (nh, seq, dh)), f16("k", (nkvh, seq, dh)), f16("v", (nkvh, seq, dh))
+    kc, vc = f16("kc_in", (nkvh, buf, dh)), f16("vc_in", (nkvh, buf, dh))
+    got = oracle.attention(q, k, v, kc, vc, pos)
+    assert np.array_equal(got.view(np.uint16).reshape(-1), G["attn_out_" + tag].reshape(-1))
+    assert np.array_equal(kc.view(np.uint16).reshape(-1), G["attn_kc_out_" + tag].reshape(-1))
+    assert np.array_equal(vc.view(np.uint16).reshape(-1), G["attn_vc_out_" + tag].reshape(-1))
