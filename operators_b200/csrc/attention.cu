@@ -231,7 +231,8 @@ __device__ __forceinline__ void scores_epilogue(const AttnArgs &a, const Work<RT
     for (uint32_t k = 0; k < WPR; ++k) m = fmaxf(m, part[0][r * WPR + k]);
     float l = 0.f;
     if (m > -INFINITY) {
-        for (uint32_t j = seg * 32 + lane; j < w.n; j += WPR * 32) l += expf(srow[j] - m);
+        // base-2 exponential on the special-function unit (2^-22 relative): the sum only serves as the denominator
+        for (uint32_t j = seg * 32 + lane; j < w.n; j += WPR * 32) l += fast_exp2((srow[j] - m) * 1.4426950408889634f);
     }
     l = warp_sum(l);
     if (lane == 0) part[1][warp] = l;
@@ -554,11 +555,18 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnA
     const Work<RT> w(a);
     const uint32_t groups = (w.n + 15) / 16;
 
+    // the first rows of V are on their way while the probabilities are formed
+    const uint16_t *vbase = a.vc + (int64_t) w.h * a.vc_s0 + (int64_t) w.c0 * a.vc_s1;
+    uint4 lo[NB], hi[NB], nlo[NB], nhi[NB];
+    if (warp < groups) load_rows16<NB>(lo, hi, vbase, a.vc_s1, warp * 16, w.n, a.dh, lane);
+
     // probabilities of the chunk: kWarps / RT warps per row, eight scores per lane and step
     {
         constexpr uint32_t WPR = kWarps / RT;
         const uint32_t r = warp / WPR, seg = warp % WPR;
         const float2 st = a.stat[(uint64_t) (w.h * a.row_tiles + w.tile) * RT + r];
+        // exp(s - max) / sum as 2^((s - max) log2 e) * (1 / sum): within 2^-21 of the quotient before the truncation
+        const float inv_sum = __frcp_rn(st.y);
         const uint16_t *srow = a.scores + w.score_at(a, r, 0);// 16-byte aligned: chunk and pitch are multiples of 64
         for (uint32_t j = (seg * 32 + lane) * 8; j < groups * 16; j += WPR * 256) {
             const uint4 raw = __ldcs(reinterpret_cast<const uint4 *>(srow + j));
@@ -568,7 +576,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnA
             for (int e = 0; e < 8; ++e) {
                 uint32_t bits = 0;// masked entries and the padding of the last group are exact zeros
                 const float sc = f16_to_f32(sc16[e]);
-                if (j + e < w.n && sc > -INFINITY) bits = f32_to_f16_ref(__fdiv_rn(expf(sc - st.x), st.y));
+                if (j + e < w.n && sc > -INFINITY) {
+                    bits = f32_to_f16_ref(fast_exp2((sc - st.x) * 1.4426950408889634f) * inv_sum);
+                }
                 packed[e >> 1] = (e & 1) ? (packed[e >> 1] | (bits << 16)) : bits;
             }
             *reinterpret_cast<uint4 *>(p16 + r * pitch16 + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -582,9 +592,6 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnA
 #pragma unroll
         for (int v = 0; v < 4; ++v) acc[blk][0][v] = acc[blk][1][v] = 0.f;
     }
-    const uint16_t *vbase = a.vc + (int64_t) w.h * a.vc_s0 + (int64_t) w.c0 * a.vc_s1;
-    uint4 lo[NB], hi[NB], nlo[NB], nhi[NB];
-    if (warp < groups) load_rows16<NB>(lo, hi, vbase, a.vc_s1, warp * 16, w.n, a.dh, lane);
     for (uint32_t gi = warp; gi < groups; gi += kWarps) {
         if (gi + kWarps < groups) load_rows16<NB>(nlo, nhi, vbase, a.vc_s1, (gi + kWarps) * 16, w.n, a.dh, lane);
         uint32_t b0 = 0, b1 = 0;// probabilities of row kr for tokens 2c, 2c+1 and eight further down
