@@ -512,8 +512,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_scores_mma_kernel(AttnA
     const uint32_t groups = (w.n + 15) / 16;
     uint4 lo[NB], hi[NB], nlo[NB], nhi[NB];
     if (warp < groups) load_rows16<NB>(lo, hi, kbase, a.kc_s1, warp * 16, w.n, a.dh, lane);
-    for (uint32_t gi = warp; gi < groups; gi += kWarps) {
-        if (gi + kWarps < groups) load_rows16<NB>(nlo, nhi, kbase, a.kc_s1, (gi + kWarps) * 16, w.n, a.dh, lane);
+    auto multiply = [&](const uint4 (&lo)[NB], const uint4 (&hi)[NB], uint32_t gi) {
         float d[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int blk = 0; blk < NB; ++blk) {
@@ -530,11 +529,14 @@ __global__ void __launch_bounds__(kThreads, 2) attention_scores_mma_kernel(AttnA
                 smem[r * pitch + j] = sc;
             }
         }
-#pragma unroll
-        for (int blk = 0; blk < NB; ++blk) {
-            lo[blk] = nlo[blk];
-            hi[blk] = nhi[blk];
-        }
+    };
+    // two sets of registers take turns: one is multiplied while the other one's rows are in flight
+    for (uint32_t gi = warp; gi < groups; gi += 2 * kWarps) {
+        if (gi + kWarps < groups) load_rows16<NB>(nlo, nhi, kbase, a.kc_s1, (gi + kWarps) * 16, w.n, a.dh, lane);
+        multiply(lo, hi, gi);
+        if (gi + kWarps >= groups) break;
+        if (gi + 2 * kWarps < groups) load_rows16<NB>(lo, hi, kbase, a.kc_s1, (gi + 2 * kWarps) * 16, w.n, a.dh, lane);
+        multiply(nlo, nhi, gi + kWarps);
     }
     __syncthreads();
     scores_epilogue<RT>(a, w, smem, pitch, &flag);
@@ -592,8 +594,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnA
 #pragma unroll
         for (int v = 0; v < 4; ++v) acc[blk][0][v] = acc[blk][1][v] = 0.f;
     }
-    for (uint32_t gi = warp; gi < groups; gi += kWarps) {
-        if (gi + kWarps < groups) load_rows16<NB>(nlo, nhi, vbase, a.vc_s1, (gi + kWarps) * 16, w.n, a.dh, lane);
+    auto multiply = [&](const uint4 (&lo)[NB], const uint4 (&hi)[NB], uint32_t gi) {
         uint32_t b0 = 0, b1 = 0;// probabilities of row kr for tokens 2c, 2c+1 and eight further down
         if (kr < RT) {
             const uint16_t *pr = p16 + kr * pitch16 + gi * 16 + 2 * c;
@@ -607,11 +608,13 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnA
             mma16816(acc[blk][1], transpose8x8(lo[blk].z), transpose8x8(lo[blk].w), transpose8x8(hi[blk].z),
                      transpose8x8(hi[blk].w), b0, b1);
         }
-#pragma unroll
-        for (int blk = 0; blk < NB; ++blk) {
-            lo[blk] = nlo[blk];
-            hi[blk] = nhi[blk];
-        }
+    };
+    for (uint32_t gi = warp; gi < groups; gi += 2 * kWarps) {// two sets of registers take turns, as in the first kernel
+        if (gi + kWarps < groups) load_rows16<NB>(nlo, nhi, vbase, a.vc_s1, (gi + kWarps) * 16, w.n, a.dh, lane);
+        multiply(lo, hi, gi);
+        if (gi + kWarps >= groups) break;
+        if (gi + 2 * kWarps < groups) load_rows16<NB>(lo, hi, vbase, a.vc_s1, (gi + 2 * kWarps) * 16, w.n, a.dh, lane);
+        multiply(nlo, nhi, gi + kWarps);
     }
     __syncthreads();// every warp is done with the probabilities
 #pragma unroll
