@@ -22,11 +22,12 @@
 // group x tokens) and one chunk of the cached tokens, so K and V are each read
 // once however many q heads share them:
 //  * attention_scores_kernel: the chunk's scores (to the workspace, fp16) with
-//    their maximum and exp-sum; the CTA that arrives last for a (kv head, row
-//    tile) merges these into the row's maximum and denominator.
-//  * attention_values_kernel: probabilities of the chunk from the scores, the
-//    chunk's p . v to the workspace; the CTA that arrives last adds the chunks
-//    up and writes `out`.
+//    their maximum and exp-sum.
+//  * attention_values_kernel: every CTA merges the chunks' maxima and exp-sums
+//    into its rows' maximum and denominator, forms the probabilities of its
+//    chunk from the scores and writes the chunk's p . v to the workspace; the
+//    CTA that arrives last for a (kv head, row tile) adds the chunks up and
+//    writes `out`.
 // Nothing waits on another CTA.  The scores cross the workspace because the
 // reference's truncation of p needs the denominator of the whole row first;
 // they are rows x tokens x 2 bytes against tokens x dh x 4 bytes of K and V.
@@ -59,7 +60,7 @@ struct AttnDesc {
     uint32_t rt, row_tiles, splits, chunk, tpk;
     bool strides_vec;             // every stride a multiple of 8 elements and dh % 8 == 0
     uint32_t score_pitch;         // splits * chunk: tokens per score row in the workspace
-    uint64_t ws_ml, ws_stat, ws_acc, ws_scores, ws_bytes;// workspace: counters at 0, then the parts named here
+    uint64_t ws_ml, ws_acc, ws_scores, ws_bytes;// workspace: counters at 0, then the parts named here
 };
 
 struct AttnArgs {
@@ -68,7 +69,6 @@ struct AttnArgs {
     uint16_t *kc, *vc;
     uint32_t *counters;
     float2 *ml;   // per (kv head, tile, chunk, row): maximum and exp-sum of the chunk
-    float2 *stat; // per (kv head, tile, row): maximum and denominator of the whole row
     float *acc;   // per (kv head, tile, chunk, row): p . v of the chunk
     uint16_t *scores;
     uint32_t nh, nkvh, group, seq, dh, pos, total;
@@ -102,7 +102,7 @@ __device__ __forceinline__ void unpack8(uint4 v, float (&f)[8]) {
 }
 
 // k, v rows -> cache rows pos .. pos+seq of both caches; block 0 also clears the counters by which the
-// other two kernels find the CTA that arrives last.
+// last kernel finds the CTA that arrives last.
 template<bool VEC>
 __global__ void __launch_bounds__(kThreads) kv_append_kernel(AttnArgs a, uint32_t n_counters) {
     if (blockIdx.x == 0) {
@@ -206,11 +206,10 @@ __device__ __forceinline__ bool arrive_last(uint32_t *counter, uint32_t expected
     return last;
 }
 
-// After the chunk's scores stand in shared memory ([RT][pitch] floats): scores to the workspace, the chunk's
-// row maxima and exp-sums, and in the CTA that arrives last the rows' maxima and denominators.
+// After the chunk's scores stand in shared memory ([RT][pitch] floats): scores to the workspace with the chunk's
+// row maxima and exp-sums.
 template<int RT>
-__device__ __forceinline__ void scores_epilogue(const AttnArgs &a, const Work<RT> &w, const float *smem, uint32_t pitch,
-                                                int *flag_ptr) {
+__device__ __forceinline__ void scores_epilogue(const AttnArgs &a, const Work<RT> &w, const float *smem, uint32_t pitch) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // per row: scores to the workspace, maximum and sum of exp(s - maximum) over the chunk; kWarps / RT warps share a row
     constexpr uint32_t WPR = kWarps / RT;
@@ -244,28 +243,30 @@ __device__ __forceinline__ void scores_epilogue(const AttnArgs &a, const Work<RT
         __stcg(a.ml + w.slot(a) + r, make_float2(m, total));
     }
 
-    // the last CTA of this (kv head, tile): row maximum and denominator over all chunks
-    if (!arrive_last(a.counters + w.h * a.row_tiles + w.tile, a.splits, flag_ptr)) return;
-    const uint64_t first = w.first_slot(a);
-    for (uint32_t r = warp; r < RT; r += kWarps) {
-        float big = -INFINITY;
-        for (uint32_t s = lane; s < a.splits; s += 32) big = fmaxf(big, __ldcg(a.ml + first + (uint64_t) s * RT + r).x);
-        big = warp_max(big);
-        float denom = 0.f;
-        for (uint32_t s = lane; s < a.splits; s += 32) {
-            const float2 ml = __ldcg(a.ml + first + (uint64_t) s * RT + r);
-            if (ml.x > -INFINITY) denom = fmaf(ml.y, expf(ml.x - big), denom);
-        }
-        denom = warp_sum(denom);
-        if (lane == 0) a.stat[(uint64_t) (w.h * a.row_tiles + w.tile) * RT + r] = make_float2(big, denom);
+}
+
+// Maximum and denominator of row r of the tile over all chunks, from the chunks' (maximum, exp-sum) pairs the
+// first kernel left; called by a whole warp.  Every CTA of the second kernel merges them for itself (a few
+// dozen pairs from L2), which spares the first kernel a fence, a counter and a last-CTA pass.
+template<int RT>
+__device__ __forceinline__ float2 row_stat(const AttnArgs &a, const Work<RT> &w, uint32_t r) {
+    const uint32_t lane = threadIdx.x & 31;
+    const float2 *ml = a.ml + w.first_slot(a) + r;
+    float big = -INFINITY;
+    for (uint32_t s = lane; s < a.splits; s += 32) big = fmaxf(big, ml[(uint64_t) s * RT].x);
+    big = warp_max(big);
+    float denom = 0.f;
+    for (uint32_t s = lane; s < a.splits; s += 32) {
+        const float2 part = ml[(uint64_t) s * RT];
+        if (part.x > -INFINITY) denom = fmaf(part.y, expf(part.x - big), denom);
     }
+    return make_float2(big, warp_sum(denom));
 }
 
 // ---- first kernel: scores = trunc16(alpha * q . k) of the chunk, row statistics ----------------------------
 template<int RT, int TPK, bool VEC>
 __global__ void __launch_bounds__(kThreads, 2) attention_scores_kernel(AttnArgs a) {
     extern __shared__ __align__(16) float smem[];// scores [RT][chunk + 1]
-    __shared__ int flag;
     __shared__ int row_limit[RT];// last token each row of the tile sees
     constexpr int KPI = kThreads / TPK;// keys per iteration of the CTA
     constexpr int KEPT = RT / TPK > 1 ? RT / TPK : 1;
@@ -331,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_scores_kernel(AttnArgs 
     }
     __syncthreads();
 
-    scores_epilogue<RT>(a, w, smem, pitch, &flag);
+    scores_epilogue<RT>(a, w, smem, pitch);
 }
 
 // After every warp's partial outputs stand in shared memory ([kWarps][RT][DHP] floats): their sum to the
@@ -351,7 +352,7 @@ __device__ __forceinline__ void values_epilogue(const AttnArgs &a, const Work<RT
     }
 
     // the last CTA of this (kv head, tile) adds the chunks up, first chunk first
-    if (!arrive_last(a.counters + a.nkvh * a.row_tiles + w.h * a.row_tiles + w.tile, a.splits, flag_ptr)) return;
+    if (!arrive_last(a.counters + w.h * a.row_tiles + w.tile, a.splits, flag_ptr)) return;
     const uint64_t first = w.first_slot(a);
     for (uint32_t o = tid; o < RT * a.dh; o += kThreads) {
         const uint32_t r = o / a.dh, d = o - r * a.dh;
@@ -378,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_kernel(AttnArgs 
     const Work<RT> w(a);
 
     for (uint32_t r = warp; r < RT; r += kWarps) {
-        const float2 st = a.stat[(uint64_t) (w.h * a.row_tiles + w.tile) * RT + r];
+        const float2 st = row_stat<RT>(a, w, r);
         for (uint32_t j = lane; j < w.n; j += 32) {
             const float s = f16_to_f32(a.scores[w.score_at(a, r, j)]);
             float p = 0.f;// masked entries are exact zeros (causal_softmax_cpu.cc:68)
@@ -481,7 +482,6 @@ __device__ __forceinline__ void load_rows16(uint4 (&lo)[NB], uint4 (&hi)[NB], co
 template<int RT, int NB>
 __global__ void __launch_bounds__(kThreads, 2) attention_scores_mma_kernel(AttnArgs a) {
     extern __shared__ __align__(16) float smem[];// scores [RT][chunk + 1]
-    __shared__ int flag;
     __shared__ int row_limit[8];
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t kr = lane >> 2, c = lane & 3;
@@ -539,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_scores_mma_kernel(AttnA
         multiply(nlo, nhi, gi + kWarps);
     }
     __syncthreads();
-    scores_epilogue<RT>(a, w, smem, pitch, &flag);
+    scores_epilogue<RT>(a, w, smem, pitch);
 }
 
 // out^T[d][row] = sum_j V[j][d] * p[row][j]: operand A is V transposed, 8 x 8 blocks at a time in registers;
@@ -566,7 +566,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnA
     {
         constexpr uint32_t WPR = kWarps / RT;
         const uint32_t r = warp / WPR, seg = warp % WPR;
-        const float2 st = a.stat[(uint64_t) (w.h * a.row_tiles + w.tile) * RT + r];
+        const float2 st = row_stat<RT>(a, w, r);
         // exp(s - max) / sum as 2^((s - max) log2 e) * (1 / sum): within 2^-21 of the quotient before the truncation
         const float inv_sum = __frcp_rn(st.y);
         const uint16_t *srow = a.scores + w.score_at(a, r, 0);// 16-byte aligned: chunk and pitch are multiples of 64
@@ -814,9 +814,8 @@ INFINIOP_API infiniopStatus_t infiniopCreateAttentionDescriptor(infiniopHandle_t
     const uint64_t tiles = (uint64_t) nkvh * d->row_tiles, slots = tiles * d->splits * d->rt;
     auto pad = [](uint64_t bytes) { return (bytes + 255) / 256 * 256; };
     d->score_pitch = d->splits * d->chunk;
-    d->ws_ml = pad(2 * tiles * sizeof(uint32_t));// one counter per kernel and tile
-    d->ws_stat = d->ws_ml + pad(slots * sizeof(float2));
-    d->ws_acc = d->ws_stat + pad(tiles * d->rt * sizeof(float2));
+    d->ws_ml = pad(tiles * sizeof(uint32_t));// one counter per tile
+    d->ws_acc = d->ws_ml + pad(slots * sizeof(float2));
     d->ws_scores = d->ws_acc + pad(slots * dh * sizeof(float));
     d->ws_bytes = d->ws_scores + pad(tiles * d->rt * (uint64_t) d->score_pitch * sizeof(uint16_t));
     *desc_ptr = reinterpret_cast<infiniopAttentionDescriptor_t>(d);
@@ -851,7 +850,6 @@ INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t de
     a.kc = reinterpret_cast<uint16_t *>(k_cache), a.vc = reinterpret_cast<uint16_t *>(v_cache);
     a.counters = reinterpret_cast<uint32_t *>(ws);
     a.ml = reinterpret_cast<float2 *>(ws + d->ws_ml);
-    a.stat = reinterpret_cast<float2 *>(ws + d->ws_stat);
     a.acc = reinterpret_cast<float *>(ws + d->ws_acc);
     a.scores = reinterpret_cast<uint16_t *>(ws + d->ws_scores);
     a.nh = d->nh, a.nkvh = d->nkvh, a.group = d->group, a.seq = d->seq, a.dh = d->dh, a.pos = d->pos, a.total = d->total;
@@ -861,7 +859,7 @@ INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t de
     a.alpha = (float) (1.0 / sqrt((double) d->dh));// `float qk_alpha = 1 / sqrt(head_dim)`, operator.cc:136
 
     const bool vec = d->strides_vec && aligned16(q) && aligned16(k) && aligned16(v) && aligned16(k_cache) && aligned16(v_cache);
-    const uint32_t n_counters = 2 * d->nkvh * d->row_tiles;
+    const uint32_t n_counters = d->nkvh * d->row_tiles;
     const uint64_t units = 2ull * d->nkvh * d->seq * (vec ? d->dh / 8 : d->dh);
     uint64_t ctas = (units + kThreads - 1) / kThreads;
     const uint64_t cap = (uint64_t) d->sm_count * 8;
