@@ -331,7 +331,7 @@ def run_b200(args):
         ms = t0.elapsed_time(t1) / args.steps
         nbytes = 2 * nkvh * (pos + 1) * dh * 2
         print(json.dumps({"only": "attention", "q_heads": nh, "kv_heads": nkvh, "head_dim": dh, "cached_tokens": pos + 1,
-                          "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "launches_per_call": 3,
+                          "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "launches_per_call": 2,
                           "note": "back-to-back calls of one operator; bytes = K and V rows read once; not a bench value"}))
         return
     inputs = make_inputs(1000 + rank, only=args.only)

@@ -15,9 +15,10 @@
 // (q.k, the softmax denominator, p.v), so `out` agrees with the CPU composite
 // to a unit in the last place of fp16, not bit for bit.  The caches are byte-exact.
 //
-// Three launches, built for decoding, where the work is one read of the K and
-// V rows of each kv head (HBM-bound: 4 * dh bytes per cached token and kv head).
-// kv_append_kernel copies the new rows into both caches.  In the other two a
+// Built for decoding, where the work is one read of the K and V rows of each kv
+// head (HBM-bound: 4 * dh bytes per cached token and kv head).  kv_append_kernel
+// copies the new rows into both caches; for a single new token the first of
+// the other two kernels does that itself and there are two launches.  In these a
 // CTA takes one kv head, up to 8 query rows that share it (the heads of its
 // group x tokens) and one chunk of the cached tokens, so K and V are each read
 // once however many q heads share them:
@@ -74,6 +75,7 @@ struct AttnArgs {
     uint32_t nh, nkvh, group, seq, dh, pos, total;
     int64_t q_s0, q_s1, k_s0, k_s1, v_s0, v_s1, kc_s0, kc_s1, vc_s0, vc_s1;
     uint32_t row_tiles, splits, chunk, score_pitch;
+    uint32_t append_here;// one new token: the first of the two kernels writes its cache rows itself
     float alpha;
 };
 
@@ -206,6 +208,28 @@ __device__ __forceinline__ bool arrive_last(uint32_t *counter, uint32_t expected
     return last;
 }
 
+// Decoding one token (seq == 1) does without the launch of kv_append_kernel: every CTA of the first kernel whose
+// chunk holds cache row `pos` copies the token's k and v rows there before it reads the chunk (CTAs that share the
+// chunk write the same bytes), and the CTAs of chunk 0 clear the counters of the second kernel.
+template<bool VEC>
+__device__ __forceinline__ void append_one_token(const AttnArgs &a, uint32_t h, uint32_t tile, uint32_t split) {
+    if (!a.append_here) return;
+    if (split == 0 && threadIdx.x == 0) a.counters[h * a.row_tiles + tile] = 0;
+    const uint32_t c0 = split * a.chunk;
+    if (a.pos < c0 || a.pos >= c0 + a.chunk) return;// the same answer in every thread of the CTA
+    const uint32_t upr = VEC ? a.dh / 8 : a.dh;
+    for (uint32_t u = threadIdx.x; u < 2 * upr; u += kThreads) {
+        const bool is_v = u >= upr;
+        const uint32_t c = is_v ? u - upr : u;
+        const uint16_t *src = is_v ? a.v + (int64_t) h * a.v_s0 : a.k + (int64_t) h * a.k_s0;
+        uint16_t *dst = is_v ? a.vc + (int64_t) h * a.vc_s0 + (int64_t) a.pos * a.vc_s1
+                             : a.kc + (int64_t) h * a.kc_s0 + (int64_t) a.pos * a.kc_s1;
+        if (VEC) *reinterpret_cast<uint4 *>(dst + c * 8) = *reinterpret_cast<const uint4 *>(src + c * 8);
+        else dst[c] = src[c];
+    }
+    __syncthreads();
+}
+
 // After the chunk's scores stand in shared memory ([RT][pitch] floats): scores to the workspace with the chunk's
 // row maxima and exp-sums.
 template<int RT>
@@ -275,6 +299,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_scores_kernel(AttnArgs 
     const bool col_live = sub * 8 < a.dh;
     const uint32_t pitch = a.chunk + 1;
     const Work<RT> w(a);
+    append_one_token<VEC>(a, w.h, w.tile, w.split);
 
     float qf[RT][8];
 #pragma unroll
@@ -487,6 +512,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_scores_mma_kernel(AttnA
     const uint32_t kr = lane >> 2, c = lane & 3;
     const uint32_t pitch = a.chunk + 1;
     const Work<RT> w(a);
+    append_one_token<true>(a, w.h, w.tile, w.split);
     if (tid < 8) row_limit[tid] = tid < RT ? w.limit(a, w.tile * RT + tid) : -1;
 
     // operand B: query row kr of the tile (zeros past the tile's rows)
@@ -865,10 +891,13 @@ INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t de
     const uint64_t cap = (uint64_t) d->sm_count * 8;
     if (ctas > cap) ctas = cap;
     if (ctas < 1) ctas = 1;
-    if (vec) kv_append_kernel<true><<<(uint32_t) ctas, kThreads, 0, st>>>(a, n_counters);
-    else kv_append_kernel<false><<<(uint32_t) ctas, kThreads, 0, st>>>(a, n_counters);
-    const infiniopStatus_t status = check_launch("attention kv append");
-    if (status != STATUS_SUCCESS) return status;
+    a.append_here = d->seq == 1;
+    if (!a.append_here) {
+        if (vec) kv_append_kernel<true><<<(uint32_t) ctas, kThreads, 0, st>>>(a, n_counters);
+        else kv_append_kernel<false><<<(uint32_t) ctas, kThreads, 0, st>>>(a, n_counters);
+        const infiniopStatus_t status = check_launch("attention kv append");
+        if (status != STATUS_SUCCESS) return status;
+    }
     // INFINIOP_ATTENTION_KERNEL (any value) forces the multiply-add kernels, which otherwise serve unaligned
     // layouts and head sizes above 128
     if (vec && d->dh <= 128 && getenv("INFINIOP_ATTENTION_KERNEL") == nullptr) return launch_mma_rows(d, a, st);

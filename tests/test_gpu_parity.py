@@ -517,6 +517,33 @@ def test_attention(oracle, cuda_lib, monkeypatch, kernels, nh, nkvh, seq, dh, po
     assert torch.equal(kcd.cpu(), k_cache) and torch.equal(vcd.cpu(), v_cache)  # the oracle updated the host caches
 
 
+def test_attention_captures_into_a_cuda_graph(oracle, cuda_lib):
+    """The three launches of one call neither allocate nor synchronise: captured after one eager
+    call (one-time kernel attribute set-up), replayed on a cleared output and workspace."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(31)
+    nh, nkvh, dh, pos = 16, 4, 128, 3000
+    q, k, v = (torch.randn(sh, generator=g).half() for sh in ((nh, 1, dh), (nkvh, 1, dh), (nkvh, 1, dh)))
+    kc, vc = torch.randn((nkvh, pos + 1, dh), generator=g).half(), torch.randn((nkvh, pos + 1, dh), generator=g).half()
+    qd, kd, vd, kcd, vcd = (t.to(DEV) for t in (q, k, v, kc, vc))
+    out = torch.zeros((1, nh, dh), dtype=torch.float16, device=DEV)
+    with ops.AttentionOp(lib, handle, out, qd, kd, vd, kcd, vcd, pos) as op:
+        op(out, qd, kd, vd, kcd, vcd)
+        torch.cuda.synchronize()
+        eager = out.clone()
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            op(out, qd, kd, vd, kcd, vcd, torch.cuda.current_stream().cuda_stream)
+        out.zero_()
+        op.workspace.fill_(0x5A)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+    want = oracle.attention(q.numpy(), k.numpy(), v.numpy(), kc.numpy(), vc.numpy(), pos)
+    _close(_bits(out).reshape(want.shape), want, 1e-3, 1e-3)
+
+
 def test_attention_status_codes(cuda_lib):
     from operators_b200 import InfiniopError
 
