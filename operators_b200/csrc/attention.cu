@@ -822,15 +822,17 @@ INFINIOP_API infiniopStatus_t infiniopCreateAttentionDescriptor(infiniopHandle_t
         delete d;
         return STATUS_BAD_TENSOR_SHAPE;
     }
-    // chunks of the cached tokens: enough CTAs for two per SM, chunks of at least 64 and at most kMaxChunk tokens
+    // Chunks of the cached tokens, 64 .. kMaxChunk tokens each.  Two CTAs fit an SM and the kernels are fastest
+    // when the grid is a whole number of such resident sets (a few CTAs beyond one would run alone at the end):
+    // the smallest number of sets whose chunks stay within kMaxChunk.
     if (total > 0) {
         const uint64_t base = (uint64_t) nkvh * d->row_tiles;
-        uint64_t splits = (2ull * d->sm_count + base - 1) / base;
-        const uint64_t most = (total + 63) / 64;
+        uint64_t per_set = 2ull * d->sm_count / base;
+        if (per_set < 1) per_set = 1;
+        const uint64_t least = (total + kMaxChunk - 1) / kMaxChunk, most = (total + 63) / 64;
+        uint64_t splits = (least + per_set - 1) / per_set * per_set;
         if (splits > most) splits = most;
-        if (splits < 1) splits = 1;
-        uint64_t chunk = ((total + splits - 1) / splits + 63) / 64 * 64;
-        if (chunk > (uint64_t) kMaxChunk) chunk = kMaxChunk;
+        const uint64_t chunk = ((total + splits - 1) / splits + 63) / 64 * 64;
         d->chunk = (uint32_t) chunk;
         d->splits = (uint32_t) ((total + chunk - 1) / chunk);
     } else {
