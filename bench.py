@@ -206,6 +206,136 @@ class DecodeStep:
         ]
 
 
+def only_rearrange(lib, handle, dev, steps, warmup):
+    """Not part of the step: the permute on the way out of attention, for ncu captures."""
+    import torch
+
+    from operators_b200 import ops as _ops
+
+    src = torch.randn((ROPE_T, ROPE_H, ROPE_DH), device=dev).half()
+    dst = torch.as_strided(torch.empty(ROPE_T * ROPE_H * ROPE_DH, device=dev, dtype=torch.float16),
+                           (ROPE_T, ROPE_H, ROPE_DH), (ROPE_DH, ROPE_T * ROPE_DH, 1))  # [heads, tokens, dh] storage
+    op = _ops.RearrangeOp(lib, handle, dst, src)
+    for _ in range(warmup):
+        op(dst, src)
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        op(dst, src)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    nbytes = 2 * src.numel() * 2
+    return {"only": "rearrange", "shape": list(src.shape), "ms": round(ms, 5),
+            "gbs": round(nbytes / ms / 1e6, 1),
+            "note": "back-to-back launches of one operator; not a bench value"}
+
+
+def only_add_rms_norm(lib, handle, dev, steps, warmup):
+    """Not part of the step: the fused residual form beside the two calls it replaces."""
+    import torch
+
+    from operators_b200 import ops as _ops
+
+    shape = (ADD_T, ADD_D)
+    a = torch.randn(shape, device=dev).half()
+    b = torch.randn(shape, device=dev).half()
+    w = torch.rand(shape[1], device=dev).half()
+    total, y = torch.empty_like(a), torch.empty_like(a)
+    fused = _ops.AddRMSNormOp(lib, handle, y, total, a, b, w)
+    add_op, norm_op = _ops.AddOp(lib, handle, total, a, b), _ops.RMSNormOp(lib, handle, y, total, w)
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / steps
+
+    ms_fused = timed(lambda: fused(y, total, a, b, w))
+    ms_pair = timed(lambda: (add_op(total, a, b), norm_op(y, total, w)))
+    nbytes = 4 * a.numel() * 2 + w.numel() * 2  # a, b read; sum, y written (268 MB per launch: larger than L2)
+    return {"only": "add_rms_norm", "shape": list(shape), "ms": round(ms_fused, 5),
+            "gbs": round(nbytes / ms_fused / 1e6, 1), "ms_add_then_rms_norm": round(ms_pair, 5),
+            "note": "back-to-back launches of one operator; not a bench value"}
+
+
+def only_rope_rearrange(lib, handle, dev, steps, warmup):
+    """Not part of the step: K rotated into the cache beside the two calls it replaces."""
+    import torch
+
+    from operators_b200 import ops as _ops
+
+    tokens, kv_heads, dh, cache_len = 4 * ROPE_T, 8, ROPE_DH, 4 * ROPE_T
+    qkv = torch.randn((tokens, (ROPE_H + 2 * kv_heads) * dh), device=dev).half()
+    k = qkv[:, ROPE_H * dh:(ROPE_H + kv_heads) * dh].view(tokens, kv_heads, dh)  # the K slice of a qkv row
+    pos = torch.arange(tokens, device=dev, dtype=torch.int64)
+    sin, cos = _ops.sin_cos_table(tokens, dh, device=dev)
+    cache = torch.zeros((kv_heads, cache_len, dh), device=dev, dtype=torch.float16)
+    dst = cache.permute(1, 0, 2)
+    fused = _ops.RoPERearrangeOp(lib, handle, dst, k, pos, sin, cos)
+    rope_op, copy_op = _ops.RoPEOp(lib, handle, k, pos, sin, cos), _ops.RearrangeOp(lib, handle, dst, k)
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / steps
+
+    ms_fused = timed(lambda: fused(dst, k, pos, sin, cos))
+    ms_pair = timed(lambda: (rope_op(k, pos, sin, cos), copy_op(dst, k)))
+    nbytes = 2 * k.numel() * 2 + 2 * sin.numel() * 4 + pos.numel() * 8
+    return {"only": "rope_rearrange", "shape": list(k.shape), "ms": round(ms_fused, 5),
+            "gbs": round(nbytes / ms_fused / 1e6, 1), "ms_rope_then_rearrange": round(ms_pair, 5),
+            "note": "back-to-back launches of one operator on L2-sized data; not a bench value"}
+
+
+def only_attention(lib, handle, dev, steps, warmup):
+    """Not part of the step: one decoding token over a long KV cache."""
+    import torch
+
+    from operators_b200 import ops as _ops
+
+    nh, nkvh, dh, pos = 32, 8, ROPE_DH, 65535  # 268 MB of K and V rows per call: larger than L2
+    q = torch.randn((nh, 1, dh), device=dev).half()
+    k = torch.randn((nkvh, 1, dh), device=dev).half()
+    v = torch.randn((nkvh, 1, dh), device=dev).half()
+    k_cache = torch.randn((nkvh, pos + 1, dh), device=dev).half()
+    v_cache = torch.randn((nkvh, pos + 1, dh), device=dev).half()
+    out = torch.empty((1, nh, dh), device=dev, dtype=torch.float16)
+    op = _ops.AttentionOp(lib, handle, out, q, k, v, k_cache, v_cache, pos)
+    for _ in range(warmup):
+        op(out, q, k, v, k_cache, v_cache)
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        op(out, q, k, v, k_cache, v_cache)
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / steps
+    nbytes = 2 * nkvh * (pos + 1) * dh * 2
+    return {"only": "attention", "q_heads": nh, "kv_heads": nkvh, "head_dim": dh, "cached_tokens": pos + 1,
+            "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "launches_per_call": 2,
+            "note": "back-to-back calls of one operator; bytes = K and V rows read once; not a bench value"}
+
+
+NEXT_ROWS = {"rearrange": only_rearrange, "add_rms_norm": only_add_rms_norm, "rope_rearrange": only_rope_rearrange,
+             "attention": only_attention}
+
+
 def run_b200(args):
     import torch
 
@@ -224,115 +354,8 @@ def run_b200(args):
     lib = open_lib(os.path.join(ROOT, "operators_b200", "lib"))
     handle = create_handle(lib, DeviceEnum.DEVICE_CUDA, local)
 
-    if args.only == "rearrange":  # not part of the step: the permute on the way out of attention, for ncu captures
-        from operators_b200 import ops as _ops
-
-        src = torch.randn((ROPE_T, ROPE_H, ROPE_DH), device=dev).half()
-        dst = torch.as_strided(torch.empty(ROPE_T * ROPE_H * ROPE_DH, device=dev, dtype=torch.float16),
-                               (ROPE_T, ROPE_H, ROPE_DH), (ROPE_DH, ROPE_T * ROPE_DH, 1))  # [heads, tokens, dh] storage
-        op = _ops.RearrangeOp(lib, handle, dst, src)
-        for _ in range(args.warmup):
-            op(dst, src)
-        torch.cuda.synchronize()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(args.steps):
-            op(dst, src)
-        t1.record()
-        torch.cuda.synchronize()
-        ms = t0.elapsed_time(t1) / args.steps
-        nbytes = 2 * src.numel() * 2
-        print(json.dumps({"only": "rearrange", "shape": list(src.shape), "ms": round(ms, 5),
-                          "gbs": round(nbytes / ms / 1e6, 1),
-                          "note": "back-to-back launches of one operator; not a bench value"}))
-        return
-    if args.only == "add_rms_norm":  # not part of the step: the fused residual form beside the two calls it replaces
-        from operators_b200 import ops as _ops
-
-        shape = (ADD_T, ADD_D)
-        a = torch.randn(shape, device=dev).half()
-        b = torch.randn(shape, device=dev).half()
-        w = torch.rand(shape[1], device=dev).half()
-        total, y = torch.empty_like(a), torch.empty_like(a)
-        fused = _ops.AddRMSNormOp(lib, handle, y, total, a, b, w)
-        add_op, norm_op = _ops.AddOp(lib, handle, total, a, b), _ops.RMSNormOp(lib, handle, y, total, w)
-
-        def timed(fn):
-            for _ in range(args.warmup):
-                fn()
-            torch.cuda.synchronize()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record()
-            for _ in range(args.steps):
-                fn()
-            t1.record()
-            torch.cuda.synchronize()
-            return t0.elapsed_time(t1) / args.steps
-
-        ms_fused = timed(lambda: fused(y, total, a, b, w))
-        ms_pair = timed(lambda: (add_op(total, a, b), norm_op(y, total, w)))
-        nbytes = 4 * a.numel() * 2 + w.numel() * 2  # a, b read; sum, y written (268 MB per launch: larger than L2)
-        print(json.dumps({"only": "add_rms_norm", "shape": list(shape), "ms": round(ms_fused, 5),
-                          "gbs": round(nbytes / ms_fused / 1e6, 1), "ms_add_then_rms_norm": round(ms_pair, 5),
-                          "note": "back-to-back launches of one operator; not a bench value"}))
-        return
-    if args.only == "rope_rearrange":  # not part of the step: K rotated into the cache beside the two calls it replaces
-        from operators_b200 import ops as _ops
-
-        tokens, kv_heads, dh, cache_len = 4 * ROPE_T, 8, ROPE_DH, 4 * ROPE_T
-        qkv = torch.randn((tokens, (ROPE_H + 2 * kv_heads) * dh), device=dev).half()
-        k = qkv[:, ROPE_H * dh:(ROPE_H + kv_heads) * dh].view(tokens, kv_heads, dh)  # the K slice of a qkv row
-        pos = torch.arange(tokens, device=dev, dtype=torch.int64)
-        sin, cos = _ops.sin_cos_table(tokens, dh, device=dev)
-        cache = torch.zeros((kv_heads, cache_len, dh), device=dev, dtype=torch.float16)
-        dst = cache.permute(1, 0, 2)
-        fused = _ops.RoPERearrangeOp(lib, handle, dst, k, pos, sin, cos)
-        rope_op, copy_op = _ops.RoPEOp(lib, handle, k, pos, sin, cos), _ops.RearrangeOp(lib, handle, dst, k)
-
-        def timed(fn):
-            for _ in range(args.warmup):
-                fn()
-            torch.cuda.synchronize()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record()
-            for _ in range(args.steps):
-                fn()
-            t1.record()
-            torch.cuda.synchronize()
-            return t0.elapsed_time(t1) / args.steps
-
-        ms_fused = timed(lambda: fused(dst, k, pos, sin, cos))
-        ms_pair = timed(lambda: (rope_op(k, pos, sin, cos), copy_op(dst, k)))
-        nbytes = 2 * k.numel() * 2 + 2 * sin.numel() * 4 + pos.numel() * 8
-        print(json.dumps({"only": "rope_rearrange", "shape": list(k.shape), "ms": round(ms_fused, 5),
-                          "gbs": round(nbytes / ms_fused / 1e6, 1), "ms_rope_then_rearrange": round(ms_pair, 5),
-                          "note": "back-to-back launches of one operator on L2-sized data; not a bench value"}))
-        return
-    if args.only == "attention":  # not part of the step: one decoding token over a long KV cache
-        from operators_b200 import ops as _ops
-
-        nh, nkvh, dh, pos = 32, 8, ROPE_DH, 65535  # 268 MB of K and V rows per call: larger than L2
-        q = torch.randn((nh, 1, dh), device=dev).half()
-        k = torch.randn((nkvh, 1, dh), device=dev).half()
-        v = torch.randn((nkvh, 1, dh), device=dev).half()
-        k_cache = torch.randn((nkvh, pos + 1, dh), device=dev).half()
-        v_cache = torch.randn((nkvh, pos + 1, dh), device=dev).half()
-        out = torch.empty((1, nh, dh), device=dev, dtype=torch.float16)
-        op = _ops.AttentionOp(lib, handle, out, q, k, v, k_cache, v_cache, pos)
-        for _ in range(args.warmup):
-            op(out, q, k, v, k_cache, v_cache)
-        torch.cuda.synchronize()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(args.steps):
-            op(out, q, k, v, k_cache, v_cache)
-        t1.record()
-        torch.cuda.synchronize()
-        ms = t0.elapsed_time(t1) / args.steps
-        nbytes = 2 * nkvh * (pos + 1) * dh * 2
-        print(json.dumps({"only": "attention", "q_heads": nh, "kv_heads": nkvh, "head_dim": dh, "cached_tokens": pos + 1,
-                          "ms": round(ms, 5), "gbs": round(nbytes / ms / 1e6, 1), "launches_per_call": 2,
-                          "note": "back-to-back calls of one operator; bytes = K and V rows read once; not a bench value"}))
+    if args.only in NEXT_ROWS:  # operators either side of the step, one at a time (for ncu captures and tuning)
+        print(json.dumps(NEXT_ROWS[args.only](lib, handle, dev, args.steps, args.warmup)))
         return
     inputs = make_inputs(1000 + rank, only=args.only)
     step = DecodeStep(lib, handle, dev, inputs)
@@ -443,7 +466,7 @@ def run_b200(args):
         big_ms = b0.elapsed_time(b1) / (12 * rot)
         big_bytes = 2 * n_big * d_big * 2 + d_big * 2
         rms_scaled = {"shape": [n_big, d_big], "bytes": big_bytes, "ms": round(big_ms, 5),
-                      "gbs": round(big_bytes / big_ms / 1e6, 1)}
+            "gbs": round(big_bytes / big_ms / 1e6, 1)}
         big.destroy()
         del xs, ys
     # ---- RoPE at four times the tokens (the configuration's 67 MB pass in a few microseconds more than launch ramp
@@ -558,7 +581,7 @@ def run_b200(args):
         gbs = ALGO_BYTES[o] * world / (per_op_ms[o] * 1e-3) / 1e9
         ops_out[o] = {"bytes": ALGO_BYTES[o], "ms": round(per_op_ms[o], 5),
                       "ms_median": round(per_op_all[o][len(per_op_all[o]) // 2], 5), "ms_best": round(per_op_all[o][0], 5),
-                      "gbs": round(gbs, 1),
+            "gbs": round(gbs, 1),
                       "frac_of_%s_peak" % peak_kind: round(gbs / world / peak, 4),
                       "frac_of_8TBs": round(gbs / world / NOMINAL_HBM_GBS, 4)}
     ops_out["random_sample"]["tokens_per_s"] = round(RS_B * world / (per_op_ms["random_sample"] * 1e-3), 1)
@@ -602,6 +625,9 @@ def run_b200(args):
     line["roofline"] = {"kernel": "swiglu_vec8_kernel", "bound": "hbm", "achieved": round(ach, 1), "peak": peak,
                         "peak_kind": "of " + peak_kind, "unit": "GB/s", "frac": round(ach / peak, 4),
                         "traffic": NCU_TRAFFIC_BYTES["swiglu"]}
+    if world == 1 and not args.only:
+        # the operators built either side of the step (not part of `value`): each timed alone after the step's runs
+        line["next_rows"] = {name: fn(lib, handle, dev, 20, 3) for name, fn in NEXT_ROWS.items()}
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(sample_seconds=20.0)
