@@ -512,6 +512,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_scores_mma_kernel(AttnA
     const uint32_t kr = lane >> 2, c = lane & 3;
     const uint32_t pitch = a.chunk + 1;
     const Work<RT> w(a);
+    asm volatile("griddepcontrol.launch_dependents;");// the second kernel's CTAs may queue up behind this one's
     append_one_token<true>(a, w.h, w.tile, w.split);
     if (tid < 8) row_limit[tid] = tid < RT ? w.limit(a, w.tile * RT + tid) : -1;
 
@@ -586,7 +587,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnA
     // the first rows of V are on their way while the probabilities are formed
     const uint16_t *vbase = a.vc + (int64_t) w.h * a.vc_s0 + (int64_t) w.c0 * a.vc_s1;
     uint4 lo[NB], hi[NB], nlo[NB], nhi[NB];
-    if (warp < groups) load_rows16<NB>(lo, hi, vbase, a.vc_s1, warp * 16, w.n, a.dh, lane);
+    // (not in the chunk whose newest row the first kernel itself writes)
+    const bool early = !(a.append_here && a.pos >= w.c0 && a.pos < w.c0 + a.chunk);
+    if (early && warp < groups) load_rows16<NB>(lo, hi, vbase, a.vc_s1, warp * 16, w.n, a.dh, lane);
+    asm volatile("griddepcontrol.wait;" ::: "memory");// everything the first kernel wrote is visible from here on
+    if (!early && warp < groups) load_rows16<NB>(lo, hi, vbase, a.vc_s1, warp * 16, w.n, a.dh, lane);
 
     // probabilities of the chunk: kWarps / RT warps per row, eight scores per lane and step
     {
@@ -681,7 +686,23 @@ infiniopStatus_t launch_mma(const AttnDesc *d, const AttnArgs &args, cudaStream_
     attention_scores_mma_kernel<RT, NB><<<grid, kThreads, smem_scores, st>>>(args);
     const infiniopStatus_t status = check_launch("attention scores");
     if (status != STATUS_SUCCESS) return status;
-    attention_values_mma_kernel<RT, NB><<<grid, kThreads, smem_values, st>>>(args);
+    // Programmatic dependent launch: the CTAs of the second kernel may take their places while the last CTAs of the
+    // first are still at work; they request their first rows of V and then wait (griddepcontrol.wait) until the
+    // whole first kernel has finished and its scores are visible.  The first kernel releases them when it starts.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_values;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, attention_values_mma_kernel<RT, NB>, args) != cudaSuccess) {
+        cudaGetLastError();
+        return STATUS_EXECUTION_FAILED;
+    }
     return check_launch("attention values");
 }
 
