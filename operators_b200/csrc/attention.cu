@@ -276,6 +276,11 @@ template<int RT>
 __device__ __forceinline__ float2 row_stat(const AttnArgs &a, const Work<RT> &w, uint32_t r) {
     const uint32_t lane = threadIdx.x & 31;
     const float2 *ml = a.ml + w.first_slot(a) + r;
+    if (a.splits <= 32) {// one pair per lane: a single trip to memory
+        const float2 part = lane < a.splits ? ml[(uint64_t) lane * RT] : make_float2(-INFINITY, 0.f);
+        const float top = warp_max(part.x);
+        return make_float2(top, warp_sum(part.x > -INFINITY ? part.y * expf(part.x - top) : 0.f));
+    }
     float big = -INFINITY;
     for (uint32_t s = lane; s < a.splits; s += 32) big = fmaxf(big, ml[(uint64_t) s * RT].x);
     big = warp_max(big);
@@ -597,12 +602,20 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnA
     {
         constexpr uint32_t WPR = kWarps / RT;
         const uint32_t r = warp / WPR, seg = warp % WPR;
+        const uint16_t *srow = a.scores + w.score_at(a, r, 0);// 16-byte aligned: chunk and pitch are multiples of 64
+        // the first scores are requested before the row's statistics are merged (both come from L2 or HBM)
+        constexpr uint32_t kStep = WPR * 256, kAhead = 4;
+        const uint32_t j0 = (seg * 32 + lane) * 8, lim = groups * 16;
+        uint4 ahead[kAhead];
+#pragma unroll
+        for (uint32_t u = 0; u < kAhead; ++u) {
+            ahead[u] = make_uint4(0, 0, 0, 0);
+            if (j0 + u * kStep < lim) ahead[u] = __ldcs(reinterpret_cast<const uint4 *>(srow + j0 + u * kStep));
+        }
         const float2 st = row_stat<RT>(a, w, r);
         // exp(s - max) / sum as 2^((s - max) log2 e) * (1 / sum): within 2^-21 of the quotient before the truncation
         const float inv_sum = __frcp_rn(st.y);
-        const uint16_t *srow = a.scores + w.score_at(a, r, 0);// 16-byte aligned: chunk and pitch are multiples of 64
-        for (uint32_t j = (seg * 32 + lane) * 8; j < groups * 16; j += WPR * 256) {
-            const uint4 raw = __ldcs(reinterpret_cast<const uint4 *>(srow + j));
+        auto emit = [&](uint4 raw, uint32_t j) {
             const uint16_t *sc16 = reinterpret_cast<const uint16_t *>(&raw);
             uint32_t packed[4];
 #pragma unroll
@@ -615,7 +628,12 @@ __global__ void __launch_bounds__(kThreads, 2) attention_values_mma_kernel(AttnA
                 packed[e >> 1] = (e & 1) ? (packed[e >> 1] | (bits << 16)) : bits;
             }
             *reinterpret_cast<uint4 *>(p16 + r * pitch16 + j) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        };
+#pragma unroll
+        for (uint32_t u = 0; u < kAhead; ++u) {
+            if (j0 + u * kStep < lim) emit(ahead[u], j0 + u * kStep);
         }
+        for (uint32_t j = j0 + kAhead * kStep; j < lim; j += kStep) emit(__ldcs(reinterpret_cast<const uint4 *>(srow + j)), j);
     }
     __syncthreads();
 
