@@ -471,6 +471,11 @@ ATTENTION_CASES = [
     (8, 2, 37, 64, 0, 64, None, None),
     (8, 4, 19, 128, 11, 64, (128, 8 * 128, 1), None),
     (3, 3, 70, 32, 2100, 2200, None, None),
+    # the smallest cases: an empty cache, a cache exactly as long as needed, five q heads on one kv head
+    (4, 4, 1, 64, 0, 4, None, None),
+    (5, 1, 1, 32, 0, 1, None, None),
+    (2, 1, 3, 16, 0, 3, None, None),
+    (10, 2, 1, 128, 63, 64, None, None),
 ]
 
 
