@@ -9,6 +9,20 @@
 #include "infiniop.h"
 
 /*
+ * Kernel-family switch for tests and benchmarks (no counterpart in the
+ * reference).  Several operators have two kernel families, chosen per call
+ * from shapes and alignment; this forces one of them process-wide so that both
+ * can be held to the same oracle on the same inputs.  variant 0 restores the
+ * library's own choice.
+ *   family 0 (RoPE):          1 = the strided kernel instead of the bulk-copy pipeline
+ *   family 1 (random sample): 1 = the global-memory kernel instead of the shared-memory cluster kernel
+ *   family 2 (attention):     1 = the multiply-add kernels instead of the tensor-core kernels
+ *   family 3 (matmul):        1 = the CUDA-core kernel instead of the tcgen05 kernel
+ * Returns STATUS_BAD_PARAM for an unknown family or a negative variant.
+ */
+INFINIOP_API infiniopStatus_t infiniopExtSelectKernel(int family, int variant);
+
+/*
  * Batched random sample: `rows` independent rows of fp16 logits
  * [rows, voc] (voc taken from the descriptor, `row_stride` elements between
  * rows) sampled in ONE launch, row r with the uniform draw random_vals[r]
@@ -83,8 +97,11 @@ INFINIOP_API infiniopStatus_t infiniopRandomSampleShardFinish(infiniopHandle_t h
  * infiniopRandomSampleBatch.
  *
  * Limits and rules:
- *  - rows * round_up(voc, 256) * 2 + 256 bytes must fit in 32 MiB (64 rows of
- *    128256 logits do); larger requests return STATUS_INSUFFICIENT_WORKSPACE
+ *  - The array is used by the kernel that serves rows of more than 262144
+ *    logits (shorter rows are sampled out of shared memory and need no scratch
+ *    at all, whatever their number).  For those long rows
+ *    rows * round_up(voc, 256) * 2 + 256 bytes must fit in 32 MiB (40 rows of
+ *    300000 logits do); larger requests return STATUS_INSUFFICIENT_WORKSPACE
  *    and print the sizes.
  *  - The first call on each device looks up the array's device address
  *    (cudaGetSymbolAddress with that device current); make that first call

@@ -939,9 +939,9 @@ INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t de
         const infiniopStatus_t status = check_launch("attention kv append");
         if (status != STATUS_SUCCESS) return status;
     }
-    // INFINIOP_ATTENTION_KERNEL (any value) forces the multiply-add kernels, which otherwise serve unaligned
-    // layouts and head sizes above 128
-    if (vec && d->dh <= 128 && getenv("INFINIOP_ATTENTION_KERNEL") == nullptr) return launch_mma_rows(d, a, st);
+    // the multiply-add kernels serve unaligned layouts and head sizes above 128 (and every layout when
+    // infiniopExtSelectKernel asked for them)
+    if (vec && d->dh <= 128 && kernel_choice(kFamilyAttention) != 1) return launch_mma_rows(d, a, st);
     return vec ? launch_rows<true>(d, a, st) : launch_rows<false>(d, a, st);
 }
 

@@ -44,16 +44,26 @@ __device__ __forceinline__ uint64_t visible_cols(uint64_t i, uint64_t seq_len, u
 // the output) as the CPU code does, which costs less than holding the row in
 // fp32 would cost in occupancy.  (The compiler is free to keep the first
 // evaluation instead; measured, that is the faster of the two on B200.)
-template<int VPT, bool CTA_ROW>
-__global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total,
-                                           uint32_t vecs, int64_t stride_b, int64_t stride_i, FastDiv seq_div) {
+//
+// Who owns a row: one warp, one CTA, or one thread-block cluster of 2, 4 or 8 CTAs whose maxima and sums meet
+// over distributed shared memory (rows of more than 8 Ki columns).  The row-per-CTA forms are launched with up
+// to 1024 threads, hence their launch bound (64 registers per thread).
+enum RowOwner { WARP_ROW = 0, CTA_ROW = 1, CLUSTER_ROW = 2 };
+
+template<int VPT, int OWNER>
+__global__ void __launch_bounds__(OWNER == WARP_ROW ? 256 : 1024)
+    causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total, uint32_t vecs,
+                               int64_t stride_b, int64_t stride_i, FastDiv seq_div) {
     __shared__ float red_m[32], red_s[32];// one slot array per reduction of a row: one barrier each
+    __shared__ float part_m, part_s;      // this CTA's maximum and sum, read by the whole cluster
     const int lane = threadIdx.x & 31;
-    const uint32_t group = CTA_ROW ? blockDim.x : 32;
-    const uint32_t t = CTA_ROW ? threadIdx.x : lane;
-    const uint64_t rows_per_cta = CTA_ROW ? 1 : (blockDim.x >> 5);
-    const uint64_t row0 = (uint64_t) blockIdx.x * rows_per_cta + (CTA_ROW ? 0 : (threadIdx.x >> 5));
-    const uint64_t row_step = (uint64_t) gridDim.x * rows_per_cta;
+    const uint32_t cl = OWNER == CLUSTER_ROW ? cluster_size() : 1;
+    const uint32_t group = OWNER == WARP_ROW ? 32 : blockDim.x * cl;
+    const uint32_t t = OWNER == WARP_ROW ? lane : (OWNER == CLUSTER_ROW ? cluster_rank() * blockDim.x : 0) + threadIdx.x;
+    const uint64_t rows_per_cta = OWNER == WARP_ROW ? (blockDim.x >> 5) : 1;
+    const uint64_t row0 = OWNER == WARP_ROW ? (uint64_t) blockIdx.x * rows_per_cta + (threadIdx.x >> 5)
+                                            : (uint64_t) (blockIdx.x / cl);
+    const uint64_t row_step = OWNER == WARP_ROW ? (uint64_t) gridDim.x * rows_per_cta : (uint64_t) (gridDim.x / cl);
     constexpr uint32_t kNegInf2 = 0xFC00FC00u;// two fp16 -inf
 
     for (uint64_t row = row0; row < rows; row += row_step) {
@@ -91,7 +101,8 @@ __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t 
             for (int k = 0; k < 4; ++k) m2 = __hmax2(m2, *reinterpret_cast<const __half2 *>(&p[k]));
         }
         float m = fmaxf(__low2float(m2), __high2float(m2));
-        m = CTA_ROW ? cta_reduce_alt<true>(m, red_m) : warp_max(m);
+        if (OWNER == CLUSTER_ROW) m = cluster_reduce<true>(m, red_m, &part_m, cl);
+        else m = OWNER == CTA_ROW ? cta_reduce_alt<true>(m, red_m) : warp_max(m);
         // exp(x - m) = 2^(x*log2e - m*log2e); the rounding of m*log2e is common to
         // the whole row and cancels in the quotient.
         const float mk = -m * kLog2e;
@@ -106,7 +117,8 @@ __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t 
                 s += fast_exp2(fmaf(f.y, kLog2e, mk));
             }
         }
-        s = CTA_ROW ? cta_reduce_alt<false>(s, red_s) : warp_sum(s);
+        if (OWNER == CLUSTER_ROW) s = cluster_reduce<false>(s, red_s, &part_s, cl);
+        else s = OWNER == CTA_ROW ? cta_reduce_alt<false>(s, red_s) : warp_sum(s);
         const float r = __frcp_rn(s);
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
@@ -126,6 +138,8 @@ __global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t 
                 st_stream(yr + (uint64_t) j * 8, out);
             }
         }
+        // no CTA may leave (or start its next row) while a neighbour still reads its maximum or sum
+        if (OWNER == CLUSTER_ROW) cluster_sync_all();
     }
 }
 
@@ -159,20 +173,27 @@ __global__ void causal_softmax_generic_kernel(uint16_t *y, uint64_t rows, uint64
 }
 
 template<int VPT>
-void launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uint32_t vecs, uint16_t *y,
+void launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, uint16_t *y,
                  cudaStream_t st) {
     const uint64_t rows = d->batch * d->seq_len;
     const FastDiv seq_div(d->seq_len <= 0xFFFFFFFFull && d->seq_len > 0 ? (uint32_t) d->seq_len : 1u);
     if (cta_row) {
-        const uint64_t cap = 0x7FFFFFFFull;// one CTA per row; rows beyond 2^31 loop
-        const uint32_t grid = (uint32_t) (rows < cap ? rows : cap);
-        causal_softmax_regs_kernel<VPT, true>
-            <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
+        if constexpr (VPT <= 4) {// eight vectors per thread exist for warp rows only
+            const uint64_t cap = 0x7FFFFFFFull / cl;// one CTA (cluster) per row; rows beyond that loop
+            const uint32_t grid = (uint32_t) (rows < cap ? rows : cap) * cl;
+            if (cl > 1) {
+                launch_cluster(causal_softmax_regs_kernel<VPT, CLUSTER_ROW>, grid, threads, cl, st, y, rows, d->seq_len,
+                               d->total, vecs, d->stride_b, d->stride_i, seq_div);
+            } else {
+                causal_softmax_regs_kernel<VPT, CTA_ROW>
+                    <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
+            }
+        }
     } else {
         const uint64_t ctas = (rows + 7) / 8;
         const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-        causal_softmax_regs_kernel<VPT, false>
+        causal_softmax_regs_kernel<VPT, WARP_ROW>
             <<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
     }
 }
@@ -225,35 +246,32 @@ INFINIOP_API infiniopStatus_t infiniopCausalSoftmax(infiniopCausalSoftmaxDescrip
     auto st = reinterpret_cast<cudaStream_t>(stream);
     auto *y = reinterpret_cast<uint16_t *>(data);
 
-    const bool vec_ok = d->total % 8 == 0 && d->total / 8 <= 8192 && d->stride_i % 8 == 0 && d->stride_b % 8 == 0 &&
+    // rows of up to 8 CTAs x 1024 threads x 4 vectors stay in registers
+    const bool vec_ok = d->total % 8 == 0 && d->total / 8 <= 32768 && d->stride_i % 8 == 0 && d->stride_b % 8 == 0 &&
                         aligned16(data);
     if (vec_ok) {
         const uint32_t vecs = (uint32_t) (d->total / 8);
         const bool big = rows * (uint64_t) vecs >= (1u << 20);
         int vpt;
         bool cta_row;
-        uint32_t threads = 256;
+        uint32_t threads = 256, cl = 1;
         if (big && vecs <= 256) {
             cta_row = false;
             const uint32_t need = (vecs + 31) / 32;
             vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
         } else {
             cta_row = true;
-            const uint32_t min_vpt = (vecs + 1023) / 1024;
             // measured at [32,512,4096]: 4 vectors per thread (128 threads per 4096-column
-            // row) 50 us, 8 per thread 52 us, 2 per thread 63 us
-            // rows of 16384 columns and more: 8 per thread (0.73 against 0.67 of the copy bandwidth at
-            // [16, 512, 16384], 0.55 against 0.50 at [8, 512, 32768]; no difference at 8192 columns)
-            uint32_t want = big ? (vecs >= 2048 ? 8 : 4) : min_vpt;
-            if (want < min_vpt) want = min_vpt;
-            vpt = want <= 1 ? 1 : want <= 2 ? 2 : want <= 4 ? 4 : 8;
-            threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;
+            // row) 50 us, 8 per thread 52 us, 2 per thread 63 us.  Rows of more than 1024 vectors
+            // are spread over a cluster of 2, 4 or 8 CTAs.
+            const RowLaunch shape = row_launch_shape(vecs, big ? 4 : 1);
+            vpt = shape.vpt, threads = shape.threads, cl = shape.cl;
         }
         switch (vpt) {
-            case 1: launch_regs<1>(d, cta_row, threads, vecs, y, st); break;
-            case 2: launch_regs<2>(d, cta_row, threads, vecs, y, st); break;
-            case 4: launch_regs<4>(d, cta_row, threads, vecs, y, st); break;
-            default: launch_regs<8>(d, cta_row, threads, vecs, y, st); break;
+            case 1: launch_regs<1>(d, cta_row, threads, cl, vecs, y, st); break;
+            case 2: launch_regs<2>(d, cta_row, threads, cl, vecs, y, st); break;
+            case 4: launch_regs<4>(d, cta_row, threads, cl, vecs, y, st); break;
+            default: launch_regs<8>(d, cta_row, threads, cl, vecs, y, st); break;
         }
         return check_launch("causal_softmax");
     }

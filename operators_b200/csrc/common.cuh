@@ -66,6 +66,10 @@ static inline infiniopStatus_t check_launch(const char *what) {
     return STATUS_SUCCESS;
 }
 
+// Kernel-family override set through infiniopExtSelectKernel (runtime.cu); 0 = the library's own choice.
+enum KernelFamily { kFamilyRoPE = 0, kFamilyRandomSample = 1, kFamilyAttention = 2, kFamilyMatmul = 3, kFamilyCount = 8 };
+int kernel_choice(int family);
+
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 static inline bool aligned4(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 3u) == 0; }
 
@@ -160,6 +164,92 @@ __device__ __forceinline__ float cta_reduce_alt(float v, float *slot) {
     __syncthreads();
     float r = slot[0];
     for (int w = 1; w < nwarps; ++w) r = IS_MAX ? fmaxf(r, slot[w]) : r + slot[w];
+    return r;
+}
+
+// ---- thread-block clusters: one row spread over up to 8 CTAs ------------------------------------------------
+// Rank of this CTA in its cluster / number of CTAs per cluster (1 when the launch carries no cluster dimension).
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+// Hardware barrier over all threads of all CTAs of the cluster (release / acquire: shared-memory writes made
+// before it are visible to distributed-shared-memory reads made after it).  Cannot hang: every thread of every
+// CTA of a cluster reaches it, the kernels below have no early exit.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Reads a float from the same shared-memory variable of CTA `rank` of the cluster.
+__device__ __forceinline__ float ld_dsmem_f32(const float *local, uint32_t rank) {
+    const uint32_t a = (uint32_t) __cvta_generic_to_shared(local);
+    uint32_t ra;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+    return v;
+}
+
+// Cluster-wide reduction for kernels that give a whole cluster (cl CTAs, a power of two up to 8) to a row:
+// the CTA-wide result goes to `*mine` (one float of shared memory per reduction of a row, not reused before the
+// row's closing cluster_sync_all), one cluster barrier, then lane r of every warp fetches CTA r's part over
+// distributed shared memory and a butterfly over the first cl lanes combines them in the same order everywhere,
+// so every thread of the cluster holds the same bits.  All threads of the cluster must call it.
+template<bool IS_MAX>
+__device__ __forceinline__ float cluster_reduce(float v, float *slot, float *mine, uint32_t cl) {
+    v = cta_reduce_alt<IS_MAX>(v, slot);
+    if (threadIdx.x == 0) *mine = v;
+    cluster_sync_all();
+    const uint32_t lane = threadIdx.x & 31;
+    float p = ld_dsmem_f32(mine, lane < cl ? lane : 0);
+    for (uint32_t o = cl >> 1; o > 0; o >>= 1) {
+        const float q = __shfl_xor_sync(0xffffffffu, p, o);
+        p = IS_MAX ? fmaxf(p, q) : p + q;
+    }
+    return __shfl_sync(0xffffffffu, p, 0);
+}
+
+// One-dimensional launch with `cl` consecutive CTAs forming a cluster (grid must be a multiple of cl).
+template<typename... KArgs, typename... Args>
+static inline cudaError_t launch_cluster(void (*kernel)(KArgs...), uint32_t grid, uint32_t threads, uint32_t cl,
+                                         cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// Shape of a launch that gives each row to one CTA or to one cluster: `cl` CTAs of `threads` threads, each
+// thread holding `vpt` 128-bit vectors.  `want_vpt` is the preferred vectors per thread (bytes in flight when
+// there are many rows); rows that need more than 1024 threads at that depth are spread over a cluster first and
+// deepened second.  Covers rows of up to 8 * 1024 * 4 vectors.
+struct RowLaunch {
+    uint32_t cl, threads;
+    int vpt;
+};
+static inline RowLaunch row_launch_shape(uint32_t vecs, uint32_t want_vpt) {
+    RowLaunch r;
+    const uint32_t ctas = (vecs + 1023) / 1024;// CTAs needed at one vector per thread
+    r.cl = ctas <= 1 ? 1 : ctas <= 2 ? 2 : ctas <= 4 ? 4 : 8;
+    const uint32_t per_cta = (vecs + r.cl - 1) / r.cl;
+    const uint32_t min_vpt = (per_cta + 1023) / 1024;
+    uint32_t want = want_vpt < min_vpt ? min_vpt : want_vpt;
+    r.vpt = want <= 1 ? 1 : want <= 2 ? 2 : 4;
+    r.threads = ((per_cta + r.vpt - 1) / r.vpt + 31) / 32 * 32;
     return r;
 }
 

@@ -42,6 +42,7 @@
 #include <cooperative_groups.h>
 
 #include <cstdlib>
+#include <atomic>
 #include <new>
 
 using namespace b200;
@@ -628,6 +629,13 @@ uint64_t random_sample_workspace_bytes(int voc, int rows) {
     return random_sample_work_pitch(voc) * 2ull * (uint64_t) rows + 256;
 }
 
+// True when this call will run the kernel that keeps the rows' working copies in the workspace (rows too long for
+// the cluster's shared memory, or that kernel asked for through infiniopExtSelectKernel).
+bool random_sample_uses_workspace(const RandomSampleArgs &a) {
+    const bool sampling = a.topp > 0.f && a.topk > 1;
+    return sampling && !(random_sample_pair_supported(a.voc) && kernel_choice(kFamilyRandomSample) != 1);
+}
+
 infiniopStatus_t random_sample_launch(const RandomSampleArgs &args_in, int rows, void *workspace,
                                       uint64_t workspace_size, cudaStream_t st) {
     RandomSampleArgs a = args_in;
@@ -639,12 +647,8 @@ infiniopStatus_t random_sample_launch(const RandomSampleArgs &args_in, int rows,
             return STATUS_BAD_PARAM;
         }
         if (!(a.temperature > 0.f)) return STATUS_BAD_PARAM;
-        // Rows that fit two CTAs' shared memory never touch the workspace.  The
-        // environment switch exists so that the tests can hold both kernels to
-        // the same oracle on the same inputs.
-        const char *pick = getenv("INFINIOP_RANDOM_SAMPLE_KERNEL");
-        const bool want_global = pick != nullptr && pick[0] == 'g';
-        if (random_sample_pair_supported(a.voc) && !want_global) return random_sample_pair_launch(a, rows, st);
+        // Rows that fit the shared memory of a cluster never touch the workspace.
+        if (!random_sample_uses_workspace(a)) return random_sample_pair_launch(a, rows, st);
         if (workspace == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
         if (workspace_size < random_sample_workspace_bytes(a.voc, rows)) return STATUS_INSUFFICIENT_WORKSPACE;
         a.work = reinterpret_cast<uint16_t *>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~(uintptr_t) 255);
@@ -788,8 +792,10 @@ static __device__ __align__(256) unsigned char g_sample_scratch[kStaticScratchBy
 
 namespace {
 constexpr int kMaxDevices = 64;
-void *g_scratch_addr[kMaxDevices];// device address of g_sample_scratch per device ordinal
-bool g_scratch_ready[kMaxDevices];
+// Device address of g_sample_scratch per device ordinal, published with a release store once it is known.
+// Two host threads that make the first call on a device together both look the address up and store the same
+// value; nobody reads a half-written entry.
+std::atomic<void *> g_scratch_addr[kMaxDevices];
 }// namespace
 
 INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchStatic(infiniopRandomSampleDescriptor_t desc, void *results,
@@ -801,30 +807,7 @@ INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchStatic(infiniopRandomSamp
     if (rows == 0) return STATUS_SUCCESS;
     auto *d = reinterpret_cast<RandomSampleDesc *>(desc);
     if (d->device_id < 0 || d->device_id >= kMaxDevices) return STATUS_BAD_DEVICE;
-    if (rows > 0x7FFFFFFFull || random_sample_workspace_bytes(d->voc, (int) rows) > kStaticScratchBytes) {
-        fprintf(stderr,
-                "infiniop[b200]: infiniopRandomSampleBatchStatic: %llu rows of %d logits need %llu bytes of scratch, "
-                "the built-in array holds %llu; use infiniopRandomSampleBatch with a workspace\n",
-                (unsigned long long) rows, d->voc,
-                (unsigned long long) (rows > 0x7FFFFFFFull ? 0 : random_sample_workspace_bytes(d->voc, (int) rows)),
-                (unsigned long long) kStaticScratchBytes);
-        return STATUS_INSUFFICIENT_WORKSPACE;
-    }
-    DeviceGuard guard(d->device_id);
-    if (!g_scratch_ready[d->device_id]) {
-        // The array's name is only a host-side handle; the kernel needs the
-        // address the array has on THIS device, asked for once per device with
-        // that device current (the guard above made it so).
-        void *p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_sample_scratch);
-        if (e != cudaSuccess || p == nullptr) {
-            fprintf(stderr, "infiniop[b200]: cudaGetSymbolAddress(g_sample_scratch) failed: %s\n", cudaGetErrorString(e));
-            cudaGetLastError();
-            return STATUS_EXECUTION_FAILED;
-        }
-        g_scratch_addr[d->device_id] = p;
-        g_scratch_ready[d->device_id] = true;
-    }
+    if (rows > 0x7FFFFFFFull) return STATUS_BAD_PARAM;
     RandomSampleArgs a{};
     a.logits = reinterpret_cast<const uint16_t *>(logits);
     a.logits_stride = row_stride;
@@ -837,6 +820,29 @@ INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchStatic(infiniopRandomSamp
     a.temperature = temperature;
     a.voc = d->voc;
     a.debug = nullptr;
-    return random_sample_launch(a, (int) rows, g_scratch_addr[d->device_id], kStaticScratchBytes,
-                                reinterpret_cast<cudaStream_t>(stream));
+    // The size limit binds only the kernel that keeps its working copies in the array (rows of more than
+    // 262144 logits); shorter rows are sampled out of shared memory and use no scratch at all.
+    if (random_sample_uses_workspace(a) && random_sample_workspace_bytes(d->voc, (int) rows) > kStaticScratchBytes) {
+        fprintf(stderr,
+                "infiniop[b200]: infiniopRandomSampleBatchStatic: %llu rows of %d logits need %llu bytes of scratch, "
+                "the built-in array holds %llu; use infiniopRandomSampleBatch with a workspace\n",
+                (unsigned long long) rows, d->voc, (unsigned long long) random_sample_workspace_bytes(d->voc, (int) rows),
+                (unsigned long long) kStaticScratchBytes);
+        return STATUS_INSUFFICIENT_WORKSPACE;
+    }
+    DeviceGuard guard(d->device_id);
+    void *scratch = g_scratch_addr[d->device_id].load(std::memory_order_acquire);
+    if (scratch == nullptr) {
+        // The array's name is only a host-side handle; the kernel needs the
+        // address the array has on THIS device, asked for once per device with
+        // that device current (the guard above made it so).
+        cudaError_t e = cudaGetSymbolAddress(&scratch, g_sample_scratch);
+        if (e != cudaSuccess || scratch == nullptr) {
+            fprintf(stderr, "infiniop[b200]: cudaGetSymbolAddress(g_sample_scratch) failed: %s\n", cudaGetErrorString(e));
+            cudaGetLastError();
+            return STATUS_EXECUTION_FAILED;
+        }
+        g_scratch_addr[d->device_id].store(scratch, std::memory_order_release);
+    }
+    return random_sample_launch(a, (int) rows, scratch, kStaticScratchBytes, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -40,6 +40,7 @@ struct RandomSampleArgs {
 bool random_sample_pair_supported(int voc);
 infiniopStatus_t random_sample_pair_launch(const RandomSampleArgs &args, int rows, cudaStream_t stream);
 
+bool random_sample_uses_workspace(const RandomSampleArgs &args);
 uint64_t random_sample_work_pitch(int voc);
 uint64_t random_sample_workspace_bytes(int voc, int rows);
 infiniopStatus_t random_sample_launch(const RandomSampleArgs &args, int rows, void *workspace, uint64_t workspace_size,

@@ -14,8 +14,10 @@
 // reduction and the scaling pass, so x is read from HBM exactly once: each
 // thread holds up to 8 x 128-bit vectors, a row is owned either by one warp
 // (shuffle reduction only) or by one CTA (shuffles + one shared-memory step).
-// Rows that are not 16-byte aligned, or longer than 64 Ki elements, take the
-// two-pass scalar kernel.
+// Rows longer than 8 Ki elements are spread over a thread-block cluster of 2, 4
+// or 8 CTAs whose partial sums meet over distributed shared memory (rows of up
+// to 256 Ki elements).  Rows that are not 16-byte aligned, or longer still,
+// take the two-pass scalar kernel.
 //
 // The same kernels serve the fused residual form (infiniopAddRMSNorm, which the
 // reference does not have): x = a + b with the Add operator's arithmetic
@@ -104,20 +106,28 @@ __device__ __forceinline__ float rms_prod(ScaleF2 k, float x, float w) {
     return __fadd_rn(t, c);
 }
 
-// VPT vectors (8 halves each) per thread; CTA_ROW: the whole CTA owns one row,
-// otherwise each warp owns one row.
-template<int VPT, bool W_F16, bool CTA_ROW, bool FUSED>
-__global__ void rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs,
-                                     uint64_t d, int64_t stride_y, int64_t stride_x, float eps, Residual res) {
-    __shared__ float red[32];
-    const int lane = threadIdx.x & 31;
-    const uint32_t group = CTA_ROW ? blockDim.x : 32;
-    const uint32_t t = CTA_ROW ? threadIdx.x : lane;
-    const uint64_t rows_per_cta = CTA_ROW ? 1 : (blockDim.x >> 5);
-    const uint64_t row0 = (uint64_t) blockIdx.x * rows_per_cta + (CTA_ROW ? 0 : (threadIdx.x >> 5));
-    const uint64_t row_step = (uint64_t) gridDim.x * rows_per_cta;
+// Who owns a row: one warp (shuffles only), one CTA (shuffles + one shared-memory step) or one thread-block
+// cluster (the CTAs' partial sums meet over distributed shared memory).
+enum RowOwner { WARP_ROW = 0, CTA_ROW = 1, CLUSTER_ROW = 2 };
 
-    // CTA_ROW: every thread of the CTA sees the same row, so the CTA-wide
+// VPT vectors (8 halves each) per thread.  Launch bounds: the row-per-CTA forms are launched with up to 1024
+// threads, so they must fit 64 registers per thread.
+template<int VPT, bool W_F16, int OWNER, bool FUSED>
+__global__ void __launch_bounds__(OWNER == WARP_ROW ? 256 : 1024)
+    rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs, uint64_t d,
+                         int64_t stride_y, int64_t stride_x, float eps, Residual res) {
+    __shared__ float red[32];
+    __shared__ float part;// this CTA's partial sum, read by the whole cluster
+    const int lane = threadIdx.x & 31;
+    const uint32_t cl = OWNER == CLUSTER_ROW ? cluster_size() : 1;
+    const uint32_t group = OWNER == WARP_ROW ? 32 : blockDim.x * cl;
+    const uint32_t t = OWNER == WARP_ROW ? lane : (OWNER == CLUSTER_ROW ? cluster_rank() * blockDim.x : 0) + threadIdx.x;
+    const uint64_t rows_per_cta = OWNER == WARP_ROW ? (blockDim.x >> 5) : 1;
+    const uint64_t row0 = OWNER == WARP_ROW ? (uint64_t) blockIdx.x * rows_per_cta + (threadIdx.x >> 5)
+                                            : (uint64_t) (blockIdx.x / cl);
+    const uint64_t row_step = OWNER == WARP_ROW ? (uint64_t) gridDim.x * rows_per_cta : (uint64_t) (gridDim.x / cl);
+
+    // CTA / cluster rows: every thread of the CTA (cluster) sees the same row, so the
     // reduction below is reached uniformly; warp rows only use shuffles.
     for (uint64_t row = row0; row < n; row += row_step) {
         const uint16_t *xr = x + (int64_t) row * stride_x;
@@ -159,7 +169,8 @@ __global__ void rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void 
                 }
             }
         }
-        ss = CTA_ROW ? cta_reduce<false>(ss, red) : warp_sum(ss);
+        if (OWNER == CLUSTER_ROW) ss = cluster_reduce<false>(ss, red, &part, cl);
+        else ss = OWNER == CTA_ROW ? cta_reduce<false>(ss, red) : warp_sum(ss);
         const ScaleF2 k = split_scale(rms_scale(ss, d, eps));
         uint16_t *yr = y + (int64_t) row * stride_y;
 #pragma unroll
@@ -190,6 +201,8 @@ __global__ void rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void 
                 st_stream(yr + (uint64_t) j * 8, out);
             }
         }
+        // no CTA may leave (or overwrite `part` for its next row) while a neighbour still reads it
+        if (OWNER == CLUSTER_ROW) cluster_sync_all();
     }
 }
 
@@ -231,32 +244,45 @@ __global__ void rms_norm_generic_kernel(uint16_t *y, const uint16_t *x, const vo
 }
 
 template<int VPT, bool W_F16, bool FUSED>
-void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t vecs, void *y, const void *x,
-                 const void *w, Residual res, cudaStream_t st) {
+void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, void *y,
+                 const void *x, const void *w, Residual res, cudaStream_t st) {
     auto *yp = reinterpret_cast<uint16_t *>(y);
     auto *xp = reinterpret_cast<const uint16_t *>(x);
+    if constexpr (VPT > 4) {
+        if (cta_row) return;// not instantiated: eight vectors per thread exist for warp rows only
+    }
     if (cta_row) {
-        const uint64_t cap = 0x7FFFFFFFull;// one CTA per row; rows beyond 2^31 loop
-        const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap);
-        rms_norm_regs_kernel<VPT, W_F16, true, FUSED>
-            <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+        if constexpr (VPT <= 4) {
+        const uint64_t cap = 0x7FFFFFFFull / cl;// one CTA (cluster) per row; rows beyond that loop
+        const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap) * cl;
+        if (cl > 1) {
+            launch_cluster(rms_norm_regs_kernel<VPT, W_F16, CLUSTER_ROW, FUSED>, grid, threads, cl, st, yp, xp, w, d->n,
+                           vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+        } else {
+            rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED>
+                <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+        }
+        }
     } else {
         const uint64_t ctas = (d->n + 7) / 8;
         const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-        rms_norm_regs_kernel<VPT, W_F16, false, FUSED>
+        rms_norm_regs_kernel<VPT, W_F16, WARP_ROW, FUSED>
             <<<grid, 256, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
     }
 }
 
 template<bool W_F16, bool FUSED>
-void dispatch_regs(const RMSNormDesc *d, int vpt, bool cta_row, uint32_t threads, uint32_t vecs, void *y,
+void dispatch_regs(const RMSNormDesc *d, int vpt, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, void *y,
                    const void *x, const void *w, Residual res, cudaStream_t st) {
     switch (vpt) {
-        case 1: launch_regs<1, W_F16, FUSED>(d, cta_row, threads, vecs, y, x, w, res, st); break;
-        case 2: launch_regs<2, W_F16, FUSED>(d, cta_row, threads, vecs, y, x, w, res, st); break;
-        case 4: launch_regs<4, W_F16, FUSED>(d, cta_row, threads, vecs, y, x, w, res, st); break;
-        default: launch_regs<8, W_F16, FUSED>(d, cta_row, threads, vecs, y, x, w, res, st); break;
+        case 1: launch_regs<1, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
+        case 2: launch_regs<2, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
+        case 4: launch_regs<4, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
+        default:// eight vectors per thread exist for warp rows only (256 threads per CTA)
+            if (cta_row) launch_regs<4, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st);
+            else launch_regs<8, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st);
+            break;
     }
 }
 
@@ -266,12 +292,11 @@ infiniopStatus_t run(const RMSNormDesc *d, void *y, const void *x, const void *w
                      cudaStream_t st) {
     const Residual res{reinterpret_cast<const uint16_t *>(b), reinterpret_cast<uint16_t *>(sum), d->stride_b,
                        d->stride_sum};
-    bool vec_ok = d->d % 8 == 0 && d->d / 8 <= 8192 && d->stride_x % 8 == 0 && d->stride_y % 8 == 0 &&
+    // rows of up to 8 CTAs x 1024 threads x 4 vectors stay in registers; longer ones go the scalar way
+    bool vec_ok = d->d % 8 == 0 && d->d / 8 <= 32768 && d->stride_x % 8 == 0 && d->stride_y % 8 == 0 &&
                   aligned16(y) && aligned16(x) && aligned16(w);
-    // the fused form holds two operands per vector: rows of up to 4096 vectors (4 per thread), longer ones go the scalar way
     if (FUSED) {
-        vec_ok = vec_ok && d->d / 8 <= 4096 && d->stride_b % 8 == 0 && d->stride_sum % 8 == 0 && aligned16(b) &&
-                 aligned16(sum);
+        vec_ok = vec_ok && d->stride_b % 8 == 0 && d->stride_sum % 8 == 0 && aligned16(b) && aligned16(sum);
     }
     if (vec_ok) {
         const uint32_t vecs = (uint32_t) (d->d / 8);
@@ -281,23 +306,21 @@ infiniopStatus_t run(const RMSNormDesc *d, void *y, const void *x, const void *w
         const bool big = d->n * (uint64_t) vecs >= (1u << 20);
         int vpt;
         bool cta_row;
-        uint32_t threads = 256;
+        uint32_t threads = 256, cl = 1;
         if (big && vecs <= (FUSED ? 128u : 256u)) {// the fused form holds two operands: half the vectors per thread
             cta_row = false;
             const uint32_t need = (vecs + 31) / 32;
             vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
         } else {
             cta_row = true;
-            const uint32_t min_vpt = (vecs + 1023) / 1024;
-            // measured on [32768, 4096] / [16384, 8192] / [8192, 16384]: 4 vectors per thread 0.88 / 0.87 / 0.81 of the
-            // copy bandwidth, 8 vectors 0.79 / 0.78 / 0.70, 2 vectors 0.75 / 0.71 / 0.59
-            uint32_t want = big ? (FUSED ? 2 : 4) : min_vpt;
-            if (want < min_vpt) want = min_vpt;
-            vpt = want <= 1 ? 1 : want <= 2 ? 2 : want <= 4 ? 4 : 8;
-            threads = ((vecs + vpt - 1) / vpt + 31) / 32 * 32;
+            // measured on [32768, 4096] / [16384, 8192] / [8192, 16384] with one CTA per row: 4 vectors per thread
+            // 0.88 / 0.87 / 0.81 of the copy bandwidth, 8 vectors 0.79 / 0.78 / 0.70, 2 vectors 0.75 / 0.71 / 0.59.
+            // Rows of more than 1024 vectors are spread over a cluster of 2, 4 or 8 CTAs.
+            const RowLaunch shape = row_launch_shape(vecs, big ? (FUSED ? 2 : 4) : 1);
+            vpt = shape.vpt, threads = shape.threads, cl = shape.cl;
         }
-        if (d->w_f16) dispatch_regs<true, FUSED>(d, vpt, cta_row, threads, vecs, y, x, w, res, st);
-        else dispatch_regs<false, FUSED>(d, vpt, cta_row, threads, vecs, y, x, w, res, st);
+        if (d->w_f16) dispatch_regs<true, FUSED>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
+        else dispatch_regs<false, FUSED>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
         return check_launch("rms_norm");
     }
     const uint64_t cap = (uint64_t) d->sm_count * 8;

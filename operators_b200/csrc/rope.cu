@@ -223,7 +223,7 @@ infiniopStatus_t run(const RoPEDesc *d, void *out, const void *t, void const *po
                     aligned16(cos_table);
     // Contiguous token rows of a size that leaves room for a few stages: the bulk-copy pipeline.
     if (in_place && v8 && d->stride_1 == (int64_t) dim && d->seq_len <= 0xFFFFFFFFull &&
-        getenv("INFINIOP_ROPE_KERNEL") == nullptr) {
+        kernel_choice(kFamilyRoPE) != 1) {
         namespace rp = rope_pipe;
         rp::Plan plan;
         plan.row_bytes = nhead * dim * 2u;

@@ -6,9 +6,26 @@
 // src/tensor/tensor_descriptor.cc:4-26.
 #include "common.cuh"
 
+#include "../../include/infiniop_ext.h"
+
+#include <atomic>
 #include <new>
 
 using namespace b200;
+
+namespace {
+std::atomic<int> g_kernel_choice[kFamilyCount];
+}
+
+int b200::kernel_choice(int family) {
+    return family >= 0 && family < kFamilyCount ? g_kernel_choice[family].load(std::memory_order_relaxed) : 0;
+}
+
+INFINIOP_API infiniopStatus_t infiniopExtSelectKernel(int family, int variant) {
+    if (family < 0 || family >= kFamilyCount || variant < 0) return STATUS_BAD_PARAM;
+    g_kernel_choice[family].store(variant, std::memory_order_relaxed);
+    return STATUS_SUCCESS;
+}
 
 INFINIOP_API infiniopStatus_t infiniopCreateHandle(infiniopHandle_t *handle_ptr, Device device, int device_id) {
     if (handle_ptr == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;

@@ -78,10 +78,23 @@ def _declare(lib):
         if fn is not None:
             fn.argtypes = argtypes
             fn.restype = c_int
+    if hasattr(lib, "infiniopExtSelectKernel"):
+        lib.infiniopExtSelectKernel.argtypes = [c_int, c_int]
+        lib.infiniopExtSelectKernel.restype = c_int
     if hasattr(lib, "infiniopRandomSampleShardRecordBytes"):
         lib.infiniopRandomSampleShardRecordBytes.argtypes = []
         lib.infiniopRandomSampleShardRecordBytes.restype = c_uint64
     lib._b200_declared = True
+
+
+KERNEL_FAMILIES = {"rope": 0, "random_sample": 1, "attention": 2, "matmul": 3}
+
+
+def select_kernel(lib, family, variant):
+    """Forces one kernel family of an operator (tests and benchmarks): see
+    infiniopExtSelectKernel in include/infiniop_ext.h.  variant 0 = the library's own choice."""
+    _declare(lib)
+    check_error(lib.infiniopExtSelectKernel(KERNEL_FAMILIES[family], int(variant)))
 
 
 def _stream_ptr(stream):

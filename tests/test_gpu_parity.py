@@ -38,7 +38,12 @@ def _few(mismatches, total, rate):
 @pytest.mark.parametrize("w_dtype", [torch.float16, torch.float32])
 @pytest.mark.parametrize("shape,stride", [((16, 2048), None), ((16, 2048), 4096), ((5, 33), None), ((1, 8), None),
                                           ((700, 4096), None), ((2048, 2048), None), ((3, 16384), None),
-                                          ((2, 70000), None), ((9, 264), 272)])
+                                          ((2, 70000), None), ((9, 264), 272),
+                                          # rows spread over a cluster of 2 / 4 / 8 CTAs (few rows: one vector per
+                                          # thread; many rows: four), the longest register-resident row, one past it
+                                          ((2, 49152), None), ((2, 65536), None), ((600, 16384), None),
+                                          ((300, 32768), 32776), ((3, 200000), None), ((2, 262144), None),
+                                          ((2, 262152), None), ((1, 8200), None)])
 def test_rms_norm(oracle, cuda_lib, shape, stride, w_dtype):
     lib, handle = cuda_lib
     g = torch.Generator().manual_seed(1)
@@ -297,7 +302,12 @@ def test_add_unaligned_views(oracle, cuda_lib):
 @pytest.mark.parametrize("shape,strides", [((32, 20, 512), None), ((32, 20, 512), (20480, 1024, 1)), ((5, 64), None),
                                            ((2, 7, 7), None), ((3, 1, 9), None), ((2, 128, 4096), None),
                                            ((4, 33, 1000), None), ((1, 3, 20000), None), ((2, 2, 70000), None),
-                                           ((8, 64, 16384), None), ((600, 1, 16384), None)])
+                                           ((8, 64, 16384), None), ((600, 1, 16384), None),
+                                           # rows spread over a cluster of 2 / 4 / 8 CTAs, up to the longest
+                                           # register-resident row and one vector past it
+                                           ((1, 2, 40960), None), ((1, 3, 65536), None), ((8, 128, 16384), None),
+                                           ((4, 40, 32768), (40 * 32776, 32776, 1)), ((1, 2, 262144), None),
+                                           ((1, 2, 262152), None), ((2, 5, 8200), None)])
 def test_causal_softmax(oracle, cuda_lib, shape, strides):
     lib, handle = cuda_lib
     g = torch.Generator().manual_seed(5)
@@ -336,14 +346,12 @@ def test_random_sample_single_row_abi(oracle, cuda_lib, voc, u, topp, topk, temp
 
 
 @pytest.fixture(params=["shared", "global"])
-def sampler_kernel(request, monkeypatch):
+def sampler_kernel(request, cuda_lib):
     """Both sampling kernels: the shared-memory resident pair kernel (default for
     voc <= 262144; clusters of two or four CTAs) and the global-memory kernel (any voc)."""
-    if request.param == "global":
-        monkeypatch.setenv("INFINIOP_RANDOM_SAMPLE_KERNEL", "global")
-    else:
-        monkeypatch.delenv("INFINIOP_RANDOM_SAMPLE_KERNEL", raising=False)
-    return request.param
+    ops.select_kernel(cuda_lib[0], "random_sample", 1 if request.param == "global" else 0)
+    yield request.param
+    ops.select_kernel(cuda_lib[0], "random_sample", 0)
 
 
 @pytest.mark.parametrize("voc,rows,topp,topk,temp,dist", [
@@ -450,6 +458,102 @@ def test_random_sample_argmax_batch(oracle, cuda_lib, voc, rows, pitch, dist):
     assert int(one[0]) == want[rows - 1]
 
 
+# ---- the five configurations the benchmark quotes, at full size -----------------------------------------
+def _rows_in_parallel(fn, n, parts=None):
+    """Runs fn(lo, hi) on row slices from a thread pool (the oracle's C functions release the GIL and
+    rows are independent), so the full-size oracle passes take a second or two."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+
+    parts = parts or min(n, os.cpu_count() or 1)
+    cuts = [n * i // parts for i in range(parts + 1)]
+    with ThreadPoolExecutor(parts) as pool:
+        list(pool.map(lambda i: fn(cuts[i], cuts[i + 1]), range(parts)))
+
+
+def test_config_rope_4096x32x128(oracle, cuda_lib):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(2)
+    t = torch.randn((4096, 32, 128), generator=g).half()
+    pos = torch.arange(4096, dtype=torch.int64)
+    sin, cos = ops.sin_cos_table(4096, 128, theta=1e4)
+    want = t.numpy().copy()
+    pn, sn, cn = pos.numpy().astype(np.uint64), sin.numpy(), cos.numpy()
+    _rows_in_parallel(lambda lo, hi: oracle.rope(want[lo:hi], pn[lo:hi], sn, cn), 4096)
+    td = t.to(DEV)
+    ops.rope(lib, handle, td, pos.to(DEV), sin.to(DEV), cos.to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(td).reshape(t.shape), want.view(np.uint16))
+
+
+def test_config_swiglu_8192x28672_halves(oracle, cuda_lib):
+    lib, handle = cuda_lib
+    tokens, di = 8192, 14336
+    g = torch.Generator().manual_seed(3)
+    gate_up = torch.randn((tokens, 2 * di), generator=g).half()
+    gn = gate_up.numpy()
+    want = np.zeros((tokens, di), np.float16)
+    _rows_in_parallel(lambda lo, hi: oracle.swiglu(gn[lo:hi, di:], gn[lo:hi, :di], c=want[lo:hi]), tokens)
+    gd = gate_up.to(DEV)
+    cd = torch.zeros((tokens, di), dtype=torch.float16, device=DEV)
+    ops.swiglu(lib, handle, cd, gd[:, di:], gd[:, :di])
+    torch.cuda.synchronize()
+    mism = _close(_bits(cd).reshape(tokens, di), want, 1e-3, 1e-3)
+    assert _few(mism, tokens * di, 2e-3)
+    assert torch.equal(gd.cpu(), gate_up)  # the operands are untouched
+
+
+def test_config_add_8192x4096(oracle, cuda_lib):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(4)
+    a, b = torch.randn((8192, 4096), generator=g).half(), torch.randn((8192, 4096), generator=g).half()
+    an, bn = a.numpy(), b.numpy()
+    want = np.zeros((8192, 4096), np.float16)
+
+    def part(lo, hi):
+        want[lo:hi] = oracle.add(an[lo:hi], bn[lo:hi])
+
+    _rows_in_parallel(part, 8192)
+    cd = torch.zeros((8192, 4096), dtype=torch.float16, device=DEV)
+    ops.add(lib, handle, cd, a.to(DEV), b.to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(_bits(cd).reshape(8192, 4096), want.view(np.uint16))
+
+
+def test_config_causal_softmax_32x512x4096(oracle, cuda_lib):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(5)
+    y = (torch.randn((32, 512, 4096), generator=g) * 2).half()
+    want = y.numpy().copy()
+    _rows_in_parallel(lambda lo, hi: oracle.causal_softmax(want[lo:hi]), 32)
+    yd = y.to(DEV)
+    ops.causal_softmax(lib, handle, yd)
+    torch.cuda.synchronize()
+    got = _bits(yd).reshape(y.shape)
+    _close(got, want, 2e-3, 2e-3)
+    # row i of every head sees 3585 + i columns; everything behind is an exact zero
+    col = np.arange(4096)[None, None, :]
+    masked = col > (np.arange(512)[None, :, None] + 4096 - 512)
+    assert (got[np.broadcast_to(masked, got.shape)] == 0).all()
+    assert (want.view(np.uint16)[np.broadcast_to(masked, got.shape)] == 0).all()
+
+
+def test_config_rms_norm_scaled_65536x2048(oracle, cuda_lib):
+    """The benchmark's scaled RMSNorm line (the 16 x 2048 configuration itself is in test_rms_norm)."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(1)
+    x = (torch.rand((65536, 2048), generator=g) * 2 - 1).half()
+    w = (torch.rand(2048, generator=g) * 2 - 1).half()
+    xn, wn = x.numpy(), w.numpy()
+    want = np.zeros((65536, 2048), np.float16)
+    _rows_in_parallel(lambda lo, hi: oracle.rms_norm(xn[lo:hi], wn, 1e-5, y=want[lo:hi]), 65536)
+    yd = torch.zeros((65536, 2048), dtype=torch.float16, device=DEV)
+    ops.rms_norm(lib, handle, yd, x.to(DEV), w.to(DEV), 1e-5)
+    torch.cuda.synchronize()
+    mism = _close(_bits(yd).reshape(65536, 2048), want, 1e-3, 1e-3)
+    assert _few(mism, x.numel(), 0.02)
+
+
 # ---- attention over a KV cache (the reference's composite) ---------------------------------------------
 ATTENTION_CASES = [
     # the reference's own three cases (operatorspy/tests/attention.py:310-357): prefill, decode, small
@@ -479,17 +583,21 @@ ATTENTION_CASES = [
 ]
 
 
-@pytest.mark.parametrize("kernels", ["tensor", "multiply_add"])
+@pytest.fixture(params=["tensor", "multiply_add"])
+def attention_kernels(request, cuda_lib):
+    """Both kernel families: the tensor-core kernels and the multiply-add kernels that otherwise
+    serve unaligned layouts and head sizes above 128."""
+    ops.select_kernel(cuda_lib[0], "attention", 1 if request.param == "multiply_add" else 0)
+    yield request.param
+    ops.select_kernel(cuda_lib[0], "attention", 0)
+
+
 @pytest.mark.parametrize("nh,nkvh,seq,dh,pos,buf_len,qkv_strides,cache_strides", ATTENTION_CASES)
-def test_attention(oracle, cuda_lib, monkeypatch, kernels, nh, nkvh, seq, dh, pos, buf_len, qkv_strides, cache_strides):
+def test_attention(oracle, cuda_lib, attention_kernels, nh, nkvh, seq, dh, pos, buf_len, qkv_strides, cache_strides):
     """out within the fp16 tolerance of the oracle's composite (only the grouping of fp32 sums
     differs, so most elements are the same bit pattern); both caches byte for byte,
     rows outside pos .. pos+seq untouched."""
     lib, handle = cuda_lib
-    if kernels == "multiply_add":  # the kernels that otherwise serve unaligned layouts and dh > 128
-        monkeypatch.setenv("INFINIOP_ATTENTION_KERNEL", "fma")
-    else:
-        monkeypatch.delenv("INFINIOP_ATTENTION_KERNEL", raising=False)
     g = torch.Generator().manual_seed(21)
     q = torch.randn((nh, seq, dh), generator=g).half()
     k = torch.randn((nkvh, seq, dh), generator=g).half()

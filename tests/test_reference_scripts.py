@@ -1,0 +1,39 @@
+"""The reference's own acceptance scripts, unmodified, against this library.
+
+The reference ships one script per operator (reference operatorspy/tests/<op>.py)
+that loads `$INFINI_ROOT/lib/libinfiniop.so` through its ctypes wrapper
+(reference operatorspy/liboperators.py:40-73), runs the operator on `--cuda`
+and compares with a torch computation.  `make -C oracle ref` copies that
+package, as it is, next to the reference CPU build (a git-ignored folder);
+here every script of an operator this library serves is run as a child process
+with INFINI_ROOT pointing at this repository's build.  A script counts as
+passed when it exits 0 and printed "Test passed" once per case at least.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SCRIPTS = os.path.join(ROOT, "oracle", "_ref", "operatorspy", "tests")
+INSTALL = os.path.join(ROOT, "operators_b200")  # holds lib/libinfiniop.so
+
+OPERATORS = ["rms_norm", "rotary_embedding", "swiglu", "add", "causal_softmax", "random_sample", "rearrange",
+             "attention", "matmul", "mlp"]
+
+
+@pytest.mark.parametrize("name", OPERATORS)
+def test_reference_script_passes_on_cuda(name):
+    script = os.path.join(SCRIPTS, name + ".py")
+    if not os.path.isfile(script):
+        pytest.skip("reference scripts not copied (run `make -C oracle ref` where the reference checkout is)")
+    assert os.path.isfile(os.path.join(INSTALL, "lib", "libinfiniop.so")), "build the library first"
+    env = dict(os.environ, INFINI_ROOT=INSTALL)
+    r = subprocess.run([sys.executable, script, "--cuda"], env=env, capture_output=True, text=True, timeout=900)
+    tail = (r.stdout + r.stderr)[-3000:]
+    assert r.returncode == 0, tail
+    assert "Test passed" in r.stdout, tail
+    assert "Traceback" not in r.stderr, tail
