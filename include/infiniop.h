@@ -272,6 +272,45 @@ INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t de
                                                 void const *v, void *k_cache, void *v_cache, void *stream);
 INFINIOP_API infiniopStatus_t infiniopDestroyAttentionDescriptor(infiniopAttentionDescriptor_t desc);
 
+/* ---- matmul: include/ops/matmul/matmul.h:7-32 ------------------------------ *
+ * c = alpha * a b + beta * c on 2-D [m,k] x [k,n] or batched 3-D matrices,
+ * fp16 or fp32, each matrix with one unit stride (src/ops/matmul/blas.h:9-113);
+ * a and b may have batch 1 against a batched c.  fp32 accumulation. */
+typedef struct MatmulDescriptor {
+    Device device;
+} MatmulDescriptor;
+typedef MatmulDescriptor *infiniopMatmulDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateMatmulDescriptor(infiniopHandle_t handle,
+                                                             infiniopMatmulDescriptor_t *desc_ptr,
+                                                             infiniopTensorDescriptor_t c_desc, float alpha,
+                                                             infiniopTensorDescriptor_t a_desc,
+                                                             infiniopTensorDescriptor_t b_desc, float beta);
+INFINIOP_API infiniopStatus_t infiniopGetMatmulWorkspaceSize(infiniopMatmulDescriptor_t desc, uint64_t *size);
+INFINIOP_API infiniopStatus_t infiniopMatmul(infiniopMatmulDescriptor_t desc, void *workspace, uint64_t workspace_size,
+                                             void *c, void const *a, void const *b, void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyMatmulDescriptor(infiniopMatmulDescriptor_t desc);
+
+/* ---- MLP: include/ops/mlp/mlp.h:9-38 ----------------------------------------- *
+ * y = (residual ? y : 0) + alpha * SwiGLU(x w12) w3 with x, y [tokens, hidden],
+ * w12 [hidden, 2 * intermediate] holding the gate columns first and the up
+ * columns second, w3 [intermediate, hidden] (src/ops/mlp/operator.cc:22-122).
+ * fp16; x and y need a unit last stride.  The workspace must hold the reported
+ * size, else STATUS_MEMORY_NOT_ALLOCATED. */
+typedef struct MLPDescriptor {
+    Device device;
+} MLPDescriptor;
+typedef MLPDescriptor *infiniopMLPDescriptor_t;
+INFINIOP_API infiniopStatus_t infiniopCreateMLPDescriptor(infiniopHandle_t handle, infiniopMLPDescriptor_t *desc_ptr,
+                                                          infiniopTensorDescriptor_t y_desc,
+                                                          infiniopTensorDescriptor_t x_desc,
+                                                          infiniopTensorDescriptor_t w12_desc,
+                                                          infiniopTensorDescriptor_t w3_desc, float alpha,
+                                                          char residual);
+INFINIOP_API infiniopStatus_t infiniopGetMLPWorkspaceSize(infiniopMLPDescriptor_t desc, uint64_t *size);
+INFINIOP_API infiniopStatus_t infiniopMLP(infiniopMLPDescriptor_t desc, void *workspace, uint64_t workspace_size,
+                                          void *y, void const *x, void const *w12, void const *w3, void *stream);
+INFINIOP_API infiniopStatus_t infiniopDestroyMLPDescriptor(infiniopMLPDescriptor_t desc);
+
 /* ---- causal softmax: include/ops/causal_softmax/causal_softmax.h:7-25 ----- *
  * In place on fp16 [.., seq_len, total_seq_len] (2-D or 3-D, unit last
  * stride): row i keeps columns j <= total_seq_len - seq_len + i, the rest

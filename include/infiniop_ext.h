@@ -23,6 +23,21 @@
 INFINIOP_API infiniopStatus_t infiniopExtSelectKernel(int family, int variant);
 
 /*
+ * Bounded waits (no counterpart in the reference).  The kernels that wait on
+ * hardware barriers for asynchronous copies (the RoPE bulk-copy pipeline, the
+ * tensor-core matmul) give every wait a limit; a wait that runs out makes its
+ * thread group stop, let its copies in flight land, and leave.  The call has
+ * then already returned STATUS_SUCCESS, and its output is incomplete.
+ * infiniopExtDeviceTimeouts reports how many groups gave up on this handle's
+ * device since the library was loaded (it synchronises the device): 0 means
+ * every result so far is complete.  infiniopExtSetWaitLimit sets the number of
+ * polls a RoPE pipeline wait may take (0 restores the default of 2^22); it
+ * exists so that a test can make the limit run out.
+ */
+INFINIOP_API infiniopStatus_t infiniopExtDeviceTimeouts(infiniopHandle_t handle, uint64_t *count);
+INFINIOP_API infiniopStatus_t infiniopExtSetWaitLimit(infiniopHandle_t handle, uint32_t polls);
+
+/*
  * Batched random sample: `rows` independent rows of fp16 logits
  * [rows, voc] (voc taken from the descriptor, `row_stride` elements between
  * rows) sampled in ONE launch, row r with the uniform draw random_vals[r]

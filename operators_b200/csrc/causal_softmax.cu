@@ -46,12 +46,12 @@ __device__ __forceinline__ uint64_t visible_cols(uint64_t i, uint64_t seq_len, u
 // evaluation instead; measured, that is the faster of the two on B200.)
 //
 // Who owns a row: one warp, one CTA, or one thread-block cluster of 2, 4 or 8 CTAs whose maxima and sums meet
-// over distributed shared memory (rows of more than 8 Ki columns).  The row-per-CTA forms are launched with up
-// to 1024 threads, hence their launch bound (64 registers per thread).
+// over distributed shared memory (rows of more than 32 Ki columns).  MAXT is the launch bound: the forms that
+// are launched with more than 512 threads must fit 64 registers per thread.
 enum RowOwner { WARP_ROW = 0, CTA_ROW = 1, CLUSTER_ROW = 2 };
 
-template<int VPT, int OWNER>
-__global__ void __launch_bounds__(OWNER == WARP_ROW ? 256 : 1024)
+template<int VPT, int OWNER, int MAXT>
+__global__ void __launch_bounds__(MAXT)
     causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total, uint32_t vecs,
                                int64_t stride_b, int64_t stride_i, FastDiv seq_div) {
     __shared__ float red_m[32], red_s[32];// one slot array per reduction of a row: one barrier each
@@ -178,22 +178,27 @@ void launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uin
     const uint64_t rows = d->batch * d->seq_len;
     const FastDiv seq_div(d->seq_len <= 0xFFFFFFFFull && d->seq_len > 0 ? (uint32_t) d->seq_len : 1u);
     if (cta_row) {
-        if constexpr (VPT <= 4) {// eight vectors per thread exist for warp rows only
-            const uint64_t cap = 0x7FFFFFFFull / cl;// one CTA (cluster) per row; rows beyond that loop
-            const uint32_t grid = (uint32_t) (rows < cap ? rows : cap) * cl;
-            if (cl > 1) {
-                launch_cluster(causal_softmax_regs_kernel<VPT, CLUSTER_ROW>, grid, threads, cl, st, y, rows, d->seq_len,
-                               d->total, vecs, d->stride_b, d->stride_i, seq_div);
-            } else {
-                causal_softmax_regs_kernel<VPT, CTA_ROW>
+        const uint64_t cap = 0x7FFFFFFFull / cl;// one CTA (cluster) per row; rows beyond that loop
+        const uint32_t grid = (uint32_t) (rows < cap ? rows : cap) * cl;
+        if (cl > 1) {
+            if constexpr (VPT == 4) {// clusters always hold four vectors per thread
+                launch_cluster(causal_softmax_regs_kernel<4, CLUSTER_ROW, 1024>, grid, threads, cl, st, y, rows,
+                               d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
+            }
+        } else if (threads > 512) {
+            if constexpr (VPT <= 4) {// eight vectors per thread never need more than 512 threads
+                causal_softmax_regs_kernel<VPT, CTA_ROW, 1024>
                     <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
             }
+        } else {
+            causal_softmax_regs_kernel<VPT, CTA_ROW, 512>
+                <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
         }
     } else {
         const uint64_t ctas = (rows + 7) / 8;
         const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-        causal_softmax_regs_kernel<VPT, WARP_ROW>
+        causal_softmax_regs_kernel<VPT, WARP_ROW, 256>
             <<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
     }
 }
@@ -262,9 +267,11 @@ INFINIOP_API infiniopStatus_t infiniopCausalSoftmax(infiniopCausalSoftmaxDescrip
         } else {
             cta_row = true;
             // measured at [32,512,4096]: 4 vectors per thread (128 threads per 4096-column
-            // row) 50 us, 8 per thread 52 us, 2 per thread 63 us.  Rows of more than 1024 vectors
-            // are spread over a cluster of 2, 4 or 8 CTAs.
-            const RowLaunch shape = row_launch_shape(vecs, big ? 4 : 1);
+            // row) 50 us, 8 per thread 52 us, 2 per thread 63 us
+            // rows of 16384 columns and more: 8 per thread (0.73 against 0.67 of the copy bandwidth at
+            // [16, 512, 16384], 0.55 against 0.50 at [8, 512, 32768]; no difference at 8192 columns).
+            // Rows of more than 4096 vectors are spread over a cluster of 2, 4 or 8 CTAs.
+            const RowLaunch shape = row_launch_shape(vecs, big ? (vecs >= 2048 ? 8 : 4) : 1);
             vpt = shape.vpt, threads = shape.threads, cl = shape.cl;
         }
         switch (vpt) {

@@ -14,7 +14,7 @@
 // reduction and the scaling pass, so x is read from HBM exactly once: each
 // thread holds up to 8 x 128-bit vectors, a row is owned either by one warp
 // (shuffle reduction only) or by one CTA (shuffles + one shared-memory step).
-// Rows longer than 8 Ki elements are spread over a thread-block cluster of 2, 4
+// Rows longer than 32 Ki elements are spread over a thread-block cluster of 2, 4
 // or 8 CTAs whose partial sums meet over distributed shared memory (rows of up
 // to 256 Ki elements).  Rows that are not 16-byte aligned, or longer still,
 // take the two-pass scalar kernel.
@@ -110,10 +110,10 @@ __device__ __forceinline__ float rms_prod(ScaleF2 k, float x, float w) {
 // cluster (the CTAs' partial sums meet over distributed shared memory).
 enum RowOwner { WARP_ROW = 0, CTA_ROW = 1, CLUSTER_ROW = 2 };
 
-// VPT vectors (8 halves each) per thread.  Launch bounds: the row-per-CTA forms are launched with up to 1024
-// threads, so they must fit 64 registers per thread.
-template<int VPT, bool W_F16, int OWNER, bool FUSED>
-__global__ void __launch_bounds__(OWNER == WARP_ROW ? 256 : 1024)
+// VPT vectors (8 halves each) per thread.  MAXT is the launch bound: the row-per-CTA forms that are launched
+// with more than 512 threads must fit 64 registers per thread.
+template<int VPT, bool W_F16, int OWNER, bool FUSED, int MAXT>
+__global__ void __launch_bounds__(MAXT)
     rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs, uint64_t d,
                          int64_t stride_y, int64_t stride_x, float eps, Residual res) {
     __shared__ float red[32];
@@ -248,26 +248,28 @@ void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t 
                  const void *x, const void *w, Residual res, cudaStream_t st) {
     auto *yp = reinterpret_cast<uint16_t *>(y);
     auto *xp = reinterpret_cast<const uint16_t *>(x);
-    if constexpr (VPT > 4) {
-        if (cta_row) return;// not instantiated: eight vectors per thread exist for warp rows only
-    }
     if (cta_row) {
-        if constexpr (VPT <= 4) {
         const uint64_t cap = 0x7FFFFFFFull / cl;// one CTA (cluster) per row; rows beyond that loop
         const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap) * cl;
         if (cl > 1) {
-            launch_cluster(rms_norm_regs_kernel<VPT, W_F16, CLUSTER_ROW, FUSED>, grid, threads, cl, st, yp, xp, w, d->n,
-                           vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+            if constexpr (VPT == 4) {// clusters always hold four vectors per thread
+                launch_cluster(rms_norm_regs_kernel<4, W_F16, CLUSTER_ROW, FUSED, 1024>, grid, threads, cl, st, yp, xp, w,
+                               d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+            }
+        } else if (threads > 512) {
+            if constexpr (VPT <= 4) {// eight vectors per thread never need more than 512 threads
+                rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED, 1024>
+                    <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+            }
         } else {
-            rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED>
+            rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED, 512>
                 <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
-        }
         }
     } else {
         const uint64_t ctas = (d->n + 7) / 8;
         const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-        rms_norm_regs_kernel<VPT, W_F16, WARP_ROW, FUSED>
+        rms_norm_regs_kernel<VPT, W_F16, WARP_ROW, FUSED, 256>
             <<<grid, 256, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
     }
 }
@@ -279,10 +281,7 @@ void dispatch_regs(const RMSNormDesc *d, int vpt, bool cta_row, uint32_t threads
         case 1: launch_regs<1, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
         case 2: launch_regs<2, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
         case 4: launch_regs<4, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
-        default:// eight vectors per thread exist for warp rows only (256 threads per CTA)
-            if (cta_row) launch_regs<4, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st);
-            else launch_regs<8, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st);
-            break;
+        default: launch_regs<8, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
     }
 }
 
@@ -315,7 +314,7 @@ infiniopStatus_t run(const RMSNormDesc *d, void *y, const void *x, const void *w
             cta_row = true;
             // measured on [32768, 4096] / [16384, 8192] / [8192, 16384] with one CTA per row: 4 vectors per thread
             // 0.88 / 0.87 / 0.81 of the copy bandwidth, 8 vectors 0.79 / 0.78 / 0.70, 2 vectors 0.75 / 0.71 / 0.59.
-            // Rows of more than 1024 vectors are spread over a cluster of 2, 4 or 8 CTAs.
+            // Rows of more than 4096 vectors are spread over a cluster of 2, 4 or 8 CTAs.
             const RowLaunch shape = row_launch_shape(vecs, big ? (FUSED ? 2 : 4) : 1);
             vpt = shape.vpt, threads = shape.threads, cl = shape.cl;
         }

@@ -160,6 +160,27 @@ __global__ void __launch_bounds__(256, 4) rope_kernel(uint16_t *dst, const uint1
 
 }// namespace
 
+namespace b200 {
+// Groups of the bulk-copy pipeline that gave up on a wait since the library was loaded (synchronises the device).
+unsigned long long rope_pipeline_timeouts_read() {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, rope_pipe::g_rope_pipeline_timeouts, sizeof(v)) != cudaSuccess) {
+        cudaGetLastError();
+        return ~0ull;
+    }
+    return v;
+}
+// Tries per mbarrier wait of the pipeline; 0 restores the default.
+bool rope_pipeline_set_wait_polls(unsigned int polls) {
+    if (polls == 0) polls = rope_pipe::kWaitPolls;
+    if (cudaMemcpyToSymbol(rope_pipe::g_rope_wait_polls, &polls, sizeof(polls)) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return true;
+}
+}// namespace b200
+
 INFINIOP_API infiniopStatus_t infiniopCreateRoPEDescriptor(infiniopHandle_t handle, infiniopRoPEDescriptor_t *desc_ptr,
                                                            infiniopTensorDescriptor_t t,
                                                            infiniopTensorDescriptor_t pos_ids,

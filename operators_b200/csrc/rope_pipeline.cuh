@@ -17,8 +17,11 @@
 // and one thread of the group issues all of its copies).
 //
 // Every wait on an mbarrier is bounded: when a copy does not arrive within the
-// limit the group records it in g_rope_pipeline_timeouts, drains its stores and
-// leaves; nothing spins forever.
+// limit (g_rope_wait_polls tries) the group stops rotating, waits for the copies
+// it still has in flight (with the full default limit), drains its stores,
+// counts itself in g_rope_pipeline_timeouts and leaves; nothing spins forever.
+// A non-zero counter means rows were left un-rotated although the call returned
+// STATUS_SUCCESS; the host reads it through infiniopExtDeviceTimeouts.
 #pragma once
 
 #include "common.cuh"
@@ -41,6 +44,7 @@ constexpr int kMaxTokensPerGroup = 32;    // a lane of the group's first warp ke
 constexpr uint32_t kWaitPolls = 1u << 22; // try_wait calls before a stage is given up
 
 __device__ unsigned int g_rope_pipeline_timeouts = 0;
+__device__ unsigned int g_rope_wait_polls = kWaitPolls;// settable from the host (infiniopExtSetWaitLimit)
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t) __cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
@@ -57,9 +61,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
                  : "memory");
     return ok != 0;
 }
-// false when the limit ran out
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitPolls; ++i) {
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// false when the limit ran out.  try_wait may itself suspend the thread for a while before it answers, so a limit
+// of a few polls (a test that wants the wait to run out) is taken with the non-blocking test_wait instead.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t polls = kWaitPolls) {
+    if (polls <= 64) {
+        for (uint32_t i = 0; i < polls; ++i) {
+            if (mbar_test_wait(bar, parity)) return true;
+        }
+        return false;
+    }
+    for (uint32_t i = 0; i < polls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 64) __nanosleep(64);
     }
@@ -149,10 +171,12 @@ rope_pipeline_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_tabl
     }
 
     const uint32_t slice = lane % plan.slices;// this lane's 8 positions of the head dimension
+    const uint32_t polls = *reinterpret_cast<volatile unsigned int *>(&g_rope_wait_polls);
     bool failed = false;
+    uint32_t j_fail = 0;
     for (uint32_t j = 0; j < cnt; ++j) {
         const uint32_t s = j % kStagesPerGroup, parity = (j / kStagesPerGroup) & 1u;
-        const bool arrived = mbar_wait_bounded(&bar[s], parity);
+        const bool arrived = mbar_wait_bounded(&bar[s], parity, polls);
         if (!__all_sync(0xffffffffu, arrived)) s_fail[group] = 1;// seen by the whole group after its barrier
         unsigned char *st = stage_ptr(s);
         if (arrived) {
@@ -180,6 +204,7 @@ rope_pipeline_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_tabl
         group_barrier(group);
         if (s_fail[group]) {// the same decision in every thread of the group
             failed = true;
+            j_fail = j;
             break;
         }
         // The stage used by token j - 1 is free once its store has read it; it takes token j - 1 + kStagesPerGroup.
@@ -199,8 +224,17 @@ rope_pipeline_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_tabl
         }
     }
     if (issuer) {
+        if (failed) {
+            // the loads of tokens j_fail .. are still in flight towards this CTA's shared memory: let them land
+            // before the CTA gives the memory back (token i + kStagesPerGroup - 1 is requested at the end of pass i)
+            uint32_t issued = j_fail == 0 ? first : j_fail + kStagesPerGroup - 1;
+            if (issued > cnt) issued = cnt;
+            for (uint32_t jj = j_fail; jj < issued; ++jj) {
+                mbar_wait_bounded(&bar[jj % kStagesPerGroup], (jj / kStagesPerGroup) & 1u);
+            }
+            atomicAdd(&g_rope_pipeline_timeouts, 1u);
+        }
         bulk_wait_all();
-        if (failed) atomicAdd(&g_rope_pipeline_timeouts, 1u);
     }
 }
 

@@ -27,6 +27,28 @@ INFINIOP_API infiniopStatus_t infiniopExtSelectKernel(int family, int variant) {
     return STATUS_SUCCESS;
 }
 
+namespace b200 {
+unsigned long long rope_pipeline_timeouts_read();
+bool rope_pipeline_set_wait_polls(unsigned int polls);
+unsigned long long tc_gemm_timeouts_read();
+}// namespace b200
+
+INFINIOP_API infiniopStatus_t infiniopExtDeviceTimeouts(infiniopHandle_t handle, uint64_t *count) {
+    if (handle == nullptr || handle->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    if (count == nullptr) return STATUS_BAD_PARAM;
+    DeviceGuard guard(reinterpret_cast<Handle *>(handle)->device_id);
+    const unsigned long long a = rope_pipeline_timeouts_read(), b = tc_gemm_timeouts_read();
+    if (a == ~0ull || b == ~0ull) return STATUS_EXECUTION_FAILED;
+    *count = a + b;
+    return STATUS_SUCCESS;
+}
+
+INFINIOP_API infiniopStatus_t infiniopExtSetWaitLimit(infiniopHandle_t handle, uint32_t polls) {
+    if (handle == nullptr || handle->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    DeviceGuard guard(reinterpret_cast<Handle *>(handle)->device_id);
+    return rope_pipeline_set_wait_polls(polls) ? STATUS_SUCCESS : STATUS_EXECUTION_FAILED;
+}
+
 INFINIOP_API infiniopStatus_t infiniopCreateHandle(infiniopHandle_t *handle_ptr, Device device, int device_id) {
     if (handle_ptr == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
     if (device_id < 0) return STATUS_BAD_PARAM;

@@ -1,0 +1,552 @@
+// Tensor-core GEMM building blocks for sm_100a: TMA tile loads into 128-byte-swizzled shared memory,
+// tcgen05.mma with the accumulator in tensor memory (TMEM), tcgen05.ld for the epilogue.
+//
+// The kernel computes D[Mp, Np] = sum_k P[Mp, k] * Q[Np, k] for fp16 operands with fp32 accumulation.
+// P is the operand on the MMA's A side (its rows become TMEM lanes, 128 per tile), Q the one on the B side
+// (its rows become TMEM columns, 16 .. 256 per tile).  Each operand may be K-major (k contiguous in memory) or
+// MN-major (its row index contiguous); the host decides which of the caller's matrices plays P and which Q, so
+// a product with few rows (decoding: a handful of tokens against a weight matrix) runs transposed with the
+// weight matrix's output dimension on the 128 lanes and the tokens on 16 columns.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0      one lane issues the TMA loads of a ring of kStages shared-memory stages (mbarrier full/empty)
+//   warp 1      allocates TMEM; one lane issues tcgen05.mma per stage and commits stage and accumulator barriers
+//   warps 2-5   epilogue: each reads its 32 TMEM lanes (tcgen05.ld), applies alpha / beta (or SwiGLU on the
+//               gate and up halves) with the reference's truncating fp32 -> fp16 rule, and stores
+// Two TMEM accumulator buffers let the epilogue of one tile overlap the main loop of the next.
+//
+// Work is a list of (tile, k-block range) items.  When the tiles alone cannot fill the GPU (decoding shapes),
+// the k-blocks of all tiles are split evenly over the CTAs ("stream-K"): a CTA that owns only part of a tile's
+// k range writes its fp32 partial tile to the workspace and counts itself on the tile; the CTA that arrives
+// last adds the partials in CTA order (deterministic) and runs the epilogue.  Nobody waits for anybody.
+//
+// Every mbarrier wait is bounded (clock64 budget).  A role that runs out of time raises the CTA's abort flag
+// and the device-wide counter g_tc_gemm_timeouts; all roles then leave their loops, the CTA waits (bounded)
+// for its TMA copies in flight, frees its TMEM and returns.
+#pragma once
+
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace b200 {
+namespace tc {
+
+constexpr int kThreads = 192;
+constexpr int kBM = 128;        // rows of P per tile = TMEM lanes
+constexpr int kBK = 64;         // k per stage: 64 fp16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;      // k per tcgen05.mma (kind::f16)
+constexpr uint32_t kPBytes = kBM * kBK * 2;// 16 KiB per stage for P
+constexpr long long kWaitBudget = 400ll * 1000 * 1000;// clock64 ticks (~0.2 s) before a wait gives up
+
+// kEpiSwiGLUCols: Q tiles hold [gate columns | matching up columns]; kEpiSwiGLULanes (transposed products): P
+// tiles hold 64 gate rows on lanes 0-63 and the matching 64 up rows on lanes 64-127.
+enum EpilogueMode { kEpiPlain = 0, kEpiSwiGLUCols = 1, kEpiSwiGLULanes = 2 };
+
+struct GemmParams {
+    uint32_t mp, np, k;       // problem in MMA orientation
+    uint32_t batch;
+    uint32_t tiles_m, tiles_n;// per batch
+    uint32_t kbs;             // 64-wide k-blocks per pipeline stage (1, 2 or 4)
+    uint32_t kblocks;         // pipeline steps over k: ceil(k / (64 * kbs))
+    uint32_t total_tiles;
+    uint32_t bn;              // columns per tile (16 .. 256, multiple of 16)
+    uint32_t q_boxes;         // TMA boxes per Q tile (1 for K-major, bn/64 for MN-major; doubled halves in SwiGLU mode)
+    uint32_t q_box_bytes;
+    uint32_t p_major_mn, q_major_mn;
+    int32_t p_batch_mul, q_batch_mul;// 0 when the operand is broadcast over the batch
+    uint32_t stages;
+    // stream-K
+    uint32_t streamk;         // 0: whole tiles, round robin; 1: k-blocks split evenly
+    uint32_t work_per_cta;
+    float *partials;          // [grid][2][kBM * bn] fp32
+    uint32_t *counters;       // [total_tiles], zero on entry
+    // epilogue
+    int mode;
+    uint32_t half_offset;     // SwiGLU: distance (rows of Q, or of P in lane mode) between the gate half and the up half
+    uint16_t *c;
+    int64_t c_lane_stride, c_col_stride, c_batch_stride;// element strides of D's lane index / column index / batch
+    float alpha, beta;
+};
+
+// Everything below is device code and is compiled by the one translation unit that launches the kernel
+// (it defines B200_TC_GEMM_KERNEL before including this header); other files only need the types above.
+#ifdef B200_TC_GEMM_KERNEL
+
+// bounded waits that gave up since the library was loaded
+static __device__ unsigned long long g_tc_gemm_timeouts = 0;
+
+// ---------------------------------------------------------------- PTX wrappers --
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t) __cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the budget ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitBudget) {
+            *abort_flag = 1;
+            atomicAdd(&g_tc_gemm_timeouts, 1ull);
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *map, uint64_t *bar, int32_t x, int32_t y,
+                                            int32_t z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], fp16 inputs, fp32 accumulation; issued by one thread.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The mbarrier receives one arrival when every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+// 16 consecutive fp32 columns of this warp's 32 TMEM lanes (lane = thread), then wait for the data.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float *v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets (all >> 4),
+// descriptor version 1 at bit 46, layout type SWIZZLE_128B (2) at bits 61-63.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = (uint64_t) ((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t) ((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t) ((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Instruction descriptor of kind::f16: D fp32 (bits 4-5 = 1), A and B fp16 (formats 0), majors at bits 15 / 16
+// (0 = K-major, 1 = MN-major), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ inline uint32_t make_idesc(uint32_t m, uint32_t n, uint32_t a_mn_major, uint32_t b_mn_major) {
+    return (1u << 4) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_f32(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
+
+// ---------------------------------------------------------------- the kernel --
+struct WorkItem {
+    uint32_t tile, kb0, kb1;// k-block range [kb0, kb1)
+};
+
+// Item `it` of CTA `cta`; false when the CTA has no more items.
+__device__ __forceinline__ bool work_item(const GemmParams &p, uint32_t cta, uint32_t grid, uint32_t it, WorkItem &w) {
+    if (!p.streamk) {
+        const uint64_t t = (uint64_t) cta + (uint64_t) it * grid;
+        if (t >= p.total_tiles) return false;
+        w.tile = (uint32_t) t, w.kb0 = 0, w.kb1 = p.kblocks;
+        return true;
+    }
+    const uint64_t total = (uint64_t) p.total_tiles * p.kblocks;
+    const uint64_t begin = (uint64_t) cta * p.work_per_cta;
+    uint64_t end = begin + p.work_per_cta;
+    if (end > total) end = total;
+    if (begin >= end) return false;
+    const uint32_t first_tile = (uint32_t) (begin / p.kblocks);
+    const uint32_t tile = first_tile + it;
+    const uint64_t t0 = (uint64_t) tile * p.kblocks;
+    if (t0 >= end) return false;
+    w.tile = tile;
+    w.kb0 = t0 < begin ? (uint32_t) (begin - t0) : 0u;
+    w.kb1 = t0 + p.kblocks > end ? (uint32_t) (end - t0) : p.kblocks;
+    return true;
+}
+
+__device__ __forceinline__ void tile_coords(const GemmParams &p, uint32_t tile, uint32_t &b, uint32_t &tm, uint32_t &tn) {
+    const uint32_t per_batch = p.tiles_m * p.tiles_n;
+    b = tile / per_batch;
+    const uint32_t r = tile - b * per_batch;
+    tn = r / p.tiles_m;
+    tm = r - tn * p.tiles_m;
+}
+
+// Final values of 16 consecutive columns of one lane, written to D.
+__device__ __forceinline__ void store_cols16(const GemmParams &p, const float *acc, uint32_t row, uint32_t col0,
+                                             uint32_t batch, uint32_t mp, uint32_t np, float alpha, float beta) {
+    if (row >= mp) return;
+    uint16_t *base = p.c + (int64_t) batch * p.c_batch_stride + (int64_t) row * p.c_lane_stride;
+    uint16_t out[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        float v = __fmul_rn(alpha, acc[j]);
+        if (beta != 0.f && col0 + j < np) {
+            v = __fadd_rn(__fmul_rn(beta, f16_to_f32(base[(int64_t) (col0 + j) * p.c_col_stride])), v);
+        }
+        out[j] = f32_to_f16_ref(v);
+    }
+    if (p.c_col_stride == 1 && col0 + 16 <= np && ((reinterpret_cast<uintptr_t>(base + col0) & 15u) == 0)) {
+        uint4 *dst = reinterpret_cast<uint4 *>(base + col0);
+        const uint4 *src = reinterpret_cast<const uint4 *>(out);
+        dst[0] = src[0];
+        dst[1] = src[1];
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (col0 + j < np) base[(int64_t) (col0 + j) * p.c_col_stride] = out[j];
+        }
+    }
+}
+
+// The epilogue of one tile for one lane: `load16(c, v)` delivers the 16 accumulator columns that start at
+// column c of the tile (from TMEM, or from the summed stream-K partials).
+template<typename Load16>
+__device__ __forceinline__ void finish_tile(const GemmParams &p, Load16 load16, uint32_t lane_row, uint32_t tm,
+                                            uint32_t tn, uint32_t b, float *xchg) {
+    if (p.mode == kEpiSwiGLUCols) {
+        const uint32_t half = p.bn / 2, row = tm * kBM + lane_row;
+        for (uint32_t c0 = 0; c0 < half; c0 += 16) {
+            float gate[16], up[16];
+            load16(c0, gate);
+            load16(half + c0, up);
+            // the reference stores x * w12 as fp16 before SwiGLU reads it back
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float g = f16_to_f32(f32_to_f16_ref(gate[j])), u = f16_to_f32(f32_to_f16_ref(up[j]));
+                gate[j] = __fmul_rn(u, silu_f32(g));
+            }
+            store_cols16(p, gate, row, tn * half + c0, b, p.mp, p.half_offset, 1.f, 0.f);
+        }
+    } else if (p.mode == kEpiSwiGLULanes) {
+        // lanes 64..127 hand their (up) values to lanes 0..63 through shared memory; all four warps pass every barrier
+        const uint32_t feature = tm * (kBM / 2) + (lane_row & 63u);
+        for (uint32_t c0 = 0; c0 < p.bn; c0 += 16) {
+            float v[16];
+            load16(c0, v);
+            if (lane_row >= 64) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) xchg[(lane_row - 64) * 17 + j] = v[j];
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (lane_row < 64) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float g = f16_to_f32(f32_to_f16_ref(v[j]));
+                    const float u = f16_to_f32(f32_to_f16_ref(xchg[lane_row * 17 + j]));
+                    v[j] = __fmul_rn(u, silu_f32(g));
+                }
+                store_cols16(p, v, feature, tn * p.bn + c0, b, p.half_offset, p.np, 1.f, 0.f);// result rows = features
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+        }
+    } else {
+        const uint32_t row = tm * kBM + lane_row;
+        for (uint32_t c0 = 0; c0 < p.bn; c0 += 16) {
+            float acc[16];
+            load16(c0, acc);
+            store_cols16(p, acc, row, tn * p.bn + c0, b, p.mp, p.np, p.alpha, p.beta);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    tc_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                   const GemmParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // carve: stages of (P tile, Q tile), 1024-byte aligned; then barriers and flags
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    const uint32_t q_bytes = p.q_boxes * p.q_box_bytes;
+    const uint32_t sub_bytes = kPBytes + ((q_bytes + 1023u) & ~1023u);// one 64-wide k-block of P and Q
+    const uint32_t stage_bytes = p.kbs * sub_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t) p.stages * stage_bytes);
+    uint64_t *full = bars, *empty = bars + p.stages, *acc_full = bars + 2 * p.stages, *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    uint32_t *last_flag = tmem_slot + 2;
+    float *xchg = reinterpret_cast<float *>(tmem_slot + 4);// 64 x 17 floats: the lane-mode SwiGLU hand-over
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t acc_cols = p.bn;                               // fp32 columns per accumulator buffer
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < 2 * acc_cols) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 128);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tensormap(&map_p);
+        prefetch_tensormap(&map_q);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            WorkItem w;
+            bool ok = true;
+            for (uint32_t it = 0; ok && work_item(p, blockIdx.x, gridDim.x, it, w); ++it) {
+                uint32_t b, tm, tn;
+                tile_coords(p, w.tile, b, tm, tn);
+                for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    unsigned char *sbase = smem + (size_t) stage * stage_bytes;
+                    mbar_expect_tx(&full[stage], p.kbs * (kPBytes + q_bytes));
+                    const int32_t pb = (int32_t) b * p.p_batch_mul, qb = (int32_t) b * p.q_batch_mul;
+                    // P first: the boxes of one step continue each other's rows in memory, so their requests reach
+                    // the memory system together (256 or 512 contiguous bytes per row instead of 128)
+                    for (uint32_t sub = 0; sub < p.kbs; ++sub) {
+                        unsigned char *sp = sbase + (size_t) sub * sub_bytes;
+                        const int32_t k0 = (int32_t) ((kb * p.kbs + sub) * kBK);
+                        if (p.mode == kEpiSwiGLULanes) {// 64 gate rows, then the matching 64 up rows
+                            const int32_t r0 = (int32_t) (tm * (kBM / 2)), r1 = r0 + (int32_t) p.half_offset;
+                            if (!p.p_major_mn) {
+                                tma_load_3d(sp, &map_p, &full[stage], k0, r0, pb);
+                                tma_load_3d(sp + kPBytes / 2, &map_p, &full[stage], k0, r1, pb);
+                            } else {
+                                tma_load_3d(sp, &map_p, &full[stage], r0, k0, pb);
+                                tma_load_3d(sp + kPBytes / 2, &map_p, &full[stage], r1, k0, pb);
+                            }
+                        } else if (!p.p_major_mn) {
+                            tma_load_3d(sp, &map_p, &full[stage], k0, (int32_t) (tm * kBM), pb);
+                        } else {
+                            tma_load_3d(sp, &map_p, &full[stage], (int32_t) (tm * kBM), k0, pb);
+                            tma_load_3d(sp + kPBytes / 2, &map_p, &full[stage], (int32_t) (tm * kBM + 64), k0, pb);
+                        }
+                    }
+                    for (uint32_t sub = 0; sub < p.kbs; ++sub) {
+                        unsigned char *sq = sbase + (size_t) sub * sub_bytes + kPBytes;
+                        const int32_t k0 = (int32_t) ((kb * p.kbs + sub) * kBK);
+                        if (p.mode == kEpiSwiGLUCols) {
+                            // Q tile = gate columns [tn * bn/2, +bn/2) followed by the matching up columns
+                            const uint32_t half = p.bn / 2, boxes_half = p.q_boxes / 2;
+                            for (uint32_t h = 0; h < 2; ++h) {
+                                const int32_t r0 = (int32_t) (tn * half + h * p.half_offset);
+                                for (uint32_t x = 0; x < boxes_half; ++x) {
+                                    unsigned char *dst = sq + (size_t) (h * boxes_half + x) * p.q_box_bytes;
+                                    if (!p.q_major_mn) tma_load_3d(dst, &map_q, &full[stage], k0, r0, qb);
+                                    else tma_load_3d(dst, &map_q, &full[stage], r0 + (int32_t) (x * 64), k0, qb);
+                                }
+                            }
+                        } else if (!p.q_major_mn) {
+                            tma_load_3d(sq, &map_q, &full[stage], k0, (int32_t) (tn * p.bn), qb);
+                        } else {
+                            for (uint32_t x = 0; x < p.q_boxes; ++x) {
+                                tma_load_3d(sq + (size_t) x * p.q_box_bytes, &map_q, &full[stage],
+                                            (int32_t) (tn * p.bn + x * 64), k0, qb);
+                            }
+                        }
+                    }
+                    if (++stage == p.stages) stage = 0, phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();// the other lanes wait here, so the warp reaches the closing barrier converged
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(kBM, p.bn, p.p_major_mn, p.q_major_mn);
+            uint32_t stage = 0, phase = 0, acc_it = 0;
+            WorkItem w;
+            bool ok = true;
+            for (uint32_t it = 0; ok && work_item(p, blockIdx.x, gridDim.x, it, w); ++it, ++acc_it) {
+                const uint32_t buf = acc_it & 1u;
+                if (!mbar_wait(&acc_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * acc_cols;
+                for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    for (uint32_t sub = 0; sub < p.kbs; ++sub) {
+                        const uint32_t sp = smem_u32(smem + (size_t) stage * stage_bytes + (size_t) sub * sub_bytes);
+                        const uint32_t sq = sp + kPBytes;
+#pragma unroll
+                        for (uint32_t j = 0; j < kBK / kUmmaK; ++j) {
+                            // K-major: 16 k = 32 bytes further along the swizzled 128-byte rows, 8-row groups 1024 bytes
+                            // apart.  MN-major: 16 k = two 8-row groups of 1024 bytes; 64-row atoms one TMA box apart.
+                            const uint64_t da = p.p_major_mn ? make_smem_desc(sp + j * 2048u, kPBytes / 2, 1024)
+                                                             : make_smem_desc(sp + j * 32u, 16, 1024);
+                            const uint64_t db = p.q_major_mn ? make_smem_desc(sq + j * 2048u, p.q_box_bytes, 1024)
+                                                             : make_smem_desc(sq + j * 32u, 16, 1024);
+                            umma_f16(d_tmem, da, db, idesc, (kb > w.kb0 || sub > 0 || j > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(&empty[stage]);// the stage may be refilled once these MMAs have read it
+                    if (++stage == p.stages) stage = 0, phase ^= 1u;
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const uint32_t quarter = warp & 3u;// TMEM lanes 32 * quarter .. + 31 belong to this warp
+        const uint32_t epi_tid = (warp - 2) * 32 + lane;
+        uint32_t acc_it = 0;
+        WorkItem w;
+        for (uint32_t it = 0; work_item(p, blockIdx.x, gridDim.x, it, w); ++it, ++acc_it) {
+            const uint32_t buf = acc_it & 1u;
+            uint32_t b, tm, tn;
+            tile_coords(p, w.tile, b, tm, tn);
+            if (!mbar_wait(&acc_full[buf], (acc_it >> 1) & 1u, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t lane_row = quarter * 32 + lane;
+            // does this lane hold a row of the matrix (lane mode: a feature below the intermediate size)?
+            const bool row_valid = p.mode == kEpiSwiGLULanes ? tm * (kBM / 2) + (lane_row & 63u) < p.half_offset
+                                                             : tm * kBM + lane_row < p.mp;
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * acc_cols;
+            const bool partial = p.streamk && !(w.kb0 == 0 && w.kb1 == p.kblocks);
+            if (!partial) {
+                finish_tile(p, [&](uint32_t c, float *v) { tmem_ld16(taddr + c, v); }, lane_row, tm, tn, b, xchg);
+                tc_fence_before();
+                mbar_arrive(&acc_empty[buf]);
+            } else {
+                // part of a tile's k range: park the fp32 partial, count this CTA on the tile, and let the CTA
+                // that arrives last add all parts in CTA order
+                const uint32_t slot = w.kb0 == 0 ? 1u : 0u;// a part that starts mid-tile opens the CTA's range (slot 0)
+                float *mine = p.partials + ((size_t) blockIdx.x * 2 + slot) * (size_t) (kBM * p.bn);
+                for (uint32_t c0 = 0; c0 < p.bn; c0 += 16) {
+                    float acc[16];
+                    tmem_ld16(taddr + c0, acc);// all lanes of the warp take part in the load
+                    if (row_valid) {           // rows beyond the matrix are never read back
+                        float4 *dst = reinterpret_cast<float4 *>(mine + (size_t) lane_row * p.bn + c0);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) __stcg(dst + j, make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&acc_empty[buf]);
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");// the four epilogue warps
+                // CTAs whose range meets this tile: first .. last
+                const uint64_t t0 = (uint64_t) w.tile * p.kblocks;
+                const uint32_t first = (uint32_t) (t0 / p.work_per_cta);
+                const uint32_t last = (uint32_t) ((t0 + p.kblocks - 1) / p.work_per_cta);
+                if (epi_tid == 0) {
+                    const uint32_t seen = atomicAdd(&p.counters[w.tile], 1u);
+                    *last_flag = seen == last - first ? 1u : 0u;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const bool is_last = *last_flag != 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (is_last) {
+                    __threadfence();
+                    if (epi_tid == 0) p.counters[w.tile] = 0;// ready for the next launch
+                    finish_tile(
+                        p,
+                        [&](uint32_t c, float *acc) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+                            if (!row_valid) return;
+                            for (uint32_t cta = first; cta <= last; ++cta) {
+                                // CTA `cta`'s part of this tile starts mid-tile exactly when its range starts inside the tile
+                                const uint64_t cb = (uint64_t) cta * p.work_per_cta;
+                                const uint32_t s = cb > t0 ? 0u : 1u;
+                                const float *src = p.partials + ((size_t) cta * 2 + s) * (size_t) (kBM * p.bn) +
+                                                   (size_t) lane_row * p.bn + c;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(src) + j);
+                                    acc[4 * j] += v.x, acc[4 * j + 1] += v.y, acc[4 * j + 2] += v.z, acc[4 * j + 3] += v.w;
+                                }
+                            }
+                        },
+                        lane_row, tm, tn, b, xchg);
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // let TMA copies that are still in flight land before the shared memory is given back
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            const long long t0 = clock64();
+            while (!mbar_try_wait(&full[s], 0) && !mbar_try_wait(&full[s], 1) && clock64() - t0 < 2000000ll) {}
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+#endif// B200_TC_GEMM_KERNEL
+
+}// namespace tc
+}// namespace b200

@@ -45,6 +45,14 @@ def _declare(lib):
         "infiniopGetAttentionWorkspaceSize": [D, POINTER(c_uint64)],
         "infiniopAttention": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "infiniopDestroyAttentionDescriptor": [D],
+        "infiniopCreateMatmulDescriptor": [H, POINTER(D), T, c_float, T, T, c_float],
+        "infiniopGetMatmulWorkspaceSize": [D, POINTER(c_uint64)],
+        "infiniopMatmul": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroyMatmulDescriptor": [D],
+        "infiniopCreateMLPDescriptor": [H, POINTER(D), T, T, T, T, c_float, ctypes.c_char],
+        "infiniopGetMLPWorkspaceSize": [D, POINTER(c_uint64)],
+        "infiniopMLP": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "infiniopDestroyMLPDescriptor": [D],
         "infiniopCreateRoPERearrangeDescriptor": [H, POINTER(D), T, T, T, T, T],
         "infiniopGetRoPERearrangeWorkspaceSize": [D, POINTER(c_uint64)],
         "infiniopRoPERearrange": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -78,6 +86,11 @@ def _declare(lib):
         if fn is not None:
             fn.argtypes = argtypes
             fn.restype = c_int
+    if hasattr(lib, "infiniopExtDeviceTimeouts"):
+        lib.infiniopExtDeviceTimeouts.argtypes = [H, POINTER(c_uint64)]
+        lib.infiniopExtDeviceTimeouts.restype = c_int
+        lib.infiniopExtSetWaitLimit.argtypes = [H, ctypes.c_uint32]
+        lib.infiniopExtSetWaitLimit.restype = c_int
     if hasattr(lib, "infiniopExtSelectKernel"):
         lib.infiniopExtSelectKernel.argtypes = [c_int, c_int]
         lib.infiniopExtSelectKernel.restype = c_int
@@ -95,6 +108,21 @@ def select_kernel(lib, family, variant):
     infiniopExtSelectKernel in include/infiniop_ext.h.  variant 0 = the library's own choice."""
     _declare(lib)
     check_error(lib.infiniopExtSelectKernel(KERNEL_FAMILIES[family], int(variant)))
+
+
+def device_timeouts(lib, handle):
+    """Thread groups that gave up on a bounded wait since the library was loaded (synchronises);
+    0 = every result so far is complete.  See infiniopExtDeviceTimeouts."""
+    _declare(lib)
+    n = c_uint64(0)
+    check_error(lib.infiniopExtDeviceTimeouts(handle, ctypes.byref(n)))
+    return n.value
+
+
+def set_wait_limit(lib, handle, polls):
+    """Polls per wait of the RoPE bulk-copy pipeline (0 = default); for the test that makes a wait run out."""
+    _declare(lib)
+    check_error(lib.infiniopExtSetWaitLimit(handle, int(polls)))
 
 
 def _stream_ptr(stream):
@@ -218,6 +246,38 @@ class AttentionOp(_Op):
         check_error(self.lib.infiniopAttention(self.desc, self._ws_ptr(), self.workspace_size, out.data_ptr(),
                                                q.data_ptr(), k.data_ptr(), v.data_ptr(), k_cache.data_ptr(),
                                                v_cache.data_ptr(), _stream_ptr(stream)))
+
+
+class MatmulOp(_Op):
+    """c = alpha * a @ b + beta * c on 2-D or batched 3-D tensors (reference operatorspy/tests/matmul.py)."""
+    _destroy, _wsize = "infiniopDestroyMatmulDescriptor", "infiniopGetMatmulWorkspaceSize"
+
+    def __init__(self, lib, handle, c, a, b, alpha=1.0, beta=0.0):
+        super().__init__(lib, handle)
+        ct, at, bt = self._t(c), self._t(a), self._t(b)
+        check_error(lib.infiniopCreateMatmulDescriptor(handle, ctypes.byref(self.desc), ct.descriptor, alpha,
+                                                       at.descriptor, bt.descriptor, beta))
+        self._make_workspace(c.device)
+
+    def __call__(self, c, a, b, stream=None):
+        check_error(self.lib.infiniopMatmul(self.desc, self._ws_ptr(), self.workspace_size, c.data_ptr(), a.data_ptr(),
+                                            b.data_ptr(), _stream_ptr(stream)))
+
+
+class MLPOp(_Op):
+    """y = (residual ? y : 0) + alpha * SwiGLU(x @ w12) @ w3 (reference operatorspy/tests/mlp.py)."""
+    _destroy, _wsize = "infiniopDestroyMLPDescriptor", "infiniopGetMLPWorkspaceSize"
+
+    def __init__(self, lib, handle, y, x, w12, w3, alpha=1.0, residual=True):
+        super().__init__(lib, handle)
+        ts = [self._t(t) for t in (y, x, w12, w3)]
+        check_error(lib.infiniopCreateMLPDescriptor(handle, ctypes.byref(self.desc), *[t.descriptor for t in ts],
+                                                    alpha, bytes([1 if residual else 0])))
+        self._make_workspace(y.device)
+
+    def __call__(self, y, x, w12, w3, stream=None):
+        check_error(self.lib.infiniopMLP(self.desc, self._ws_ptr(), self.workspace_size, y.data_ptr(), x.data_ptr(),
+                                         w12.data_ptr(), w3.data_ptr(), _stream_ptr(stream)))
 
 
 class RoPERearrangeOp(_Op):
@@ -352,6 +412,16 @@ class RandomSampleOp(_Op):
 def attention(lib, handle, out, q, k, v, k_cache, v_cache, pos, stream=None):
     with AttentionOp(lib, handle, out, q, k, v, k_cache, v_cache, pos) as op:
         op(out, q, k, v, k_cache, v_cache, stream)
+
+
+def matmul(lib, handle, c, a, b, alpha=1.0, beta=0.0, stream=None):
+    with MatmulOp(lib, handle, c, a, b, alpha, beta) as op:
+        op(c, a, b, stream)
+
+
+def mlp(lib, handle, y, x, w12, w3, alpha=1.0, residual=True, stream=None):
+    with MLPOp(lib, handle, y, x, w12, w3, alpha, residual) as op:
+        op(y, x, w12, w3, stream)
 
 
 def rope_rearrange(lib, handle, dst, src, pos_ids, sin_table, cos_table, stream=None):

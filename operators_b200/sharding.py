@@ -8,10 +8,12 @@ the unchanged single-device C ABI:
   leading axis) need no communication: `row_range` / `shard_rows` give each rank
   a contiguous slice and the rank builds its descriptors for that slice.
 * `VocabShardedSampler` samples from logits whose vocabulary axis is split over
-  the ranks (the layout a tensor-parallel LM head leaves them in): a local
-  candidate kernel on every rank, ONE all-gather of ~1 KB per row per rank, a
-  finishing kernel.  The gathered records are in local memory before any kernel
-  reads them; nothing here loads from a peer's memory.
+  the ranks (the layout a tensor-parallel LM head leaves them in).  Its default
+  mode is index-exact: one all-to-all hands every rank whole rows, the exact
+  batched kernel samples them, one all-gather returns the indices.  Its fast mode
+  exchanges ~1 KB of candidates per row per rank in ONE all-gather.  Received
+  data is in local memory before any kernel reads it; nothing here loads from a
+  peer's memory.
 """
 
 from .ops import _declare, _stream_ptr
@@ -37,19 +39,78 @@ def vocab_range(voc_total, world_size, rank):
     return row_range(voc_total, world_size, rank)
 
 
-class VocabShardedSampler:
-    """Sampling branch of random sample (topp > 0, 2 <= topk <= 64) over
-    vocabulary shards.  `all_gather(out, inp)` defaults to
-    torch.distributed.all_gather_into_tensor on `group`."""
+def exchange_plan(rows, voc_total, world_size, rank):
+    """Who sends what when every rank holds all rows of its vocabulary shard and rank r is to own whole rows
+    row_range(rows, world_size, r): (my row range, element counts this rank sends to each peer, element counts
+    it receives from each peer, the shards' column ranges)."""
+    cols = [vocab_range(voc_total, world_size, r) for r in range(world_size)]
+    my_cols = cols[rank][1] - cols[rank][0]
+    owned = [row_range(rows, world_size, r) for r in range(world_size)]
+    mine = owned[rank][1] - owned[rank][0]
+    send = [(e - b) * my_cols for b, e in owned]
+    recv = [mine * (e - b) for b, e in cols]
+    return owned[rank], send, recv, cols
 
-    def __init__(self, lib, handle, sample_op, voc_total, shard_offset, world_size, group=None, all_gather=None):
+
+def assemble_rows(received, n_rows, cols, out=None):
+    """The flat buffer an all-to-all delivers (peer after peer: [n_rows, that peer's columns]) re-laid as
+    [n_rows, voc_total]."""
+    import torch
+
+    voc_total = cols[-1][1]
+    if out is None:
+        out = torch.empty((n_rows, voc_total), dtype=received.dtype, device=received.device)
+    off = 0
+    for b, e in cols:
+        n = n_rows * (e - b)
+        out[:, b:e].copy_(received[off:off + n].view(n_rows, e - b))
+        off += n
+    return out
+
+
+class VocabShardedSampler:
+    """Sampling branch of random sample (topp > 0, 2 <= topk <= 64) over vocabulary shards; every rank gets
+    the same results.
+
+    mode "exact" (default): the sampled index is the unsharded entry point's, i.e. the reference CPU path's,
+    for every row.  The reference's softmax denominator is a sequential fp32 sum over the whole row, which no
+    per-shard partial can reproduce, so the rows are redistributed instead: ONE all-to-all gives rank r the whole
+    rows row_range(rows, world, r), the exact batched kernel samples them, one all-gather of the indices (8 bytes
+    per row) closes the call.
+
+    mode "fast": a local candidate kernel on every rank, ONE all-gather of ~1 KB per row per rank, a finishing
+    kernel.  Top-k set, tie order and numerators are the reference's; the denominator is the correctly rounded
+    sum instead of the sequential one, so a small fraction of rows picks a neighbouring candidate.
+
+    Received data is in local memory before any kernel reads it; nothing here loads from a peer's memory.
+    `stream`, when given, must be a torch.cuda.Stream: the collectives and the library's kernels are all issued
+    on it.  `all_gather(out, inp)` / `all_to_all(out, inp, out_splits, in_splits)` replace the
+    torch.distributed calls on `group` (tests play several ranks in one process with them)."""
+
+    def __init__(self, lib, handle, sample_op, voc_total, shard_offset, world_size, group=None, all_gather=None,
+                 mode="exact", rank=None, all_to_all=None):
         _declare(lib)
+        assert mode in ("exact", "fast")
         self.lib, self.handle, self.op = lib, handle, sample_op
         self.voc_total, self.shard_offset, self.world = int(voc_total), int(shard_offset), int(world_size)
-        self.group = group
+        self.group, self.mode = group, mode
         self.record_bytes = int(lib.infiniopRandomSampleShardRecordBytes())
-        self._gather = all_gather
+        self._gather, self._a2a = all_gather, all_to_all
+        if rank is None:
+            rank = 0
+            if self.world > 1 and all_to_all is None:
+                import torch.distributed as dist
+
+                rank = dist.get_rank(group)
+        self.rank = int(rank)
         self._bufs = {}
+        self._exact = {}
+        self.last_events = None
+
+    def destroy(self):
+        for _, _, _, op in self._exact.values():
+            op.destroy()
+        self._exact = {}
 
     def _buffers(self, rows, device):
         import torch
@@ -62,16 +123,95 @@ class VocabShardedSampler:
                                torch.zeros(1, dtype=torch.int32, device=device))
         return self._bufs[key]
 
-    def sample(self, results, local_logits, random_vals, topp, topk, temperature, stream=None, check=True):
-        """local_logits fp16 [rows, voc_local] (this rank's columns), random_vals
-        fp32 [rows] and results int64/uint64 [rows] on the device; every rank gets
-        the same results."""
+    def _exact_buffers(self, rows, device):
+        import torch
+
+        from .ops import RandomSampleOp
+
+        key = (rows, str(device))
+        if key not in self._exact:
+            (r0, r1), _, recv, _ = exchange_plan(rows, self.voc_total, self.world, self.rank)
+            most = max(e - b for b, e in (row_range(rows, self.world, r) for r in range(self.world)))
+            received = torch.empty(max(1, sum(recv)), dtype=torch.float16, device=device)
+            full = torch.empty((max(1, r1 - r0), self.voc_total), dtype=torch.float16, device=device)
+            picked = torch.zeros((self.world, most), dtype=torch.int64, device=device)
+            op = RandomSampleOp(self.lib, self.handle, picked[0, :1], full[0])
+            op._ensure_batch_ws(max(1, r1 - r0), device)
+            self._exact[key] = (received, full, picked, op)
+        return self._exact[key]
+
+    def sample(self, results, local_logits, random_vals, topp, topk, temperature, stream=None, check=True,
+               timed=False):
+        """local_logits fp16 [rows, voc_local] (this rank's columns), random_vals fp32 [rows] and results
+        int64/uint64 [rows] on the device.  timed=True records CUDA events between the stages in
+        self.last_events (names and events, in issue order)."""
+        import contextlib
+
+        import torch
+
+        ctx = torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext()
+        events = []
+
+        def mark(name):
+            if timed:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                events.append((name, ev))
+
+        with ctx:
+            sp = _stream_ptr(torch.cuda.current_stream(local_logits.device)) if local_logits.is_cuda else None
+            mark("start")
+            if self.mode == "exact":
+                self._sample_exact(results, local_logits, random_vals, topp, topk, temperature, sp, mark)
+            else:
+                self._sample_fast(results, local_logits, random_vals, topp, topk, temperature, sp, check, mark)
+        self.last_events = events
+        return results
+
+    def _sample_exact(self, results, local_logits, random_vals, topp, topk, temperature, sp, mark):
+        import torch
+
+        rows = local_logits.shape[0]
+        (r0, r1), send, recv, cols = exchange_plan(rows, self.voc_total, self.world, self.rank)
+        mine = r1 - r0
+        received, full, picked, op = self._exact_buffers(rows, local_logits.device)
+        src = local_logits if local_logits.is_contiguous() else local_logits.contiguous()
+        if self._a2a is not None:
+            self._a2a(received, src.view(-1), recv, send)
+        elif self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_to_all_single(received[:sum(recv)], src.view(-1), recv, send, group=self.group)
+        else:
+            received[:src.numel()].copy_(src.view(-1))
+        mark("all_to_all")
+        if mine:
+            assemble_rows(received, mine, cols, out=full)
+            mark("assemble")
+            op.batch(picked[self.rank, :mine], full[:mine], random_vals[r0:r1], topp, topk, temperature, stream=sp)
+        mark("sample")
+        if self._gather is not None:
+            self._gather(picked, picked[self.rank])
+        elif self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_gather_into_tensor(picked.view(-1), picked[self.rank], group=self.group)
+        mark("all_gather")
+        if rows % self.world == 0:
+            results.view(torch.int64).copy_(picked.view(-1))
+        else:
+            for r in range(self.world):
+                b, e = row_range(rows, self.world, r)
+                results.view(torch.int64)[b:e].copy_(picked[r, :e - b])
+        mark("finish")
+
+    def _sample_fast(self, results, local_logits, random_vals, topp, topk, temperature, sp, check, mark):
         rows = local_logits.shape[0]
         local, gathered, status = self._buffers(rows, local_logits.device)
-        sp = _stream_ptr(stream)
         check_error(self.lib.infiniopRandomSampleShardLocal(
             self.op.desc, local.data_ptr(), local_logits.data_ptr(), local_logits.stride(0), rows, self.shard_offset,
             topk, temperature, sp))
+        mark("local")
         if self._gather is not None:
             self._gather(gathered, local)
         elif self.world > 1:
@@ -80,11 +220,12 @@ class VocabShardedSampler:
             dist.all_gather_into_tensor(gathered.view(-1), local.view(-1), group=self.group)
         else:
             gathered[0].copy_(local)
+        mark("all_gather")
         status.zero_()
         check_error(self.lib.infiniopRandomSampleShardFinish(
             self.handle, results.data_ptr(), gathered.data_ptr(), self.world, rows, self.voc_total,
             random_vals.data_ptr(), topp, topk, temperature, status.data_ptr(), sp))
+        mark("finish")
         if check and int(status.item()) != 0:
             raise RuntimeError("vocabulary-sharded sampling: a shard held more than 128 tied candidates in some row; "
                                "gather the logits and use the unsharded entry point for this batch")
-        return results

@@ -52,6 +52,9 @@ def lib():
         L.oracle_rearrange.argtypes = [vp, vp, u64, u64, vp, vp, vp]
         L.oracle_causal_softmax_f16.argtypes = [vp, u64, u64, u64, i64, i64, i64]
         L.oracle_matmul_f16.argtypes, L.oracle_matmul_f16.restype = [vp, vp, vp, cf, u64, u64, u64, u64, vp, vp, vp], None
+        L.oracle_matmul_f16_beta.argtypes = [vp, vp, vp, cf, cf, u64, u64, u64, u64, vp, vp, vp]
+        L.oracle_matmul_f16_beta.restype = None
+        L.oracle_matmul_f32.argtypes, L.oracle_matmul_f32.restype = [vp, vp, vp, cf, cf, u64, u64, u64, u64, vp, vp, vp], None
         L.oracle_random_sample_f16.argtypes = [vp, vp, vp, ci, cf, cf, ci, cf]
         L.oracle_random_sample_workspace.argtypes, L.oracle_random_sample_workspace.restype = [ci], u64
         L.oracle_random_sample_trace.argtypes = [vp, vp, ci, ci, cf, vp, vp, vp, vp]
@@ -193,6 +196,43 @@ def matmul(a, b, alpha=1.0):
     lib().oracle_matmul_f16(_ptr(c), _ptr(au), _ptr(bu), float(alpha), au.shape[0], au.shape[1], bu.shape[2],
                             au.shape[2], ctypes.addressof(sc), ctypes.addressof(sa), ctypes.addressof(sb))
     return c.view(np.float16)
+
+
+def matmul_into(c, a, b, alpha=1.0, beta=0.0):
+    """c = alpha * a @ b + beta * c in place on numpy views (2-D or batched 3-D, fp16 or fp32, the arrays' own
+    strides; a and b may have batch 1 against a batched c).  src/ops/matmul/cpu/matmul_cpu.cc:44-78."""
+    c3, a3, b3 = (x if x.ndim == 3 else x[None] for x in (c, a, b))
+    batch, m, n = c3.shape
+    k = a3.shape[2]
+    assert a3.shape[1:] == (m, k) and b3.shape[1:] == (k, n) and a3.shape[0] in (1, batch) and b3.shape[0] in (1, batch)
+
+    def strides(x):
+        st = _elem_strides(x)
+        if x.shape[0] == 1:
+            st[0] = 0
+        return (ctypes.c_int64 * 3)(*st)
+
+    sc, sa, sb = strides(c3), strides(a3), strides(b3)
+    if c.dtype == np.float32:
+        assert a.dtype == np.float32 and b.dtype == np.float32
+        lib().oracle_matmul_f32(_ptr(c3), _ptr(a3), _ptr(b3), float(alpha), float(beta), batch, m, n, k,
+                                ctypes.addressof(sc), ctypes.addressof(sa), ctypes.addressof(sb))
+    else:
+        cu, au, bu = _u16(c3), _u16(a3), _u16(b3)
+        lib().oracle_matmul_f16_beta(_ptr(cu), _ptr(au), _ptr(bu), float(alpha), float(beta), batch, m, n, k,
+                                     ctypes.addressof(sc), ctypes.addressof(sa), ctypes.addressof(sb))
+    return c
+
+
+def mlp(y, x, w12, w3, alpha=1.0, residual=True):
+    """The MLP composite, src/ops/mlp/operator.cc:22-122, with the operators above: gate_up = x @ w12 stored as
+    fp16, act = up * silu(gate) on its column halves (gate first), y = alpha * act @ w3 (+ y).  In place on y."""
+    tokens, di = x.shape[0], w12.shape[1] // 2
+    gate_up = np.zeros((tokens, 2 * di), np.float16)
+    matmul_into(gate_up, x, w12)
+    act = swiglu(gate_up[:, di:], gate_up[:, :di])
+    matmul_into(y, act, w3, alpha, 1.0 if residual else 0.0)
+    return y
 
 
 def attention(q, k, v, k_cache, v_cache, pos):

@@ -160,6 +160,58 @@ def test_attention(oracle, ref_cpu, nh, nkvh, seq, dh, pos, buf_len, qkv_strides
     assert torch.equal(kc2, k_cache) and torch.equal(vc2, v_cache)
 
 
+# the reference's own matmul cases (operatorspy/tests/matmul.py:296-308) and a few ragged / broadcast ones
+MATMUL_CASES = [
+    (1.0, 0.0, (1, 2048), (2048, 2048), (1, 2048), None, None, None),
+    (1.0, 0.0, (2, 4, 2048), (2, 2048, 2048), (2, 4, 2048), None, None, None),
+    (1.0, 0.0, (1, 2048), (2048, 2048), (1, 2048), (4096, 1), (4096, 1), (4096, 1)),
+    (1.0, 1.0, (6, 2048), (2048, 2560), (6, 2560), (2048, 1), (1, 2048), (2560, 1)),
+    (1.0 / 8.0, 0.0, (4, 8 * 6, 64), (4, 64, 6), (4, 8 * 6, 6), None, None, None),
+    (0.5, 2.0, (37, 100), (100, 19), (37, 19), (1, 37), None, (1, 40)),
+    (1.0, 0.0, (3, 9, 40), (1, 40, 24), (3, 9, 24), None, None, None),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("alpha,beta,a_shape,b_shape,c_shape,a_stride,b_stride,c_stride", MATMUL_CASES)
+def test_matmul(oracle, ref_cpu, alpha, beta, a_shape, b_shape, c_shape, a_stride, b_stride, c_stride, dtype):
+    lib, handle = ref_cpu
+    g = torch.Generator().manual_seed(8)
+    a, b, c = (torch.rand(s, generator=g).to(dtype) for s in (a_shape, b_shape, c_shape))
+    a, b, c = (t if st is None else rearrange_tensor(t, st) for t, st in ((a, a_stride), (b, b_stride), (c, c_stride)))
+    mine = c.clone()
+    if c_stride is not None:
+        mine = rearrange_tensor(mine, c_stride)
+    oracle.matmul_into(mine.numpy(), a.numpy(), b.numpy(), alpha, beta)
+    ops.matmul(lib, handle, c, a, b, alpha, beta)
+    assert torch.equal(mine.view(torch.int16 if dtype == torch.float16 else torch.int32),
+                       c.view(torch.int16 if dtype == torch.float16 else torch.int32))
+
+
+@pytest.mark.parametrize("tokens,hidden,di,alpha,residual,x_stride,w12_stride,w3_stride", [
+    (4, 256, 688, 1.0, True, None, None, None), (4, 256, 688, 1.0, False, (512, 1), None, None),
+    (3, 128, 344, 0.5, True, None, (1, 128), (1, 344)), (2, 4096, 11008, 1.0, True, None, None, None)])
+def test_mlp(oracle, ref_cpu, tokens, hidden, di, alpha, residual, x_stride, w12_stride, w3_stride):
+    """The reference composite (src/ops/mlp/operator.cc) and the oracle's restatement of its three steps write
+    the same bits (shapes of operatorspy/tests/mlp.py:245-, scaled down except for the last)."""
+    lib, handle = ref_cpu
+    g = torch.Generator().manual_seed(9)
+    y = (torch.rand((tokens, hidden), generator=g) * 0.01).half()
+    x = (torch.rand((tokens, hidden), generator=g) * 0.01).half()
+    w12 = (torch.rand((hidden, 2 * di), generator=g) * 0.01).half()
+    w3 = (torch.rand((di, hidden), generator=g) * 0.01).half()
+    if x_stride is not None:
+        x, y = rearrange_tensor(x, x_stride), rearrange_tensor(y, x_stride)
+    if w12_stride is not None:
+        w12, w3 = rearrange_tensor(w12, w12_stride), rearrange_tensor(w3, w3_stride)
+    mine = y.clone()
+    if x_stride is not None:
+        mine = rearrange_tensor(mine, x_stride)
+    oracle.mlp(mine.numpy(), x.numpy(), w12.numpy(), w3.numpy(), alpha, residual)
+    ops.mlp(lib, handle, y, x, w12, w3, alpha, residual)
+    assert torch.equal(mine.view(torch.int16), y.view(torch.int16))
+
+
 @pytest.mark.parametrize("shape", [(32, 20, 512), (5, 64), (2, 7, 7), (3, 1, 9)])
 def test_causal_softmax(oracle, ref_cpu, shape):
     lib, handle = ref_cpu
