@@ -48,10 +48,17 @@ OPS = list(ALGO_BYTES)
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the
-# dominant kernel from the ncu capture summarised in profiles/swiglu_vec8_kernel_8192x14336.md
-# (469.79 MB read + 196.16 MB written; the last ~39 MB of output were still in L2 when the kernel ended).
-NCU_TRAFFIC_BYTES = {"swiglu": 665952000}
+def ncu_traffic_bytes(profile):
+    """DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from the
+    line `dram_traffic_bytes_per_launch: N` of the committed ncu summary profiles/<profile>; None when absent."""
+    import re
+
+    try:
+        text = open(os.path.join(ROOT, "profiles", profile)).read()
+    except OSError:
+        return None
+    m = re.search(r"dram_traffic_bytes_per_launch:\s*(\d+)", text)
+    return int(m.group(1)) if m else None
 
 
 def measured_peak():
@@ -62,6 +69,14 @@ def measured_peak():
         except Exception:
             pass
     return FALLBACK_HBM_GBS, "fallback"
+
+
+def measured_tflops():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
 
 
 def make_inputs(seed, rows_fraction=1.0, only=None):
@@ -166,6 +181,34 @@ class ClockSampler:
         reasons = sorted(k for k, bit in self.REASONS.items() if self.reason_bits & bit)
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz, "reasons": reasons,
                 "samples": len(sm)}
+
+
+def pin_to_gpu_numa_node(torch, local):
+    """Moves this process onto the CPUs of the NUMA node the GPU hangs off (read from sysfs), so that the pinned
+    staging buffers allocated afterwards are first touched there.  Returns what was done, for the JSON line."""
+    try:
+        nodes = [d for d in os.listdir("/sys/devices/system/node") if d.startswith("node") and d[4:].isdigit()]
+    except OSError:
+        nodes = []
+    if len(nodes) <= 1:
+        return "host exposes one NUMA node: all ranks stage through it"
+    try:
+        props = torch.cuda.get_device_properties(local)
+        bdf = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/%s/numa_node" % bdf).read().strip())
+        if node < 0:
+            return "GPU %s reports no NUMA node; affinity left as it was" % bdf
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if not allowed:
+            return "node %d of GPU %s has no CPU this process may use; affinity left as it was" % (node, bdf)
+        os.sched_setaffinity(0, allowed)
+        return "rank pinned to NUMA node %d (%d CPUs) of GPU %s" % (node, len(allowed), bdf)
+    except Exception as exc:  # noqa: BLE001
+        return "NUMA node of the GPU not found (%s); affinity left as it was" % exc
 
 
 # ---- this library ------------------------------------------------------------------------
@@ -332,7 +375,80 @@ def only_attention(lib, handle, dev, steps, warmup):
             "note": "back-to-back calls of one operator; bytes = K and V rows read once; not a bench value"}
 
 
-NEXT_ROWS = {"rearrange": only_rearrange, "add_rms_norm": only_add_rms_norm, "rope_rearrange": only_rope_rearrange,
+def _timed_calls(torch, fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / steps
+
+
+def only_matmul(lib, handle, dev, steps, warmup):
+    """Not part of the step: the gate / up projection of the SwiGLU configuration, [tokens, 4096] x [4096, 28672],
+    for a prefill-sized and two decoding token counts, weights in both layouts.  Prefill shapes are judged in
+    TFLOP/s against the measured cuBLAS bf16 peak, decoding shapes in GB/s against the measured copy bandwidth
+    (the 235 MB weight matrix is read once; it is larger than L2)."""
+    import torch
+
+    from operators_b200 import ops as _ops
+
+    hidden, n = ADD_D, 2 * SWI_DI
+    peak_tf, tf_kind = measured_tflops()
+    peak_bw, bw_kind = measured_peak()
+    w_kn = torch.randn((hidden, n), device=dev).half() * 0.02       # [k, n] row-major: n contiguous
+    w_nk = (torch.randn((n, hidden), device=dev).half() * 0.02).t()  # [k, n] view of a [n, k] weight: k contiguous
+    out = {"only": "matmul", "k": hidden, "n": n, "cases": [],
+           "note": "back-to-back calls of one operator; not a bench value"}
+    for tokens in (SWI_T, 16, 1):
+        a = torch.randn((tokens, hidden), device=dev).half()
+        c = torch.empty((tokens, n), device=dev, dtype=torch.float16)
+        for name, w in (("k_contiguous", w_nk), ("n_contiguous", w_kn)):
+            op = _ops.MatmulOp(lib, handle, c, a, w)
+            ms = _timed_calls(torch, lambda: op(c, a, w), max(3, steps // (4 if tokens > 64 else 1)), warmup)
+            op.destroy()
+            flops, nbytes = 2.0 * tokens * hidden * n, 2.0 * (tokens * hidden + hidden * n + tokens * n)
+            case = {"tokens": tokens, "weights": name, "ms": round(ms, 5), "tflops": round(flops / ms / 1e9, 1),
+                    "gbs": round(nbytes / ms / 1e6, 1)}
+            if tokens > 64:
+                case["frac_of_%s_bf16_peak" % tf_kind] = round(flops / ms / 1e9 / peak_tf, 4)
+            else:
+                case["frac_of_%s_hbm_peak" % bw_kind] = round(nbytes / ms / 1e6 / peak_bw, 4)
+            out["cases"].append(case)
+        del a, c
+    return out
+
+
+def only_mlp(lib, handle, dev, steps, warmup):
+    """Not part of the step: the MLP composite at hidden 4096, intermediate 14336 (SwiGLU runs as the epilogue of
+    the first product: the [tokens, 2 x 14336] tensor of the SwiGLU configuration never reaches HBM)."""
+    import torch
+
+    from operators_b200 import ops as _ops
+
+    hidden, di = ADD_D, SWI_DI
+    w12 = torch.randn((hidden, 2 * di), device=dev).half() * 0.02
+    w3 = torch.randn((di, hidden), device=dev).half() * 0.02
+    out = {"only": "mlp", "hidden": hidden, "intermediate": di, "cases": [],
+           "note": "back-to-back calls of one operator; not a bench value"}
+    for tokens in (SWI_T, 16):
+        x = torch.randn((tokens, hidden), device=dev).half() * 0.1
+        y = torch.randn((tokens, hidden), device=dev).half()
+        op = _ops.MLPOp(lib, handle, y, x, w12, w3, 1.0, True)
+        ms = _timed_calls(torch, lambda: op(y, x, w12, w3), max(3, steps // (4 if tokens > 64 else 1)), warmup)
+        op.destroy()
+        flops, wbytes = 2.0 * tokens * hidden * 3 * di, 2.0 * 3 * hidden * di
+        out["cases"].append({"tokens": tokens, "ms": round(ms, 5), "tflops": round(flops / ms / 1e9, 1),
+                             "weight_gbs": round(wbytes / ms / 1e6, 1)})
+        del x, y
+    return out
+
+
+NEXT_ROWS = {"matmul": only_matmul, "mlp": only_mlp, "rearrange": only_rearrange, "add_rms_norm": only_add_rms_norm, "rope_rearrange": only_rope_rearrange,
              "attention": only_attention}
 
 
@@ -379,6 +495,9 @@ def run_b200(args):
         return
     stream = torch.cuda.current_stream()
     sptr = stream.cuda_stream
+    from operators_b200 import ops as _ops_mod
+
+    device_timeouts_before = _ops_mod.device_timeouts(lib, handle)
 
     def barrier():
         if world > 1:
@@ -427,6 +546,28 @@ def run_b200(args):
     t_end.record(stream)
     barrier()
     ms_per_step = t_begin.elapsed_time(t_end) / args.steps
+
+    # ---- sustained: the same step replayed for at least a second (the K timed steps above last milliseconds and
+    # say nothing about the power-capped state); clocks sampled over this second alone ----
+    sustained = None
+    if args.sustain_seconds > 0:
+        n_sus = max(args.steps, int(args.sustain_seconds * 1e3 / max(ms_per_step, 1e-3)) + 1)
+        sus_clocks = ClockSampler(local)
+        barrier()
+        sus_clocks.start()
+        s_begin, s_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_begin.record(stream)
+        for k in range(n_sus):
+            if graph is not None:
+                graph.replay()
+            else:
+                for _, fn in calls:
+                    fn(sptr)
+        s_end.record(stream)
+        barrier()
+        sus_clk = sus_clocks.stop()
+        sus_ms = s_begin.elapsed_time(s_end) / n_sus
+        sustained = (sus_ms, n_sus, sus_clk)
 
     # ---- the same K steps again with an event after every operator: the per-operator breakdown ----
     # (an event between two launches costs about a microsecond of device time, so these sum to a little more
@@ -500,6 +641,7 @@ def run_b200(args):
     barrier()
 
     # ---- end to end: host buffers in, host results out, every step ----
+    numa = pin_to_gpu_numa_node(torch, local)  # before the pinned buffers are allocated and first touched
     host_in = {k: inputs[k].pin_memory() for k in
                ("rms_x", "rms_w", "rope_t", "rope_pos", "rope_sin", "rope_cos", "gate_up", "add_a", "add_b", "att",
                 "logits", "u")}
@@ -536,14 +678,45 @@ def run_b200(args):
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
-    # ---- vocabulary-sharded sampling (N > 1): local stage, one NCCL all-gather, finishing stage ----
-    sharded_ms = None
+    # ---- N > 1: ONE configuration split over the ranks (strong scaling) ----
+    # rows for RMSNorm (scaled shape) / RoPE / SwiGLU / Add, heads for causal softmax; no collective.  Every rank
+    # times its slice, the slowest rank counts; the full-size time beside it is this rank's own from the pass above.
+    strong = None
+    sharded = None
     if world > 1:
         import torch.distributed as dist
 
         from operators_b200 import ops as _ops
-        from operators_b200.sharding import VocabShardedSampler, vocab_range
+        from operators_b200.sharding import VocabShardedSampler, shard_rows, vocab_range
 
+        t = step.t
+        sl = {k: shard_rows(t[k], world, rank) for k in ("rope_t", "rope_pos", "gate_up", "swi_c", "add_a", "add_b", "add_c", "att")}
+        s_ops = [
+            ("rope", _ops.RoPEOp(lib, handle, sl["rope_t"], sl["rope_pos"], t["rope_sin"], t["rope_cos"]),
+             lambda op: op(sl["rope_t"], sl["rope_pos"], t["rope_sin"], t["rope_cos"], sptr)),
+            ("swiglu", _ops.SwiGLUOp(lib, handle, sl["swi_c"], sl["gate_up"][:, SWI_DI:], sl["gate_up"][:, :SWI_DI]),
+             lambda op: op(sl["swi_c"], sl["gate_up"][:, SWI_DI:], sl["gate_up"][:, :SWI_DI], sptr)),
+            ("add", _ops.AddOp(lib, handle, sl["add_c"], sl["add_a"], sl["add_b"]),
+             lambda op: op(sl["add_c"], sl["add_a"], sl["add_b"], sptr)),
+            ("causal_softmax", _ops.CausalSoftmaxOp(lib, handle, sl["att"]), lambda op: op(sl["att"], sptr)),
+        ]
+        strong_ms = {}
+        for name, op, call in s_ops:
+            for _ in range(3):
+                call(op)
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            for _ in range(args.steps):
+                call(op)
+            a1.record(stream)
+            barrier()
+            strong_ms[name] = a0.elapsed_time(a1) / args.steps
+            op.destroy()
+        strong = strong_ms
+
+        # ---- vocabulary-sharded sampling: index-exact mode (all-to-all of rows, exact kernel, all-gather of the
+        # indices) and fast mode (local candidates, one all-gather, finishing kernel), with a stage breakdown ----
         gsh = torch.Generator().manual_seed(77)  # the same logits on every rank, each keeps its columns
         full = (torch.randn((RS_B, RS_V), generator=gsh) * 3).half()
         ush = torch.rand(RS_B, generator=gsh).to(dev)
@@ -551,28 +724,83 @@ def run_b200(args):
         shard = full[:, b0:e0].contiguous().to(dev)
         out = torch.zeros(RS_B, dtype=torch.int64, device=dev)
         sop = _ops.RandomSampleOp(lib, handle, out[:1], shard[0])
-        sampler = VocabShardedSampler(lib, handle, sop, RS_V, b0, world)
-        for _ in range(3):
-            sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, sptr, check=False)
-        barrier()
-        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s0.record(stream)
-        for _ in range(args.steps):
-            sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, sptr, check=False)
-        s1.record(stream)
-        barrier()
-        sharded_ms = s0.elapsed_time(s1) / args.steps
+        sharded = {}
+        for mode in ("exact", "fast"):
+            sampler = VocabShardedSampler(lib, handle, sop, RS_V, b0, world, mode=mode, rank=rank)
+            for _ in range(3):
+                sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, check=False)
+            barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record(stream)
+            for _ in range(args.steps):
+                sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, check=False)
+            s1.record(stream)
+            barrier()
+            res = {"ms": s0.elapsed_time(s1) / args.steps}
+            # the stages one by one (events between them; a few runs, mean)
+            acc = {}
+            for _ in range(5):
+                sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, check=False, timed=True)
+                torch.cuda.synchronize()
+                evs = sampler.last_events
+                for (_, ea), (nb, eb) in zip(evs, evs[1:]):
+                    acc[nb] = acc.get(nb, 0.0) + ea.elapsed_time(eb) / 5
+            res["stages_ms"] = acc
+            # the whole call as one CUDA graph (collectives included), when the capture works
+            res["ms_graph"] = None
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(stream)
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=side):
+                    sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, check=False)
+                stream.wait_stream(side)
+                gr.replay()
+                barrier()
+                g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                g0.record(stream)
+                for _ in range(args.steps):
+                    gr.replay()
+                g1.record(stream)
+                barrier()
+                res["ms_graph"] = g0.elapsed_time(g1) / args.steps
+            except Exception as exc:  # noqa: BLE001
+                res["graph_error"] = str(exc)[:200]
+                torch.cuda.synchronize()
+            if mode == "exact":
+                res["indices"] = out.cpu().tolist()
+            sharded[mode] = res
+            sampler.destroy()
+        sharded_ms = sharded["exact"]["ms"]
+    else:
+        sharded_ms = None
+
+    device_timeouts_after = _ops_mod.device_timeouts(lib, handle)
 
     # ---- max over ranks ----
-    vals = torch.tensor([ms_per_step, e2e_ms, sharded_ms or 0.0] + [per_op_ms[o] for o in OPS], dtype=torch.float64,
-                        device=dev)
+    extra_names, extra_vals = [], []
+    if sustained is not None:
+        extra_names.append("sustained"), extra_vals.append(sustained[0])
+    if strong is not None:
+        for k, v in strong.items():
+            extra_names.append("strong." + k), extra_vals.append(v)
+    if sharded is not None:
+        for mode, res in sharded.items():
+            extra_names.append("sharded.%s.ms" % mode), extra_vals.append(res["ms"])
+            extra_names.append("sharded.%s.ms_graph" % mode), extra_vals.append(res["ms_graph"] or 0.0)
+            for k, v in res["stages_ms"].items():
+                extra_names.append("sharded.%s.stage.%s" % (mode, k)), extra_vals.append(v)
+    vals = torch.tensor([ms_per_step, e2e_ms, sharded_ms or 0.0] + [per_op_ms[o] for o in OPS] + extra_vals,
+                        dtype=torch.float64, device=dev)
     if world > 1:
         import torch.distributed as dist
 
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
     vals = vals.cpu().tolist()
     ms_per_step, e2e_ms, sharded_ms = vals[0], vals[1], vals[2]
-    per_op_ms = dict(zip(OPS, vals[3:]))
+    own_per_op_ms = dict(per_op_ms)  # this rank's full-size times, the baseline of the strong-scaling speed-ups
+    per_op_ms = dict(zip(OPS, vals[3:3 + len(OPS)]))
+    extra = dict(zip(extra_names, vals[3 + len(OPS):]))
 
     step_bytes = sum(ALGO_BYTES.values())
     peak, peak_kind = measured_peak()
@@ -611,20 +839,52 @@ def run_b200(args):
         "ops": ops_out,
         "sample_tokens_per_s": ops_out["random_sample"]["tokens_per_s"],
         "e2e": {"value": round(step_bytes * world / (e2e_ms * 1e-3) / 1e9, 2), "unit": "GB/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3)},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3), "numa": numa},
         "gpu_launches": step.launches_per_step * args.steps,
         "clocks": clk,
     }
+    if sustained is not None:
+        sus_ms = extra["sustained"]
+        line["sustained"] = {"value": round(step_bytes * world / (sus_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+                             "ms_per_step": round(sus_ms, 4), "steps": sustained[1],
+                             "seconds": round(sus_ms * sustained[1] / 1e3, 2), "clocks": sustained[2]}
+    line["device_timeouts"] = device_timeouts_after - device_timeouts_before
     if world > 1:
-        line["random_sample_vocab_sharded"] = {
-            "ms": round(sharded_ms, 4), "tokens_per_s": round(RS_B / (sharded_ms * 1e-3), 1),
-            "what": "64 rows, vocabulary 128256 split over %d GPUs: local candidates, one NCCL all-gather of "
-                    "%d bytes per rank, finishing kernel" % (world, RS_B * 1056)}
+        # strong scaling: the SAME configuration split over the ranks (rows; heads for causal softmax), slowest rank
+        split = {}
+        for o in ("rope", "swiglu", "add", "causal_softmax"):
+            ms = extra["strong." + o]
+            split[o] = {"ms_split": round(ms, 5), "ms_one_gpu": round(own_per_op_ms[o], 5),
+                        "speedup": round(own_per_op_ms[o] / ms, 2),
+                        "gbs": round(ALGO_BYTES[o] / (ms * 1e-3) / 1e9, 1)}
+        line["strong_scaling"] = {
+            "what": "each BASELINE.json configuration split over %d GPUs (token rows; heads for causal softmax), no "
+                    "collective; ms_split = slowest rank; ms_one_gpu = the whole configuration on rank 0's GPU in the "
+                    "same run.  RMSNorm [16, 2048] (8 KB per GPU at 8 GPUs) and slices that take under ~10 us are "
+                    "launch latency, not bandwidth" % world,
+            "ops": split}
+        rs = {}
+        for mode in ("exact", "fast"):
+            rs[mode] = {"ms": round(extra["sharded.%s.ms" % mode], 4),
+                        "ms_graph": round(extra["sharded.%s.ms_graph" % mode], 4) or None,
+                        "tokens_per_s": round(RS_B / (extra["sharded.%s.ms" % mode] * 1e-3), 1),
+                        "stages_ms": {k.split(".stage.")[1]: round(v, 4) for k, v in extra.items()
+                                      if k.startswith("sharded.%s.stage." % mode)}}
+            if "graph_error" in sharded[mode]:
+                rs[mode]["graph_error"] = sharded[mode]["graph_error"]
+        rs["exact"]["what"] = ("64 rows, vocabulary 128256 split over %d GPUs; default mode, index-exact: one NCCL "
+                               "all-to-all hands every rank %d whole rows (%d bytes received per rank), the exact "
+                               "kernel samples them, one all-gather returns the indices" %
+                               (world, RS_B // world, RS_B // world * RS_V * 2 * (world - 1) // world))
+        rs["fast"]["what"] = ("local candidate kernel, one NCCL all-gather of %d bytes per rank, finishing kernel; "
+                              "denominator correctly rounded instead of sequential" % (RS_B * 1056))
+        rs["one_gpu_unsharded_ms"] = round(own_per_op_ms["random_sample"], 4)
+        line["random_sample_vocab_sharded"] = rs
     sw_ms = per_op_ms["swiglu"]
     ach = ALGO_BYTES["swiglu"] / (sw_ms * 1e-3) / 1e9
     line["roofline"] = {"kernel": "swiglu_vec8_kernel", "bound": "hbm", "achieved": round(ach, 1), "peak": peak,
                         "peak_kind": "of " + peak_kind, "unit": "GB/s", "frac": round(ach / peak, 4),
-                        "traffic": NCU_TRAFFIC_BYTES["swiglu"]}
+                        "traffic": ncu_traffic_bytes("swiglu_vec8_kernel_8192x14336.md")}
     if world == 1 and not args.only:
         # the operators built either side of the step (not part of `value`): each timed alone after the step's runs
         line["next_rows"] = {name: fn(lib, handle, dev, 20, 3) for name, fn in NEXT_ROWS.items()}
@@ -788,8 +1048,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
+    ap.add_argument("--sustain-seconds", type=float, default=1.0,
+                    help="replay the step for this long after the timed K steps and report it as `sustained`")
     ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of a CUDA graph of the step")
-    ap.add_argument("--only", choices=OPS + ["rearrange", "add_rms_norm", "rope_rearrange", "attention"],
+    ap.add_argument("--only", choices=OPS + list(NEXT_ROWS),
                     help="launch a single operator at its configuration (for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

@@ -16,7 +16,8 @@
  * library's own choice.
  *   family 0 (RoPE):          1 = the strided kernel instead of the bulk-copy pipeline
  *   family 1 (random sample): 1 = the global-memory kernel instead of the shared-memory cluster kernel
- *   family 2 (attention):     1 = the multiply-add kernels instead of the tensor-core kernels
+ *   family 2 (attention):     1 = the multiply-add kernels instead of the tensor-core kernels,
+ *                             2 = the row-tile mma.sync kernels also where the tcgen05 path (several new tokens) applies
  *   family 3 (matmul):        1 = the CUDA-core kernel instead of the tcgen05 kernel
  * Returns STATUS_BAD_PARAM for an unknown family or a negative variant.
  */

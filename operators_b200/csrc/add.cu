@@ -1,4 +1,5 @@
-// Add: c = a + b with numpy-style broadcasting, contiguous fp16 / fp32 tensors.
+// Add: c = a + b with numpy-style broadcasting, contiguous fp16 / fp32 tensors (and bf16, an extension: see
+// StoreType in common.cuh).
 //
 // Replaces reference src/ops/add/cuda/add.cu:12-116 and src/ops/add/cuda/add.cc:
 // 5-73 behind include/ops/add/add.h.  Arithmetic follows the CPU backend
@@ -38,14 +39,15 @@ struct AddDesc {
     Device device;
     int device_id;
     int sm_count;
-    bool is_f16;
+    int dt;// StoreType
     bool broadcast;
     uint64_t total;// elements of c
     BroadcastDims dims;
 };
 
-template<bool F16>
+template<int DT>
 __device__ __forceinline__ uint4 add_vec(uint4 x, uint4 y) {
+    constexpr bool F16 = DT != kF32;// 16-bit storage
     uint4 r;
     const uint32_t *px = reinterpret_cast<const uint32_t *>(&x);
     const uint32_t *py = reinterpret_cast<const uint32_t *>(&y);
@@ -53,8 +55,8 @@ __device__ __forceinline__ uint4 add_vec(uint4 x, uint4 y) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         if (F16) {
-            float2 fx = unpack2(px[k]), fy = unpack2(py[k]);
-            pr[k] = pack2_ref(__fadd_rn(fx.x, fy.x), __fadd_rn(fx.y, fy.y));
+            float2 fx = unpack2_t<DT>(px[k]), fy = unpack2_t<DT>(py[k]);
+            pr[k] = pack2_t<DT>(__fadd_rn(fx.x, fy.x), __fadd_rn(fx.y, fy.y));
         } else {
             pr[k] = __float_as_uint(__fadd_rn(__uint_as_float(px[k]), __uint_as_float(py[k])));
         }
@@ -62,9 +64,10 @@ __device__ __forceinline__ uint4 add_vec(uint4 x, uint4 y) {
     return r;
 }
 
-template<bool F16>
+template<int DT>
 __global__ void __launch_bounds__(kThreads)
     add_flat_kernel(void *c, const void *a, const void *b, uint64_t total_vecs, uint64_t total) {
+    constexpr bool F16 = DT != kF32;
     const uint4 *av = reinterpret_cast<const uint4 *>(a);
     const uint4 *bv = reinterpret_cast<const uint4 *>(b);
     uint4 *cv = reinterpret_cast<uint4 *>(c);
@@ -82,7 +85,7 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
             const uint64_t v = base + (uint64_t) u * kThreads;
-            if (v < total_vecs) st_stream(cv + v, add_vec<F16>(x[u], y[u]));
+            if (v < total_vecs) st_stream(cv + v, add_vec<DT>(x[u], y[u]));
         }
     }
     // Fewer than one vector of elements may remain at the end.
@@ -92,8 +95,8 @@ __global__ void __launch_bounds__(kThreads)
         const uint64_t i = done + threadIdx.x;
         if (F16) {
             auto *cp = reinterpret_cast<uint16_t *>(c);
-            cp[i] = f32_to_f16_ref(__fadd_rn(f16_to_f32(reinterpret_cast<const uint16_t *>(a)[i]),
-                                             f16_to_f32(reinterpret_cast<const uint16_t *>(b)[i])));
+            cp[i] = store16<DT>(__fadd_rn(load16<DT>(reinterpret_cast<const uint16_t *>(a)[i]),
+                                          load16<DT>(reinterpret_cast<const uint16_t *>(b)[i])));
         } else {
             reinterpret_cast<float *>(c)[i] =
                 __fadd_rn(reinterpret_cast<const float *>(a)[i], reinterpret_cast<const float *>(b)[i]);
@@ -103,9 +106,10 @@ __global__ void __launch_bounds__(kThreads)
 
 // Any alignment and any broadcast pattern: one element per thread per step,
 // operand offsets rebuilt from the collapsed multi-index.
-template<bool F16, bool FLAT>
+template<int DT, bool FLAT>
 __global__ void __launch_bounds__(kThreads)
     add_general_kernel(void *c, const void *a, const void *b, uint64_t total, BroadcastDims dims) {
+    constexpr bool F16 = DT != kF32;
     for (uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x; i < total; i += (uint64_t) gridDim.x * kThreads) {
         uint64_t rem = i;
         int64_t oa = FLAT ? (int64_t) i : 0, ob = oa;
@@ -121,8 +125,8 @@ __global__ void __launch_bounds__(kThreads)
         }
         if (F16) {
             reinterpret_cast<uint16_t *>(c)[i] =
-                f32_to_f16_ref(__fadd_rn(f16_to_f32(reinterpret_cast<const uint16_t *>(a)[oa]),
-                                         f16_to_f32(reinterpret_cast<const uint16_t *>(b)[ob])));
+                store16<DT>(__fadd_rn(load16<DT>(reinterpret_cast<const uint16_t *>(a)[oa]),
+                                      load16<DT>(reinterpret_cast<const uint16_t *>(b)[ob])));
         } else {
             reinterpret_cast<float *>(c)[i] =
                 __fadd_rn(reinterpret_cast<const float *>(a)[oa], reinterpret_cast<const float *>(b)[ob]);
@@ -143,9 +147,10 @@ struct VecDims {
     bool a_inner, b_inner;// operand spans the innermost axis
 };
 
-template<bool F16>
+template<int DT>
 __global__ void __launch_bounds__(kThreads)
     add_bcast_vec_kernel(void *c, const void *a, const void *b, uint32_t total_vecs, VecDims dims) {
+    constexpr bool F16 = DT != kF32;
     constexpr int V = F16 ? 8 : 4;
     using E = typename std::conditional<F16, uint16_t, uint32_t>::type;
     const E *ae = reinterpret_cast<const E *>(a), *be = reinterpret_cast<const E *>(b);
@@ -182,7 +187,7 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
         const uint32_t v = base + u * kThreads;
-        if (v < total_vecs) st_stream(cv + v, add_vec<F16>(x[u], y[u]));
+        if (v < total_vecs) st_stream(cv + v, add_vec<DT>(x[u], y[u]));
     }
 }
 
@@ -224,7 +229,7 @@ INFINIOP_API infiniopStatus_t infiniopCreateAddDescriptor(infiniopHandle_t handl
     // Same checks, same order, same codes as reference add.cc:11-23.
     if (!valid_broadcast(a, b, c)) return STATUS_BAD_TENSOR_SHAPE;
     if (!contiguous(a) || !contiguous(b) || !contiguous(c)) return STATUS_BAD_TENSOR_STRIDES;
-    if (!dt_eq(c->dt, F16) && !dt_eq(c->dt, F32)) return STATUS_BAD_TENSOR_DTYPE;
+    if (store_type_of(c->dt) < 0) return STATUS_BAD_TENSOR_DTYPE;// fp16, fp32 (reference) or bf16 (extension)
     if (!dt_eq(c->dt, a->dt) || !dt_eq(c->dt, b->dt)) return STATUS_BAD_TENSOR_DTYPE;
 
     const uint64_t nd = c->ndim;
@@ -241,7 +246,7 @@ INFINIOP_API infiniopStatus_t infiniopCreateAddDescriptor(infiniopHandle_t handl
     d->device = DevNvGpu;
     d->device_id = h->device_id;
     d->sm_count = h->sm_count;
-    d->is_f16 = dt_eq(c->dt, F16);
+    d->dt = store_type_of(c->dt);
     d->broadcast = broadcast;
     d->total = total;
     d->dims.ndim = 0;
@@ -293,22 +298,20 @@ INFINIOP_API infiniopStatus_t infiniopAdd(infiniopAddDescriptor_t desc, void *c,
     auto st = reinterpret_cast<cudaStream_t>(stream);
 
     if (!d->broadcast && aligned16(c) && aligned16(a) && aligned16(b)) {
-        const uint64_t per_vec = d->is_f16 ? 8 : 4;
+        const uint64_t per_vec = d->dt != kF32 ? 8 : 4;
         const uint64_t vecs = d->total / per_vec;
         const uint64_t tiles = (vecs + kThreads * kUnroll - 1) / (kThreads * kUnroll);
         if (tiles > 0x7FFFFFFFull) return STATUS_BAD_TENSOR_SHAPE;// > 2^41 elements
         const uint64_t grid = tiles == 0 ? 1 : tiles;
-        if (d->is_f16) {
-            add_flat_kernel<true><<<(uint32_t) grid, kThreads, 0, st>>>(c, a, b, vecs, d->total);
-        } else {
-            add_flat_kernel<false><<<(uint32_t) grid, kThreads, 0, st>>>(c, a, b, vecs, d->total);
-        }
+        if (d->dt == kF16) add_flat_kernel<kF16><<<(uint32_t) grid, kThreads, 0, st>>>(c, a, b, vecs, d->total);
+        else if (d->dt == kBF16) add_flat_kernel<kBF16><<<(uint32_t) grid, kThreads, 0, st>>>(c, a, b, vecs, d->total);
+        else add_flat_kernel<kF32><<<(uint32_t) grid, kThreads, 0, st>>>(c, a, b, vecs, d->total);
         return check_launch("add");
     }
     if (d->broadcast && d->dims.ndim >= 1 && aligned16(c) && aligned16(a) && aligned16(b)) {
         const BroadcastDims &bd = d->dims;
         const int in = bd.ndim - 1;
-        const uint32_t V = d->is_f16 ? 8u : 4u;
+        const uint32_t V = d->dt != kF32 ? 8u : 4u;
         bool ok = bd.shape[in] % V == 0 && (bd.sa[in] == 0 || bd.sa[in] == 1) && (bd.sb[in] == 0 || bd.sb[in] == 1) &&
                   d->total / V <= 0xFFFFFFFFull;
         VecDims vd;
@@ -326,8 +329,9 @@ INFINIOP_API infiniopStatus_t infiniopAdd(infiniopAddDescriptor_t desc, void *c,
         if (ok) {
             const uint32_t vecs = (uint32_t) (d->total / V);
             const uint32_t tiles = (vecs + kThreads * kUnroll - 1) / (kThreads * kUnroll);
-            if (d->is_f16) add_bcast_vec_kernel<true><<<tiles, kThreads, 0, st>>>(c, a, b, vecs, vd);
-            else add_bcast_vec_kernel<false><<<tiles, kThreads, 0, st>>>(c, a, b, vecs, vd);
+            if (d->dt == kF16) add_bcast_vec_kernel<kF16><<<tiles, kThreads, 0, st>>>(c, a, b, vecs, vd);
+            else if (d->dt == kBF16) add_bcast_vec_kernel<kBF16><<<tiles, kThreads, 0, st>>>(c, a, b, vecs, vd);
+            else add_bcast_vec_kernel<kF32><<<tiles, kThreads, 0, st>>>(c, a, b, vecs, vd);
             return check_launch("add");
         }
     }
@@ -337,11 +341,13 @@ INFINIOP_API infiniopStatus_t infiniopAdd(infiniopAddDescriptor_t desc, void *c,
     if (blocks > cap) blocks = cap;
     const uint32_t g = (uint32_t) blocks;
     if (d->broadcast) {
-        if (d->is_f16) add_general_kernel<true, false><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
-        else add_general_kernel<false, false><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
+        if (d->dt == kF16) add_general_kernel<kF16, false><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
+        else if (d->dt == kBF16) add_general_kernel<kBF16, false><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
+        else add_general_kernel<kF32, false><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
     } else {
-        if (d->is_f16) add_general_kernel<true, true><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
-        else add_general_kernel<false, true><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
+        if (d->dt == kF16) add_general_kernel<kF16, true><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
+        else if (d->dt == kBF16) add_general_kernel<kBF16, true><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
+        else add_general_kernel<kF32, true><<<g, kThreads, 0, st>>>(c, a, b, d->total, d->dims);
     }
     return check_launch("add");
 }

@@ -35,6 +35,7 @@
 // Prefill (many query rows) runs through the same kernels one row tile at a
 // time, re-reading K and V per tile from L2: correct, not tuned; a tensor-core
 // kernel is the next step for it.
+#include "attention_prefill.cuh"
 #include "common.cuh"
 
 #include <cmath>
@@ -62,6 +63,8 @@ struct AttnDesc {
     bool strides_vec;             // every stride a multiple of 8 elements and dh % 8 == 0
     uint32_t score_pitch;         // splits * chunk: tokens per score row in the workspace
     uint64_t ws_ml, ws_acc, ws_scores, ws_bytes;// workspace: counters at 0, then the parts named here
+    AttnPrefill *prefill;         // tensor-core path for calls with several new tokens, or null
+    uint64_t prefill_ws_bytes;
 };
 
 struct AttnArgs {
@@ -885,6 +888,14 @@ INFINIOP_API infiniopStatus_t infiniopCreateAttentionDescriptor(infiniopHandle_t
     d->ws_acc = d->ws_ml + pad(slots * sizeof(float2));
     d->ws_scores = d->ws_acc + pad(slots * dh * sizeof(float));
     d->ws_bytes = d->ws_scores + pad(tiles * d->rt * (uint64_t) d->score_pitch * sizeof(uint16_t));
+    // several new tokens per q head: the products go to the tensor-core matmul (attention_prefill.cu)
+    d->prefill = nullptr;
+    d->prefill_ws_bytes = 0;
+    if (seq >= 8 && d->strides_vec && total > 0) {
+        const AttnPrefillShape shape{d->nh, d->group, d->seq, d->dh, d->total, d->q_s0, d->q_s1, d->kc_s0, d->kc_s1, d->vc_s0, d->vc_s1};
+        d->prefill = attn_prefill_create(handle, shape, &d->prefill_ws_bytes);
+        if (d->prefill != nullptr && d->prefill_ws_bytes > d->ws_bytes) d->ws_bytes = d->prefill_ws_bytes;
+    }
     *desc_ptr = reinterpret_cast<infiniopAttentionDescriptor_t>(d);
     return STATUS_SUCCESS;
 }
@@ -939,6 +950,10 @@ INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t de
         const infiniopStatus_t status = check_launch("attention kv append");
         if (status != STATUS_SUCCESS) return status;
     }
+    // several new tokens: scores, softmax and values as three tensor-core / streaming launches
+    if (d->prefill != nullptr && vec && kernel_choice(kFamilyAttention) == 0) {
+        return attn_prefill_run(d->prefill, workspace, out, q, k_cache, v_cache, st);
+    }
     // the multiply-add kernels serve unaligned layouts and head sizes above 128 (and every layout when
     // infiniopExtSelectKernel asked for them)
     if (vec && d->dh <= 128 && kernel_choice(kFamilyAttention) != 1) return launch_mma_rows(d, a, st);
@@ -947,6 +962,8 @@ INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t de
 
 INFINIOP_API infiniopStatus_t infiniopDestroyAttentionDescriptor(infiniopAttentionDescriptor_t desc) {
     if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
-    delete reinterpret_cast<AttnDesc *>(desc);
+    auto *d = reinterpret_cast<AttnDesc *>(desc);
+    attn_prefill_destroy(d->prefill);
+    delete d;
     return STATUS_SUCCESS;
 }

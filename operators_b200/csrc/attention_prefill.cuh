@@ -1,0 +1,21 @@
+// Interface between the attention entry points (attention.cu) and the tensor-core path for calls with several
+// new tokens (attention_prefill.cu).
+#pragma once
+#include "matmul.cuh"
+
+namespace b200 {
+
+struct AttnPrefillShape {
+    uint32_t nh, group, seq, dh, total;
+    int64_t q_s0, q_s1, kc_s0, kc_s1, vc_s0, vc_s1;// element strides of q [nh, seq, dh] and the caches [nkvh, buf, dh]
+};
+
+struct AttnPrefill;
+// nullptr when the layouts cannot go through TMA descriptors (the caller keeps its other kernels).
+AttnPrefill *attn_prefill_create(infiniopHandle_t handle, const AttnPrefillShape &shape, uint64_t *workspace_bytes);
+// After the new k and v rows are in the caches.  `workspace` holds *workspace_bytes of attn_prefill_create.
+infiniopStatus_t attn_prefill_run(AttnPrefill *p, void *workspace, void *out, const void *q, const void *k_cache,
+                                  const void *v_cache, cudaStream_t stream);
+void attn_prefill_destroy(AttnPrefill *p);
+
+}// namespace b200

@@ -29,6 +29,7 @@ struct CausalSoftmaxDesc {
     int sm_count;
     uint64_t batch, seq_len, total;
     int64_t stride_b, stride_i;
+    int dt;// kF16, or kBF16 (an extension: bf16 storage, same fp32 arithmetic)
 };
 
 // Number of visible columns of query row i (at least 1: column 0 always is).
@@ -50,7 +51,16 @@ __device__ __forceinline__ uint64_t visible_cols(uint64_t i, uint64_t seq_len, u
 // are launched with more than 512 threads must fit 64 registers per thread.
 enum RowOwner { WARP_ROW = 0, CTA_ROW = 1, CLUSTER_ROW = 2 };
 
-template<int VPT, int OWNER, int MAXT>
+// packed maximum of two 16-bit pairs
+template<int DT>
+__device__ __forceinline__ uint32_t max2_packed(uint32_t a, uint32_t b) {
+    uint32_t r;
+    if (DT == kBF16) asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    else asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+template<int VPT, int OWNER, int MAXT, int DT>
 __global__ void __launch_bounds__(MAXT)
     causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total, uint32_t vecs,
                                int64_t stride_b, int64_t stride_i, FastDiv seq_div) {
@@ -64,7 +74,8 @@ __global__ void __launch_bounds__(MAXT)
     const uint64_t row0 = OWNER == WARP_ROW ? (uint64_t) blockIdx.x * rows_per_cta + (threadIdx.x >> 5)
                                             : (uint64_t) (blockIdx.x / cl);
     const uint64_t row_step = OWNER == WARP_ROW ? (uint64_t) gridDim.x * rows_per_cta : (uint64_t) (gridDim.x / cl);
-    constexpr uint32_t kNegInf2 = 0xFC00FC00u;// two fp16 -inf
+    constexpr uint32_t kNegInf1 = DT == kBF16 ? 0xFF80u : 0xFC00u;// -inf
+    constexpr uint32_t kNegInf2 = kNegInf1 * 0x00010001u;          // two of them
 
     for (uint64_t row = row0; row < rows; row += row_step) {
         uint64_t b, i;
@@ -85,7 +96,7 @@ __global__ void __launch_bounds__(MAXT)
             if (j < vecs && j * 8 < vis) raw[u] = ld_stream(yr + (uint64_t) j * 8);
             else raw[u] = make_uint4(kNegInf2, kNegInf2, kNegInf2, kNegInf2);// masked: exp -> 0, output 0
         }
-        __half2 m2 = __halves2half2(__ushort_as_half((unsigned short) 0xFC00), __ushort_as_half((unsigned short) 0xFC00));
+        uint32_t m2 = kNegInf2;
 #pragma unroll
         for (int u = 0; u < VPT; ++u) {
             const uint32_t j = t + u * group;
@@ -93,14 +104,15 @@ __global__ void __launch_bounds__(MAXT)
             if (j * 8 < vis && j * 8 + 8 > vis) {// the one vector that straddles the mask boundary
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    if (j * 8 + 2 * k >= vis) p[k] = (p[k] & 0xFFFF0000u) | 0xFC00u;
-                    if (j * 8 + 2 * k + 1 >= vis) p[k] = (p[k] & 0x0000FFFFu) | 0xFC000000u;
+                    if (j * 8 + 2 * k >= vis) p[k] = (p[k] & 0xFFFF0000u) | kNegInf1;
+                    if (j * 8 + 2 * k + 1 >= vis) p[k] = (p[k] & 0x0000FFFFu) | (kNegInf1 << 16);
                 }
             }
 #pragma unroll
-            for (int k = 0; k < 4; ++k) m2 = __hmax2(m2, *reinterpret_cast<const __half2 *>(&p[k]));
+            for (int k = 0; k < 4; ++k) m2 = max2_packed<DT>(m2, p[k]);
         }
-        float m = fmaxf(__low2float(m2), __high2float(m2));
+        const float2 mm = unpack2_t<DT>(m2);
+        float m = fmaxf(mm.x, mm.y);
         if (OWNER == CLUSTER_ROW) m = cluster_reduce<true>(m, red_m, &part_m, cl);
         else m = OWNER == CTA_ROW ? cta_reduce_alt<true>(m, red_m) : warp_max(m);
         // exp(x - m) = 2^(x*log2e - m*log2e); the rounding of m*log2e is common to
@@ -112,7 +124,7 @@ __global__ void __launch_bounds__(MAXT)
             const uint32_t *p = reinterpret_cast<const uint32_t *>(&raw[u]);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const float2 f = unpack2(p[k]);
+                const float2 f = unpack2_t<DT>(p[k]);
                 s += fast_exp2(fmaf(f.x, kLog2e, mk));
                 s += fast_exp2(fmaf(f.y, kLog2e, mk));
             }
@@ -129,11 +141,12 @@ __global__ void __launch_bounds__(MAXT)
                 uint32_t *po = reinterpret_cast<uint32_t *>(&out);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float2 f = unpack2(p[k]);
+                    const float2 f = unpack2_t<DT>(p[k]);
                     const float q0 = __fmul_rn(fast_exp2(fmaf(f.x, kLog2e, mk)), r);
                     const float q1 = __fmul_rn(fast_exp2(fmaf(f.y, kLog2e, mk)), r);
                     // quotients lie in [0, 1]: the packed truncating convert needs no range check
-                    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(po[k]) : "f"(q1), "f"(q0));
+                    if (DT == kBF16) po[k] = (__float_as_uint(q0) >> 16) | (__float_as_uint(q1) & 0xFFFF0000u);
+                    else asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(po[k]) : "f"(q1), "f"(q0));
                 }
                 st_stream(yr + (uint64_t) j * 8, out);
             }
@@ -145,6 +158,7 @@ __global__ void __launch_bounds__(MAXT)
 
 // Any alignment, any column stride, any row length: one CTA per row, three
 // passes (max / sum / write), the later ones served by L2.
+template<int DT>
 __global__ void causal_softmax_generic_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total,
                                               int64_t stride_b, int64_t stride_i) {
     __shared__ float red[32];
@@ -153,18 +167,18 @@ __global__ void causal_softmax_generic_kernel(uint16_t *y, uint64_t rows, uint64
         uint16_t *yr = y + (int64_t) b * stride_b + (int64_t) i * stride_i;
         const uint64_t vis = visible_cols(i, seq_len, total);
         float m = -INFINITY;
-        for (uint64_t j = threadIdx.x; j < vis; j += blockDim.x) m = fmaxf(m, f16_to_f32(yr[j]));
+        for (uint64_t j = threadIdx.x; j < vis; j += blockDim.x) m = fmaxf(m, load16<DT>(yr[j]));
         m = cta_reduce<true>(m, red);
         float s = 0.f;
-        for (uint64_t j = threadIdx.x; j < vis; j += blockDim.x) s += expf(__fsub_rn(f16_to_f32(yr[j]), m));
+        for (uint64_t j = threadIdx.x; j < vis; j += blockDim.x) s += expf(__fsub_rn(load16<DT>(yr[j]), m));
         s = cta_reduce<false>(s, red);
         const float r = __frcp_rn(s);
         for (uint64_t j = threadIdx.x; j < total; j += blockDim.x) {
             uint16_t out = 0;
             if (j < vis) {
-                const float e = expf(__fsub_rn(f16_to_f32(yr[j]), m));
+                const float e = expf(__fsub_rn(load16<DT>(yr[j]), m));
                 const float q0 = __fmul_rn(e, r);
-                out = f32_to_f16_ref(fmaf(fmaf(-q0, s, e), r, q0));
+                out = store16<DT>(fmaf(fmaf(-q0, s, e), r, q0));
             }
             yr[j] = out;
         }
@@ -172,7 +186,7 @@ __global__ void causal_softmax_generic_kernel(uint16_t *y, uint64_t rows, uint64
     }
 }
 
-template<int VPT>
+template<int VPT, int DT>
 void launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, uint16_t *y,
                  cudaStream_t st) {
     const uint64_t rows = d->batch * d->seq_len;
@@ -182,23 +196,23 @@ void launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uin
         const uint32_t grid = (uint32_t) (rows < cap ? rows : cap) * cl;
         if (cl > 1) {
             if constexpr (VPT == 4) {// clusters always hold four vectors per thread
-                launch_cluster(causal_softmax_regs_kernel<4, CLUSTER_ROW, 1024>, grid, threads, cl, st, y, rows,
+                launch_cluster(causal_softmax_regs_kernel<4, CLUSTER_ROW, 1024, DT>, grid, threads, cl, st, y, rows,
                                d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
             }
         } else if (threads > 512) {
             if constexpr (VPT <= 4) {// eight vectors per thread never need more than 512 threads
-                causal_softmax_regs_kernel<VPT, CTA_ROW, 1024>
+                causal_softmax_regs_kernel<VPT, CTA_ROW, 1024, DT>
                     <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
             }
         } else {
-            causal_softmax_regs_kernel<VPT, CTA_ROW, 512>
+            causal_softmax_regs_kernel<VPT, CTA_ROW, 512, DT>
                 <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
         }
     } else {
         const uint64_t ctas = (rows + 7) / 8;
         const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-        causal_softmax_regs_kernel<VPT, WARP_ROW, 256>
+        causal_softmax_regs_kernel<VPT, WARP_ROW, 256, DT>
             <<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
     }
 }
@@ -214,7 +228,7 @@ INFINIOP_API infiniopStatus_t infiniopCreateCausalSoftmaxDescriptor(infiniopHand
     // Checks, order and codes of reference causal_softmax.cc:8-24.
     const uint64_t ndim = y->ndim;
     if (ndim != 2 && ndim != 3) return STATUS_BAD_TENSOR_SHAPE;
-    if (!dt_eq(y->dt, F16)) return STATUS_BAD_TENSOR_DTYPE;
+    if (!dt_eq(y->dt, F16) && !dt_eq(y->dt, BF16)) return STATUS_BAD_TENSOR_DTYPE;// bf16: an extension
     if (y->strides[ndim - 1] != 1) return STATUS_BAD_TENSOR_STRIDES;
     auto *h = reinterpret_cast<Handle *>(handle);
     auto *d = new (std::nothrow) CausalSoftmaxDesc{DevNvGpu,
@@ -224,7 +238,8 @@ INFINIOP_API infiniopStatus_t infiniopCreateCausalSoftmaxDescriptor(infiniopHand
                                                    y->shape[ndim - 2],
                                                    y->shape[ndim - 1],
                                                    ndim == 3 ? y->strides[0] : 0,
-                                                   y->strides[ndim - 2]};
+                                                   y->strides[ndim - 2],
+                                                   store_type_of(y->dt)};
     if (d == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
     *desc_ptr = reinterpret_cast<infiniopCausalSoftmaxDescriptor_t>(d);
     return STATUS_SUCCESS;
@@ -274,17 +289,27 @@ INFINIOP_API infiniopStatus_t infiniopCausalSoftmax(infiniopCausalSoftmaxDescrip
             const RowLaunch shape = row_launch_shape(vecs, big ? (vecs >= 2048 ? 8 : 4) : 1);
             vpt = shape.vpt, threads = shape.threads, cl = shape.cl;
         }
-        switch (vpt) {
-            case 1: launch_regs<1>(d, cta_row, threads, cl, vecs, y, st); break;
-            case 2: launch_regs<2>(d, cta_row, threads, cl, vecs, y, st); break;
-            case 4: launch_regs<4>(d, cta_row, threads, cl, vecs, y, st); break;
-            default: launch_regs<8>(d, cta_row, threads, cl, vecs, y, st); break;
+        if (d->dt == kBF16) {
+            switch (vpt) {
+                case 1: launch_regs<1, kBF16>(d, cta_row, threads, cl, vecs, y, st); break;
+                case 2: launch_regs<2, kBF16>(d, cta_row, threads, cl, vecs, y, st); break;
+                case 4: launch_regs<4, kBF16>(d, cta_row, threads, cl, vecs, y, st); break;
+                default: launch_regs<8, kBF16>(d, cta_row, threads, cl, vecs, y, st); break;
+            }
+        } else {
+            switch (vpt) {
+                case 1: launch_regs<1, kF16>(d, cta_row, threads, cl, vecs, y, st); break;
+                case 2: launch_regs<2, kF16>(d, cta_row, threads, cl, vecs, y, st); break;
+                case 4: launch_regs<4, kF16>(d, cta_row, threads, cl, vecs, y, st); break;
+                default: launch_regs<8, kF16>(d, cta_row, threads, cl, vecs, y, st); break;
+            }
         }
         return check_launch("causal_softmax");
     }
     const uint64_t cap = (uint64_t) d->sm_count * 8;
     const uint32_t grid = (uint32_t) (rows < cap ? rows : cap);
-    causal_softmax_generic_kernel<<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, d->stride_b, d->stride_i);
+    auto *generic = d->dt == kBF16 ? causal_softmax_generic_kernel<kBF16> : causal_softmax_generic_kernel<kF16>;
+    generic<<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, d->stride_b, d->stride_i);
     return check_launch("causal_softmax");
 }
 

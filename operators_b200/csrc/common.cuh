@@ -112,6 +112,40 @@ __device__ __forceinline__ float2 unpack2(uint32_t w) {
     return __half22float2(*reinterpret_cast<const __half2 *>(&w));
 }
 
+// ---- storage types -------------------------------------------------------------------------------------
+// fp16 is the reference's type.  bf16 storage is an extension of this library (the reference only carries the
+// BF16 layout constant, include/data_type.h:44): the same arithmetic in fp32 with bf16 decode (exact: the upper
+// half of the fp32 pattern) and encode by TRUNCATION of the mantissa, the counterpart of the reference's
+// truncating fp16 rule; NaN stays NaN (sign | 0x7FC0).
+enum StoreType { kF32 = 0, kF16 = 1, kBF16 = 2 };
+
+static inline int store_type_of(DataLayout d) { return dt_eq(d, F16) ? kF16 : dt_eq(d, BF16) ? kBF16 : dt_eq(d, F32) ? kF32 : -1; }
+
+__device__ __forceinline__ uint16_t f32_to_bf16_trunc(float v) {
+    const uint32_t u = __float_as_uint(v);
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t) (((u >> 16) & 0x8000u) | 0x7FC0u);
+    return (uint16_t) (u >> 16);
+}
+template<int DT>
+__device__ __forceinline__ float load16(uint16_t h) {
+    return DT == kBF16 ? __uint_as_float((uint32_t) h << 16) : f16_to_f32(h);
+}
+template<int DT>
+__device__ __forceinline__ uint16_t store16(float v) {
+    return DT == kBF16 ? f32_to_bf16_trunc(v) : f32_to_f16_ref(v);
+}
+// two elements per 32-bit word
+template<int DT>
+__device__ __forceinline__ float2 unpack2_t(uint32_t w) {
+    if (DT == kBF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+    return unpack2(w);
+}
+template<int DT>
+__device__ __forceinline__ uint32_t pack2_t(float lo, float hi) {
+    if (DT == kBF16) return (uint32_t) f32_to_bf16_trunc(lo) | ((uint32_t) f32_to_bf16_trunc(hi) << 16);
+    return pack2_ref(lo, hi);
+}
+
 // 2^x by the special-function unit (ex2.approx: relative error about 2^-22,
 // -inf -> +0, results below 2^-126 flush to zero).
 __device__ __forceinline__ float fast_exp2(float x) {

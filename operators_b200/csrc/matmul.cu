@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(256)
     __shared__ float sa[kSimtK][kSimtTile + 1], sb[kSimtK][kSimtTile + 1];
     const uint32_t batch = blockIdx.z;
     const uint32_t m0 = blockIdx.y * kSimtTile, n0 = blockIdx.x * kSimtTile;
-    const T *ab = a + (int64_t) batch * va.batch_stride, *bb = b + (int64_t) batch * vb.batch_stride;
+    const T *ab = a + (int64_t) (batch / va.batch_div) * va.batch_stride, *bb = b + (int64_t) (batch / vb.batch_div) * vb.batch_stride;
     T *cb = c + (int64_t) batch * vc.batch_stride;
     const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;// thread computes rows ty*4.., columns tx*4..
     float acc[4][4] = {};
@@ -135,7 +135,9 @@ bool operand_from_view(TcOperand &o, const MatView &v, bool rows_are_view_rows, 
     const uint32_t rows = rows_are_view_rows ? v.rows : v.cols, k = rows_are_view_rows ? v.cols : v.rows;
     const int64_t row_stride = rows_are_view_rows ? v.row_stride : v.col_stride;
     const int64_t k_stride = rows_are_view_rows ? v.col_stride : v.row_stride;
-    o.rows = rows, o.k = k, o.batch = batch, o.batch_stride = v.batch > 1 ? v.batch_stride : 0;
+    o.rows = rows, o.k = k, o.batch = v.batch, o.batch_stride = v.batch > 1 ? v.batch_stride : 0;
+    o.batch_div = v.batch_div;
+    (void) batch;
     if (k_stride == 1 && (rows == 1 || (row_stride % 8 == 0 && row_stride >= (int64_t) k))) {
         o.mn_major = 0, o.ld = row_stride;
     } else if (row_stride == 1 && (k == 1 || (k_stride % 8 == 0 && k_stride >= (int64_t) rows))) {
@@ -194,7 +196,7 @@ namespace b200 {
 
 infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTensorDescriptor_t c_desc, float alpha,
                                     infiniopTensorDescriptor_t a_desc, infiniopTensorDescriptor_t b_desc, float beta,
-                                    int epilogue_mode) {
+                                    int epilogue_mode, uint32_t b_batch_div) {
     if (c_desc == nullptr || a_desc == nullptr || b_desc == nullptr) return STATUS_BAD_PARAM;
     // dtype first, then the layout checks in the reference's order a, b, c (matmul_cuda.cc:12-20, blas.h:19-48)
     const bool f16 = dt_eq(c_desc->dt, F16), f32 = dt_eq(c_desc->dt, F32);
@@ -204,6 +206,7 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
     for (int i = 0; i < 3; ++i) {
         infiniopTensorDescriptor_t t = descs[i];
         MatView &v = views[i];
+        v.batch_div = 1;
         if (t->ndim == 2) {
             v.batch = 1, v.batch_stride = 0;
             v.rows = (uint32_t) t->shape[0], v.cols = (uint32_t) t->shape[1];
@@ -224,7 +227,13 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
     const bool swiglu = epilogue_mode == tc::kEpiSwiGLUCols;// c holds up * silu(gate): half of b's columns
     if (swiglu && vb.cols % 2 != 0) return STATUS_BAD_TENSOR_SHAPE;
     if (vc.rows != va.rows || vc.cols != (swiglu ? vb.cols / 2 : vb.cols) || va.cols != vb.rows) return STATUS_BAD_TENSOR_SHAPE;
-    if (!(va.batch == vc.batch || va.batch == 1) || !(vb.batch == vc.batch || vb.batch == 1)) return STATUS_BAD_PARAM;
+    if (b_batch_div > 1) {
+        if ((uint64_t) views[1].batch * b_batch_div != vc.batch) return STATUS_BAD_PARAM;
+        views[1].batch_div = b_batch_div;
+    } else if (!(vb.batch == vc.batch || vb.batch == 1)) {
+        return STATUS_BAD_PARAM;
+    }
+    if (!(va.batch == vc.batch || va.batch == 1)) return STATUS_BAD_PARAM;
     if (!dt_eq(a_desc->dt, c_desc->dt) || !dt_eq(b_desc->dt, c_desc->dt)) return STATUS_BAD_TENSOR_DTYPE;
     if (va.row_stride < 0 || va.col_stride < 0 || vb.row_stride < 0 || vb.col_stride < 0 || vc.row_stride < 0 ||
         vc.col_stride < 0) {
@@ -260,6 +269,7 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
     g.mp = pl.p.rows, g.np = pl.q.rows, g.k = pl.k, g.batch = pl.batch;
     g.p_major_mn = pl.p.mn_major, g.q_major_mn = pl.q.mn_major;
     g.p_batch_mul = pl.p.batch_stride == 0 ? 0 : 1, g.q_batch_mul = pl.q.batch_stride == 0 ? 0 : 1;
+    g.p_batch_div = pl.p.batch_div, g.q_batch_div = pl.q.batch_div;
     g.tiles_m = (g.mp + tc::kBM - 1) / tc::kBM;
     pl.p_box_rows = tc::kBM;
     const uint32_t gran = g.q_major_mn ? 64u : 16u;// MN-major tiles come in 64-row TMA boxes

@@ -12,6 +12,7 @@ namespace b200 {
 struct MatView {
     uint32_t batch, rows, cols;
     int64_t batch_stride, row_stride, col_stride;// elements; batch_stride 0 = broadcast
+    uint32_t batch_div;                          // this matrix's batch index = result batch index / batch_div
 };
 
 // A matrix as a tensor-core operand: `rows` x k, K-major (k contiguous) or MN-major (rows contiguous).
@@ -19,6 +20,7 @@ struct TcOperand {
     uint32_t rows, k, batch, mn_major;
     int64_t ld;          // elements between consecutive rows (K-major) or consecutive k (MN-major)
     int64_t batch_stride;// 0 = broadcast
+    uint32_t batch_div;  // operand batch = result batch / batch_div
 };
 
 struct MatmulPlan {
@@ -47,10 +49,11 @@ struct TcMapCache {
 
 // Checks of reference matmul_cuda.cc:12-20 / blas.h:19-100 and the kernel plan.  `epilogue_mode` kEpiSwiGLUCols:
 // b holds [gate | up] column halves and c receives up * silu(gate) ([m, n / 2]; c_desc must then describe that
-// result's strides with n columns ignored beyond n / 2).
+// result's strides with n columns ignored beyond n / 2).  `b_batch_div` > 1: b has batch(c) / b_batch_div matrices
+// and result batch i multiplies with b's matrix i / b_batch_div (grouped attention heads sharing one K or V).
 infiniopStatus_t matmul_plan_create(MatmulPlan &plan, const Handle *h, infiniopTensorDescriptor_t c_desc, float alpha,
                                     infiniopTensorDescriptor_t a_desc, infiniopTensorDescriptor_t b_desc, float beta,
-                                    int epilogue_mode);
+                                    int epilogue_mode, uint32_t b_batch_div = 1);
 void matmul_plan_destroy(MatmulPlan &plan);
 infiniopStatus_t matmul_plan_run(MatmulPlan &plan, TcMapCache &cache, void *workspace, uint64_t workspace_size, void *c,
                                  const void *a, const void *b, cudaStream_t stream);

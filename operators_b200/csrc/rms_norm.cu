@@ -43,6 +43,7 @@ struct RMSNormDesc {
     float epsilon;
     bool fused;                 // x = a + b, written to `sum`
     int64_t stride_b, stride_sum;
+    int dt;                     // kF16, or kBF16 (an extension: bf16 rows and, when 16-bit, weights; same arithmetic)
 };
 
 // Second operand and destination of the sum in the fused form.
@@ -52,6 +53,7 @@ struct Residual {
     int64_t stride_b, stride_sum;
 };
 
+template<int DT>
 __device__ __forceinline__ uint4 add_vec_f16(uint4 x, uint4 y) {
     uint4 r;
     const uint32_t *px = reinterpret_cast<const uint32_t *>(&x);
@@ -59,8 +61,8 @@ __device__ __forceinline__ uint4 add_vec_f16(uint4 x, uint4 y) {
     uint32_t *pr = reinterpret_cast<uint32_t *>(&r);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-        const float2 fx = unpack2(px[k]), fy = unpack2(py[k]);
-        pr[k] = pack2_ref(__fadd_rn(fx.x, fy.x), __fadd_rn(fx.y, fy.y));
+        const float2 fx = unpack2_t<DT>(px[k]), fy = unpack2_t<DT>(py[k]);
+        pr[k] = pack2_t<DT>(__fadd_rn(fx.x, fy.x), __fadd_rn(fx.y, fy.y));
     }
     return r;
 }
@@ -77,8 +79,13 @@ __device__ __forceinline__ double rms_scale(float ss, uint64_t d, float eps) {
     return rsqrt((double) m);
 }
 
+template<int DT>
+__device__ __forceinline__ double h2d_t(uint16_t h) {
+    return DT == kBF16 ? (double) load16<kBF16>(h) : h2d(h);
+}
+template<int DT>
 __device__ __forceinline__ uint16_t rms_out(double k, uint16_t x, double w) {
-    return f32_to_f16_ref(__double2float_rn(__dmul_rn(__dmul_rn(k, h2d(x)), w)));
+    return store16<DT>(__double2float_rn(__dmul_rn(__dmul_rn(k, h2d_t<DT>(x)), w)));
 }
 
 // The same product on the fp32 pipe (double conversions and multiplies run at a fraction of the fp32 rate
@@ -112,7 +119,7 @@ enum RowOwner { WARP_ROW = 0, CTA_ROW = 1, CLUSTER_ROW = 2 };
 
 // VPT vectors (8 halves each) per thread.  MAXT is the launch bound: the row-per-CTA forms that are launched
 // with more than 512 threads must fit 64 registers per thread.
-template<int VPT, bool W_F16, int OWNER, bool FUSED, int MAXT>
+template<int VPT, bool W_F16, int OWNER, bool FUSED, int MAXT, int DT>
 __global__ void __launch_bounds__(MAXT)
     rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs, uint64_t d,
                          int64_t stride_y, int64_t stride_x, float eps, Residual res) {
@@ -151,7 +158,7 @@ __global__ void __launch_bounds__(MAXT)
             for (int u = 0; u < VPT; ++u) {
                 const uint32_t j = t + u * group;
                 if (j < vecs) {
-                    v[u] = add_vec_f16(v[u], o[u]);
+                    v[u] = add_vec_f16<DT>(v[u], o[u]);
                     st_stream(sr + (uint64_t) j * 8, v[u]);
                 }
             }
@@ -163,7 +170,7 @@ __global__ void __launch_bounds__(MAXT)
                 const uint32_t *p = reinterpret_cast<const uint32_t *>(&v[u]);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float2 f = unpack2(p[k]);
+                    const float2 f = unpack2_t<DT>(p[k]);
                     ss = fmaf(f.x, f.x, ss);
                     ss = fmaf(f.y, f.y, ss);
                 }
@@ -185,8 +192,8 @@ __global__ void __launch_bounds__(MAXT)
                     const uint32_t *pw = reinterpret_cast<const uint32_t *>(&wv);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float2 xf = unpack2(px[e]), wf = unpack2(pw[e]);
-                        po[e] = pack2_ref(rms_prod<true>(k, xf.x, wf.x), rms_prod<true>(k, xf.y, wf.y));
+                        const float2 xf = unpack2_t<DT>(px[e]), wf = unpack2_t<DT>(pw[e]);
+                        po[e] = pack2_t<DT>(rms_prod<true>(k, xf.x, wf.x), rms_prod<true>(k, xf.y, wf.y));
                     }
                 } else {
                     const float4 w0 = __ldg(reinterpret_cast<const float4 *>(w) + 2 * j);
@@ -194,8 +201,8 @@ __global__ void __launch_bounds__(MAXT)
                     const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float2 xf = unpack2(px[e]);
-                        po[e] = pack2_ref(rms_prod<false>(k, xf.x, wf[2 * e]), rms_prod<false>(k, xf.y, wf[2 * e + 1]));
+                        const float2 xf = unpack2_t<DT>(px[e]);
+                        po[e] = pack2_t<DT>(rms_prod<false>(k, xf.x, wf[2 * e]), rms_prod<false>(k, xf.y, wf[2 * e + 1]));
                     }
                 }
                 st_stream(yr + (uint64_t) j * 8, out);
@@ -208,7 +215,7 @@ __global__ void __launch_bounds__(MAXT)
 
 // Any alignment, any d: one CTA per row, two passes over x (the second one is
 // served by L2).
-template<bool W_F16, bool FUSED>
+template<bool W_F16, bool FUSED, int DT>
 __global__ void rms_norm_generic_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint64_t d,
                                         int64_t stride_y, int64_t stride_x, float eps, Residual res) {
     __shared__ float red[32];
@@ -220,30 +227,30 @@ __global__ void rms_norm_generic_kernel(uint16_t *y, const uint16_t *x, const vo
             const uint16_t *br = res.b + (int64_t) row * res.stride_b;
             uint16_t *sr = res.sum + (int64_t) row * res.stride_sum;
             for (uint64_t j = threadIdx.x; j < d; j += blockDim.x) {
-                const uint16_t h = f32_to_f16_ref(__fadd_rn(f16_to_f32(xr[j]), f16_to_f32(br[j])));
+                const uint16_t h = store16<DT>(__fadd_rn(load16<DT>(xr[j]), load16<DT>(br[j])));
                 sr[j] = h;
-                const float f = f16_to_f32(h);
+                const float f = load16<DT>(h);
                 ss = fmaf(f, f, ss);
             }
             xr = sr;
         } else {
             for (uint64_t j = threadIdx.x; j < d; j += blockDim.x) {
-                const float f = f16_to_f32(xr[j]);
+                const float f = load16<DT>(xr[j]);
                 ss = fmaf(f, f, ss);
             }
         }
         ss = cta_reduce<false>(ss, red);
         const double k = rms_scale(ss, d, eps);
         for (uint64_t j = threadIdx.x; j < d; j += blockDim.x) {
-            const double wv = W_F16 ? h2d(reinterpret_cast<const uint16_t *>(w)[j])
+            const double wv = W_F16 ? h2d_t<DT>(reinterpret_cast<const uint16_t *>(w)[j])
                                     : (double) reinterpret_cast<const float *>(w)[j];
-            yr[j] = rms_out(k, xr[j], wv);
+            yr[j] = rms_out<DT>(k, xr[j], wv);
         }
         __syncthreads();
     }
 }
 
-template<int VPT, bool W_F16, bool FUSED>
+template<int VPT, bool W_F16, bool FUSED, int DT>
 void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, void *y,
                  const void *x, const void *w, Residual res, cudaStream_t st) {
     auto *yp = reinterpret_cast<uint16_t *>(y);
@@ -253,35 +260,35 @@ void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t 
         const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap) * cl;
         if (cl > 1) {
             if constexpr (VPT == 4) {// clusters always hold four vectors per thread
-                launch_cluster(rms_norm_regs_kernel<4, W_F16, CLUSTER_ROW, FUSED, 1024>, grid, threads, cl, st, yp, xp, w,
+                launch_cluster(rms_norm_regs_kernel<4, W_F16, CLUSTER_ROW, FUSED, 1024, DT>, grid, threads, cl, st, yp, xp, w,
                                d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
             }
         } else if (threads > 512) {
             if constexpr (VPT <= 4) {// eight vectors per thread never need more than 512 threads
-                rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED, 1024>
+                rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED, 1024, DT>
                     <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
             }
         } else {
-            rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED, 512>
+            rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED, 512, DT>
                 <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
         }
     } else {
         const uint64_t ctas = (d->n + 7) / 8;
         const uint64_t cap = 0x7FFFFFFFull;
         const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-        rms_norm_regs_kernel<VPT, W_F16, WARP_ROW, FUSED, 256>
+        rms_norm_regs_kernel<VPT, W_F16, WARP_ROW, FUSED, 256, DT>
             <<<grid, 256, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
     }
 }
 
-template<bool W_F16, bool FUSED>
+template<bool W_F16, bool FUSED, int DT>
 void dispatch_regs(const RMSNormDesc *d, int vpt, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, void *y,
                    const void *x, const void *w, Residual res, cudaStream_t st) {
     switch (vpt) {
-        case 1: launch_regs<1, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
-        case 2: launch_regs<2, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
-        case 4: launch_regs<4, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
-        default: launch_regs<8, W_F16, FUSED>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
+        case 1: launch_regs<1, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
+        case 2: launch_regs<2, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
+        case 4: launch_regs<4, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
+        default: launch_regs<8, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
     }
 }
 
@@ -318,21 +325,22 @@ infiniopStatus_t run(const RMSNormDesc *d, void *y, const void *x, const void *w
             const RowLaunch shape = row_launch_shape(vecs, big ? (FUSED ? 2 : 4) : 1);
             vpt = shape.vpt, threads = shape.threads, cl = shape.cl;
         }
-        if (d->w_f16) dispatch_regs<true, FUSED>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
-        else dispatch_regs<false, FUSED>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
+        if (d->dt == kBF16) {
+            if (d->w_f16) dispatch_regs<true, FUSED, kBF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
+            else dispatch_regs<false, FUSED, kBF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
+        } else {
+            if (d->w_f16) dispatch_regs<true, FUSED, kF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
+            else dispatch_regs<false, FUSED, kF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
+        }
         return check_launch("rms_norm");
     }
     const uint64_t cap = (uint64_t) d->sm_count * 8;
     const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap);
     auto *yp = reinterpret_cast<uint16_t *>(y);
     auto *xp = reinterpret_cast<const uint16_t *>(x);
-    if (d->w_f16) {
-        rms_norm_generic_kernel<true, FUSED>
-            <<<grid, 256, 0, st>>>(yp, xp, w, d->n, d->d, d->stride_y, d->stride_x, d->epsilon, res);
-    } else {
-        rms_norm_generic_kernel<false, FUSED>
-            <<<grid, 256, 0, st>>>(yp, xp, w, d->n, d->d, d->stride_y, d->stride_x, d->epsilon, res);
-    }
+    auto *generic = d->dt == kBF16 ? (d->w_f16 ? rms_norm_generic_kernel<true, FUSED, kBF16> : rms_norm_generic_kernel<false, FUSED, kBF16>)
+                                   : (d->w_f16 ? rms_norm_generic_kernel<true, FUSED, kF16> : rms_norm_generic_kernel<false, FUSED, kF16>);
+    generic<<<grid, 256, 0, st>>>(yp, xp, w, d->n, d->d, d->stride_y, d->stride_x, d->epsilon, res);
     return check_launch("rms_norm");
 }
 
@@ -353,14 +361,17 @@ INFINIOP_API infiniopStatus_t infiniopCreateRMSNormDescriptor(infiniopHandle_t h
     // The reference defers the dtype check to the compute call
     // (rms_norm.cu:165-171: anything but fp16 data -> BAD_TENSOR_DTYPE) and reads
     // any non-fp16 weight as fp32; the weight must really be one of the two here.
-    if (!dt_eq(y_desc->dt, F16) || !dt_eq(x_desc->dt, F16)) return STATUS_BAD_TENSOR_DTYPE;
-    if (!dt_eq(w_desc->dt, F16) && !dt_eq(w_desc->dt, F32)) return STATUS_BAD_TENSOR_DTYPE;
+    // bf16 rows are an extension of this library: x and y bf16, the weight bf16 or fp32
+    const int dt = store_type_of(y_desc->dt);
+    if ((dt != kF16 && dt != kBF16) || !dt_eq(x_desc->dt, y_desc->dt)) return STATUS_BAD_TENSOR_DTYPE;
+    if (!dt_eq(w_desc->dt, y_desc->dt) && !dt_eq(w_desc->dt, F32)) return STATUS_BAD_TENSOR_DTYPE;
     if (y_desc->strides[1] != 1 || x_desc->strides[1] != 1 || w_desc->strides[0] != 1) return STATUS_BAD_TENSOR_STRIDES;
 
     auto *h = reinterpret_cast<Handle *>(handle);
     auto *r = new (std::nothrow) RMSNormDesc{DevNvGpu, h->device_id,         h->sm_count,           n,
-                                             d,        y_desc->strides[0],   x_desc->strides[0],    dt_eq(w_desc->dt, F16),
-                                             epsilon,  false,                0,                     0};
+                                             d,        y_desc->strides[0],   x_desc->strides[0],    !dt_eq(w_desc->dt, F32),
+                                             epsilon,  false,                0,                     0,
+                                             dt};
     if (r == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
     *desc_ptr = reinterpret_cast<infiniopRMSNormDescriptor_t>(r);
     return STATUS_SUCCESS;
@@ -418,10 +429,12 @@ INFINIOP_API infiniopStatus_t infiniopCreateAddRMSNormDescriptor(infiniopHandle_
         if (t->shape[0] != n || t->shape[1] != d) return STATUS_BAD_TENSOR_SHAPE;
     }
     if (w_desc->shape[0] != d) return STATUS_BAD_TENSOR_SHAPE;
+    const int dt = store_type_of(y_desc->dt);
+    if (dt != kF16 && dt != kBF16) return STATUS_BAD_TENSOR_DTYPE;
     for (auto *t : rows) {
-        if (!dt_eq(t->dt, F16)) return STATUS_BAD_TENSOR_DTYPE;
+        if (!dt_eq(t->dt, y_desc->dt)) return STATUS_BAD_TENSOR_DTYPE;
     }
-    if (!dt_eq(w_desc->dt, F16) && !dt_eq(w_desc->dt, F32)) return STATUS_BAD_TENSOR_DTYPE;
+    if (!dt_eq(w_desc->dt, y_desc->dt) && !dt_eq(w_desc->dt, F32)) return STATUS_BAD_TENSOR_DTYPE;
     for (auto *t : rows) {
         if (t->strides[1] != 1) return STATUS_BAD_TENSOR_STRIDES;
     }
@@ -429,8 +442,9 @@ INFINIOP_API infiniopStatus_t infiniopCreateAddRMSNormDescriptor(infiniopHandle_
 
     auto *h = reinterpret_cast<Handle *>(handle);
     auto *r = new (std::nothrow) RMSNormDesc{DevNvGpu, h->device_id,        h->sm_count,          n,
-                                             d,        y_desc->strides[0],  a_desc->strides[0],   dt_eq(w_desc->dt, F16),
-                                             epsilon,  true,                b_desc->strides[0],   sum_desc->strides[0]};
+                                             d,        y_desc->strides[0],  a_desc->strides[0],   !dt_eq(w_desc->dt, F32),
+                                             epsilon,  true,                b_desc->strides[0],   sum_desc->strides[0],
+                                             dt};
     if (r == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
     *desc_ptr = reinterpret_cast<infiniopAddRMSNormDescriptor_t>(r);
     return STATUS_SUCCESS;

@@ -45,6 +45,7 @@ struct RoPEDesc {
     int64_t stride_0, stride_1;
     bool to_dst;                 // RoPERearrange: rotated values go to a second view
     int64_t dstride_0, dstride_1;
+    int dt;                      // kF16, or kBF16 (an extension: bf16 storage, the same un-fused fp32 arithmetic)
 };
 
 // One slice = V halves of one head (V = 8: a 128-bit vector, V = 2: one pair).
@@ -85,7 +86,7 @@ constexpr int kHeadsInFlight = 4;// measured at [4096,32,128]: 4 -> 23 us, 2 -> 
 // Block = tokens_per_cta x threads_per_token.  threads_per_token is a multiple
 // of slices_per_head, so a thread's slice index within the head never changes
 // while it strides over (head, slice) items: its table values load once.
-template<int V, bool ALIGNED>
+template<int V, bool ALIGNED, int DT>
 __global__ void __launch_bounds__(256, 4) rope_kernel(uint16_t *dst, const uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table,
                             uint64_t seq_len, uint32_t nhead, uint32_t dim, int64_t stride_0, int64_t stride_1,
                             int64_t dstride_0, int64_t dstride_1, uint32_t threads_per_token, uint32_t slices_per_head) {
@@ -138,10 +139,10 @@ __global__ void __launch_bounds__(256, 4) rope_kernel(uint16_t *dst, const uint1
                     if (hh < nhead) {
 #pragma unroll
                         for (int k = 0; k < V / 2; ++k) {
-                            const float2 ab = unpack2(x[u].w[k]);
+                            const float2 ab = unpack2_t<DT>(x[u].w[k]);
                             const float r0 = __fsub_rn(__fmul_rn(ab.x, cs[2 * k]), __fmul_rn(ab.y, sn[2 * k]));
                             const float r1 = __fadd_rn(__fmul_rn(ab.x, sn[2 * k + 1]), __fmul_rn(ab.y, cs[2 * k + 1]));
-                            x[u].w[k] = pack2_ref(r0, r1);// both halves with one truncating conversion
+                            x[u].w[k] = pack2_t<DT>(r0, r1);// both halves with one truncating conversion
                         }
                         x[u].store(out + (int64_t) hh * dstride_1);
                     }
@@ -203,14 +204,14 @@ INFINIOP_API infiniopStatus_t infiniopCreateRoPEDescriptor(infiniopHandle_t hand
     if (t->strides[2] != 1 || pos_ids->strides[0] != 1 || sin_table->strides[1] != 1 || cos_table->strides[1] != 1) {
         return STATUS_BAD_TENSOR_STRIDES;
     }
-    if (!dt_eq(t->dt, F16)) return STATUS_BAD_TENSOR_DTYPE;
+    if (!dt_eq(t->dt, F16) && !dt_eq(t->dt, BF16)) return STATUS_BAD_TENSOR_DTYPE;// bf16: an extension
     if (!dt_eq(sin_table->dt, F32) || !dt_eq(cos_table->dt, F32)) return STATUS_BAD_TENSOR_DTYPE;
     if (!dt_eq(pos_ids->dt, U64)) return STATUS_BAD_TENSOR_DTYPE;
 
     auto *h = reinterpret_cast<Handle *>(handle);
     auto *d = new (std::nothrow)
         RoPEDesc{DevNvGpu, h->device_id, h->sm_count, h->max_smem_optin, seq_len, nhead, dim, t->strides[0], t->strides[1],
-                 false,    0,            0};
+                 false,    0,            0,         store_type_of(t->dt)};
     if (d == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
     *desc_ptr = reinterpret_cast<infiniopRoPEDescriptor_t>(d);
     return STATUS_SUCCESS;
@@ -264,7 +265,9 @@ infiniopStatus_t run(const RoPEDesc *d, void *out, const void *t, void const *po
             per_group <= (uint64_t) rp::kMaxTokensPerGroup) {
             static thread_local int configured_dev = -1, configured_bytes = 0;
             if (configured_dev != d->device_id || configured_bytes < (int) plan.smem_bytes) {
-                if (cudaFuncSetAttribute(rp::rope_pipeline_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                if (cudaFuncSetAttribute(rp::rope_pipeline_kernel<kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int) plan.smem_bytes) != cudaSuccess ||
+                    cudaFuncSetAttribute(rp::rope_pipeline_kernel<kBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int) plan.smem_bytes) != cudaSuccess) {
                     cudaGetLastError();
                     return STATUS_EXECUTION_FAILED;
@@ -272,8 +275,8 @@ infiniopStatus_t run(const RoPEDesc *d, void *out, const void *t, void const *po
                 configured_dev = d->device_id;
                 configured_bytes = (int) plan.smem_bytes;
             }
-            rp::rope_pipeline_kernel<<<grid, rp::kThreads, plan.smem_bytes, st>>>(tp, pp, sp, cp, (uint32_t) d->seq_len, dim,
-                                                                              d->stride_0, plan);
+            auto *kernel = d->dt == kBF16 ? rp::rope_pipeline_kernel<kBF16> : rp::rope_pipeline_kernel<kF16>;
+            kernel<<<grid, rp::kThreads, plan.smem_bytes, st>>>(tp, pp, sp, cp, (uint32_t) d->seq_len, dim, d->stride_0, plan);
             return check_launch("rope_pipeline");
         }
     }
@@ -298,16 +301,19 @@ infiniopStatus_t run(const RoPEDesc *d, void *out, const void *t, void const *po
     const uint64_t ctas = (d->seq_len + tokens_per_cta - 1) / tokens_per_cta;
     const uint64_t cap = 0x7FFFFFFFull;// one CTA per token group; more tokens than that loop
     const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-    if (v8) {
-        rope_kernel<8, true><<<grid, threads, 0, st>>>(op, tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1,
-                                                        dstride_0, dstride_1, tpt, slices);
-    } else if (v2_aligned) {
-        rope_kernel<2, true><<<grid, threads, 0, st>>>(op, tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1,
-                                                        dstride_0, dstride_1, tpt, slices);
+#define B200_ROPE_LAUNCH(V_, AL_, DT_)                                                                                    \
+    rope_kernel<V_, AL_, DT_><<<grid, threads, 0, st>>>(op, tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1, \
+                                                       dstride_0, dstride_1, tpt, slices)
+    if (d->dt == kBF16) {
+        if (v8) B200_ROPE_LAUNCH(8, true, kBF16);
+        else if (v2_aligned) B200_ROPE_LAUNCH(2, true, kBF16);
+        else B200_ROPE_LAUNCH(2, false, kBF16);
     } else {
-        rope_kernel<2, false><<<grid, threads, 0, st>>>(op, tp, pp, sp, cp, d->seq_len, nhead, dim, d->stride_0, d->stride_1,
-                                                        dstride_0, dstride_1, tpt, slices);
+        if (v8) B200_ROPE_LAUNCH(8, true, kF16);
+        else if (v2_aligned) B200_ROPE_LAUNCH(2, true, kF16);
+        else B200_ROPE_LAUNCH(2, false, kF16);
     }
+#undef B200_ROPE_LAUNCH
     return check_launch("rope");
 }
 
@@ -355,7 +361,7 @@ INFINIOP_API infiniopStatus_t infiniopCreateRoPERearrangeDescriptor(infiniopHand
         bad = STATUS_BAD_TENSOR_SHAPE;
     } else if (dst->strides[2] != 1) {
         bad = STATUS_BAD_TENSOR_STRIDES;
-    } else if (!dt_eq(dst->dt, F16)) {
+    } else if (store_type_of(dst->dt) != d->dt) {
         bad = STATUS_BAD_TENSOR_DTYPE;
     }
     if (bad != STATUS_SUCCESS) {

@@ -124,6 +124,7 @@ __device__ __forceinline__ void group_barrier(int group) {
 
 // t rows contiguous ([tokens] x nhead*dh halves, token stride >= row, all 16-byte aligned).
 // Token order: group g of CTA c takes tokens c + G * (g + kGroups * j), j = 0, 1, ...
+template<int DT>
 __global__ void __launch_bounds__(kThreads, 1)
 rope_pipeline_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table, uint32_t seq_len,
                      uint32_t dim, int64_t stride_0, Plan plan) {
@@ -192,10 +193,10 @@ rope_pipeline_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_tabl
                 uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    const float2 ab = unpack2(w[k]);
+                    const float2 ab = unpack2_t<DT>(w[k]);
                     const float r0 = __fsub_rn(__fmul_rn(ab.x, cs[2 * k]), __fmul_rn(ab.y, sn[2 * k]));
                     const float r1 = __fadd_rn(__fmul_rn(ab.x, sn[2 * k + 1]), __fmul_rn(ab.y, cs[2 * k + 1]));
-                    w[k] = pack2_ref(r0, r1);
+                    w[k] = pack2_t<DT>(r0, r1);
                 }
                 row[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }

@@ -32,6 +32,7 @@ struct SwiGLUDesc {
     int sm_count;
     uint64_t seq_len, di;
     int64_t stride_c, stride_a, stride_b;
+    int dt;// kF16, or kBF16 (an extension: bf16 storage, same fp32 arithmetic)
 };
 
 __device__ __forceinline__ float swiglu_one(float a, float b) {
@@ -50,6 +51,7 @@ __device__ __forceinline__ float swiglu_one(float a, float b) {
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
+template<int DT>
 __global__ void __launch_bounds__(kThreads)
     swiglu_vec8_kernel(uint16_t *c, const uint16_t *a, const uint16_t *b, int64_t stride_c, int64_t stride_a,
                        int64_t stride_b, FastDiv vecs_per_row, uint32_t total_vecs) {
@@ -78,8 +80,8 @@ __global__ void __launch_bounds__(kThreads)
                 uint32_t *po = reinterpret_cast<uint32_t *>(&out);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
-                    float2 fa = unpack2(pa[k]), fb = unpack2(pb[k]);
-                    po[k] = pack2_ref(swiglu_one(fa.x, fb.x), swiglu_one(fa.y, fb.y));
+                    float2 fa = unpack2_t<DT>(pa[k]), fb = unpack2_t<DT>(pb[k]);
+                    po[k] = pack2_t<DT>(swiglu_one(fa.x, fb.x), swiglu_one(fa.y, fb.y));
                 }
                 st_stream(c + off_c[u], out);
             }
@@ -88,14 +90,15 @@ __global__ void __launch_bounds__(kThreads)
 }
 
 // Any alignment, any row length: one element per thread per step.
+template<int DT>
 __global__ void __launch_bounds__(kThreads)
     swiglu_scalar_kernel(uint16_t *c, const uint16_t *a, const uint16_t *b, int64_t stride_c, int64_t stride_a,
                          int64_t stride_b, uint64_t di, uint64_t total) {
     for (uint64_t i = (uint64_t) blockIdx.x * kThreads + threadIdx.x; i < total; i += (uint64_t) gridDim.x * kThreads) {
         const uint64_t row = i / di, col = i - row * di;
-        const float av = f16_to_f32(a[(int64_t) row * stride_a + (int64_t) col]);
-        const float bv = f16_to_f32(b[(int64_t) row * stride_b + (int64_t) col]);
-        c[(int64_t) row * stride_c + (int64_t) col] = f32_to_f16_ref(swiglu_one(av, bv));
+        const float av = load16<DT>(a[(int64_t) row * stride_a + (int64_t) col]);
+        const float bv = load16<DT>(b[(int64_t) row * stride_b + (int64_t) col]);
+        c[(int64_t) row * stride_c + (int64_t) col] = store16<DT>(swiglu_one(av, bv));
     }
 }
 
@@ -111,7 +114,7 @@ INFINIOP_API infiniopStatus_t infiniopCreateSwiGLUDescriptor(infiniopHandle_t ha
     if (c_desc == nullptr || a_desc == nullptr || b_desc == nullptr) return STATUS_BAD_PARAM;
     // Same checks, same order, same codes as reference swiglu_cuda.cc:10-36.
     if (c_desc->ndim != 2 || a_desc->ndim != 2 || b_desc->ndim != 2) return STATUS_BAD_TENSOR_SHAPE;
-    if (!dt_eq(c_desc->dt, F16)) return STATUS_BAD_TENSOR_DTYPE;
+    if (!dt_eq(c_desc->dt, F16) && !dt_eq(c_desc->dt, BF16)) return STATUS_BAD_TENSOR_DTYPE;// bf16: an extension
     if (a_desc->strides[1] != 1 || b_desc->strides[1] != 1 || c_desc->strides[1] != 1) return STATUS_BAD_TENSOR_STRIDES;
     const uint64_t seq_len = c_desc->shape[0], di = c_desc->shape[1];
     if (a_desc->shape[0] != seq_len || a_desc->shape[1] != di || !dt_eq(a_desc->dt, c_desc->dt) ||
@@ -120,7 +123,8 @@ INFINIOP_API infiniopStatus_t infiniopCreateSwiGLUDescriptor(infiniopHandle_t ha
     }
     auto *h = reinterpret_cast<Handle *>(handle);
     auto *d = new (std::nothrow) SwiGLUDesc{DevNvGpu,          h->device_id,       h->sm_count,       seq_len, di,
-                                            c_desc->strides[0], a_desc->strides[0], b_desc->strides[0]};
+                                            c_desc->strides[0], a_desc->strides[0], b_desc->strides[0],
+                                            store_type_of(c_desc->dt)};
     if (d == nullptr) return STATUS_MEMORY_NOT_ALLOCATED;
     *desc_ptr = reinterpret_cast<infiniopSwiGLUDescriptor_t>(d);
     return STATUS_SUCCESS;
@@ -150,10 +154,10 @@ INFINIOP_API infiniopStatus_t infiniopSwiGLU(infiniopSwiGLUDescriptor_t desc, vo
                 const uint64_t rows = (d->seq_len - r0 < rows_per_launch) ? d->seq_len - r0 : rows_per_launch;
                 const uint32_t total = (uint32_t) (rows * vpr);
                 const uint32_t tiles = (total + kThreads * kUnroll - 1) / (kThreads * kUnroll);
-                swiglu_vec8_kernel<<<tiles, kThreads, 0, st>>>(cp + (int64_t) r0 * d->stride_c,
-                                                              ap + (int64_t) r0 * d->stride_a,
-                                                              bp + (int64_t) r0 * d->stride_b, d->stride_c,
-                                                              d->stride_a, d->stride_b, FastDiv((uint32_t) vpr), total);
+                auto *kernel = d->dt == kBF16 ? swiglu_vec8_kernel<kBF16> : swiglu_vec8_kernel<kF16>;
+                kernel<<<tiles, kThreads, 0, st>>>(cp + (int64_t) r0 * d->stride_c, ap + (int64_t) r0 * d->stride_a,
+                                                  bp + (int64_t) r0 * d->stride_b, d->stride_c, d->stride_a, d->stride_b,
+                                                  FastDiv((uint32_t) vpr), total);
             }
             return check_launch("swiglu");
         }
@@ -162,8 +166,8 @@ INFINIOP_API infiniopStatus_t infiniopSwiGLU(infiniopSwiGLUDescriptor_t desc, vo
     uint64_t blocks = (total + kThreads - 1) / kThreads;
     const uint64_t cap = (uint64_t) d->sm_count * 16;
     if (blocks > cap) blocks = cap;
-    swiglu_scalar_kernel<<<(uint32_t) blocks, kThreads, 0, st>>>(cp, ap, bp, d->stride_c, d->stride_a, d->stride_b,
-                                                                 d->di, total);
+    auto *scalar = d->dt == kBF16 ? swiglu_scalar_kernel<kBF16> : swiglu_scalar_kernel<kF16>;
+    scalar<<<(uint32_t) blocks, kThreads, 0, st>>>(cp, ap, bp, d->stride_c, d->stride_a, d->stride_b, d->di, total);
     return check_launch("swiglu");
 }
 

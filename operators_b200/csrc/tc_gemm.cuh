@@ -55,6 +55,7 @@ struct GemmParams {
     uint32_t q_box_bytes;
     uint32_t p_major_mn, q_major_mn;
     int32_t p_batch_mul, q_batch_mul;// 0 when the operand is broadcast over the batch
+    uint32_t p_batch_div, q_batch_div;// operand batch = result batch / div (grouped heads share one operand)
     uint32_t stages;
     // stream-K
     uint32_t streamk;         // 0: whole tiles, round robin; 1: k-blocks split evenly
@@ -361,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                     unsigned char *sbase = smem + (size_t) stage * stage_bytes;
                     mbar_expect_tx(&full[stage], p.kbs * (kPBytes + q_bytes));
-                    const int32_t pb = (int32_t) b * p.p_batch_mul, qb = (int32_t) b * p.q_batch_mul;
+                    const int32_t pb = (int32_t) (b / p.p_batch_div) * p.p_batch_mul, qb = (int32_t) (b / p.q_batch_div) * p.q_batch_mul;
                     // P first: the boxes of one step continue each other's rows in memory, so their requests reach
                     // the memory system together (256 or 512 contiguous bytes per row instead of 128)
                     for (uint32_t sub = 0; sub < p.kbs; ++sub) {

@@ -55,6 +55,7 @@ def lib():
         L.oracle_matmul_f16_beta.argtypes = [vp, vp, vp, cf, cf, u64, u64, u64, u64, vp, vp, vp]
         L.oracle_matmul_f16_beta.restype = None
         L.oracle_matmul_f32.argtypes, L.oracle_matmul_f32.restype = [vp, vp, vp, cf, cf, u64, u64, u64, u64, vp, vp, vp], None
+        L.oracle_set_storage.argtypes, L.oracle_set_storage.restype = [ci], None
         L.oracle_random_sample_f16.argtypes = [vp, vp, vp, ci, cf, cf, ci, cf]
         L.oracle_random_sample_workspace.argtypes, L.oracle_random_sample_workspace.restype = [ci], u64
         L.oracle_random_sample_trace.argtypes = [vp, vp, ci, ci, cf, vp, vp, vp, vp]
@@ -63,6 +64,18 @@ def lib():
             getattr(L, f).restype = None
         _LIB = L
     return _LIB
+
+
+class bf16_storage:
+    """`with bf16_storage():` makes rms_norm / rope / swiglu / add / causal_softmax called from THIS thread read and
+    write bf16 bit patterns (uint16 arrays) instead of fp16: the extension's oracle, the same restated arithmetic
+    with bf16 decode and truncating encode.  The reference itself has no bf16 operator."""
+
+    def __enter__(self):
+        lib().oracle_set_storage(1)
+
+    def __exit__(self, *exc):
+        lib().oracle_set_storage(0)
 
 
 def _u16(a):
@@ -139,8 +152,8 @@ def add(a, b):
     """Broadcasting add of contiguous fp16 / fp32 arrays.  src/ops/add/cpu/add_cpu.cc:18-89."""
     a = np.asarray(a, order="C")
     b = np.asarray(b, order="C")
-    is_f16 = a.dtype == np.float16
-    assert a.dtype == b.dtype and a.dtype in (np.float16, np.float32)
+    is_f16 = a.dtype in (np.float16, np.uint16)  # uint16: 16-bit patterns (bf16 inside `with bf16_storage()`)
+    assert a.dtype == b.dtype and a.dtype in (np.float16, np.uint16, np.float32)
     shape = np.broadcast_shapes(a.shape, b.shape)
     nd = len(shape)
     out = np.zeros(shape, a.dtype)

@@ -489,6 +489,104 @@ def test_random_sample_argmax_batch(oracle, cuda_lib, voc, rows, pitch, dist):
     assert int(one[0]) == want[rows - 1]
 
 
+# ---- bf16 storage (an extension: the reference has no bf16 operator; oracle = the same restated arithmetic with
+# bf16 decode and truncating encode, oracle.bf16_storage) -------------------------------------------------------
+def _bf16_bits(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def _bf16_within_one_ulp(got, want):
+    """Bit patterns equal, or neighbours of the same sign (one bf16 ulp apart); returns the number of mismatches."""
+    got, want = got.reshape(-1).astype(np.int32), want.reshape(-1).astype(np.int32)
+    diff = np.abs(got - want)
+    both_zero = ((got & 0x7FFF) == 0) & ((want & 0x7FFF) == 0)
+    assert ((diff <= 1) | both_zero).all(), "max pattern distance %d" % diff[~both_zero].max()
+    return int(((diff != 0) & ~both_zero).sum())
+
+
+@pytest.mark.parametrize("shapes", [((3, 3), (3, 3)), ((2, 20, 3), (2, 1, 3)), ((64, 4096), (4096,)), ((1000003,), (1000003,)),
+                                    ((300, 8), (8,))])
+def test_bf16_add(oracle, cuda_lib, shapes):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(40)
+    a = (torch.randn(shapes[0], generator=g) * 100).bfloat16()
+    b = torch.randn(shapes[1], generator=g).bfloat16()
+    with oracle.bf16_storage():
+        want = oracle.add(_bf16_bits(a).reshape(a.shape), _bf16_bits(b).reshape(b.shape))
+    cd = torch.zeros(want.shape, dtype=torch.bfloat16, device=DEV)
+    ops.add(lib, handle, cd, a.to(DEV), b.to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(_bf16_bits(cd).reshape(want.shape), want)
+
+
+@pytest.mark.parametrize("shape,strides", [((1187, 32, 128), None), ((64, 32, 128), None), ((5, 3, 6), (37, 7, 1)),
+                                           ((9, 40, 128), (40 * 256, 256, 1))])
+def test_bf16_rope(oracle, cuda_lib, shape, strides):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(41)
+    t = torch.randn(shape, generator=g).bfloat16()
+    pos = torch.randperm(2 * shape[0], generator=g)[: shape[0]].to(torch.int64)
+    sin, cos = ops.sin_cos_table(2 * shape[0], shape[2])
+    want = _bf16_bits(t).reshape(shape).copy()
+    with oracle.bf16_storage():
+        oracle.rope(want, pos.numpy().astype(np.uint64), sin.numpy(), cos.numpy())
+    td = t.to(DEV)
+    if strides is not None:
+        td = rearrange_tensor(td, strides)
+    ops.rope(lib, handle, td, pos.to(DEV), sin.to(DEV), cos.to(DEV))
+    torch.cuda.synchronize()
+    assert np.array_equal(_bf16_bits(td).reshape(shape), want)
+
+
+@pytest.mark.parametrize("w_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(16, 2048), (5, 33), (700, 4096), (2048, 2048), (2, 70000), (2, 65536)])
+def test_bf16_rms_norm(oracle, cuda_lib, shape, w_dtype):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(42)
+    x = (torch.rand(shape, generator=g) * 2 - 1).bfloat16()
+    w = (torch.rand(shape[1], generator=g) * 2 - 1).to(w_dtype)
+    wn = _bf16_bits(w) if w_dtype == torch.bfloat16 else w.numpy()
+    with oracle.bf16_storage():
+        want = oracle.rms_norm(_bf16_bits(x).reshape(shape), wn, 1e-5).view(np.uint16)
+    yd = torch.zeros(shape, dtype=torch.bfloat16, device=DEV)
+    ops.rms_norm(lib, handle, yd, x.to(DEV), w.to(DEV), 1e-5)
+    torch.cuda.synchronize()
+    assert _few(_bf16_within_one_ulp(_bf16_bits(yd), want), x.numel(), 0.02)
+
+
+@pytest.mark.parametrize("shape,stride", [((13, 4), None), ((16, 5632), None), ((257, 1024), 2048)])
+def test_bf16_swiglu(oracle, cuda_lib, shape, stride):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(43)
+    a = torch.randn(shape, generator=g).bfloat16()
+    b = (torch.randn(shape, generator=g) * 4).bfloat16()
+    with oracle.bf16_storage():
+        want = oracle.swiglu(_bf16_bits(a).reshape(shape), _bf16_bits(b).reshape(shape)).view(np.uint16)
+    ad, bd = a.to(DEV), b.to(DEV)
+    if stride is not None:
+        ad, bd = rearrange_tensor(ad, (stride, 1)), rearrange_tensor(bd, (stride, 1))
+    cd = torch.zeros(shape, dtype=torch.bfloat16, device=DEV)
+    ops.swiglu(lib, handle, cd, ad, bd)
+    torch.cuda.synchronize()
+    assert _few(_bf16_within_one_ulp(_bf16_bits(cd), want), a.numel(), 2e-3)
+
+
+@pytest.mark.parametrize("shape", [(32, 20, 512), (5, 64), (2, 128, 4096), (4, 33, 1000), (1, 2, 40960), (2, 2, 300000)])
+def test_bf16_causal_softmax(oracle, cuda_lib, shape):
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(44)
+    y = (torch.randn(shape, generator=g) * 2).bfloat16()
+    want = _bf16_bits(y).reshape(shape).copy()
+    with oracle.bf16_storage():
+        oracle.causal_softmax(want)
+    yd = y.to(DEV)
+    ops.causal_softmax(lib, handle, yd)
+    torch.cuda.synchronize()
+    got = _bf16_bits(yd).reshape(shape)
+    _bf16_within_one_ulp(got, want)
+    assert (got[want == 0] == 0).all()  # masked entries are exact zeros
+
+
 # ---- matmul (the reference's cases, operatorspy/tests/matmul.py:296-308, and the layouts either kernel serves) ----
 MATMUL_CASES = [
     # alpha, beta, a_shape, b_shape, c_shape, a_stride, b_stride, c_stride
@@ -764,14 +862,22 @@ ATTENTION_CASES = [
     (5, 1, 1, 32, 0, 1, None, None),
     (2, 1, 3, 16, 0, 3, None, None),
     (10, 2, 1, 128, 63, 64, None, None),
+    # several new tokens on the tcgen05 path: prefill from an empty cache, a long prefix, speculative decoding,
+    # token counts and cache lengths that are not multiples of anything
+    (32, 8, 512, 128, 0, 512, None, None),
+    (32, 8, 16, 128, 4096, 4112, None, None),
+    (8, 2, 300, 64, 77, 400, None, None),
+    (4, 4, 130, 128, 1000, 1200, None, None),
+    (16, 2, 9, 256, 31, 64, None, None),
 ]
 
 
-@pytest.fixture(params=["tensor", "multiply_add"])
+@pytest.fixture(params=["tensor", "multiply_add", "row_tiles"])
 def attention_kernels(request, cuda_lib):
-    """Both kernel families: the tensor-core kernels and the multiply-add kernels that otherwise
-    serve unaligned layouts and head sizes above 128."""
-    ops.select_kernel(cuda_lib[0], "attention", 1 if request.param == "multiply_add" else 0)
+    """The kernel families: the library's own choice (tcgen05 products for calls with several new tokens, the
+    mma.sync row-tile kernels for decoding), the multiply-add kernels that otherwise serve unaligned layouts and
+    head sizes above 128, and the row-tile kernels everywhere."""
+    ops.select_kernel(cuda_lib[0], "attention", {"tensor": 0, "multiply_add": 1, "row_tiles": 2}[request.param])
     yield request.param
     ops.select_kernel(cuda_lib[0], "attention", 0)
 

@@ -30,7 +30,7 @@ def _free_port():
 def _worker(rank, world, port, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    from operators_b200.sharding import row_range, shard_rows, vocab_range
+    from operators_b200.sharding import assemble_rows, exchange_plan, row_range, shard_rows, vocab_range
     from oracle import cpu_oracle as oracle
     from shard_protocol_cpu import finish_numpy, pack_record_numpy
 
@@ -73,6 +73,28 @@ def _worker(rank, world, port, out_dir):
     both = [torch.zeros_like(mine_t) for _ in range(world)]
     dist.all_gather(both, mine_t)
     ok &= all(torch.equal(both[0], t) for t in both)
+    # --- index-exact mode: one all-to-all hands every rank whole rows, the oracle samples them (the exact kernel's
+    # stand-in), one all-gather returns the indices: every row's index is the unsharded answer
+    rows2, voc2 = 7, 5003  # neither divides by the world size
+    logits2 = (torch.randn((rows2, voc2), generator=g) * 3).half()
+    u2 = torch.rand(rows2, generator=g)
+    (r0, r1), send, recv, cols = exchange_plan(rows2, voc2, world, rank)
+    mine_cols = logits2[:, cols[rank][0]:cols[rank][1]].contiguous()
+    received = torch.zeros(sum(recv), dtype=torch.int32)  # gloo's all-to-all takes no 16-bit types: bit patterns as int32
+    dist.all_to_all_single(received, mine_cols.view(torch.int16).view(-1).to(torch.int32), recv, send)
+    full = assemble_rows(received, r1 - r0, cols).to(torch.int16).view(torch.float16)
+    ok &= torch.equal(full, logits2[r0:r1])
+    most = max(e - b for b, e in (row_range(rows2, world, r) for r in range(world)))
+    picked = torch.full((most,), -1, dtype=torch.int64)
+    for i in range(r1 - r0):
+        picked[i] = oracle.random_sample(full[i].numpy(), float(u2[r0 + i]), topp, topk, temp)
+    everybody = [torch.zeros_like(picked) for _ in range(world)]
+    dist.all_gather(everybody, picked)
+    got2 = []
+    for r in range(world):
+        b2, e2 = row_range(rows2, world, r)
+        got2 += everybody[r][:e2 - b2].tolist()
+    ok &= got2 == [oracle.random_sample(logits2[r].numpy(), float(u2[r]), topp, topk, temp) for r in range(rows2)]
     open(os.path.join(out_dir, "ok_%d" % rank), "w").write("1" if ok else "0")
     dist.destroy_process_group()
 
