@@ -388,6 +388,9 @@ def _timed_calls(torch, fn, steps, warmup):
     return t0.elapsed_time(t1) / steps
 
 
+MATMUL_CASE = {"tokens": None, "weights": None}  # --tokens / --weights: one case only (ncu captures)
+
+
 def only_matmul(lib, handle, dev, steps, warmup):
     """Not part of the step: the gate / up projection of the SwiGLU configuration, [tokens, 4096] x [4096, 28672],
     for a prefill-sized and two decoding token counts, weights in both layouts.  Prefill shapes are judged in
@@ -405,9 +408,13 @@ def only_matmul(lib, handle, dev, steps, warmup):
     out = {"only": "matmul", "k": hidden, "n": n, "cases": [],
            "note": "back-to-back calls of one operator; not a bench value"}
     for tokens in (SWI_T, 16, 1):
+        if MATMUL_CASE["tokens"] not in (None, tokens):
+            continue
         a = torch.randn((tokens, hidden), device=dev).half()
         c = torch.empty((tokens, n), device=dev, dtype=torch.float16)
         for name, w in (("k_contiguous", w_nk), ("n_contiguous", w_kn)):
+            if MATMUL_CASE["weights"] not in (None, name):
+                continue
             op = _ops.MatmulOp(lib, handle, c, a, w)
             ms = _timed_calls(torch, lambda: op(c, a, w), max(3, steps // (4 if tokens > 64 else 1)), warmup)
             op.destroy()
@@ -466,7 +473,10 @@ def run_b200(args):
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=torch.device(dev))
+        import datetime
+
+        # a collective that a peer never joins ends with an error after five minutes instead of hanging the box
+        dist.init_process_group("nccl", device_id=torch.device(dev), timeout=datetime.timedelta(minutes=5))
     lib = open_lib(os.path.join(ROOT, "operators_b200", "lib"))
     handle = create_handle(lib, DeviceEnum.DEVICE_CUDA, local)
 
@@ -638,6 +648,31 @@ def run_b200(args):
                        "gbs": round(r_bytes / r_ms / 1e6, 1)}
         rbig.destroy()
         del ts
+        # what a plain device copy of the configuration's bytes takes under the same conditions (back-to-back
+        # launches over three rotating buffers): 33.5 MB in, 33.5 MB out are a few microseconds of HBM time, so ramp
+        # and tail weigh as much as the transfer; the copy is the yardstick for what 67 MB can reach at all
+        srcs = [torch.randn((ROPE_T, ROPE_H, ROPE_DH), device=dev).half() for _ in range(3)]
+        dsts = [torch.empty_like(x) for x in srcs]
+        for i in range(3):
+            dsts[i].copy_(srcs[i])
+        torch.cuda.synchronize()
+        b0.record(stream)
+        for _ in range(12):
+            for i in range(3):
+                dsts[i].copy_(srcs[i])
+        b1.record(stream)
+        torch.cuda.synchronize()
+        rope_scaled["copy_of_config_bytes_ms"] = round(b0.elapsed_time(b1) / 36, 5)
+        rcfg = _ops.RoPEOp(lib, handle, srcs[0], step.t["rope_pos"], step.t["rope_sin"], step.t["rope_cos"])
+        b0.record(stream)
+        for _ in range(12):
+            for i in range(3):
+                rcfg(srcs[i], step.t["rope_pos"], step.t["rope_sin"], step.t["rope_cos"], sptr)
+        b1.record(stream)
+        torch.cuda.synchronize()
+        rope_scaled["config_back_to_back_ms"] = round(b0.elapsed_time(b1) / 36, 5)
+        rcfg.destroy()
+        del srcs, dsts
     barrier()
 
     # ---- end to end: host buffers in, host results out, every step ----
@@ -746,8 +781,17 @@ def run_b200(args):
                 for (_, ea), (nb, eb) in zip(evs, evs[1:]):
                     acc[nb] = acc.get(nb, 0.0) + ea.elapsed_time(eb) / 5
             res["stages_ms"] = acc
-            # the whole call as one CUDA graph (collectives included), when the capture works
+            # the whole call as one CUDA graph (collectives included), when the capture works on every rank;
+            # only on request: a process that still holds a graph with captured NCCL kernels can block in
+            # destroy_process_group, so the graph is dropped before the group is
             res["ms_graph"] = None
+            gr = None
+            if not args.sharded_graph:
+                if mode == "exact":
+                    res["indices"] = out.cpu().tolist()
+                sharded[mode] = res
+                sampler.destroy()
+                continue
             try:
                 side = torch.cuda.Stream()
                 side.wait_stream(stream)
@@ -755,6 +799,13 @@ def run_b200(args):
                 with torch.cuda.graph(gr, stream=side):
                     sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, check=False)
                 stream.wait_stream(side)
+            except Exception as exc:  # noqa: BLE001
+                res["graph_error"] = str(exc)[:200]
+                gr = None
+            torch.cuda.synchronize()
+            captured = torch.tensor([1 if gr is not None else 0], device=dev)
+            dist.all_reduce(captured, op=dist.ReduceOp.MIN)  # replay only when every rank holds a graph
+            if int(captured.item()) == 1:
                 gr.replay()
                 barrier()
                 g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -764,9 +815,8 @@ def run_b200(args):
                 g1.record(stream)
                 barrier()
                 res["ms_graph"] = g0.elapsed_time(g1) / args.steps
-            except Exception as exc:  # noqa: BLE001
-                res["graph_error"] = str(exc)[:200]
-                torch.cuda.synchronize()
+            del gr
+            torch.cuda.synchronize()
             if mode == "exact":
                 res["indices"] = out.cpu().tolist()
             sharded[mode] = res
@@ -1050,10 +1100,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg (profiling runs)")
     ap.add_argument("--sustain-seconds", type=float, default=1.0,
                     help="replay the step for this long after the timed K steps and report it as `sustained`")
+    ap.add_argument("--sharded-graph", action="store_true",
+                    help="N > 1: also time vocabulary-sharded sampling replayed as one CUDA graph (NCCL calls captured)")
     ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of a CUDA graph of the step")
     ap.add_argument("--only", choices=OPS + list(NEXT_ROWS),
                     help="launch a single operator at its configuration (for ncu captures)")
+    ap.add_argument("--tokens", type=int, choices=[SWI_T, 16, 1], help="with --only matmul: this token count only")
+    ap.add_argument("--weights", choices=["k_contiguous", "n_contiguous"], help="with --only matmul: this weight layout only")
     args = ap.parse_args()
+    MATMUL_CASE["tokens"], MATMUL_CASE["weights"] = args.tokens, args.weights
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)

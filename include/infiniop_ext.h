@@ -18,7 +18,8 @@
  *   family 1 (random sample): 1 = the global-memory kernel instead of the shared-memory cluster kernel
  *   family 2 (attention):     1 = the multiply-add kernels instead of the tensor-core kernels,
  *                             2 = the row-tile mma.sync kernels also where the tcgen05 path (several new tokens) applies
- *   family 3 (matmul):        1 = the CUDA-core kernel instead of the tcgen05 kernel
+ *   family 3 (matmul):        1 = the CUDA-core kernel instead of the tcgen05 kernels, 2 (read when a descriptor is
+ *                             created) = the single-CTA tcgen05 kernel also where CTA pairs (cta_group::2) apply
  * Returns STATUS_BAD_PARAM for an unknown family or a negative variant.
  */
 INFINIOP_API infiniopStatus_t infiniopExtSelectKernel(int family, int variant);

@@ -250,6 +250,23 @@ __device__ __forceinline__ float cluster_reduce(float v, float *slot, float *min
 
 // One-dimensional launch with `cl` consecutive CTAs forming a cluster (grid must be a multiple of cl).
 template<typename... KArgs, typename... Args>
+static inline cudaError_t launch_cluster_smem(void (*kernel)(KArgs...), uint32_t grid, uint32_t threads, uint32_t cl,
+                                              size_t smem_bytes, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+template<typename... KArgs, typename... Args>
 static inline cudaError_t launch_cluster(void (*kernel)(KArgs...), uint32_t grid, uint32_t threads, uint32_t cl,
                                          cudaStream_t st, Args... args) {
     cudaLaunchConfig_t cfg = {};

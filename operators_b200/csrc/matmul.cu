@@ -338,6 +338,30 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
         grid = g.total_tiles;
     }
     pl.grid = grid;
+    // Large products: 256 x 256 tiles on CTA pairs (tc_gemm_pair_kernel), when they give every pair at least one tile
+    pl.pair = false;
+    // (infiniopExtSelectKernel(matmul, 2) at descriptor creation keeps the single-CTA kernel: tests, comparisons)
+    if (!pl.swapped && g.mode != tc::kEpiSwiGLULanes && g.mp >= 512 && n_out >= 256 && kernel_choice(kFamilyMatmul) != 2) {
+        const uint32_t pairs = (uint32_t) pl.sm_count / 2;
+        const uint32_t tm2 = (g.mp + 255) / 256;
+        const uint32_t tn2 = g.mode == tc::kEpiSwiGLUCols ? (n_out + 127) / 128 : (g.np + 255) / 256;
+        if ((uint64_t) tm2 * tn2 * pl.batch >= pairs) {
+            if (pl.counter_slot >= 0) counter_slot_release(pl.counter_slot);
+            pl.counter_slot = -1;
+            pl.pair = true;
+            g.streamk = 0, g.kbs = 1;
+            g.kblocks = (pl.k + tc::kBK - 1) / tc::kBK;
+            g.tiles_m = tm2, g.tiles_n = tn2, g.bn = tc::kPairBN;
+            g.total_tiles = tm2 * tn2 * pl.batch;
+            g.stages = (budget - 8192u) / tc::kPairStageBytes;
+            if (g.stages > 8) g.stages = 8;
+            pl.smem_bytes = g.stages * tc::kPairStageBytes + 8192;
+            pl.q_box_rows = g.q_major_mn ? 64 : 128;
+            pl.workspace_bytes = pl.partials_bytes = pl.counters_bytes = 0;
+            const uint64_t want = 2ull * g.total_tiles;
+            pl.grid = (uint32_t) (want < 2ull * pairs ? want : 2ull * pairs);
+        }
+    }
     // D's lane index is c's row (or, transposed, its column)
     g.c_lane_stride = pl.swapped ? vc.col_stride : vc.row_stride;
     g.c_col_stride = pl.swapped ? vc.row_stride : vc.col_stride;
@@ -388,7 +412,16 @@ infiniopStatus_t matmul_plan_run(MatmulPlan &pl, TcMapCache &cache, void *worksp
                 cudaSuccess) {
                 return check_launch("matmul attribute");
             }
-            tc::tc_gemm_kernel<<<pl.grid, tc::kThreads, pl.smem_bytes, st>>>(cache.map_p, cache.map_q, g);
+            if (pl.pair) {
+                if (cudaFuncSetAttribute(tc::tc_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+                    cudaSuccess) {
+                    return check_launch("matmul attribute");
+                }
+                launch_cluster_smem(tc::tc_gemm_pair_kernel, pl.grid, tc::kThreads, 2, pl.smem_bytes, st, cache.map_p,
+                                    cache.map_q, g);
+            } else {
+                tc::tc_gemm_kernel<<<pl.grid, tc::kThreads, pl.smem_bytes, st>>>(cache.map_p, cache.map_q, g);
+            }
         }
         return check_launch("matmul (tcgen05)");
     }

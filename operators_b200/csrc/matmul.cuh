@@ -32,6 +32,7 @@ struct MatmulPlan {
     int mode;            // tc::EpilogueMode
     // tensor-core path
     bool use_tc, swapped;// swapped: the MMA computes c^T = b^T a^T
+    bool pair;           // 256 x 256 tiles on CTA pairs (cta_group::2)
     TcOperand p, q;
     uint32_t p_box_rows, q_box_rows, grid, smem_bytes;
     int counter_slot;    // slot of library-owned stream-K counters, -1: counters in the workspace

@@ -216,12 +216,19 @@ __device__ __forceinline__ bool work_item(const GemmParams &p, uint32_t cta, uin
     return true;
 }
 
+// Tile order: within a batch entry, bands of kRasterRows tile rows are walked column by column, so the CTAs that
+// run at the same time share a few tile rows of P and a few tile columns of Q (about 16 + 9 tiles' worth of
+// operands for 148 tiles in flight, instead of a whole operand), which keeps both in L2.
+constexpr uint32_t kRasterRows = 16;
 __device__ __forceinline__ void tile_coords(const GemmParams &p, uint32_t tile, uint32_t &b, uint32_t &tm, uint32_t &tn) {
     const uint32_t per_batch = p.tiles_m * p.tiles_n;
     b = tile / per_batch;
     const uint32_t r = tile - b * per_batch;
-    tn = r / p.tiles_m;
-    tm = r - tn * p.tiles_m;
+    const uint32_t band = r / (kRasterRows * p.tiles_n);
+    const uint32_t in_band = r - band * (kRasterRows * p.tiles_n);
+    const uint32_t rows_here = min(kRasterRows, p.tiles_m - band * kRasterRows);
+    tn = in_band / rows_here;
+    tm = band * kRasterRows + (in_band - tn * rows_here);
 }
 
 // Final values of 16 consecutive columns of one lane, written to D.
@@ -337,14 +344,22 @@ __global__ void __launch_bounds__(kThreads, 1)
         prefetch_tensormap(&map_p);
         prefetch_tensormap(&map_q);
     }
-    if (warp == 1) {
-        tmem_alloc(tmem_slot, tmem_cols);
-        tmem_relinquish();
+    // The producer does not need the TMEM address: warp 0 only announces that the barriers exist (bar.arrive) and
+    // starts loading, while warp 1 allocates TMEM and the other warps wait for both.
+    uint32_t tmem_base = 0;
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("bar.arrive 3, %0;" ::"n"(kThreads) : "memory");
+    } else {
+        if (warp == 1) {
+            tmem_alloc(tmem_slot, tmem_cols);
+            tmem_relinquish();
+        }
+        tc_fence_before();
+        asm volatile("bar.sync 3, %0;" ::"n"(kThreads) : "memory");
+        tc_fence_after();
+        tmem_base = *tmem_slot;
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -489,19 +504,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 tc_fence_before();
                 mbar_arrive(&acc_empty[buf]);
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");// the four epilogue warps
+                asm volatile("bar.sync 1, 128;" ::: "memory");// the four epilogue warps: all parts are written
                 // CTAs whose range meets this tile: first .. last
                 const uint64_t t0 = (uint64_t) w.tile * p.kblocks;
                 const uint32_t first = (uint32_t) (t0 / p.work_per_cta);
                 const uint32_t last = (uint32_t) ((t0 + p.kblocks - 1) / p.work_per_cta);
                 if (epi_tid == 0) {
+                    __threadfence();// release: the barrier above made the other threads' stores this thread's to publish
                     const uint32_t seen = atomicAdd(&p.counters[w.tile], 1u);
                     *last_flag = seen == last - first ? 1u : 0u;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                const bool is_last = *last_flag != 0;
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const bool is_last = *last_flag != 0;// rewritten only behind the next part's first barrier
                 if (is_last) {
                     __threadfence();
                     if (epi_tid == 0) p.counters[w.tile] = 0;// ready for the next launch
@@ -544,6 +558,223 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// ---------------------------------------------------------------- CTA pairs (cta_group::2) --
+// Large products: a cluster of two CTAs owns a 256 x 256 tile.  Each CTA loads its 128 rows of P and its 128
+// rows of Q per stage (32 KB instead of the 48 KB a lone CTA needs for 128 x 256), the leader CTA issues
+// tcgen05.mma.cta_group::2 (M = 256 over both CTAs, each reading the other's half of Q from its shared memory),
+// and each CTA finds its 128 rows of the accumulator in its own tensor memory.  One CTA alone spends the shared
+// memory port twice over (TMA writes plus operand reads of A and all of B: 192 bytes per cycle at the full MMA
+// rate against a 128-byte port); the pair needs 128.  Barriers: the peer's TMA loads complete on the LEADER's
+// full barrier (cta_group::2 form of the copy), the leader's commits are multicast to both CTAs' empty and
+// accumulator barriers, the peer's epilogue arrives on the leader's accumulator-empty barrier remotely.  The loads
+// themselves carry no multicast.  Plain and column-mode SwiGLU epilogues; no stream-K.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+// TMA load whose mbarrier may live in the peer CTA of the pair (address in the cluster window).
+__device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
+                                                 int32_t x, int32_t y, int32_t z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// one arrival on the barrier at this shared-memory offset in BOTH CTAs of the pair, once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask)
+                 : "memory");
+}
+
+constexpr uint32_t kPairBN = 256;
+constexpr uint32_t kPairStageBytes = 2 * kPBytes;// 128 x 64 of P and 128 x 64 of Q per CTA
+
+// Tile `it` of pair `pair` (round robin over the pairs); tiles are 256 x 256.
+__device__ __forceinline__ bool pair_tile(const GemmParams &p, uint32_t pair, uint32_t pairs, uint32_t it, uint32_t &tile) {
+    const uint64_t t = (uint64_t) pair + (uint64_t) it * pairs;
+    if (t >= p.total_tiles) return false;
+    tile = (uint32_t) t;
+    return true;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    tc_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                        const GemmParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t) p.stages * kPairStageBytes);
+    uint64_t *full = bars, *empty = bars + p.stages, *acc_full = bars + 2 * p.stages, *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();// 0 = leader
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    constexpr uint32_t kTmemCols = 512;  // two accumulators of 256 fp32 columns
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1); // the leader's arrive.expect_tx; bytes from both CTAs (used in the leader only)
+            mbar_init(&empty[s], 1);// one multicast commit
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);   // one multicast commit
+            mbar_init(&acc_empty[b], 256);// the epilogue threads of both CTAs (used in the leader only)
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tensormap(&map_p);
+        prefetch_tensormap(&map_q);
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();// both CTAs' barriers are initialised before anybody signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (one lane in each CTA)
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, tile;
+            bool ok = true;
+            for (uint32_t it = 0; ok && pair_tile(p, pair, pairs, it, tile); ++it) {
+                uint32_t b, tm, tn;
+                tile_coords(p, tile, b, tm, tn);
+                const int32_t pb = (int32_t) (b / p.p_batch_div) * p.p_batch_mul, qb = (int32_t) (b / p.q_batch_div) * p.q_batch_mul;
+                const int32_t prow = (int32_t) (tm * 256 + rank * 128);
+                // rows of Q this CTA holds: its half of the 256 columns, or (SwiGLU) the gate half in the leader and
+                // the matching up half in the peer
+                const int32_t qrow = p.mode == kEpiSwiGLUCols ? (int32_t) (tn * 128 + rank * p.half_offset)
+                                                              : (int32_t) (tn * 256 + rank * 128);
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    unsigned char *sp = smem + (size_t) stage * kPairStageBytes, *sq = sp + kPBytes;
+                    const uint32_t full_leader = mapa_u32(smem_u32(&full[stage]), 0);
+                    if (rank == 0) mbar_expect_tx(&full[stage], 2 * kPairStageBytes);
+                    const int32_t k0 = (int32_t) (kb * kBK);
+                    if (!p.p_major_mn) {
+                        tma_load_3d_pair(sp, &map_p, full_leader, k0, prow, pb);
+                    } else {
+                        tma_load_3d_pair(sp, &map_p, full_leader, prow, k0, pb);
+                        tma_load_3d_pair(sp + kPBytes / 2, &map_p, full_leader, prow + 64, k0, pb);
+                    }
+                    if (!p.q_major_mn) {
+                        tma_load_3d_pair(sq, &map_q, full_leader, k0, qrow, qb);
+                    } else {
+                        tma_load_3d_pair(sq, &map_q, full_leader, qrow, k0, qb);
+                        tma_load_3d_pair(sq + kPBytes / 2, &map_q, full_leader, qrow + 64, k0, qb);
+                    }
+                    if (++stage == p.stages) stage = 0, phase ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = make_idesc(256, kPairBN, p.p_major_mn, p.q_major_mn);
+            uint32_t stage = 0, phase = 0, acc_it = 0, tile;
+            bool ok = true;
+            for (uint32_t it = 0; ok && pair_tile(p, pair, pairs, it, tile); ++it, ++acc_it) {
+                const uint32_t buf = acc_it & 1u;
+                if (!mbar_wait(&acc_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * kPairBN;
+                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sp = smem_u32(smem + (size_t) stage * kPairStageBytes), sq = sp + kPBytes;
+#pragma unroll
+                    for (uint32_t j = 0; j < kBK / kUmmaK; ++j) {
+                        const uint64_t da = p.p_major_mn ? make_smem_desc(sp + j * 2048u, kPBytes / 2, 1024)
+                                                         : make_smem_desc(sp + j * 32u, 16, 1024);
+                        const uint64_t db = p.q_major_mn ? make_smem_desc(sq + j * 2048u, kPBytes / 2, 1024)
+                                                         : make_smem_desc(sq + j * 32u, 16, 1024);
+                        umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(&empty[stage]);
+                    if (++stage == p.stages) stage = 0, phase ^= 1u;
+                }
+                if (ok) umma_commit_pair(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+        const uint32_t quarter = warp & 3u;
+        uint32_t acc_it = 0, tile;
+        for (uint32_t it = 0; pair_tile(p, pair, pairs, it, tile); ++it, ++acc_it) {
+            const uint32_t buf = acc_it & 1u;
+            uint32_t b, tm, tn;
+            tile_coords(p, tile, b, tm, tn);
+            if (!mbar_wait(&acc_full[buf], (acc_it >> 1) & 1u, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t lane_row = quarter * 32 + lane;
+            const uint32_t row = tm * 256 + rank * 128 + lane_row;
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * kPairBN;
+            if (p.mode == kEpiSwiGLUCols) {
+                for (uint32_t c0 = 0; c0 < 128; c0 += 16) {
+                    float gate[16], up[16];
+                    tmem_ld16(taddr + c0, gate);
+                    tmem_ld16(taddr + 128 + c0, up);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float g = f16_to_f32(f32_to_f16_ref(gate[j])), u = f16_to_f32(f32_to_f16_ref(up[j]));
+                        gate[j] = __fmul_rn(u, silu_f32(g));
+                    }
+                    store_cols16(p, gate, row, tn * 128 + c0, b, p.mp, p.half_offset, 1.f, 0.f);
+                }
+            } else {
+                for (uint32_t c0 = 0; c0 < kPairBN; c0 += 16) {
+                    float acc[16];
+                    tmem_ld16(taddr + c0, acc);
+                    store_cols16(p, acc, row, tn * kPairBN + c0, b, p.mp, p.np, p.alpha, p.beta);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive_remote(mapa_u32(smem_u32(&acc_empty[buf]), 0));
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000ll) {}// copies in flight towards either CTA land (about 2 ms)
+    }
+    cluster_sync_all();// nobody leaves while the other CTA may still signal its barriers or read its shared memory
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 

@@ -108,8 +108,10 @@ class VocabShardedSampler:
         self.last_events = None
 
     def destroy(self):
-        for _, _, _, op in self._exact.values():
-            op.destroy()
+        for entry in self._exact.values():
+            entry[3].destroy()
+            if entry[4] is not None:
+                entry[4].destroy()
         self._exact = {}
 
     def _buffers(self, rows, device):
@@ -137,7 +139,16 @@ class VocabShardedSampler:
             picked = torch.zeros((self.world, most), dtype=torch.int64, device=device)
             op = RandomSampleOp(self.lib, self.handle, picked[0, :1], full[0])
             op._ensure_batch_ws(max(1, r1 - r0), device)
-            self._exact[key] = (received, full, picked, op)
+            op_copy = full_view = received_view = None
+            mine = r1 - r0
+            if mine and self.voc_total % self.world == 0 and received.is_cuda:
+                from .ops import RearrangeOp
+
+                vl = self.voc_total // self.world
+                full_view = full[:mine].view(mine, self.world, vl).permute(1, 0, 2)  # [shard, row, cols] view of the rows
+                received_view = received[:self.world * mine * vl].view(self.world, mine, vl)
+                op_copy = RearrangeOp(self.lib, self.handle, full_view, received_view)
+            self._exact[key] = (received, full, picked, op, op_copy, full_view, received_view)
         return self._exact[key]
 
     def sample(self, results, local_logits, random_vals, topp, topk, temperature, stream=None, check=True,
@@ -174,7 +185,7 @@ class VocabShardedSampler:
         rows = local_logits.shape[0]
         (r0, r1), send, recv, cols = exchange_plan(rows, self.voc_total, self.world, self.rank)
         mine = r1 - r0
-        received, full, picked, op = self._exact_buffers(rows, local_logits.device)
+        received, full, picked, op, op_copy, full_view, received_view = self._exact_buffers(rows, local_logits.device)
         src = local_logits if local_logits.is_contiguous() else local_logits.contiguous()
         if self._a2a is not None:
             self._a2a(received, src.view(-1), recv, send)
@@ -186,18 +197,27 @@ class VocabShardedSampler:
             received[:src.numel()].copy_(src.view(-1))
         mark("all_to_all")
         if mine:
-            assemble_rows(received, mine, cols, out=full)
+            if op_copy is not None:  # equal shards: [shard][row][cols] -> [row][shard][cols] in one strided copy
+                op_copy(full_view, received_view, stream=sp)
+            else:
+                assemble_rows(received, mine, cols, out=full)
             mark("assemble")
             op.batch(picked[self.rank, :mine], full[:mine], random_vals[r0:r1], topp, topk, temperature, stream=sp)
         mark("sample")
+        even = rows % self.world == 0
         if self._gather is not None:
             self._gather(picked, picked[self.rank])
         elif self.world > 1:
             import torch.distributed as dist
 
+            if even and results.is_contiguous():  # equal row counts: the indices are gathered straight into `results`
+                dist.all_gather_into_tensor(results.view(torch.int64), picked[self.rank, :mine], group=self.group)
+                mark("all_gather")
+                mark("finish")
+                return
             dist.all_gather_into_tensor(picked.view(-1), picked[self.rank], group=self.group)
         mark("all_gather")
-        if rows % self.world == 0:
+        if even:
             results.view(torch.int64).copy_(picked.view(-1))
         else:
             for r in range(self.world):
