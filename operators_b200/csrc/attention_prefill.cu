@@ -62,6 +62,16 @@ AttnPrefill *attn_prefill_create(infiniopHandle_t handle, const AttnPrefillShape
     ok = ok && matmul_plan_create(p->values, h, &od, 1.f, &sc, &vd, 0.f, tc::kEpiPlain, s.group) == STATUS_SUCCESS &&
          p->values.use_tc;
     ok = ok && infiniopCreateCausalSoftmaxDescriptor(handle, &p->softmax, &sc) == STATUS_SUCCESS;
+    if (ok) {
+        // causal structure: score tiles wholly behind the mask are never read by the softmax (it writes their zeros
+        // itself), and a row block's probabilities are zero beyond its last row's mask
+        for (MatmulPlan *pl : {&p->scores, &p->values}) {
+            if (!pl->swapped && !pl->g.streamk) {
+                pl->g.causal_mode = pl == &p->scores ? 1u : 2u;
+                pl->g.causal_seq = s.seq, pl->g.causal_total = s.total;
+            }
+        }
+    }
     if (!ok) {
         attn_prefill_destroy(p);
         return nullptr;

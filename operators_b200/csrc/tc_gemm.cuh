@@ -68,7 +68,24 @@ struct GemmParams {
     uint16_t *c;
     int64_t c_lane_stride, c_col_stride, c_batch_stride;// element strides of D's lane index / column index / batch
     float alpha, beta;
+    // Causal structure of attention (rows = new tokens, row r sees columns j <= causal_total - causal_seq + r):
+    // mode 1 (scores: D's columns are cached tokens) skips tiles that lie wholly behind the mask, nobody reads them;
+    // mode 2 (values: k runs over cached tokens) stops a tile's k range where its last row's mask begins, the
+    // probabilities behind it are exact zeros.  Not combined with the transposed orientation or stream-K.
+    uint32_t causal_mode, causal_seq, causal_total;
 };
+
+// k-blocks (pipeline steps) tile (tm, tn) of `rows` x `cols` needs: all of them, none, or a causal prefix.
+__device__ __forceinline__ uint32_t tile_kblocks(const GemmParams &p, uint32_t tm, uint32_t tn, uint32_t rows, uint32_t cols) {
+    if (p.causal_mode == 0) return p.kblocks;
+    uint32_t last_row = tm * rows + rows - 1;
+    if (last_row > p.causal_seq - 1) last_row = p.causal_seq - 1;
+    const uint32_t last_col = p.causal_total - p.causal_seq + last_row;// last visible column of the tile's last row
+    if (p.causal_mode == 1) return tn * cols > last_col ? 0u : p.kblocks;
+    const uint32_t per_step = kBK * p.kbs;
+    const uint32_t need = (last_col + per_step) / per_step;// ceil((last_col + 1) / per_step)
+    return need < p.kblocks ? need : p.kblocks;
+}
 
 // Everything below is device code and is compiled by the one translation unit that launches the kernel
 // (it defines B200_TC_GEMM_KERNEL before including this header); other files only need the types above.
@@ -189,6 +206,21 @@ __host__ __device__ inline uint32_t make_idesc(uint32_t m, uint32_t n, uint32_t 
 __device__ __forceinline__ float silu_f32(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }
 
 // ---------------------------------------------------------------- the kernel --
+// Tile order: within a batch entry, bands of kRasterRows tile rows are walked column by column, so the CTAs that
+// run at the same time share a few tile rows of P and a few tile columns of Q (about 16 + 9 tiles' worth of
+// operands for 148 tiles in flight, instead of a whole operand), which keeps both in L2.
+constexpr uint32_t kRasterRows = 16;
+__device__ __forceinline__ void tile_coords(const GemmParams &p, uint32_t tile, uint32_t &b, uint32_t &tm, uint32_t &tn) {
+    const uint32_t per_batch = p.tiles_m * p.tiles_n;
+    b = tile / per_batch;
+    const uint32_t r = tile - b * per_batch;
+    const uint32_t band = r / (kRasterRows * p.tiles_n);
+    const uint32_t in_band = r - band * (kRasterRows * p.tiles_n);
+    const uint32_t rows_here = min(kRasterRows, p.tiles_m - band * kRasterRows);
+    tn = in_band / rows_here;
+    tm = band * kRasterRows + (in_band - tn * rows_here);
+}
+
 struct WorkItem {
     uint32_t tile, kb0, kb1;// k-block range [kb0, kb1)
 };
@@ -199,6 +231,11 @@ __device__ __forceinline__ bool work_item(const GemmParams &p, uint32_t cta, uin
         const uint64_t t = (uint64_t) cta + (uint64_t) it * grid;
         if (t >= p.total_tiles) return false;
         w.tile = (uint32_t) t, w.kb0 = 0, w.kb1 = p.kblocks;
+        if (p.causal_mode != 0) {
+            uint32_t b, tm, tn;
+            tile_coords(p, w.tile, b, tm, tn);
+            w.kb1 = tile_kblocks(p, tm, tn, kBM, p.bn);// 0: the tile lies behind the causal mask and is skipped
+        }
         return true;
     }
     const uint64_t total = (uint64_t) p.total_tiles * p.kblocks;
@@ -214,21 +251,6 @@ __device__ __forceinline__ bool work_item(const GemmParams &p, uint32_t cta, uin
     w.kb0 = t0 < begin ? (uint32_t) (begin - t0) : 0u;
     w.kb1 = t0 + p.kblocks > end ? (uint32_t) (end - t0) : p.kblocks;
     return true;
-}
-
-// Tile order: within a batch entry, bands of kRasterRows tile rows are walked column by column, so the CTAs that
-// run at the same time share a few tile rows of P and a few tile columns of Q (about 16 + 9 tiles' worth of
-// operands for 148 tiles in flight, instead of a whole operand), which keeps both in L2.
-constexpr uint32_t kRasterRows = 16;
-__device__ __forceinline__ void tile_coords(const GemmParams &p, uint32_t tile, uint32_t &b, uint32_t &tm, uint32_t &tn) {
-    const uint32_t per_batch = p.tiles_m * p.tiles_n;
-    b = tile / per_batch;
-    const uint32_t r = tile - b * per_batch;
-    const uint32_t band = r / (kRasterRows * p.tiles_n);
-    const uint32_t in_band = r - band * (kRasterRows * p.tiles_n);
-    const uint32_t rows_here = min(kRasterRows, p.tiles_m - band * kRasterRows);
-    tn = in_band / rows_here;
-    tm = band * kRasterRows + (in_band - tn * rows_here);
 }
 
 // Final values of 16 consecutive columns of one lane, written to D.
@@ -370,7 +392,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (uint32_t it = 0; ok && work_item(p, blockIdx.x, gridDim.x, it, w); ++it) {
                 uint32_t b, tm, tn;
                 tile_coords(p, w.tile, b, tm, tn);
-                for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {
+                for (uint32_t kb = w.kb0; kb < w.kb1; ++kb) {// no pass for a tile behind the causal mask
                     if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -434,7 +456,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t stage = 0, phase = 0, acc_it = 0;
             WorkItem w;
             bool ok = true;
-            for (uint32_t it = 0; ok && work_item(p, blockIdx.x, gridDim.x, it, w); ++it, ++acc_it) {
+            for (uint32_t it = 0; ok && work_item(p, blockIdx.x, gridDim.x, it, w); ++it) {
+                if (w.kb1 <= w.kb0) continue;// a tile behind the causal mask: no accumulator, no epilogue
                 const uint32_t buf = acc_it & 1u;
                 if (!mbar_wait(&acc_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag)) break;
                 tc_fence_after();
@@ -463,6 +486,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (++stage == p.stages) stage = 0, phase ^= 1u;
                 }
                 if (ok) umma_commit(&acc_full[buf]);
+                ++acc_it;
             }
         }
         __syncwarp();
@@ -472,7 +496,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t epi_tid = (warp - 2) * 32 + lane;
         uint32_t acc_it = 0;
         WorkItem w;
-        for (uint32_t it = 0; work_item(p, blockIdx.x, gridDim.x, it, w); ++it, ++acc_it) {
+        for (uint32_t it = 0; work_item(p, blockIdx.x, gridDim.x, it, w); ++it) {
+            if (w.kb1 <= w.kb0) continue;
             const uint32_t buf = acc_it & 1u;
             uint32_t b, tm, tn;
             tile_coords(p, w.tile, b, tm, tn);
@@ -541,6 +566,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                         lane_row, tm, tn, b, xchg);
                 }
             }
+            ++acc_it;
         }
     }
 
@@ -668,7 +694,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 // the matching up half in the peer
                 const int32_t qrow = p.mode == kEpiSwiGLUCols ? (int32_t) (tn * 128 + rank * p.half_offset)
                                                               : (int32_t) (tn * 256 + rank * 128);
-                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                const uint32_t kbs_here = tile_kblocks(p, tm, tn, 256, kPairBN);// 0: behind the causal mask
+                for (uint32_t kb = 0; kb < kbs_here; ++kb) {
                     if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
                         ok = false;
                         break;
@@ -700,12 +727,16 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t idesc = make_idesc(256, kPairBN, p.p_major_mn, p.q_major_mn);
             uint32_t stage = 0, phase = 0, acc_it = 0, tile;
             bool ok = true;
-            for (uint32_t it = 0; ok && pair_tile(p, pair, pairs, it, tile); ++it, ++acc_it) {
+            for (uint32_t it = 0; ok && pair_tile(p, pair, pairs, it, tile); ++it) {
+                uint32_t b, tm, tn;
+                tile_coords(p, tile, b, tm, tn);
+                const uint32_t kbs_here = tile_kblocks(p, tm, tn, 256, kPairBN);
+                if (kbs_here == 0) continue;
                 const uint32_t buf = acc_it & 1u;
                 if (!mbar_wait(&acc_empty[buf], ((acc_it >> 1) & 1u) ^ 1u, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * kPairBN;
-                for (uint32_t kb = 0; kb < p.kblocks; ++kb) {
+                for (uint32_t kb = 0; kb < kbs_here; ++kb) {
                     if (!mbar_wait(&full[stage], phase, abort_flag)) {
                         ok = false;
                         break;
@@ -724,6 +755,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (++stage == p.stages) stage = 0, phase ^= 1u;
                 }
                 if (ok) umma_commit_pair(&acc_full[buf]);
+                ++acc_it;
             }
         }
         __syncwarp();
@@ -731,10 +763,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         // ------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
         const uint32_t quarter = warp & 3u;
         uint32_t acc_it = 0, tile;
-        for (uint32_t it = 0; pair_tile(p, pair, pairs, it, tile); ++it, ++acc_it) {
-            const uint32_t buf = acc_it & 1u;
+        for (uint32_t it = 0; pair_tile(p, pair, pairs, it, tile); ++it) {
             uint32_t b, tm, tn;
             tile_coords(p, tile, b, tm, tn);
+            if (tile_kblocks(p, tm, tn, 256, kPairBN) == 0) continue;
+            const uint32_t buf = acc_it & 1u;
             if (!mbar_wait(&acc_full[buf], (acc_it >> 1) & 1u, abort_flag)) break;
             tc_fence_after();
             const uint32_t lane_row = quarter * 32 + lane;
@@ -761,6 +794,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             tc_fence_before();
             mbar_arrive_remote(mapa_u32(smem_u32(&acc_empty[buf]), 0));
+            ++acc_it;
         }
     }
 
