@@ -47,8 +47,7 @@ __device__ __forceinline__ uint64_t visible_cols(uint64_t i, uint64_t seq_len, u
 // evaluation instead; measured, that is the faster of the two on B200.)
 //
 // Who owns a row: one warp, one CTA, or one thread-block cluster of 2, 4 or 8 CTAs whose maxima and sums meet
-// over distributed shared memory (rows of more than 32 Ki columns).  MAXT is the launch bound: the forms that
-// are launched with more than 512 threads must fit 64 registers per thread.
+// over distributed shared memory (rows of more than 32 Ki columns).
 enum RowOwner { WARP_ROW = 0, CTA_ROW = 1, CLUSTER_ROW = 2 };
 
 // packed maximum of two 16-bit pairs
@@ -60,10 +59,9 @@ __device__ __forceinline__ uint32_t max2_packed(uint32_t a, uint32_t b) {
     return r;
 }
 
-template<int VPT, int OWNER, int MAXT, int DT>
-__global__ void __launch_bounds__(MAXT)
-    causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total, uint32_t vecs,
-                               int64_t stride_b, int64_t stride_i, FastDiv seq_div) {
+template<int VPT, int OWNER, int DT>
+__device__ __forceinline__ void causal_softmax_regs_body(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total,
+                                                         uint32_t vecs, int64_t stride_b, int64_t stride_i, FastDiv seq_div) {
     __shared__ float red_m[32], red_s[32];// one slot array per reduction of a row: one barrier each
     __shared__ float part_m, part_s;      // this CTA's maximum and sum, read by the whole cluster
     const int lane = threadIdx.x & 31;
@@ -156,6 +154,21 @@ __global__ void __launch_bounds__(MAXT)
     }
 }
 
+// Two kernels around the one body: without a launch bound for up to 512 threads (the compiler's own register
+// choice), bounded to 1024 threads (64 registers) for the forms launched with more.
+template<int VPT, int OWNER, int MAXT, int DT>
+__global__ void causal_softmax_regs_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total, uint32_t vecs,
+                                           int64_t stride_b, int64_t stride_i, FastDiv seq_div) {
+    static_assert(MAXT <= 512, "launches of more than 512 threads use causal_softmax_regs_kernel_1024");
+    causal_softmax_regs_body<VPT, OWNER, DT>(y, rows, seq_len, total, vecs, stride_b, stride_i, seq_div);
+}
+template<int VPT, int OWNER, int DT>
+__global__ void __launch_bounds__(1024)
+    causal_softmax_regs_kernel_1024(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total, uint32_t vecs,
+                                    int64_t stride_b, int64_t stride_i, FastDiv seq_div) {
+    causal_softmax_regs_body<VPT, OWNER, DT>(y, rows, seq_len, total, vecs, stride_b, stride_i, seq_div);
+}
+
 // Any alignment, any column stride, any row length: one CTA per row, three
 // passes (max / sum / write), the later ones served by L2.
 template<int DT>
@@ -186,8 +199,9 @@ __global__ void causal_softmax_generic_kernel(uint16_t *y, uint64_t rows, uint64
     }
 }
 
+// false: no register-resident kernel fits this shape (the caller takes the three-pass kernel)
 template<int VPT, int DT>
-void launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, uint16_t *y,
+bool launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, uint16_t *y,
                  cudaStream_t st) {
     const uint64_t rows = d->batch * d->seq_len;
     const FastDiv seq_div(d->seq_len <= 0xFFFFFFFFull && d->seq_len > 0 ? (uint32_t) d->seq_len : 1u);
@@ -196,25 +210,31 @@ void launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uin
         const uint32_t grid = (uint32_t) (rows < cap ? rows : cap) * cl;
         if (cl > 1) {
             if constexpr (VPT == 4) {// clusters always hold four vectors per thread
-                launch_cluster(causal_softmax_regs_kernel<4, CLUSTER_ROW, 1024, DT>, grid, threads, cl, st, y, rows,
+                launch_cluster(causal_softmax_regs_kernel_1024<4, CLUSTER_ROW, DT>, grid, threads, cl, st, y, rows,
                                d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
+                return true;
             }
-        } else if (threads > 512) {
-            if constexpr (VPT <= 4) {// eight vectors per thread never need more than 512 threads
-                causal_softmax_regs_kernel<VPT, CTA_ROW, 1024, DT>
-                    <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
-            }
-        } else {
+            return false;
+        }
+        if (threads <= 512 && fits_register_file<causal_softmax_regs_kernel<VPT, CTA_ROW, 512, DT>>(threads)) {
             causal_softmax_regs_kernel<VPT, CTA_ROW, 512, DT>
                 <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
+            return true;
         }
-    } else {
-        const uint64_t ctas = (rows + 7) / 8;
-        const uint64_t cap = 0x7FFFFFFFull;
-        const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-        causal_softmax_regs_kernel<VPT, WARP_ROW, 256, DT>
-            <<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
+        if constexpr (VPT <= 4) {// bounded to 64 registers: any block size
+            causal_softmax_regs_kernel_1024<VPT, CTA_ROW, DT>
+                <<<grid, threads, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
+            return true;
+        }
+        return false;
     }
+    const uint64_t ctas = (rows + 7) / 8;
+    const uint64_t cap = 0x7FFFFFFFull;
+    const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
+    if (!fits_register_file<causal_softmax_regs_kernel<VPT, WARP_ROW, 256, DT>>(256)) return false;
+    causal_softmax_regs_kernel<VPT, WARP_ROW, 256, DT>
+        <<<grid, 256, 0, st>>>(y, rows, d->seq_len, d->total, vecs, d->stride_b, d->stride_i, seq_div);
+    return true;
 }
 
 }// namespace
@@ -289,22 +309,19 @@ INFINIOP_API infiniopStatus_t infiniopCausalSoftmax(infiniopCausalSoftmaxDescrip
             const RowLaunch shape = row_launch_shape(vecs, big ? (vecs >= 2048 ? 8 : 4) : 1);
             vpt = shape.vpt, threads = shape.threads, cl = shape.cl;
         }
+        bool launched;
         if (d->dt == kBF16) {
-            switch (vpt) {
-                case 1: launch_regs<1, kBF16>(d, cta_row, threads, cl, vecs, y, st); break;
-                case 2: launch_regs<2, kBF16>(d, cta_row, threads, cl, vecs, y, st); break;
-                case 4: launch_regs<4, kBF16>(d, cta_row, threads, cl, vecs, y, st); break;
-                default: launch_regs<8, kBF16>(d, cta_row, threads, cl, vecs, y, st); break;
-            }
+            launched = vpt == 1 ? launch_regs<1, kBF16>(d, cta_row, threads, cl, vecs, y, st)
+                     : vpt == 2 ? launch_regs<2, kBF16>(d, cta_row, threads, cl, vecs, y, st)
+                     : vpt == 4 ? launch_regs<4, kBF16>(d, cta_row, threads, cl, vecs, y, st)
+                                : launch_regs<8, kBF16>(d, cta_row, threads, cl, vecs, y, st);
         } else {
-            switch (vpt) {
-                case 1: launch_regs<1, kF16>(d, cta_row, threads, cl, vecs, y, st); break;
-                case 2: launch_regs<2, kF16>(d, cta_row, threads, cl, vecs, y, st); break;
-                case 4: launch_regs<4, kF16>(d, cta_row, threads, cl, vecs, y, st); break;
-                default: launch_regs<8, kF16>(d, cta_row, threads, cl, vecs, y, st); break;
-            }
+            launched = vpt == 1 ? launch_regs<1, kF16>(d, cta_row, threads, cl, vecs, y, st)
+                     : vpt == 2 ? launch_regs<2, kF16>(d, cta_row, threads, cl, vecs, y, st)
+                     : vpt == 4 ? launch_regs<4, kF16>(d, cta_row, threads, cl, vecs, y, st)
+                                : launch_regs<8, kF16>(d, cta_row, threads, cl, vecs, y, st);
         }
-        return check_launch("causal_softmax");
+        if (launched) return check_launch("causal_softmax");
     }
     const uint64_t cap = (uint64_t) d->sm_count * 8;
     const uint32_t grid = (uint32_t) (rows < cap ? rows : cap);

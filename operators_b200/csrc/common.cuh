@@ -284,6 +284,23 @@ static inline cudaError_t launch_cluster(void (*kernel)(KArgs...), uint32_t grid
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Does a block of `threads` threads of this kernel fit the SM's 65536 registers?  (Kernels without a launch bound
+// are compiled with whatever register count serves them best; the launch shapes are checked against it here
+// instead of trusting a table.)  One query per kernel and process.
+template<auto Kernel>
+static inline bool fits_register_file(uint32_t threads) {
+    static const int regs = [] {
+        cudaFuncAttributes a;
+        if (cudaFuncGetAttributes(&a, Kernel) != cudaSuccess) {
+            cudaGetLastError();
+            return 255;
+        }
+        return a.numRegs;
+    }();
+    const uint32_t per_thread = ((uint32_t) regs + 7u) / 8u * 8u;// allocation granularity
+    return per_thread * ((threads + 31u) / 32u * 32u) <= 65536u;
+}
+
 // Shape of a launch that gives each row to one CTA or to one cluster: `cl` CTAs of `threads` threads, each
 // thread holding `vpt` 128-bit vectors.  `want_vpt` is the preferred vectors per thread (bytes in flight when
 // there are many rows).  One CTA holds rows of up to 4096 vectors (512 threads x 8 or 1024 x 4; measured on

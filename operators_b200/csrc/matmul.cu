@@ -271,6 +271,7 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
     g.p_batch_mul = pl.p.batch_stride == 0 ? 0 : 1, g.q_batch_mul = pl.q.batch_stride == 0 ? 0 : 1;
     g.p_batch_div = pl.p.batch_div, g.q_batch_div = pl.q.batch_div;
     g.tiles_m = (g.mp + tc::kBM - 1) / tc::kBM;
+    g.p_tiles = 1;
     pl.p_box_rows = tc::kBM;
     const uint32_t gran = g.q_major_mn ? 64u : 16u;// MN-major tiles come in 64-row TMA boxes
     uint32_t bn;
@@ -283,10 +284,10 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
         g.half_offset = n_out;
         g.np = n_out;
     } else {
-        if (g.mode == tc::kEpiSwiGLULanes) {// a tile = 64 features: their gate rows on lanes 0-63, their up rows on 64-127
+        if (g.mode == tc::kEpiSwiGLULanes) {// a tile = 128 features: gate rows and up rows feed two accumulators
             g.mp = n_out, g.half_offset = n_out;
-            g.tiles_m = (n_out + tc::kBM / 2 - 1) / (tc::kBM / 2);
-            pl.p_box_rows = tc::kBM / 2;
+            g.tiles_m = (n_out + tc::kBM - 1) / tc::kBM;
+            g.p_tiles = 2;
         }
         const uint32_t np_round = (g.np + gran - 1) / gran * gran;
         bn = np_round < 256 ? np_round : 256;
@@ -309,12 +310,12 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
         pl.q_box_rows = bn;
     }
     const uint32_t q_bytes = g.q_boxes * g.q_box_bytes;
-    const uint32_t sub_bytes = tc::kPBytes + ((q_bytes + 1023u) & ~1023u);
+    const uint32_t sub_bytes = g.p_tiles * tc::kPBytes + ((q_bytes + 1023u) & ~1023u);
     const uint32_t budget = (uint32_t) h->max_smem_optin - 8192u;// alignment slack, barriers, the epilogue's hand-over buffer
     // Narrow tiles are weight streaming: four 64-wide k-blocks per pipeline step, so that a step asks for 512
     // contiguous bytes of every weight row at once (measured on [16, 4096] x [4096, 28672]: 51.8 / 51.2 / 48.5 us
     // with one / two / four k-blocks per step)
-    g.kbs = bn <= 64 && budget / (4 * sub_bytes) >= 3 ? 4u : 1u;
+    g.kbs = bn > 64 ? 1u : budget / (4 * sub_bytes) >= 3 ? 4u : budget / (2 * sub_bytes) >= 3 ? 2u : 1u;
     g.kblocks = (pl.k + tc::kBK * g.kbs - 1) / (tc::kBK * g.kbs);
     const uint32_t stage_bytes = g.kbs * sub_bytes;
     uint32_t stages = budget / stage_bytes;
@@ -330,7 +331,7 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
         if (total_work < grid) grid = (uint32_t) total_work;
         g.work_per_cta = (uint32_t) ((total_work + grid - 1) / grid);
         grid = (uint32_t) ((total_work + g.work_per_cta - 1) / g.work_per_cta);
-        pl.partials_bytes = (uint64_t) grid * 2ull * tc::kBM * bn * 4ull;
+        pl.partials_bytes = (uint64_t) grid * 2ull * tc::kBM * (g.p_tiles * bn) * 4ull;
         pl.counters_bytes = ((uint64_t) g.total_tiles * 4 + 255) / 256 * 256;
         pl.workspace_bytes = pl.partials_bytes + pl.counters_bytes + 256;
         pl.counter_slot = g.total_tiles <= kSlotCounters ? counter_slot_acquire() : -1;

@@ -117,12 +117,12 @@ __device__ __forceinline__ float rms_prod(ScaleF2 k, float x, float w) {
 // cluster (the CTAs' partial sums meet over distributed shared memory).
 enum RowOwner { WARP_ROW = 0, CTA_ROW = 1, CLUSTER_ROW = 2 };
 
-// VPT vectors (8 halves each) per thread.  MAXT is the launch bound: the row-per-CTA forms that are launched
-// with more than 512 threads must fit 64 registers per thread.
-template<int VPT, bool W_F16, int OWNER, bool FUSED, int MAXT, int DT>
-__global__ void __launch_bounds__(MAXT)
-    rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs, uint64_t d,
-                         int64_t stride_y, int64_t stride_x, float eps, Residual res) {
+// VPT vectors (8 halves each) per thread.  The body is shared by two kernels: one without a launch bound (up to
+// 512 threads: the compiler's own register choice, measured faster than any bound) and one bounded to 1024
+// threads = 64 registers per thread for the forms that are launched with more than 512.
+template<int VPT, bool W_F16, int OWNER, bool FUSED, int DT>
+__device__ __forceinline__ void rms_norm_regs_body(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs,
+                                                   uint64_t d, int64_t stride_y, int64_t stride_x, float eps, Residual res) {
     __shared__ float red[32];
     __shared__ float part;// this CTA's partial sum, read by the whole cluster
     const int lane = threadIdx.x & 31;
@@ -213,6 +213,19 @@ __global__ void __launch_bounds__(MAXT)
     }
 }
 
+template<int VPT, bool W_F16, int OWNER, bool FUSED, int MAXT, int DT>
+__global__ void rms_norm_regs_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs, uint64_t d,
+                                     int64_t stride_y, int64_t stride_x, float eps, Residual res) {
+    static_assert(MAXT <= 512, "launches of more than 512 threads use rms_norm_regs_kernel_1024");
+    rms_norm_regs_body<VPT, W_F16, OWNER, FUSED, DT>(y, x, w, n, vecs, d, stride_y, stride_x, eps, res);
+}
+template<int VPT, bool W_F16, int OWNER, bool FUSED, int DT>
+__global__ void __launch_bounds__(1024)
+    rms_norm_regs_kernel_1024(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs, uint64_t d,
+                              int64_t stride_y, int64_t stride_x, float eps, Residual res) {
+    rms_norm_regs_body<VPT, W_F16, OWNER, FUSED, DT>(y, x, w, n, vecs, d, stride_y, stride_x, eps, res);
+}
+
 // Any alignment, any d: one CTA per row, two passes over x (the second one is
 // served by L2).
 template<bool W_F16, bool FUSED, int DT>
@@ -250,8 +263,9 @@ __global__ void rms_norm_generic_kernel(uint16_t *y, const uint16_t *x, const vo
     }
 }
 
+// false: no register-resident kernel fits this shape (the caller takes the two-pass kernel)
 template<int VPT, bool W_F16, bool FUSED, int DT>
-void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, void *y,
+bool launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, void *y,
                  const void *x, const void *w, Residual res, cudaStream_t st) {
     auto *yp = reinterpret_cast<uint16_t *>(y);
     auto *xp = reinterpret_cast<const uint16_t *>(x);
@@ -260,35 +274,41 @@ void launch_regs(const RMSNormDesc *d, bool cta_row, uint32_t threads, uint32_t 
         const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap) * cl;
         if (cl > 1) {
             if constexpr (VPT == 4) {// clusters always hold four vectors per thread
-                launch_cluster(rms_norm_regs_kernel<4, W_F16, CLUSTER_ROW, FUSED, 1024, DT>, grid, threads, cl, st, yp, xp, w,
+                launch_cluster(rms_norm_regs_kernel_1024<4, W_F16, CLUSTER_ROW, FUSED, DT>, grid, threads, cl, st, yp, xp, w,
                                d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+                return true;
             }
-        } else if (threads > 512) {
-            if constexpr (VPT <= 4) {// eight vectors per thread never need more than 512 threads
-                rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED, 1024, DT>
-                    <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
-            }
-        } else {
+            return false;
+        }
+        if (threads <= 512 && fits_register_file<rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED, 512, DT>>(threads)) {
             rms_norm_regs_kernel<VPT, W_F16, CTA_ROW, FUSED, 512, DT>
                 <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+            return true;
         }
-    } else {
-        const uint64_t ctas = (d->n + 7) / 8;
-        const uint64_t cap = 0x7FFFFFFFull;
-        const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
-        rms_norm_regs_kernel<VPT, W_F16, WARP_ROW, FUSED, 256, DT>
-            <<<grid, 256, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+        if constexpr (VPT <= 4) {// bounded to 64 registers: any block size
+            rms_norm_regs_kernel_1024<VPT, W_F16, CTA_ROW, FUSED, DT>
+                <<<grid, threads, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+            return true;
+        }
+        return false;
     }
+    const uint64_t ctas = (d->n + 7) / 8;
+    const uint64_t cap = 0x7FFFFFFFull;
+    const uint32_t grid = (uint32_t) (ctas < cap ? ctas : cap);
+    if (!fits_register_file<rms_norm_regs_kernel<VPT, W_F16, WARP_ROW, FUSED, 256, DT>>(256)) return false;
+    rms_norm_regs_kernel<VPT, W_F16, WARP_ROW, FUSED, 256, DT>
+        <<<grid, 256, 0, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x, d->epsilon, res);
+    return true;
 }
 
 template<bool W_F16, bool FUSED, int DT>
-void dispatch_regs(const RMSNormDesc *d, int vpt, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, void *y,
+bool dispatch_regs(const RMSNormDesc *d, int vpt, bool cta_row, uint32_t threads, uint32_t cl, uint32_t vecs, void *y,
                    const void *x, const void *w, Residual res, cudaStream_t st) {
     switch (vpt) {
-        case 1: launch_regs<1, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
-        case 2: launch_regs<2, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
-        case 4: launch_regs<4, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
-        default: launch_regs<8, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st); break;
+        case 1: return launch_regs<1, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st);
+        case 2: return launch_regs<2, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st);
+        case 4: return launch_regs<4, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st);
+        default: return launch_regs<8, W_F16, FUSED, DT>(d, cta_row, threads, cl, vecs, y, x, w, res, st);
     }
 }
 
@@ -325,14 +345,15 @@ infiniopStatus_t run(const RMSNormDesc *d, void *y, const void *x, const void *w
             const RowLaunch shape = row_launch_shape(vecs, big ? (FUSED ? 2 : 4) : 1);
             vpt = shape.vpt, threads = shape.threads, cl = shape.cl;
         }
+        bool launched;
         if (d->dt == kBF16) {
-            if (d->w_f16) dispatch_regs<true, FUSED, kBF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
-            else dispatch_regs<false, FUSED, kBF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
+            launched = d->w_f16 ? dispatch_regs<true, FUSED, kBF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st)
+                                : dispatch_regs<false, FUSED, kBF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
         } else {
-            if (d->w_f16) dispatch_regs<true, FUSED, kF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
-            else dispatch_regs<false, FUSED, kF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
+            launched = d->w_f16 ? dispatch_regs<true, FUSED, kF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st)
+                                : dispatch_regs<false, FUSED, kF16>(d, vpt, cta_row, threads, cl, vecs, y, x, w, res, st);
         }
-        return check_launch("rms_norm");
+        if (launched) return check_launch("rms_norm");
     }
     const uint64_t cap = (uint64_t) d->sm_count * 8;
     const uint32_t grid = (uint32_t) (d->n < cap ? d->n : cap);

@@ -39,14 +39,16 @@ constexpr int kUmmaK = 16;      // k per tcgen05.mma (kind::f16)
 constexpr uint32_t kPBytes = kBM * kBK * 2;// 16 KiB per stage for P
 constexpr long long kWaitBudget = 400ll * 1000 * 1000;// clock64 ticks (~0.2 s) before a wait gives up
 
-// kEpiSwiGLUCols: Q tiles hold [gate columns | matching up columns]; kEpiSwiGLULanes (transposed products): P
-// tiles hold 64 gate rows on lanes 0-63 and the matching 64 up rows on lanes 64-127.
+// kEpiSwiGLUCols: Q tiles hold [gate columns | matching up columns]; kEpiSwiGLULanes (transposed products): a tile
+// is 128 features, their gate rows and their up rows of P feed two accumulators side by side in TMEM (p_tiles = 2),
+// so a lane finds gate and up of its feature in its own columns.
 enum EpilogueMode { kEpiPlain = 0, kEpiSwiGLUCols = 1, kEpiSwiGLULanes = 2 };
 
 struct GemmParams {
     uint32_t mp, np, k;       // problem in MMA orientation
     uint32_t batch;
     uint32_t tiles_m, tiles_n;// per batch
+    uint32_t p_tiles;         // 128-row tiles of P per k-block: 1, or 2 in lane-mode SwiGLU (gate rows, up rows)
     uint32_t kbs;             // 64-wide k-blocks per pipeline stage (1, 2 or 4)
     uint32_t kblocks;         // pipeline steps over k: ceil(k / (64 * kbs))
     uint32_t total_tiles;
@@ -284,7 +286,7 @@ __device__ __forceinline__ void store_cols16(const GemmParams &p, const float *a
 // column c of the tile (from TMEM, or from the summed stream-K partials).
 template<typename Load16>
 __device__ __forceinline__ void finish_tile(const GemmParams &p, Load16 load16, uint32_t lane_row, uint32_t tm,
-                                            uint32_t tn, uint32_t b, float *xchg) {
+                                            uint32_t tn, uint32_t b) {
     if (p.mode == kEpiSwiGLUCols) {
         const uint32_t half = p.bn / 2, row = tm * kBM + lane_row;
         for (uint32_t c0 = 0; c0 < half; c0 += 16) {
@@ -300,26 +302,17 @@ __device__ __forceinline__ void finish_tile(const GemmParams &p, Load16 load16, 
             store_cols16(p, gate, row, tn * half + c0, b, p.mp, p.half_offset, 1.f, 0.f);
         }
     } else if (p.mode == kEpiSwiGLULanes) {
-        // lanes 64..127 hand their (up) values to lanes 0..63 through shared memory; all four warps pass every barrier
-        const uint32_t feature = tm * (kBM / 2) + (lane_row & 63u);
+        const uint32_t feature = tm * kBM + lane_row;// columns [0, bn): gate, [bn, 2 bn): up, both of this feature
         for (uint32_t c0 = 0; c0 < p.bn; c0 += 16) {
-            float v[16];
-            load16(c0, v);
-            if (lane_row >= 64) {
+            float gate[16], up[16];
+            load16(c0, gate);
+            load16(p.bn + c0, up);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) xchg[(lane_row - 64) * 17 + j] = v[j];
+            for (int j = 0; j < 16; ++j) {
+                const float g = f16_to_f32(f32_to_f16_ref(gate[j])), u = f16_to_f32(f32_to_f16_ref(up[j]));
+                gate[j] = __fmul_rn(u, silu_f32(g));
             }
-            asm volatile("bar.sync 2, 128;" ::: "memory");
-            if (lane_row < 64) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float g = f16_to_f32(f32_to_f16_ref(v[j]));
-                    const float u = f16_to_f32(f32_to_f16_ref(xchg[lane_row * 17 + j]));
-                    v[j] = __fmul_rn(u, silu_f32(g));
-                }
-                store_cols16(p, v, feature, tn * p.bn + c0, b, p.half_offset, p.np, 1.f, 0.f);// result rows = features
-            }
-            asm volatile("bar.sync 2, 128;" ::: "memory");
+            store_cols16(p, gate, feature, tn * p.bn + c0, b, p.half_offset, p.np, 1.f, 0.f);// result rows = features
         }
     } else {
         const uint32_t row = tm * kBM + lane_row;
@@ -338,17 +331,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     // carve: stages of (P tile, Q tile), 1024-byte aligned; then barriers and flags
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
     const uint32_t q_bytes = p.q_boxes * p.q_box_bytes;
-    const uint32_t sub_bytes = kPBytes + ((q_bytes + 1023u) & ~1023u);// one 64-wide k-block of P and Q
+    const uint32_t p_bytes = p.p_tiles * kPBytes;
+    const uint32_t sub_bytes = p_bytes + ((q_bytes + 1023u) & ~1023u);// one 64-wide k-block of P and Q
     const uint32_t stage_bytes = p.kbs * sub_bytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t) p.stages * stage_bytes);
     uint64_t *full = bars, *empty = bars + p.stages, *acc_full = bars + 2 * p.stages, *acc_empty = acc_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     uint32_t *last_flag = tmem_slot + 2;
-    float *xchg = reinterpret_cast<float *>(tmem_slot + 4);// 64 x 17 floats: the lane-mode SwiGLU hand-over
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t acc_cols = p.bn;                               // fp32 columns per accumulator buffer
+    const uint32_t acc_cols = p.p_tiles * p.bn;                   // fp32 columns per accumulator buffer
     uint32_t tmem_cols = 32;
     while (tmem_cols < 2 * acc_cols) tmem_cols <<= 1;
 
@@ -398,31 +391,26 @@ __global__ void __launch_bounds__(kThreads, 1)
                         break;
                     }
                     unsigned char *sbase = smem + (size_t) stage * stage_bytes;
-                    mbar_expect_tx(&full[stage], p.kbs * (kPBytes + q_bytes));
+                    mbar_expect_tx(&full[stage], p.kbs * (p_bytes + q_bytes));
                     const int32_t pb = (int32_t) (b / p.p_batch_div) * p.p_batch_mul, qb = (int32_t) (b / p.q_batch_div) * p.q_batch_mul;
                     // P first: the boxes of one step continue each other's rows in memory, so their requests reach
                     // the memory system together (256 or 512 contiguous bytes per row instead of 128)
                     for (uint32_t sub = 0; sub < p.kbs; ++sub) {
                         unsigned char *sp = sbase + (size_t) sub * sub_bytes;
                         const int32_t k0 = (int32_t) ((kb * p.kbs + sub) * kBK);
-                        if (p.mode == kEpiSwiGLULanes) {// 64 gate rows, then the matching 64 up rows
-                            const int32_t r0 = (int32_t) (tm * (kBM / 2)), r1 = r0 + (int32_t) p.half_offset;
+                        for (uint32_t t = 0; t < p.p_tiles; ++t) {// lane-mode SwiGLU: the gate rows, then the up rows
+                            unsigned char *dst = sp + (size_t) t * kPBytes;
+                            const int32_t r0 = (int32_t) (tm * kBM + t * p.half_offset);
                             if (!p.p_major_mn) {
-                                tma_load_3d(sp, &map_p, &full[stage], k0, r0, pb);
-                                tma_load_3d(sp + kPBytes / 2, &map_p, &full[stage], k0, r1, pb);
+                                tma_load_3d(dst, &map_p, &full[stage], k0, r0, pb);
                             } else {
-                                tma_load_3d(sp, &map_p, &full[stage], r0, k0, pb);
-                                tma_load_3d(sp + kPBytes / 2, &map_p, &full[stage], r1, k0, pb);
+                                tma_load_3d(dst, &map_p, &full[stage], r0, k0, pb);
+                                tma_load_3d(dst + kPBytes / 2, &map_p, &full[stage], r0 + 64, k0, pb);
                             }
-                        } else if (!p.p_major_mn) {
-                            tma_load_3d(sp, &map_p, &full[stage], k0, (int32_t) (tm * kBM), pb);
-                        } else {
-                            tma_load_3d(sp, &map_p, &full[stage], (int32_t) (tm * kBM), k0, pb);
-                            tma_load_3d(sp + kPBytes / 2, &map_p, &full[stage], (int32_t) (tm * kBM + 64), k0, pb);
                         }
                     }
                     for (uint32_t sub = 0; sub < p.kbs; ++sub) {
-                        unsigned char *sq = sbase + (size_t) sub * sub_bytes + kPBytes;
+                        unsigned char *sq = sbase + (size_t) sub * sub_bytes + p_bytes;
                         const int32_t k0 = (int32_t) ((kb * p.kbs + sub) * kBK);
                         if (p.mode == kEpiSwiGLUCols) {
                             // Q tile = gate columns [tn * bn/2, +bn/2) followed by the matching up columns
@@ -469,17 +457,21 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                     tc_fence_after();
                     for (uint32_t sub = 0; sub < p.kbs; ++sub) {
-                        const uint32_t sp = smem_u32(smem + (size_t) stage * stage_bytes + (size_t) sub * sub_bytes);
-                        const uint32_t sq = sp + kPBytes;
+                        const uint32_t sp0 = smem_u32(smem + (size_t) stage * stage_bytes + (size_t) sub * sub_bytes);
+                        const uint32_t sq = sp0 + p_bytes;
+                        for (uint32_t t = 0; t < p.p_tiles; ++t) {
+                            const uint32_t sp = sp0 + t * kPBytes;
 #pragma unroll
-                        for (uint32_t j = 0; j < kBK / kUmmaK; ++j) {
-                            // K-major: 16 k = 32 bytes further along the swizzled 128-byte rows, 8-row groups 1024 bytes
-                            // apart.  MN-major: 16 k = two 8-row groups of 1024 bytes; 64-row atoms one TMA box apart.
-                            const uint64_t da = p.p_major_mn ? make_smem_desc(sp + j * 2048u, kPBytes / 2, 1024)
-                                                             : make_smem_desc(sp + j * 32u, 16, 1024);
-                            const uint64_t db = p.q_major_mn ? make_smem_desc(sq + j * 2048u, p.q_box_bytes, 1024)
-                                                             : make_smem_desc(sq + j * 32u, 16, 1024);
-                            umma_f16(d_tmem, da, db, idesc, (kb > w.kb0 || sub > 0 || j > 0) ? 1u : 0u);
+                            for (uint32_t j = 0; j < kBK / kUmmaK; ++j) {
+                                // K-major: 16 k = 32 bytes further along the swizzled 128-byte rows, 8-row groups 1024
+                                // bytes apart.  MN-major: 16 k = two 8-row groups of 1024 bytes; 64-row atoms one TMA
+                                // box apart.
+                                const uint64_t da = p.p_major_mn ? make_smem_desc(sp + j * 2048u, kPBytes / 2, 1024)
+                                                                 : make_smem_desc(sp + j * 32u, 16, 1024);
+                                const uint64_t db = p.q_major_mn ? make_smem_desc(sq + j * 2048u, p.q_box_bytes, 1024)
+                                                                 : make_smem_desc(sq + j * 32u, 16, 1024);
+                                umma_f16(d_tmem + t * p.bn, da, db, idesc, (kb > w.kb0 || sub > 0 || j > 0) ? 1u : 0u);
+                            }
                         }
                     }
                     umma_commit(&empty[stage]);// the stage may be refilled once these MMAs have read it
@@ -505,24 +497,23 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
             const uint32_t lane_row = quarter * 32 + lane;
             // does this lane hold a row of the matrix (lane mode: a feature below the intermediate size)?
-            const bool row_valid = p.mode == kEpiSwiGLULanes ? tm * (kBM / 2) + (lane_row & 63u) < p.half_offset
-                                                             : tm * kBM + lane_row < p.mp;
+            const bool row_valid = tm * kBM + lane_row < p.mp;
             const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * acc_cols;
             const bool partial = p.streamk && !(w.kb0 == 0 && w.kb1 == p.kblocks);
             if (!partial) {
-                finish_tile(p, [&](uint32_t c, float *v) { tmem_ld16(taddr + c, v); }, lane_row, tm, tn, b, xchg);
+                finish_tile(p, [&](uint32_t c, float *v) { tmem_ld16(taddr + c, v); }, lane_row, tm, tn, b);
                 tc_fence_before();
                 mbar_arrive(&acc_empty[buf]);
             } else {
                 // part of a tile's k range: park the fp32 partial, count this CTA on the tile, and let the CTA
                 // that arrives last add all parts in CTA order
                 const uint32_t slot = w.kb0 == 0 ? 1u : 0u;// a part that starts mid-tile opens the CTA's range (slot 0)
-                float *mine = p.partials + ((size_t) blockIdx.x * 2 + slot) * (size_t) (kBM * p.bn);
-                for (uint32_t c0 = 0; c0 < p.bn; c0 += 16) {
+                float *mine = p.partials + ((size_t) blockIdx.x * 2 + slot) * (size_t) (kBM * acc_cols);
+                for (uint32_t c0 = 0; c0 < acc_cols; c0 += 16) {
                     float acc[16];
                     tmem_ld16(taddr + c0, acc);// all lanes of the warp take part in the load
                     if (row_valid) {           // rows beyond the matrix are never read back
-                        float4 *dst = reinterpret_cast<float4 *>(mine + (size_t) lane_row * p.bn + c0);
+                        float4 *dst = reinterpret_cast<float4 *>(mine + (size_t) lane_row * acc_cols + c0);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) __stcg(dst + j, make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
                     }
@@ -554,8 +545,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                                 // CTA `cta`'s part of this tile starts mid-tile exactly when its range starts inside the tile
                                 const uint64_t cb = (uint64_t) cta * p.work_per_cta;
                                 const uint32_t s = cb > t0 ? 0u : 1u;
-                                const float *src = p.partials + ((size_t) cta * 2 + s) * (size_t) (kBM * p.bn) +
-                                                   (size_t) lane_row * p.bn + c;
+                                const float *src = p.partials + ((size_t) cta * 2 + s) * (size_t) (kBM * acc_cols) +
+                                                   (size_t) lane_row * acc_cols + c;
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
                                     const float4 v = __ldcg(reinterpret_cast<const float4 *>(src) + j);
@@ -563,7 +554,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                                 }
                             }
                         },
-                        lane_row, tm, tn, b, xchg);
+                        lane_row, tm, tn, b);
                 }
             }
             ++acc_it;

@@ -959,6 +959,34 @@ def test_attention(oracle, cuda_lib, attention_kernels, nh, nkvh, seq, dh, pos, 
     assert torch.equal(kcd.cpu(), k_cache) and torch.equal(vcd.cpu(), v_cache)  # the oracle updated the host caches
 
 
+@pytest.mark.parametrize("nh,nkvh,seq,dh,pos", [(8, 2, 1024, 128, 0), (8, 4, 600, 64, 1000), (4, 1, 1536, 128, 512)])
+def test_attention_long_prefill_against_float32(cuda_lib, nh, nkvh, seq, dh, pos):
+    """Token counts at which the products run on CTA pairs with the causal tile skipping (several 256-row blocks per
+    head).  The oracle would take minutes here, so the check is against a float32 evaluation of the same
+    composite on the GPU (scores, causal mask, softmax, values) with a tolerance that covers the two fp16
+    roundings in between; the smaller cases of test_attention pin the same path to the oracle."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(23)
+    total = pos + seq
+    q = torch.randn((nh, seq, dh), generator=g).half().to(DEV)
+    k = torch.randn((nkvh, seq, dh), generator=g).half().to(DEV)
+    v = torch.randn((nkvh, seq, dh), generator=g).half().to(DEV)
+    kc = torch.randn((nkvh, total, dh), generator=g).half().to(DEV)
+    vc = torch.randn((nkvh, total, dh), generator=g).half().to(DEV)
+    out = torch.zeros((seq, nh, dh), dtype=torch.float16, device=DEV)
+    ops.attention(lib, handle, out, q, k, v, kc, vc, pos)
+    torch.cuda.synchronize()
+    assert torch.equal(kc[:, pos:], k) and torch.equal(vc[:, pos:], v)
+    group = nh // nkvh
+    kf, vf = kc.float().repeat_interleave(group, 0), vc.float().repeat_interleave(group, 0)
+    scores = torch.einsum("hsd,htd->hst", q.float(), kf) / dh ** 0.5
+    cols, rows = torch.arange(total, device=DEV)[None, None, :], torch.arange(seq, device=DEV)[None, :, None]
+    scores = scores.masked_fill(cols > rows + (total - seq), float("-inf"))
+    want = torch.einsum("hst,htd->hsd", torch.softmax(scores, -1), vf).permute(1, 0, 2)
+    err = (out.float() - want).abs()
+    assert float(err.max()) < 4e-3 + 4e-3 * float(want.abs().max())
+
+
 def test_attention_captures_into_a_cuda_graph(oracle, cuda_lib):
     """The three launches of one call neither allocate nor synchronise: captured after one eager
     call (one-time kernel attribute set-up), replayed on a cleared output and workspace."""
