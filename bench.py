@@ -479,6 +479,11 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=torch.device(dev), timeout=datetime.timedelta(minutes=5))
     lib = open_lib(os.path.join(ROOT, "operators_b200", "lib"))
     handle = create_handle(lib, DeviceEnum.DEVICE_CUDA, local)
+    for item in args.select_kernel:
+        from operators_b200 import ops as _sel
+
+        family, _, variant = item.partition("=")
+        _sel.select_kernel(lib, family, int(variant))
 
     if args.only in NEXT_ROWS:  # operators either side of the step, one at a time (for ncu captures and tuning)
         print(json.dumps(NEXT_ROWS[args.only](lib, handle, dev, args.steps, args.warmup)))
@@ -1105,6 +1110,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time plain launches instead of a CUDA graph of the step")
     ap.add_argument("--only", choices=OPS + list(NEXT_ROWS),
                     help="launch a single operator at its configuration (for ncu captures)")
+    ap.add_argument("--select-kernel", action="append", default=[], metavar="FAMILY=VARIANT",
+                    help="force a kernel family for this run (infiniopExtSelectKernel), e.g. rope=2; for comparisons")
     ap.add_argument("--tokens", type=int, choices=[SWI_T, 16, 1], help="with --only matmul: this token count only")
     ap.add_argument("--weights", choices=["k_contiguous", "n_contiguous"], help="with --only matmul: this weight layout only")
     args = ap.parse_args()

@@ -14,7 +14,8 @@
  * from shapes and alignment; this forces one of them process-wide so that both
  * can be held to the same oracle on the same inputs.  variant 0 restores the
  * library's own choice.
- *   family 0 (RoPE):          1 = the strided kernel instead of the bulk-copy pipeline
+ *   family 0 (RoPE):          1 = the strided kernel instead of the bulk-copy pipeline, 2 = the pipeline with bulk
+ *                             stores out of shared memory instead of the threads' own stores
  *   family 1 (random sample): 1 = the global-memory kernel instead of the shared-memory cluster kernel
  *   family 2 (attention):     1 = the multiply-add kernels instead of the tensor-core kernels,
  *                             2 = the row-tile mma.sync kernels also where the tcgen05 path (several new tokens) applies

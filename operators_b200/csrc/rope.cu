@@ -250,6 +250,11 @@ infiniopStatus_t run(const RoPEDesc *d, void *out, const void *t, void const *po
         rp::Plan plan;
         plan.row_bytes = nhead * dim * 2u;
         plan.tab_bytes = dim * 4u;
+        // Rotated vectors are stored by the threads themselves (measured back to back at [4096, 32, 128] / [16384, 32,
+        // 128]: 16.4 / 52.6 us against 17.2 / 55.6 us when they go back into the stage and a bulk copy returns the row;
+        // infiniopExtSelectKernel(rope, 2) keeps that form).  Padding the table rows in the stage against the two-way
+        // bank conflicts of their reads costs more bulk copies than it saves: 17.1 / 54.0 us; left out.
+        const bool direct = kernel_choice(kFamilyRoPE) != 2;
         plan.stage_bytes = (plan.row_bytes + 2u * plan.tab_bytes + 127u) & ~127u;
         plan.slices = dim / 8u;
         plan.row_vecs = plan.row_bytes / 16u;
@@ -265,9 +270,13 @@ infiniopStatus_t run(const RoPEDesc *d, void *out, const void *t, void const *po
             per_group <= (uint64_t) rp::kMaxTokensPerGroup) {
             static thread_local int configured_dev = -1, configured_bytes = 0;
             if (configured_dev != d->device_id || configured_bytes < (int) plan.smem_bytes) {
-                if (cudaFuncSetAttribute(rp::rope_pipeline_kernel<kF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                if (cudaFuncSetAttribute(rp::rope_pipeline_kernel<kF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int) plan.smem_bytes) != cudaSuccess ||
-                    cudaFuncSetAttribute(rp::rope_pipeline_kernel<kBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                    cudaFuncSetAttribute(rp::rope_pipeline_kernel<kF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int) plan.smem_bytes) != cudaSuccess ||
+                    cudaFuncSetAttribute(rp::rope_pipeline_kernel<kBF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int) plan.smem_bytes) != cudaSuccess ||
+                    cudaFuncSetAttribute(rp::rope_pipeline_kernel<kBF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int) plan.smem_bytes) != cudaSuccess) {
                     cudaGetLastError();
                     return STATUS_EXECUTION_FAILED;
@@ -275,7 +284,8 @@ infiniopStatus_t run(const RoPEDesc *d, void *out, const void *t, void const *po
                 configured_dev = d->device_id;
                 configured_bytes = (int) plan.smem_bytes;
             }
-            auto *kernel = d->dt == kBF16 ? rp::rope_pipeline_kernel<kBF16> : rp::rope_pipeline_kernel<kF16>;
+            auto *kernel = d->dt == kBF16 ? (direct ? rp::rope_pipeline_kernel<kBF16, true> : rp::rope_pipeline_kernel<kBF16, false>)
+                                          : (direct ? rp::rope_pipeline_kernel<kF16, true> : rp::rope_pipeline_kernel<kF16, false>);
             kernel<<<grid, rp::kThreads, plan.smem_bytes, st>>>(tp, pp, sp, cp, (uint32_t) d->seq_len, dim, d->stride_0, plan);
             return check_launch("rope_pipeline");
         }

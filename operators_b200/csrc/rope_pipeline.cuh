@@ -124,7 +124,9 @@ __device__ __forceinline__ void group_barrier(int group) {
 
 // t rows contiguous ([tokens] x nhead*dh halves, token stride >= row, all 16-byte aligned).
 // Token order: group g of CTA c takes tokens c + G * (g + kGroups * j), j = 0, 1, ...
-template<int DT>
+// DIRECT: the rotated vectors are stored to global memory by the threads themselves; otherwise they go back into the
+// stage and one bulk copy returns the row.
+template<int DT, bool DIRECT>
 __global__ void __launch_bounds__(kThreads, 1)
 rope_pipeline_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_table, const float *cos_table, uint32_t seq_len,
                      uint32_t dim, int64_t stride_0, Plan plan) {
@@ -187,6 +189,7 @@ rope_pipeline_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_tabl
             const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
             const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
             uint4 *row = reinterpret_cast<uint4 *>(st);
+            uint16_t *grow = row_of(j);
 #pragma unroll 8
             for (uint32_t v = gtid; v < plan.row_vecs; v += kGroupThreads) {
                 const uint4 q = row[v];
@@ -198,44 +201,57 @@ rope_pipeline_kernel(uint16_t *t, const uint64_t *pos_ids, const float *sin_tabl
                     const float r1 = __fadd_rn(__fmul_rn(ab.x, sn[2 * k + 1]), __fmul_rn(ab.y, cs[2 * k + 1]));
                     w[k] = pack2_t<DT>(r0, r1);
                 }
-                row[v] = make_uint4(w[0], w[1], w[2], w[3]);
+                if (DIRECT) st_stream(grow + (size_t) v * 8, make_uint4(w[0], w[1], w[2], w[3]));
+                else row[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
-        fence_async_shared();
-        group_barrier(group);
+        if (!DIRECT) fence_async_shared();
+        group_barrier(group);// every thread of the group has read (and, with bulk stores, rewritten) stage s
         if (s_fail[group]) {// the same decision in every thread of the group
             failed = true;
             j_fail = j;
             break;
         }
-        // The stage used by token j - 1 is free once its store has read it; it takes token j - 1 + kStagesPerGroup.
-        const uint32_t jn = j + kStagesPerGroup - 1;
-        const bool refill = j >= 1 && jn < cnt;
-        const uint64_t pn = __shfl_sync(0xffffffffu, my_pos, jn & 31u);
-        if (issuer) {
-            bulk_store(row_of(j), st, plan.row_bytes);
-            bulk_commit();
-            if (refill) {
-                bulk_wait_read<1>();
-                const uint32_t sr = (j - 1) % kStagesPerGroup;
-                mbar_expect_tx(&bar[sr], plan.row_bytes + 2 * plan.tab_bytes);
-                bulk_load(stage_ptr(sr), row_of(jn), plan.row_bytes, &bar[sr]);
-                load_tables(pn, sr);
+        if (DIRECT) {
+            // Stage s is free again: it takes token j + kStagesPerGroup.
+            const uint32_t jn = j + kStagesPerGroup;
+            const bool refill = jn < cnt;
+            const uint64_t pn = __shfl_sync(0xffffffffu, my_pos, jn & 31u);
+            if (issuer && refill) {
+                mbar_expect_tx(&bar[s], plan.row_bytes + 2 * plan.tab_bytes);
+                bulk_load(stage_ptr(s), row_of(jn), plan.row_bytes, &bar[s]);
+                load_tables(pn, s);
+            }
+        } else {
+            // The stage used by token j - 1 is free once its store has read it; it takes token j - 1 + kStagesPerGroup.
+            const uint32_t jn = j + kStagesPerGroup - 1;
+            const bool refill = j >= 1 && jn < cnt;
+            const uint64_t pn = __shfl_sync(0xffffffffu, my_pos, jn & 31u);
+            if (issuer) {
+                bulk_store(row_of(j), st, plan.row_bytes);
+                bulk_commit();
+                if (refill) {
+                    bulk_wait_read<1>();
+                    const uint32_t sr = (j - 1) % kStagesPerGroup;
+                    mbar_expect_tx(&bar[sr], plan.row_bytes + 2 * plan.tab_bytes);
+                    bulk_load(stage_ptr(sr), row_of(jn), plan.row_bytes, &bar[sr]);
+                    load_tables(pn, sr);
+                }
             }
         }
     }
     if (issuer) {
         if (failed) {
             // the loads of tokens j_fail .. are still in flight towards this CTA's shared memory: let them land
-            // before the CTA gives the memory back (token i + kStagesPerGroup - 1 is requested at the end of pass i)
-            uint32_t issued = j_fail == 0 ? first : j_fail + kStagesPerGroup - 1;
+            // before the CTA gives the memory back (token i + kStagesPerGroup is requested at the end of pass i)
+            uint32_t issued = DIRECT ? j_fail + kStagesPerGroup : (j_fail == 0 ? first : j_fail + kStagesPerGroup - 1);
             if (issued > cnt) issued = cnt;
             for (uint32_t jj = j_fail; jj < issued; ++jj) {
                 mbar_wait_bounded(&bar[jj % kStagesPerGroup], (jj / kStagesPerGroup) & 1u);
             }
             atomicAdd(&g_rope_pipeline_timeouts, 1u);
         }
-        bulk_wait_all();
+        if (!DIRECT) bulk_wait_all();
     }
 }
 

@@ -134,8 +134,10 @@ def test_add_rms_norm_status_codes(cuda_lib):
                                            # one token, more tokens than the pipeline takes (-> strided kernel)
                                            ((9000, 32, 64), None), ((1187, 32, 128), None), ((33, 8, 256), None),
                                            ((9000, 8, 64), None), ((40000, 64, 32), None), ((300, 16, 8), None)])
-def test_rope(oracle, cuda_lib, shape, strides):
+@pytest.mark.parametrize("stores", ["threads", "bulk"])
+def test_rope(oracle, cuda_lib, shape, strides, stores):
     lib, handle = cuda_lib
+    ops.select_kernel(lib, "rope", 2 if stores == "bulk" else 0)  # both forms of the bulk-copy pipeline
     g = torch.Generator().manual_seed(2)
     t = torch.randn(shape, generator=g).half()
     pos = torch.randperm(2 * shape[0], generator=g)[: shape[0]].to(torch.int64)
@@ -144,8 +146,11 @@ def test_rope(oracle, cuda_lib, shape, strides):
     td = t.to(DEV)
     if strides is not None:
         td = rearrange_tensor(td, strides)
-    ops.rope(lib, handle, td, pos.to(DEV), sin.to(DEV), cos.to(DEV))
-    torch.cuda.synchronize()
+    try:
+        ops.rope(lib, handle, td, pos.to(DEV), sin.to(DEV), cos.to(DEV))
+        torch.cuda.synchronize()
+    finally:
+        ops.select_kernel(lib, "rope", 0)
     assert np.array_equal(_bits(td).reshape(shape), want.view(np.uint16))
 
 
