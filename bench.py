@@ -765,8 +765,9 @@ def run_b200(args):
         out = torch.zeros(RS_B, dtype=torch.int64, device=dev)
         sop = _ops.RandomSampleOp(lib, handle, out[:1], shard[0])
         sharded = {}
-        for mode in ("exact", "fast"):
-            sampler = VocabShardedSampler(lib, handle, sop, RS_V, b0, world, mode=mode, rank=rank)
+        for mode in ("exact", "exact_all_to_all", "exact_all_gather", "fast"):
+            exch = mode[6:] if mode.startswith("exact_") else "auto"
+            sampler = VocabShardedSampler(lib, handle, sop, RS_V, b0, world, mode=mode[:5].rstrip("_"), rank=rank, exchange=exch)
             for _ in range(3):
                 sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, check=False)
             barrier()
@@ -791,6 +792,7 @@ def run_b200(args):
             # destroy_process_group, so the graph is dropped before the group is
             res["ms_graph"] = None
             gr = None
+            res["exchange"] = sampler.exchange if mode != "fast" else None
             if not args.sharded_graph:
                 if mode == "exact":
                     res["indices"] = out.cpu().tolist()
@@ -919,8 +921,8 @@ def run_b200(args):
                     "launch latency, not bandwidth" % world,
             "ops": split}
         rs = {}
-        for mode in ("exact", "fast"):
-            rs[mode] = {"ms": round(extra["sharded.%s.ms" % mode], 4),
+        for mode in ("exact", "exact_all_to_all", "exact_all_gather", "fast"):
+            rs[mode] = {"ms": round(extra["sharded.%s.ms" % mode], 4), "exchange": sharded[mode].get("exchange"),
                         "ms_graph": round(extra["sharded.%s.ms_graph" % mode], 4) or None,
                         "tokens_per_s": round(RS_B / (extra["sharded.%s.ms" % mode] * 1e-3), 1),
                         "stages_ms": {k.split(".stage.")[1]: round(v, 4) for k, v in extra.items()
@@ -928,9 +930,11 @@ def run_b200(args):
             if "graph_error" in sharded[mode]:
                 rs[mode]["graph_error"] = sharded[mode]["graph_error"]
         rs["exact"]["what"] = ("64 rows, vocabulary 128256 split over %d GPUs; default mode, index-exact: one NCCL "
-                               "all-to-all hands every rank %d whole rows (%d bytes received per rank), the exact "
-                               "kernel samples them, one all-gather returns the indices" %
-                               (world, RS_B // world, RS_B // world * RS_V * 2 * (world - 1) // world))
+                               "collective (all-to-all: %d bytes received per rank; or all-gather of all shards: %d "
+                               "bytes) gives every rank %d whole rows, the exact kernel samples them, one all-gather "
+                               "returns the indices; exact_all_to_all / exact_all_gather force one exchange each" %
+                               (world, RS_B // world * RS_V * 2 * (world - 1) // world,
+                                RS_B * RS_V * 2 * (world - 1) // world, RS_B // world))
         rs["fast"]["what"] = ("local candidate kernel, one NCCL all-gather of %d bytes per rank, finishing kernel; "
                               "denominator correctly rounded instead of sequential" % (RS_B * 1056))
         rs["one_gpu_unsharded_ms"] = round(own_per_op_ms["random_sample"], 4)

@@ -21,6 +21,8 @@
  *                             2 = the row-tile mma.sync kernels also where the tcgen05 path (several new tokens) applies
  *   family 3 (matmul):        1 = the CUDA-core kernel instead of the tcgen05 kernels, 2 (read when a descriptor is
  *                             created) = the single-CTA tcgen05 kernel also where CTA pairs (cta_group::2) apply
+ *   family 4 (long rows of RMSNorm / causal softmax): 1 = the register-resident kernels only, 2 = the shared-memory
+ *                             ring for every row of 4096 elements and more
  * Returns STATUS_BAD_PARAM for an unknown family or a negative variant.
  */
 INFINIOP_API infiniopStatus_t infiniopExtSelectKernel(int family, int variant);

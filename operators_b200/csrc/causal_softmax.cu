@@ -15,6 +15,7 @@
 // once; masked tails are never read.  A row lives in registers between the
 // three steps (max, exp+sum, scale), owned by one warp or one CTA.
 #include "common.cuh"
+#include "row_ring.cuh"
 #include "fastdiv.h"
 
 #include <new>
@@ -169,6 +170,14 @@ __global__ void __launch_bounds__(1024)
     causal_softmax_regs_body<VPT, OWNER, DT>(y, rows, seq_len, total, vecs, stride_b, stride_i, seq_div);
 }
 
+// Rows of 32 Ki columns and more, many of them: the shared-memory ring of row_ring.cuh.
+template<int DT>
+__global__ void __launch_bounds__(ring::kThreads, 1)
+    causal_softmax_ring_kernel(uint16_t *y, uint64_t rows, uint64_t seq_len, uint64_t total, uint32_t vecs,
+                               int64_t stride_b, int64_t stride_i, ring::Plan plan) {
+    ring::causal_softmax_ring_body<DT>(y, rows, seq_len, total, vecs, stride_b, stride_i, plan);
+}
+
 // Any alignment, any column stride, any row length: one CTA per row, three
 // passes (max / sum / write), the later ones served by L2.
 template<int DT>
@@ -239,6 +248,17 @@ bool launch_regs(const CausalSoftmaxDesc *d, bool cta_row, uint32_t threads, uin
 
 }// namespace
 
+namespace b200 {
+unsigned long long causal_softmax_ring_timeouts_read() {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, ring::g_row_ring_timeouts, sizeof(v)) != cudaSuccess) {
+        cudaGetLastError();
+        return ~0ull;
+    }
+    return v;
+}
+}// namespace b200
+
 INFINIOP_API infiniopStatus_t infiniopCreateCausalSoftmaxDescriptor(infiniopHandle_t handle,
                                                                     infiniopCausalSoftmaxDescriptor_t *desc_ptr,
                                                                     infiniopTensorDescriptor_t y) {
@@ -292,6 +312,27 @@ INFINIOP_API infiniopStatus_t infiniopCausalSoftmax(infiniopCausalSoftmaxDescrip
     if (vec_ok) {
         const uint32_t vecs = (uint32_t) (d->total / 8);
         const bool big = rows * (uint64_t) vecs >= (1u << 20);
+        // The shared-memory ring never beat the register kernels here (32768 columns: 175 against 148 us, 65536: equal,
+        // longer rows slower): it runs only when infiniopExtSelectKernel(long rows, 2) asks for it (4096 columns and more).
+        const int ring_choice = kernel_choice(kFamilyLongRows);
+        if (ring_choice == 2 && vecs >= 512) {
+            ring::Plan plan;
+            if (ring::make_plan(plan, vecs, rows, d->sm_count)) {
+                auto *kernel = d->dt == kBF16 ? causal_softmax_ring_kernel<kBF16> : causal_softmax_ring_kernel<kF16>;
+                if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) plan.smem_bytes) ==
+                    cudaSuccess) {
+                    if (plan.cl > 1) {
+                        launch_cluster_smem(kernel, plan.grid, ring::kThreads, plan.cl, plan.smem_bytes, st, y, rows,
+                                            d->seq_len, d->total, vecs, d->stride_b, d->stride_i, plan);
+                    } else {
+                        kernel<<<plan.grid, ring::kThreads, plan.smem_bytes, st>>>(y, rows, d->seq_len, d->total, vecs,
+                                                                                  d->stride_b, d->stride_i, plan);
+                    }
+                    return check_launch("causal_softmax (ring)");
+                }
+                cudaGetLastError();
+            }
+        }
         int vpt;
         bool cta_row;
         uint32_t threads = 256, cl = 1;

@@ -67,7 +67,7 @@ static inline infiniopStatus_t check_launch(const char *what) {
 }
 
 // Kernel-family override set through infiniopExtSelectKernel (runtime.cu); 0 = the library's own choice.
-enum KernelFamily { kFamilyRoPE = 0, kFamilyRandomSample = 1, kFamilyAttention = 2, kFamilyMatmul = 3, kFamilyCount = 8 };
+enum KernelFamily { kFamilyRoPE = 0, kFamilyRandomSample = 1, kFamilyAttention = 2, kFamilyMatmul = 3, kFamilyLongRows = 4, kFamilyCount = 8 };
 int kernel_choice(int family);
 
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

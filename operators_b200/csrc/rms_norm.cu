@@ -26,12 +26,18 @@
 // without being read back: 8 bytes per element instead of the 10 of Add
 // followed by RMSNorm.
 #include "common.cuh"
+#include "row_ring.cuh"
 
 #include <new>
 
 using namespace b200;
 
 namespace {
+
+// Many rows of 32768 .. 65536 elements go through the shared-memory ring (measured at 256 MB of rows: 125 against
+// 144 us at 32768 elements, 166 against 195 us at 65536; shorter rows are faster from registers, longer ones on the
+// register kernels spread over a cluster).
+constexpr uint32_t kRingMinVecs = 4096, kRingMaxVecs = 8192;
 
 struct RMSNormDesc {
     Device device;
@@ -226,6 +232,61 @@ __global__ void __launch_bounds__(1024)
     rms_norm_regs_body<VPT, W_F16, OWNER, FUSED, DT>(y, x, w, n, vecs, d, stride_y, stride_x, eps, res);
 }
 
+// Rows of 16 Ki elements and more, many of them: the shared-memory ring of row_ring.cuh (plain form only).
+template<bool W_F16, int DT>
+__global__ void __launch_bounds__(ring::kThreads, 1)
+    rms_norm_ring_kernel(uint16_t *y, const uint16_t *x, const void *w, uint64_t n, uint32_t vecs, uint64_t d,
+                         int64_t stride_y, int64_t stride_x, float eps, ring::Plan plan) {
+    ring::rms_norm_ring_body<DT, W_F16>(
+        y, x, w, n, vecs, d, stride_y, stride_x, eps, plan,
+        [](float ss, uint64_t dd, float e) { return split_scale(rms_scale(ss, dd, e)); },
+        [](ScaleF2 k, uint4 q, const void *wp, uint32_t j) {
+            const uint32_t *px = reinterpret_cast<const uint32_t *>(&q);
+            uint4 out;
+            uint32_t *po = reinterpret_cast<uint32_t *>(&out);
+            if (W_F16) {
+                const uint4 wv = __ldg(reinterpret_cast<const uint4 *>(wp) + j);
+                const uint32_t *pw = reinterpret_cast<const uint32_t *>(&wv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 xf = unpack2_t<DT>(px[e]), wf = unpack2_t<DT>(pw[e]);
+                    po[e] = pack2_t<DT>(rms_prod<true>(k, xf.x, wf.x), rms_prod<true>(k, xf.y, wf.y));
+                }
+            } else {
+                const float4 w0 = __ldg(reinterpret_cast<const float4 *>(wp) + 2 * j);
+                const float4 w1 = __ldg(reinterpret_cast<const float4 *>(wp) + 2 * j + 1);
+                const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 xf = unpack2_t<DT>(px[e]);
+                    po[e] = pack2_t<DT>(rms_prod<false>(k, xf.x, wf[2 * e]), rms_prod<false>(k, xf.y, wf[2 * e + 1]));
+                }
+            }
+            return out;
+        });
+}
+
+template<bool W_F16, int DT>
+bool launch_ring(const RMSNormDesc *d, uint32_t vecs, void *y, const void *x, const void *w, cudaStream_t st) {
+    ring::Plan plan;
+    if (!ring::make_plan(plan, vecs, d->n, d->sm_count)) return false;
+    auto *kernel = rms_norm_ring_kernel<W_F16, DT>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) plan.smem_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    auto *yp = reinterpret_cast<uint16_t *>(y);
+    auto *xp = reinterpret_cast<const uint16_t *>(x);
+    if (plan.cl > 1) {
+        launch_cluster_smem(kernel, plan.grid, ring::kThreads, plan.cl, plan.smem_bytes, st, yp, xp, w, d->n, vecs, d->d,
+                            d->stride_y, d->stride_x, d->epsilon, plan);
+    } else {
+        kernel<<<plan.grid, ring::kThreads, plan.smem_bytes, st>>>(yp, xp, w, d->n, vecs, d->d, d->stride_y, d->stride_x,
+                                                                  d->epsilon, plan);
+    }
+    return true;
+}
+
 // Any alignment, any d: one CTA per row, two passes over x (the second one is
 // served by L2).
 template<bool W_F16, bool FUSED, int DT>
@@ -330,6 +391,16 @@ infiniopStatus_t run(const RMSNormDesc *d, void *y, const void *x, const void *w
         // vectors each, a warp per row when the row fits).  Few rows: favour
         // latency, spread each row over as many threads as it has vectors.
         const bool big = d->n * (uint64_t) vecs >= (1u << 20);
+        // infiniopExtSelectKernel(long rows, 1) keeps the register kernels, 2 takes the ring for every row of 4096
+        // elements and more
+        const int ring_choice = kernel_choice(kFamilyLongRows);
+        if (!FUSED && ring_choice != 1 && ((big && vecs >= kRingMinVecs && vecs <= kRingMaxVecs) || (ring_choice == 2 && vecs >= 512))) {
+            const bool launched = d->dt == kBF16 ? (d->w_f16 ? launch_ring<true, kBF16>(d, vecs, y, x, w, st)
+                                                            : launch_ring<false, kBF16>(d, vecs, y, x, w, st))
+                                                 : (d->w_f16 ? launch_ring<true, kF16>(d, vecs, y, x, w, st)
+                                                            : launch_ring<false, kF16>(d, vecs, y, x, w, st));
+            if (launched) return check_launch("rms_norm (ring)");
+        }
         int vpt;
         bool cta_row;
         uint32_t threads = 256, cl = 1;
@@ -366,6 +437,17 @@ infiniopStatus_t run(const RMSNormDesc *d, void *y, const void *x, const void *w
 }
 
 }// namespace
+
+namespace b200 {
+unsigned long long rms_norm_ring_timeouts_read() {
+    unsigned int v = 0;
+    if (cudaMemcpyFromSymbol(&v, ring::g_row_ring_timeouts, sizeof(v)) != cudaSuccess) {
+        cudaGetLastError();
+        return ~0ull;
+    }
+    return v;
+}
+}// namespace b200
 
 INFINIOP_API infiniopStatus_t infiniopCreateRMSNormDescriptor(infiniopHandle_t handle,
                                                               infiniopRMSNormDescriptor_t *desc_ptr,

@@ -100,7 +100,7 @@ def _declare(lib):
     lib._b200_declared = True
 
 
-KERNEL_FAMILIES = {"rope": 0, "random_sample": 1, "attention": 2, "matmul": 3}
+KERNEL_FAMILIES = {"rope": 0, "random_sample": 1, "attention": 2, "matmul": 3, "long_rows": 4}
 
 
 def select_kernel(lib, family, variant):

@@ -88,9 +88,19 @@ class VocabShardedSampler:
     torch.distributed calls on `group` (tests play several ranks in one process with them)."""
 
     def __init__(self, lib, handle, sample_op, voc_total, shard_offset, world_size, group=None, all_gather=None,
-                 mode="exact", rank=None, all_to_all=None):
+                 mode="exact", rank=None, all_to_all=None, exchange="auto"):
         _declare(lib)
-        assert mode in ("exact", "fast")
+        assert mode in ("exact", "fast") and exchange in ("auto", "all_to_all", "all_gather")
+        # How the exact mode moves the rows: "all_to_all" sends every rank only the rows it will own;
+        # "all_gather" hands every rank all shards (world_size times the bytes, but one collective whose latency
+        # does not grow with the number of peers the way the send / receive pairs of an all-to-all do) and lets it
+        # pick its rows.  It needs equal shards; "auto" takes it from four ranks up.
+        equal = int(voc_total) % int(world_size) == 0
+        if exchange == "auto":
+            exchange = "all_gather" if (int(world_size) >= 4 and equal and all_to_all is None) else "all_to_all"
+        if exchange == "all_gather" and not equal:
+            exchange = "all_to_all"
+        self.exchange = exchange
         self.lib, self.handle, self.op = lib, handle, sample_op
         self.voc_total, self.shard_offset, self.world = int(voc_total), int(shard_offset), int(world_size)
         self.group, self.mode = group, mode
@@ -134,7 +144,8 @@ class VocabShardedSampler:
         if key not in self._exact:
             (r0, r1), _, recv, _ = exchange_plan(rows, self.voc_total, self.world, self.rank)
             most = max(e - b for b, e in (row_range(rows, self.world, r) for r in range(self.world)))
-            received = torch.empty(max(1, sum(recv)), dtype=torch.float16, device=device)
+            n_recv = rows * self.voc_total if self.exchange == "all_gather" else sum(recv)
+            received = torch.empty(max(1, n_recv), dtype=torch.float16, device=device)
             full = torch.empty((max(1, r1 - r0), self.voc_total), dtype=torch.float16, device=device)
             picked = torch.zeros((self.world, most), dtype=torch.int64, device=device)
             op = RandomSampleOp(self.lib, self.handle, picked[0, :1], full[0])
@@ -146,7 +157,10 @@ class VocabShardedSampler:
 
                 vl = self.voc_total // self.world
                 full_view = full[:mine].view(mine, self.world, vl).permute(1, 0, 2)  # [shard, row, cols] view of the rows
-                received_view = received[:self.world * mine * vl].view(self.world, mine, vl)
+                if self.exchange == "all_gather":  # every shard arrives whole: [shard][all rows][cols]; this rank's rows of each
+                    received_view = received[:self.world * rows * vl].view(self.world, rows, vl)[:, r0:r1, :]
+                else:
+                    received_view = received[:self.world * mine * vl].view(self.world, mine, vl)
                 op_copy = RearrangeOp(self.lib, self.handle, full_view, received_view)
             self._exact[key] = (received, full, picked, op, op_copy, full_view, received_view)
         return self._exact[key]
@@ -192,10 +206,13 @@ class VocabShardedSampler:
         elif self.world > 1:
             import torch.distributed as dist
 
-            dist.all_to_all_single(received[:sum(recv)], src.view(-1), recv, send, group=self.group)
+            if self.exchange == "all_gather":
+                dist.all_gather_into_tensor(received[:self.world * src.numel()], src.view(-1), group=self.group)
+            else:
+                dist.all_to_all_single(received[:sum(recv)], src.view(-1), recv, send, group=self.group)
         else:
             received[:src.numel()].copy_(src.view(-1))
-        mark("all_to_all")
+        mark("exchange")
         if mine:
             if op_copy is not None:  # equal shards: [shard][row][cols] -> [row][shard][cols] in one strided copy
                 op_copy(full_view, received_view, stream=sp)

@@ -44,8 +44,11 @@ def _few(mismatches, total, rate):
                                           ((2, 49152), None), ((2, 65536), None), ((600, 16384), None),
                                           ((300, 32768), 32776), ((3, 200000), None), ((2, 262144), None),
                                           ((2, 262152), None), ((1, 8200), None)])
-def test_rms_norm(oracle, cuda_lib, shape, stride, w_dtype):
+@pytest.mark.parametrize("long_rows", ["auto", "ring"])
+def test_rms_norm(oracle, cuda_lib, shape, stride, w_dtype, long_rows):
     lib, handle = cuda_lib
+    if long_rows == "ring" and shape[1] < 4096:
+        pytest.skip("the shared-memory ring starts at rows of 4096 elements")
     g = torch.Generator().manual_seed(1)
     x = (torch.rand(shape, generator=g) * 2 - 1).half()
     w = (torch.rand(shape[1], generator=g) * 2 - 1).to(w_dtype)
@@ -54,8 +57,12 @@ def test_rms_norm(oracle, cuda_lib, shape, stride, w_dtype):
     yd = torch.full(shape, 7.0, dtype=torch.float16, device=DEV)
     if stride is not None:
         xd, yd = rearrange_tensor(xd, (stride, 1)), rearrange_tensor(yd, (stride, 1))
-    ops.rms_norm(lib, handle, yd, xd, w.to(DEV), 1e-5)
-    torch.cuda.synchronize()
+    ops.select_kernel(lib, "long_rows", 2 if long_rows == "ring" else 0)  # the ring wherever it can run, or the library's choice
+    try:
+        ops.rms_norm(lib, handle, yd, xd, w.to(DEV), 1e-5)
+        torch.cuda.synchronize()
+    finally:
+        ops.select_kernel(lib, "long_rows", 0)
     mism = _close(_bits(yd).reshape(shape), want, 1e-3, 1e-3)
     # only the order of the fp32 sum of squares differs; the oracle's sequential sum over rows of 10^5 elements
     # and more is itself a few fp32 ulps off, which moves a few per cent of the outputs by one fp16 ulp
@@ -342,18 +349,25 @@ def test_add_unaligned_views(oracle, cuda_lib):
                                            # rows spread over a cluster of 2 / 4 / 8 CTAs, up to the longest
                                            # register-resident row and one vector past it
                                            ((1, 2, 40960), None), ((1, 3, 65536), None), ((8, 128, 16384), None),
-                                           ((4, 40, 32768), (40 * 32776, 32776, 1)), ((1, 2, 262144), None),
+                                           ((4, 40, 32768), (40 * 32776, 32776, 1)), ((2, 150, 32768), None), ((1, 2, 262144), None),
                                            ((1, 2, 262152), None), ((2, 5, 8200), None)])
-def test_causal_softmax(oracle, cuda_lib, shape, strides):
+@pytest.mark.parametrize("long_rows", ["auto", "ring"])
+def test_causal_softmax(oracle, cuda_lib, shape, strides, long_rows):
     lib, handle = cuda_lib
+    if long_rows == "ring" and shape[-1] < 4096:
+        pytest.skip("the shared-memory ring starts at rows of 4096 columns")
     g = torch.Generator().manual_seed(5)
     y = (torch.randn(shape, generator=g) * 2).half()
     want = oracle.causal_softmax(y.numpy().copy())
     yd = y.to(DEV)
     if strides is not None:
         yd = rearrange_tensor(yd, strides)
-    ops.causal_softmax(lib, handle, yd)
-    torch.cuda.synchronize()
+    ops.select_kernel(lib, "long_rows", 2 if long_rows == "ring" else 0)
+    try:
+        ops.causal_softmax(lib, handle, yd)
+        torch.cuda.synchronize()
+    finally:
+        ops.select_kernel(lib, "long_rows", 0)
     got = _bits(yd).reshape(shape)
     _close(got, want, 2e-3, 2e-3)
     # masked entries are exact zeros, as the reference's own test demands
@@ -1096,15 +1110,18 @@ def _sharded_inputs(oracle, voc, rows, topp, topk, temp, dist):
     return _sharded_oracle_cache[key]
 
 
+@pytest.mark.parametrize("exchange", ["all_to_all", "all_gather"])
 @pytest.mark.parametrize("ranks", [1, 2, 4, 8])
 @pytest.mark.parametrize("voc,rows,topp,topk,temp,dist", SHARDED_CASES)
-def test_vocab_sharded_sampling_is_index_exact(oracle, cuda_lib, ranks, voc, rows, topp, topk, temp, dist):
+def test_vocab_sharded_sampling_is_index_exact(oracle, cuda_lib, ranks, voc, rows, topp, topk, temp, dist, exchange):
     """The default mode: every rank receives whole rows through one all-to-all, samples them with the exact
     kernel and the indices are all-gathered.  EVERY row's index must be the oracle's.  The collectives are
     played by closures that hand each rank what the other ranks would send."""
     from operators_b200.sharding import VocabShardedSampler, exchange_plan, row_range, vocab_range
 
     lib, handle = cuda_lib
+    if exchange == "all_gather" and voc % ranks != 0:
+        pytest.skip("the all-gather exchange needs equal shards")
     logits, u, want = _sharded_inputs(oracle, voc, rows, topp, topk, temp, dist)
     ld, ud = logits.to(DEV), u.to(DEV)
     sent = {}
@@ -1116,6 +1133,10 @@ def test_vocab_sharded_sampling_is_index_exact(oracle, cuda_lib, ranks, voc, row
         def all_to_all(out, inp, out_splits, in_splits, r=r):
             (r0, r1), send, recv, cols = exchange_plan(rows, voc, ranks, r)
             assert list(out_splits) == recv and list(in_splits) == send and inp.numel() == sum(send)
+            if exchange == "all_gather":  # every shard whole, rank after rank: [ranks][rows][columns]
+                vl = voc // ranks
+                out[:ranks * rows * vl].view(ranks, rows, vl).copy_(ld.view(rows, ranks, vl).permute(1, 0, 2))
+                return
             off = 0
             for (cb, ce), n in zip(cols, recv):
                 out[off:off + n].copy_(ld[r0:r1, cb:ce].reshape(-1))
@@ -1129,7 +1150,8 @@ def test_vocab_sharded_sampling_is_index_exact(oracle, cuda_lib, ranks, voc, row
 
         res = torch.full((rows,), -1, dtype=torch.int64, device=DEV)
         with ops.RandomSampleOp(lib, handle, res[:1], shard[0]) as op:
-            s = VocabShardedSampler(lib, handle, op, voc, b, ranks, rank=r, all_to_all=all_to_all, all_gather=all_gather)
+            s = VocabShardedSampler(lib, handle, op, voc, b, ranks, rank=r, all_to_all=all_to_all, all_gather=all_gather,
+                                    exchange=exchange)
             s.sample(res, shard, ud, topp, topk, temp)
             torch.cuda.synchronize()
             s.destroy()
