@@ -18,7 +18,9 @@
  *                             stores out of shared memory instead of the threads' own stores
  *   family 1 (random sample): 1 = the global-memory kernel instead of the shared-memory cluster kernel
  *   family 2 (attention):     1 = the multiply-add kernels instead of the tensor-core kernels,
- *                             2 = the row-tile mma.sync kernels also where the tcgen05 path (several new tokens) applies
+ *                             2 = the row-tile mma.sync kernels also where the tcgen05 paths (several new tokens) apply,
+ *                             3 / 4 (read when a descriptor is created) = for several new tokens the three-launch
+ *                             form (scores, softmax, values) / the one-kernel form wherever it applies
  *   family 3 (matmul):        1 = the CUDA-core kernel instead of the tcgen05 kernels, 2 (read when a descriptor is
  *                             created) = the single-CTA tcgen05 kernel also where CTA pairs (cta_group::2) apply
  *   family 4 (long rows of RMSNorm / causal softmax): 1 = the register-resident kernels only, 2 = the shared-memory

@@ -52,6 +52,8 @@ constexpr int kMaxRows = 8;       // query rows per CTA
 constexpr int kMaxChunk = 2048;   // cached tokens per CTA: their scores live in shared memory
 constexpr int kMaxHeadDim = 256;
 constexpr int kUnroll = 4;        // 128-bit loads in flight per thread
+// several new tokens: the one-kernel path from this many CTAs, or up to this many tiles of 64 cached tokens per CTA
+constexpr uint64_t kFusedMinCtas = 64, kFusedMaxSerialTiles = 32;
 
 struct AttnDesc {
     Device device;
@@ -63,7 +65,8 @@ struct AttnDesc {
     bool strides_vec;             // every stride a multiple of 8 elements and dh % 8 == 0
     uint32_t score_pitch;         // splits * chunk: tokens per score row in the workspace
     uint64_t ws_ml, ws_acc, ws_scores, ws_bytes;// workspace: counters at 0, then the parts named here
-    AttnPrefill *prefill;         // tensor-core path for calls with several new tokens, or null
+    AttnPrefill *prefill;         // tensor-core path for calls with several new tokens (three launches), or null
+    AttnFused *fused;             // the same in one kernel, or null
     uint64_t prefill_ws_bytes;
 };
 
@@ -893,10 +896,22 @@ INFINIOP_API infiniopStatus_t infiniopCreateAttentionDescriptor(infiniopHandle_t
     d->prefill_ws_bytes = 0;
     // (measured, 32 q / 8 kv heads, dh 128: 8 new tokens over 4096 cached 46 us against 29 us for the row-tile kernels,
     // 16 tokens 48 against 40, 64 tokens over 8192 cached 146 against 191, 512 tokens from an empty cache 92 against 115)
+    d->fused = nullptr;
     if (seq >= 32 && d->strides_vec && total > 0) {
         const AttnPrefillShape shape{d->nh, d->group, d->seq, d->dh, d->total, d->q_s0, d->q_s1, d->kc_s0, d->kc_s1, d->vc_s0, d->vc_s1};
-        d->prefill = attn_prefill_create(handle, shape, &d->prefill_ws_bytes);
-        if (d->prefill != nullptr && d->prefill_ws_bytes > d->ws_bytes) d->ws_bytes = d->prefill_ws_bytes;
+        // One kernel that keeps the scores on chip (attention_fused.cu) when its CTAs (one per 128 query rows of a
+        // head, each walking its visible tokens alone) are many or short; few new tokens over a long cache keep
+        // the three launches, which spread the cached tokens over the whole GPU.  The choice is made here because
+        // the two paths need different workspaces; infiniopExtSelectKernel(attention, 3 / 4) forces either.
+        const int choice = kernel_choice(kFamilyAttention);
+        const uint64_t ctas = (uint64_t) ((seq + 127) / 128) * d->nh, kv_tiles = (total + 63) / 64;
+        if (choice == 4 || (choice != 3 && (ctas >= kFusedMinCtas || kv_tiles <= kFusedMaxSerialTiles))) {
+            d->fused = attn_fused_create(handle, shape);
+        }
+        if (d->fused == nullptr) {
+            d->prefill = attn_prefill_create(handle, shape, &d->prefill_ws_bytes);
+            if (d->prefill != nullptr && d->prefill_ws_bytes > d->ws_bytes) d->ws_bytes = d->prefill_ws_bytes;
+        }
     }
     *desc_ptr = reinterpret_cast<infiniopAttentionDescriptor_t>(d);
     return STATUS_SUCCESS;
@@ -952,8 +967,12 @@ INFINIOP_API infiniopStatus_t infiniopAttention(infiniopAttentionDescriptor_t de
         const infiniopStatus_t status = check_launch("attention kv append");
         if (status != STATUS_SUCCESS) return status;
     }
-    // several new tokens: scores, softmax and values as three tensor-core / streaming launches
-    if (d->prefill != nullptr && vec && kernel_choice(kFamilyAttention) == 0) {
+    // several new tokens: one kernel, or scores, softmax and values as three tensor-core / streaming launches
+    const int choice = kernel_choice(kFamilyAttention);
+    if (d->fused != nullptr && vec && aligned16(out) && (choice == 0 || choice >= 3)) {
+        return attn_fused_run(d->fused, out, q, k_cache, v_cache, st);
+    }
+    if (d->prefill != nullptr && vec && (choice == 0 || choice >= 3)) {
         return attn_prefill_run(d->prefill, workspace, out, q, k_cache, v_cache, st);
     }
     // the multiply-add kernels serve unaligned layouts and head sizes above 128 (and every layout when
@@ -966,6 +985,7 @@ INFINIOP_API infiniopStatus_t infiniopDestroyAttentionDescriptor(infiniopAttenti
     if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
     auto *d = reinterpret_cast<AttnDesc *>(desc);
     attn_prefill_destroy(d->prefill);
+    attn_fused_destroy(d->fused);
     delete d;
     return STATUS_SUCCESS;
 }

@@ -1,0 +1,420 @@
+// Attention with several new tokens per call in ONE kernel: the scores of a block of 128 query rows never leave the
+// SM.
+//
+// The reference composite (src/ops/attention/operator.cc:252-305) materialises the fp16 score tensor
+// [n_q_head, seq, total] between its two matmuls; at 4096 x 4096 tokens that tensor (1 GB written, read, written
+// and read again) sets the pace, not the tensor cores.  Here a CTA owns 128 query rows of one q head and walks the
+// visible cached tokens in tiles of 64, twice:
+//   pass 1  S = q k^T on tcgen05.mma into tensor memory; the four softmax warps (one thread per query row = TMEM
+//           lane) read S, apply the reference's two roundings' first half (alpha * s rounded to fp16 like the score
+//           tensor) and keep the row's running maximum and sum of exponentials;
+//   pass 2  S again (the tensor pipe has time to spare: the exponentials bound the kernel), the probability
+//           exp(s - max) / sum truncated to fp16 exactly as the causal softmax stores it, written as the K-major A
+//           operand into 128-byte-swizzled shared memory, and O += P v on tcgen05.mma with v read as an MN-major B
+//           operand straight from the cache rows; O stays in tensor memory over the whole pass.
+// The epilogue truncates O to fp16 and writes out[row, head, :], which is the reference's closing rearrange.
+// Because the maximum and the sum are final before any probability is formed, O needs no rescaling and every value
+// that the reference rounds (score, probability, output) is rounded at the same place; only the grouping of the
+// fp32 sums differs.
+//
+// Roles (192 threads, two CTAs per SM so that one CTA's exponentials overlap the other's products):
+//   warps 0-3  softmax / epilogue, warp w owns TMEM lanes 32 w .. 32 w + 31
+//   warp 4     one lane issues the TMA loads: q once, k tiles through two stages (both passes), v tiles (pass 2)
+//   warp 5     allocates TMEM (S twice 64 columns, O dh columns); one lane issues the MMAs.  S of tile j + 1 is
+//              issued before P v of tile j, so it runs while the softmax warps work on tile j.
+// Every mbarrier wait is bounded (tc_ptx.cuh); a role that gives up raises the CTA's abort flag, all roles leave,
+// copies in flight are awaited (bounded), TMEM is freed, and infiniopExtDeviceTimeouts reports it.
+#include "attention_prefill.cuh"
+#include "tc_ptx.cuh"
+
+#include <mutex>
+#include <new>
+
+namespace b200 {
+
+namespace {
+
+using namespace tc;
+
+constexpr int kSoftmaxThreads = 256;                 // two threads per query row, 32 of a tile's 64 columns each
+constexpr int kFusedThreads = kSoftmaxThreads + 64;  // + the warp that loads and the warp that issues the MMAs
+constexpr uint32_t kRows = 128;// query rows per CTA = TMEM lanes
+constexpr uint32_t kKeys = 64; // cached tokens per tile: one 128-byte swizzle row of P
+constexpr uint32_t kTmemCols = 256;// S0 [0, 64), S1 [64, 128), O [128, 128 + dh)
+constexpr uint32_t kMinSmem = 80 * 1024;// keeps a third CTA (and its TMEM request) off the SM
+
+struct FusedParams {
+    uint32_t nh, group, seq, total, tiles_m;
+    float alpha;
+    uint16_t *out;// [seq, nh, dh]
+};
+
+enum Bar { kQFull = 0, kKFull = 1, kKEmpty = 3, kVFull = 5, kVEmpty = 6, kSFull = 7, kSEmpty = 9, kPFull = 11, kPEmpty = 12, kOFull = 13, kBars = 14 };
+
+__device__ __forceinline__ uint32_t hmax2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("max.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t hmin2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("min.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+// 32 scores of one query row (columns col0 .. col0 + 31 of the score matrix) as the reference's fp16 score tensor
+// holds them, two per word: alpha * s truncated to fp16, columns beyond vis_last at -inf.  The packed conversion
+// saturates where the reference's rule (common.cuh f32_to_f16_ref) produces its overflow patterns, so a chunk whose
+// extreme values reach the largest finite fp16 is redone element by element with that rule; `exact` says that an
+// earlier chunk of the row needed it.
+__device__ __forceinline__ void pack_scores(const float *s, uint32_t *w, float alpha, uint32_t col0, uint32_t vis_last, bool &exact) {
+    uint32_t hi = 0xFC00FC00u, lo = 0x7C007C00u;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(__fmul_rn(alpha, s[2 * i + 1])), "f"(__fmul_rn(alpha, s[2 * i])));
+        hi = hmax2_u32(hi, w[i]);
+        lo = hmin2_u32(lo, w[i]);
+    }
+    const uint32_t big = 0x7BFFu;
+    if (exact || (hi & 0xFFFFu) == big || (hi >> 16) == big || (lo & 0xFFFFu) == (big | 0x8000u) || (lo >> 16) == (big | 0x8000u)) {
+        exact = true;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) w[i] = pack2_ref(__fmul_rn(alpha, s[2 * i]), __fmul_rn(alpha, s[2 * i + 1]));
+    }
+    if (col0 + 31 > vis_last) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t c = col0 + 2 * i;
+            if (c > vis_last) w[i] = 0xFC00FC00u;
+            else if (c + 1 > vis_last) w[i] = (w[i] & 0xFFFFu) | 0xFC000000u;
+        }
+    }
+}
+
+template<int DHB>// dh / 64
+__global__ void __launch_bounds__(kFusedThreads, 2)
+    attn_fused_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const FusedParams p) {
+    constexpr uint32_t kQBytes = DHB * kRows * 128u;// DHB boxes of 128 rows x 64 elements
+    constexpr uint32_t kKVBytes = DHB * kKeys * 128u;// DHB boxes of 64 rows x 64 elements
+    constexpr uint32_t kPBytes = kRows * kKeys * 2u;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
+    unsigned char *sq = smem, *sk = sq + kQBytes, *sv = sk + 2 * kKVBytes, *sp = sv + kKVBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sp + kPBytes);
+    float2 *ml = reinterpret_cast<float2 *>(bars + kBars);// [2][128]: each half's maximum and sum of a row
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(ml + 2 * kRows);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the longest blocks (last query rows) start first
+    const uint32_t tm = p.tiles_m - 1 - blockIdx.x / p.nh, h = blockIdx.x % p.nh, kvh = h / p.group;
+    const uint32_t row0 = tm * kRows;
+    const uint32_t last_row = min(row0 + kRows - 1, p.seq - 1);
+    const uint32_t tiles = (p.total - p.seq + last_row) / kKeys + 1;// tiles that hold a visible column
+
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < kBars; ++b) {
+            mbar_init(&bars[b], (b == kSEmpty || b == kSEmpty + 1 || b == kPFull) ? (uint32_t) kSoftmaxThreads : 1u);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+    }
+    if (warp == 9) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(&bars[kQFull], kQBytes);
+            for (int kb = 0; kb < DHB; ++kb) tma_load_3d(sq + kb * (kRows * 128u), &map_q, &bars[kQFull], kb * 64, (int32_t) row0, (int32_t) h);
+            for (uint32_t n = 0; n < 2 * tiles; ++n) {
+                const uint32_t j = n < tiles ? n : n - tiles, b = n & 1u, ph = (n >> 1) & 1u;
+                if (!mbar_wait(&bars[kKEmpty + b], ph ^ 1u, abort_flag)) break;
+                mbar_expect_tx(&bars[kKFull + b], kKVBytes);
+                for (int kb = 0; kb < DHB; ++kb) {
+                    tma_load_3d(sk + b * kKVBytes + kb * (kKeys * 128u), &map_k, &bars[kKFull + b], kb * 64, (int32_t) (j * kKeys), (int32_t) kvh);
+                }
+                if (n >= tiles) {
+                    if (!mbar_wait(&bars[kVEmpty], (j & 1u) ^ 1u, abort_flag)) break;
+                    mbar_expect_tx(&bars[kVFull], kKVBytes);
+                    for (int x = 0; x < DHB; ++x) {
+                        tma_load_3d(sv + x * (kKeys * 128u), &map_v, &bars[kVFull], x * 64, (int32_t) (j * kKeys), (int32_t) kvh);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 9) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_s = make_idesc(kRows, kKeys, 0, 0), idesc_o = make_idesc(kRows, DHB * 64, 0, 1);
+            const uint32_t aq = smem_u32(sq), ak = smem_u32(sk), av = smem_u32(sv), ap = smem_u32(sp);
+            // S(n) = q k(n)^T into S buffer n & 1: waits for the k tile and for the softmax warps to have read S(n - 2)
+            auto issue_s = [&](uint32_t n) -> bool {
+                const uint32_t b = n & 1u, ph = (n >> 1) & 1u;
+                if (!mbar_wait(&bars[kKFull + b], ph, abort_flag)) return false;
+                if (!mbar_wait(&bars[kSEmpty + b], ph ^ 1u, abort_flag)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int kb = 0; kb < DHB; ++kb) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        const uint64_t da = make_smem_desc(aq + kb * (kRows * 128u) + i * 32u, 16, 1024);
+                        const uint64_t db = make_smem_desc(ak + b * kKVBytes + kb * (kKeys * 128u) + i * 32u, 16, 1024);
+                        umma_f16(tmem_base + b * kKeys, da, db, idesc_s, (kb > 0 || i > 0) ? 1u : 0u);
+                    }
+                }
+                umma_commit(&bars[kKEmpty + b]);
+                umma_commit(&bars[kSFull + b]);
+                return true;
+            };
+            bool ok = mbar_wait(&bars[kQFull], 0, abort_flag);
+            uint32_t n = 0;
+            for (; ok && n < tiles; ++n) ok = issue_s(n);// pass 1
+            if (ok) ok = issue_s(n++);                   // pass 2, tile 0
+            for (uint32_t j = 0; ok && j < tiles; ++j) {
+                if (j + 1 < tiles) {
+                    ok = issue_s(n++);
+                    if (!ok) break;
+                }
+                if (!mbar_wait(&bars[kPFull], j & 1u, abort_flag) || !mbar_wait(&bars[kVFull], j & 1u, abort_flag)) break;
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    // P: K-major, 16 keys = 32 bytes along the swizzled rows; v: MN-major, 16 keys = 16 rows of 128
+                    // bytes, the second 64 head elements one box further
+                    const uint64_t da = make_smem_desc(ap + i * 32u, 16, 1024);
+                    const uint64_t db = make_smem_desc(av + i * 2048u, kKeys * 128u, 1024);
+                    umma_f16(tmem_base + 2 * kKeys, da, db, idesc_o, (j > 0 || i > 0) ? 1u : 0u);
+                }
+                umma_commit(&bars[kPEmpty]);
+                umma_commit(&bars[kVEmpty]);
+                if (j + 1 == tiles) umma_commit(&bars[kOFull]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ softmax and epilogue (warps 0..7)
+        // warp w reads TMEM lanes 32 (w & 3) .. + 31 (the lanes a warp may touch follow from its index) and the
+        // columns 32 (w >> 2) .. + 31 of every tile
+        const uint32_t quarter = warp & 3u, half = warp >> 2;
+        const uint32_t lane_row = quarter * 32 + lane, row = row0 + lane_row;
+        const uint32_t vis_last = p.total - p.seq + row;// last visible column of this row
+        const uint32_t t_lane = tmem_base + ((quarter * 32u) << 16);
+        float m = -INFINITY, l = 0.f;
+        bool exact = false, ok = true;
+        uint32_t w[16];
+        // this thread's 32 scores of tile j (S index n), packed
+        auto load_scores = [&](uint32_t n, uint32_t j) -> bool {
+            const uint32_t b = n & 1u;
+            if (!mbar_wait(&bars[kSFull + b], (n >> 1) & 1u, abort_flag)) return false;
+            tc_fence_after();
+            float s[32];
+            tmem_ld32(t_lane + b * kKeys + half * 32u, s);
+            tc_fence_before();
+            mbar_arrive(&bars[kSEmpty + b]);
+            pack_scores(s, w, p.alpha, j * kKeys + half * 32u, vis_last, exact);
+            return true;
+        };
+#pragma unroll 1
+        for (uint32_t n = 0; n < tiles; ++n) {// pass 1: maximum and sum over this thread's columns of the row
+            if (!(ok = load_scores(n, n))) break;
+            uint32_t t8[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) t8[i] = hmax2_u32(w[i], w[i + 8]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) t8[i] = hmax2_u32(t8[i], t8[i + 4]);
+            const float2 mt = unpack2(hmax2_u32(hmax2_u32(t8[0], t8[1]), hmax2_u32(t8[2], t8[3])));
+            const float m_new = fmaxf(m, fmaxf(mt.x, mt.y));
+            if (m_new != -INFINITY) {// else: all of this thread's columns so far are masked
+                const float mk = -m_new * kLog2e;
+                float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float2 f = unpack2(w[i]);
+                    part[(2 * i) & 3] += fast_exp2(fmaf(f.x, kLog2e, mk));
+                    part[(2 * i + 1) & 3] += fast_exp2(fmaf(f.y, kLog2e, mk));
+                }
+                const float scale = m == -INFINITY ? 0.f : fast_exp2(fmaf(m, kLog2e, mk));
+                l = fmaf(l, scale, (part[0] + part[1]) + (part[2] + part[3]));
+                m = m_new;
+            }
+        }
+        // the two halves of a row meet: (m, l) of the whole row
+        ml[half * kRows + lane_row] = make_float2(m, l);
+        asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+        {
+            const float2 o = ml[(half ^ 1u) * kRows + lane_row];
+            const float m_all = fmaxf(m, o.x), mk_all = -m_all * kLog2e;// column 0 is visible to every row: finite
+            const float mine = m == -INFINITY ? 0.f : l * fast_exp2(fmaf(m, kLog2e, mk_all));
+            const float theirs = o.x == -INFINITY ? 0.f : o.y * fast_exp2(fmaf(o.x, kLog2e, mk_all));
+            l = half == 0 ? mine + theirs : theirs + mine;// the same sum in both threads
+            m = m_all;
+        }
+        const float mk = -m * kLog2e, rinv = __frcp_rn(l);
+#pragma unroll 1
+        for (uint32_t j = 0; ok && j < tiles; ++j) {// pass 2: probabilities into shared memory for P v
+            if (!(ok = load_scores(tiles + j, j))) break;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float2 f = unpack2(w[i]);
+                const float q0 = __fmul_rn(fast_exp2(fmaf(f.x, kLog2e, mk)), rinv);
+                const float q1 = __fmul_rn(fast_exp2(fmaf(f.y, kLog2e, mk)), rinv);
+                asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(q1), "f"(q0));
+            }
+            if (!(ok = mbar_wait(&bars[kPEmpty], (j & 1u) ^ 1u, abort_flag))) break;
+            // row r of the K-major operand: 128 bytes, 16-byte chunk c at position c ^ (r & 7) (128-byte swizzle)
+            unsigned char *prow = sp + lane_row * 128u;
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) {
+                *reinterpret_cast<uint4 *>(prow + (((half * 4 + c) ^ (lane_row & 7u)) << 4)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");// the MMA reads P through the async proxy
+            mbar_arrive(&bars[kPFull]);
+        }
+        if (ok && mbar_wait(&bars[kOFull], 0, abort_flag)) {
+            tc_fence_after();
+            constexpr uint32_t kCols = DHB * 32;// this thread's half of the row's dh outputs
+            uint16_t *orow = p.out + ((size_t) row * p.nh + h) * (DHB * 64) + half * kCols;
+#pragma unroll
+            for (uint32_t c0 = 0; c0 < kCols; c0 += 16) {
+                float acc[16];
+                tmem_ld16(t_lane + 2 * kKeys + half * kCols + c0, acc);// every lane takes part in the load
+                uint32_t o[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[i] = pack2_ref(acc[2 * i], acc[2 * i + 1]);
+                if (row < p.seq) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(orow + c0);
+                    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // let TMA copies that are still in flight land before the shared memory is given back
+        const int loads[4] = {kQFull, kKFull, kKFull + 1, kVFull};
+        for (int i = 0; i < 4; ++i) {
+            const long long t0 = clock64();
+            while (!mbar_try_wait(&bars[loads[i]], 0) && !mbar_try_wait(&bars[loads[i]], 1) && clock64() - t0 < 2000000ll) {}
+        }
+    }
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+size_t fused_smem_bytes(uint32_t dhb) {
+    const size_t need = (size_t) dhb * kRows * 128 + 3 * (size_t) dhb * kKeys * 128 + kRows * kKeys * 2 + kBars * 8 + 2 * kRows * 8 + 16 + 1024;
+    return need < kMinSmem ? kMinSmem : need;
+}
+
+}// namespace
+
+struct AttnFused {
+    int device_id;
+    AttnPrefillShape shape;
+    uint32_t dhb, tiles_m;
+    size_t smem_bytes;
+    std::mutex mu;
+    bool valid = false;
+    const void *q_ptr = nullptr, *k_ptr = nullptr, *v_ptr = nullptr;
+    CUtensorMap map_q, map_k, map_v;
+};
+
+static bool encode_maps(AttnFused *f, const void *q, const void *k_cache, const void *v_cache) {
+    const AttnPrefillShape &s = f->shape;
+    const uint32_t nkvh = s.nh / s.group;
+    // rows beyond seq / total read as zeros: the caches' unused rows are never touched
+    return tc_encode_tiles_f16(&f->map_q, q, s.dh, s.seq, s.nh, (uint64_t) s.q_s1 * 2, (uint64_t) s.q_s0 * 2, kRows) &&
+           tc_encode_tiles_f16(&f->map_k, k_cache, s.dh, s.total, nkvh, (uint64_t) s.kc_s1 * 2, (uint64_t) s.kc_s0 * 2, kKeys) &&
+           tc_encode_tiles_f16(&f->map_v, v_cache, s.dh, s.total, nkvh, (uint64_t) s.vc_s1 * 2, (uint64_t) s.vc_s0 * 2, kKeys);
+}
+
+AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s) {
+    auto *h = reinterpret_cast<Handle *>(handle);
+    if (s.dh != 64 && s.dh != 128) return nullptr;
+    if (s.seq == 0 || s.total < s.seq || s.group == 0 || s.nh % s.group != 0) return nullptr;
+    // TMA: strides in bytes are multiples of 16 and positive, rows do not overlap
+    for (int64_t st : {s.q_s0, s.q_s1, s.kc_s0, s.kc_s1, s.vc_s0, s.vc_s1}) {
+        if (st <= 0 || st % 8 != 0 || st >= ((int64_t) 1 << 38)) return nullptr;
+    }
+    if (s.q_s1 < (int64_t) s.dh || s.kc_s1 < (int64_t) s.dh || s.vc_s1 < (int64_t) s.dh) return nullptr;
+    const uint32_t dhb = s.dh / 64;
+    const size_t smem = fused_smem_bytes(dhb);
+    if (smem > (size_t) h->max_smem_optin) return nullptr;
+    const uint64_t tiles_m = (s.seq + kRows - 1) / kRows;
+    if (tiles_m * s.nh > 0x7FFFFFFFull) return nullptr;
+    auto *kernel = dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    auto *f = new (std::nothrow) AttnFused{};
+    if (f == nullptr) return nullptr;
+    f->device_id = h->device_id;
+    f->shape = s;
+    f->dhb = dhb, f->tiles_m = (uint32_t) tiles_m, f->smem_bytes = smem;
+    // the encoder checks extents and strides, not the memory: a trial with a placeholder address tells now whether
+    // these layouts can be described, so that the caller can keep its other path
+    const void *probe = reinterpret_cast<const void *>((uintptr_t) 1 << 20);
+    if (!encode_maps(f, probe, probe, probe)) {
+        delete f;
+        return nullptr;
+    }
+    return f;
+}
+
+infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const void *k_cache, const void *v_cache,
+                                cudaStream_t st) {
+    const AttnPrefillShape &s = f->shape;
+    CUtensorMap mq, mk, mv;
+    {
+        std::lock_guard<std::mutex> lock(f->mu);
+        if (!f->valid || f->q_ptr != q || f->k_ptr != k_cache || f->v_ptr != v_cache) {
+            if (!encode_maps(f, q, k_cache, v_cache)) {
+                f->valid = false;
+                return STATUS_EXECUTION_FAILED;
+            }
+            f->valid = true, f->q_ptr = q, f->k_ptr = k_cache, f->v_ptr = v_cache;
+        }
+        mq = f->map_q, mk = f->map_k, mv = f->map_v;
+    }
+    FusedParams p{};
+    p.nh = s.nh, p.group = s.group, p.seq = s.seq, p.total = s.total, p.tiles_m = f->tiles_m;
+    p.alpha = (float) (1.0 / sqrt((double) s.dh));// `float qk_alpha = 1 / sqrt(head_dim)`, operator.cc:136
+    p.out = reinterpret_cast<uint16_t *>(out);
+    const uint32_t grid = f->tiles_m * s.nh;
+    if (f->dhb == 1) attn_fused_kernel<1><<<grid, kFusedThreads, f->smem_bytes, st>>>(mq, mk, mv, p);
+    else attn_fused_kernel<2><<<grid, kFusedThreads, f->smem_bytes, st>>>(mq, mk, mv, p);
+    return check_launch("attention (fused, several new tokens)");
+}
+
+void attn_fused_destroy(AttnFused *f) { delete f; }
+
+unsigned long long attn_fused_timeouts_read() {
+    unsigned long long v = 0;
+    if (cudaMemcpyFromSymbol(&v, tc::g_tc_gemm_timeouts, sizeof(v)) != cudaSuccess) {
+        cudaGetLastError();
+        return ~0ull;
+    }
+    return v;
+}
+
+}// namespace b200

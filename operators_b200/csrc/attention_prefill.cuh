@@ -18,4 +18,14 @@ infiniopStatus_t attn_prefill_run(AttnPrefill *p, void *workspace, void *out, co
                                   const void *v_cache, cudaStream_t stream);
 void attn_prefill_destroy(AttnPrefill *p);
 
+// The same computation in one kernel (attention_fused.cu): head sizes 64 and 128, no workspace.  nullptr when the
+// shape or the strides do not fit it.
+struct AttnFused;
+AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &shape);
+infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const void *k_cache, const void *v_cache,
+                                cudaStream_t stream);
+void attn_fused_destroy(AttnFused *f);
+// Waits that ran out of time inside the fused kernel since the library was loaded (synchronises); ~0 on error.
+unsigned long long attn_fused_timeouts_read();
+
 }// namespace b200

@@ -920,15 +920,25 @@ ATTENTION_CASES = [
     (8, 2, 300, 64, 77, 400, None, None),
     (4, 4, 130, 128, 1000, 1200, None, None),
     (16, 2, 33, 256, 31, 64, None, None),
+    # the same with the reference's strided layouts (q, k, v as [seq, head, dh]; caches as [token, head, dh]) and
+    # with exactly one / exactly two blocks of 128 query rows
+    (32, 4, 200, 64, 100, 2048, (64, 2560, 1), (64, 11264, 1)),
+    (4, 2, 128, 128, 0, 128, None, None),
+    (4, 1, 256, 64, 64, 320, None, None),
 ]
 
 
-@pytest.fixture(params=["tensor", "multiply_add", "row_tiles"])
+ATTENTION_KERNELS = {"tensor": 0, "multiply_add": 1, "row_tiles": 2, "three_launches": 3, "one_kernel": 4}
+
+
+@pytest.fixture(params=list(ATTENTION_KERNELS))
 def attention_kernels(request, cuda_lib):
     """The kernel families: the library's own choice (tcgen05 products for calls with several new tokens, the
     mma.sync row-tile kernels for decoding), the multiply-add kernels that otherwise serve unaligned layouts and
-    head sizes above 128, and the row-tile kernels everywhere."""
-    ops.select_kernel(cuda_lib[0], "attention", {"tensor": 0, "multiply_add": 1, "row_tiles": 2}[request.param])
+    head sizes above 128, the row-tile kernels everywhere, and for several new tokens the two tcgen05 forms (scores,
+    softmax and values as three launches; one kernel that keeps the scores on chip) wherever each applies.  The
+    choice is read when the descriptor is created."""
+    ops.select_kernel(cuda_lib[0], "attention", ATTENTION_KERNELS[request.param])
     yield request.param
     ops.select_kernel(cuda_lib[0], "attention", 0)
 
@@ -942,6 +952,8 @@ def test_attention(oracle, cuda_lib, attention_kernels, nh, nkvh, seq, dh, pos, 
     differs, so most elements are the same bit pattern); both caches byte for byte,
     rows outside pos .. pos+seq untouched."""
     lib, handle = cuda_lib
+    if attention_kernels in ("three_launches", "one_kernel") and seq < 32:
+        pytest.skip("fewer than 32 new tokens never take the tcgen05 forms")
     g = torch.Generator().manual_seed(21)
     q = torch.randn((nh, seq, dh), generator=g).half()
     k = torch.randn((nkvh, seq, dh), generator=g).half()
@@ -976,15 +988,20 @@ def test_attention(oracle, cuda_lib, attention_kernels, nh, nkvh, seq, dh, pos, 
     # sums of thousands of terms of both signs: a different grouping moves the last bit of more elements than elsewhere
     assert _few(mism, want.size, 0.25)
     assert torch.equal(kcd.cpu(), k_cache) and torch.equal(vcd.cpu(), v_cache)  # the oracle updated the host caches
+    assert ops.device_timeouts(lib, handle) == 0
 
 
-@pytest.mark.parametrize("nh,nkvh,seq,dh,pos", [(8, 2, 1024, 128, 0), (8, 4, 600, 64, 1000), (4, 1, 1536, 128, 512)])
-def test_attention_long_prefill_against_float32(cuda_lib, nh, nkvh, seq, dh, pos):
-    """Token counts at which the products run on CTA pairs with the causal tile skipping (several 256-row blocks per
-    head).  The oracle would take minutes here, so the check is against a float32 evaluation of the same
-    composite on the GPU (scores, causal mask, softmax, values) with a tolerance that covers the two fp16
-    roundings in between; the smaller cases of test_attention pin the same path to the oracle."""
+@pytest.mark.parametrize("kernels", ["three_launches", "one_kernel"])
+@pytest.mark.parametrize("nh,nkvh,seq,dh,pos", [(8, 2, 1024, 128, 0), (8, 4, 600, 64, 1000), (4, 1, 1536, 128, 512),
+                                                (16, 4, 2048, 128, 0)])
+def test_attention_long_prefill_against_float32(cuda_lib, nh, nkvh, seq, dh, pos, kernels):
+    """Token counts at which the three-launch form runs its products on CTA pairs with the causal tile skipping
+    (several 256-row blocks per head) and the one-kernel form walks dozens of tiles per block of query rows.  The
+    oracle would take minutes here, so the check is against a float32 evaluation of the same composite on the GPU
+    (scores, causal mask, softmax, values) with a tolerance that covers the two fp16 roundings in between; the
+    smaller cases of test_attention pin the same paths to the oracle."""
     lib, handle = cuda_lib
+    ops.select_kernel(lib, "attention", ATTENTION_KERNELS[kernels])
     g = torch.Generator().manual_seed(23)
     total = pos + seq
     q = torch.randn((nh, seq, dh), generator=g).half().to(DEV)
@@ -993,8 +1010,12 @@ def test_attention_long_prefill_against_float32(cuda_lib, nh, nkvh, seq, dh, pos
     kc = torch.randn((nkvh, total, dh), generator=g).half().to(DEV)
     vc = torch.randn((nkvh, total, dh), generator=g).half().to(DEV)
     out = torch.zeros((seq, nh, dh), dtype=torch.float16, device=DEV)
-    ops.attention(lib, handle, out, q, k, v, kc, vc, pos)
-    torch.cuda.synchronize()
+    try:
+        ops.attention(lib, handle, out, q, k, v, kc, vc, pos)
+        torch.cuda.synchronize()
+    finally:
+        ops.select_kernel(lib, "attention", 0)
+    assert ops.device_timeouts(lib, handle) == 0
     assert torch.equal(kc[:, pos:], k) and torch.equal(vc[:, pos:], v)
     group = nh // nkvh
     kf, vf = kc.float().repeat_interleave(group, 0), vc.float().repeat_interleave(group, 0)
