@@ -375,6 +375,43 @@ def only_attention(lib, handle, dev, steps, warmup):
             "note": "back-to-back calls of one operator; bytes = K and V rows read once; not a bench value"}
 
 
+PREFILL_CASE = {"new_tokens": None}  # --new-tokens: one case only (ncu captures)
+
+
+def only_attention_prefill(lib, handle, dev, steps, warmup):
+    """Not part of the step: attention for a prompt (new tokens into an empty cache), 32 q / 8 kv heads, dh 128.  FLOPs
+    count the visible half of the two products (4 * heads * dh * tokens * (tokens + 1) / 2)."""
+    import torch
+
+    from operators_b200 import ops as _ops
+
+    nh, nkvh, dh = 32, 8, ROPE_DH
+    peak = measured_tflops()
+    cases = {}
+    for seq in (512, 2048, 4096):
+        if PREFILL_CASE["new_tokens"] not in (None, seq):
+            continue
+        q = torch.randn((nh, seq, dh), device=dev).half()
+        k = torch.randn((nkvh, seq, dh), device=dev).half()
+        v = torch.randn((nkvh, seq, dh), device=dev).half()
+        k_cache = torch.zeros((nkvh, seq, dh), device=dev, dtype=torch.float16)
+        v_cache = torch.zeros((nkvh, seq, dh), device=dev, dtype=torch.float16)
+        out = torch.empty((seq, nh, dh), device=dev, dtype=torch.float16)
+        op = _ops.AttentionOp(lib, handle, out, q, k, v, k_cache, v_cache, 0)
+        ms = _timed_calls(torch, lambda: op(out, q, k, v, k_cache, v_cache), steps, warmup)
+        op.destroy()
+        flops = 4.0 * nh * dh * seq * (seq + 1) / 2
+        cases["%d_new_tokens" % seq] = {"ms": round(ms, 5), "tflops": round(flops / ms / 1e9, 1),
+                                        "frac_of_measured_bf16": round(flops / ms / 1e9 / peak[0], 3) if peak[0] else None}
+        del q, k, v, k_cache, v_cache, out
+    return {"only": "attention_prefill", "q_heads": nh, "kv_heads": nkvh, "head_dim": dh, "cases": cases,
+            "peak_tflops": {"value": peak[0], "source": peak[1]},
+            "note": "back-to-back calls: cache append + one kernel that keeps the scores on chip (--select-kernel "
+                    "attention=3: scores, softmax and values as three launches); the exponentials (two per visible "
+                    "score: the reference's rounding needs the row sum before any probability), not the tensor "
+                    "pipe, bound the one kernel; not a bench value"}
+
+
 def _timed_calls(torch, fn, steps, warmup):
     for _ in range(warmup):
         fn()
@@ -456,7 +493,7 @@ def only_mlp(lib, handle, dev, steps, warmup):
 
 
 NEXT_ROWS = {"matmul": only_matmul, "mlp": only_mlp, "rearrange": only_rearrange, "add_rms_norm": only_add_rms_norm, "rope_rearrange": only_rope_rearrange,
-             "attention": only_attention}
+             "attention": only_attention, "attention_prefill": only_attention_prefill}
 
 
 def run_b200(args):
@@ -1118,8 +1155,10 @@ def main():
                     help="force a kernel family for this run (infiniopExtSelectKernel), e.g. rope=2; for comparisons")
     ap.add_argument("--tokens", type=int, choices=[SWI_T, 16, 1], help="with --only matmul: this token count only")
     ap.add_argument("--weights", choices=["k_contiguous", "n_contiguous"], help="with --only matmul: this weight layout only")
+    ap.add_argument("--new-tokens", type=int, choices=[512, 2048, 4096], help="with --only attention_prefill: this prompt length only")
     args = ap.parse_args()
     MATMUL_CASE["tokens"], MATMUL_CASE["weights"] = args.tokens, args.weights
+    PREFILL_CASE["new_tokens"] = args.new_tokens
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)

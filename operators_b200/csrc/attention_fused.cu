@@ -17,11 +17,14 @@
 // that the reference rounds (score, probability, output) is rounded at the same place; only the grouping of the
 // fp32 sums differs.
 //
-// Roles (192 threads, two CTAs per SM so that one CTA's exponentials overlap the other's products):
-//   warps 0-3  softmax / epilogue, warp w owns TMEM lanes 32 w .. 32 w + 31
-//   warp 4     one lane issues the TMA loads: q once, k tiles through two stages (both passes), v tiles (pass 2)
-//   warp 5     allocates TMEM (S twice 64 columns, O dh columns); one lane issues the MMAs.  S of tile j + 1 is
-//              issued before P v of tile j, so it runs while the softmax warps work on tile j.
+// Roles (320 threads, two CTAs per SM so that one CTA's exponentials overlap the other's products):
+//   warps 0-7  softmax / epilogue: two threads per query row, 32 of a tile's 64 columns each; warp w owns TMEM
+//              lanes 32 (w & 3) .. + 31; the halves of a row exchange maximum and sum once, between the passes
+//   warp 8     one lane issues the TMA loads: q once, then k tiles (both passes) and v tiles (pass 2) through one
+//              ring of shared-memory slots, as far ahead as the ring is long
+//   warp 9     allocates TMEM (S twice 64 columns, O dh columns); one lane issues the MMAs.  S of tile j + 2 is
+//              issued before P v of tile j (its buffer is free once S of tile j has been read), so the softmax
+//              warps find their next scores ready.
 // Every mbarrier wait is bounded (tc_ptx.cuh); a role that gives up raises the CTA's abort flag, all roles leave,
 // copies in flight are awaited (bounded), TMEM is freed, and infiniopExtDeviceTimeouts reports it.
 #include "attention_prefill.cuh"
@@ -29,6 +32,7 @@
 
 #include <mutex>
 #include <new>
+#include <type_traits>
 
 namespace b200 {
 
@@ -45,11 +49,29 @@ constexpr uint32_t kMinSmem = 80 * 1024;// keeps a third CTA (and its TMEM reque
 
 struct FusedParams {
     uint32_t nh, group, seq, total, tiles_m;
+    uint32_t slots;// k / v tiles of the shared-memory ring (4 when two CTAs share an SM, more for a CTA alone)
     float alpha;
     uint16_t *out;// [seq, nh, dh]
 };
 
-enum Bar { kQFull = 0, kKFull = 1, kKEmpty = 3, kVFull = 5, kVEmpty = 6, kSFull = 7, kSEmpty = 9, kPFull = 11, kPEmpty = 12, kOFull = 13, kBars = 14 };
+constexpr uint32_t kMaxSlots = 16;// k / v tiles in flight per CTA
+// Waiting roles sleep in the barrier instead of polling: twenty warps share an SM and the exponentials need the issue
+// slots (polling producer and MMA lanes took four of ten issued instructions).
+constexpr uint32_t kSuspendNs = 20000;
+
+// Development aid (-DB200_ATTN_FUSED_TRACE): thread 0 of CTA 0 adds up the clock ticks it spends in each step of the
+// softmax loops.  Not compiled into the library.
+#ifdef B200_ATTN_FUSED_TRACE
+__device__ unsigned long long g_attn_trace[16];
+#define TRACE_NOW(var) const long long var = clock64()
+#define TRACE_ADD(slot, t0, t1) \
+    if (threadIdx.x == 0 && blockIdx.x == 0) g_attn_trace[slot] += (unsigned long long) ((t1) - (t0))
+#else
+#define TRACE_NOW(var)
+#define TRACE_ADD(slot, t0, t1)
+#endif
+// barriers: the ring's full / empty pairs first
+enum Bar { kFull = 0, kEmpty = kMaxSlots, kQFull = 2 * kMaxSlots, kSFull, kSFull1, kSEmpty, kSEmpty1, kPFull, kPEmpty, kOFull, kBars };
 
 __device__ __forceinline__ uint32_t hmax2_u32(uint32_t a, uint32_t b) {
     uint32_t r;
@@ -64,20 +86,23 @@ __device__ __forceinline__ uint32_t hmin2_u32(uint32_t a, uint32_t b) {
 
 // 32 scores of one query row (columns col0 .. col0 + 31 of the score matrix) as the reference's fp16 score tensor
 // holds them, two per word: alpha * s truncated to fp16, columns beyond vis_last at -inf.  The packed conversion
-// saturates where the reference's rule (common.cuh f32_to_f16_ref) produces its overflow patterns, so a chunk whose
-// extreme values reach the largest finite fp16 is redone element by element with that rule; `exact` says that an
-// earlier chunk of the row needed it.
+// saturates where the reference's rule (common.cuh f32_to_f16_ref) produces its overflow patterns, so in pass 1
+// (CHECK) a chunk whose extreme values reach the largest finite fp16 is redone element by element with that rule
+// and `exact` stays set for the rest of the row's columns of this thread; pass 2 converts the same elements again
+// and only reads the flag.
+template<bool CHECK>
 __device__ __forceinline__ void pack_scores(const float *s, uint32_t *w, float alpha, uint32_t col0, uint32_t vis_last, bool &exact) {
     uint32_t hi = 0xFC00FC00u, lo = 0x7C007C00u;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(__fmul_rn(alpha, s[2 * i + 1])), "f"(__fmul_rn(alpha, s[2 * i])));
-        hi = hmax2_u32(hi, w[i]);
-        lo = hmin2_u32(lo, w[i]);
+        if (CHECK) hi = hmax2_u32(hi, w[i]), lo = hmin2_u32(lo, w[i]);
     }
     const uint32_t big = 0x7BFFu;
-    if (exact || (hi & 0xFFFFu) == big || (hi >> 16) == big || (lo & 0xFFFFu) == (big | 0x8000u) || (lo >> 16) == (big | 0x8000u)) {
+    if (CHECK && ((hi & 0xFFFFu) == big || (hi >> 16) == big || (lo & 0xFFFFu) == (big | 0x8000u) || (lo >> 16) == (big | 0x8000u))) {
         exact = true;
+    }
+    if (exact) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) w[i] = pack2_ref(__fmul_rn(alpha, s[2 * i]), __fmul_rn(alpha, s[2 * i + 1]));
     }
@@ -99,11 +124,16 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
     constexpr uint32_t kKVBytes = DHB * kKeys * 128u;// DHB boxes of 64 rows x 64 elements
     constexpr uint32_t kPBytes = kRows * kKeys * 2u;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t) 1023);
-    unsigned char *sq = smem, *sk = sq + kQBytes, *sv = sk + 2 * kKVBytes, *sp = sv + kKVBytes;
+    // q | ring of k / v tiles | P | barriers.  The swizzled tiles need 1024-byte alignment; the request leaves no room
+    // to round the base up (two CTAs fill the SM), so a base that is not aligned ends the CTA before it starts.
+    if ((smem_u32(smem_raw) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicAdd(&g_tc_gemm_timeouts, 1ull);
+        return;
+    }
+    unsigned char *sq = smem_raw, *ring = sq + kQBytes, *sp = ring + p.slots * kKVBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(sp + kPBytes);
-    float2 *ml = reinterpret_cast<float2 *>(bars + kBars);// [2][128]: each half's maximum and sum of a row
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(ml + 2 * kRows);
+    float2 *ml = reinterpret_cast<float2 *>(sp);// [2][128]: each half's maximum and sum of a row, between the passes
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -115,7 +145,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
 
     if (threadIdx.x == 0) {
         for (int b = 0; b < kBars; ++b) {
-            mbar_init(&bars[b], (b == kSEmpty || b == kSEmpty + 1 || b == kPFull) ? (uint32_t) kSoftmaxThreads : 1u);
+            mbar_init(&bars[b], (b == kSEmpty || b == kSEmpty1 || b == kPFull) ? (uint32_t) kSoftmaxThreads : 1u);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -137,20 +167,25 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         if (lane == 0) {
             mbar_expect_tx(&bars[kQFull], kQBytes);
             for (int kb = 0; kb < DHB; ++kb) tma_load_3d(sq + kb * (kRows * 128u), &map_q, &bars[kQFull], kb * 64, (int32_t) row0, (int32_t) h);
-            for (uint32_t n = 0; n < 2 * tiles; ++n) {
-                const uint32_t j = n < tiles ? n : n - tiles, b = n & 1u, ph = (n >> 1) & 1u;
-                if (!mbar_wait(&bars[kKEmpty + b], ph ^ 1u, abort_flag)) break;
-                mbar_expect_tx(&bars[kKFull + b], kKVBytes);
-                for (int kb = 0; kb < DHB; ++kb) {
-                    tma_load_3d(sk + b * kKVBytes + kb * (kKeys * 128u), &map_k, &bars[kKFull + b], kb * 64, (int32_t) (j * kKeys), (int32_t) kvh);
+            // The ring is a queue: tiles are loaded in the order in which the MMA lane uses them.  Pass 1: k(0) ..
+            // k(T - 1); pass 2: k(0), k(1), then k(j + 2), v(j) for j = 0 .. T - 1.
+            uint32_t slot = 0, ph = 0;
+            auto load = [&](bool is_v, uint32_t j) -> bool {
+                if (!mbar_wait<kSuspendNs>(&bars[kEmpty + slot], ph ^ 1u, abort_flag)) return false;
+                mbar_expect_tx(&bars[kFull + slot], kKVBytes);
+                for (int x = 0; x < DHB; ++x) {// k: 64 of the dh elements per box (K-major); v: the same boxes (MN-major)
+                    tma_load_3d(ring + slot * kKVBytes + x * (kKeys * 128u), is_v ? &map_v : &map_k, &bars[kFull + slot], x * 64,
+                                (int32_t) (j * kKeys), (int32_t) kvh);
                 }
-                if (n >= tiles) {
-                    if (!mbar_wait(&bars[kVEmpty], (j & 1u) ^ 1u, abort_flag)) break;
-                    mbar_expect_tx(&bars[kVFull], kKVBytes);
-                    for (int x = 0; x < DHB; ++x) {
-                        tma_load_3d(sv + x * (kKeys * 128u), &map_v, &bars[kVFull], x * 64, (int32_t) (j * kKeys), (int32_t) kvh);
-                    }
-                }
+                if (++slot == p.slots) slot = 0, ph ^= 1u;
+                return true;
+            };
+            bool ok = true;
+            for (uint32_t n = 0; ok && n < tiles; ++n) ok = load(false, n);
+            for (uint32_t n = 0; ok && n < 2 && n < tiles; ++n) ok = load(false, n);
+            for (uint32_t j = 0; ok && j < tiles; ++j) {
+                if (j + 2 < tiles) ok = load(false, j + 2);
+                if (ok) ok = load(true, j);
             }
         }
         __syncwarp();
@@ -158,47 +193,52 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc_s = make_idesc(kRows, kKeys, 0, 0), idesc_o = make_idesc(kRows, DHB * 64, 0, 1);
-            const uint32_t aq = smem_u32(sq), ak = smem_u32(sk), av = smem_u32(sv), ap = smem_u32(sp);
+            const uint32_t aq = smem_u32(sq), aring = smem_u32(ring), ap = smem_u32(sp);
+            uint32_t slot = 0, slot_ph = 0;// the ring slot of the next tile in the producer's order
             // S(n) = q k(n)^T into S buffer n & 1: waits for the k tile and for the softmax warps to have read S(n - 2)
             auto issue_s = [&](uint32_t n) -> bool {
                 const uint32_t b = n & 1u, ph = (n >> 1) & 1u;
-                if (!mbar_wait(&bars[kKFull + b], ph, abort_flag)) return false;
-                if (!mbar_wait(&bars[kSEmpty + b], ph ^ 1u, abort_flag)) return false;
+                if (!mbar_wait<kSuspendNs>(&bars[kFull + slot], slot_ph, abort_flag)) return false;
+                if (!mbar_wait<kSuspendNs>(&bars[kSEmpty + b], ph ^ 1u, abort_flag)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int kb = 0; kb < DHB; ++kb) {
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
                         const uint64_t da = make_smem_desc(aq + kb * (kRows * 128u) + i * 32u, 16, 1024);
-                        const uint64_t db = make_smem_desc(ak + b * kKVBytes + kb * (kKeys * 128u) + i * 32u, 16, 1024);
+                        const uint64_t db = make_smem_desc(aring + slot * kKVBytes + kb * (kKeys * 128u) + i * 32u, 16, 1024);
                         umma_f16(tmem_base + b * kKeys, da, db, idesc_s, (kb > 0 || i > 0) ? 1u : 0u);
                     }
                 }
-                umma_commit(&bars[kKEmpty + b]);
+                umma_commit(&bars[kEmpty + slot]);
                 umma_commit(&bars[kSFull + b]);
+                if (++slot == p.slots) slot = 0, slot_ph ^= 1u;
                 return true;
             };
-            bool ok = mbar_wait(&bars[kQFull], 0, abort_flag);
+            bool ok = mbar_wait<kSuspendNs>(&bars[kQFull], 0, abort_flag);
             uint32_t n = 0;
             for (; ok && n < tiles; ++n) ok = issue_s(n);// pass 1
-            if (ok) ok = issue_s(n++);                   // pass 2, tile 0
+            for (uint32_t j = 0; ok && j < 2 && j < tiles; ++j) ok = issue_s(n++);// pass 2, tiles 0 and 1
             for (uint32_t j = 0; ok && j < tiles; ++j) {
-                if (j + 1 < tiles) {
+                // S of tile j + 2 goes first: its buffer is free as soon as the softmax warps have read S of tile j,
+                // long before they deliver P of tile j, so no product waits behind the exponentials
+                if (j + 2 < tiles) {
                     ok = issue_s(n++);
                     if (!ok) break;
                 }
-                if (!mbar_wait(&bars[kPFull], j & 1u, abort_flag) || !mbar_wait(&bars[kVFull], j & 1u, abort_flag)) break;
+                if (!mbar_wait<kSuspendNs>(&bars[kPFull], j & 1u, abort_flag) || !mbar_wait<kSuspendNs>(&bars[kFull + slot], slot_ph, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
                 for (uint32_t i = 0; i < 4; ++i) {
                     // P: K-major, 16 keys = 32 bytes along the swizzled rows; v: MN-major, 16 keys = 16 rows of 128
                     // bytes, the second 64 head elements one box further
                     const uint64_t da = make_smem_desc(ap + i * 32u, 16, 1024);
-                    const uint64_t db = make_smem_desc(av + i * 2048u, kKeys * 128u, 1024);
+                    const uint64_t db = make_smem_desc(aring + slot * kKVBytes + i * 2048u, kKeys * 128u, 1024);
                     umma_f16(tmem_base + 2 * kKeys, da, db, idesc_o, (j > 0 || i > 0) ? 1u : 0u);
                 }
                 umma_commit(&bars[kPEmpty]);
-                umma_commit(&bars[kVEmpty]);
+                umma_commit(&bars[kEmpty + slot]);
+                if (++slot == p.slots) slot = 0, slot_ph ^= 1u;
                 if (j + 1 == tiles) umma_commit(&bars[kOFull]);
             }
         }
@@ -215,20 +255,29 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         bool exact = false, ok = true;
         uint32_t w[16];
         // this thread's 32 scores of tile j (S index n), packed
-        auto load_scores = [&](uint32_t n, uint32_t j) -> bool {
+        auto load_scores = [&](uint32_t n, uint32_t j, auto first_pass) -> bool {
             const uint32_t b = n & 1u;
-            if (!mbar_wait(&bars[kSFull + b], (n >> 1) & 1u, abort_flag)) return false;
+            constexpr int kT = decltype(first_pass)::value ? 0 : 4;
+            TRACE_NOW(t0);
+            if (!mbar_wait<kSuspendNs>(&bars[kSFull + b], (n >> 1) & 1u, abort_flag)) return false;
+            TRACE_NOW(t1);
             tc_fence_after();
             float s[32];
             tmem_ld32(t_lane + b * kKeys + half * 32u, s);
             tc_fence_before();
             mbar_arrive(&bars[kSEmpty + b]);
-            pack_scores(s, w, p.alpha, j * kKeys + half * 32u, vis_last, exact);
+            TRACE_NOW(t2);
+            pack_scores<decltype(first_pass)::value>(s, w, p.alpha, j * kKeys + half * 32u, vis_last, exact);
+            TRACE_NOW(t3);
+            TRACE_ADD(kT + 0, t0, t1);
+            TRACE_ADD(kT + 1, t1, t2);
+            TRACE_ADD(kT + 2, t2, t3);
             return true;
         };
 #pragma unroll 1
         for (uint32_t n = 0; n < tiles; ++n) {// pass 1: maximum and sum over this thread's columns of the row
-            if (!(ok = load_scores(n, n))) break;
+            if (!(ok = load_scores(n, n, std::true_type{}))) break;
+            TRACE_NOW(ta);
             uint32_t t8[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) t8[i] = hmax2_u32(w[i], w[i + 8]);
@@ -249,6 +298,8 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
                 l = fmaf(l, scale, (part[0] + part[1]) + (part[2] + part[3]));
                 m = m_new;
             }
+            TRACE_NOW(tb);
+            TRACE_ADD(3, ta, tb);
         }
         // the two halves of a row meet: (m, l) of the whole row
         ml[half * kRows + lane_row] = make_float2(m, l);
@@ -261,18 +312,21 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
             l = half == 0 ? mine + theirs : theirs + mine;// the same sum in both threads
             m = m_all;
         }
-        const float mk = -m * kLog2e, rinv = __frcp_rn(l);
+        asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");// the exchange area becomes P again
+        // exp(x - m) / l as one exponential: 2^(x log2e - m log2e - log2 l)
+        const float mk = fmaf(-m, kLog2e, -log2f(l));
 #pragma unroll 1
         for (uint32_t j = 0; ok && j < tiles; ++j) {// pass 2: probabilities into shared memory for P v
-            if (!(ok = load_scores(tiles + j, j))) break;
+            if (!(ok = load_scores(tiles + j, j, std::false_type{}))) break;
+            TRACE_NOW(ta);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const float2 f = unpack2(w[i]);
-                const float q0 = __fmul_rn(fast_exp2(fmaf(f.x, kLog2e, mk)), rinv);
-                const float q1 = __fmul_rn(fast_exp2(fmaf(f.y, kLog2e, mk)), rinv);
-                asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(q1), "f"(q0));
+                asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(fast_exp2(fmaf(f.y, kLog2e, mk))), "f"(fast_exp2(fmaf(f.x, kLog2e, mk))));
             }
-            if (!(ok = mbar_wait(&bars[kPEmpty], (j & 1u) ^ 1u, abort_flag))) break;
+            TRACE_NOW(tb);
+            if (!(ok = mbar_wait<kSuspendNs>(&bars[kPEmpty], (j & 1u) ^ 1u, abort_flag))) break;
+            TRACE_NOW(tc_);
             // row r of the K-major operand: 128 bytes, 16-byte chunk c at position c ^ (r & 7) (128-byte swizzle)
             unsigned char *prow = sp + lane_row * 128u;
 #pragma unroll
@@ -281,8 +335,12 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");// the MMA reads P through the async proxy
             mbar_arrive(&bars[kPFull]);
+            TRACE_NOW(td);
+            TRACE_ADD(7, ta, tb);
+            TRACE_ADD(8, tb, tc_);
+            TRACE_ADD(9, tc_, td);
         }
-        if (ok && mbar_wait(&bars[kOFull], 0, abort_flag)) {
+        if (ok && mbar_wait<kSuspendNs>(&bars[kOFull], 0, abort_flag)) {
             tc_fence_after();
             constexpr uint32_t kCols = DHB * 32;// this thread's half of the row's dh outputs
             uint16_t *orow = p.out + ((size_t) row * p.nh + h) * (DHB * 64) + half * kCols;
@@ -307,10 +365,10 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
     __syncthreads();
     if (*abort_flag && threadIdx.x == 0) {
         // let TMA copies that are still in flight land before the shared memory is given back
-        const int loads[4] = {kQFull, kKFull, kKFull + 1, kVFull};
-        for (int i = 0; i < 4; ++i) {
+        for (uint32_t i = 0; i <= p.slots; ++i) {
+            uint64_t *bar = i < p.slots ? &bars[kFull + i] : &bars[kQFull];
             const long long t0 = clock64();
-            while (!mbar_try_wait(&bars[loads[i]], 0) && !mbar_try_wait(&bars[loads[i]], 1) && clock64() - t0 < 2000000ll) {}
+            while (!mbar_try_wait(bar, 0) && !mbar_try_wait(bar, 1) && clock64() - t0 < 2000000ll) {}
         }
     }
     __syncthreads();
@@ -320,9 +378,16 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
     }
 }
 
-size_t fused_smem_bytes(uint32_t dhb) {
-    const size_t need = (size_t) dhb * kRows * 128 + 3 * (size_t) dhb * kKeys * 128 + kRows * kKeys * 2 + kBars * 8 + 2 * kRows * 8 + 16 + 1024;
+// Shared memory of a CTA with `slots` ring tiles.
+size_t fused_smem_bytes(uint32_t dhb, uint32_t slots) {
+    const size_t need = (size_t) dhb * kRows * 128 + (size_t) slots * dhb * kKeys * 128 + kRows * kKeys * 2 + kBars * 8 + 16;
     return need < kMinSmem ? kMinSmem : need;
+}
+// The most ring tiles that fit `budget` bytes (at most kMaxSlots); 0 when not even four fit.
+uint32_t fused_slots(uint32_t dhb, size_t budget) {
+    uint32_t slots = kMaxSlots;
+    while (slots >= 4 && fused_smem_bytes(dhb, slots) > budget) --slots;
+    return slots >= 4 ? slots : 0;
 }
 
 }// namespace
@@ -330,7 +395,7 @@ size_t fused_smem_bytes(uint32_t dhb) {
 struct AttnFused {
     int device_id;
     AttnPrefillShape shape;
-    uint32_t dhb, tiles_m;
+    uint32_t dhb, tiles_m, slots;
     size_t smem_bytes;
     std::mutex mu;
     bool valid = false;
@@ -357,12 +422,24 @@ AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s)
     }
     if (s.q_s1 < (int64_t) s.dh || s.kc_s1 < (int64_t) s.dh || s.vc_s1 < (int64_t) s.dh) return nullptr;
     const uint32_t dhb = s.dh / 64;
-    const size_t smem = fused_smem_bytes(dhb);
-    if (smem > (size_t) h->max_smem_optin) return nullptr;
     const uint64_t tiles_m = (s.seq + kRows - 1) / kRows;
     if (tiles_m * s.nh > 0x7FFFFFFFull) return nullptr;
+    // A grid that leaves every CTA an SM of its own gets the whole shared memory for its ring of k / v tiles (the
+    // loads of up to 11 tiles in flight hide the latency one CTA sees); otherwise two CTAs share an SM and each
+    // takes half (4 tiles at dh 128), less the kilobyte the system keeps per CTA.
+    int sm_bytes = 0;
+    if (cudaDeviceGetAttribute(&sm_bytes, cudaDevAttrMaxSharedMemoryPerMultiprocessor, h->device_id) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    const uint32_t slots_alone = fused_slots(dhb, (size_t) h->max_smem_optin);
+    const uint32_t slots_shared = fused_slots(dhb, (size_t) sm_bytes / 2 - 1024);
+    const uint32_t slots = tiles_m * s.nh <= (uint64_t) h->sm_count ? slots_alone : slots_shared;
+    if (slots == 0 || slots_alone == 0) return nullptr;
+    const size_t smem = fused_smem_bytes(dhb, slots);
     auto *kernel = dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fused_smem_bytes(dhb, slots_alone)) != cudaSuccess ||
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
         cudaGetLastError();
         return nullptr;
     }
@@ -370,7 +447,7 @@ AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s)
     if (f == nullptr) return nullptr;
     f->device_id = h->device_id;
     f->shape = s;
-    f->dhb = dhb, f->tiles_m = (uint32_t) tiles_m, f->smem_bytes = smem;
+    f->dhb = dhb, f->tiles_m = (uint32_t) tiles_m, f->slots = slots, f->smem_bytes = smem;
     // the encoder checks extents and strides, not the memory: a trial with a placeholder address tells now whether
     // these layouts can be described, so that the caller can keep its other path
     const void *probe = reinterpret_cast<const void *>((uintptr_t) 1 << 20);
@@ -397,7 +474,7 @@ infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const vo
         mq = f->map_q, mk = f->map_k, mv = f->map_v;
     }
     FusedParams p{};
-    p.nh = s.nh, p.group = s.group, p.seq = s.seq, p.total = s.total, p.tiles_m = f->tiles_m;
+    p.nh = s.nh, p.group = s.group, p.seq = s.seq, p.total = s.total, p.tiles_m = f->tiles_m, p.slots = f->slots;
     p.alpha = (float) (1.0 / sqrt((double) s.dh));// `float qk_alpha = 1 / sqrt(head_dim)`, operator.cc:136
     p.out = reinterpret_cast<uint16_t *>(out);
     const uint32_t grid = f->tiles_m * s.nh;
@@ -407,6 +484,17 @@ infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const vo
 }
 
 void attn_fused_destroy(AttnFused *f) { delete f; }
+
+#ifdef B200_ATTN_FUSED_TRACE
+extern "C" __attribute__((visibility("default"))) int infiniopDebugAttnTrace(unsigned long long *out16, int reset) {
+    if (cudaMemcpyFromSymbol(out16, g_attn_trace, 16 * sizeof(unsigned long long)) != cudaSuccess) return 1;
+    if (reset) {
+        unsigned long long zero[16] = {};
+        if (cudaMemcpyToSymbol(g_attn_trace, zero, sizeof(zero)) != cudaSuccess) return 1;
+    }
+    return 0;
+}
+#endif
 
 unsigned long long attn_fused_timeouts_read() {
     unsigned long long v = 0;

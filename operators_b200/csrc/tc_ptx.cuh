@@ -38,11 +38,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the budget ran out or another role already gave up.
+// The same with a time limit (ns) up to which the hardware may keep the thread suspended: a waiting thread then
+// costs no issue slots, and resumes when the phase completes.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the budget ran out or another role already gave up.  SUSPEND_NS > 0: the polls carry that
+// suspend-time hint (for roles that wait long while other warps of the SM need the issue slots).
+template<uint32_t SUSPEND_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    while (!(SUSPEND_NS > 0 ? mbar_try_wait_hint(bar, parity, SUSPEND_NS) : mbar_try_wait(bar, parity))) {
         if (*abort_flag) return false;
         if (clock64() - t0 > kWaitBudget) {
             *abort_flag = 1;
