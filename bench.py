@@ -425,6 +425,7 @@ def _timed_calls(torch, fn, steps, warmup):
     return t0.elapsed_time(t1) / steps
 
 
+SHARDED_MODES = ("exact", "exact_all_to_all", "exact_all_gather", "exact_peer_memory", "fast")
 MATMUL_CASE = {"tokens": None, "weights": None}  # --tokens / --weights: one case only (ncu captures)
 
 
@@ -764,7 +765,7 @@ def run_b200(args):
         import torch.distributed as dist
 
         from operators_b200 import ops as _ops
-        from operators_b200.sharding import VocabShardedSampler, shard_rows, vocab_range
+        from operators_b200.sharding import PeerBlocks, VocabShardedSampler, shard_rows, vocab_range
 
         t = step.t
         sl = {k: shard_rows(t[k], world, rank) for k in ("rope_t", "rope_pos", "gate_up", "swi_c", "add_a", "add_b", "add_c", "att")}
@@ -798,13 +799,20 @@ def run_b200(args):
         full = (torch.randn((RS_B, RS_V), generator=gsh) * 3).half()
         ush = torch.rand(RS_B, generator=gsh).to(dev)
         b0, e0 = vocab_range(RS_V, world, rank)
-        shard = full[:, b0:e0].contiguous().to(dev)
-        out = torch.zeros(RS_B, dtype=torch.int64, device=dev)
-        sop = _ops.RandomSampleOp(lib, handle, out[:1], shard[0])
+        shard_own = full[:, b0:e0].contiguous().to(dev)
+        out_own = torch.zeros(RS_B, dtype=torch.int64, device=dev)
+        sop = _ops.RandomSampleOp(lib, handle, out_own[:1], shard_own[0])
         sharded = {}
-        for mode in ("exact", "exact_all_to_all", "exact_all_gather", "fast"):
+        exact_indices = None
+        for mode in SHARDED_MODES:
             exch = mode[6:] if mode.startswith("exact_") else "auto"
-            sampler = VocabShardedSampler(lib, handle, sop, RS_V, b0, world, mode=mode[:5].rstrip("_"), rank=rank, exchange=exch)
+            out, shard, pb = out_own, shard_own, None
+            if exch == "peer_memory":  # shard and results live in the block the peers address: no copy on the way
+                pb = PeerBlocks(lib, handle, RS_B, e0 - b0, world, rank, dev)
+                pb.logits.copy_(shard_own)
+                out, shard = pb.results, pb.logits
+            sampler = VocabShardedSampler(lib, handle, sop, RS_V, b0, world, mode=mode[:5].rstrip("_"), rank=rank,
+                                          exchange=exch, peer_blocks=pb)
             for _ in range(3):
                 sampler.sample(out, shard, ush, RS_TOPP, RS_TOPK, RS_TEMP, check=False)
             barrier()
@@ -832,9 +840,15 @@ def run_b200(args):
             res["exchange"] = sampler.exchange if mode != "fast" else None
             if not args.sharded_graph:
                 if mode == "exact":
-                    res["indices"] = out.cpu().tolist()
+                    exact_indices = out.cpu().tolist()
+                    res["indices"] = exact_indices
+                elif mode.startswith("exact_"):
+                    res["same_indices_as_exact"] = out.cpu().tolist() == exact_indices
                 sharded[mode] = res
                 sampler.destroy()
+                if pb is not None:
+                    barrier()  # nobody frees a block that a peer may still read
+                    pb.destroy()
                 continue
             try:
                 side = torch.cuda.Stream()
@@ -862,9 +876,15 @@ def run_b200(args):
             del gr
             torch.cuda.synchronize()
             if mode == "exact":
-                res["indices"] = out.cpu().tolist()
+                exact_indices = out.cpu().tolist()
+                res["indices"] = exact_indices
+            elif mode.startswith("exact_"):
+                res["same_indices_as_exact"] = out.cpu().tolist() == exact_indices
             sharded[mode] = res
             sampler.destroy()
+            if pb is not None:
+                barrier()
+                pb.destroy()
         sharded_ms = sharded["exact"]["ms"]
     else:
         sharded_ms = None
@@ -958,7 +978,7 @@ def run_b200(args):
                     "launch latency, not bandwidth" % world,
             "ops": split}
         rs = {}
-        for mode in ("exact", "exact_all_to_all", "exact_all_gather", "fast"):
+        for mode in SHARDED_MODES:
             rs[mode] = {"ms": round(extra["sharded.%s.ms" % mode], 4), "exchange": sharded[mode].get("exchange"),
                         "ms_graph": round(extra["sharded.%s.ms_graph" % mode], 4) or None,
                         "tokens_per_s": round(RS_B / (extra["sharded.%s.ms" % mode] * 1e-3), 1),
@@ -966,12 +986,19 @@ def run_b200(args):
                                       if k.startswith("sharded.%s.stage." % mode)}}
             if "graph_error" in sharded[mode]:
                 rs[mode]["graph_error"] = sharded[mode]["graph_error"]
+            if "same_indices_as_exact" in sharded[mode]:
+                rs[mode]["same_indices_as_exact"] = sharded[mode]["same_indices_as_exact"]
         rs["exact"]["what"] = ("64 rows, vocabulary 128256 split over %d GPUs; default mode, index-exact: one NCCL "
                                "collective (all-to-all: %d bytes received per rank; or all-gather of all shards: %d "
                                "bytes) gives every rank %d whole rows, the exact kernel samples them, one all-gather "
                                "returns the indices; exact_all_to_all / exact_all_gather force one exchange each" %
                                (world, RS_B // world * RS_V * 2 * (world - 1) // world,
                                 RS_B * RS_V * 2 * (world - 1) // world, RS_B // world))
+        rs["exact_peer_memory"]["what"] = ("no collective library: every rank's shard, results and flags in a block the "
+                                           "peers opened through CUDA IPC; one kernel of this library pulls the rank's "
+                                           "%d rows out of the peers' shards over NVLink (plain loads, bounded flag "
+                                           "waits), the exact kernel samples them, one kernel pushes the indices to "
+                                           "every peer" % (RS_B // world))
         rs["fast"]["what"] = ("local candidate kernel, one NCCL all-gather of %d bytes per rank, finishing kernel; "
                               "denominator correctly rounded instead of sequential" % (RS_B * 1056))
         rs["one_gpu_unsharded_ms"] = round(own_per_op_ms["random_sample"], 4)

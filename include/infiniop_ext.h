@@ -32,7 +32,8 @@ INFINIOP_API infiniopStatus_t infiniopExtSelectKernel(int family, int variant);
 /*
  * Bounded waits (no counterpart in the reference).  The kernels that wait on
  * hardware barriers for asynchronous copies (the RoPE bulk-copy pipeline, the
- * tensor-core matmul) give every wait a limit; a wait that runs out makes its
+ * tensor-core matmul and attention kernels, the long-row ring) or on another
+ * GPU's flag (the peer-memory exchange) give every wait a limit; a wait that runs out makes its
  * thread group stop, let its copies in flight land, and leave.  The call has
  * then already returned STATUS_SUCCESS, and its output is incomplete.
  * infiniopExtDeviceTimeouts reports how many groups gave up on this handle's
@@ -136,5 +137,49 @@ INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchStatic(infiniopRandomSamp
                                                               void const *logits, int64_t row_stride, uint64_t rows,
                                                               void const *random_vals, float topp, int topk,
                                                               float temperature, void *stream);
+
+/*
+ * Rows of a column-sharded matrix over peer memory (no counterpart in the
+ * reference, which has no multi-device code).  For vocabulary-sharded
+ * sampling on the GPUs of one node: every rank holds columns
+ * [col0_r, col0_r + cols_r) of a [rows, voc] fp16 matrix in a block of device
+ * memory that the other ranks have opened through CUDA IPC, and needs the
+ * whole rows [row0, row0 + nrows).
+ *
+ * infiniopExtPeerAlloc is the one call of this library that allocates device
+ * memory: `bytes` of zeroed memory from cudaMalloc (so that the block can be
+ * exported) and the 64-byte IPC handle to send to the other ranks' processes;
+ * infiniopExtPeerOpen maps another rank's block (not the caller's own: use
+ * the pointer from PeerAlloc), infiniopExtPeerClose / infiniopExtPeerFree undo
+ * them.  The first 256 bytes of every block belong to the library (flags and a
+ * call counter, zero at the start and never written by the caller).
+ *
+ * infiniopExtPeerGatherRows: `shards[r]`, `shard_row_strides[r]` (elements),
+ * `shard_col0[r]`, `shard_cols[r]` describe rank r's columns as this process
+ * addresses them, `flags[r]` is the start of rank r's block.  The kernel tells
+ * every peer that this rank's shard is final (everything issued earlier on
+ * `stream` has completed), waits for each peer's word and copies the peers'
+ * columns of this rank's rows into `full` ([nrows, voc], `full_row_stride`
+ * elements).  infiniopExtPeerPublishResults writes `picked` (u64[nrows], this
+ * rank's results) to rows [row0, row0 + nrows) of every `results[r]` (u64
+ * arrays inside the blocks), and returns to the stream only when every rank has
+ * done the same: afterwards results[rank] holds all rows, and the shard may
+ * be overwritten.  Every rank must issue the same sequence of these two calls.
+ * Plain peer loads and stores; no multicast.  Waits are bounded (about a
+ * second) and reported by infiniopExtDeviceTimeouts.  world <= 16.
+ */
+INFINIOP_API infiniopStatus_t infiniopExtPeerAlloc(infiniopHandle_t handle, uint64_t bytes, void **ptr,
+                                                   unsigned char *ipc_handle64);
+INFINIOP_API infiniopStatus_t infiniopExtPeerOpen(infiniopHandle_t handle, const unsigned char *ipc_handle64, void **ptr);
+INFINIOP_API infiniopStatus_t infiniopExtPeerClose(infiniopHandle_t handle, void *ptr);
+INFINIOP_API infiniopStatus_t infiniopExtPeerFree(infiniopHandle_t handle, void *ptr);
+INFINIOP_API infiniopStatus_t infiniopExtPeerGatherRows(infiniopHandle_t handle, void *full, int64_t full_row_stride,
+                                                        void *const *shards, const int64_t *shard_row_strides,
+                                                        const uint64_t *shard_col0, const uint64_t *shard_cols,
+                                                        void *const *flags, uint32_t world, uint32_t rank,
+                                                        uint64_t row0, uint64_t nrows, void *stream);
+INFINIOP_API infiniopStatus_t infiniopExtPeerPublishResults(infiniopHandle_t handle, void *const *results,
+                                                            const void *picked, void *const *flags, uint32_t world,
+                                                            uint32_t rank, uint64_t row0, uint64_t nrows, void *stream);
 
 #endif /* INFINIOP_B200_EXT_H */

@@ -11,9 +11,13 @@ the unchanged single-device C ABI:
   the ranks (the layout a tensor-parallel LM head leaves them in).  Its default
   mode is index-exact: one all-to-all hands every rank whole rows, the exact
   batched kernel samples them, one all-gather returns the indices.  Its fast mode
-  exchanges ~1 KB of candidates per row per rank in ONE all-gather.  Received
-  data is in local memory before any kernel reads it; nothing here loads from a
-  peer's memory.
+  exchanges ~1 KB of candidates per row per rank in ONE all-gather.  With the
+  collectives, received data is in local memory before any kernel reads it.
+* `PeerBlocks` + `exchange="peer_memory"`: the exact mode without a collective
+  library.  Every rank's shard, results and flags live in one block that the
+  other ranks opened through CUDA IPC; two small kernels of this library pull a
+  rank's rows from the peers' shards and push its indices to every peer, with
+  plain loads and stores over NVLink and bounded flag waits.
 """
 
 from .ops import _declare, _stream_ptr
@@ -68,6 +72,84 @@ def assemble_rows(received, n_rows, cols, out=None):
     return out
 
 
+class _DeviceArray:
+    """A raw device pointer as something torch.as_tensor accepts."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False),
+                                         "version": 3, "strides": None}
+
+
+class PeerBlocks:
+    """One block of device memory per rank that every other rank of the node can address: 256 bytes of flags (the
+    library's), `max_rows` int64 results, and this rank's fp16 logits shard [max_rows, shard_cols].
+
+    Collective: every rank of `group` constructs it at the same point (the IPC handles travel through
+    all_gather_object).  `local_blocks` replaces the exchange in tests that play several ranks in one process: a
+    list that every played rank appends its own block to before any of them samples."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, lib, handle, max_rows, shard_cols, world_size, rank, device, group=None, local_blocks=None):
+        import ctypes
+
+        import torch
+
+        _declare(lib)
+        self.lib, self.handle, self.world, self.rank = lib, handle, int(world_size), int(rank)
+        self.max_rows, self.shard_cols = int(max_rows), int(shard_cols)
+        self.results_off = self.FLAG_BYTES
+        self.logits_off = self.results_off + (self.max_rows * 8 + 255) // 256 * 256
+        self.nbytes = self.logits_off + self.max_rows * self.shard_cols * 2
+        ptr, ipc = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(device):
+            check_error(lib.infiniopExtPeerAlloc(handle, self.nbytes, ctypes.byref(ptr), ipc))
+        self.ptr, self._opened = int(ptr.value), []
+        if local_blocks is not None:
+            local_blocks.append(self)
+            self._local_blocks, self.bases = local_blocks, None
+        else:
+            self._local_blocks = None
+            handles = [None] * self.world
+            if self.world > 1:
+                import torch.distributed as dist
+
+                dist.all_gather_object(handles, bytes(ipc), group=group)
+            self.bases = []
+            for r in range(self.world):
+                if r == self.rank:
+                    self.bases.append(self.ptr)
+                    continue
+                other = ctypes.c_void_p()
+                raw = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
+                with torch.cuda.device(device):
+                    check_error(lib.infiniopExtPeerOpen(handle, raw, ctypes.byref(other)))
+                self._opened.append(int(other.value))
+                self.bases.append(int(other.value))
+        self.device = device
+        self.results = torch.as_tensor(_DeviceArray(self.ptr + self.results_off, (self.max_rows,), "<i8"), device=device)
+        self.logits = torch.as_tensor(_DeviceArray(self.ptr + self.logits_off, (self.max_rows, self.shard_cols), "<f2"),
+                                      device=device)
+        self.flags = torch.as_tensor(_DeviceArray(self.ptr, (self.FLAG_BYTES // 4,), "<i4"), device=device)
+
+    def base_of(self, r):
+        if self._local_blocks is not None:
+            return self._local_blocks[r].ptr
+        return self.bases[r]
+
+    def destroy(self):
+        import torch
+
+        if self.ptr is None:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for other in self._opened:
+                self.lib.infiniopExtPeerClose(self.handle, other)
+            self.lib.infiniopExtPeerFree(self.handle, self.ptr)
+        self.ptr, self._opened, self.results, self.logits, self.flags = None, [], None, None, None
+
+
 class VocabShardedSampler:
     """Sampling branch of random sample (topp > 0, 2 <= topk <= 64) over vocabulary shards; every rank gets
     the same results.
@@ -88,9 +170,15 @@ class VocabShardedSampler:
     torch.distributed calls on `group` (tests play several ranks in one process with them)."""
 
     def __init__(self, lib, handle, sample_op, voc_total, shard_offset, world_size, group=None, all_gather=None,
-                 mode="exact", rank=None, all_to_all=None, exchange="auto"):
+                 mode="exact", rank=None, all_to_all=None, exchange="auto", peer_blocks=None):
         _declare(lib)
-        assert mode in ("exact", "fast") and exchange in ("auto", "all_to_all", "all_gather")
+        assert mode in ("exact", "fast") and exchange in ("auto", "all_to_all", "all_gather", "peer_memory")
+        # "peer_memory": no collective at all.  `peer_blocks` (PeerBlocks, built collectively beforehand) holds every
+        # rank's shard where the others can read it; the caller writes its logits into peer_blocks.logits[:rows]
+        # (sample() copies them there when it is handed another tensor) and two kernels of the library move rows
+        # in and indices out.  All ranks then read their results from peer_blocks.results as well.
+        assert (exchange == "peer_memory") == (peer_blocks is not None)
+        self.peer = peer_blocks
         # How the exact mode moves the rows: "all_to_all" sends every rank only the rows it will own;
         # "all_gather" hands every rank all shards (world_size times the bytes, but one collective whose latency
         # does not grow with the number of peers the way the send / receive pairs of an all-to-all do) and lets it
@@ -145,6 +233,8 @@ class VocabShardedSampler:
             (r0, r1), _, recv, _ = exchange_plan(rows, self.voc_total, self.world, self.rank)
             most = max(e - b for b, e in (row_range(rows, self.world, r) for r in range(self.world)))
             n_recv = rows * self.voc_total if self.exchange == "all_gather" else sum(recv)
+            if self.exchange == "peer_memory":
+                n_recv = 1
             received = torch.empty(max(1, n_recv), dtype=torch.float16, device=device)
             full = torch.empty((max(1, r1 - r0), self.voc_total), dtype=torch.float16, device=device)
             picked = torch.zeros((self.world, most), dtype=torch.int64, device=device)
@@ -152,7 +242,7 @@ class VocabShardedSampler:
             op._ensure_batch_ws(max(1, r1 - r0), device)
             op_copy = full_view = received_view = None
             mine = r1 - r0
-            if mine and self.voc_total % self.world == 0 and received.is_cuda:
+            if mine and self.voc_total % self.world == 0 and received.is_cuda and self.exchange != "peer_memory":
                 from .ops import RearrangeOp
 
                 vl = self.voc_total // self.world
@@ -200,6 +290,10 @@ class VocabShardedSampler:
         (r0, r1), send, recv, cols = exchange_plan(rows, self.voc_total, self.world, self.rank)
         mine = r1 - r0
         received, full, picked, op, op_copy, full_view, received_view = self._exact_buffers(rows, local_logits.device)
+        if self.exchange == "peer_memory":
+            self._sample_peer(results, local_logits, random_vals, topp, topk, temperature, sp, mark, rows, r0, r1,
+                              cols, full, picked, op)
+            return
         src = local_logits if local_logits.is_contiguous() else local_logits.contiguous()
         if self._a2a is not None:
             self._a2a(received, src.view(-1), recv, send)
@@ -240,6 +334,45 @@ class VocabShardedSampler:
             for r in range(self.world):
                 b, e = row_range(rows, self.world, r)
                 results.view(torch.int64)[b:e].copy_(picked[r, :e - b])
+        mark("finish")
+
+    def _peer_tables(self, rows, cols):
+        import ctypes
+
+        key = ("tables", rows)
+        if key not in self._bufs:
+            pb, w = self.peer, self.world
+            assert rows <= pb.max_rows and pb.shard_cols == cols[self.rank][1] - cols[self.rank][0]
+            widths = [e - b for b, e in cols]
+            shards = (ctypes.c_void_p * w)(*[pb.base_of(r) + pb.logits_off for r in range(w)])
+            strides = (ctypes.c_int64 * w)(*widths)  # every rank's shard is [max_rows, its columns], dense
+            col0 = (ctypes.c_uint64 * w)(*[b for b, _ in cols])
+            ncols = (ctypes.c_uint64 * w)(*widths)
+            flags = (ctypes.c_void_p * w)(*[pb.base_of(r) for r in range(w)])
+            res = (ctypes.c_void_p * w)(*[pb.base_of(r) + pb.results_off for r in range(w)])
+            self._bufs[key] = (shards, strides, col0, ncols, flags, res)
+        return self._bufs[key]
+
+    def _sample_peer(self, results, local_logits, random_vals, topp, topk, temperature, sp, mark, rows, r0, r1, cols,
+                     full, picked, op):
+        import torch
+
+        pb, mine = self.peer, r1 - r0
+        shards, strides, col0, ncols, flags, res = self._peer_tables(rows, cols)
+        if local_logits.data_ptr() != pb.logits.data_ptr():
+            pb.logits[:rows].copy_(local_logits)
+        check_error(self.lib.infiniopExtPeerGatherRows(
+            self.handle, full.data_ptr(), full.stride(0), shards, strides, col0, ncols, flags, self.world, self.rank,
+            r0, mine, sp))
+        mark("exchange")
+        if mine:
+            op.batch(picked[self.rank, :mine], full[:mine], random_vals[r0:r1], topp, topk, temperature, stream=sp)
+        mark("sample")
+        check_error(self.lib.infiniopExtPeerPublishResults(
+            self.handle, res, picked[self.rank].data_ptr(), flags, self.world, self.rank, r0, mine, sp))
+        mark("publish")
+        if results.data_ptr() != pb.results.data_ptr():
+            results.view(torch.int64).copy_(pb.results[:rows])
         mark("finish")
 
     def _sample_fast(self, results, local_logits, random_vals, topp, topk, temperature, sp, check, mark):

@@ -6,6 +6,8 @@ sampled indices identical for the same uniform draw.  Shapes cover the
 reference's own test cases (reference operatorspy/tests/*.py) and ragged /
 unaligned / strided / in-place variants.
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -1186,6 +1188,68 @@ def test_vocab_sharded_sampling_is_index_exact(oracle, cuda_lib, ranks, voc, row
     for r in range(ranks):  # what each rank contributed: exactly its own rows
         r0, r1 = row_range(rows, ranks, r)
         assert sent[r][:r1 - r0].cpu().tolist() == want[r0:r1]
+
+
+@pytest.mark.parametrize("ranks", [1, 2, 4, 8])
+@pytest.mark.parametrize("voc,rows,topp,topk,temp,dist", SHARDED_CASES)
+def test_vocab_sharded_sampling_over_peer_memory_blocks(oracle, cuda_lib, ranks, voc, rows, topp, topk, temp, dist):
+    """The exact mode without collectives: every rank's shard sits in a block the others address, one kernel pulls a
+    rank's rows out of all blocks, one pushes its indices into all of them.  Here the ranks are played one after the
+    other on one GPU, their blocks all local; kernels that wait for each other must not run as separate launches
+    on one GPU, so the flags that the absent peers would raise are set beforehand and no launch ever waits.  What is
+    checked is the addressing (rows, column ranges, unequal shards), the call counter over two rounds, and that
+    every block ends up with every row's index = the oracle's.  The flag protocol between real ranks runs in
+    tests/peer_ranks.py on two GPUs."""
+    from operators_b200.sharding import PeerBlocks, VocabShardedSampler, vocab_range
+
+    lib, handle = cuda_lib
+    logits, u, want = _sharded_inputs(oracle, voc, rows, topp, topk, temp, dist)
+    ld, ud = logits.to(DEV), u.to(DEV)
+    timeouts_before = ops.device_timeouts(lib, handle)
+    blocks, samplers, keep = [], [], []
+    for r in range(ranks):
+        b, e = vocab_range(voc, ranks, r)
+        pb = PeerBlocks(lib, handle, rows, e - b, ranks, r, DEV, local_blocks=blocks)
+        op = ops.RandomSampleOp(lib, handle, pb.results[:1], pb.logits[0])
+        keep.append(op)
+        samplers.append(VocabShardedSampler(lib, handle, op, voc, b, ranks, rank=r, exchange="peer_memory", peer_blocks=pb))
+    try:
+        for round_no in range(2):
+            for r, pb in enumerate(blocks):
+                b, e = vocab_range(voc, ranks, r)
+                pb.logits[:rows].copy_(ld[:, b:e])
+                pb.results.fill_(-1)
+                pb.flags[:32].fill_(0x3FFFFFFF)  # as if every peer had raised its flags for this and any later call
+            for r, s in enumerate(samplers):
+                s.sample(blocks[r].results, blocks[r].logits[:rows], ud, topp, topk, temp)
+            torch.cuda.synchronize()
+            for pb in blocks:
+                assert pb.results[:rows].cpu().tolist() == want
+                assert int(pb.flags[32].item()) == round_no + 1  # the call counter the kernels keep in the block
+        assert ops.device_timeouts(lib, handle) == timeouts_before
+    finally:
+        torch.cuda.synchronize()
+        for s in samplers:
+            s.destroy()
+        for op in keep:
+            op.destroy()
+        for pb in blocks:
+            pb.destroy()
+
+
+def test_vocab_sharded_sampling_over_peer_memory_two_gpus():
+    """Two real ranks on two GPUs: CUDA IPC blocks, the flag protocol, three rounds, indices against the unsharded
+    sampler; tests/peer_ranks.py is the program both ranks run."""
+    import subprocess
+    import sys
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = os.path.join(os.path.dirname(os.path.abspath(__file__)), "peer_ranks.py")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29533", script],
+                       capture_output=True, text=True, timeout=300, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0 and "peer ranks ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
 @pytest.mark.parametrize("ranks", [1, 2, 8])
