@@ -838,7 +838,8 @@ def run_b200(args):
             res["ms_graph"] = None
             gr = None
             res["exchange"] = sampler.exchange if mode != "fast" else None
-            if not args.sharded_graph:
+            # (the peer-memory mode holds no NCCL kernel, so its graph is always timed)
+            if not (args.sharded_graph or exch == "peer_memory"):
                 if mode == "exact":
                     exact_indices = out.cpu().tolist()
                     res["indices"] = exact_indices
