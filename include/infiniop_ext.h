@@ -182,4 +182,21 @@ INFINIOP_API infiniopStatus_t infiniopExtPeerPublishResults(infiniopHandle_t han
                                                             const void *picked, void *const *flags, uint32_t world,
                                                             uint32_t rank, uint64_t row0, uint64_t nrows, void *stream);
 
+/*
+ * The same exchange folded into the sampling kernel: ONE launch waits for the
+ * peers' shards, samples rows [row0, row0 + nrows) out of them with peer
+ * loads, stores every index into every rank's result array and closes with
+ * the "done" round.  `desc` describes whole rows (voc = world * shard_cols).
+ * Conditions: topp > 0, 2 <= topk <= 64, voc <= 262144, equal shards of a
+ * multiple of 8 columns, nrows >= 1; otherwise STATUS_BAD_PARAM, and the three
+ * calls above (GatherRows, infiniopRandomSampleBatch, PublishResults) apply.
+ * A rank without rows takes part with GatherRows and PublishResults (nrows 0).
+ */
+INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchPeer(infiniopRandomSampleDescriptor_t desc, void *const *results,
+                                                            void *const *shards, const int64_t *shard_row_strides,
+                                                            uint64_t shard_cols, void *const *flags, uint32_t world,
+                                                            uint32_t rank, uint64_t row0, uint64_t nrows,
+                                                            void const *random_vals, float topp, int topk,
+                                                            float temperature, void *stream);
+
 #endif /* INFINIOP_B200_EXT_H */

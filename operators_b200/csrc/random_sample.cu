@@ -779,6 +779,53 @@ INFINIOP_API infiniopStatus_t infiniopRandomSampleBatch(infiniopRandomSampleDesc
                                           random_vals, topp, topk, temperature, nullptr, stream);
 }
 
+// ---- batched sampling of vocabulary-sharded rows over peer memory, one launch --------
+//
+// The exchange of peer_exchange.cu folded into the sampling kernel: its CTAs wait for the peers' "shard is final"
+// words, read their row out of the `world` shards with peer loads, and the thread that picks a row's index stores it
+// into every rank's result array; the row that finishes last runs the "done" round.  Same flag words and call
+// counter as infiniopExtPeerGatherRows / infiniopExtPeerPublishResults, so a rank without rows of its own takes part
+// with those two (nrows = 0).  Conditions: the sampling branch (topp > 0, 2 <= topk <= 64), rows of at most 262144
+// logits, equal shards of a multiple of 8 columns; otherwise STATUS_BAD_PARAM and the three-launch form applies.
+INFINIOP_API infiniopStatus_t infiniopRandomSampleBatchPeer(infiniopRandomSampleDescriptor_t desc, void *const *results,
+                                                            void *const *shards, const int64_t *shard_row_strides,
+                                                            uint64_t shard_cols, void *const *flags, uint32_t world,
+                                                            uint32_t rank, uint64_t row0, uint64_t nrows,
+                                                            void const *random_vals, float topp, int topk,
+                                                            float temperature, void *stream) {
+    if (desc == nullptr || desc->device != DevNvGpu) return STATUS_BAD_DEVICE;
+    auto *d = reinterpret_cast<RandomSampleDesc *>(desc);
+    if (results == nullptr || shards == nullptr || shard_row_strides == nullptr || flags == nullptr || random_vals == nullptr) {
+        return STATUS_BAD_PARAM;
+    }
+    if (world == 0 || world > kPeerMaxRanks || rank >= world || nrows == 0 || nrows > 0x7FFFFFull) return STATUS_BAD_PARAM;
+    const int k = topk > d->voc ? d->voc : topk;
+    if (!(topp > 0.f) || topk < 2 || k > kSlots || !(temperature > 0.f)) return STATUS_BAD_PARAM;
+    if (!random_sample_pair_supported(d->voc) || kernel_choice(kFamilyRandomSample) == 1) return STATUS_BAD_PARAM;
+    if (shard_cols == 0 || shard_cols % 8 != 0 || shard_cols * world != (uint64_t) d->voc) return STATUS_BAD_PARAM;
+    RandomSampleArgs a{};
+    a.random_vals = reinterpret_cast<const float *>(random_vals);
+    a.topp = topp, a.topk = topk, a.temperature = temperature, a.voc = d->voc;
+    a.peer.world = world, a.peer.rank = rank, a.peer.shard_vecs = (uint32_t) (shard_cols / 8);
+    a.peer.rows = (uint32_t) nrows, a.peer.row0 = row0;
+    for (uint32_t r = 0; r < world; ++r) {
+        if (results[r] == nullptr || shards[r] == nullptr || flags[r] == nullptr || !aligned16(shards[r]) ||
+            shard_row_strides[r] % 8 != 0) {
+            return STATUS_BAD_PARAM;
+        }
+        a.peer.shard[r] = reinterpret_cast<const uint16_t *>(shards[r]);
+        a.peer.shard_stride[r] = shard_row_strides[r];
+        a.peer.flags[r] = reinterpret_cast<uint32_t *>(flags[r]);
+        a.peer.results[r] = reinterpret_cast<unsigned long long *>(results[r]);
+    }
+    a.logits = a.peer.shard[rank];// unused by the sharded load; kept non-null
+    a.logits_stride = shard_row_strides[rank];
+    a.result = reinterpret_cast<uint64_t *>(results[rank]) + row0;
+    a.result_stride = 1;
+    DeviceGuard guard(d->device_id);
+    return random_sample_pair_launch(a, (int) nrows, reinterpret_cast<cudaStream_t>(stream));
+}
+
 // ---- batched sampling without a caller-provided workspace -----------------------
 //
 // Some hosts of this library may not allocate device memory at the point where

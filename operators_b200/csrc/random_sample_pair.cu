@@ -412,6 +412,35 @@ __device__ __forceinline__ void exact_at_level(float term, int e0, int level, ui
     tie = sh > 0 && rem == half;
 }
 
+// ---- peer memory (vocabulary-sharded rows) ----------------------------------------------
+constexpr long long kPeerWaitBudget = 2000ll * 1000 * 1000;// clock64 ticks, about a second
+__device__ unsigned long long g_pair_peer_timeouts = 0;
+
+__device__ __forceinline__ void peer_st_release(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void peer_st_u64(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint4 peer_ld_v4(const void *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+// Until *flag has reached `call` (the counters wrap; the difference counts).  Bounded: a wait that runs out is counted.
+__device__ __forceinline__ void peer_wait(const uint32_t *flag, uint32_t call) {
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int32_t) (v - call) >= 0) return;
+        if (clock64() - t0 > kPeerWaitBudget) {
+            atomicAdd(&g_pair_peer_timeouts, 1ull);
+            return;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomSampleArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint16_t *raw = reinterpret_cast<uint16_t *>(smem_raw);// this CTA's part of the row, fp16 bit patterns
@@ -453,8 +482,25 @@ __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomS
         return cluster.map_shared_rank(raw, g >> 8) + (g & 255u) * kBlk;
     };
 
+    // ---- sharded rows: tell the peers that this rank's shard is final, wait for theirs ----
+    const PeerRowSource &pr = a.peer;
+    uint32_t peer_call = 0;
+    if (pr.world) {
+        uint32_t *mine = pr.flags[pr.rank];
+        peer_call = mine[kPeerCalls] + 1;// raised by the CTA that finishes last, after every CTA has read it
+        if (blockIdx.x == 0 && tid < (int) pr.world) peer_st_release(&pr.flags[tid][kPeerReady + pr.rank], peer_call);
+        if (tid < (int) pr.world && tid != (int) pr.rank) peer_wait(&mine[kPeerReady + tid], peer_call);
+        __syncthreads();// a wait that ran out is counted; the row is then sampled from what the shard holds
+    }
+    // vector v (8 elements) of this CTA's part of the row
+    auto vec_src = [&](uint32_t base) -> const uint16_t * {
+        if (!pr.world) return logits + base;
+        const uint32_t gv = (my_base + base) >> 3, p = gv / pr.shard_vecs;
+        return pr.shard[p] + (int64_t) (pr.row0 + row) * pr.shard_stride[p] + (size_t) (gv - p * pr.shard_vecs) * 8;
+    };
+
     // ---- P1: this CTA's part of the row -> shared memory; per-thread maxima --------------
-    const bool in_aligned = (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
+    const bool in_aligned = pr.world != 0 || (reinterpret_cast<uintptr_t>(logits) & 15u) == 0;
     __half2 tmax2 = h2_of(0xFC00FC00u), m0_2 = tmax2, mA_2 = tmax2, mB_2 = tmax2;// running maximum; after 1, 2 and 4 vectors
     auto max4 = [](const uint4 q) { return __hmax2(__hmax2(h2_of(q.x), h2_of(q.y)), __hmax2(h2_of(q.z), h2_of(q.w))); };
     constexpr int kInFlight = 8;
@@ -464,7 +510,8 @@ __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomS
         for (int u = 0; u < kInFlight; ++u) {
             const uint32_t base = base0 + u * kThreads * 8;
             ld[u] = make_uint4(0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u);
-            if (in_aligned && base + 8 <= my_n) ld[u] = ld_stream(logits + base);
+            // peer memory: volatile, so that no line of an earlier call's logits comes out of L1
+            if (in_aligned && base + 8 <= my_n) ld[u] = pr.world ? peer_ld_v4(vec_src(base)) : ld_stream(logits + base);
         }
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
@@ -1345,7 +1392,25 @@ __global__ void __launch_bounds__(kThreads, 1) random_sample_pair_kernel(RandomS
                 dbg[129 + 13] = (float) unsure;
                 dbg[129 + 12] = (float) int_replays;
             }
-            pick_from_topk(ax.top_term, ax.top_idx, k, a.topp, random_val, a.result + (int64_t) row * a.result_stride);
+            uint64_t *slot = a.result + (int64_t) row * a.result_stride;
+            pick_from_topk(ax.top_term, ax.top_idx, k, a.topp, random_val, slot);
+            if (pr.world) {
+                // the index to every rank's results; the row that reports last closes the call for this rank: "done"
+                // to every peer, wait for theirs (then all rows are local and nobody reads this rank's shard any more)
+                const unsigned long long picked = *slot;
+                for (uint32_t p = 0; p < pr.world; ++p) {
+                    if (p != pr.rank) peer_st_u64(pr.results[p] + pr.row0 + row, picked);
+                }
+                __threadfence_system();
+                uint32_t *mine = pr.flags[pr.rank];
+                if (atomicAdd(&mine[kPeerFinished], 1u) == pr.rows - 1) {
+                    mine[kPeerFinished] = 0;
+                    __threadfence_system();
+                    for (uint32_t p = 0; p < pr.world; ++p) peer_st_release(&pr.flags[p][kPeerDone + pr.rank], peer_call);
+                    for (uint32_t p = 0; p < pr.world; ++p) peer_wait(&mine[kPeerDone + p], peer_call);
+                    mine[kPeerCalls] = peer_call;
+                }
+            }
         }
     }
 }
@@ -1357,6 +1422,15 @@ namespace b200 {
 // Sampling branch for rows of at most 262144 logits and topk <= 64: one CTA per row up to 65536 logits, a
 // cluster of two up to 131072, of four beyond.
 bool random_sample_pair_supported(int voc) { return voc >= 1 && voc <= kMaxRanks * kHalfElems; }
+
+unsigned long long random_sample_pair_timeouts_read() {
+    unsigned long long v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_pair_peer_timeouts, sizeof(v)) != cudaSuccess) {
+        cudaGetLastError();
+        return ~0ull;
+    }
+    return v;
+}
 
 infiniopStatus_t random_sample_pair_launch(const RandomSampleArgs &a, int rows, cudaStream_t st) {
     static thread_local int configured_dev = -1;

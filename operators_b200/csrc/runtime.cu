@@ -35,15 +35,17 @@ unsigned long long rms_norm_ring_timeouts_read();
 unsigned long long causal_softmax_ring_timeouts_read();
 unsigned long long attn_fused_timeouts_read();
 unsigned long long peer_exchange_timeouts_read();
+unsigned long long random_sample_pair_timeouts_read();
 }// namespace b200
 
 INFINIOP_API infiniopStatus_t infiniopExtDeviceTimeouts(infiniopHandle_t handle, uint64_t *count) {
     if (handle == nullptr || handle->device != DevNvGpu) return STATUS_BAD_DEVICE;
     if (count == nullptr) return STATUS_BAD_PARAM;
     DeviceGuard guard(reinterpret_cast<Handle *>(handle)->device_id);
-    const unsigned long long parts[6] = {rope_pipeline_timeouts_read(), tc_gemm_timeouts_read(),
+    const unsigned long long parts[7] = {rope_pipeline_timeouts_read(), tc_gemm_timeouts_read(),
                                          rms_norm_ring_timeouts_read(), causal_softmax_ring_timeouts_read(),
-                                         attn_fused_timeouts_read(), peer_exchange_timeouts_read()};
+                                         attn_fused_timeouts_read(), peer_exchange_timeouts_read(),
+                                         random_sample_pair_timeouts_read()};
     unsigned long long sum = 0;
     for (unsigned long long v : parts) {
         if (v == ~0ull) return STATUS_EXECUTION_FAILED;

@@ -80,6 +80,9 @@ def _declare(lib):
                                             c_float, c_void_p, c_void_p],
         "infiniopRandomSampleBatchTrace": [D, c_void_p, c_uint64, c_void_p, c_void_p, c_int64, c_uint64, c_void_p,
                                            c_float, c_int, c_float, c_void_p, c_void_p],
+        "infiniopRandomSampleBatchPeer": [D, POINTER(c_void_p), POINTER(c_void_p), POINTER(c_int64), c_uint64,
+                                          POINTER(c_void_p), ctypes.c_uint32, ctypes.c_uint32, c_uint64, c_uint64, c_void_p,
+                                          c_float, c_int, c_float, c_void_p],
         "infiniopExtPeerAlloc": [H, c_uint64, POINTER(c_void_p), c_void_p],
         "infiniopExtPeerOpen": [H, c_void_p, POINTER(c_void_p)],
         "infiniopExtPeerClose": [H, c_void_p],

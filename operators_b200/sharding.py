@@ -170,7 +170,7 @@ class VocabShardedSampler:
     torch.distributed calls on `group` (tests play several ranks in one process with them)."""
 
     def __init__(self, lib, handle, sample_op, voc_total, shard_offset, world_size, group=None, all_gather=None,
-                 mode="exact", rank=None, all_to_all=None, exchange="auto", peer_blocks=None):
+                 mode="exact", rank=None, all_to_all=None, exchange="auto", peer_blocks=None, one_launch=True):
         _declare(lib)
         assert mode in ("exact", "fast") and exchange in ("auto", "all_to_all", "all_gather", "peer_memory")
         # "peer_memory": no collective at all.  `peer_blocks` (PeerBlocks, built collectively beforehand) holds every
@@ -179,6 +179,9 @@ class VocabShardedSampler:
         # in and indices out.  All ranks then read their results from peer_blocks.results as well.
         assert (exchange == "peer_memory") == (peer_blocks is not None)
         self.peer = peer_blocks
+        # peer memory: fold the exchange into the sampling kernel where its conditions hold (equal shards of a multiple
+        # of 8 columns, rows of at most 262144 logits); False keeps the three launches (gather, sample, publish)
+        self.one_launch = one_launch
         # How the exact mode moves the rows: "all_to_all" sends every rank only the rows it will own;
         # "all_gather" hands every rank all shards (world_size times the bytes, but one collective whose latency
         # does not grow with the number of peers the way the send / receive pairs of an all-to-all do) and lets it
@@ -361,6 +364,19 @@ class VocabShardedSampler:
         shards, strides, col0, ncols, flags, res = self._peer_tables(rows, cols)
         if local_logits.data_ptr() != pb.logits.data_ptr():
             pb.logits[:rows].copy_(local_logits)
+        vl = pb.shard_cols
+        one_launch = (self.one_launch and mine > 0 and vl * self.world == self.voc_total and vl % 8 == 0
+                      and self.voc_total <= 262144 and topp > 0 and 2 <= topk <= 64)
+        if one_launch:
+            # the exchange inside the sampling kernel: peers' shards read by its own loads, indices stored to every rank
+            check_error(self.lib.infiniopRandomSampleBatchPeer(
+                op.desc, res, shards, strides, vl, flags, self.world, self.rank, r0, mine,
+                random_vals[r0:r1].data_ptr(), topp, topk, temperature, sp))
+            mark("sample")
+            if results.data_ptr() != pb.results.data_ptr():
+                results.view(torch.int64).copy_(pb.results[:rows])
+            mark("finish")
+            return
         check_error(self.lib.infiniopExtPeerGatherRows(
             self.handle, full.data_ptr(), full.stride(0), shards, strides, col0, ncols, flags, self.world, self.rank,
             r0, mine, sp))

@@ -25,7 +25,8 @@ def main():
     handle = create_handle(lib, DeviceEnum.DEVICE_CUDA, local)
     before = ops.device_timeouts(lib, handle)
     bad = 0
-    for voc, rows in ((128256, 64), (32000, 13), (4099, 5)):  # equal shards, uneven rows, uneven shards and fewer rows than ranks + 3
+    # equal shards (the exchange inside the sampling kernel, then as launches of its own), uneven rows, uneven shards
+    for voc, rows, one_launch in ((128256, 64, True), (128256, 64, False), (32000, 13, True), (4099, 5, True), (4096, 1, True)):
         g = torch.Generator().manual_seed(100 + voc)
         b, e = vocab_range(voc, world, rank)
         pb = PeerBlocks(lib, handle, rows, e - b, world, rank, dev)
@@ -33,7 +34,8 @@ def main():
         want = torch.zeros(rows, dtype=torch.int64, device=dev)
         op = ops.RandomSampleOp(lib, handle, pb.results[:1], pb.logits[0])
         ref = ops.RandomSampleOp(lib, handle, want[:1], whole[0])
-        s = VocabShardedSampler(lib, handle, op, voc, b, world, rank=rank, exchange="peer_memory", peer_blocks=pb)
+        s = VocabShardedSampler(lib, handle, op, voc, b, world, rank=rank, exchange="peer_memory", peer_blocks=pb,
+                                one_launch=one_launch)
         for _ in range(3):
             logits = (torch.randn((rows, voc), generator=g) * 3).half()  # the same on every rank
             u = torch.rand(rows, generator=g)

@@ -1190,16 +1190,18 @@ def test_vocab_sharded_sampling_is_index_exact(oracle, cuda_lib, ranks, voc, row
         assert sent[r][:r1 - r0].cpu().tolist() == want[r0:r1]
 
 
+@pytest.mark.parametrize("one_launch", [True, False], ids=["one_launch", "three_launches"])
 @pytest.mark.parametrize("ranks", [1, 2, 4, 8])
 @pytest.mark.parametrize("voc,rows,topp,topk,temp,dist", SHARDED_CASES)
-def test_vocab_sharded_sampling_over_peer_memory_blocks(oracle, cuda_lib, ranks, voc, rows, topp, topk, temp, dist):
+def test_vocab_sharded_sampling_over_peer_memory_blocks(oracle, cuda_lib, ranks, voc, rows, topp, topk, temp, dist, one_launch):
     """The exact mode without collectives: every rank's shard sits in a block the others address, one kernel pulls a
     rank's rows out of all blocks, one pushes its indices into all of them.  Here the ranks are played one after the
     other on one GPU, their blocks all local; kernels that wait for each other must not run as separate launches
     on one GPU, so the flags that the absent peers would raise are set beforehand and no launch ever waits.  What is
     checked is the addressing (rows, column ranges, unequal shards), the call counter over two rounds, and that
-    every block ends up with every row's index = the oracle's.  The flag protocol between real ranks runs in
-    tests/peer_ranks.py on two GPUs."""
+    every block ends up with every row's index = the oracle's, with the exchange as two launches around the sampling
+    kernel and folded into it (where shards are equal and whole vectors; other shapes take the three launches
+    either way).  The flag protocol between real ranks runs in tests/peer_ranks.py on two GPUs."""
     from operators_b200.sharding import PeerBlocks, VocabShardedSampler, vocab_range
 
     lib, handle = cuda_lib
@@ -1212,7 +1214,8 @@ def test_vocab_sharded_sampling_over_peer_memory_blocks(oracle, cuda_lib, ranks,
         pb = PeerBlocks(lib, handle, rows, e - b, ranks, r, DEV, local_blocks=blocks)
         op = ops.RandomSampleOp(lib, handle, pb.results[:1], pb.logits[0])
         keep.append(op)
-        samplers.append(VocabShardedSampler(lib, handle, op, voc, b, ranks, rank=r, exchange="peer_memory", peer_blocks=pb))
+        samplers.append(VocabShardedSampler(lib, handle, op, voc, b, ranks, rank=r, exchange="peer_memory", peer_blocks=pb,
+                                            one_launch=one_launch))
     try:
         for round_no in range(2):
             for r, pb in enumerate(blocks):
