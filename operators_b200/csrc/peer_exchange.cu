@@ -19,6 +19,7 @@
 // that infiniopExtDeviceTimeouts reports, the kernel finishes with whatever has arrived, and the call has returned
 // STATUS_SUCCESS long before: a host that needs certainty reads the counter.
 #include "common.cuh"
+#include "random_sample.cuh"
 
 #include <cstring>
 
@@ -26,9 +27,10 @@ using namespace b200;
 
 namespace {
 
-constexpr uint32_t kMaxRanks = 16;
-constexpr uint32_t kFlagWords = 64;      // per block: ready[16], done[16], call counter, padding = 256 bytes
-constexpr uint32_t kReady = 0, kDone = 16, kCalls = 32;
+// A block starts with 64 flag words (256 bytes): ready[16], done[16], the call counter, the counter of finished rows of
+// the one-launch form (random_sample_pair.cu), padding.  The indices are shared with that kernel (random_sample.cuh).
+constexpr uint32_t kMaxRanks = kPeerMaxRanks;
+constexpr uint32_t kReady = kPeerReady, kDone = kPeerDone, kCalls = kPeerCalls;
 constexpr long long kPeerWaitBudget = 2000ll * 1000 * 1000;// clock64 ticks, about a second
 constexpr int kCopyThreads = 256;
 

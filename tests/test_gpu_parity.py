@@ -1240,6 +1240,55 @@ def test_vocab_sharded_sampling_over_peer_memory_blocks(oracle, cuda_lib, ranks,
             pb.destroy()
 
 
+@pytest.mark.parametrize("one_launch", [True, False], ids=["one_launch", "three_launches"])
+def test_peer_memory_wait_runs_out_when_a_rank_never_shows_up(cuda_lib, one_launch):
+    """Failure detection without a fault: of two ranks only rank 0 samples, so the words rank 1 would raise never
+    arrive.  Every wait gives up after its clock budget (about a second), the call has returned STATUS_SUCCESS
+    long before, the context stays usable, and infiniopExtDeviceTimeouts reports the waits that ran out.  (The
+    one-launch form then samples from what the shards hold; the gather kernel of the three-launch form leaves the
+    columns of a peer it gave up on unwritten.)"""
+    import time
+
+    from operators_b200.sharding import PeerBlocks, VocabShardedSampler, vocab_range
+
+    lib, handle = cuda_lib
+    voc, rows, ranks = 4096, 2, 2
+    g = torch.Generator().manual_seed(5)
+    ld = (torch.randn((rows, voc), generator=g) * 3).half().to(DEV)
+    ud = torch.rand(rows, generator=g).to(DEV)
+    before = ops.device_timeouts(lib, handle)
+    blocks = []
+    for r in range(ranks):
+        b, e = vocab_range(voc, ranks, r)
+        pb = PeerBlocks(lib, handle, rows, e - b, ranks, r, DEV, local_blocks=blocks)  # appends itself to `blocks`
+        pb.logits[:rows].copy_(ld[:, b:e])
+    op = ops.RandomSampleOp(lib, handle, blocks[0].results[:1], blocks[0].logits[0])
+    s = VocabShardedSampler(lib, handle, op, voc, 0, ranks, rank=0, exchange="peer_memory", peer_blocks=blocks[0],
+                            one_launch=one_launch)
+    whole = torch.zeros(rows, dtype=torch.int64, device=DEV)
+    ref = ops.RandomSampleOp(lib, handle, whole[:1], ld[0])
+    try:
+        ref.batch(whole, ld, ud, 0.9, 50, 0.8)
+        t0 = time.time()
+        s.sample(blocks[0].results, blocks[0].logits[:rows], ud, 0.9, 50, 0.8)  # returns at once
+        issued = time.time() - t0
+        torch.cuda.synchronize()
+        waited = time.time() - t0
+        assert issued < 0.5 and 0.5 < waited < 20.0
+        assert ops.device_timeouts(lib, handle) > before
+        if one_launch:  # rank 0 owns row 0; the one-launch form reads the shards after its wait, and the data was there
+            assert int(blocks[0].results[0].item()) == int(whole[0].item())
+        y = torch.ones(8, device=DEV) * 2  # the context still works
+        assert float(y.sum().item()) == 16.0
+    finally:
+        torch.cuda.synchronize()
+        s.destroy()
+        op.destroy()
+        ref.destroy()
+        for pb in blocks:
+            pb.destroy()
+
+
 def test_vocab_sharded_sampling_over_peer_memory_two_gpus():
     """Two real ranks on two GPUs: CUDA IPC blocks, the flag protocol, three rounds, indices against the unsharded
     sampler; tests/peer_ranks.py is the program both ranks run."""
