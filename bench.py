@@ -989,17 +989,20 @@ def run_b200(args):
                 rs[mode]["graph_error"] = sharded[mode]["graph_error"]
             if "same_indices_as_exact" in sharded[mode]:
                 rs[mode]["same_indices_as_exact"] = sharded[mode]["same_indices_as_exact"]
-        rs["exact"]["what"] = ("64 rows, vocabulary 128256 split over %d GPUs; default mode, index-exact: one NCCL "
-                               "collective (all-to-all: %d bytes received per rank; or all-gather of all shards: %d "
-                               "bytes) gives every rank %d whole rows, the exact kernel samples them, one all-gather "
-                               "returns the indices; exact_all_to_all / exact_all_gather force one exchange each" %
-                               (world, RS_B // world * RS_V * 2 * (world - 1) // world,
-                                RS_B * RS_V * 2 * (world - 1) // world, RS_B // world))
-        rs["exact_peer_memory"]["what"] = ("no collective library: every rank's shard, results and flags in a block the "
-                                           "peers opened through CUDA IPC; one kernel of this library pulls the rank's "
-                                           "%d rows out of the peers' shards over NVLink (plain loads, bounded flag "
-                                           "waits), the exact kernel samples them, one kernel pushes the indices to "
-                                           "every peer" % (RS_B // world))
+        rs["exact"]["what"] = ("64 rows, vocabulary 128256 split over %d GPUs; default mode, index-exact, every rank "
+                               "samples %d whole rows.  exchange 'peer_memory' (the default where the ranks can share "
+                               "memory over CUDA IPC): the caller's shard is copied into the rank's block, the sampling "
+                               "kernel reads the peers' shards and stores the indices to every rank, the results are "
+                               "copied out.  exact_all_to_all / exact_all_gather force the NCCL exchanges (all-to-all: %d "
+                               "bytes received per rank; all-gather of all shards: %d bytes; then one all-gather of the "
+                               "indices)" %
+                               (world, RS_B // world, RS_B // world * RS_V * 2 * (world - 1) // world,
+                                RS_B * RS_V * 2 * (world - 1) // world))
+        rs["exact_peer_memory"]["what"] = ("the same exchange with the logits produced in and the results read from "
+                                           "the rank's block (no copies): ONE launch per rank, whose CTAs wait for the "
+                                           "peers' flag words, read their %d rows out of the peers' shards over NVLink "
+                                           "(plain loads), store the indices to every peer and run the closing flag "
+                                           "round; every wait bounded" % (RS_B // world))
         rs["fast"]["what"] = ("local candidate kernel, one NCCL all-gather of %d bytes per rank, finishing kernel; "
                               "denominator correctly rounded instead of sequential" % (RS_B * 1056))
         rs["one_gpu_unsharded_ms"] = round(own_per_op_ms["random_sample"], 4)

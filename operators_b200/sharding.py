@@ -103,30 +103,43 @@ class PeerBlocks:
         self.nbytes = self.logits_off + self.max_rows * self.shard_cols * 2
         ptr, ipc = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
         with torch.cuda.device(device):
-            check_error(lib.infiniopExtPeerAlloc(handle, self.nbytes, ctypes.byref(ptr), ipc))
-        self.ptr, self._opened = int(ptr.value), []
+            status = lib.infiniopExtPeerAlloc(handle, self.nbytes, ctypes.byref(ptr), ipc)
+        self.ptr, self._opened, self.device = (int(ptr.value) if status == 0 else None), [], device
         if local_blocks is not None:
+            check_error(status)
             local_blocks.append(self)
             self._local_blocks, self.bases = local_blocks, None
         else:
+            # Every rank takes part in both exchanges whatever happened to it, and all ranks reach the same verdict:
+            # either every block is allocated and opened everywhere, or every rank frees what it has and raises.
             self._local_blocks = None
-            handles = [None] * self.world
+            handles = [bytes(ipc) if status == 0 else None]
             if self.world > 1:
                 import torch.distributed as dist
 
-                dist.all_gather_object(handles, bytes(ipc), group=group)
-            self.bases = []
-            for r in range(self.world):
+                handles = [None] * self.world
+                dist.all_gather_object(handles, bytes(ipc) if status == 0 else None, group=group)
+            self.bases, opened_all = [], all(h is not None for h in handles)
+            for r in range(self.world if opened_all else 0):
                 if r == self.rank:
                     self.bases.append(self.ptr)
                     continue
                 other = ctypes.c_void_p()
                 raw = (ctypes.c_ubyte * 64).from_buffer_copy(handles[r])
                 with torch.cuda.device(device):
-                    check_error(lib.infiniopExtPeerOpen(handle, raw, ctypes.byref(other)))
+                    if lib.infiniopExtPeerOpen(handle, raw, ctypes.byref(other)) != 0:
+                        opened_all = False
+                        break
                 self._opened.append(int(other.value))
                 self.bases.append(int(other.value))
-        self.device = device
+            verdicts = [opened_all]
+            if self.world > 1:
+                verdicts = [None] * self.world
+                dist.all_gather_object(verdicts, opened_all, group=group)
+            if not all(verdicts):
+                self.results = self.logits = self.flags = None
+                self.destroy()
+                raise RuntimeError("peer memory blocks could not be allocated and opened on every rank")
         self.results = torch.as_tensor(_DeviceArray(self.ptr + self.results_off, (self.max_rows,), "<i8"), device=device)
         self.logits = torch.as_tensor(_DeviceArray(self.ptr + self.logits_off, (self.max_rows, self.shard_cols), "<f2"),
                                       device=device)
@@ -140,13 +153,12 @@ class PeerBlocks:
     def destroy(self):
         import torch
 
-        if self.ptr is None:
-            return
         with torch.cuda.device(self.device):
             torch.cuda.synchronize()
             for other in self._opened:
                 self.lib.infiniopExtPeerClose(self.handle, other)
-            self.lib.infiniopExtPeerFree(self.handle, self.ptr)
+            if self.ptr is not None:
+                self.lib.infiniopExtPeerFree(self.handle, self.ptr)
         self.ptr, self._opened, self.results, self.logits, self.flags = None, [], None, None, None
 
 
@@ -156,15 +168,17 @@ class VocabShardedSampler:
 
     mode "exact" (default): the sampled index is the unsharded entry point's, i.e. the reference CPU path's,
     for every row.  The reference's softmax denominator is a sequential fp32 sum over the whole row, which no
-    per-shard partial can reproduce, so the rows are redistributed instead: ONE all-to-all gives rank r the whole
-    rows row_range(rows, world, r), the exact batched kernel samples them, one all-gather of the indices (8 bytes
-    per row) closes the call.
+    per-shard partial can reproduce, so the rows are redistributed instead: rank r gets the whole rows
+    row_range(rows, world, r), the exact batched kernel samples them, the indices go back to every rank.  How the rows
+    travel (`exchange`): "auto" shares one block per rank over CUDA IPC at the first call and lets the sampling
+    kernel itself read the peers' shards and store the indices to every rank (PeerBlocks; one launch, no
+    collective); where the blocks cannot be shared on every rank it uses "all_gather" (from four ranks with equal
+    shards) or "all_to_all", one NCCL collective in and one all-gather of 8 bytes per row out.
 
     mode "fast": a local candidate kernel on every rank, ONE all-gather of ~1 KB per row per rank, a finishing
     kernel.  Top-k set, tie order and numerators are the reference's; the denominator is the correctly rounded
     sum instead of the sequential one, so a small fraction of rows picks a neighbouring candidate.
 
-    Received data is in local memory before any kernel reads it; nothing here loads from a peer's memory.
     `stream`, when given, must be a torch.cuda.Stream: the collectives and the library's kernels are all issued
     on it.  `all_gather(out, inp)` / `all_to_all(out, inp, out_splits, in_splits)` replace the
     torch.distributed calls on `group` (tests play several ranks in one process with them)."""
@@ -187,6 +201,12 @@ class VocabShardedSampler:
         # does not grow with the number of peers the way the send / receive pairs of an all-to-all do) and lets it
         # pick its rows.  It needs equal shards; "auto" takes it from four ranks up.
         equal = int(voc_total) % int(world_size) == 0
+        # "auto" with real ranks: peer memory, set up at the first call (collective; the blocks are sized for that
+        # call's rows and made anew when a later call has more); when the blocks cannot be shared on every rank, the
+        # collective exchanges below.  destroy() is then collective as well (nobody frees a block a peer may read).
+        self._auto_peer = (exchange == "auto" and mode == "exact" and int(world_size) > 1 and all_to_all is None
+                           and all_gather is None)
+        self._own_peer = False
         if exchange == "auto":
             exchange = "all_gather" if (int(world_size) >= 4 and equal and all_to_all is None) else "all_to_all"
         if exchange == "all_gather" and not equal:
@@ -214,6 +234,37 @@ class VocabShardedSampler:
             if entry[4] is not None:
                 entry[4].destroy()
         self._exact = {}
+        self._drop_own_peer()
+
+    def _drop_own_peer(self):
+        if self._own_peer and self.peer is not None:
+            import torch
+            import torch.distributed as dist
+
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+            self.peer.destroy()
+            self.peer, self._own_peer = None, False
+            self._bufs = {k: v for k, v in self._bufs.items() if not (isinstance(k, tuple) and k[0] == "tables")}
+
+    def _auto_peer_setup(self, rows, device):
+        """First exact call of an "auto" sampler with real ranks (and any later call with more rows): try to share
+        blocks over CUDA IPC; every rank reaches the same verdict (PeerBlocks), so either all switch to peer memory
+        or all keep the collective exchange."""
+        if self.peer is not None and self._own_peer and rows > self.peer.max_rows:
+            self._drop_own_peer()
+            for entry in self._exact.values():  # buffers sized for the other exchange
+                entry[3].destroy()
+                if entry[4] is not None:
+                    entry[4].destroy()
+            self._exact = {}
+        if self.peer is None:
+            b, e = vocab_range(self.voc_total, self.world, self.rank)
+            try:
+                self.peer = PeerBlocks(self.lib, self.handle, rows, e - b, self.world, self.rank, device, group=self.group)
+                self._own_peer, self._fallback_exchange, self.exchange = True, self.exchange, "peer_memory"
+            except RuntimeError:
+                self._auto_peer = False
 
     def _buffers(self, rows, device):
         import torch
@@ -290,6 +341,8 @@ class VocabShardedSampler:
         import torch
 
         rows = local_logits.shape[0]
+        if self._auto_peer and local_logits.is_cuda and (self.peer is None or rows > self.peer.max_rows):
+            self._auto_peer_setup(rows, local_logits.device)
         (r0, r1), send, recv, cols = exchange_plan(rows, self.voc_total, self.world, self.rank)
         mine = r1 - r0
         received, full, picked, op, op_copy, full_view, received_view = self._exact_buffers(rows, local_logits.device)
