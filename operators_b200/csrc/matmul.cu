@@ -26,16 +26,15 @@ using namespace b200;
 namespace {
 
 // ---- CUDA-core kernel: any strides, fp16 or fp32 storage, fp32 accumulation ------------------------------
-template<typename T>
-__device__ __forceinline__ float load_elem(const T *p);
-template<>
-__device__ __forceinline__ float load_elem<uint16_t>(const uint16_t *p) { return f16_to_f32(*p); }
-template<>
-__device__ __forceinline__ float load_elem<float>(const float *p) { return *p; }
+template<int DT, typename T>
+__device__ __forceinline__ float load_elem(const T *p) {
+    if constexpr (sizeof(T) == 2) return load16<DT>(*p);
+    else return *p;
+}
 
 constexpr int kSimtTile = 64, kSimtK = 16;
 
-template<typename T>
+template<typename T, int DT>
 __global__ void __launch_bounds__(256)
     matmul_simt_kernel(T *c, const T *a, const T *b, MatView vc, MatView va, MatView vb, uint32_t m, uint32_t n,
                        uint32_t k, float alpha, float beta) {
@@ -53,13 +52,13 @@ __global__ void __launch_bounds__(256)
             if (va.col_stride == 1) kk = e % kSimtK, r = e / kSimtK;
             else r = e % kSimtTile, kk = e / kSimtTile;
             float v = 0.f;
-            if (m0 + r < m && k0 + kk < k) v = load_elem(ab + (int64_t) (m0 + r) * va.row_stride + (int64_t) (k0 + kk) * va.col_stride);
+            if (m0 + r < m && k0 + kk < k) v = load_elem<DT>(ab + (int64_t) (m0 + r) * va.row_stride + (int64_t) (k0 + kk) * va.col_stride);
             sa[kk][r] = v;
             uint32_t cn, kb;
             if (vb.col_stride == 1) cn = e % kSimtTile, kb = e / kSimtTile;
             else kb = e % kSimtK, cn = e / kSimtK;
             v = 0.f;
-            if (n0 + cn < n && k0 + kb < k) v = load_elem(bb + (int64_t) (k0 + kb) * vb.row_stride + (int64_t) (n0 + cn) * vb.col_stride);
+            if (n0 + cn < n && k0 + kb < k) v = load_elem<DT>(bb + (int64_t) (k0 + kb) * vb.row_stride + (int64_t) (n0 + cn) * vb.col_stride);
             sb[kb][cn] = v;
         }
         __syncthreads();
@@ -83,8 +82,8 @@ __global__ void __launch_bounds__(256)
             if (r < m && cn < n) {
                 T *dst = cb + (int64_t) r * vc.row_stride + (int64_t) cn * vc.col_stride;
                 float v = __fmul_rn(alpha, acc[i][j]);
-                if (beta != 0.f) v = __fadd_rn(__fmul_rn(beta, load_elem(dst)), v);
-                if constexpr (sizeof(T) == 2) *dst = f32_to_f16_ref(v);
+                if (beta != 0.f) v = __fadd_rn(__fmul_rn(beta, load_elem<DT>(dst)), v);
+                if constexpr (sizeof(T) == 2) *dst = store16<DT>(v);
                 else *dst = v;
             }
         }
@@ -111,7 +110,7 @@ EncodeTiledFn encode_fn() {
 }
 
 // One operand seen as rows x k (fp16): K-major when k is contiguous, MN-major when the rows are.
-bool encode_operand(CUtensorMap *map, const void *base, const TcOperand &o, uint32_t box_rows) {
+bool encode_operand(CUtensorMap *map, const void *base, const TcOperand &o, uint32_t box_rows, bool bf16) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return false;
     // leading dimension in bytes; a dimension of extent 1 gets any legal stride
@@ -124,8 +123,8 @@ bool encode_operand(CUtensorMap *map, const void *base, const TcOperand &o, uint
     cuuint64_t strides[2] = {ld_bytes, batch_bytes};
     cuuint32_t box[3] = {64, o.mn_major ? 64u : box_rows, 1};
     cuuint32_t estr[3] = {1, 1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    const CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                          const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
@@ -212,7 +211,9 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
                                     int epilogue_mode, uint32_t b_batch_div) {
     if (c_desc == nullptr || a_desc == nullptr || b_desc == nullptr) return STATUS_BAD_PARAM;
     // dtype first, then the layout checks in the reference's order a, b, c (matmul_cuda.cc:12-20, blas.h:19-48)
-    const bool f16 = dt_eq(c_desc->dt, F16), f32 = dt_eq(c_desc->dt, F32);
+    // (bf16 is an extension of this library: the reference's matmul takes fp16 and fp32)
+    const bool bf16 = dt_eq(c_desc->dt, BF16);
+    const bool f16 = dt_eq(c_desc->dt, F16) || bf16, f32 = dt_eq(c_desc->dt, F32);
     if (!f16 && !f32) return STATUS_BAD_TENSOR_DTYPE;
     infiniopTensorDescriptor_t descs[3] = {a_desc, b_desc, c_desc};
     MatView views[3];
@@ -255,7 +256,7 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
 
     pl = MatmulPlan{};
     pl.device_id = h->device_id, pl.sm_count = h->sm_count;
-    pl.f16 = f16;
+    pl.f16 = f16, pl.bf16 = bf16;
     pl.a = va, pl.b = vb, pl.c = vc;
     pl.batch = vc.batch, pl.m = vc.rows, pl.n = vb.cols, pl.k = va.cols;
     pl.alpha = alpha, pl.beta = beta;
@@ -281,6 +282,7 @@ infiniopStatus_t matmul_plan_create(MatmulPlan &pl, const Handle *h, infiniopTen
     if (swiglu && (pl.swapped ? pl.p.mn_major : pl.q.mn_major) && n_out % 8 != 0) return STATUS_SUCCESS;
     g.mp = pl.p.rows, g.np = pl.q.rows, g.k = pl.k, g.batch = pl.batch;
     g.p_major_mn = pl.p.mn_major, g.q_major_mn = pl.q.mn_major;
+    g.bf16 = pl.bf16 ? 1u : 0u;
     g.p_batch_mul = pl.p.batch_stride == 0 ? 0 : 1, g.q_batch_mul = pl.q.batch_stride == 0 ? 0 : 1;
     g.p_batch_div = pl.p.batch_div, g.q_batch_div = pl.q.batch_div;
     g.tiles_m = (g.mp + tc::kBM - 1) / tc::kBM;
@@ -415,7 +417,8 @@ infiniopStatus_t matmul_plan_run(MatmulPlan &pl, TcMapCache &cache, void *worksp
         {
             std::lock_guard<std::mutex> lock(cache.mu);
             if (!cache.valid || cache.p_ptr != pp || cache.q_ptr != qp) {
-                if (!encode_operand(&cache.map_p, pp, pl.p, pl.p_box_rows) || !encode_operand(&cache.map_q, qp, pl.q, pl.q_box_rows)) {
+                if (!encode_operand(&cache.map_p, pp, pl.p, pl.p_box_rows, pl.bf16) ||
+                    !encode_operand(&cache.map_q, qp, pl.q, pl.q_box_rows, pl.bf16)) {
                     fprintf(stderr, "infiniop[b200]: matmul: cuTensorMapEncodeTiled refused the operands\n");
                     return STATUS_EXECUTION_FAILED;
                 }
@@ -443,11 +446,12 @@ infiniopStatus_t matmul_plan_run(MatmulPlan &pl, TcMapCache &cache, void *worksp
     const dim3 grid((pl.n + kSimtTile - 1) / kSimtTile, (pl.m + kSimtTile - 1) / kSimtTile, pl.batch);
     if (grid.y > 65535 || grid.z > 65535) return STATUS_BAD_TENSOR_SHAPE;
     if (pl.f16) {
-        matmul_simt_kernel<uint16_t><<<grid, 256, 0, st>>>(reinterpret_cast<uint16_t *>(c), reinterpret_cast<const uint16_t *>(a),
-                                                         reinterpret_cast<const uint16_t *>(b), pl.c, pl.a, pl.b, pl.m,
-                                                         pl.n, pl.k, pl.alpha, pl.beta);
+        auto *kernel = pl.bf16 ? matmul_simt_kernel<uint16_t, kBF16> : matmul_simt_kernel<uint16_t, kF16>;
+        kernel<<<grid, 256, 0, st>>>(reinterpret_cast<uint16_t *>(c), reinterpret_cast<const uint16_t *>(a),
+                                     reinterpret_cast<const uint16_t *>(b), pl.c, pl.a, pl.b, pl.m, pl.n, pl.k, pl.alpha,
+                                     pl.beta);
     } else {
-        matmul_simt_kernel<float><<<grid, 256, 0, st>>>(reinterpret_cast<float *>(c), reinterpret_cast<const float *>(a),
+        matmul_simt_kernel<float, kF32><<<grid, 256, 0, st>>>(reinterpret_cast<float *>(c), reinterpret_cast<const float *>(a),
                                                       reinterpret_cast<const float *>(b), pl.c, pl.a, pl.b, pl.m, pl.n,
                                                       pl.k, pl.alpha, pl.beta);
     }

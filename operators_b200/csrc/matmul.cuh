@@ -25,7 +25,8 @@ struct TcOperand {
 
 struct MatmulPlan {
     int device_id, sm_count;
-    bool f16;
+    bool f16; // 16-bit storage (fp16, or bf16 when `bf16` is set); otherwise fp32
+    bool bf16;
     MatView a, b, c;
     uint32_t batch, m, n, k;
     float alpha, beta;

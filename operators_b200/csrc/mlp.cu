@@ -26,7 +26,7 @@ struct MLPDesc {
     uint64_t act_bytes, gate_up_bytes, scratch_bytes, workspace_bytes;
 };
 
-TensorDescriptor make_desc(uint64_t *shape, int64_t *strides) { return TensorDescriptor{F16, 2, shape, strides}; }
+TensorDescriptor make_desc(DataLayout dt, uint64_t *shape, int64_t *strides) { return TensorDescriptor{dt, 2, shape, strides}; }
 
 uint64_t round256(uint64_t v) { return (v + 255) / 256 * 256; }
 
@@ -44,7 +44,9 @@ INFINIOP_API infiniopStatus_t infiniopCreateMLPDescriptor(infiniopHandle_t handl
     // checks and codes of reference operator.cc:30-36
     if (y_desc->ndim != 2 || x_desc->ndim != 2 || w12_desc->ndim != 2 || w3_desc->ndim != 2) return STATUS_BAD_TENSOR_SHAPE;
     if (x_desc->strides[1] != 1 || y_desc->strides[1] != 1) return STATUS_BAD_TENSOR_STRIDES;
-    if (!dt_eq(x_desc->dt, F16)) return STATUS_BAD_TENSOR_DTYPE;
+    // (bf16 is an extension of this library: all four tensors bf16; the reference's MLP is fp16)
+    if (!dt_eq(x_desc->dt, F16) && !dt_eq(x_desc->dt, BF16)) return STATUS_BAD_TENSOR_DTYPE;
+    const DataLayout dt = x_desc->dt;
     const uint64_t tokens = x_desc->shape[0], hidden = x_desc->shape[1], di = w12_desc->shape[1] / 2;
     if (w12_desc->shape[1] % 2 != 0) return STATUS_BAD_TENSOR_SHAPE;
 
@@ -58,7 +60,7 @@ INFINIOP_API infiniopStatus_t infiniopCreateMLPDescriptor(infiniopHandle_t handl
 
     uint64_t act_shape[2] = {tokens, di};
     int64_t act_strides[2] = {(int64_t) di, 1};
-    TensorDescriptor act = make_desc(act_shape, act_strides);
+    TensorDescriptor act = make_desc(dt, act_shape, act_strides);
     infiniopStatus_t s = matmul_plan_create(d->up, h, &act, 1.0f, x_desc, w12_desc, 0.0f, tc::kEpiSwiGLUCols);
     d->fused = s == STATUS_SUCCESS && d->up.use_tc;
     d->act_bytes = round256(tokens * di * 2);
@@ -68,10 +70,10 @@ INFINIOP_API infiniopStatus_t infiniopCreateMLPDescriptor(infiniopHandle_t handl
         // the reference's three steps: [tokens, 2 di], SwiGLU on its halves (operator.cc:38-57)
         uint64_t gu_shape[2] = {tokens, 2 * di};
         int64_t gu_strides[2] = {(int64_t) (2 * di), 1};
-        TensorDescriptor gu = make_desc(gu_shape, gu_strides);
+        TensorDescriptor gu = make_desc(dt, gu_shape, gu_strides);
         s = matmul_plan_create(d->up, h, &gu, 1.0f, x_desc, w12_desc, 0.0f, tc::kEpiPlain);
         if (s == STATUS_SUCCESS) {
-            TensorDescriptor half = make_desc(act_shape, gu_strides);
+            TensorDescriptor half = make_desc(dt, act_shape, gu_strides);
             s = infiniopCreateSwiGLUDescriptor(handle, &d->swiglu, &act, &half, &half);
         }
         d->gate_up_bytes = round256(tokens * 2 * di * 2);

@@ -58,6 +58,7 @@ struct GemmParams {
     uint32_t q_boxes;         // TMA boxes per Q tile (1 for K-major, bn/64 for MN-major; doubled halves in SwiGLU mode)
     uint32_t q_box_bytes;
     uint32_t p_major_mn, q_major_mn;
+    uint32_t bf16;            // operands and result are bf16 (an extension; the reference's matmul is fp16 / fp32)
     int32_t p_batch_mul, q_batch_mul;// 0 when the operand is broadcast over the batch
     uint32_t p_batch_div, q_batch_div;// operand batch = result batch / div (grouped heads share one operand)
     uint32_t stages;
@@ -143,6 +144,15 @@ __device__ __forceinline__ bool work_item(const GemmParams &p, uint32_t cta, uin
     return true;
 }
 
+// The 16-bit storage type of D and of the intermediate the SwiGLU epilogue rounds through: fp16 with the reference's
+// truncating rule, or bf16 truncated likewise.
+__device__ __forceinline__ uint16_t to_store16(const GemmParams &p, float v) {
+    return p.bf16 ? f32_to_bf16_trunc(v) : f32_to_f16_ref(v);
+}
+__device__ __forceinline__ float load_store16(const GemmParams &p, uint16_t h) {
+    return p.bf16 ? __uint_as_float((uint32_t) h << 16) : f16_to_f32(h);
+}
+
 // Final values of 16 consecutive columns of one lane, written to D.
 __device__ __forceinline__ void store_cols16(const GemmParams &p, const float *acc, uint32_t row, uint32_t col0,
                                              uint32_t batch, uint32_t mp, uint32_t np, float alpha, float beta) {
@@ -153,9 +163,9 @@ __device__ __forceinline__ void store_cols16(const GemmParams &p, const float *a
     for (int j = 0; j < 16; ++j) {
         float v = __fmul_rn(alpha, acc[j]);
         if (beta != 0.f && col0 + j < np) {
-            v = __fadd_rn(__fmul_rn(beta, f16_to_f32(base[(int64_t) (col0 + j) * p.c_col_stride])), v);
+            v = __fadd_rn(__fmul_rn(beta, load_store16(p, base[(int64_t) (col0 + j) * p.c_col_stride])), v);
         }
-        out[j] = f32_to_f16_ref(v);
+        out[j] = to_store16(p, v);
     }
     if (p.c_col_stride == 1 && col0 + 16 <= np && ((reinterpret_cast<uintptr_t>(base + col0) & 15u) == 0)) {
         uint4 *dst = reinterpret_cast<uint4 *>(base + col0);
@@ -184,7 +194,7 @@ __device__ __forceinline__ void finish_tile(const GemmParams &p, Load16 load16, 
             // the reference stores x * w12 as fp16 before SwiGLU reads it back
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const float g = f16_to_f32(f32_to_f16_ref(gate[j])), u = f16_to_f32(f32_to_f16_ref(up[j]));
+                const float g = load_store16(p, to_store16(p, gate[j])), u = load_store16(p, to_store16(p, up[j]));
                 gate[j] = __fmul_rn(u, silu_f32(g));
             }
             store_cols16(p, gate, row, tn * half + c0, b, p.mp, p.half_offset, 1.f, 0.f);
@@ -197,7 +207,7 @@ __device__ __forceinline__ void finish_tile(const GemmParams &p, Load16 load16, 
             load16(p.bn + c0, up);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const float g = f16_to_f32(f32_to_f16_ref(gate[j])), u = f16_to_f32(f32_to_f16_ref(up[j]));
+                const float g = load_store16(p, to_store16(p, gate[j])), u = load_store16(p, to_store16(p, up[j]));
                 gate[j] = __fmul_rn(u, silu_f32(g));
             }
             store_cols16(p, gate, feature, tn * p.bn + c0, b, p.half_offset, p.np, 1.f, 0.f);// result rows = features
@@ -328,7 +338,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            const uint32_t idesc = make_idesc(kBM, p.bn, p.p_major_mn, p.q_major_mn);
+            const uint32_t idesc = make_idesc(kBM, p.bn, p.p_major_mn, p.q_major_mn, p.bf16);
             uint32_t stage = 0, phase = 0, acc_it = 0;
             WorkItem w;
             bool ok = true;
@@ -603,7 +613,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && rank == 0) {
-            const uint32_t idesc = make_idesc(256, kPairBN, p.p_major_mn, p.q_major_mn);
+            const uint32_t idesc = make_idesc(256, kPairBN, p.p_major_mn, p.q_major_mn, p.bf16);
             uint32_t stage = 0, phase = 0, acc_it = 0, tile;
             bool ok = true;
             for (uint32_t it = 0; ok && pair_tile(p, pair, pairs, it, tile); ++it) {
@@ -659,7 +669,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     tmem_ld16(taddr + 128 + c0, up);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const float g = f16_to_f32(f32_to_f16_ref(gate[j])), u = f16_to_f32(f32_to_f16_ref(up[j]));
+                        const float g = load_store16(p, to_store16(p, gate[j])), u = load_store16(p, to_store16(p, up[j]));
                         gate[j] = __fmul_rn(u, silu_f32(g));
                     }
                     store_cols16(p, gate, row, tn * 128 + c0, b, p.mp, p.half_offset, 1.f, 0.f);

@@ -154,10 +154,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
     return d;
 }
 
-// Instruction descriptor of kind::f16: D fp32 (bits 4-5 = 1), A and B fp16 (formats 0), majors at bits 15 / 16
-// (0 = K-major, 1 = MN-major), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
-__host__ __device__ inline uint32_t make_idesc(uint32_t m, uint32_t n, uint32_t a_mn_major, uint32_t b_mn_major) {
-    return (1u << 4) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+// Instruction descriptor of kind::f16: D fp32 (bits 4-5 = 1), A and B formats at bits 7-9 / 10-12 (0 = fp16, 1 = bf16),
+// majors at bits 15 / 16 (0 = K-major, 1 = MN-major), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__host__ __device__ inline uint32_t make_idesc(uint32_t m, uint32_t n, uint32_t a_mn_major, uint32_t b_mn_major,
+                                               uint32_t bf16 = 0) {
+    return (1u << 4) | (bf16 << 7) | (bf16 << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
+           ((m >> 4) << 24);
 }
 
 __device__ __forceinline__ float silu_f32(float x) { return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))); }

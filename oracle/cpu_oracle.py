@@ -241,7 +241,7 @@ def mlp(y, x, w12, w3, alpha=1.0, residual=True):
     """The MLP composite, src/ops/mlp/operator.cc:22-122, with the operators above: gate_up = x @ w12 stored as
     fp16, act = up * silu(gate) on its column halves (gate first), y = alpha * act @ w3 (+ y).  In place on y."""
     tokens, di = x.shape[0], w12.shape[1] // 2
-    gate_up = np.zeros((tokens, 2 * di), np.float16)
+    gate_up = np.zeros((tokens, 2 * di), x.dtype)  # fp16, or 16-bit patterns inside `with bf16_storage()`
     matmul_into(gate_up, x, w12)
     act = swiglu(gate_up[:, di:], gate_up[:, :di])
     matmul_into(y, act, w3, alpha, 1.0 if residual else 0.0)

@@ -525,6 +525,15 @@ def _bf16_within_one_ulp(got, want):
     return int(((diff != 0) & ~both_zero).sum())
 
 
+def _bf16_close(got_bits, want_bits, atol, rtol):
+    """|got - want| <= atol + rtol * |want| on bf16 patterns; returns the number of patterns that differ."""
+    got = (got_bits.reshape(-1).astype(np.uint32) << 16).view(np.float32)
+    want = (want_bits.reshape(-1).astype(np.uint32) << 16).view(np.float32)
+    err = np.abs(got - want)
+    assert (err <= atol + rtol * np.abs(want)).all(), "max err %g" % err.max()
+    return int((got_bits.reshape(-1) != want_bits.reshape(-1)).sum())
+
+
 @pytest.mark.parametrize("shapes", [((3, 3), (3, 3)), ((2, 20, 3), (2, 1, 3)), ((64, 4096), (4096,)), ((1000003,), (1000003,)),
                                     ((300, 8), (8,))])
 def test_bf16_add(oracle, cuda_lib, shapes):
@@ -791,6 +800,53 @@ def test_mlp(oracle, cuda_lib, tokens, hidden, di, alpha, residual, x_stride, w1
     torch.cuda.synchronize()
     _close(_bits(yd).reshape(tokens, hidden), want, 1e-3, 1e-3)
     assert torch.equal(xd.cpu(), x)
+
+
+# ---- bf16 matmul and MLP (an extension: the reference's are fp16 / fp32; oracle = the restated functions on bf16
+# patterns, oracle.bf16_storage) ---------------------------------------------------------------------------
+@pytest.mark.parametrize("alpha,beta,a_shape,b_shape,c_shape,a_stride,b_stride,c_stride",
+                         [c for c in MATMUL_CASES if c[2][-2] <= 512][:8] + [(1.0, 0.0, (600, 256), (256, 384), (600, 384), None, None, None),
+                                                                             (0.5, 1.0, (3, 256), (256, 1024), (3, 1024), None, (1, 256), None)])
+def test_bf16_matmul(oracle, cuda_lib, matmul_kernels, alpha, beta, a_shape, b_shape, c_shape, a_stride, b_stride, c_stride):
+    """Within one bf16 ulp (2^-8 of the value) of the oracle, plus 1e-5 absolute for sums that cancel: only the
+    grouping of the fp32 sum over k differs, so most elements are the same pattern."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(18)
+    a, b, c = ((torch.rand(sh, generator=g) - 0.5).bfloat16() for sh in (a_shape, b_shape, c_shape))
+    a, b, c = (t if st is None else rearrange_tensor(t, st) for t, st in ((a, a_stride), (b, b_stride), (c, c_stride)))
+    want = c.clone()
+    if c_stride is not None:
+        want = rearrange_tensor(want, c_stride)
+    with oracle.bf16_storage():
+        oracle.matmul_into(want.view(torch.int16).numpy().view(np.uint16), a.view(torch.int16).numpy().view(np.uint16),
+                           b.view(torch.int16).numpy().view(np.uint16), alpha, beta)
+    ad, bd, cd = (t.to(DEV) for t in (a, b, c))
+    ad, bd, cd = (t if st is None else rearrange_tensor(t, st) for t, st in ((ad, a_stride), (bd, b_stride), (cd, c_stride)))
+    ops.matmul(lib, handle, cd, ad, bd, alpha, beta)
+    torch.cuda.synchronize()
+    assert _few(_bf16_close(_bf16_bits(cd), _bf16_bits(want), 1e-5, 2.0 ** -7), c.numel(), 0.25)
+
+
+@pytest.mark.parametrize("tokens,hidden,di,alpha,residual", [(16, 512, 1408, 1.0, True), (300, 512, 1376, 0.5, True),
+                                                             (640, 256, 512, 1.0, False), (7, 72, 36, 1.0, False)])
+def test_bf16_mlp(oracle, cuda_lib, tokens, hidden, di, alpha, residual):
+    """The MLP composite on bf16 tensors: fused SwiGLU epilogue (transposed and plain orientation, CTA pairs at 640
+    tokens) and the three-step form for the last shape; within two bf16 ulps of the oracle (an intermediate that
+    differs by one ulp moves a few sums by one more), plus 1e-4 absolute for sums that cancel."""
+    lib, handle = cuda_lib
+    g = torch.Generator().manual_seed(19)
+    y = (torch.rand((tokens, hidden), generator=g) - 0.5).bfloat16()
+    x = (torch.rand((tokens, hidden), generator=g) - 0.5).bfloat16()
+    w12 = ((torch.rand((hidden, 2 * di), generator=g) - 0.5) * 0.1).bfloat16()
+    w3 = ((torch.rand((di, hidden), generator=g) - 0.5) * 0.1).bfloat16()
+    want = _bf16_bits(y).reshape(tokens, hidden).copy()
+    with oracle.bf16_storage():
+        oracle.mlp(want, _bf16_bits(x).reshape(x.shape), _bf16_bits(w12).reshape(w12.shape), _bf16_bits(w3).reshape(w3.shape),
+                   alpha, residual)
+    yd, xd, w12d, w3d = (t.to(DEV) for t in (y, x, w12, w3))
+    ops.mlp(lib, handle, yd, xd, w12d, w3d, alpha, residual)
+    torch.cuda.synchronize()
+    assert _few(_bf16_close(_bf16_bits(yd), want, 1e-4, 2.0 ** -6), y.numel(), 0.25)
 
 
 # ---- the five configurations the benchmark quotes, at full size -----------------------------------------
