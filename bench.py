@@ -379,8 +379,8 @@ PREFILL_CASE = {"new_tokens": None}  # --new-tokens: one case only (ncu captures
 
 
 def only_attention_prefill(lib, handle, dev, steps, warmup):
-    """Not part of the step: attention for a prompt (new tokens into an empty cache), 32 q / 8 kv heads, dh 128.  FLOPs
-    count the visible half of the two products (4 * heads * dh * tokens * (tokens + 1) / 2)."""
+    """Not part of the step: attention for a prompt (new tokens into an empty cache) and for a chunk of a prompt over a
+    cached prefix, 32 q / 8 kv heads, dh 128.  FLOPs count the visible part of the two products."""
     import torch
 
     from operators_b200 import ops as _ops
@@ -388,21 +388,23 @@ def only_attention_prefill(lib, handle, dev, steps, warmup):
     nh, nkvh, dh = 32, 8, ROPE_DH
     peak = measured_tflops()
     cases = {}
-    for seq in (512, 2048, 4096):
-        if PREFILL_CASE["new_tokens"] not in (None, seq):
+    for seq, pos in ((512, 0), (2048, 0), (4096, 0), (512, 32768), (64, 8192)):
+        if PREFILL_CASE["new_tokens"] is not None and (PREFILL_CASE["new_tokens"] != seq or pos != 0):
             continue
+        total = pos + seq
         q = torch.randn((nh, seq, dh), device=dev).half()
         k = torch.randn((nkvh, seq, dh), device=dev).half()
         v = torch.randn((nkvh, seq, dh), device=dev).half()
-        k_cache = torch.zeros((nkvh, seq, dh), device=dev, dtype=torch.float16)
-        v_cache = torch.zeros((nkvh, seq, dh), device=dev, dtype=torch.float16)
+        k_cache = torch.randn((nkvh, total, dh), device=dev).half()
+        v_cache = torch.randn((nkvh, total, dh), device=dev).half()
         out = torch.empty((seq, nh, dh), device=dev, dtype=torch.float16)
-        op = _ops.AttentionOp(lib, handle, out, q, k, v, k_cache, v_cache, 0)
+        op = _ops.AttentionOp(lib, handle, out, q, k, v, k_cache, v_cache, pos)
         ms = _timed_calls(torch, lambda: op(out, q, k, v, k_cache, v_cache), steps, warmup)
         op.destroy()
-        flops = 4.0 * nh * dh * seq * (seq + 1) / 2
-        cases["%d_new_tokens" % seq] = {"ms": round(ms, 5), "tflops": round(flops / ms / 1e9, 1),
-                                        "frac_of_measured_bf16": round(flops / ms / 1e9 / peak[0], 3) if peak[0] else None}
+        flops = 4.0 * nh * dh * (seq * pos + seq * (seq + 1) / 2)
+        name = "%d_new_tokens" % seq if pos == 0 else "%d_new_over_%d_cached" % (seq, pos)
+        cases[name] = {"ms": round(ms, 5), "tflops": round(flops / ms / 1e9, 1),
+                       "frac_of_measured_bf16": round(flops / ms / 1e9 / peak[0], 3) if peak[0] else None}
         del q, k, v, k_cache, v_cache, out
     return {"only": "attention_prefill", "q_heads": nh, "kv_heads": nkvh, "head_dim": dh, "cases": cases,
             "peak_tflops": {"value": peak[0], "source": peak[1]},

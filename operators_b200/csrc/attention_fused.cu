@@ -25,6 +25,12 @@
 //   warp 9     allocates TMEM (S twice 64 columns, O dh columns); one lane issues the MMAs.  S of tile j + 2 is
 //              issued before P v of tile j (its buffer is free once S of tile j has been read), so the softmax
 //              warps find their next scores ready.
+// Few blocks of query rows over many cached tokens (a chunk of a prompt, speculative drafts): 2, 4 or 8 CTAs, one
+// thread-block cluster, share a block and each takes a range of its tiles.  After pass 1 they exchange their rows'
+// maximum and sum over distributed shared memory (one mbarrier per CTA that every CTA of the cluster arrives on; the
+// waits acquire at cluster scope), after pass 2 each parks its fp32 partial of O in its shared memory and CTA r
+// adds rows [r * 128 / S, ...) of all partials in rank order, truncates and stores them.  A CTA whose range is empty
+// (the first rows of a prompt see fewer tiles than the cluster has CTAs) contributes -inf, 0 and zeros.
 // Every mbarrier wait is bounded (tc_ptx.cuh); a role that gives up raises the CTA's abort flag, all roles leave,
 // copies in flight are awaited (bounded), TMEM is freed, and infiniopExtDeviceTimeouts reports it.
 #include "attention_prefill.cuh"
@@ -50,11 +56,13 @@ constexpr uint32_t kMinSmem = 80 * 1024;// keeps a third CTA (and its TMEM reque
 struct FusedParams {
     uint32_t nh, group, seq, total, tiles_m;
     uint32_t slots;// k / v tiles of the shared-memory ring (4 when two CTAs share an SM, more for a CTA alone)
+    uint32_t splits;// CTAs (one cluster) that share a block of query rows, each with a range of the cached tokens
     float alpha;
     uint16_t *out;// [seq, nh, dh]
 };
 
 constexpr uint32_t kMaxSlots = 16;// k / v tiles in flight per CTA
+constexpr uint32_t kMaxSplits = 8;// CTAs of a cluster that share a block of query rows (the portable cluster size)
 // Waiting roles sleep in the barrier instead of polling: twenty warps share an SM and the exponentials need the issue
 // slots (polling producer and MMA lanes took four of ten issued instructions).
 constexpr uint32_t kSuspendNs = 20000;
@@ -71,7 +79,9 @@ __device__ unsigned long long g_attn_trace[16];
 #define TRACE_ADD(slot, t0, t1)
 #endif
 // barriers: the ring's full / empty pairs first
-enum Bar { kFull = 0, kEmpty = kMaxSlots, kQFull = 2 * kMaxSlots, kSFull, kSFull1, kSEmpty, kSEmpty1, kPFull, kPEmpty, kOFull, kBars };
+enum Bar { kFull = 0, kEmpty = kMaxSlots, kQFull = 2 * kMaxSlots, kSFull, kSFull1, kSEmpty, kSEmpty1, kPFull, kPEmpty, kOFull,
+           kStatsFull, kStatsRead, kOStaged,// between the CTAs of a cluster (splits > 1): one arrival per CTA
+           kBars };
 
 __device__ __forceinline__ uint32_t hmax2_u32(uint32_t a, uint32_t b) {
     uint32_t r;
@@ -133,19 +143,26 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
     unsigned char *sq = smem_raw, *ring = sq + kQBytes, *sp = ring + p.slots * kKVBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(sp + kPBytes);
     float2 *ml = reinterpret_cast<float2 *>(sp);// [2][128]: each half's maximum and sum of a row, between the passes
+    float2 *ml_cta = ml + 2 * kRows;           // [128]: this CTA's maximum and sum of a row, read by its cluster
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the longest blocks (last query rows) start first
-    const uint32_t tm = p.tiles_m - 1 - blockIdx.x / p.nh, h = blockIdx.x % p.nh, kvh = h / p.group;
+    const uint32_t S = p.splits, split = S > 1 ? cluster_rank() : 0u, unit = blockIdx.x / S;
+    const uint32_t tm = p.tiles_m - 1 - unit / p.nh, h = unit % p.nh, kvh = h / p.group;
     const uint32_t row0 = tm * kRows;
     const uint32_t last_row = min(row0 + kRows - 1, p.seq - 1);
-    const uint32_t tiles = (p.total - p.seq + last_row) / kKeys + 1;// tiles that hold a visible column
+    const uint32_t tiles_all = (p.total - p.seq + last_row) / kKeys + 1;// tiles that hold a visible column
+    // this CTA's share of them (possibly none): its maxima, sums and outputs meet the other CTAs' over distributed
+    // shared memory
+    const uint32_t t_begin = split * tiles_all / S, tiles = (split + 1) * tiles_all / S - t_begin;
 
     if (threadIdx.x == 0) {
         for (int b = 0; b < kBars; ++b) {
-            mbar_init(&bars[b], (b == kSEmpty || b == kSEmpty1 || b == kPFull) ? (uint32_t) kSoftmaxThreads : 1u);
+            const bool softmax_arrives = b == kSEmpty || b == kSEmpty1 || b == kPFull;
+            const bool ctas_arrive = b == kStatsFull || b == kStatsRead || b == kOStaged;
+            mbar_init(&bars[b], softmax_arrives ? (uint32_t) kSoftmaxThreads : ctas_arrive ? S : 1u);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -159,6 +176,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
     }
     tc_fence_before();
     __syncthreads();
+    if (S > 1) cluster_sync_all();// nobody arrives on a barrier of another CTA before it exists
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -181,11 +199,11 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
                 return true;
             };
             bool ok = true;
-            for (uint32_t n = 0; ok && n < tiles; ++n) ok = load(false, n);
-            for (uint32_t n = 0; ok && n < 2 && n < tiles; ++n) ok = load(false, n);
+            for (uint32_t n = 0; ok && n < tiles; ++n) ok = load(false, t_begin + n);
+            for (uint32_t n = 0; ok && n < 2 && n < tiles; ++n) ok = load(false, t_begin + n);
             for (uint32_t j = 0; ok && j < tiles; ++j) {
-                if (j + 2 < tiles) ok = load(false, j + 2);
-                if (ok) ok = load(true, j);
+                if (j + 2 < tiles) ok = load(false, t_begin + j + 2);
+                if (ok) ok = load(true, t_begin + j);
             }
         }
         __syncwarp();
@@ -257,7 +275,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         // this thread's 32 scores of tile j (S index n), packed
         auto load_scores = [&](uint32_t n, uint32_t j, auto first_pass) -> bool {
             const uint32_t b = n & 1u;
-            constexpr int kT = decltype(first_pass)::value ? 0 : 4;
+            [[maybe_unused]] constexpr int kT = decltype(first_pass)::value ? 0 : 4;
             TRACE_NOW(t0);
             if (!mbar_wait<kSuspendNs>(&bars[kSFull + b], (n >> 1) & 1u, abort_flag)) return false;
             TRACE_NOW(t1);
@@ -276,7 +294,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         };
 #pragma unroll 1
         for (uint32_t n = 0; n < tiles; ++n) {// pass 1: maximum and sum over this thread's columns of the row
-            if (!(ok = load_scores(n, n, std::true_type{}))) break;
+            if (!(ok = load_scores(n, t_begin + n, std::true_type{}))) break;
             TRACE_NOW(ta);
             uint32_t t8[8];
 #pragma unroll
@@ -306,18 +324,53 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
         {
             const float2 o = ml[(half ^ 1u) * kRows + lane_row];
-            const float m_all = fmaxf(m, o.x), mk_all = -m_all * kLog2e;// column 0 is visible to every row: finite
+            // (column 0 is visible to every row, so the maximum is finite in the CTA that holds tile 0; a CTA whose
+            // tiles are all masked for a row, or that has no tiles, carries -inf and 0)
+            const float m_all = fmaxf(m, o.x), mk_all = -m_all * kLog2e;
             const float mine = m == -INFINITY ? 0.f : l * fast_exp2(fmaf(m, kLog2e, mk_all));
             const float theirs = o.x == -INFINITY ? 0.f : o.y * fast_exp2(fmaf(o.x, kLog2e, mk_all));
             l = half == 0 ? mine + theirs : theirs + mine;// the same sum in both threads
             m = m_all;
+        }
+        if (S > 1) {
+            // the CTAs of the cluster meet: every CTA publishes its rows' (m, l), raises a barrier in every CTA, and
+            // combines all of them in rank order (the same bits everywhere)
+            if (half == 0) ml_cta[lane_row] = make_float2(m, l);
+            asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+            if (threadIdx.x == 0) {
+                for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(mapa_u32(smem_u32(&bars[kStatsFull]), r));
+            }
+            if (ok) ok = mbar_wait_cluster(&bars[kStatsFull], 0, abort_flag);
+            if (ok) {
+                const uint32_t mine_addr = smem_u32(&ml_cta[lane_row]);
+                float m_all = -INFINITY;
+                float2 part[kMaxSplits];
+#pragma unroll
+                for (uint32_t r = 0; r < kMaxSplits; ++r) {
+                    part[r] = r < S ? ld_cluster_f2(mapa_u32(mine_addr, r)) : make_float2(-INFINITY, 0.f);
+                    m_all = fmaxf(m_all, part[r].x);
+                }
+                const float mk_all = -m_all * kLog2e;
+                float l_all = 0.f;
+#pragma unroll
+                for (uint32_t r = 0; r < kMaxSplits; ++r) {
+                    if (part[r].x != -INFINITY) l_all += part[r].y * fast_exp2(fmaf(part[r].x, kLog2e, mk_all));
+                }
+                m = m_all, l = l_all;
+            }
+            // nobody overwrites its (m, l) with P before every CTA has read them
+            asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+            if (threadIdx.x == 0) {
+                for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(mapa_u32(smem_u32(&bars[kStatsRead]), r));
+            }
+            if (ok) ok = mbar_wait_cluster(&bars[kStatsRead], 0, abort_flag);
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");// the exchange area becomes P again
         // exp(x - m) / l as one exponential: 2^(x log2e - m log2e - log2 l)
         const float mk = fmaf(-m, kLog2e, -log2f(l));
 #pragma unroll 1
         for (uint32_t j = 0; ok && j < tiles; ++j) {// pass 2: probabilities into shared memory for P v
-            if (!(ok = load_scores(tiles + j, j, std::false_type{}))) break;
+            if (!(ok = load_scores(tiles + j, t_begin + j, std::false_type{}))) break;
             TRACE_NOW(ta);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -340,21 +393,67 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
             TRACE_ADD(8, tb, tc_);
             TRACE_ADD(9, tc_, td);
         }
-        if (ok && mbar_wait<kSuspendNs>(&bars[kOFull], 0, abort_flag)) {
-            tc_fence_after();
-            constexpr uint32_t kCols = DHB * 32;// this thread's half of the row's dh outputs
-            uint16_t *orow = p.out + ((size_t) row * p.nh + h) * (DHB * 64) + half * kCols;
+        constexpr uint32_t kCols = DHB * 32;// this thread's half of the row's dh outputs
+        if (S == 1) {
+            if (ok && mbar_wait<kSuspendNs>(&bars[kOFull], 0, abort_flag)) {
+                tc_fence_after();
+                uint16_t *orow = p.out + ((size_t) row * p.nh + h) * (DHB * 64) + half * kCols;
 #pragma unroll
-            for (uint32_t c0 = 0; c0 < kCols; c0 += 16) {
-                float acc[16];
-                tmem_ld16(t_lane + 2 * kKeys + half * kCols + c0, acc);// every lane takes part in the load
-                uint32_t o[8];
+                for (uint32_t c0 = 0; c0 < kCols; c0 += 16) {
+                    float acc[16];
+                    tmem_ld16(t_lane + 2 * kKeys + half * kCols + c0, acc);// every lane takes part in the load
+                    uint32_t o[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = pack2_ref(acc[2 * i], acc[2 * i + 1]);
-                if (row < p.seq) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(orow + c0);
-                    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    for (int i = 0; i < 8; ++i) o[i] = pack2_ref(acc[2 * i], acc[2 * i + 1]);
+                    if (row < p.seq) {
+                        uint4 *dst = reinterpret_cast<uint4 *>(orow + c0);
+                        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    }
+                }
+            }
+        } else {
+            // Every CTA parks its fp32 partial of O in its shared memory (q and the ring are idle by now; row r's
+            // 16-byte groups at position g ^ (r % groups), so that a warp's stores spread over the banks), the
+            // cluster meets, and CTA `split` adds rows [split * 128 / S, ...) of all partials in rank order,
+            // truncates and stores them.
+            constexpr uint32_t kGroups = DHB * 16;// float4 groups per row
+            float4 *stage = reinterpret_cast<float4 *>(sq);
+            const bool have = tiles > 0;
+            if (have && ok) ok = mbar_wait<kSuspendNs>(&bars[kOFull], 0, abort_flag);
+            if (ok) {
+                tc_fence_after();
+#pragma unroll
+                for (uint32_t c0 = 0; c0 < kCols; c0 += 16) {
+                    float acc[16];
+                    if (have) tmem_ld16(t_lane + 2 * kKeys + half * kCols + c0, acc);// uniform over the CTA
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        const uint32_t g = (half * kCols + c0) / 4 + i;
+                        stage[lane_row * kGroups + (g ^ (lane_row & (kGroups - 1)))] =
+                            have ? make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+            if (threadIdx.x == 0) {
+                for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(mapa_u32(smem_u32(&bars[kOStaged]), r));
+            }
+            if (ok) ok = mbar_wait_cluster(&bars[kOStaged], 0, abort_flag);
+            if (ok) {
+                const uint32_t rows_per = kRows / S, r_first = split * rows_per;
+                for (uint32_t idx = threadIdx.x; idx < rows_per * kGroups; idx += kSoftmaxThreads) {
+                    const uint32_t r = r_first + idx / kGroups, g = idx % kGroups;
+                    const uint32_t addr = smem_u32(&stage[r * kGroups + (g ^ (r & (kGroups - 1)))]);
+                    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (uint32_t c = 0; c < S; ++c) {
+                        const float4 v = ld_cluster_f4(mapa_u32(addr, c));
+                        sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
+                    }
+                    if (row0 + r < p.seq) {
+                        uint2 *dst = reinterpret_cast<uint2 *>(p.out + ((size_t) (row0 + r) * p.nh + h) * (DHB * 64) + g * 4);
+                        *dst = make_uint2(pack2_ref(sum.x, sum.y), pack2_ref(sum.z, sum.w));
+                    }
                 }
             }
         }
@@ -372,6 +471,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         }
     }
     __syncthreads();
+    if (S > 1) cluster_sync_all();// no CTA leaves while another may still read its shared memory
     if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
@@ -395,7 +495,7 @@ uint32_t fused_slots(uint32_t dhb, size_t budget) {
 struct AttnFused {
     int device_id;
     AttnPrefillShape shape;
-    uint32_t dhb, tiles_m, slots;
+    uint32_t dhb, tiles_m, slots, splits;
     size_t smem_bytes;
     std::mutex mu;
     bool valid = false;
@@ -410,6 +510,15 @@ static bool encode_maps(AttnFused *f, const void *q, const void *k_cache, const 
     return tc_encode_tiles_f16(&f->map_q, q, s.dh, s.seq, s.nh, (uint64_t) s.q_s1 * 2, (uint64_t) s.q_s0 * 2, kRows) &&
            tc_encode_tiles_f16(&f->map_k, k_cache, s.dh, s.total, nkvh, (uint64_t) s.kc_s1 * 2, (uint64_t) s.kc_s0 * 2, kKeys) &&
            tc_encode_tiles_f16(&f->map_v, v_cache, s.dh, s.total, nkvh, (uint64_t) s.vc_s1 * 2, (uint64_t) s.vc_s0 * 2, kKeys);
+}
+
+// Few blocks of query rows over many cached tokens: 2, 4 or 8 CTAs (one cluster) share a block and split its tokens,
+// as long as all CTAs still run at once (two per SM) and every CTA keeps at least four tiles.
+uint32_t attn_fused_splits(const AttnPrefillShape &s, int sm_count) {
+    const uint64_t ctas = (uint64_t) ((s.seq + kRows - 1) / kRows) * s.nh, kv_tiles = (s.total + kKeys - 1) / kKeys;
+    uint32_t splits = 1;
+    while (splits < kMaxSplits && ctas * splits * 2 <= 2ull * (uint64_t) sm_count && kv_tiles >= 8ull * splits) splits *= 2;
+    return splits;
 }
 
 AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s) {
@@ -434,7 +543,8 @@ AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s)
     }
     const uint32_t slots_alone = fused_slots(dhb, (size_t) h->max_smem_optin);
     const uint32_t slots_shared = fused_slots(dhb, (size_t) sm_bytes / 2 - 1024);
-    const uint32_t slots = tiles_m * s.nh <= (uint64_t) h->sm_count ? slots_alone : slots_shared;
+    const uint32_t splits = attn_fused_splits(s, h->sm_count);
+    const uint32_t slots = tiles_m * s.nh * splits <= (uint64_t) h->sm_count ? slots_alone : slots_shared;
     if (slots == 0 || slots_alone == 0) return nullptr;
     const size_t smem = fused_smem_bytes(dhb, slots);
     auto *kernel = dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
@@ -447,7 +557,7 @@ AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s)
     if (f == nullptr) return nullptr;
     f->device_id = h->device_id;
     f->shape = s;
-    f->dhb = dhb, f->tiles_m = (uint32_t) tiles_m, f->slots = slots, f->smem_bytes = smem;
+    f->dhb = dhb, f->tiles_m = (uint32_t) tiles_m, f->slots = slots, f->splits = splits, f->smem_bytes = smem;
     // the encoder checks extents and strides, not the memory: a trial with a placeholder address tells now whether
     // these layouts can be described, so that the caller can keep its other path
     const void *probe = reinterpret_cast<const void *>((uintptr_t) 1 << 20);
@@ -475,11 +585,17 @@ infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const vo
     }
     FusedParams p{};
     p.nh = s.nh, p.group = s.group, p.seq = s.seq, p.total = s.total, p.tiles_m = f->tiles_m, p.slots = f->slots;
+    p.splits = f->splits;
     p.alpha = (float) (1.0 / sqrt((double) s.dh));// `float qk_alpha = 1 / sqrt(head_dim)`, operator.cc:136
     p.out = reinterpret_cast<uint16_t *>(out);
-    const uint32_t grid = f->tiles_m * s.nh;
-    if (f->dhb == 1) attn_fused_kernel<1><<<grid, kFusedThreads, f->smem_bytes, st>>>(mq, mk, mv, p);
-    else attn_fused_kernel<2><<<grid, kFusedThreads, f->smem_bytes, st>>>(mq, mk, mv, p);
+    const uint32_t grid = f->tiles_m * s.nh * f->splits;
+    auto *kernel = f->dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
+    if (f->splits == 1) {
+        kernel<<<grid, kFusedThreads, f->smem_bytes, st>>>(mq, mk, mv, p);
+    } else if (launch_cluster_smem(kernel, grid, kFusedThreads, f->splits, f->smem_bytes, st, mq, mk, mv, p) != cudaSuccess) {
+        cudaGetLastError();
+        return STATUS_EXECUTION_FAILED;
+    }
     return check_launch("attention (fused, several new tokens)");
 }
 

@@ -486,11 +486,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 // full barrier (cta_group::2 form of the copy), the leader's commits are multicast to both CTAs' empty and
 // accumulator barriers, the peer's epilogue arrives on the leader's accumulator-empty barrier remotely.  The loads
 // themselves carry no multicast.  Plain and column-mode SwiGLU epilogues; no stream-K.
-__device__ __forceinline__ uint32_t mapa_u32(uint32_t local, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
-    return r;
-}
 // TMA load whose mbarrier may live in the peer CTA of the pair (address in the cluster window).
 __device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const CUtensorMap *map, uint32_t bar_cluster_addr,
                                                  int32_t x, int32_t y, int32_t z) {
@@ -498,9 +493,6 @@ __device__ __forceinline__ void tma_load_3d_pair(void *smem_dst, const CUtensorM
         "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
         : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                               uint32_t accumulate) {

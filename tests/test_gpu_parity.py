@@ -1052,7 +1052,11 @@ def test_attention(oracle, cuda_lib, attention_kernels, nh, nkvh, seq, dh, pos, 
 
 @pytest.mark.parametrize("kernels", ["three_launches", "one_kernel"])
 @pytest.mark.parametrize("nh,nkvh,seq,dh,pos", [(8, 2, 1024, 128, 0), (8, 4, 600, 64, 1000), (4, 1, 1536, 128, 512),
-                                                (16, 4, 2048, 128, 0)])
+                                                (16, 4, 2048, 128, 0),
+                                                # few blocks of query rows: clusters of CTAs split the cached tokens (the
+                                                # first block of the first shape sees two tiles, so two of its four
+                                                # CTAs have none), few new tokens over a long prefix
+                                                (4, 1, 1024, 128, 0), (8, 2, 64, 128, 6000), (2, 2, 200, 64, 3000)])
 def test_attention_long_prefill_against_float32(cuda_lib, nh, nkvh, seq, dh, pos, kernels):
     """Token counts at which the three-launch form runs its products on CTA pairs with the causal tile skipping
     (several 256-row blocks per head) and the one-kernel form walks dozens of tiles per block of query rows.  The
