@@ -53,9 +53,9 @@ constexpr int kMaxChunk = 2048;   // cached tokens per CTA: their scores live in
 constexpr int kMaxHeadDim = 256;
 constexpr int kUnroll = 4;        // 128-bit loads in flight per thread
 // Several new tokens, one kernel or three launches (microseconds, fitted to measurements at 32 q / 8 kv heads, dh
-// 128): a CTA of the one-kernel form walks its tiles of 64 cached tokens alone, 1.64 us per tile; the three launches
-// cost 50 us plus 6 ps per score.  Grids that fill the GPU always take the one kernel (4096 new tokens: 0.28 ms
-// against 1.70 ms).
+// 128): a CTA of the one-kernel form walks its tiles of 64 cached tokens alone, 1.64 us per tile (a cluster of up
+// to 8 CTAs shares the tiles of a block of query rows when there are few blocks); the three launches cost 50 us
+// plus 6 ps per score.  Grids that fill the GPU always take the one kernel (4096 new tokens: 0.28 ms against 1.70 ms).
 constexpr double kFusedUsPerTile = 1.64, kFusedUsFixed = 8.0, kThreeUsFixed = 50.0, kThreeUsPerScore = 6e-6;
 
 struct AttnDesc {
@@ -902,10 +902,10 @@ INFINIOP_API infiniopStatus_t infiniopCreateAttentionDescriptor(infiniopHandle_t
     d->fused = nullptr;
     if (seq >= 32 && d->strides_vec && total > 0) {
         const AttnPrefillShape shape{d->nh, d->group, d->seq, d->dh, d->total, d->q_s0, d->q_s1, d->kc_s0, d->kc_s1, d->vc_s0, d->vc_s1};
-        // One kernel that keeps the scores on chip (attention_fused.cu) when its CTAs (one per 128 query rows of a
-        // head, each walking its visible tokens alone) are many or short; few new tokens over a long cache keep
-        // the three launches, which spread the cached tokens over the whole GPU (64 new tokens over 8192 cached:
-        // 143 against 222 us).  The choice is made here because
+        // One kernel that keeps the scores on chip (attention_fused.cu) unless the model says that its CTAs (per
+        // 128 query rows of a head: one, or a cluster of up to 8 that splits the cached tokens) would walk their
+        // tokens for longer than the three launches take, which spread the cached tokens over the whole GPU
+        // (few heads and a very long cache).  The choice is made here because
         // the two paths need different workspaces; infiniopExtSelectKernel(attention, 3 / 4) forces either.
         const int choice = kernel_choice(kFamilyAttention);
         const uint64_t ctas = (uint64_t) ((seq + 127) / 128) * d->nh, kv_tiles = (total + 63) / 64;
