@@ -900,7 +900,9 @@ INFINIOP_API infiniopStatus_t infiniopCreateAttentionDescriptor(infiniopHandle_t
     // (measured, 32 q / 8 kv heads, dh 128: 8 new tokens over 4096 cached 46 us against 29 us for the row-tile kernels,
     // 16 tokens 48 against 40, 64 tokens over 8192 cached 146 against 191, 512 tokens from an empty cache 92 against 115)
     d->fused = nullptr;
-    if (seq >= 32 && d->strides_vec && total > 0) {
+    // (from 16 tokens when the q heads of a kv head can share a block of query rows: 16 tokens over 4096 cached run
+    // faster there than on the row-tile kernels)
+    if (seq >= (d->group > 1 ? 16u : 32u) && d->strides_vec && total > 0) {
         const AttnPrefillShape shape{d->nh, d->group, d->seq, d->dh, d->total, d->q_s0, d->q_s1, d->kc_s0, d->kc_s1, d->vc_s0, d->vc_s1};
         // One kernel that keeps the scores on chip (attention_fused.cu) unless the model says that its CTAs (per
         // 128 query rows of a head: one, or a cluster of up to 8 that splits the cached tokens) would walk their

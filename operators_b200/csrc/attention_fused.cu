@@ -25,6 +25,9 @@
 //   warp 9     allocates TMEM (S twice 64 columns, O dh columns); one lane issues the MMAs.  S of tile j + 2 is
 //              issued before P v of tile j (its buffer is free once S of tile j has been read), so the softmax
 //              warps find their next scores ready.
+// Calls of fewer than 128 tokens with several q heads per kv head: a block holds 128 / group tokens of all q heads
+// of one kv head (row = token * group + head), loaded by one TMA box [tokens][heads][64], so the block is full and k
+// and v are loaded once per kv head.
 // Few blocks of query rows over many cached tokens (a chunk of a prompt, speculative drafts): 2, 4 or 8 CTAs, one
 // thread-block cluster, share a block and each takes a range of its tiles.  After pass 1 they exchange their rows'
 // maximum and sum over distributed shared memory (one mbarrier per CTA that every CTA of the cluster arrives on; the
@@ -57,6 +60,10 @@ struct FusedParams {
     uint32_t nh, group, seq, total, tiles_m;
     uint32_t slots;// k / v tiles of the shared-memory ring (4 when two CTAs share an SM, more for a CTA alone)
     uint32_t splits;// CTAs (one cluster) that share a block of query rows, each with a range of the cached tokens
+    // Rows of a block: 128 tokens of one q head (pack = 1), or, for calls of few tokens, tok tokens of all `pack` q
+    // heads of one kv head (row = token * pack + head within the group), so that the block is full and k / v are
+    // loaded once per kv head.  tiles_m counts the blocks of tokens either way.
+    uint32_t pack, tok;
     float alpha;
     uint16_t *out;// [seq, nh, dh]
 };
@@ -150,10 +157,12 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the longest blocks (last query rows) start first
     const uint32_t S = p.splits, split = S > 1 ? cluster_rank() : 0u, unit = blockIdx.x / S;
-    const uint32_t tm = p.tiles_m - 1 - unit / p.nh, h = unit % p.nh, kvh = h / p.group;
-    const uint32_t row0 = tm * kRows;
-    const uint32_t last_row = min(row0 + kRows - 1, p.seq - 1);
-    const uint32_t tiles_all = (p.total - p.seq + last_row) / kKeys + 1;// tiles that hold a visible column
+    const uint32_t heads = p.pack > 1 ? p.nh / p.group : p.nh;// blocks per block of tokens: kv heads when packed
+    const uint32_t tm = p.tiles_m - 1 - unit / heads, hb = unit % heads;
+    const uint32_t h0 = p.pack > 1 ? hb * p.group : hb, kvh = h0 / p.group;// first (or only) q head of the block
+    const uint32_t tok0 = tm * p.tok;                                       // first token of the block
+    const uint32_t last_tok = min(tok0 + p.tok - 1, p.seq - 1);
+    const uint32_t tiles_all = (p.total - p.seq + last_tok) / kKeys + 1;// tiles that hold a visible column
     // this CTA's share of them (possibly none): its maxima, sums and outputs meet the other CTAs' over distributed
     // shared memory
     const uint32_t t_begin = split * tiles_all / S, tiles = (split + 1) * tiles_all / S - t_begin;
@@ -183,8 +192,12 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
     if (warp == 8) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            mbar_expect_tx(&bars[kQFull], kQBytes);
-            for (int kb = 0; kb < DHB; ++kb) tma_load_3d(sq + kb * (kRows * 128u), &map_q, &bars[kQFull], kb * 64, (int32_t) row0, (int32_t) h);
+            // one box per 64 head elements: [128 tokens] of head h0, or [tok tokens][pack heads] (the map's box)
+            mbar_expect_tx(&bars[kQFull], DHB * p.tok * p.pack * 128u);
+            for (int kb = 0; kb < DHB; ++kb) {
+                if (p.pack > 1) tma_load_3d(sq + kb * (kRows * 128u), &map_q, &bars[kQFull], kb * 64, (int32_t) h0, (int32_t) tok0);
+                else tma_load_3d(sq + kb * (kRows * 128u), &map_q, &bars[kQFull], kb * 64, (int32_t) tok0, (int32_t) h0);
+            }
             // The ring is a queue: tiles are loaded in the order in which the MMA lane uses them.  Pass 1: k(0) ..
             // k(T - 1); pass 2: k(0), k(1), then k(j + 2), v(j) for j = 0 .. T - 1.
             uint32_t slot = 0, ph = 0;
@@ -266,7 +279,9 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         // warp w reads TMEM lanes 32 (w & 3) .. + 31 (the lanes a warp may touch follow from its index) and the
         // columns 32 (w >> 2) .. + 31 of every tile
         const uint32_t quarter = warp & 3u, half = warp >> 2;
-        const uint32_t lane_row = quarter * 32 + lane, row = row0 + lane_row;
+        const uint32_t lane_row = quarter * 32 + lane;
+        const uint32_t row = tok0 + lane_row / p.pack, head = h0 + lane_row % p.pack;// this row's token and q head
+        const bool row_valid = row < p.seq && lane_row < p.tok * p.pack;
         const uint32_t vis_last = p.total - p.seq + row;// last visible column of this row
         const uint32_t t_lane = tmem_base + ((quarter * 32u) << 16);
         float m = -INFINITY, l = 0.f;
@@ -397,7 +412,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         if (S == 1) {
             if (ok && mbar_wait<kSuspendNs>(&bars[kOFull], 0, abort_flag)) {
                 tc_fence_after();
-                uint16_t *orow = p.out + ((size_t) row * p.nh + h) * (DHB * 64) + half * kCols;
+                uint16_t *orow = p.out + ((size_t) row * p.nh + head) * (DHB * 64) + half * kCols;
 #pragma unroll
                 for (uint32_t c0 = 0; c0 < kCols; c0 += 16) {
                     float acc[16];
@@ -405,7 +420,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
                     uint32_t o[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) o[i] = pack2_ref(acc[2 * i], acc[2 * i + 1]);
-                    if (row < p.seq) {
+                    if (row_valid) {
                         uint4 *dst = reinterpret_cast<uint4 *>(orow + c0);
                         dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
                         dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
@@ -450,8 +465,9 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
                         const float4 v = ld_cluster_f4(mapa_u32(addr, c));
                         sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
                     }
-                    if (row0 + r < p.seq) {
-                        uint2 *dst = reinterpret_cast<uint2 *>(p.out + ((size_t) (row0 + r) * p.nh + h) * (DHB * 64) + g * 4);
+                    const uint32_t tok = tok0 + r / p.pack;
+                    if (tok < p.seq && r < p.tok * p.pack) {
+                        uint2 *dst = reinterpret_cast<uint2 *>(p.out + ((size_t) tok * p.nh + h0 + r % p.pack) * (DHB * 64) + g * 4);
                         *dst = make_uint2(pack2_ref(sum.x, sum.y), pack2_ref(sum.z, sum.w));
                     }
                 }
@@ -495,7 +511,7 @@ uint32_t fused_slots(uint32_t dhb, size_t budget) {
 struct AttnFused {
     int device_id;
     AttnPrefillShape shape;
-    uint32_t dhb, tiles_m, slots, splits;
+    uint32_t dhb, tiles_m, slots, splits, pack, tok;
     size_t smem_bytes;
     std::mutex mu;
     bool valid = false;
@@ -503,11 +519,21 @@ struct AttnFused {
     CUtensorMap map_q, map_k, map_v;
 };
 
+// Blocks of query rows: few tokens per call and several q heads per kv head -> the heads of a group share a block.
+static void fused_blocks(const AttnPrefillShape &s, uint32_t &pack, uint32_t &tok, uint64_t &blocks) {
+    pack = (s.group > 1 && s.group <= kRows && s.seq < kRows) ? s.group : 1u;
+    tok = kRows / pack;
+    blocks = (uint64_t) ((s.seq + tok - 1) / tok) * (pack > 1 ? s.nh / s.group : s.nh);
+}
+
 static bool encode_maps(AttnFused *f, const void *q, const void *k_cache, const void *v_cache) {
     const AttnPrefillShape &s = f->shape;
     const uint32_t nkvh = s.nh / s.group;
     // rows beyond seq / total read as zeros: the caches' unused rows are never touched
-    return tc_encode_tiles_f16(&f->map_q, q, s.dh, s.seq, s.nh, (uint64_t) s.q_s1 * 2, (uint64_t) s.q_s0 * 2, kRows) &&
+    const bool q_ok = f->pack > 1
+        ? tc_encode_tiles_f16(&f->map_q, q, s.dh, s.nh, s.seq, (uint64_t) s.q_s0 * 2, (uint64_t) s.q_s1 * 2, f->pack, f->tok)
+        : tc_encode_tiles_f16(&f->map_q, q, s.dh, s.seq, s.nh, (uint64_t) s.q_s1 * 2, (uint64_t) s.q_s0 * 2, kRows);
+    return q_ok &&
            tc_encode_tiles_f16(&f->map_k, k_cache, s.dh, s.total, nkvh, (uint64_t) s.kc_s1 * 2, (uint64_t) s.kc_s0 * 2, kKeys) &&
            tc_encode_tiles_f16(&f->map_v, v_cache, s.dh, s.total, nkvh, (uint64_t) s.vc_s1 * 2, (uint64_t) s.vc_s0 * 2, kKeys);
 }
@@ -515,7 +541,10 @@ static bool encode_maps(AttnFused *f, const void *q, const void *k_cache, const 
 // Few blocks of query rows over many cached tokens: 2, 4 or 8 CTAs (one cluster) share a block and split its tokens,
 // as long as all CTAs still run at once (two per SM) and every CTA keeps at least four tiles.
 uint32_t attn_fused_splits(const AttnPrefillShape &s, int sm_count) {
-    const uint64_t ctas = (uint64_t) ((s.seq + kRows - 1) / kRows) * s.nh, kv_tiles = (s.total + kKeys - 1) / kKeys;
+    uint32_t pack, tok;
+    uint64_t ctas;
+    fused_blocks(s, pack, tok, ctas);
+    const uint64_t kv_tiles = (s.total + kKeys - 1) / kKeys;
     uint32_t splits = 1;
     while (splits < kMaxSplits && ctas * splits * 2 <= 2ull * (uint64_t) sm_count && kv_tiles >= 8ull * splits) splits *= 2;
     return splits;
@@ -531,8 +560,11 @@ AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s)
     }
     if (s.q_s1 < (int64_t) s.dh || s.kc_s1 < (int64_t) s.dh || s.vc_s1 < (int64_t) s.dh) return nullptr;
     const uint32_t dhb = s.dh / 64;
-    const uint64_t tiles_m = (s.seq + kRows - 1) / kRows;
-    if (tiles_m * s.nh > 0x7FFFFFFFull) return nullptr;
+    uint32_t pack, tok;
+    uint64_t blocks;
+    fused_blocks(s, pack, tok, blocks);
+    const uint64_t tiles_m = (s.seq + tok - 1) / tok;
+    if (blocks > 0x7FFFFFFull) return nullptr;
     // A grid that leaves every CTA an SM of its own gets the whole shared memory for its ring of k / v tiles (the
     // loads of up to 11 tiles in flight hide the latency one CTA sees); otherwise two CTAs share an SM and each
     // takes half (4 tiles at dh 128), less the kilobyte the system keeps per CTA.
@@ -544,7 +576,10 @@ AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s)
     const uint32_t slots_alone = fused_slots(dhb, (size_t) h->max_smem_optin);
     const uint32_t slots_shared = fused_slots(dhb, (size_t) sm_bytes / 2 - 1024);
     const uint32_t splits = attn_fused_splits(s, h->sm_count);
-    const uint32_t slots = tiles_m * s.nh * splits <= (uint64_t) h->sm_count ? slots_alone : slots_shared;
+    // (clusters: only while half the SMs suffice.  A cluster must find all its SMs in one GPC, and 16 clusters of
+    // 8 CTAs with an SM each did not fit the GPCs at once: 86 us against 47 us with two CTAs per SM)
+    const bool alone = blocks * splits <= (uint64_t) h->sm_count / (splits > 1 ? 2 : 1);
+    const uint32_t slots = alone ? slots_alone : slots_shared;
     if (slots == 0 || slots_alone == 0) return nullptr;
     const size_t smem = fused_smem_bytes(dhb, slots);
     auto *kernel = dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
@@ -558,6 +593,7 @@ AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s)
     f->device_id = h->device_id;
     f->shape = s;
     f->dhb = dhb, f->tiles_m = (uint32_t) tiles_m, f->slots = slots, f->splits = splits, f->smem_bytes = smem;
+    f->pack = pack, f->tok = tok;
     // the encoder checks extents and strides, not the memory: a trial with a placeholder address tells now whether
     // these layouts can be described, so that the caller can keep its other path
     const void *probe = reinterpret_cast<const void *>((uintptr_t) 1 << 20);
@@ -585,10 +621,10 @@ infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const vo
     }
     FusedParams p{};
     p.nh = s.nh, p.group = s.group, p.seq = s.seq, p.total = s.total, p.tiles_m = f->tiles_m, p.slots = f->slots;
-    p.splits = f->splits;
+    p.splits = f->splits, p.pack = f->pack, p.tok = f->tok;
     p.alpha = (float) (1.0 / sqrt((double) s.dh));// `float qk_alpha = 1 / sqrt(head_dim)`, operator.cc:136
     p.out = reinterpret_cast<uint16_t *>(out);
-    const uint32_t grid = f->tiles_m * s.nh * f->splits;
+    const uint32_t grid = f->tiles_m * (f->pack > 1 ? s.nh / s.group : s.nh) * f->splits;
     auto *kernel = f->dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
     if (f->splits == 1) {
         kernel<<<grid, kFusedThreads, f->smem_bytes, st>>>(mq, mk, mv, p);

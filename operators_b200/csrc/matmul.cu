@@ -194,12 +194,12 @@ uint32_t *counter_pool_address(int device) {
 namespace b200 {
 
 bool tc_encode_tiles_f16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t batch,
-                         uint64_t outer_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_outer) {
+                         uint64_t outer_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_outer, uint32_t box_batch) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return false;
     cuuint64_t dims[3] = {inner, outer, batch};
     cuuint64_t strides[2] = {outer_stride_bytes, batch_stride_bytes};
-    cuuint32_t box[3] = {64, box_outer, 1};
+    cuuint32_t box[3] = {64, box_outer, box_batch};
     cuuint32_t estr[3] = {1, 1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

@@ -60,9 +60,9 @@ void matmul_plan_destroy(MatmulPlan &plan);
 infiniopStatus_t matmul_plan_run(MatmulPlan &plan, TcMapCache &cache, void *workspace, uint64_t workspace_size, void *c,
                                  const void *a, const void *b, cudaStream_t stream);
 // Tensor map of an fp16 tensor [batch][outer][inner] (inner contiguous, byte strides multiples of 16) read in boxes of
-// 64 x box_outer elements into 128-byte-swizzled shared memory; elements outside the extents read as zero.
+// 64 x box_outer (x box_batch) elements into 128-byte-swizzled shared memory; elements outside the extents read as zero.
 bool tc_encode_tiles_f16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t batch,
-                         uint64_t outer_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_outer);
+                         uint64_t outer_stride_bytes, uint64_t batch_stride_bytes, uint32_t box_outer, uint32_t box_batch = 1);
 // Waits that ran out of time inside the tensor-core kernel since the library was loaded (synchronises).
 unsigned long long tc_gemm_timeouts_read();
 

@@ -983,6 +983,12 @@ ATTENTION_CASES = [
     (32, 4, 200, 64, 100, 2048, (64, 2560, 1), (64, 11264, 1)),
     (4, 2, 128, 128, 0, 128, None, None),
     (4, 1, 256, 64, 64, 320, None, None),
+    # 16 .. 127 new tokens with several q heads per kv head: the heads of a group share a block of 128 query rows
+    # (groups of 4, 3 and 8; the reference's strided layouts; a block that the tokens do not fill)
+    (32, 8, 16, 128, 500, 600, None, None),
+    (12, 4, 40, 64, 300, 400, None, None),
+    (16, 2, 20, 128, 70, 128, None, None),
+    (32, 4, 50, 64, 100, 2048, (64, 2560, 1), (64, 11264, 1)),
 ]
 
 
@@ -1010,8 +1016,8 @@ def test_attention(oracle, cuda_lib, attention_kernels, nh, nkvh, seq, dh, pos, 
     differs, so most elements are the same bit pattern); both caches byte for byte,
     rows outside pos .. pos+seq untouched."""
     lib, handle = cuda_lib
-    if attention_kernels in ("three_launches", "one_kernel") and seq < 32:
-        pytest.skip("fewer than 32 new tokens never take the tcgen05 forms")
+    if attention_kernels in ("three_launches", "one_kernel") and seq < (16 if nh > nkvh else 32):
+        pytest.skip("fewer than 32 new tokens (16 with several q heads per kv head) never take the tcgen05 forms")
     timeouts_before = ops.device_timeouts(lib, handle)  # counts since the library was loaded
     g = torch.Generator().manual_seed(21)
     q = torch.randn((nh, seq, dh), generator=g).half()
