@@ -375,7 +375,7 @@ def only_attention(lib, handle, dev, steps, warmup):
             "note": "back-to-back calls of one operator; bytes = K and V rows read once; not a bench value"}
 
 
-PREFILL_CASE = {"new_tokens": None}  # --new-tokens: one case only (ncu captures)
+PREFILL_CASE = {"new_tokens": None, "cached_tokens": 0}  # --new-tokens / --cached-tokens: one case only (ncu captures)
 
 
 def only_attention_prefill(lib, handle, dev, steps, warmup):
@@ -389,7 +389,7 @@ def only_attention_prefill(lib, handle, dev, steps, warmup):
     peak = measured_tflops()
     cases = {}
     for seq, pos in ((512, 0), (2048, 0), (4096, 0), (512, 32768), (64, 8192)):
-        if PREFILL_CASE["new_tokens"] is not None and (PREFILL_CASE["new_tokens"] != seq or pos != 0):
+        if PREFILL_CASE["new_tokens"] is not None and (PREFILL_CASE["new_tokens"], PREFILL_CASE["cached_tokens"]) != (seq, pos):
             continue
         total = pos + seq
         q = torch.randn((nh, seq, dh), device=dev).half()
@@ -1188,10 +1188,12 @@ def main():
                     help="force a kernel family for this run (infiniopExtSelectKernel), e.g. rope=2; for comparisons")
     ap.add_argument("--tokens", type=int, choices=[SWI_T, 16, 1], help="with --only matmul: this token count only")
     ap.add_argument("--weights", choices=["k_contiguous", "n_contiguous"], help="with --only matmul: this weight layout only")
-    ap.add_argument("--new-tokens", type=int, choices=[512, 2048, 4096], help="with --only attention_prefill: this prompt length only")
+    ap.add_argument("--new-tokens", type=int, choices=[64, 512, 2048, 4096], help="with --only attention_prefill: this case only")
+    ap.add_argument("--cached-tokens", type=int, choices=[0, 8192, 32768], default=0,
+                    help="with --only attention_prefill --new-tokens: the case with this many tokens already cached")
     args = ap.parse_args()
     MATMUL_CASE["tokens"], MATMUL_CASE["weights"] = args.tokens, args.weights
-    PREFILL_CASE["new_tokens"] = args.new_tokens
+    PREFILL_CASE["new_tokens"], PREFILL_CASE["cached_tokens"] = args.new_tokens, args.cached_tokens
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)

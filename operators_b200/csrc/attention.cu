@@ -911,7 +911,7 @@ INFINIOP_API infiniopStatus_t infiniopCreateAttentionDescriptor(infiniopHandle_t
         // the two paths need different workspaces; infiniopExtSelectKernel(attention, 3 / 4) forces either.
         const int choice = kernel_choice(kFamilyAttention);
         const uint64_t ctas = (uint64_t) ((seq + 127) / 128) * d->nh, kv_tiles = (total + 63) / 64;
-        const uint32_t splits = attn_fused_splits(shape, d->sm_count);// CTAs of a cluster that share a block of query rows
+        const uint32_t splits = attn_fused_splits(shape, d->sm_count, d->device_id);// CTAs of a cluster that share a block of query rows
         const double one_us = kFusedUsFixed + kFusedUsPerTile * (double) ((kv_tiles + splits - 1) / splits) + (splits > 1 ? 6.0 : 0.0);
         const double three_us = kThreeUsFixed + kThreeUsPerScore * (double) d->nh * (double) seq * (double) total;
         if (choice == 4 || (choice != 3 && (ctas > (uint64_t) d->sm_count || one_us < three_us))) {

@@ -456,8 +456,9 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
             }
             if (ok) ok = mbar_wait_cluster(&bars[kOStaged], 0, abort_flag);
             if (ok) {
-                const uint32_t rows_per = kRows / S, r_first = split * rows_per;
-                for (uint32_t idx = threadIdx.x; idx < rows_per * kGroups; idx += kSoftmaxThreads) {
+                const uint32_t rows_per = (kRows + S - 1) / S, r_first = min(split * rows_per, kRows);
+                const uint32_t rows_mine = min(rows_per, kRows - r_first);
+                for (uint32_t idx = threadIdx.x; idx < rows_mine * kGroups; idx += kSoftmaxThreads) {
                     const uint32_t r = r_first + idx / kGroups, g = idx % kGroups;
                     const uint32_t addr = smem_u32(&stage[r * kGroups + (g ^ (r & (kGroups - 1)))]);
                     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -538,15 +539,47 @@ static bool encode_maps(AttnFused *f, const void *q, const void *k_cache, const 
            tc_encode_tiles_f16(&f->map_v, v_cache, s.dh, s.total, nkvh, (uint64_t) s.vc_s1 * 2, (uint64_t) s.vc_s0 * 2, kKeys);
 }
 
-// Few blocks of query rows over many cached tokens: 2, 4 or 8 CTAs (one cluster) share a block and split its tokens,
-// as long as all CTAs still run at once (two per SM) and every CTA keeps at least four tiles.
-uint32_t attn_fused_splits(const AttnPrefillShape &s, int sm_count) {
+// Few blocks of query rows over many cached tokens: up to 8 CTAs (one cluster) share a block and split its tokens, as
+// long as all CTAs still run at once (two per SM) and every CTA keeps at least four tiles.  Doubling finds the size;
+// when the hardware cannot hold that many clusters of that size at once (a cluster needs its SMs in one GPC: 15
+// clusters of 8 CTAs, where 16 blocks wanted 16), a slightly smaller cluster that runs them all in one go is better
+// than a second round.
+uint32_t attn_fused_splits(const AttnPrefillShape &s, int sm_count, int device_id) {
     uint32_t pack, tok;
     uint64_t ctas;
     fused_blocks(s, pack, tok, ctas);
     const uint64_t kv_tiles = (s.total + kKeys - 1) / kKeys;
     uint32_t splits = 1;
     while (splits < kMaxSplits && ctas * splits * 2 <= 2ull * (uint64_t) sm_count && kv_tiles >= 8ull * splits) splits *= 2;
+    if (splits <= 2 || (s.dh != 64 && s.dh != 128)) return splits;
+    DeviceGuard guard(device_id);
+    int sm_bytes = 0;
+    if (cudaDeviceGetAttribute(&sm_bytes, cudaDevAttrMaxSharedMemoryPerMultiprocessor, device_id) != cudaSuccess) {
+        cudaGetLastError();
+        return splits;
+    }
+    const uint32_t dhb = s.dh / 64;
+    auto *kernel = dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
+    for (uint32_t c = splits; c > splits / 2; --c) {
+        const bool alone = ctas * c <= (uint64_t) sm_count / 2;
+        const uint32_t slots = alone ? fused_slots(dhb, (size_t) sm_bytes - 1024) : fused_slots(dhb, (size_t) sm_bytes / 2 - 1024);
+        if (slots == 0) break;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned) (ctas * c));
+        cfg.blockDim = dim3(kFusedThreads);
+        cfg.dynamicSmemBytes = fused_smem_bytes(dhb, slots);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = c, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr, cfg.numAttrs = 1;
+        int active = 0;
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) cfg.dynamicSmemBytes) != cudaSuccess ||
+            cudaOccupancyMaxActiveClusters(&active, kernel, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            return splits;
+        }
+        if ((uint64_t) active >= ctas) return c;
+    }
     return splits;
 }
 
@@ -575,7 +608,7 @@ AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s)
     }
     const uint32_t slots_alone = fused_slots(dhb, (size_t) h->max_smem_optin);
     const uint32_t slots_shared = fused_slots(dhb, (size_t) sm_bytes / 2 - 1024);
-    const uint32_t splits = attn_fused_splits(s, h->sm_count);
+    const uint32_t splits = attn_fused_splits(s, h->sm_count, h->device_id);
     // (clusters: only while half the SMs suffice.  A cluster must find all its SMs in one GPC, and 16 clusters of
     // 8 CTAs with an SM each did not fit the GPCs at once: 86 us against 47 us with two CTAs per SM)
     const bool alone = blocks * splits <= (uint64_t) h->sm_count / (splits > 1 ? 2 : 1);

@@ -26,7 +26,7 @@ infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const vo
                                 cudaStream_t stream);
 void attn_fused_destroy(AttnFused *f);
 // CTAs (one cluster) that share a block of 128 query rows of this shape, each with a range of the cached tokens.
-uint32_t attn_fused_splits(const AttnPrefillShape &shape, int sm_count);
+uint32_t attn_fused_splits(const AttnPrefillShape &shape, int sm_count, int device_id);
 // Waits that ran out of time inside the fused kernel since the library was loaded (synchronises); ~0 on error.
 unsigned long long attn_fused_timeouts_read();
 
