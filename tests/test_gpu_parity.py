@@ -1097,10 +1097,10 @@ def test_attention_long_prefill_against_float32(cuda_lib, nh, nkvh, seq, dh, pos
     assert float(err.max()) < 4e-3 + 4e-3 * float(want.abs().max())
 
 
-@pytest.mark.parametrize("seq,pos", [(1, 3000), (160, 100)])
+@pytest.mark.parametrize("seq,pos", [(1, 3000), (160, 100), (40, 3000)])
 def test_attention_captures_into_a_cuda_graph(oracle, cuda_lib, seq, pos):
-    """The launches of one call (decoding: two; a prompt: the cache append and the one-kernel form) neither allocate
-    nor synchronise: captured after one eager call (one-time kernel attribute set-up), replayed on a cleared output
+    """The launches of one call (decoding: two; a prompt: the cache append and the one-kernel form; a short chunk over
+    a long prefix: the same as a cluster launch) neither allocate nor synchronise: captured after one eager call (one-time kernel attribute set-up), replayed on a cleared output
     and workspace."""
     lib, handle = cuda_lib
     g = torch.Generator().manual_seed(31)
