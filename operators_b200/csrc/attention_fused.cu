@@ -69,6 +69,7 @@ struct FusedParams {
 };
 
 constexpr uint32_t kMaxSlots = 16;// k / v tiles in flight per CTA
+constexpr float kExactFrom = 1024.f;// row maxima from here on: x - max formed before the multiplication by log2(e)
 constexpr uint32_t kMaxSplits = 8;// CTAs of a cluster that share a block of query rows (the portable cluster size)
 // Waiting roles sleep in the barrier instead of polling: twenty warps share an SM and the exponentials need the issue
 // slots (polling producer and MMA lanes took four of ten issued instructions).
@@ -318,16 +319,29 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
             for (int i = 0; i < 4; ++i) t8[i] = hmax2_u32(t8[i], t8[i + 4]);
             const float2 mt = unpack2(hmax2_u32(hmax2_u32(t8[0], t8[1]), hmax2_u32(t8[2], t8[3])));
             const float m_new = fmaxf(m, fmaxf(mt.x, mt.y));
+            // exp(x - m) as 2^(x log2e - m log2e) in one multiply-add: the product m log2e is rounded, an error of
+            // |m| 2^-24 in the exponent, nothing for ordinary scores; a warp that holds a row with a maximum beyond
+            // kExactFrom forms x - m first (exact: both are fp16 values), one more instruction per score
+            const bool far = __any_sync(0xffffffffu, m_new != -INFINITY && fabsf(m_new) >= kExactFrom);
             if (m_new != -INFINITY) {// else: all of this thread's columns so far are masked
-                const float mk = -m_new * kLog2e;
                 float part[4] = {0.f, 0.f, 0.f, 0.f};
+                if (!far) {
+                    const float mk = -m_new * kLog2e;
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float2 f = unpack2(w[i]);
-                    part[(2 * i) & 3] += fast_exp2(fmaf(f.x, kLog2e, mk));
-                    part[(2 * i + 1) & 3] += fast_exp2(fmaf(f.y, kLog2e, mk));
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 f = unpack2(w[i]);
+                        part[(2 * i) & 3] += fast_exp2(fmaf(f.x, kLog2e, mk));
+                        part[(2 * i + 1) & 3] += fast_exp2(fmaf(f.y, kLog2e, mk));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float2 f = unpack2(w[i]);
+                        part[(2 * i) & 3] += fast_exp2((f.x - m_new) * kLog2e);
+                        part[(2 * i + 1) & 3] += fast_exp2((f.y - m_new) * kLog2e);
+                    }
                 }
-                const float scale = m == -INFINITY ? 0.f : fast_exp2(fmaf(m, kLog2e, mk));
+                const float scale = m == -INFINITY ? 0.f : fast_exp2((m - m_new) * kLog2e);
                 l = fmaf(l, scale, (part[0] + part[1]) + (part[2] + part[3]));
                 m = m_new;
             }
@@ -341,9 +355,9 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
             const float2 o = ml[(half ^ 1u) * kRows + lane_row];
             // (column 0 is visible to every row, so the maximum is finite in the CTA that holds tile 0; a CTA whose
             // tiles are all masked for a row, or that has no tiles, carries -inf and 0)
-            const float m_all = fmaxf(m, o.x), mk_all = -m_all * kLog2e;
-            const float mine = m == -INFINITY ? 0.f : l * fast_exp2(fmaf(m, kLog2e, mk_all));
-            const float theirs = o.x == -INFINITY ? 0.f : o.y * fast_exp2(fmaf(o.x, kLog2e, mk_all));
+            const float m_all = fmaxf(m, o.x);
+            const float mine = m == -INFINITY ? 0.f : l * fast_exp2((m - m_all) * kLog2e);
+            const float theirs = o.x == -INFINITY ? 0.f : o.y * fast_exp2((o.x - m_all) * kLog2e);
             l = half == 0 ? mine + theirs : theirs + mine;// the same sum in both threads
             m = m_all;
         }
@@ -365,11 +379,10 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
                     part[r] = r < S ? ld_cluster_f2(mapa_u32(mine_addr, r)) : make_float2(-INFINITY, 0.f);
                     m_all = fmaxf(m_all, part[r].x);
                 }
-                const float mk_all = -m_all * kLog2e;
                 float l_all = 0.f;
 #pragma unroll
                 for (uint32_t r = 0; r < kMaxSplits; ++r) {
-                    if (part[r].x != -INFINITY) l_all += part[r].y * fast_exp2(fmaf(part[r].x, kLog2e, mk_all));
+                    if (part[r].x != -INFINITY) l_all += part[r].y * fast_exp2((part[r].x - m_all) * kLog2e);
                 }
                 m = m_all, l = l_all;
             }
@@ -381,16 +394,27 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
             if (ok) ok = mbar_wait_cluster(&bars[kStatsRead], 0, abort_flag);
         }
         asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");// the exchange area becomes P again
-        // exp(x - m) / l as one exponential: 2^(x log2e - m log2e - log2 l)
-        const float mk = fmaf(-m, kLog2e, -log2f(l));
+        // exp(x - m) / l as one exponential: 2^(x log2e - m log2e - log2 l), or 2^((x - m) log2e - log2 l) for a warp that
+        // holds a row with a distant maximum (see pass 1)
+        const float log2l = log2f(l), mk = fmaf(-m, kLog2e, -log2l);
+        const bool far = __any_sync(0xffffffffu, fabsf(m) >= kExactFrom);
 #pragma unroll 1
         for (uint32_t j = 0; ok && j < tiles; ++j) {// pass 2: probabilities into shared memory for P v
             if (!(ok = load_scores(tiles + j, t_begin + j, std::false_type{}))) break;
             TRACE_NOW(ta);
+            if (!far) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float2 f = unpack2(w[i]);
-                asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(fast_exp2(fmaf(f.y, kLog2e, mk))), "f"(fast_exp2(fmaf(f.x, kLog2e, mk))));
+                for (int i = 0; i < 16; ++i) {
+                    const float2 f = unpack2(w[i]);
+                    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(w[i]) : "f"(fast_exp2(fmaf(f.y, kLog2e, mk))), "f"(fast_exp2(fmaf(f.x, kLog2e, mk))));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float2 f = unpack2(w[i]);
+                    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(w[i])
+                        : "f"(fast_exp2(fmaf(f.y - m, kLog2e, -log2l))), "f"(fast_exp2(fmaf(f.x - m, kLog2e, -log2l))));
+                }
             }
             TRACE_NOW(tb);
             if (!(ok = mbar_wait<kSuspendNs>(&bars[kPEmpty], (j & 1u) ^ 1u, abort_flag))) break;

@@ -1057,6 +1057,32 @@ def test_attention(oracle, cuda_lib, attention_kernels, nh, nkvh, seq, dh, pos, 
 
 
 @pytest.mark.parametrize("kernels", ["three_launches", "one_kernel"])
+def test_attention_scores_at_the_top_of_the_fp16_range(oracle, cuda_lib, kernels):
+    """q = k = 90.5 in every element: alpha * q.k = 65522, which the reference's truncating rule stores as the largest
+    finite fp16 (65504).  The one-kernel form converts scores two at a time with a saturating instruction and
+    redoes a chunk element by element when it sees that value; this is the case that takes that path (and the row
+    of equal scores makes every probability 1 / visible columns)."""
+    lib, handle = cuda_lib
+    nh, nkvh, seq, dh, pos = 4, 2, 40, 64, 30
+    g = torch.Generator().manual_seed(29)
+    q = torch.full((nh, seq, dh), 90.5).half()
+    k = torch.full((nkvh, seq, dh), 90.5).half()
+    v = torch.randn((nkvh, seq, dh), generator=g).half()
+    kc = torch.full((nkvh, pos + seq, dh), 90.5).half()
+    vc = torch.randn((nkvh, pos + seq, dh), generator=g).half()
+    want = oracle.attention(q.numpy(), k.numpy(), v.numpy(), kc.numpy().copy(), vc.numpy().copy(), pos)
+    assert np.isfinite(want.astype(np.float32)).all()
+    out = torch.zeros((seq, nh, dh), dtype=torch.float16, device=DEV)
+    ops.select_kernel(lib, "attention", ATTENTION_KERNELS[kernels])
+    try:
+        ops.attention(lib, handle, out, q.to(DEV), k.to(DEV), v.to(DEV), kc.to(DEV), vc.to(DEV), pos)
+        torch.cuda.synchronize()
+    finally:
+        ops.select_kernel(lib, "attention", 0)
+    _close(_bits(out).reshape(want.shape), want, 1e-3, 1e-3)
+
+
+@pytest.mark.parametrize("kernels", ["three_launches", "one_kernel"])
 @pytest.mark.parametrize("nh,nkvh,seq,dh,pos", [(8, 2, 1024, 128, 0), (8, 4, 600, 64, 1000), (4, 1, 1536, 128, 512),
                                                 (16, 4, 2048, 128, 0),
                                                 # few blocks of query rows: clusters of CTAs split the cached tokens (the
