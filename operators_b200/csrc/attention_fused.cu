@@ -58,6 +58,7 @@ constexpr uint32_t kMinSmem = 80 * 1024;// keeps a third CTA (and its TMEM reque
 
 struct FusedParams {
     uint32_t nh, group, seq, total, tiles_m;
+    uint32_t dh;// head size, a multiple of 8 up to 64 * DHB: the boxes read the elements beyond it as zeros
     uint32_t slots;// k / v tiles of the shared-memory ring (4 when two CTAs share an SM, more for a CTA alone)
     uint32_t splits;// CTAs (one cluster) that share a block of query rows, each with a range of the cached tokens
     // Rows of a block: 128 tokens of one q head (pack = 1), or, for calls of few tokens, tok tokens of all `pack` q
@@ -436,7 +437,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         if (S == 1) {
             if (ok && mbar_wait<kSuspendNs>(&bars[kOFull], 0, abort_flag)) {
                 tc_fence_after();
-                uint16_t *orow = p.out + ((size_t) row * p.nh + head) * (DHB * 64) + half * kCols;
+                uint16_t *orow = p.out + ((size_t) row * p.nh + head) * p.dh + half * kCols;
 #pragma unroll
                 for (uint32_t c0 = 0; c0 < kCols; c0 += 16) {
                     float acc[16];
@@ -444,10 +445,10 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
                     uint32_t o[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) o[i] = pack2_ref(acc[2 * i], acc[2 * i + 1]);
-                    if (row_valid) {
+                    if (row_valid) {// (columns beyond dh are the zero padding of v)
                         uint4 *dst = reinterpret_cast<uint4 *>(orow + c0);
-                        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-                        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                        if (half * kCols + c0 < p.dh) dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                        if (half * kCols + c0 + 8 < p.dh) dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
                     }
                 }
             }
@@ -491,8 +492,8 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
                         sum.x += v.x, sum.y += v.y, sum.z += v.z, sum.w += v.w;
                     }
                     const uint32_t tok = tok0 + r / p.pack;
-                    if (tok < p.seq && r < p.tok * p.pack) {
-                        uint2 *dst = reinterpret_cast<uint2 *>(p.out + ((size_t) tok * p.nh + h0 + r % p.pack) * (DHB * 64) + g * 4);
+                    if (tok < p.seq && r < p.tok * p.pack && g * 4 < p.dh) {
+                        uint2 *dst = reinterpret_cast<uint2 *>(p.out + ((size_t) tok * p.nh + h0 + r % p.pack) * p.dh + g * 4);
                         *dst = make_uint2(pack2_ref(sum.x, sum.y), pack2_ref(sum.z, sum.w));
                     }
                 }
@@ -575,14 +576,14 @@ uint32_t attn_fused_splits(const AttnPrefillShape &s, int sm_count, int device_i
     const uint64_t kv_tiles = (s.total + kKeys - 1) / kKeys;
     uint32_t splits = 1;
     while (splits < kMaxSplits && ctas * splits * 2 <= 2ull * (uint64_t) sm_count && kv_tiles >= 8ull * splits) splits *= 2;
-    if (splits <= 2 || (s.dh != 64 && s.dh != 128)) return splits;
+    if (splits <= 2 || s.dh % 8 != 0 || s.dh > 128) return splits;
     DeviceGuard guard(device_id);
     int sm_bytes = 0;
     if (cudaDeviceGetAttribute(&sm_bytes, cudaDevAttrMaxSharedMemoryPerMultiprocessor, device_id) != cudaSuccess) {
         cudaGetLastError();
         return splits;
     }
-    const uint32_t dhb = s.dh / 64;
+    const uint32_t dhb = (s.dh + 63) / 64;
     auto *kernel = dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
     for (uint32_t c = splits; c > splits / 2; --c) {
         const bool alone = ctas * c <= (uint64_t) sm_count / 2;
@@ -609,14 +610,16 @@ uint32_t attn_fused_splits(const AttnPrefillShape &s, int sm_count, int device_i
 
 AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s) {
     auto *h = reinterpret_cast<Handle *>(handle);
-    if (s.dh != 64 && s.dh != 128) return nullptr;
+    // head sizes that are whole 16-byte vectors, up to 128: the TMA boxes are 64 elements wide and read what lies
+    // beyond the head size as zeros, which changes neither q k^T nor the first dh columns of P v
+    if (s.dh % 8 != 0 || s.dh == 0 || s.dh > 128) return nullptr;
     if (s.seq == 0 || s.total < s.seq || s.group == 0 || s.nh % s.group != 0) return nullptr;
     // TMA: strides in bytes are multiples of 16 and positive, rows do not overlap
     for (int64_t st : {s.q_s0, s.q_s1, s.kc_s0, s.kc_s1, s.vc_s0, s.vc_s1}) {
         if (st <= 0 || st % 8 != 0 || st >= ((int64_t) 1 << 38)) return nullptr;
     }
     if (s.q_s1 < (int64_t) s.dh || s.kc_s1 < (int64_t) s.dh || s.vc_s1 < (int64_t) s.dh) return nullptr;
-    const uint32_t dhb = s.dh / 64;
+    const uint32_t dhb = (s.dh + 63) / 64;
     uint32_t pack, tok;
     uint64_t blocks;
     fused_blocks(s, pack, tok, blocks);
@@ -678,6 +681,7 @@ infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const vo
     }
     FusedParams p{};
     p.nh = s.nh, p.group = s.group, p.seq = s.seq, p.total = s.total, p.tiles_m = f->tiles_m, p.slots = f->slots;
+    p.dh = s.dh;
     p.splits = f->splits, p.pack = f->pack, p.tok = f->tok;
     p.alpha = (float) (1.0 / sqrt((double) s.dh));// `float qk_alpha = 1 / sqrt(head_dim)`, operator.cc:136
     p.out = reinterpret_cast<uint16_t *>(out);

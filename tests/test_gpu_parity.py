@@ -989,6 +989,10 @@ ATTENTION_CASES = [
     (12, 4, 40, 64, 300, 400, None, None),
     (16, 2, 20, 128, 70, 128, None, None),
     (32, 4, 50, 64, 100, 2048, (64, 2560, 1), (64, 11264, 1)),
+    # head sizes between the 64-element boxes of the tcgen05 kernel (the boxes read the rest as zeros)
+    (12, 4, 48, 80, 200, 256, None, None),
+    (4, 4, 150, 96, 30, 256, None, None),
+    (8, 2, 40, 40, 1000, 1100, None, None),
 ]
 
 
