@@ -53,7 +53,9 @@ constexpr int kSoftmaxThreads = 256;                 // two threads per query ro
 constexpr int kFusedThreads = kSoftmaxThreads + 64;  // + the warp that loads and the warp that issues the MMAs
 constexpr uint32_t kRows = 128;// query rows per CTA = TMEM lanes
 constexpr uint32_t kKeys = 64; // cached tokens per tile: one 128-byte swizzle row of P
-constexpr uint32_t kTmemCols = 256;// S0 [0, 64), S1 [64, 128), O [128, 128 + dh)
+// TMEM columns: S0 [0, 64), S1 [64, 128), O [128, 128 + 64 * DHB); a power of two, so 256 up to dh 128 (two CTAs per
+// SM) and all 512 beyond (one CTA per SM)
+__host__ __device__ constexpr uint32_t tmem_cols(int dhb) { return dhb <= 2 ? 256u : 512u; }
 constexpr uint32_t kMinSmem = 80 * 1024;// keeps a third CTA (and its TMEM request) off the SM
 
 struct FusedParams {
@@ -182,7 +184,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
         prefetch_tensormap(&map_v);
     }
     if (warp == 9) {
-        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_alloc(tmem_slot, tmem_cols(DHB));
         tmem_relinquish();
     }
     tc_fence_before();
@@ -454,7 +456,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
             }
         } else {
             // Every CTA parks its fp32 partial of O in its shared memory (q and the ring are idle by now; row r's
-            // 16-byte groups at position g ^ (r % groups), so that a warp's stores spread over the banks), the
+            // 16-byte groups at position g ^ (r % 16), so that a warp's stores spread over the banks), the
             // cluster meets, and CTA `split` adds rows [split * 128 / S, ...) of all partials in rank order,
             // truncates and stores them.
             constexpr uint32_t kGroups = DHB * 16;// float4 groups per row
@@ -470,7 +472,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
                         const uint32_t g = (half * kCols + c0) / 4 + i;
-                        stage[lane_row * kGroups + (g ^ (lane_row & (kGroups - 1)))] =
+                        stage[lane_row * kGroups + (g ^ (lane_row & 15u))] =
                             have ? make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]) : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
                 }
@@ -485,7 +487,7 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
                 const uint32_t rows_mine = min(rows_per, kRows - r_first);
                 for (uint32_t idx = threadIdx.x; idx < rows_mine * kGroups; idx += kSoftmaxThreads) {
                     const uint32_t r = r_first + idx / kGroups, g = idx % kGroups;
-                    const uint32_t addr = smem_u32(&stage[r * kGroups + (g ^ (r & (kGroups - 1)))]);
+                    const uint32_t addr = smem_u32(&stage[r * kGroups + (g ^ (r & 15u))]);
                     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (uint32_t c = 0; c < S; ++c) {
                         const float4 v = ld_cluster_f4(mapa_u32(addr, c));
@@ -516,8 +518,13 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
     if (S > 1) cluster_sync_all();// no CTA leaves while another may still read its shared memory
     if (warp == 9) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, kTmemCols);
+        tmem_dealloc(tmem_base, tmem_cols(DHB));
     }
+}
+
+using FusedKernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const FusedParams);
+FusedKernel fused_kernel(uint32_t dhb) {
+    return dhb == 1 ? attn_fused_kernel<1> : dhb == 2 ? attn_fused_kernel<2> : dhb == 3 ? attn_fused_kernel<3> : attn_fused_kernel<4>;
 }
 
 // Shared memory of a CTA with `slots` ring tiles.
@@ -575,20 +582,27 @@ uint32_t attn_fused_splits(const AttnPrefillShape &s, int sm_count, int device_i
     fused_blocks(s, pack, tok, ctas);
     const uint64_t kv_tiles = (s.total + kKeys - 1) / kKeys;
     uint32_t splits = 1;
-    while (splits < kMaxSplits && ctas * splits * 2 <= 2ull * (uint64_t) sm_count && kv_tiles >= 8ull * splits) splits *= 2;
-    if (splits <= 2 || s.dh % 8 != 0 || s.dh > 128) return splits;
+    const uint32_t dhb = (s.dh + 63) / 64;
+    const uint64_t places = (uint64_t) sm_count * (dhb <= 2 ? 2 : 1);// CTAs that run at once
+    while (splits < kMaxSplits && ctas * splits * 2 <= places && kv_tiles >= 8ull * splits) splits *= 2;
+    if (splits <= 2 || s.dh % 8 != 0 || s.dh > 256) return splits;
     DeviceGuard guard(device_id);
     int sm_bytes = 0;
     if (cudaDeviceGetAttribute(&sm_bytes, cudaDevAttrMaxSharedMemoryPerMultiprocessor, device_id) != cudaSuccess) {
         cudaGetLastError();
         return splits;
     }
-    const uint32_t dhb = (s.dh + 63) / 64;
-    auto *kernel = dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
+    FusedKernel kernel = fused_kernel(dhb);
+    const uint32_t slots_alone = fused_slots(dhb, (size_t) sm_bytes - 1024), slots_shared = fused_slots(dhb, (size_t) sm_bytes / 2 - 1024);
+    // (the attribute is the most any launch of the kernel may ask for: never lower it for the query)
+    if (slots_alone == 0 ||
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fused_smem_bytes(dhb, slots_alone)) != cudaSuccess) {
+        cudaGetLastError();
+        return splits;
+    }
     for (uint32_t c = splits; c > splits / 2; --c) {
-        const bool alone = ctas * c <= (uint64_t) sm_count / 2;
-        const uint32_t slots = alone ? fused_slots(dhb, (size_t) sm_bytes - 1024) : fused_slots(dhb, (size_t) sm_bytes / 2 - 1024);
-        if (slots == 0) break;
+        const bool alone = slots_shared == 0 || ctas * c <= (uint64_t) sm_count / 2;
+        const uint32_t slots = alone ? slots_alone : slots_shared;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned) (ctas * c));
         cfg.blockDim = dim3(kFusedThreads);
@@ -598,8 +612,7 @@ uint32_t attn_fused_splits(const AttnPrefillShape &s, int sm_count, int device_i
         attr[0].val.clusterDim.x = c, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr, cfg.numAttrs = 1;
         int active = 0;
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) cfg.dynamicSmemBytes) != cudaSuccess ||
-            cudaOccupancyMaxActiveClusters(&active, kernel, &cfg) != cudaSuccess) {
+        if (cudaOccupancyMaxActiveClusters(&active, kernel, &cfg) != cudaSuccess) {
             cudaGetLastError();
             return splits;
         }
@@ -610,9 +623,9 @@ uint32_t attn_fused_splits(const AttnPrefillShape &s, int sm_count, int device_i
 
 AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s) {
     auto *h = reinterpret_cast<Handle *>(handle);
-    // head sizes that are whole 16-byte vectors, up to 128: the TMA boxes are 64 elements wide and read what lies
+    // head sizes that are whole 16-byte vectors, up to 256: the TMA boxes are 64 elements wide and read what lies
     // beyond the head size as zeros, which changes neither q k^T nor the first dh columns of P v
-    if (s.dh % 8 != 0 || s.dh == 0 || s.dh > 128) return nullptr;
+    if (s.dh % 8 != 0 || s.dh == 0 || s.dh > 256) return nullptr;
     if (s.seq == 0 || s.total < s.seq || s.group == 0 || s.nh % s.group != 0) return nullptr;
     // TMA: strides in bytes are multiples of 16 and positive, rows do not overlap
     for (int64_t st : {s.q_s0, s.q_s1, s.kc_s0, s.kc_s1, s.vc_s0, s.vc_s1}) {
@@ -638,11 +651,12 @@ AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &s)
     const uint32_t splits = attn_fused_splits(s, h->sm_count, h->device_id);
     // (clusters: only while half the SMs suffice.  A cluster must find all its SMs in one GPC, and 16 clusters of
     // 8 CTAs with an SM each did not fit the GPCs at once: 86 us against 47 us with two CTAs per SM)
-    const bool alone = blocks * splits <= (uint64_t) h->sm_count / (splits > 1 ? 2 : 1);
+    // (head sizes beyond 128 take all of an SM's tensor memory and most of its shared memory: always alone)
+    const bool alone = slots_shared == 0 || blocks * splits <= (uint64_t) h->sm_count / (splits > 1 ? 2 : 1);
     const uint32_t slots = alone ? slots_alone : slots_shared;
     if (slots == 0 || slots_alone == 0) return nullptr;
     const size_t smem = fused_smem_bytes(dhb, slots);
-    auto *kernel = dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
+    FusedKernel kernel = fused_kernel(dhb);
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fused_smem_bytes(dhb, slots_alone)) != cudaSuccess ||
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
         cudaGetLastError();
@@ -686,7 +700,7 @@ infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const vo
     p.alpha = (float) (1.0 / sqrt((double) s.dh));// `float qk_alpha = 1 / sqrt(head_dim)`, operator.cc:136
     p.out = reinterpret_cast<uint16_t *>(out);
     const uint32_t grid = f->tiles_m * (f->pack > 1 ? s.nh / s.group : s.nh) * f->splits;
-    auto *kernel = f->dhb == 1 ? attn_fused_kernel<1> : attn_fused_kernel<2>;
+    FusedKernel kernel = fused_kernel(f->dhb);
     if (f->splits == 1) {
         kernel<<<grid, kFusedThreads, f->smem_bytes, st>>>(mq, mk, mv, p);
     } else if (launch_cluster_smem(kernel, grid, kFusedThreads, f->splits, f->smem_bytes, st, mq, mk, mv, p) != cudaSuccess) {

@@ -18,7 +18,7 @@ infiniopStatus_t attn_prefill_run(AttnPrefill *p, void *workspace, void *out, co
                                   const void *v_cache, cudaStream_t stream);
 void attn_prefill_destroy(AttnPrefill *p);
 
-// The same computation in one kernel (attention_fused.cu): head sizes that are multiples of 8 up to 128, no workspace.  nullptr when the
+// The same computation in one kernel (attention_fused.cu): head sizes that are multiples of 8 up to 256, no workspace.  nullptr when the
 // shape or the strides do not fit it.
 struct AttnFused;
 AttnFused *attn_fused_create(infiniopHandle_t handle, const AttnPrefillShape &shape);

@@ -993,6 +993,9 @@ ATTENTION_CASES = [
     (12, 4, 48, 80, 200, 256, None, None),
     (4, 4, 150, 96, 30, 256, None, None),
     (8, 2, 40, 40, 1000, 1100, None, None),
+    # head sizes beyond 128: all of an SM's tensor memory, one CTA per SM; with and without a cluster
+    (4, 4, 140, 192, 20, 200, None, None),
+    (8, 2, 40, 256, 1500, 1600, None, None),
 ]
 
 
