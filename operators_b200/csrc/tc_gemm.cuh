@@ -31,6 +31,7 @@
 #endif
 
 #include <cuda.h>
+#include <type_traits>
 
 namespace b200 {
 namespace tc {
@@ -146,11 +147,28 @@ __device__ __forceinline__ bool work_item(const GemmParams &p, uint32_t cta, uin
 
 // The 16-bit storage type of D and of the intermediate the SwiGLU epilogue rounds through: fp16 with the reference's
 // truncating rule, or bf16 truncated likewise.
-__device__ __forceinline__ uint16_t to_store16(const GemmParams &p, float v) {
-    return p.bf16 ? f32_to_bf16_trunc(v) : f32_to_f16_ref(v);
+// (the type is decided once per 16 columns, so that the loops over the columns carry no branch)
+template<bool BF16>
+__device__ __forceinline__ uint16_t to_store16(float v) {
+    return BF16 ? f32_to_bf16_trunc(v) : f32_to_f16_ref(v);
 }
-__device__ __forceinline__ float load_store16(const GemmParams &p, uint16_t h) {
-    return p.bf16 ? __uint_as_float((uint32_t) h << 16) : f16_to_f32(h);
+template<bool BF16>
+__device__ __forceinline__ float load_store16(uint16_t h) {
+    return BF16 ? __uint_as_float((uint32_t) h << 16) : f16_to_f32(h);
+}
+// gate[j] = up[j] * silu(gate[j]) on values rounded through the storage type, as the reference stores x * w12 before
+// SwiGLU reads it back
+template<bool BF16>
+__device__ __forceinline__ void swiglu16_t(float *gate, const float *up) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float g = load_store16<BF16>(to_store16<BF16>(gate[j])), u = load_store16<BF16>(to_store16<BF16>(up[j]));
+        gate[j] = __fmul_rn(u, silu_f32(g));
+    }
+}
+__device__ __forceinline__ void swiglu16(const GemmParams &p, float *gate, const float *up) {
+    if (p.bf16) swiglu16_t<true>(gate, up);
+    else swiglu16_t<false>(gate, up);
 }
 
 // Final values of 16 consecutive columns of one lane, written to D.
@@ -159,14 +177,19 @@ __device__ __forceinline__ void store_cols16(const GemmParams &p, const float *a
     if (row >= mp) return;
     uint16_t *base = p.c + (int64_t) batch * p.c_batch_stride + (int64_t) row * p.c_lane_stride;
     uint16_t out[16];
+    auto convert = [&](auto bf16) {
+        constexpr bool kBf16 = decltype(bf16)::value;
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        float v = __fmul_rn(alpha, acc[j]);
-        if (beta != 0.f && col0 + j < np) {
-            v = __fadd_rn(__fmul_rn(beta, load_store16(p, base[(int64_t) (col0 + j) * p.c_col_stride])), v);
+        for (int j = 0; j < 16; ++j) {
+            float v = __fmul_rn(alpha, acc[j]);
+            if (beta != 0.f && col0 + j < np) {
+                v = __fadd_rn(__fmul_rn(beta, load_store16<kBf16>(base[(int64_t) (col0 + j) * p.c_col_stride])), v);
+            }
+            out[j] = to_store16<kBf16>(v);
         }
-        out[j] = to_store16(p, v);
-    }
+    };
+    if (p.bf16) convert(std::true_type{});
+    else convert(std::false_type{});
     if (p.c_col_stride == 1 && col0 + 16 <= np && ((reinterpret_cast<uintptr_t>(base + col0) & 15u) == 0)) {
         uint4 *dst = reinterpret_cast<uint4 *>(base + col0);
         const uint4 *src = reinterpret_cast<const uint4 *>(out);
@@ -191,12 +214,7 @@ __device__ __forceinline__ void finish_tile(const GemmParams &p, Load16 load16, 
             float gate[16], up[16];
             load16(c0, gate);
             load16(half + c0, up);
-            // the reference stores x * w12 as fp16 before SwiGLU reads it back
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float g = load_store16(p, to_store16(p, gate[j])), u = load_store16(p, to_store16(p, up[j]));
-                gate[j] = __fmul_rn(u, silu_f32(g));
-            }
+            swiglu16(p, gate, up);
             store_cols16(p, gate, row, tn * half + c0, b, p.mp, p.half_offset, 1.f, 0.f);
         }
     } else if (p.mode == kEpiSwiGLULanes) {
@@ -205,11 +223,7 @@ __device__ __forceinline__ void finish_tile(const GemmParams &p, Load16 load16, 
             float gate[16], up[16];
             load16(c0, gate);
             load16(p.bn + c0, up);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float g = load_store16(p, to_store16(p, gate[j])), u = load_store16(p, to_store16(p, up[j]));
-                gate[j] = __fmul_rn(u, silu_f32(g));
-            }
+            swiglu16(p, gate, up);
             store_cols16(p, gate, feature, tn * p.bn + c0, b, p.half_offset, p.np, 1.f, 0.f);// result rows = features
         }
     } else {
@@ -659,11 +673,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     float gate[16], up[16];
                     tmem_ld16(taddr + c0, gate);
                     tmem_ld16(taddr + 128 + c0, up);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float g = load_store16(p, to_store16(p, gate[j])), u = load_store16(p, to_store16(p, up[j]));
-                        gate[j] = __fmul_rn(u, silu_f32(g));
-                    }
+                    swiglu16(p, gate, up);
                     store_cols16(p, gate, row, tn * 128 + c0, b, p.mp, p.half_offset, 1.f, 0.f);
                 }
             } else {
