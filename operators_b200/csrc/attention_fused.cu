@@ -5,9 +5,9 @@
 // [n_q_head, seq, total] between its two matmuls; at 4096 x 4096 tokens that tensor (1 GB written, read, written
 // and read again) sets the pace, not the tensor cores.  Here a CTA owns 128 query rows of one q head and walks the
 // visible cached tokens in tiles of 64, twice:
-//   pass 1  S = q k^T on tcgen05.mma into tensor memory; the four softmax warps (one thread per query row = TMEM
-//           lane) read S, apply the reference's two roundings' first half (alpha * s rounded to fp16 like the score
-//           tensor) and keep the row's running maximum and sum of exponentials;
+//   pass 1  S = q k^T on tcgen05.mma into tensor memory; the softmax warps (two threads per query row = TMEM lane)
+//           read S, round alpha * s to fp16 as the reference's score tensor holds it, and keep the row's running
+//           maximum and sum of exponentials;
 //   pass 2  S again (the tensor pipe has time to spare: the exponentials bound the kernel), the probability
 //           exp(s - max) / sum truncated to fp16 exactly as the causal softmax stores it, written as the K-major A
 //           operand into 128-byte-swizzled shared memory, and O += P v on tcgen05.mma with v read as an MN-major B
@@ -28,11 +28,13 @@
 // Calls of fewer than 128 tokens with several q heads per kv head: a block holds 128 / group tokens of all q heads
 // of one kv head (row = token * group + head), loaded by one TMA box [tokens][heads][64], so the block is full and k
 // and v are loaded once per kv head.
-// Few blocks of query rows over many cached tokens (a chunk of a prompt, speculative drafts): 2, 4 or 8 CTAs, one
+// Head sizes: multiples of 8 up to 256; the 64-element boxes read what lies beyond the head size as zeros (DHB boxes;
+// beyond 128 a CTA takes all 512 TMEM columns and an SM to itself).
+// Few blocks of query rows over many cached tokens (a chunk of a prompt, speculative drafts): up to 8 CTAs, one
 // thread-block cluster, share a block and each takes a range of its tiles.  After pass 1 they exchange their rows'
 // maximum and sum over distributed shared memory (one mbarrier per CTA that every CTA of the cluster arrives on; the
 // waits acquire at cluster scope), after pass 2 each parks its fp32 partial of O in its shared memory and CTA r
-// adds rows [r * 128 / S, ...) of all partials in rank order, truncates and stores them.  A CTA whose range is empty
+// adds its share of the rows of all partials in rank order, truncates and stores them.  A CTA whose range is empty
 // (the first rows of a prompt see fewer tiles than the cluster has CTAs) contributes -inf, 0 and zeros.
 // Every mbarrier wait is bounded (tc_ptx.cuh); a role that gives up raises the CTA's abort flag, all roles leave,
 // copies in flight are awaited (bounded), TMEM is freed, and infiniopExtDeviceTimeouts reports it.
