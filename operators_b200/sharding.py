@@ -110,7 +110,7 @@ class PeerBlocks:
             local_blocks.append(self)
             self._local_blocks, self.bases = local_blocks, None
         else:
-            # Every rank takes part in both exchanges whatever happened to it, and all ranks reach the same verdict:
+            # Every rank takes part in both exchanges whatever happened to it, and all ranks come to the same decision:
             # either every block is allocated and opened everywhere, or every rank frees what it has and raises.
             self._local_blocks = None
             handles = [bytes(ipc) if status == 0 else None]
@@ -132,11 +132,11 @@ class PeerBlocks:
                         break
                 self._opened.append(int(other.value))
                 self.bases.append(int(other.value))
-            verdicts = [opened_all]
+            decisions = [opened_all]
             if self.world > 1:
-                verdicts = [None] * self.world
-                dist.all_gather_object(verdicts, opened_all, group=group)
-            if not all(verdicts):
+                decisions = [None] * self.world
+                dist.all_gather_object(decisions, opened_all, group=group)
+            if not all(decisions):
                 self.results = self.logits = self.flags = None
                 self.destroy()
                 raise RuntimeError("peer memory blocks could not be allocated and opened on every rank")
@@ -249,7 +249,7 @@ class VocabShardedSampler:
 
     def _auto_peer_setup(self, rows, device):
         """First exact call of an "auto" sampler with real ranks (and any later call with more rows): try to share
-        blocks over CUDA IPC; every rank reaches the same verdict (PeerBlocks), so either all switch to peer memory
+        blocks over CUDA IPC; every rank comes to the same decision (PeerBlocks), so either all switch to peer memory
         or all keep the collective exchange."""
         if self.peer is not None and self._own_peer and rows > self.peer.max_rows:
             self._drop_own_peer()
