@@ -1388,6 +1388,44 @@ def test_peer_memory_wait_runs_out_when_a_rank_never_shows_up(cuda_lib, one_laun
             pb.destroy()
 
 
+def test_random_sample_batch_peer_status_codes(cuda_lib):
+    """The one-launch form states its conditions as status codes (the caller then takes the three launches): no
+    rows, the greedy branch, shards that are not whole 16-byte vectors, shards that do not add up to the row."""
+    import ctypes
+
+    from operators_b200.sharding import PeerBlocks
+
+    lib, handle = cuda_lib
+    rows, voc = 4, 4096
+    blocks = []
+    pb = PeerBlocks(lib, handle, rows, voc, 1, 0, DEV, local_blocks=blocks)
+    op = ops.RandomSampleOp(lib, handle, pb.results[:1], pb.logits[0])
+    u = torch.rand(rows, device=DEV)
+    one = lambda v: (ctypes.c_void_p * 1)(v)  # noqa: E731
+    shards, flags, res = one(pb.ptr + pb.logits_off), one(pb.ptr), one(pb.ptr + pb.results_off)
+    strides = (ctypes.c_int64 * 1)(voc)
+
+    def call(nrows=rows, cols=voc, topp=0.9, topk=50, temp=0.8, stride=None):
+        st = strides if stride is None else (ctypes.c_int64 * 1)(stride)
+        return lib.infiniopRandomSampleBatchPeer(op.desc, res, shards, st, cols, flags, 1, 0, 0, nrows, u.data_ptr(), topp, topk,
+                                                 temp, None)
+
+    try:
+        assert call() == 0
+        torch.cuda.synchronize()
+        bad_param = 2  # STATUS_BAD_PARAM
+        assert call(nrows=0) == bad_param
+        assert call(topp=0.0) == bad_param and call(topk=1) == bad_param and call(temp=0.0) == bad_param
+        assert call(cols=voc - 8) == bad_param      # shards do not add up to the descriptor's row
+        assert call(stride=voc + 4) == bad_param    # rows that do not start on 16-byte boundaries
+        assert lib.infiniopRandomSampleBatchPeer(op.desc, res, shards, strides, voc, flags, 17, 0, 0, rows, u.data_ptr(), 0.9, 50,
+                                                 0.8, None) == bad_param
+    finally:
+        torch.cuda.synchronize()
+        op.destroy()
+        pb.destroy()
+
+
 def test_vocab_sharded_sampling_over_peer_memory_two_gpus():
     """Two real ranks on two GPUs: CUDA IPC blocks, the flag protocol, three rounds, indices against the unsharded
     sampler; tests/peer_ranks.py is the program both ranks run."""
