@@ -116,6 +116,9 @@ __device__ __forceinline__ void unpack8(uint4 v, float (&f)[8]) {
 // last kernel finds the CTA that arrives last.
 template<bool VEC>
 __global__ void __launch_bounds__(kThreads) kv_append_kernel(AttnArgs a, uint32_t n_counters) {
+    // a kernel launched behind this one as a programmatic dependent (the one-kernel attention form) may set itself
+    // up meanwhile; it waits (griddepcontrol.wait) before it reads the caches
+    asm volatile("griddepcontrol.launch_dependents;");
     if (blockIdx.x == 0) {
         for (uint32_t i = threadIdx.x; i < n_counters; i += kThreads) a.counters[i] = 0;
     }

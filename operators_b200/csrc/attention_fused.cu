@@ -204,6 +204,8 @@ __global__ void __launch_bounds__(kFusedThreads, 2)
                 if (p.pack > 1) tma_load_3d(sq + kb * (kRows * 128u), &map_q, &bars[kQFull], kb * 64, (int32_t) h0, (int32_t) tok0);
                 else tma_load_3d(sq + kb * (kRows * 128u), &map_q, &bars[kQFull], kb * 64, (int32_t) tok0, (int32_t) h0);
             }
+            // the caches are complete once the append kernel ahead of this one has finished (q does not depend on it)
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             // The ring is a queue: tiles are loaded in the order in which the MMA lane uses them.  Pass 1: k(0) ..
             // k(T - 1); pass 2: k(0), k(1), then k(j + 2), v(j) for j = 0 .. T - 1.
             uint32_t slot = 0, ph = 0;
@@ -703,9 +705,21 @@ infiniopStatus_t attn_fused_run(AttnFused *f, void *out, const void *q, const vo
     p.out = reinterpret_cast<uint16_t *>(out);
     const uint32_t grid = f->tiles_m * (f->pack > 1 ? s.nh / s.group : s.nh) * f->splits;
     FusedKernel kernel = fused_kernel(f->dhb);
-    if (f->splits == 1) {
-        kernel<<<grid, kFusedThreads, f->smem_bytes, st>>>(mq, mk, mv, p);
-    } else if (launch_cluster_smem(kernel, grid, kFusedThreads, f->splits, f->smem_bytes, st, mq, mk, mv, p) != cudaSuccess) {
+    // Programmatic dependent launch behind the cache append: the CTAs take their places, set up barriers and tensor
+    // memory and load q while the append still runs; the loading lane waits for it before the first k tile.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kFusedThreads);
+    cfg.dynamicSmemBytes = f->smem_bytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = f->splits, attr[1].val.clusterDim.y = 1, attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = f->splits > 1 ? 2 : 1;
+    if (cudaLaunchKernelEx(&cfg, kernel, mq, mk, mv, p) != cudaSuccess) {
         cudaGetLastError();
         return STATUS_EXECUTION_FAILED;
     }
