@@ -173,7 +173,9 @@ class VocabShardedSampler:
     travel (`exchange`): "auto" shares one block per rank over CUDA IPC at the first call and lets the sampling
     kernel itself read the peers' shards and store the indices to every rank (PeerBlocks; one launch, no
     collective); where the blocks cannot be shared on every rank it uses "all_gather" (from four ranks with equal
-    shards) or "all_to_all", one NCCL collective in and one all-gather of 8 bytes per row out.
+    shards) or "all_to_all", one NCCL collective in and one all-gather of 8 bytes per row out.  The set-up allocates
+    and exchanges handles, so the first call (and the first with more rows than any before) belongs outside stream
+    capture; later calls launch kernels only.
 
     mode "fast": a local candidate kernel on every rank, ONE all-gather of ~1 KB per row per rank, a finishing
     kernel.  Top-k set, tie order and numerators are the reference's; the denominator is the correctly rounded
