@@ -530,6 +530,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_scores_mma_kernel(AttnA
     const uint32_t pitch = a.chunk + 1;
     const Work<RT> w(a);
     asm volatile("griddepcontrol.launch_dependents;");// the second kernel's CTAs may queue up behind this one's
+    // behind a cache append (several new tokens) this kernel is itself launched as a programmatic dependent: its CTAs
+    // are in place when the append ends; without one the wait returns at once
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     append_one_token<true>(a, w.h, w.tile, w.split);
     if (tid < 8) row_limit[tid] = tid < RT ? w.limit(a, w.tile * RT + tid) : -1;
 
@@ -713,7 +716,24 @@ infiniopStatus_t launch_mma(const AttnDesc *d, const AttnArgs &args, cudaStream_
         configured_dev = d->device_id;
     }
     const dim3 grid(d->splits, d->nkvh, d->row_tiles);
-    attention_scores_mma_kernel<RT, NB><<<grid, kThreads, smem_scores, st>>>(args);
+    if (args.append_here) {
+        attention_scores_mma_kernel<RT, NB><<<grid, kThreads, smem_scores, st>>>(args);
+    } else {// the append kernel runs ahead of this one
+        cudaLaunchConfig_t first = {};
+        first.gridDim = grid;
+        first.blockDim = dim3(kThreads);
+        first.dynamicSmemBytes = smem_scores;
+        first.stream = st;
+        cudaLaunchAttribute dep[1];
+        dep[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        dep[0].val.programmaticStreamSerializationAllowed = 1;
+        first.attrs = dep;
+        first.numAttrs = 1;
+        if (cudaLaunchKernelEx(&first, attention_scores_mma_kernel<RT, NB>, args) != cudaSuccess) {
+            cudaGetLastError();
+            return STATUS_EXECUTION_FAILED;
+        }
+    }
     const infiniopStatus_t status = check_launch("attention scores");
     if (status != STATUS_SUCCESS) return status;
     // Programmatic dependent launch: the CTAs of the second kernel may take their places while the last CTAs of the
